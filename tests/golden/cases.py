@@ -1,0 +1,98 @@
+"""Seeded case definitions shared by the fixture generator and the tests."""
+from __future__ import annotations
+
+import dataclasses
+import math
+
+import torch
+
+from nanokv_b200 import synthetic
+from nanokv_b200.synthetic import Shape
+
+
+@dataclasses.dataclass(frozen=True)
+class CodecCase:
+    name: str
+    shape: Shape
+    segments: tuple[int, ...]   # tokens per encoded segment
+    layer: int = 0
+    iters: int = 2
+    seed: int = 0
+    mean_std: float = 0.0
+    attn_stride: int = 1        # query rows stored in the fixture
+
+
+@dataclasses.dataclass(frozen=True)
+class FastCase:
+    name: str
+    codec: CodecCase
+    low_segments: int                       # leading segments read through readers
+    groups: tuple[tuple[tuple[int, ...], int], ...]
+
+
+C1 = CodecCase("c1_roundtrip_f32", synthetic.CONFIGS["c1_roundtrip_f32"], (2048,),
+               attn_stride=4)
+MINI_F32 = CodecCase(
+    "mini_mg_f32", Shape("mini_f32", 2, 128, 64, 8, 512, 70, "f32"), (300, 212),
+    layer=5, seed=11, mean_std=0.05)
+MINI_BF16 = CodecCase(
+    "mini_mg_bf16", Shape("mini_bf16", 2, 128, 64, 8, 512, 70, "bf16"), (300, 212),
+    layer=3, seed=7, mean_std=0.05)
+MINI_LB = CodecCase(
+    "mini_lb_bf16", Shape("mini_lb", 2, 128, 64, 8, 300, 70, "bf16"), (300,),
+    layer=1, seed=5, mean_std=0.05)
+
+MG_CASES = (C1, MINI_F32, MINI_BF16)
+LINGBOT_CASES = (MINI_LB,)
+
+_FAST_SHAPE_F32 = Shape("fast_f32", 4, 128, 64, 8, 640, 70, "f32")
+_FAST_SHAPE_BF16 = Shape("fast_bf16", 4, 128, 64, 8, 640, 70, "bf16")
+FAST_CASES = (
+    FastCase("fast_mini_f32",
+             CodecCase("fast_mini_f32", _FAST_SHAPE_F32, (256, 256, 128), layer=2, seed=21,
+                       mean_std=0.05),
+             2, (((0, 2), 32), ((1, 3), 128))),
+    FastCase("fast_mini_bf16",
+             CodecCase("fast_mini_bf16", _FAST_SHAPE_BF16, (256, 256, 128), layer=2, seed=23,
+                       mean_std=0.05),
+             2, (((0, 2), 32), ((1, 3), 128))),
+)
+
+
+def build(case: CodecCase) -> dict:
+    """All inputs of a codec case, deterministically from its seed."""
+    shape = case.shape
+    gen = synthetic.generator(case.seed)
+    dtype = shape.torch_dtype
+    out = {}
+    for kind in ("k", "v"):
+        centers = synthetic.make_centers(shape, gen)
+        out[f"{kind}_true_centers"] = centers
+        out[f"{kind}_chunks"] = [synthetic.make_rows(n, centers, gen, dtype=dtype)
+                                 for n in case.segments]
+        out[f"{kind}_op"] = synthetic.make_operator(shape, gen, mean_std=case.mean_std)
+    out["q"] = synthetic.make_queries(shape, gen)
+    return out
+
+
+def build_reader(case: FastCase, data: dict) -> dict:
+    gen = synthetic.generator(case.codec.seed + 1000)
+    groups = [(list(heads), width) for heads, width in case.groups]
+    return synthetic.make_reader(case.codec.shape, gen, groups,
+                                 k_decoder=data["k_op"]["decoder"],
+                                 v_decoder=data["v_op"]["decoder"])
+
+
+def build_merge():
+    """Two partitions with every -inf combination among the rows."""
+    gen = synthetic.generator(99)
+    out_a = torch.randn(1, 3, 16, 128, generator=gen).to(torch.bfloat16)
+    out_b = torch.randn(1, 3, 16, 128, generator=gen).to(torch.bfloat16)
+    lse_a = 3.0 * torch.randn(1, 3, 16, generator=gen)
+    lse_b = 3.0 * torch.randn(1, 3, 16, generator=gen)
+    lse_a[0, 0, :4] = -math.inf
+    lse_b[0, 0, 2:6] = -math.inf
+    lse_b[0, 1, 0] = lse_a[0, 1, 0]
+    out_a[0, 0, :4] = 0
+    out_b[0, 0, 2:6] = 0
+    return out_a, lse_a, out_b, lse_b

@@ -1,0 +1,177 @@
+"""Generate the golden fixtures by running the UNMODIFIED reference on CPU.
+
+    python tests/golden/make_golden.py [--reference /path/to/NanoKV]
+
+Needs a checkout of the reference project (it is imported, never copied).
+Inputs are regenerated from seeds by ``tests/golden/cases.py``; only the
+reference's outputs (and a digest of each input, to detect generator drift)
+are stored, as compressed ``.npz`` files next to this script.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parent.parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(HERE))
+
+import cases  # noqa: E402
+from nanokv_b200.synthetic import checksum  # noqa: E402
+from oracle import ref_import  # noqa: E402
+
+
+def bits(tensor: torch.Tensor) -> np.ndarray:
+    """Store 16-bit floats as their bit patterns (numpy has no bf16)."""
+    tensor = tensor.detach().contiguous()
+    if tensor.dtype in (torch.bfloat16, torch.float16):
+        return tensor.view(torch.int16).numpy()
+    return tensor.numpy()
+
+
+def save(name: str, arrays: dict) -> None:
+    arrays["torch_version"] = np.frombuffer(torch.__version__.encode(), dtype=np.uint8)
+    np.savez_compressed(HERE / f"{name}.npz", **arrays)
+    size = (HERE / f"{name}.npz").stat().st_size
+    print(f"wrote {name}.npz ({size / 1024:.0f} KiB)")
+
+
+def mg_segment_arrays(prefix: str, payload: dict, out: dict) -> None:
+    out[f"{prefix}_ids"] = payload["ids"].numpy()
+    out[f"{prefix}_packed"] = payload["packed_codes"].numpy()
+    out[f"{prefix}_scale"] = bits(payload["scale"])
+    out[f"{prefix}_centers"] = bits(payload["centers"])
+
+
+def run_mg_case(case: cases.CodecCase, root) -> dict:
+    """encode_tensor / decode_value / attention_lse of the Matrix-Game modules."""
+    codec = ref_import.load_mg_codec(root)
+    core = ref_import.load_mg_core(root)
+    os.environ["MG35_KVCODEC_C64_CLUSTERS"] = str(case.shape.centers)
+    os.environ["MG35_KVCODEC_C64_ITERS"] = str(case.iters)
+    data = cases.build(case)
+    out = {}
+    for kind in ("k", "v"):
+        op = data[f"{kind}_op"]
+        ref_import.inject_mg_operator(codec, kind, case.layer, mean=op["mean"],
+                                      encoder=op["encoder"], decoder=op["decoder"])
+        out[f"{kind}_input_digest"] = np.array([checksum(t) for t in data[f"{kind}_chunks"]],
+                                               dtype=np.uint64)
+    containers = {}
+    for kind in ("k", "v"):
+        container = None
+        for index, chunk in enumerate(data[f"{kind}_chunks"]):
+            payload = codec.encode_tensor(kind, case.layer, chunk[None])
+            mg_segment_arrays(f"{kind}{index}", payload, out)
+            container = codec.concat_values(container, payload)
+        containers[kind] = container
+    dtype = case.shape.torch_dtype
+    key, value = codec.decode_pair_values(containers["k"], containers["v"], dtype=dtype,
+                                          device=torch.device("cpu"))
+    out["k_decoded_head"] = bits(key[0, :64])
+    out["v_decoded_head"] = bits(value[0, :64])
+    out["k_decoded_digest"] = np.array([checksum(key)], dtype=np.uint64)
+    out["v_decoded_digest"] = np.array([checksum(value)], dtype=np.uint64)
+    heads, dim = case.shape.heads, case.shape.head_dim
+    q = data["q"][None].permute(0, 2, 1, 3).contiguous()
+    kk = key.reshape(1, -1, heads, dim).permute(0, 2, 1, 3)
+    vv = value.reshape(1, -1, heads, dim).permute(0, 2, 1, 3)
+    attn, lse = core.attention_lse(q, kk, vv)
+    out["q_digest"] = np.array([checksum(data["q"])], dtype=np.uint64)
+    out["attn_rows"] = bits(attn[0, :, ::case.attn_stride])
+    out["attn_digest"] = np.array([checksum(attn)], dtype=np.uint64)
+    out["lse"] = lse[0].numpy()
+    return out
+
+
+def run_lingbot_case(case: cases.CodecCase, root) -> dict:
+    """encode_tensor / decode_tensor of the LingBot module (always bf16 operators)."""
+    codec = ref_import.load_lingbot_codec(root)
+    data = cases.build(case)
+    heads, dim = case.shape.heads, case.shape.head_dim
+    out = {}
+    for kind in ("k", "v"):
+        op = data[f"{kind}_op"]
+        ref_import.inject_lingbot_operator(
+            codec, "synthetic", kind, case.layer, joint_dim=case.shape.joint,
+            rank=case.shape.rank, mean=op["mean"], encoder=op["encoder"], decoder=op["decoder"])
+        chunk = data[f"{kind}_chunks"][0]
+        payload = codec.encode_tensor(
+            chunk.reshape(1, -1, heads, dim), target=kind, layer=case.layer, sp_rank=0,
+            basis_root="synthetic", rank=case.shape.rank, clusters=case.shape.centers,
+            iters=case.iters)
+        out[f"{kind}_input_digest"] = np.array([checksum(chunk)], dtype=np.uint64)
+        out[f"{kind}0_ids"] = payload["ids"].numpy()
+        out[f"{kind}0_packed"] = payload["latent_packed"].numpy()
+        out[f"{kind}0_scale"] = bits(payload["latent_scale"])
+        out[f"{kind}0_centers"] = bits(payload["centers"])
+        decoded = codec.decode_tensor(payload, dtype=torch.bfloat16, device=torch.device("cpu"))
+        out[f"{kind}_decoded"] = bits(decoded.reshape(-1, case.shape.joint))
+    return out
+
+
+def run_fast_case(case: cases.FastCase, root) -> dict:
+    """hybrid_attention of codec_native/core.py over MG payloads."""
+    codec = ref_import.load_mg_codec(root)
+    core = ref_import.load_mg_core(root)
+    os.environ["MG35_KVCODEC_C64_CLUSTERS"] = str(case.codec.shape.centers)
+    os.environ["MG35_KVCODEC_C64_ITERS"] = str(case.codec.iters)
+    data = cases.build(case.codec)
+    shape = case.codec.shape
+    heads, dim, dtype = shape.heads, shape.head_dim, shape.torch_dtype
+    for kind in ("k", "v"):
+        op = data[f"{kind}_op"]
+        ref_import.inject_mg_operator(codec, kind, case.codec.layer, mean=op["mean"],
+                                      encoder=op["encoder"], decoder=op["decoder"])
+    payloads = {kind: [codec.encode_tensor(kind, case.codec.layer, chunk[None])
+                       for chunk in data[f"{kind}_chunks"]] for kind in ("k", "v")}
+    device = torch.device("cpu")
+    low_k = {"codec": "worldplay_segments_v1", "segments": payloads["k"][:case.low_segments]}
+    low_v = {"codec": "worldplay_segments_v1", "segments": payloads["v"][:case.low_segments]}
+    low = codec.direct_latent_pair_segments(low_k, low_v, device=device)
+    native = []
+    for pk, pv in zip(payloads["k"][case.low_segments:], payloads["v"][case.low_segments:]):
+        key = codec.decode_tensor(pk, dtype=dtype, device=device)
+        value = codec.decode_tensor(pv, dtype=dtype, device=device)
+        native.append((key.reshape(1, -1, heads, dim).permute(0, 2, 1, 3),
+                       value.reshape(1, -1, heads, dim).permute(0, 2, 1, 3), None))
+    reader_payload = cases.build_reader(case, data)
+    reader = core.ReaderLayer(reader_payload)
+    q = data["q"][None].permute(0, 2, 1, 3).contiguous()
+    result = core.hybrid_attention(
+        q, q, native, low, reader,
+        query_position=lambda value, group: value,
+        kv_position=lambda kk, vv, segment, group: (kk, vv))
+    return {"hybrid": bits(result[0]), "q_digest": np.array([checksum(data["q"])], dtype=np.uint64)}
+
+
+def run_merge_case(root) -> dict:
+    core = ref_import.load_mg_core(root)
+    out_a, lse_a, out_b, lse_b = cases.build_merge()
+    out, lse = core.merge(out_a, lse_a, out_b, lse_b)
+    return {"out": bits(out), "lse": lse.numpy()}
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--reference", default=None)
+    args = parser.parse_args()
+    root = ref_import.reference_root(args.reference)
+    torch.set_num_threads(1)  # one thread: bit-stable reductions in the stored outputs
+    for case in cases.MG_CASES:
+        save(case.name, run_mg_case(case, root))
+    for case in cases.LINGBOT_CASES:
+        save(case.name, run_lingbot_case(case, root))
+    for case in cases.FAST_CASES:
+        save(case.name, run_fast_case(case, root))
+    save("merge_edge", run_merge_case(root))
+
+
+if __name__ == "__main__":
+    main()

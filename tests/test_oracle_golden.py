@@ -1,0 +1,138 @@
+"""The CPU oracle against outputs of the unmodified reference (tests/golden/*.npz)."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from nanokv_b200.synthetic import checksum
+from oracle import nkv_oracle as oracle
+
+GOLDEN = Path(__file__).parent / "golden"
+
+
+def load(name):
+    return np.load(GOLDEN / f"{name}.npz")
+
+
+def from_bits(array, dtype):
+    tensor = torch.from_numpy(np.ascontiguousarray(array))
+    return tensor.view(dtype) if dtype in (torch.bfloat16, torch.float16) else tensor
+
+
+def encode_all(case, data, *, lingbot=False):
+    """Oracle encode of every segment with the reference flavour's parameters."""
+    segments = {"k": [], "v": []}
+    for kind in ("k", "v"):
+        op = data[f"{kind}_op"]
+        for chunk in data[f"{kind}_chunks"]:
+            if lingbot:
+                seed = 20260826 + case.layer * 17 + (kind == "v")
+                flavour = dict(eps=1e-12, in_coeff_dtype=False)
+            else:
+                seed = 20260804 + case.layer
+                flavour = dict(eps=oracle.F32_EPS, in_coeff_dtype=True)
+            segments[kind].append(oracle.encode_rows(
+                chunk[None], encoder=op["encoder"], mean=op["mean"],
+                clusters=case.shape.centers, iters=case.iters, seed=seed, **flavour))
+    return segments
+
+
+def check_segments(gold, segments):
+    for kind in ("k", "v"):
+        for index, seg in enumerate(segments[kind]):
+            assert np.array_equal(gold[f"{kind}{index}_ids"].reshape(-1),
+                                  seg["ids"].reshape(-1).numpy()), "centre ids"
+            assert np.array_equal(gold[f"{kind}{index}_packed"], seg["packed"].numpy()), "codes"
+            assert np.array_equal(gold[f"{kind}{index}_scale"].reshape(-1),
+                                  seg["scale"].view(torch.int16).reshape(-1).numpy()), "scales"
+            assert np.array_equal(gold[f"{kind}{index}_centers"],
+                                  seg["centers"].view(torch.int16).numpy()), "centres"
+
+
+@pytest.mark.parametrize("case", cases.MG_CASES, ids=lambda c: c.name)
+def test_mg_codec_and_attention(case):
+    torch.set_num_threads(1)
+    gold = load(case.name)
+    data = cases.build(case)
+    for kind in ("k", "v"):
+        digests = [checksum(t) for t in data[f"{kind}_chunks"]]
+        assert digests == list(gold[f"{kind}_input_digest"]), "seeded inputs drifted"
+    segments = encode_all(case, data)
+    check_segments(gold, segments)
+    dtype = case.shape.torch_dtype
+    heads = case.shape.heads
+    k_op, v_op = data["k_op"], data["v_op"]
+    for kind, op in (("k", k_op), ("v", v_op)):
+        decoded = torch.cat([oracle.decode_rows(s, decoder=op["decoder"], mean=op["mean"],
+                                                dtype=dtype) for s in segments[kind]], 1)
+        assert checksum(decoded) == int(gold[f"{kind}_decoded_digest"][0]), "decoded rows"
+    out, lse = oracle.codec_attention(
+        data["q"][None], segments["k"], segments["v"], k_decoder=k_op["decoder"],
+        k_mean=k_op["mean"], v_decoder=v_op["decoder"], v_mean=v_op["mean"], heads=heads,
+        dtype=dtype)
+    out_bhqd = out.permute(0, 2, 1, 3).contiguous()
+    assert checksum(out_bhqd) == int(gold["attn_digest"][0]), "attention output"
+    assert np.array_equal(gold["lse"], lse[0].numpy())
+
+
+@pytest.mark.parametrize("case", cases.LINGBOT_CASES, ids=lambda c: c.name)
+def test_lingbot_codec(case):
+    torch.set_num_threads(1)
+    gold = load(case.name)
+    data = cases.build(case)
+    segments = encode_all(case, data, lingbot=True)
+    check_segments(gold, segments)
+    for kind in ("k", "v"):
+        op = data[f"{kind}_op"]
+        decoded = oracle.decode_rows(segments[kind][0], decoder=op["decoder"], mean=op["mean"],
+                                     dtype=torch.bfloat16)
+        assert np.array_equal(gold[f"{kind}_decoded"],
+                              decoded.reshape(-1, case.shape.joint).view(torch.int16).numpy())
+
+
+@pytest.mark.parametrize("case", cases.FAST_CASES, ids=lambda c: c.name)
+def test_hybrid_attention(case):
+    torch.set_num_threads(1)
+    gold = load(case.name)
+    data = cases.build(case.codec)
+    shape = case.codec.shape
+    dtype = shape.torch_dtype
+    segments = encode_all(case.codec, data)
+    low, native = [], []
+    for index in range(len(case.codec.segments)):
+        seg_k, seg_v = segments["k"][index], segments["v"][index]
+        if index < case.low_segments:
+            entry = {}
+            for kind, seg in (("k", seg_k), ("v", seg_v)):
+                latent = oracle.dequantize_rows(seg["codes"], seg["scale"])[None]
+                entry[kind] = (latent, seg["centers"].float(), seg["ids"].long(),
+                               data[f"{kind}_op"]["mean"])
+            low.append(entry)
+        else:
+            pair = []
+            for kind, seg in (("k", seg_k), ("v", seg_v)):
+                op = data[f"{kind}_op"]
+                rows = oracle.decode_rows(seg, decoder=op["decoder"], mean=op["mean"], dtype=dtype)
+                pair.append(rows.reshape(1, -1, shape.heads, shape.head_dim).permute(0, 2, 1, 3))
+            native.append(tuple(pair))
+    reader = cases.build_reader(case, data)
+    q = data["q"][None].permute(0, 2, 1, 3).contiguous()
+    result = oracle.hybrid_attention(q, q, native, low, reader)
+    want = from_bits(gold["hybrid"], dtype)
+    assert torch.equal(result[0], want)
+
+
+def test_merge_edge_cases():
+    gold = load("merge_edge")
+    out, lse = oracle.merge(*cases.build_merge())
+    assert np.array_equal(gold["out"], out.view(torch.int16).numpy())
+    assert np.array_equal(gold["lse"], lse.numpy(), equal_nan=True)
+
+
+def test_pack_roundtrip_and_nibble_order():
+    codes = torch.tensor([[-7, 7, 0, 3], [1, -1, 6, -6]], dtype=torch.int8)
+    packed, count = oracle.pack_int4(codes)
+    assert packed.tolist() == [0 | (14 << 4), 7 | (10 << 4), 8 | (6 << 4), 13 | (1 << 4)]
+    assert torch.equal(oracle.unpack_int4(packed, count, codes.shape), codes)
