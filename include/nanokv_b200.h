@@ -1,0 +1,218 @@
+/*
+ * nanokv_b200 -- C ABI of the B200 (sm_100a) compressed-KV hot path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (a cudaStream_t passed as void*), enqueues its kernels on that stream and
+ * returns NKV_OK or a negative status; nothing here allocates device memory,
+ * synchronises the device, or traps.  nkv_last_error() gives the detail text
+ * of the calling thread's last failure.
+ *
+ * "Reference" citations name the function of the NanoKV project that each
+ * entry point replaces, by path inside that project:
+ *   MGM/ = models/Matrix-Game-3.5/fast/diffsynth/models/
+ *   MGC/ = models/Matrix-Game-3.5/fast/codec_native/
+ *   LB/  = models/LingBot-World-2.0/fast/wan/modules/
+ *   HY/  = models/HY-WorldPlay/fast/hyvideo/models/transformers/modules/
+ *
+ * Symbols: J = heads * head_dim (joint width), r = rank, C = centres of one
+ * segment, G = quantisation group (G == r is the reference's per-token scale),
+ * S = tokens encoded by a call, N = history tokens read, Q = query tokens.
+ */
+#ifndef NANOKV_B200_H
+#define NANOKV_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NKV_ABI_VERSION 1
+
+/* status codes */
+#define NKV_OK               0
+#define NKV_ERR_INVALID     (-1)  /* bad shape / argument          -> ValueError   */
+#define NKV_ERR_CUDA        (-2)  /* CUDA runtime reported an error -> RuntimeError */
+#define NKV_ERR_UNSUPPORTED (-3)  /* shape outside the built kernels -> RuntimeError */
+#define NKV_ERR_DEVICE_WAIT (-4)  /* a bounded device-side wait gave up             */
+#define NKV_ERR_TOO_LARGE   (-5)  /* exceeds a stated fixed capacity                */
+
+/* element types */
+#define NKV_F32  0
+#define NKV_BF16 1
+#define NKV_F16  2
+
+/* quantiser arithmetic (nkv_quant_pack / nkv_encode_append) */
+#define NKV_QUANT_F32      0  /* upcast to fp32 first: LB/lingbot_v2_kv_codec.py:285-287, HY/kv_codecs.py:237-255 */
+#define NKV_QUANT_IN_BF16  1  /* amax, /7 and z/scale rounded to bf16: MGM/nanokv_codec.py:349-350 with a bf16 operator */
+
+const char* nkv_status_string(int status);
+const char* nkv_last_error(void);
+int nkv_version(void);
+
+/*
+ * One compressed history tensor (K or V of one layer), struct-of-arrays in
+ * HBM.  Token t belongs to segment s with seg_start[s] <= t < seg_start[s+1];
+ * its centre is row seg_center_row[s] + ids[t] of `centers`.
+ * Reference payloads: MGM/nanokv_codec.py:352-365 (packed_codes, scale,
+ * centers, ids per segment; segments concatenated by concat_values :600-609),
+ * LB/lingbot_v2_kv_codec.py:288-297.
+ */
+typedef struct nkv_history {
+  const uint8_t* codes;          /* [tokens, rank/2]  two INT4 per byte, even index in the low nibble */
+  const void*    scales;         /* [tokens, rank/group]  bf16 or fp16 */
+  const void*    ids;            /* [tokens]  uint8 or uint16 centre id inside the token's segment */
+  const void*    centers;        /* [center_rows, center_width]  bf16, all segments' tables stacked */
+  const int32_t* seg_start;      /* [segments + 1] device array of token offsets */
+  const int32_t* seg_center_row; /* [segments]     device array of first centre row per segment */
+  int32_t tokens;
+  int32_t segments;
+  int32_t rank;
+  int32_t group;
+  int32_t scale_dtype;           /* NKV_BF16 | NKV_F16 */
+  int32_t id_bytes;              /* 1 | 2 */
+  int32_t center_rows;
+  int32_t center_width;          /* row pitch of `centers` in elements */
+} nkv_history;
+
+/* ------------------------------------------------------------------ encode */
+
+/*
+ * ids[t] = argmin_c ||x[t] - centers[c]||^2 evaluated as
+ * ||x||^2 + ||c||^2 - 2 x.c in fp32, lowest index on ties.
+ * Reference: the assignment step of semantic_residual,
+ * MGM/nanokv_codec.py:316-321, LB/lingbot_v2_kv_codec.py:226-230.
+ * x [S,J] (f32|bf16), centers [C,J] (f32|bf16), ids [S] of id_bytes each.
+ */
+int nkv_assign(const void* x, int x_dtype, const void* centers, int centers_dtype,
+               int S, int J, int C, void* ids, int id_bytes, void* stream);
+
+/*
+ * Online C-means over one chunk: `iters` rounds of assign + deterministic
+ * centre update (empty clusters keep their centre); ids are those of the last
+ * assignment; stored centres are rounded to bf16.
+ * Reference: semantic_residual, MGM/nanokv_codec.py:302-330,
+ * LB/lingbot_v2_kv_codec.py:210-239 (the seeded randperm that picks
+ * init_rows stays on the host, as it does there).
+ * workspace: nkv_kmeans_workspace_bytes(S, J, C) bytes of device scratch.
+ */
+size_t nkv_kmeans_workspace_bytes(int S, int J, int C);
+int nkv_kmeans(const void* x, int x_dtype, int S, int J, int C, int iters,
+               const int32_t* init_rows, void* centers_bf16, void* ids, int id_bytes,
+               void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * coeff[t] = ((x[t] - centers[ids[t]]) - mean) @ encoder^T.
+ * bf16 encoder: the residual is formed in fp32, rounded to bf16, multiplied
+ * with fp32 accumulation and stored as bf16; f32 encoder: fp32 throughout.
+ * Reference: MGM/nanokv_codec.py:326-330,345-348 with _operator_linear
+ * :134-141; LB/lingbot_v2_kv_codec.py:236-239,280 with _linear :102-106.
+ * x [S,J], centers bf16 [C,J], mean f32 [J], encoder [r,J], coeff [S,r] in
+ * the encoder's dtype.
+ */
+int nkv_project(const void* x, int x_dtype, const void* centers_bf16, const void* ids,
+                int id_bytes, const float* mean, const void* encoder, int encoder_dtype,
+                int S, int J, int r, void* coeff, void* stream);
+
+/*
+ * Per-group symmetric INT4: scale = max(amax, eps) / 7, code =
+ * clamp(rint(z / scale), -7, 7) with round-half-even, bytes = (code+7) pairs
+ * with the even coefficient in the low nibble; the stored scale is rounded
+ * to scale_dtype after the codes were formed.
+ * Reference: MGM/nanokv_codec.py:349-351 + _pack_int4 :282-292;
+ * LB/lingbot_v2_kv_codec.py:285-287 + :242-247 (Triton twins
+ * LB/lingbot_v2_kv_codec_triton.py:12-67); HY/kv_codecs.py:237-255.
+ * coeff [S,r] (f32|bf16) -> codes [S,r/2], scales [S,r/group].
+ * Writing at an offset into a history cache is the append (E5).
+ */
+int nkv_quant_pack(const void* coeff, int coeff_dtype, int S, int r, int group, float eps,
+                   int quant_mode, int scale_dtype, uint8_t* codes, void* scales,
+                   void* stream);
+
+/*
+ * Whole encoder of one chunk against given (stored, bf16) centres: assign,
+ * project, quantise, pack, and write codes / scales / ids at token `offset`
+ * of the destination arrays (the append).
+ * Reference: encode_tensor, MGM/nanokv_codec.py:334-365,
+ * LB/lingbot_v2_kv_codec.py:256-297.
+ * workspace: S * r elements of the encoder dtype.
+ */
+int nkv_encode_append(const void* x, int x_dtype, const void* centers_bf16, int C,
+                      const float* mean, const void* encoder, int encoder_dtype,
+                      int S, int J, int r, int group, float eps, int quant_mode,
+                      int scale_dtype, int id_bytes, int offset,
+                      uint8_t* codes, void* scales, void* ids,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------- decode */
+
+/*
+ * rows = latent @ decoder^T + mean, then + centre, for tokens
+ * rows_index[0..n) (or 0..n when rows_index is NULL) of a history tensor.
+ * bf16 decoder: latent = bf16(code * scale), bf16(acc + bf16(mean)), then the
+ * bf16 centre is added and the sum rounded to bf16; f32 decoder: fp32.
+ * Reference: decode_tensor MGM/nanokv_codec.py:369-390, _decode_method_segments
+ * :393-455, LB/lingbot_v2_kv_codec.py:301-326,404-437 (row / slice forms).
+ * decoder [J,r], mean f32 [J], out [n,J] (f32|bf16).
+ */
+int nkv_decode_rows(const nkv_history* hist, const int32_t* rows_index, int n,
+                    const void* decoder, int decoder_dtype, const float* mean, int J,
+                    void* out, int out_dtype, void* stream);
+
+/* ---------------------------------------------------------------- attention */
+
+/*
+ * Fused codec-attention over a compressed history.  For every head h and
+ * history token t the kernel rebuilds, on chip,
+ *     K[t,h,:] = bf16( bf16(latent_k[t] @ wk[h]^T + bias_k[h]) + centers_k[row(t), h*dk : (h+1)*dk] )
+ *     V[t,h,:] likewise with wv / bias_v / centers_v,
+ * and computes O = softmax(q K^T * scale) V with an online softmax, returning
+ * O and the natural-log LSE.  No K or V row is written to global memory.
+ * With wk / wv = the decoder viewed as [heads, head_dim, r] and bias = mean
+ * this is the full-dimensional read (decode + attention); with reader
+ * matrices and projected centre tables it is the NanoKV-Fast low-width read.
+ * Reference: decode (above) + attention_lse MGC/core.py:45-72 /
+ * LB/codec_native_attention.py:53-104; reader read MGC/core.py:168-200.
+ * q [Q, heads, dk] with strides (elements); wk [heads, dk, r]; wv [heads, dv, r];
+ * bias_k f32 [heads, dk]; bias_v f32 [heads, dv]; out [Q, heads, dv] in the
+ * dtype of q; lse f32 [Q, heads].  dtype NKV_BF16 runs on tcgen05 tensor
+ * cores; NKV_F32 is the fp32 CUDA-core path.  An empty history yields
+ * (0, -inf).
+ */
+int nkv_attn_codec(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head,
+                   int Q, int heads, int dk, int dv,
+                   const nkv_history* hist_k, const nkv_history* hist_v,
+                   const void* wk, const float* bias_k, const void* wv, const float* bias_v,
+                   float scale, void* out, float* lse, int32_t* status_word, void* stream);
+
+/*
+ * Plain attention with LSE over K / V rows that are already full width (the
+ * protected / current-chunk partition): O = softmax(q K^T * scale) V.
+ * Reference: attention_lse, MGC/core.py:45-72;
+ * _attention_lse LB/codec_native_attention.py:53-104.
+ * q [Q, heads, d], k [N, heads, d], v [N, heads, dv] (token-major, strides in
+ * elements), out [Q, heads, dv], lse f32 [Q, heads].
+ */
+int nkv_attention_lse(const void* q, const void* k, const void* v, int dtype,
+                      int64_t q_stride_token, int64_t q_stride_head,
+                      int64_t kv_stride_token, int64_t kv_stride_head,
+                      int Q, int N, int heads, int d, int dv, float scale,
+                      void* out, float* lse, void* stream);
+
+/*
+ * P-way log-sum-exp merge of attention partials: lse = logsumexp_p lse_p,
+ * O = sum_p O_p * exp(lse_p - lse) in fp32 with one final rounding; a row
+ * whose partials are all empty (-inf) gives (0, -inf).
+ * Reference: merge MGC/core.py:33-42, _merge LB/codec_native_attention.py:43-50,
+ * LB/codec_native_merge_triton.py:7-18 (two-way; folded here over P).
+ * outs: P pointers (host array) to [rows, d] tensors; lses: P pointers to
+ * f32 [rows]; out [rows, d]; lse_out f32 [rows].
+ */
+int nkv_lse_merge(const void* const* outs, const float* const* lses, int parts,
+                  int64_t rows, int d, int dtype, void* out, float* lse_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NANOKV_B200_H */

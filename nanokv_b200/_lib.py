@@ -1,0 +1,88 @@
+"""ctypes binding of libnanokv_b200.so (the C ABI in include/nanokv_b200.h).
+
+There is no fallback: if the shared library is missing and cannot be built,
+importing the product path raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+
+from . import build as _build
+
+NKV_OK = 0
+NKV_ERR_INVALID, NKV_ERR_CUDA, NKV_ERR_UNSUPPORTED, NKV_ERR_DEVICE_WAIT, NKV_ERR_TOO_LARGE = (
+    -1, -2, -3, -4, -5)
+NKV_F32, NKV_BF16, NKV_F16 = 0, 1, 2
+NKV_QUANT_F32, NKV_QUANT_IN_BF16 = 0, 1
+
+
+class History(ctypes.Structure):
+    """struct nkv_history"""
+    _fields_ = [
+        ("codes", c_void_p), ("scales", c_void_p), ("ids", c_void_p), ("centers", c_void_p),
+        ("seg_start", c_void_p), ("seg_center_row", c_void_p),
+        ("tokens", c_int32), ("segments", c_int32), ("rank", c_int32), ("group", c_int32),
+        ("scale_dtype", c_int32), ("id_bytes", c_int32), ("center_rows", c_int32),
+        ("center_width", c_int32),
+    ]
+
+
+# name -> (restype, argtypes); every symbol the header declares
+SIGNATURES = {
+    "nkv_status_string": (c_char_p, [c_int]),
+    "nkv_last_error": (c_char_p, []),
+    "nkv_version": (c_int, []),
+    "nkv_assign": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                           c_void_p]),
+    "nkv_kmeans_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "nkv_kmeans": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                           c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
+    "nkv_project": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                            c_int, c_int, c_int, c_void_p, c_void_p]),
+    "nkv_quant_pack": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                               c_void_p, c_void_p, c_void_p]),
+    "nkv_encode_append": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                  c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
+                                  c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "nkv_decode_rows": (c_int, [POINTER(History), c_void_p, c_int, c_void_p, c_int, c_void_p,
+                                c_int, c_void_p, c_int, c_void_p]),
+    "nkv_attn_codec": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int,
+                               POINTER(History), POINTER(History), c_void_p, c_void_p, c_void_p,
+                               c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nkv_attention_lse": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64,
+                                  c_int64, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                  c_void_p, c_void_p]),
+    "nkv_lse_merge": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_int, c_int64, c_int, c_int,
+                              c_void_p, c_void_p, c_void_p]),
+}
+
+_EXCEPTIONS = {NKV_ERR_INVALID: ValueError, NKV_ERR_TOO_LARGE: ValueError}
+
+_lib = None
+
+
+def library() -> ctypes.CDLL:
+    """Load (building first if the tree has no up-to-date .so) and bind."""
+    global _lib
+    if _lib is None:
+        path = _build.build()
+        lib = ctypes.CDLL(str(path))
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(lib, name)   # AttributeError if the library lacks a declared symbol
+            fn.restype = restype
+            fn.argtypes = argtypes
+        lib.nkv_debug_force_simt.restype = None
+        lib.nkv_debug_force_simt.argtypes = [c_int]
+        _lib = lib
+    return _lib
+
+
+def check(status: int) -> None:
+    """Map a status code to the exception class the reference API raises."""
+    if status == NKV_OK:
+        return
+    lib = library()
+    detail = lib.nkv_last_error().decode()
+    kind = lib.nkv_status_string(status).decode()
+    raise _EXCEPTIONS.get(status, RuntimeError)(f"nanokv_b200: {kind}: {detail}")

@@ -1,0 +1,146 @@
+"""Read path: fused codec-attention, NanoKV-Fast hybrid attention, LSE merge."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import ops
+from .cache import CompressedHistory
+from .codec import Operator
+from .ops import HistoryView
+
+
+def _view(hist) -> HistoryView:
+    return hist.view() if isinstance(hist, CompressedHistory) else hist
+
+
+def codec_attention(q: torch.Tensor, hist_k, hist_v, op_k: Operator, op_v: Operator, *,
+                    scale: float | None = None, status: torch.Tensor | None = None):
+    """Full-dimensional read: q [Q,H,D] -> (O [Q,H,D], lse f32 [Q,H]).
+
+    K and V of every history token are rebuilt on chip from codes, scales, the
+    decoder slice of each head and the token's centre; nothing full-width is
+    written to HBM.  Replaces decode + attention of the reference
+    (MGM/nanokv_codec.py:393-455 + MGC/core.py:45-72).
+    """
+    Q, H, D = q.shape
+    if H * D != op_k.joint:
+        raise ValueError("query heads do not match the operator's joint width")
+    scale = D ** -0.5 if scale is None else scale
+    wk = op_k.decoder.view(H, D, op_k.rank)
+    wv = op_v.decoder.view(H, D, op_v.rank)
+    return ops.attn_codec(q, _view(hist_k), _view(hist_v), wk, op_k.bias.view(H, D), wv,
+                          op_v.bias.view(H, D), scale=scale, status=status)
+
+
+def merge(out_a, lse_a, out_b, lse_b):
+    """Two-partition softmax merge (MGC/core.py:33-42)."""
+    return ops.lse_merge([(out_a.contiguous(), lse_a.contiguous()),
+                          (out_b.contiguous(), lse_b.contiguous())])
+
+
+# ------------------------------------------------------------------ NanoKV-Fast
+class ReaderGroup:
+    """Device-resident reader of one head-width group (MGC/core.py:155-204)."""
+
+    def __init__(self, state: dict, *, dtype: torch.dtype, device, native_dim: int):
+        self.heads = state["heads"].long().to(device)
+        self.width = int(state["k_read"].shape[1])
+        self.value_width = int(state["v_read"].shape[1])
+        if self.width != self.value_width:
+            raise ValueError("reader groups with different K and V widths are not built")
+        self.dtype, self.native_dim = dtype, native_dim
+        to = dict(device=device, dtype=dtype)
+        self.q_reduce = state["q_reduce"].to(**to)
+        self.k_affine = state["k_affine"].to(**to)
+        self.v_affine = state["v_affine"].to(**to)
+        self.lift = state["lift"].to(**to)
+        # bf16 tensor-core tiles are at least 64 wide: narrower readers are zero-padded
+        pad_to = 64 if (dtype == torch.bfloat16 and self.width < 64) else self.width
+        self.padded = pad_to
+
+        def pad_rows(weight):  # [h, d, r] -> [h, pad, r]
+            out = torch.zeros(weight.shape[0], pad_to, weight.shape[2], **to)
+            out[:, :weight.shape[1]] = weight.to(**to)
+            return out.contiguous()
+        self.k_read = pad_rows(state["k_read"])
+        self.v_read = pad_rows(state["v_read"])
+        self._tables: dict = {}
+
+    def _pad_last(self, tensor):
+        if tensor.shape[-1] == self.padded:
+            return tensor.contiguous()
+        out = tensor.new_zeros(*tensor.shape[:-1], self.padded)
+        out[..., :tensor.shape[-1]] = tensor
+        return out
+
+    def bias(self, mean: torch.Tensor, target: str) -> torch.Tensor:
+        """(mean_h @ affine) in the working dtype, as float [h, pad] (MGC/core.py:179-180)."""
+        affine = self.k_affine if target == "k" else self.v_affine
+        mean_heads = mean.reshape(-1, self.native_dim).index_select(0, self.heads).to(self.dtype)
+        return self._pad_last(torch.einsum("hd,hde->he", mean_heads, affine).float())
+
+    def projected_centers(self, hist: CompressedHistory, target: str) -> HistoryView:
+        """History view whose centre table is projected to this group's heads and width
+        (MGC/core.py:194-195); cached per (history, segments) as derived state."""
+        key = (id(hist), target, hist.segments)
+        if key not in self._tables:
+            affine = self.k_affine if target == "k" else self.v_affine
+            table = hist.centers.view(hist.centers.shape[0], -1, self.native_dim)
+            table = table.index_select(1, self.heads).to(self.dtype)
+            projected = self._pad_last(torch.einsum("chd,hde->che", table, affine))
+            self._tables = {k: v for k, v in self._tables.items() if k[0] != id(hist) or k[1] != target}
+            self._tables[key] = projected.reshape(projected.shape[0], -1).contiguous()
+        view = hist.view()
+        view.centers = self._tables[key]
+        return view
+
+
+class Reader:
+    """All groups of one layer; groups partition the heads (MGC/core.py:207-224)."""
+
+    def __init__(self, payload: dict, *, dtype: torch.dtype, device="cuda"):
+        self.heads, self.native_dim = int(payload["heads"]), int(payload["native_dim"])
+        self.rank = int(payload["rank"])
+        self.groups = [ReaderGroup(s, dtype=dtype, device=device, native_dim=self.native_dim)
+                       for s in payload["groups"]]
+        listed = sorted(int(h) for g in self.groups for h in g.heads.tolist())
+        if listed != list(range(self.heads)):
+            raise ValueError("Reader groups must partition heads exactly once")
+
+
+def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segments,
+                     low_segments, reader: Reader):
+    """Mixed-dimensional read (MGC/core.py:278-310) with identity positional hooks.
+
+    q_pre / q_native [Q,H,D]; native_segments [(K [n,H,D], V [n,H,D])] full
+    width (protected history, current chunk); low_segments [{"k": history,
+    "v": history, "k_mean": f32 [J], "v_mean": f32 [J]}] read through the
+    reader projections.  Returns O [Q,H,D].
+    """
+    Q, H, D = q_native.shape
+    scale = reader.native_dim ** -0.5
+    native_out = torch.zeros_like(q_native)
+    native_lse = torch.full((Q, H), -math.inf, device=q_native.device)
+    for key, value in native_segments:
+        out, lse = ops.attention_lse(q_native.contiguous(), key.contiguous(), value.contiguous(),
+                                     scale=scale)
+        native_out, native_lse = ops.lse_merge([(native_out, native_lse), (out, lse)])
+    result = torch.empty_like(q_native)
+    for group in reader.groups:
+        head = group.heads
+        query = torch.einsum("nhd,hde->nhe", q_pre.index_select(1, head), group.q_reduce)
+        query = group._pad_last(query)
+        out = native_out.index_select(1, head).contiguous()
+        lse = native_lse.index_select(1, head).contiguous()
+        for segment in low_segments:
+            view_k = group.projected_centers(segment["k"], "k")
+            view_v = group.projected_centers(segment["v"], "v")
+            oo, ll = ops.attn_codec(
+                query, view_k, view_v, group.k_read, group.bias(segment["k_mean"], "k"),
+                group.v_read, group.bias(segment["v_mean"], "v"), scale=scale)
+            lifted = torch.einsum("nhe,hed->nhd", oo[..., :group.width], group.lift).contiguous()
+            out, lse = ops.lse_merge([(out, lse), (lifted, ll)])
+        result.index_copy_(1, head, out)
+    return result

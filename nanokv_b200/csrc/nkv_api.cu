@@ -1,0 +1,270 @@
+// extern "C" surface of libnanokv_b200: argument checks and kernel dispatch.
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "nkv_internal.h"
+#include "nkv_tc.cuh"
+
+namespace nkv {
+
+static thread_local char g_error[512] = "";
+static int g_force_simt = -1;
+
+int fail(int status, const char* fmt, ...) {
+  va_list args;
+  va_start(args, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, args);
+  va_end(args);
+  return status;
+}
+
+bool simt_forced() {
+  if (g_force_simt < 0) {
+    const char* env = getenv("NKV_FORCE_SIMT");
+    g_force_simt = (env && env[0] == '1') ? 1 : 0;
+  }
+  return g_force_simt == 1;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int encode_tensor_map(CUtensorMap* map, int elem_bytes, const void* base, int rank,
+                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                      bool swizzle128) {
+  static EncodeTiledFn encode = nullptr;
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    NKV_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &query));
+    NKV_REQUIRE(fn != nullptr && query == cudaDriverEntryPointSuccess, NKV_ERR_CUDA,
+                "driver does not export cuTensorMapEncodeTiled");
+    encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  NKV_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, NKV_ERR_INVALID,
+              "TMA source %p is not 16-byte aligned", base);
+  cuuint64_t gdims[5];
+  cuuint64_t gstrides[4];
+  cuuint32_t gbox[5], estrides[5];
+  for (int i = 0; i < rank; ++i) {
+    gdims[i] = dims[i];
+    gbox[i] = box[i];
+    estrides[i] = 1;
+    if (i > 0) {
+      NKV_REQUIRE(strides_bytes[i - 1] % 16 == 0, NKV_ERR_INVALID,
+                  "TMA stride %llu is not a multiple of 16 bytes",
+                  static_cast<unsigned long long>(strides_bytes[i - 1]));
+      gstrides[i - 1] = strides_bytes[i - 1];
+    }
+  }
+  CUresult rc = encode(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8,
+                       static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdims, gstrides, gbox,
+                       estrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  NKV_REQUIRE(rc == CUDA_SUCCESS, NKV_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d",
+              static_cast<int>(rc));
+  return NKV_OK;
+}
+
+static int check_history(const nkv_history* h, const char* name) {
+  NKV_REQUIRE(h != nullptr, NKV_ERR_INVALID, "%s history is NULL", name);
+  NKV_REQUIRE(h->tokens >= 0 && h->rank > 0 && h->rank % 2 == 0, NKV_ERR_INVALID,
+              "%s history: tokens=%d rank=%d", name, h->tokens, h->rank);
+  NKV_REQUIRE(h->group > 0 && h->rank % h->group == 0 && h->group % 2 == 0, NKV_ERR_INVALID,
+              "%s history: group %d must be even and divide rank %d", name, h->group, h->rank);
+  NKV_REQUIRE(h->scale_dtype == NKV_BF16 || h->scale_dtype == NKV_F16, NKV_ERR_INVALID,
+              "%s history: scales must be bf16 or fp16", name);
+  NKV_REQUIRE(h->id_bytes == 1 || h->id_bytes == 2, NKV_ERR_INVALID,
+              "%s history: id_bytes must be 1 or 2", name);
+  if (h->tokens > 0)
+    NKV_REQUIRE(h->segments >= 1 && h->seg_start && h->seg_center_row && h->codes && h->scales &&
+                    h->ids && h->centers,
+                NKV_ERR_INVALID, "%s history: missing arrays or segment table", name);
+  return NKV_OK;
+}
+
+}  // namespace nkv
+
+using namespace nkv;
+
+extern "C" {
+
+const char* nkv_status_string(int status) {
+  switch (status) {
+    case NKV_OK: return "ok";
+    case NKV_ERR_INVALID: return "invalid argument";
+    case NKV_ERR_CUDA: return "CUDA error";
+    case NKV_ERR_UNSUPPORTED: return "unsupported shape";
+    case NKV_ERR_DEVICE_WAIT: return "device-side wait gave up";
+    case NKV_ERR_TOO_LARGE: return "fixed capacity exceeded";
+    default: return "unknown status";
+  }
+}
+
+const char* nkv_last_error(void) { return g_error; }
+
+int nkv_version(void) { return NKV_ABI_VERSION; }
+
+void nkv_debug_force_simt(int on) { g_force_simt = on ? 1 : 0; }
+
+int nkv_assign(const void* x, int x_dtype, const void* centers, int centers_dtype, int S, int J,
+               int C, void* ids, int id_bytes, void* stream) {
+  NKV_REQUIRE(S >= 0 && J > 0 && C > 0, NKV_ERR_INVALID, "assign: S=%d J=%d C=%d", S, J, C);
+  NKV_REQUIRE(id_bytes == 1 || id_bytes == 2, NKV_ERR_INVALID, "assign: id_bytes=%d", id_bytes);
+  NKV_REQUIRE(C <= (id_bytes == 1 ? 256 : 65536), NKV_ERR_INVALID,
+              "assign: %d centres do not fit %d-byte ids", C, id_bytes);
+  NKV_REQUIRE(x_dtype == NKV_F32 || x_dtype == NKV_BF16, NKV_ERR_INVALID, "assign: x dtype");
+  NKV_REQUIRE(centers_dtype == NKV_F32 || centers_dtype == NKV_BF16, NKV_ERR_INVALID,
+              "assign: centres dtype");
+  auto s = static_cast<cudaStream_t>(stream);
+  if (x_dtype == NKV_BF16 && centers_dtype == NKV_BF16 && !simt_forced() &&
+      tc_assign_supported(J, C))
+    return tc_assign(x, centers, S, J, C, ids, id_bytes, s);
+  return simt_assign(x, x_dtype, centers, centers_dtype, S, J, C, ids, id_bytes, nullptr, s);
+}
+
+size_t nkv_kmeans_workspace_bytes(int S, int J, int C) {
+  return sizeof(float) * static_cast<size_t>(C) * J + sizeof(int32_t) * static_cast<size_t>(S) + 256;
+}
+
+int nkv_kmeans(const void* x, int x_dtype, int S, int J, int C, int iters,
+               const int32_t* init_rows, void* centers_bf16, void* ids, int id_bytes,
+               void* workspace, size_t workspace_bytes, void* stream) {
+  NKV_REQUIRE(S > 0 && J > 0 && C > 0 && C <= S, NKV_ERR_INVALID,
+              "kmeans: clusters must be in [1, S]; got C=%d S=%d", C, S);
+  NKV_REQUIRE(iters >= 0, NKV_ERR_INVALID, "kmeans: iters=%d", iters);
+  NKV_REQUIRE(id_bytes == 1 || id_bytes == 2, NKV_ERR_INVALID, "kmeans: id_bytes=%d", id_bytes);
+  NKV_REQUIRE(C <= (id_bytes == 1 ? 256 : 65536), NKV_ERR_INVALID,
+              "kmeans: %d centres do not fit %d-byte ids", C, id_bytes);
+  NKV_REQUIRE(workspace && workspace_bytes >= nkv_kmeans_workspace_bytes(S, J, C), NKV_ERR_INVALID,
+              "kmeans: workspace of %zu bytes is too small", workspace_bytes);
+  auto s = static_cast<cudaStream_t>(stream);
+  float* centers = static_cast<float*>(workspace);
+  int32_t* labels = reinterpret_cast<int32_t*>(centers + static_cast<size_t>(C) * J);
+  int rc = kmeans_gather_init(x, x_dtype, J, C, init_rows, centers, s);
+  if (rc != NKV_OK) return rc;
+  NKV_CUDA(cudaMemsetAsync(labels, 0, sizeof(int32_t) * S, s));
+  for (int it = 0; it < iters; ++it) {
+    rc = simt_assign(x, x_dtype, centers, NKV_F32, S, J, C, nullptr, id_bytes, labels, s);
+    if (rc != NKV_OK) return rc;
+    rc = kmeans_update(x, x_dtype, S, J, C, labels, centers, s);
+    if (rc != NKV_OK) return rc;
+  }
+  return kmeans_store(centers, labels, S, J, C, centers_bf16, ids, id_bytes, s);
+}
+
+int nkv_project(const void* x, int x_dtype, const void* centers_bf16, const void* ids,
+                int id_bytes, const float* mean, const void* encoder, int encoder_dtype, int S,
+                int J, int r, void* coeff, void* stream) {
+  NKV_REQUIRE(S >= 0 && J > 0 && r > 0, NKV_ERR_INVALID, "project: S=%d J=%d r=%d", S, J, r);
+  NKV_REQUIRE(encoder_dtype == NKV_F32 || encoder_dtype == NKV_BF16, NKV_ERR_INVALID,
+              "project: encoder dtype");
+  auto s = static_cast<cudaStream_t>(stream);
+  if (encoder_dtype == NKV_BF16 && x_dtype == NKV_BF16 && !simt_forced() &&
+      tc_project_supported(J, r))
+    return tc_project(x, centers_bf16, ids, id_bytes, mean, encoder, S, J, r, coeff, s);
+  return simt_project(x, x_dtype, centers_bf16, ids, id_bytes, mean, encoder, encoder_dtype, S, J,
+                      r, coeff, s);
+}
+
+int nkv_quant_pack(const void* coeff, int coeff_dtype, int S, int r, int group, float eps,
+                   int quant_mode, int scale_dtype, uint8_t* codes, void* scales, void* stream) {
+  NKV_REQUIRE(S >= 0 && r > 0 && group > 0 && r % group == 0 && group % 2 == 0, NKV_ERR_INVALID,
+              "quant_pack: S=%d r=%d group=%d (group must be even and divide r)", S, r, group);
+  NKV_REQUIRE(coeff_dtype == NKV_F32 || coeff_dtype == NKV_BF16, NKV_ERR_INVALID,
+              "quant_pack: coefficient dtype");
+  NKV_REQUIRE(scale_dtype == NKV_BF16 || scale_dtype == NKV_F16, NKV_ERR_INVALID,
+              "quant_pack: scale dtype");
+  NKV_REQUIRE(quant_mode == NKV_QUANT_F32 || quant_mode == NKV_QUANT_IN_BF16, NKV_ERR_INVALID,
+              "quant_pack: quant_mode=%d", quant_mode);
+  NKV_REQUIRE(quant_mode != NKV_QUANT_IN_BF16 || coeff_dtype == NKV_BF16, NKV_ERR_INVALID,
+              "quant_pack: NKV_QUANT_IN_BF16 needs bf16 coefficients");
+  return quant_pack(coeff, coeff_dtype, S, r, group, eps, quant_mode, scale_dtype, codes, scales,
+                    static_cast<cudaStream_t>(stream));
+}
+
+int nkv_encode_append(const void* x, int x_dtype, const void* centers_bf16, int C,
+                      const float* mean, const void* encoder, int encoder_dtype, int S, int J,
+                      int r, int group, float eps, int quant_mode, int scale_dtype, int id_bytes,
+                      int offset, uint8_t* codes, void* scales, void* ids, void* workspace,
+                      size_t workspace_bytes, void* stream) {
+  NKV_REQUIRE(offset >= 0, NKV_ERR_INVALID, "encode_append: offset=%d", offset);
+  NKV_REQUIRE(r > 0 && group > 0 && r % group == 0, NKV_ERR_INVALID,
+              "encode_append: r=%d group=%d", r, group);
+  NKV_REQUIRE(workspace && workspace_bytes >= static_cast<size_t>(S) * r * dtype_bytes(encoder_dtype),
+              NKV_ERR_INVALID, "encode_append: workspace of %zu bytes is too small", workspace_bytes);
+  void* ids_at = static_cast<uint8_t*>(ids) + static_cast<size_t>(offset) * id_bytes;
+  uint8_t* codes_at = codes + static_cast<size_t>(offset) * (r / 2);
+  void* scales_at = static_cast<uint8_t*>(scales) + static_cast<size_t>(offset) * (r / group) * 2;
+  int rc = nkv_assign(x, x_dtype, centers_bf16, NKV_BF16, S, J, C, ids_at, id_bytes, stream);
+  if (rc != NKV_OK) return rc;
+  rc = nkv_project(x, x_dtype, centers_bf16, ids_at, id_bytes, mean, encoder, encoder_dtype, S, J,
+                   r, workspace, stream);
+  if (rc != NKV_OK) return rc;
+  return nkv_quant_pack(workspace, encoder_dtype, S, r, group, eps, quant_mode, scale_dtype,
+                        codes_at, scales_at, stream);
+}
+
+int nkv_decode_rows(const nkv_history* hist, const int32_t* rows_index, int n,
+                    const void* decoder, int decoder_dtype, const float* mean, int J, void* out,
+                    int out_dtype, void* stream) {
+  int rc = check_history(hist, "decode");
+  if (rc != NKV_OK) return rc;
+  NKV_REQUIRE(n >= 0 && J > 0, NKV_ERR_INVALID, "decode_rows: n=%d J=%d", n, J);
+  NKV_REQUIRE(rows_index != nullptr || n <= hist->tokens, NKV_ERR_INVALID,
+              "decode_rows: %d rows requested from %d tokens", n, hist->tokens);
+  NKV_REQUIRE(decoder_dtype == NKV_F32 || decoder_dtype == NKV_BF16, NKV_ERR_INVALID,
+              "decode_rows: decoder dtype");
+  return simt_decode_rows(*hist, rows_index, n, decoder, decoder_dtype, mean, J, out, out_dtype,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int nkv_attn_codec(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head, int Q,
+                   int heads, int dk, int dv, const nkv_history* hist_k,
+                   const nkv_history* hist_v, const void* wk, const float* bias_k, const void* wv,
+                   const float* bias_v, float scale, void* out, float* lse, int32_t* status_word,
+                   void* stream) {
+  int rc = check_history(hist_k, "K");
+  if (rc != NKV_OK) return rc;
+  rc = check_history(hist_v, "V");
+  if (rc != NKV_OK) return rc;
+  NKV_REQUIRE(hist_k->tokens == hist_v->tokens && hist_k->rank == hist_v->rank &&
+                  hist_k->group == hist_v->group && hist_k->scale_dtype == hist_v->scale_dtype,
+              NKV_ERR_INVALID, "K and V histories differ in tokens / rank / group / scale dtype");
+  NKV_REQUIRE(dtype == NKV_F32 || dtype == NKV_BF16, NKV_ERR_INVALID, "attn_codec: dtype");
+  NKV_REQUIRE(Q >= 0 && heads >= 0, NKV_ERR_INVALID, "attn_codec: Q=%d heads=%d", Q, heads);
+  auto s = static_cast<cudaStream_t>(stream);
+  if (dtype == NKV_BF16 && !simt_forced())
+    return tc_attn_codec(q, q_stride_token, q_stride_head, Q, heads, dk, dv, hist_k, hist_v, wk,
+                         bias_k, wv, bias_v, scale, out, lse, status_word, s);
+  return simt_attn(q, dtype, q_stride_token, q_stride_head, Q, heads, dk, dv, hist_k, hist_v, wk,
+                   bias_k, wv, bias_v, nullptr, nullptr, 0, 0, hist_k->tokens, scale, out, lse, s);
+}
+
+int nkv_attention_lse(const void* q, const void* k, const void* v, int dtype,
+                      int64_t q_stride_token, int64_t q_stride_head, int64_t kv_stride_token,
+                      int64_t kv_stride_head, int Q, int N, int heads, int d, int dv, float scale,
+                      void* out, float* lse, void* stream) {
+  NKV_REQUIRE(dtype == NKV_F32 || dtype == NKV_BF16, NKV_ERR_INVALID, "attention_lse: dtype");
+  NKV_REQUIRE(Q >= 0 && N >= 0 && heads >= 0, NKV_ERR_INVALID, "attention_lse: Q=%d N=%d heads=%d",
+              Q, N, heads);
+  return simt_attn(q, dtype, q_stride_token, q_stride_head, Q, heads, d, dv, nullptr, nullptr,
+                   nullptr, nullptr, nullptr, nullptr, k, v, kv_stride_token, kv_stride_head, N,
+                   scale, out, lse, static_cast<cudaStream_t>(stream));
+}
+
+int nkv_lse_merge(const void* const* outs, const float* const* lses, int parts, int64_t rows,
+                  int d, int dtype, void* out, float* lse_out, void* stream) {
+  NKV_REQUIRE(outs && lses && rows >= 0 && d > 0, NKV_ERR_INVALID, "lse_merge: rows=%lld d=%d",
+              static_cast<long long>(rows), d);
+  NKV_REQUIRE(dtype == NKV_F32 || dtype == NKV_BF16, NKV_ERR_INVALID, "lse_merge: dtype");
+  return lse_merge(outs, lses, parts, rows, d, dtype, out, lse_out,
+                   static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,382 @@
+// Encoder GEMMs on tcgen05: nearest-centre assignment and residual projection.
+//
+// Both are [128 tokens x K=J] x [N x K]^T tiles with fp32 accumulators in TMEM,
+// K streamed 64 columns at a time through a two-stage shared-memory ring.
+//   assign : A = token rows (TMA), B = centre rows (TMA), N = C <= 512.  While
+//            a stage is resident the compute warps accumulate ||x||^2 and
+//            ||c||^2 from the same tiles; the epilogue evaluates
+//            (||x||^2 + ||c||^2) - 2 x.c in fp32 and keeps the first minimum.
+//   project: A = bf16((x - centre[id]) - mean), formed by the compute warps in
+//            the swizzled operand layout; B = encoder rows (TMA); the epilogue
+//            rounds once to bf16.
+// A CTA covers up to 512 output columns as 1 or 2 accumulators of NB <= 256.
+// Warps 0-7 compute, warp 8 lane 0 issues TMA, warp 9 lane 0 issues MMA.
+#include "nkv_internal.h"
+#include "nkv_tc.cuh"
+
+namespace nkv {
+namespace {
+
+using namespace tc;
+
+constexpr int TM = 128;
+constexpr int COMPUTE_THREADS = 256;
+constexpr int THREADS = COMPUTE_THREADS + 64;
+constexpr int A_BYTES = 128 * 128;
+
+enum Bar { TMA_FULL = 0, A_FULL = 2, STAGE_FREE = 4, ACC_DONE = 6, SIDE_READY = 7, CAND_READY = 8, NUM_BARS = 9 };
+
+struct Params {
+  int S, J, NB, NACC, n_total;      // n_total = r (project) or C (assign)
+  // project
+  const uint16_t* x; const uint16_t* centers; const void* ids; int id_bytes;
+  const float* mean; uint16_t* coeff;
+  // assign
+  void* ids_out;
+};
+
+__device__ __forceinline__ float sumsq8(uint4 w) {
+  const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float a = __uint_as_float(words[i] << 16), b = __uint_as_float(words[i] & 0xFFFF0000u);
+    s = fmaf(a, a, s);
+    s = fmaf(b, b, s);
+  }
+  return s;
+}
+
+template <bool ASSIGN>
+__global__ void __launch_bounds__(THREADS, 1)
+encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
+                   const __grid_constant__ CUtensorMap map_b, Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const int b_bytes = p.NB * 128;                       // one accumulator's B tile
+  const int stage_bytes = A_BYTES + p.NACC * b_bytes;
+  uint8_t* meta = smem + 2 * stage_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(meta);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(meta + NUM_BARS * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(meta + NUM_BARS * 8 + 4);
+  float* xn_part = reinterpret_cast<float*>(meta + 128);          // [128][2]
+  float* cand_d = xn_part + 256;                                  // [128]
+  int* cand_i = reinterpret_cast<int*>(cand_d + 128);             // [128]
+  float* cn_part = reinterpret_cast<float*>(cand_i + 128);        // [C][2]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int m0 = blockIdx.x * TM;
+  const int n_base = blockIdx.y * p.NACC * p.NB;
+  const int nchunks = p.J / 64;
+
+  if (tid == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars[TMA_FULL + s], 1);
+      mbar_init(&bars[A_FULL + s], COMPUTE_THREADS);
+      mbar_init(&bars[STAGE_FREE + s], ASSIGN ? 1 + COMPUTE_THREADS : 1);
+    }
+    mbar_init(&bars[ACC_DONE], 1);
+    mbar_init(&bars[SIDE_READY], COMPUTE_THREADS);
+    mbar_init(&bars[CAND_READY], 128);
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 9) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      prefetch_tensormap(&map_b);
+      if (ASSIGN) prefetch_tensormap(&map_a);
+      bool ok = true;
+      for (int c = 0; c < nchunks && ok; ++c) {
+        const int s = c & 1, u = c >> 1;
+        if (u >= 1) ok = mbar_wait(&bars[STAGE_FREE + s], (u - 1) & 1, abort_flag, 400 + s);
+        if (!ok) break;
+        uint8_t* stage = smem + s * stage_bytes;
+        mbar_arrive_expect_tx(&bars[TMA_FULL + s], p.NACC * b_bytes + (ASSIGN ? A_BYTES : 0));
+        if (ASSIGN) tma_load_2d(stage, &map_a, c * 64, m0, &bars[TMA_FULL + s]);
+        for (int a = 0; a < p.NACC; ++a)
+          tma_load_2d(stage + A_BYTES + a * b_bytes, &map_b, c * 64, n_base + a * p.NB,
+                      &bars[TMA_FULL + s]);
+      }
+      if (!ok) {
+        const long long start = clock64();
+        while (clock64() - start < (1ll << 21)) {}
+      }
+    }
+    __syncwarp();
+  } else if (warp == 9) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(128, p.NB);
+      const uint32_t smem_base = smem_u32(smem);
+      bool ok = true;
+      for (int c = 0; c < nchunks && ok; ++c) {
+        const int s = c & 1, u = c >> 1;
+        ok = mbar_wait(&bars[TMA_FULL + s], u & 1, abort_flag, 410 + s);
+        if (ok && !ASSIGN) ok = mbar_wait(&bars[A_FULL + s], u & 1, abort_flag, 412 + s);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t stage = smem_base + s * stage_bytes;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          for (int a = 0; a < p.NACC; ++a)
+            mma_bf16(tmem_base + a * 256, make_smem_desc_sw128(stage + k * 32),
+                     make_smem_desc_sw128(stage + A_BYTES + a * b_bytes + k * 32), idesc,
+                     c > 0 || k > 0);
+        mma_commit(&bars[STAGE_FREE + s]);
+      }
+      if (ok) mma_commit(&bars[ACC_DONE]);
+    }
+    __syncwarp();
+  } else {
+    const int row = tid & 127, wg = tid >> 7;
+    const uint32_t lane_sel = static_cast<uint32_t>(32 * (warp & 3)) << 16;
+    bool ok = true;
+    if (ASSIGN) {
+      // ---- squared norms from the resident tiles
+      const int C = p.n_total;
+      float xs = 0.f, cs[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int c = 0; c < nchunks && ok; ++c) {
+        const int s = c & 1, u = c >> 1;
+        ok = mbar_wait(&bars[TMA_FULL + s], u & 1, abort_flag, 420 + s);
+        if (!ok) break;
+        const uint8_t* stage = smem + s * stage_bytes;
+        {
+          const uint4* src = reinterpret_cast<const uint4*>(stage + (tid >> 1) * 128 + (tid & 1) * 64);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) xs += sumsq8(src[j]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int item = tid + i * COMPUTE_THREADS;
+          if (item < 2 * C) {
+            const uint4* src = reinterpret_cast<const uint4*>(stage + A_BYTES + (item >> 1) * 128 + (item & 1) * 64);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) cs[i] += sumsq8(src[j]);
+          }
+        }
+        mbar_arrive(&bars[STAGE_FREE + s]);
+      }
+      if (ok) {
+        xn_part[tid] = xs;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int item = tid + i * COMPUTE_THREADS;
+          if (item < 2 * C) cn_part[item] = cs[i];
+        }
+        mbar_arrive(&bars[SIDE_READY]);
+        ok = mbar_wait(&bars[SIDE_READY], 0, abort_flag, 430) &&
+             mbar_wait(&bars[ACC_DONE], 0, abort_flag, 431);
+      }
+      if (ok) {
+        tc_fence_after();
+        const float xn = xn_part[2 * row] + xn_part[2 * row + 1];
+        const int chunks = (C + 31) / 32, split = (chunks + 1) / 2;
+        const int first = wg == 0 ? 0 : split, last = wg == 0 ? split : chunks;
+        float best = INFINITY;
+        int best_i = 0x7fffffff;
+#pragma unroll 1
+        for (int cc = first; cc < last; ++cc) {
+          const int col = cc * 32, acc = col / p.NB;
+          float v[32];
+          tmem_ld32(tmem_base + lane_sel + acc * 256 + (col - acc * p.NB), v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int cidx = col + j;
+            if (cidx < C) {
+              const float cn = cn_part[2 * cidx] + cn_part[2 * cidx + 1];
+              const float dist = __fsub_rn(__fadd_rn(xn, cn), __fmul_rn(2.0f, v[j]));
+              if (dist < best) { best = dist; best_i = cidx; }
+            }
+          }
+        }
+        if (wg == 1) {
+          cand_d[row] = best;
+          cand_i[row] = best_i;
+          mbar_arrive(&bars[CAND_READY]);
+        } else {
+          ok = mbar_wait(&bars[CAND_READY], 0, abort_flag, 432);
+          if (ok) {
+            if (cand_d[row] < best) { best = cand_d[row]; best_i = cand_i[row]; }
+            const int t = m0 + row;
+            if (t < p.S) {
+              if (p.id_bytes == 1) static_cast<uint8_t*>(p.ids_out)[t] = static_cast<uint8_t>(best_i);
+              else static_cast<uint16_t*>(p.ids_out)[t] = static_cast<uint16_t>(best_i);
+            }
+          }
+        }
+      }
+    } else {
+      // ---- residual operand: bf16((x - centre[id]) - mean), 32 columns per thread
+      const int r = tid >> 1, half = tid & 1;
+      const int t = m0 + r;
+      const bool in = t < p.S;
+      const uint16_t* xrow = p.x + static_cast<size_t>(in ? t : 0) * p.J;
+      const uint16_t* crow = p.centers + static_cast<size_t>(in ? load_id(p.ids, p.id_bytes, t) : 0) * p.J;
+      for (int c = 0; c < nchunks && ok; ++c) {
+        const int s = c & 1, u = c >> 1;
+        if (u >= 1) ok = mbar_wait(&bars[STAGE_FREE + s], (u - 1) & 1, abort_flag, 440 + s);
+        if (!ok) break;
+        uint8_t* stage = smem + s * stage_bytes;
+        const int j0 = c * 64 + half * 32;
+        const uint4* xs = reinterpret_cast<const uint4*>(xrow + j0);
+        const uint4* cs = reinterpret_cast<const uint4*>(crow + j0);
+        const float4* ms = reinterpret_cast<const float4*>(p.mean + j0);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 out = make_uint4(0, 0, 0, 0);
+          if (in) {
+            const uint4 xw = __ldg(xs + j), cw = __ldg(cs + j);
+            const float4 m0v = __ldg(ms + 2 * j), m1v = __ldg(ms + 2 * j + 1);
+            const uint32_t xwords[4] = {xw.x, xw.y, xw.z, xw.w};
+            const uint32_t cwords[4] = {cw.x, cw.y, cw.z, cw.w};
+            const float mv[8] = {m0v.x, m0v.y, m0v.z, m0v.w, m1v.x, m1v.y, m1v.z, m1v.w};
+            uint32_t* o = &out.x;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              float lo = __fsub_rn(__fsub_rn(__uint_as_float(xwords[w] << 16),
+                                             __uint_as_float(cwords[w] << 16)), mv[2 * w]);
+              float hi = __fsub_rn(__fsub_rn(__uint_as_float(xwords[w] & 0xFFFF0000u),
+                                             __uint_as_float(cwords[w] & 0xFFFF0000u)), mv[2 * w + 1]);
+              o[w] = pack_bf16x2(lo, hi);
+            }
+          }
+          *reinterpret_cast<uint4*>(stage + sw128_offset(r, half * 32 + j * 8)) = out;
+        }
+        fence_proxy_async();
+        mbar_arrive(&bars[A_FULL + s]);
+      }
+      if (ok) ok = mbar_wait(&bars[ACC_DONE], 0, abort_flag, 450);
+      if (ok) {
+        tc_fence_after();
+        const int nc = p.NACC * p.NB;
+        const int tok = m0 + row;
+#pragma unroll 1
+        for (int cc = wg; cc < nc / 32; cc += 2) {
+          const int col = cc * 32, acc = col / p.NB;
+          float v[32];
+          tmem_ld32(tmem_base + lane_sel + acc * 256 + (col - acc * p.NB), v);
+          if (tok < p.S) {
+            uint16_t* dst = p.coeff + static_cast<size_t>(tok) * p.n_total + n_base + col;
+#pragma unroll
+            for (int j4 = 0; j4 < 4; ++j4) {
+              uint4 w;
+              w.x = pack_bf16x2(v[j4 * 8 + 0], v[j4 * 8 + 1]);
+              w.y = pack_bf16x2(v[j4 * 8 + 2], v[j4 * 8 + 3]);
+              w.z = pack_bf16x2(v[j4 * 8 + 4], v[j4 * 8 + 5]);
+              w.w = pack_bf16x2(v[j4 * 8 + 6], v[j4 * 8 + 7]);
+              *reinterpret_cast<uint4*>(dst + j4 * 8) = w;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc(tmem_base, 512);
+}
+
+// split n_total columns into grid.y CTAs x NACC accumulators x NB columns
+bool plan_columns(int n_total, int* gy, int* nacc, int* nb) {
+  for (int g = 1; g <= 16; ++g) {
+    if (n_total % g) continue;
+    int nc = n_total / g;
+    if (nc <= 256 && nc % 32 == 0) { *gy = g; *nacc = 1; *nb = nc; return true; }
+    if (nc <= 512 && nc % 64 == 0) { *gy = g; *nacc = 2; *nb = nc / 2; return true; }
+  }
+  return false;
+}
+
+size_t smem_bytes(int nacc, int nb, int n_total) {
+  return 2 * static_cast<size_t>(A_BYTES + nacc * nb * 128) + 128 + 4 * (256 + 128 + 128) +
+         8 * static_cast<size_t>(n_total) + 1024;
+}
+
+}  // namespace
+
+bool tc_project_supported(int J, int r) {
+  int gy, nacc, nb;
+  return J % 64 == 0 && plan_columns(r, &gy, &nacc, &nb) &&
+         smem_bytes(nacc, nb, 0) <= 232448;
+}
+
+bool tc_assign_supported(int J, int C) {
+  if (J % 64 || C % 16 || C > 512) return false;
+  return C <= 256 || C % 64 == 0;
+}
+
+int tc_project(const void* x_bf16, const void* centers_bf16, const void* ids, int id_bytes,
+               const float* mean, const void* encoder_bf16, int S, int J, int r, void* coeff,
+               cudaStream_t stream) {
+  if (S == 0) return NKV_OK;
+  Params p{};
+  int gy;
+  NKV_REQUIRE(plan_columns(r, &gy, &p.NACC, &p.NB), NKV_ERR_UNSUPPORTED,
+              "projection rank %d cannot be tiled", r);
+  NKV_REQUIRE((reinterpret_cast<uintptr_t>(x_bf16) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(centers_bf16) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(mean) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(coeff) & 15) == 0,
+              NKV_ERR_INVALID, "projection operands must be 16-byte aligned");
+  p.S = S; p.J = J; p.n_total = r;
+  p.x = static_cast<const uint16_t*>(x_bf16);
+  p.centers = static_cast<const uint16_t*>(centers_bf16);
+  p.ids = ids; p.id_bytes = id_bytes; p.mean = mean;
+  p.coeff = static_cast<uint16_t*>(coeff);
+  CUtensorMap map_b;
+  uint64_t dims[2] = {static_cast<uint64_t>(J), static_cast<uint64_t>(r)};
+  uint64_t strides[1] = {static_cast<uint64_t>(J) * 2};
+  uint32_t box[2] = {64, static_cast<uint32_t>(p.NB)};
+  int rc = encode_tensor_map(&map_b, 2, encoder_bf16, 2, dims, strides, box, true);
+  if (rc != NKV_OK) return rc;
+  size_t smem = smem_bytes(p.NACC, p.NB, 0);
+  auto kernel = encode_gemm_kernel<false>;
+  NKV_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                static_cast<int>(smem)));
+  dim3 grid(ceil_div(S, TM), gy);
+  kernel<<<grid, THREADS, smem, stream>>>(map_b, map_b, p);
+  NKV_LAUNCH_CHECK("encode_gemm_kernel<project>");
+  return NKV_OK;
+}
+
+int tc_assign(const void* x_bf16, const void* centers_bf16, int S, int J, int C, void* ids,
+              int id_bytes, cudaStream_t stream) {
+  if (S == 0) return NKV_OK;
+  Params p{};
+  p.S = S; p.J = J; p.n_total = C;
+  p.NACC = C > 256 ? 2 : 1;
+  p.NB = C / p.NACC;
+  p.ids_out = ids; p.id_bytes = id_bytes;
+  CUtensorMap map_a, map_b;
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(J), static_cast<uint64_t>(S)};
+    uint64_t strides[1] = {static_cast<uint64_t>(J) * 2};
+    uint32_t box[2] = {64, TM};
+    int rc = encode_tensor_map(&map_a, 2, x_bf16, 2, dims, strides, box, true);
+    if (rc != NKV_OK) return rc;
+  }
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(J), static_cast<uint64_t>(C)};
+    uint64_t strides[1] = {static_cast<uint64_t>(J) * 2};
+    uint32_t box[2] = {64, static_cast<uint32_t>(p.NB)};
+    int rc = encode_tensor_map(&map_b, 2, centers_bf16, 2, dims, strides, box, true);
+    if (rc != NKV_OK) return rc;
+  }
+  size_t smem = smem_bytes(p.NACC, p.NB, C);
+  auto kernel = encode_gemm_kernel<true>;
+  NKV_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                static_cast<int>(smem)));
+  dim3 grid(ceil_div(S, TM), 1);
+  kernel<<<grid, THREADS, smem, stream>>>(map_a, map_b, p);
+  NKV_LAUNCH_CHECK("encode_gemm_kernel<assign>");
+  return NKV_OK;
+}
+
+}  // namespace nkv

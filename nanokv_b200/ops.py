@@ -1,0 +1,217 @@
+"""Tensor-level wrappers over the C ABI.
+
+Each function takes CUDA tensors, enqueues on torch's current stream and
+returns without synchronising.  PyTorch is used for device memory and streams
+only; all arithmetic happens in libnanokv_b200.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from ._lib import NKV_BF16, NKV_F16, NKV_F32, NKV_QUANT_F32, NKV_QUANT_IN_BF16, History
+
+_DTYPE = {torch.float32: NKV_F32, torch.bfloat16: NKV_BF16, torch.float16: NKV_F16}
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE[dtype]
+    except KeyError:
+        raise ValueError(f"unsupported dtype {dtype}") from None
+
+
+def _ptr(tensor: torch.Tensor | None):
+    return None if tensor is None else ctypes.c_void_p(tensor.data_ptr())
+
+
+def _stream(device: torch.device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _require_cuda(*tensors: torch.Tensor) -> torch.device:
+    device = None
+    for tensor in tensors:
+        if tensor is None:
+            continue
+        if not tensor.is_cuda:
+            raise RuntimeError("nanokv_b200 runs on CUDA tensors only (there is no CPU path)")
+        if not tensor.is_contiguous():
+            raise ValueError("nanokv_b200 expects contiguous tensors")
+        device = device or tensor.device
+    return device
+
+
+def id_dtype(clusters: int) -> torch.dtype:
+    """uint8 ids up to 256 centres (the reference's storage), int16 bit patterns beyond."""
+    return torch.uint8 if clusters <= 256 else torch.int16
+
+
+# --------------------------------------------------------------------------- encode
+def assign(x: torch.Tensor, centers: torch.Tensor, ids: torch.Tensor | None = None) -> torch.Tensor:
+    """Nearest-centre ids of rows x [S,J] against centers [C,J]."""
+    device = _require_cuda(x, centers, ids)
+    S, J = x.shape
+    C = centers.shape[0]
+    if ids is None:
+        ids = torch.empty(S, dtype=id_dtype(C), device=device)
+    _lib.check(_lib.library().nkv_assign(
+        _ptr(x), dtype_code(x.dtype), _ptr(centers), dtype_code(centers.dtype), S, J, C,
+        _ptr(ids), ids.element_size(), _stream(device)))
+    return ids
+
+
+def kmeans(x: torch.Tensor, clusters: int, iters: int, init_rows: torch.Tensor, *,
+           centers: torch.Tensor | None = None, ids: torch.Tensor | None = None):
+    """Online C-means of one chunk -> (stored centres bf16 [C,J], ids [S])."""
+    device = _require_cuda(x, centers, ids)
+    S, J = x.shape
+    lib = _lib.library()
+    if not 0 < clusters <= S:
+        raise ValueError(f"clusters must be in [1, S]; got {clusters} for S={S}")
+    if centers is None:
+        centers = torch.empty(clusters, J, dtype=torch.bfloat16, device=device)
+    if ids is None:
+        ids = torch.empty(S, dtype=id_dtype(clusters), device=device)
+    nbytes = lib.nkv_kmeans_workspace_bytes(S, J, clusters)
+    workspace = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    init_rows = init_rows.to(device=device, dtype=torch.int32).contiguous()
+    _lib.check(lib.nkv_kmeans(
+        _ptr(x), dtype_code(x.dtype), S, J, clusters, iters, _ptr(init_rows), _ptr(centers),
+        _ptr(ids), ids.element_size(), _ptr(workspace), nbytes, _stream(device)))
+    return centers, ids
+
+
+def project(x, centers_bf16, ids, mean, encoder) -> torch.Tensor:
+    """coeff [S,r] = ((x - centre[id]) - mean) @ encoder^T in the encoder dtype."""
+    device = _require_cuda(x, centers_bf16, ids, mean, encoder)
+    S, J = x.shape
+    r = encoder.shape[0]
+    coeff = torch.empty(S, r, dtype=encoder.dtype, device=device)
+    _lib.check(_lib.library().nkv_project(
+        _ptr(x), dtype_code(x.dtype), _ptr(centers_bf16), _ptr(ids), ids.element_size(),
+        _ptr(mean), _ptr(encoder), dtype_code(encoder.dtype), S, J, r, _ptr(coeff),
+        _stream(device)))
+    return coeff
+
+
+def quant_pack(coeff, *, group=None, eps=1.1920928955078125e-07, in_coeff_dtype=False,
+               scale_dtype=torch.bfloat16, codes=None, scales=None):
+    """INT4 quantise + pack -> (codes u8 [S,r/2], scales [S,r/group])."""
+    device = _require_cuda(coeff, codes, scales)
+    S, r = coeff.shape
+    group = r if group is None else int(group)
+    if codes is None:
+        codes = torch.empty(S, r // 2, dtype=torch.uint8, device=device)
+    if scales is None:
+        scales = torch.empty(S, r // group, dtype=scale_dtype, device=device)
+    _lib.check(_lib.library().nkv_quant_pack(
+        _ptr(coeff), dtype_code(coeff.dtype), S, r, group, float(eps),
+        NKV_QUANT_IN_BF16 if in_coeff_dtype else NKV_QUANT_F32, dtype_code(scales.dtype),
+        _ptr(codes), _ptr(scales), _stream(device)))
+    return codes, scales
+
+
+# ---------------------------------------------------------------------- history view
+@dataclass
+class HistoryView:
+    """Device arrays of one compressed tensor plus the struct the ABI takes."""
+    codes: torch.Tensor
+    scales: torch.Tensor
+    ids: torch.Tensor
+    centers: torch.Tensor
+    seg_start: torch.Tensor
+    seg_center_row: torch.Tensor
+    tokens: int
+    segments: int
+    rank: int
+    group: int
+
+    def struct(self) -> History:
+        return History(
+            self.codes.data_ptr(), self.scales.data_ptr(), self.ids.data_ptr(),
+            self.centers.data_ptr(), self.seg_start.data_ptr(), self.seg_center_row.data_ptr(),
+            self.tokens, self.segments, self.rank, self.group, dtype_code(self.scales.dtype),
+            self.ids.element_size(), self.centers.shape[0], self.centers.shape[1])
+
+
+def decode_rows(view: HistoryView, decoder, mean, *, rows=None, dtype=None) -> torch.Tensor:
+    """Reconstruct rows (all, or those listed in ``rows``) -> [n, J]."""
+    device = _require_cuda(decoder, mean, rows)
+    J = decoder.shape[0]
+    n = view.tokens if rows is None else rows.numel()
+    dtype = decoder.dtype if dtype is None else dtype
+    out = torch.empty(n, J, dtype=dtype, device=device)
+    if rows is not None:
+        rows = rows.to(dtype=torch.int32).contiguous()
+    struct = view.struct()
+    _lib.check(_lib.library().nkv_decode_rows(
+        ctypes.byref(struct), _ptr(rows), n, _ptr(decoder), dtype_code(decoder.dtype), _ptr(mean),
+        J, _ptr(out), dtype_code(dtype), _stream(device)))
+    return out
+
+
+# ------------------------------------------------------------------------ attention
+def attn_codec(q, view_k: HistoryView, view_v: HistoryView, wk, bias_k, wv, bias_v, *,
+               scale: float, status: torch.Tensor | None = None):
+    """Fused read: q [Q,H,dk] -> (O [Q,H,dv], lse f32 [Q,H]).
+
+    wk [H,dk,r], wv [H,dv,r] in q's dtype; bias f32 [H,dk] / [H,dv].
+    """
+    device = _require_cuda(wk, bias_k, wv, bias_v, status)
+    if not q.is_cuda:
+        raise RuntimeError("nanokv_b200 runs on CUDA tensors only (there is no CPU path)")
+    Q, H, dk = q.shape
+    dv = wv.shape[1]
+    if q.stride(2) != 1:
+        raise ValueError("queries must be contiguous along the head dimension")
+    out = torch.empty(Q, H, dv, dtype=q.dtype, device=device)
+    lse = torch.empty(Q, H, dtype=torch.float32, device=device)
+    sk, sv = view_k.struct(), view_v.struct()
+    _lib.check(_lib.library().nkv_attn_codec(
+        _ptr(q), dtype_code(q.dtype), q.stride(0), q.stride(1), Q, H, dk, dv, ctypes.byref(sk),
+        ctypes.byref(sv), _ptr(wk), _ptr(bias_k), _ptr(wv), _ptr(bias_v), float(scale), _ptr(out),
+        _ptr(lse), _ptr(status), _stream(device)))
+    return out, lse
+
+
+def attention_lse(q, k, v, *, scale: float):
+    """Plain attention: q [Q,H,d], k [N,H,d], v [N,H,dv] -> (O [Q,H,dv], lse [Q,H])."""
+    device = _require_cuda(q, k, v)
+    Q, H, d = q.shape
+    N, dv = k.shape[0], v.shape[2]
+    out = torch.empty(Q, H, dv, dtype=q.dtype, device=device)
+    lse = torch.empty(Q, H, dtype=torch.float32, device=device)
+    if k.stride() != v.stride() and d == dv:
+        raise ValueError("k and v must share a layout")
+    _lib.check(_lib.library().nkv_attention_lse(
+        _ptr(q), _ptr(k), _ptr(v), dtype_code(q.dtype), q.stride(0), q.stride(1), k.stride(0),
+        k.stride(1), Q, N, H, d, dv, float(scale), _ptr(out), _ptr(lse), _stream(device)))
+    return out, lse
+
+
+def lse_merge(partials):
+    """[(O [rows..., d], lse [rows...])] -> merged (O, lse); an empty partition is (0, -inf)."""
+    outs = [o for o, _ in partials]
+    lses = [l for _, l in partials]
+    device = _require_cuda(*outs, *lses)
+    first = outs[0]
+    d = first.shape[-1]
+    rows = first.numel() // d
+    out = torch.empty_like(first)
+    lse = torch.empty_like(lses[0])
+    n = len(partials)
+    out_ptrs = (ctypes.c_void_p * n)(*[o.data_ptr() for o in outs])
+    lse_ptrs = (ctypes.c_void_p * n)(*[l.data_ptr() for l in lses])
+    _lib.check(_lib.library().nkv_lse_merge(
+        out_ptrs, lse_ptrs, n, rows, d, dtype_code(first.dtype), _ptr(out), _ptr(lse),
+        _stream(device)))
+    return out, lse
+
+
+def force_simt(on: bool) -> None:
+    """Triage hook: run bf16 work on the fp32 CUDA-core kernels (same rounding points)."""
+    _lib.library().nkv_debug_force_simt(1 if on else 0)

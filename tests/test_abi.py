@@ -1,0 +1,61 @@
+"""The C ABI: the library builds, loads, and exports every symbol the header declares."""
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "nanokv_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(nkv_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_symbols()
+    for required in ("nkv_assign", "nkv_kmeans", "nkv_project", "nkv_quant_pack",
+                     "nkv_encode_append", "nkv_decode_rows", "nkv_attn_codec",
+                     "nkv_attention_lse", "nkv_lse_merge", "nkv_status_string", "nkv_version"):
+        assert required in names
+
+
+def test_library_exports_every_declared_symbol():
+    from nanokv_b200 import _lib
+    lib = _lib.library()
+    for name in declared_symbols():
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
+    assert lib.nkv_version() == 1
+    assert lib.nkv_status_string(0) == b"ok"
+    assert lib.nkv_status_string(-4) == b"device-side wait gave up"
+
+
+def test_argument_errors_need_no_gpu():
+    """Validation happens before any CUDA call, so bad arguments are reported on any host."""
+    from nanokv_b200 import _lib
+    lib = _lib.library()
+    status = lib.nkv_quant_pack(None, _lib.NKV_BF16, 4, 64, 48, 1e-7, 0, _lib.NKV_BF16, None,
+                                None, None)
+    assert status == _lib.NKV_ERR_INVALID
+    assert b"group" in lib.nkv_last_error()
+    with pytest.raises(ValueError):
+        _lib.check(status)
+    status = lib.nkv_assign(None, _lib.NKV_BF16, None, _lib.NKV_BF16, 8, 64, 300, None, 1, None)
+    assert status == _lib.NKV_ERR_INVALID
+
+
+def test_product_path_has_no_cpu_fallback():
+    import torch
+    from nanokv_b200 import ops
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        ops.quant_pack(torch.zeros(4, 64))
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        ops.assign(torch.zeros(4, 64), torch.zeros(2, 64))
+
+
+def test_product_never_imports_the_oracle():
+    for path in (ROOT / "nanokv_b200").rglob("*.py"):
+        text = path.read_text()
+        assert "oracle" not in text.replace("no CPU", ""), f"{path} mentions the oracle"

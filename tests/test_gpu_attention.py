@@ -1,0 +1,204 @@
+"""GPU parity of the read path: decode, fused codec-attention, merge, hybrid attention."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from helpers import (BF16_REL_TOL, F32_REL_TOL, device_operator, history_from_segments, rel_err)
+from nanokv_b200 import attention, codec, ops, synthetic
+from oracle import nkv_oracle as oracle
+from test_oracle_golden import encode_all, from_bits, load
+
+pytestmark = pytest.mark.gpu
+
+
+def oracle_segments(case):
+    data = cases.build(case)
+    return data, encode_all(case, data)
+
+
+@pytest.mark.parametrize("case", [cases.MINI_F32, cases.MINI_BF16], ids=lambda c: c.name)
+def test_decode_rows_matches_oracle(case):
+    data, segments = oracle_segments(case)
+    dtype = case.shape.torch_dtype
+    for kind in ("k", "v"):
+        op = data[f"{kind}_op"]
+        hist = history_from_segments(segments[kind], joint=case.shape.joint, rank=case.shape.rank)
+        want = torch.cat([oracle.decode_rows(s, decoder=op["decoder"], mean=op["mean"], dtype=dtype)
+                          for s in segments[kind]], 1)[0]
+        dev = device_operator(op)
+        got = codec.decode(hist, dev, dtype=dtype).cpu()
+        if dtype == torch.float32:
+            assert torch.allclose(got, want, rtol=1e-5, atol=1e-5)
+        else:
+            assert rel_err(got, want) <= 2.0 ** -7
+            assert float((got != want).float().mean()) < 0.02
+        rows = torch.tensor([0, 299, 300, 511, 17, 17], dtype=torch.int32)
+        picked = codec.decode(hist, dev, rows=rows.cuda(), dtype=dtype).cpu()
+        assert torch.equal(picked, got[rows.long()])
+
+
+def run_codec_attention(case, data, segments, *, group=None, scale_dtype=torch.bfloat16):
+    ops_k, ops_v = device_operator(data["k_op"]), device_operator(data["v_op"])
+    hist_k = history_from_segments(segments["k"], joint=case.shape.joint, rank=case.shape.rank,
+                                   group=group, scale_dtype=scale_dtype)
+    hist_v = history_from_segments(segments["v"], joint=case.shape.joint, rank=case.shape.rank,
+                                   group=group, scale_dtype=scale_dtype)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out, lse = attention.codec_attention(data["q"].cuda(), hist_k, hist_v, ops_k, ops_v,
+                                         status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, f"device-side wait gave up at site {int(status.item())}"
+    return out.cpu(), lse.cpu()
+
+
+@pytest.mark.parametrize("case", [cases.MINI_F32, cases.C1], ids=lambda c: c.name)
+def test_codec_attention_f32_against_reference_fixture(case):
+    gold = load(case.name)
+    data, segments = oracle_segments(case)
+    out, lse = run_codec_attention(case, data, segments)
+    want_rows = torch.from_numpy(gold["attn_rows"])            # [H, Q/stride, D]
+    got_rows = out.permute(1, 0, 2)[:, ::case.attn_stride]
+    assert rel_err(got_rows, want_rows) <= F32_REL_TOL
+    assert float((lse.t() - torch.from_numpy(gold["lse"])).abs().max()) <= F32_REL_TOL
+
+
+def test_codec_attention_bf16_against_reference_fixture():
+    case = cases.MINI_BF16
+    gold = load(case.name)
+    data, segments = oracle_segments(case)
+    out, lse = run_codec_attention(case, data, segments)
+    want_rows = from_bits(gold["attn_rows"], torch.bfloat16)
+    assert rel_err(out.permute(1, 0, 2), want_rows) <= BF16_REL_TOL
+    assert float((lse.t() - torch.from_numpy(gold["lse"])).abs().max()) <= BF16_REL_TOL
+
+
+@pytest.mark.parametrize("heads,rank,history,queries,group,scale_dtype", [
+    (2, 64, 128, 128, None, torch.bfloat16),      # exactly one tile each way
+    (2, 64, 1, 1, None, torch.bfloat16),          # single token, single query
+    (3, 128, 517, 300, None, torch.bfloat16),     # ragged everything, two query tiles
+    (2, 192, 700, 257, 32, torch.float16),        # grouped scales in fp16
+    (2, 640, 300, 130, None, torch.bfloat16),     # Wan-shaped rank
+])
+def test_codec_attention_bf16_shapes(heads, rank, history, queries, group, scale_dtype):
+    shape = synthetic.Shape("t", heads, 128, rank, 8, history, queries, "bf16")
+    segs = (history,) if history < 200 else (history - 130, 130)
+    case = cases.CodecCase("t", shape, segs, seed=31, mean_std=0.05)
+    data = cases.build(case)
+    segments = {"k": [], "v": []}
+    for kind in ("k", "v"):
+        op = data[f"{kind}_op"]
+        for chunk in data[f"{kind}_chunks"]:
+            segments[kind].append(oracle.encode_rows(
+                chunk[None], encoder=op["encoder"], mean=op["mean"],
+                centers=data[f"{kind}_true_centers"][None].to(torch.bfloat16), group=group,
+                scale_dtype=scale_dtype))
+    out, lse = run_codec_attention(case, data, segments, group=group, scale_dtype=scale_dtype)
+    k_op, v_op = data["k_op"], data["v_op"]
+    want, want_lse = oracle.codec_attention(
+        data["q"][None], segments["k"], segments["v"], k_decoder=k_op["decoder"],
+        k_mean=k_op["mean"], v_decoder=v_op["decoder"], v_mean=v_op["mean"], heads=heads,
+        dtype=torch.bfloat16)
+    assert rel_err(out, want[0]) <= BF16_REL_TOL
+    assert float((lse - want_lse[0].t()).abs().max()) <= BF16_REL_TOL
+
+
+def test_codec_attention_bf16_tensor_core_vs_cuda_core_emulation():
+    """Same inputs through the tcgen05 kernel and the fp32 CUDA-core kernel with bf16 rounding."""
+    shape = synthetic.Shape("t", 4, 128, 256, 16, 1500, 520, "bf16")
+    case = cases.CodecCase("t", shape, (700, 800), seed=41, mean_std=0.05)
+    data, segments = oracle_segments(case)
+    out_tc, lse_tc = run_codec_attention(case, data, segments)
+    ops.force_simt(True)
+    try:
+        out_sm, lse_sm = run_codec_attention(case, data, segments)
+    finally:
+        ops.force_simt(False)
+    assert rel_err(out_tc, out_sm) <= BF16_REL_TOL
+    assert float((lse_tc - lse_sm).abs().max()) <= 5e-3
+
+
+def test_codec_attention_empty_history():
+    shape = synthetic.Shape("t", 2, 128, 64, 8, 0, 40, "bf16")
+    gen = synthetic.generator(1)
+    op = device_operator(synthetic.make_operator(shape, gen))
+    hist = history_from_segments([], joint=256, rank=64)
+    q = synthetic.make_queries(shape, gen).cuda()
+    for query in (q, q.float()):
+        opx = op if query.dtype == torch.bfloat16 else device_operator(
+            synthetic.make_operator(shape, gen, dtype=torch.float32))
+        out, lse = attention.codec_attention(query, hist, hist, opx, opx)
+        assert float(out.abs().max()) == 0.0
+        assert bool(torch.isinf(lse).all()) and bool((lse < 0).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_plain_attention_lse(dtype):
+    gen = synthetic.generator(5)
+    q = torch.randn(200, 3, 128, generator=gen).to(dtype)
+    k = torch.randn(333, 3, 128, generator=gen).to(dtype)
+    v = torch.randn(333, 3, 128, generator=gen).to(dtype)
+    want, want_lse = oracle.attention_lse(q.permute(1, 0, 2)[None], k.permute(1, 0, 2)[None],
+                                          v.permute(1, 0, 2)[None])
+    out, lse = ops.attention_lse(q.cuda(), k.cuda(), v.cuda(), scale=128 ** -0.5)
+    tol = F32_REL_TOL if dtype == torch.float32 else BF16_REL_TOL
+    assert rel_err(out.cpu(), want[0].permute(1, 0, 2)) <= tol
+    assert float((lse.cpu() - want_lse[0].t()).abs().max()) <= tol
+
+
+def test_merge_edge_cases_against_reference_fixture():
+    gold = load("merge_edge")
+    out_a, lse_a, out_b, lse_b = (t.cuda() for t in cases.build_merge())
+    out, lse = attention.merge(out_a, lse_a, out_b, lse_b)
+    want = from_bits(gold["out"], torch.bfloat16)
+    want_lse = torch.from_numpy(gold["lse"])
+    got_lse = lse.cpu()
+    finite = torch.isfinite(want_lse)
+    assert torch.equal(torch.isfinite(got_lse), finite)
+    assert torch.allclose(got_lse[finite], want_lse[finite], rtol=1e-6, atol=1e-6)
+    assert rel_err(out.cpu(), want) <= 2.0 ** -7
+    assert float(out.cpu()[0, 0, 2:4].abs().max()) == 0.0    # both partitions empty -> zeros
+
+
+def test_merge_many_partitions_equals_unsplit_attention():
+    gen = synthetic.generator(6)
+    q = torch.randn(150, 2, 128, generator=gen).cuda()
+    k = torch.randn(1000, 2, 128, generator=gen).cuda()
+    v = torch.randn(1000, 2, 128, generator=gen).cuda()
+    scale = 128 ** -0.5
+    whole, whole_lse = ops.attention_lse(q, k, v, scale=scale)
+    bounds = [0, 100, 100, 400, 777, 1000]        # includes an empty shard
+    parts = [ops.attention_lse(q, k[a:b].contiguous(), v[a:b].contiguous(), scale=scale)
+             for a, b in zip(bounds[:-1], bounds[1:])]
+    out, lse = ops.lse_merge(parts)
+    assert rel_err(out.cpu(), whole.cpu()) <= 1e-5
+    assert float((lse - whole_lse).abs().max()) <= 1e-5
+
+
+@pytest.mark.parametrize("case", cases.FAST_CASES, ids=lambda c: c.name)
+def test_hybrid_attention_against_reference_fixture(case):
+    gold = load(case.name)
+    codec_case = case.codec
+    shape = codec_case.shape
+    dtype = shape.torch_dtype
+    data, segments = oracle_segments(codec_case)
+    low = case.low_segments
+    ops_k, ops_v = device_operator(data["k_op"]), device_operator(data["v_op"])
+    low_k = history_from_segments(segments["k"][:low], joint=shape.joint, rank=shape.rank)
+    low_v = history_from_segments(segments["v"][:low], joint=shape.joint, rank=shape.rank)
+    native = []
+    for sk, sv in zip(segments["k"][low:], segments["v"][low:]):
+        hk = history_from_segments([sk], joint=shape.joint, rank=shape.rank)
+        hv = history_from_segments([sv], joint=shape.joint, rank=shape.rank)
+        native.append((codec.decode(hk, ops_k, dtype=dtype).view(-1, shape.heads, shape.head_dim),
+                       codec.decode(hv, ops_v, dtype=dtype).view(-1, shape.heads, shape.head_dim)))
+    reader = attention.Reader(cases.build_reader(case, data), dtype=dtype)
+    q = data["q"].cuda()
+    got = attention.hybrid_attention(
+        q, q, native, [{"k": low_k, "v": low_v, "k_mean": ops_k.mean, "v_mean": ops_v.mean}],
+        reader)
+    want = from_bits(gold["hybrid"], dtype)                  # [H, Q, D]
+    tol = F32_REL_TOL if dtype == torch.float32 else BF16_REL_TOL
+    assert rel_err(got.cpu().permute(1, 0, 2), want) <= tol
