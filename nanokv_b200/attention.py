@@ -91,7 +91,8 @@ class ReaderGroup:
             table = table.index_select(1, self.heads).to(self.dtype)
             projected = self._pad_last(torch.einsum("chd,hde->che", table, affine))
             self._tables = {k: v for k, v in self._tables.items() if k[0] != id(hist) or k[1] != target}
-            self._tables[key] = projected.reshape(projected.shape[0], -1).contiguous()
+            # stored like every centre table: bf16
+            self._tables[key] = projected.reshape(projected.shape[0], -1).to(torch.bfloat16).contiguous()
         view = hist.view()
         view.centers = self._tables[key]
         return view
