@@ -1,0 +1,376 @@
+"""Headline benchmark: fused INT4 codec-attention (and encode) on the Wan-shaped history.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one pass of codec-attention over every layer's compressed history
+(99,840 tokens per layer, 4,680 queries, 40 layers, H 40 x D 128, rank 640,
+512 centres) on synthetic, seeded inputs.  With N > 1 (torchrun) the history
+is sharded by token range over the ranks; each rank attends its shard, the
+(O, lse) partials are all-gathered over NCCL and merged by log-sum-exp.
+Rank 0 prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+from nanokv_b200 import synthetic  # noqa: E402
+
+SHAPE = synthetic.CONFIGS["c3_wan_shaped"]
+FRAME = 1560
+METRIC = "codec_attention_history_tokens_per_s"
+UNIT = "history-tokens/s"
+
+
+def measured_peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def attention_flops(tokens: int, queries: int, joint: int, rank: int) -> float:
+    """Algorithmic flops of one layer: QK^T + PV (4*Q*J) plus one decode of K and V (4*r*J)."""
+    return float(tokens) * (4.0 * queries * joint + 4.0 * rank * joint)
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "200"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, peak, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for row in self.rows:
+            if len(row) < 9:
+                continue
+            try:
+                clocks.append(float(row[1]))
+                peak = float(row[2])
+            except ValueError:
+                continue
+            for name, flag in zip(names, row[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": peak,
+                "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------- workload
+def build_layers(shape, frames: range, layers: int, device, encode_frames: int = 8):
+    """Encode this rank's frames of every layer into compressed histories (fixed centres).
+
+    Returns (layer list, seconds spent in encode kernels, tokens encoded).  Rows are
+    drawn on the device from a seeded generator: centre[uniform id] + 0.3 * N(0,1).
+    """
+    from nanokv_b200.cache import CompressedHistory
+    from nanokv_b200.codec import Operator, QuantSpec, encode_append
+    gen = torch.Generator(device=device).manual_seed(1234)
+    tokens = len(frames) * FRAME
+    segments = (len(frames) + encode_frames - 1) // encode_frames
+    result = []
+    quant = QuantSpec()
+    for layer in range(layers):
+        entry = {}
+        for kind in ("k", "v"):
+            cpu_gen = synthetic.generator(1000 * layer + (kind == "v"))
+            operator = synthetic.make_operator(shape, cpu_gen)
+            op = Operator(operator["mean"], operator["encoder"], operator["decoder"], device=device)
+            centers = torch.randn(shape.centers, shape.joint, generator=gen, device=device)
+            hist = CompressedHistory(joint=shape.joint, rank=shape.rank, capacity=max(tokens, 1),
+                                     max_segments=max(segments, 1),
+                                     centers_per_segment=shape.centers, device=device,
+                                     shared_centers=True)
+            hist.centers.copy_(centers.to(torch.bfloat16))
+            for first in range(0, len(frames), encode_frames):
+                count = min(encode_frames, len(frames) - first) * FRAME
+                pick = torch.randint(shape.centers, (count,), generator=gen, device=device)
+                rows = centers.index_select(0, pick)
+                rows.add_(torch.randn(count, shape.joint, generator=gen, device=device), alpha=0.3)
+                encode_append(hist, rows.to(torch.bfloat16), op, quant, centers="resident")
+            entry[kind] = (hist, op)
+        result.append(entry)
+    return result
+
+
+def time_encode(shape, device, steps: int, warmup: int, frames: int = 8):
+    """Encode tokens/s: K and V rows of `frames` frames (fixed centres), device resident."""
+    from nanokv_b200.cache import CompressedHistory
+    from nanokv_b200.codec import Operator, QuantSpec, encode_append
+    gen = torch.Generator(device=device).manual_seed(77)
+    cpu_gen = synthetic.generator(5)
+    operator = synthetic.make_operator(shape, cpu_gen)
+    op = Operator(operator["mean"], operator["encoder"], operator["decoder"], device=device)
+    centers = torch.randn(shape.centers, shape.joint, generator=gen, device=device)
+    count = frames * FRAME
+    pick = torch.randint(shape.centers, (count,), generator=gen, device=device)
+    rows = (centers.index_select(0, pick) +
+            0.3 * torch.randn(count, shape.joint, generator=gen, device=device)).to(torch.bfloat16)
+    total = steps + warmup
+    hist = CompressedHistory(joint=shape.joint, rank=shape.rank, capacity=count * total * 2,
+                             max_segments=2 * total, centers_per_segment=shape.centers,
+                             device=device, shared_centers=True)
+    hist.centers.copy_(centers.to(torch.bfloat16))
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for index in range(total):
+        if index == warmup:
+            torch.cuda.synchronize()
+            start.record()
+        encode_append(hist, rows, op, QuantSpec(), centers="resident")   # "K"
+        encode_append(hist, rows, op, QuantSpec(), centers="resident")   # "V"
+    stop.record()
+    torch.cuda.synchronize()
+    seconds = start.elapsed_time(stop) / 1e3 / steps
+    flops = count * 2 * 2.0 * shape.joint * (shape.centers + shape.rank)
+    bytes_ = count * 2 * (shape.joint * 2 + shape.rank // 2 + 2 + 2)
+    return {"tokens_per_s": count / seconds, "ms": seconds * 1e3, "tokens_per_call": count,
+            "tflops": flops / seconds / 1e12, "gbs": bytes_ / seconds / 1e9}
+
+
+def run_ours(args) -> dict:
+    import torch.distributed as dist
+    from nanokv_b200 import attention, context_parallel
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    shape, layers = SHAPE, args.layers
+    total_frames = shape.history // FRAME
+    bounds = context_parallel.shard_bounds(total_frames, world)
+    frames = range(*bounds[rank])
+    built = build_layers(shape, frames, layers, device)
+    local_tokens = len(frames) * FRAME
+    gen = synthetic.generator(4242)
+    q_host = synthetic.make_queries(shape, gen).pin_memory()          # same queries on every rank
+    q_dev = q_host.to(device, non_blocking=True)
+    out_host = torch.empty(shape.queries, shape.heads, shape.head_dim, dtype=torch.bfloat16).pin_memory()
+    lse_host = torch.empty(shape.queries, shape.heads, dtype=torch.float32).pin_memory()
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def step(host_io: bool):
+        merged = None
+        for entry in built:
+            q = q_host.to(device, non_blocking=True) if host_io else q_dev
+            (hk, ok), (hv, ov) = entry["k"], entry["v"]
+            out, lse = attention.codec_attention(q, hk, hv, ok, ov, status=status)
+            merged = context_parallel.gather_and_merge(out, lse)
+            if host_io:
+                out_host.copy_(merged[0], non_blocking=True)
+                lse_host.copy_(merged[1], non_blocking=True)
+        return merged
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(host_io: bool, steps: int, warmup: int) -> float:
+        for _ in range(warmup):
+            step(host_io)
+        barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            step(host_io)
+        stop.record()
+        barrier()
+        ms = torch.tensor([start.elapsed_time(stop)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()) / 1e3
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    seconds = timed(False, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    e2e_seconds = timed(True, max(1, args.steps // 2), 1)
+    e2e_steps = max(1, args.steps // 2)
+    if int(status.item()) != 0:
+        raise RuntimeError(f"device-side wait gave up at site {int(status.item())}")
+
+    # the dominant kernel alone, on this rank's shard: per-launch duration for the roofline
+    kernel_ms = []
+    entry = built[0]
+    (hk, ok), (hv, ov) = entry["k"], entry["v"]
+    for index in range(3 + 5):
+        other = built[index % len(built)]
+        (hk, ok), (hv, ov) = other["k"], other["v"]
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        attention.codec_attention(q_dev, hk, hv, ok, ov, status=status)
+        stop.record()
+        torch.cuda.synchronize()
+        if index >= 3:
+            kernel_ms.append(start.elapsed_time(stop))
+    kernel_s = statistics.mean(kernel_ms) / 1e3
+    encode = time_encode(shape, device, steps=5, warmup=3) if rank == 0 else None
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return {}
+    peaks, peak_kind = measured_peaks()
+    step_ms = seconds / args.steps * 1e3
+    tokens_per_step = shape.history * layers
+    flops_launch = attention_flops(local_tokens, shape.queries, shape.joint, shape.rank)
+    achieved = flops_launch / kernel_s / 1e12
+    peak = float(peaks["bf16_tflops_sustained"])
+    q_bytes = q_host.numel() * 2
+    o_bytes = out_host.numel() * 2 + lse_host.numel() * 4
+    cpu = cpu_baseline(shape) if world == 1 and not args.no_cpu else None
+    line = {
+        "metric": METRIC, "value": tokens_per_step / (seconds / args.steps), "unit": UNIT,
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": shape.name, "heads": shape.heads, "head_dim": shape.head_dim,
+                   "rank": shape.rank, "centers": shape.centers, "history_tokens": shape.history,
+                   "queries": shape.queries, "layers": layers, "quant_group": shape.rank,
+                   "scale_dtype": "bf16", "parallelism": f"cp{world}",
+                   "l2_policy": "inputs larger than L2 (distinct compressed history per layer)"},
+        "e2e": {"value": tokens_per_step / (e2e_seconds / e2e_steps), "unit": UNIT,
+                "h2d_bytes_per_step": q_bytes * layers, "d2h_bytes_per_step": o_bytes * layers},
+        "gpu_launches": args.steps * layers * (2 if world > 1 else 1),
+        "roofline": {"bound": "tensor", "kernel": "attn_codec_kernel<128>", "achieved": achieved,
+                     "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                     "peak_source": f"bf16_tflops_sustained of {peak_kind}",
+                     "launch_ms": kernel_s * 1e3, "flops_per_launch": flops_launch,
+                     "traffic": None},
+        "encode": encode,
+        "clocks": clocks,
+    }
+    if cpu:
+        line["cpu_baseline"] = cpu
+    if world > 1:
+        dist.destroy_process_group()
+    return line
+
+
+# ------------------------------------------------------------------ CPU baseline / reference arm
+def cpu_sample(shape, sample_tokens: int):
+    """The oracle port (CPU restatement of the reference) on a history subsample, all host threads."""
+    from oracle import nkv_oracle as oracle
+    torch.set_num_threads(os.cpu_count() or 1)
+    gen = synthetic.generator(9)
+    segments, ops_ = {"k": [], "v": []}, {}
+    for kind in ("k", "v"):
+        centers = synthetic.make_centers(shape, gen)
+        rows = synthetic.make_rows(sample_tokens, centers, gen, dtype=torch.bfloat16)
+        ops_[kind] = synthetic.make_operator(shape, gen)
+        segments[kind].append(oracle.encode_rows(
+            rows[None], encoder=ops_[kind]["encoder"], mean=ops_[kind]["mean"],
+            centers=centers[None].to(torch.bfloat16), eps=oracle.F32_EPS))
+    q = synthetic.make_queries(shape, gen)
+
+    def run():
+        return oracle.codec_attention(
+            q[None], segments["k"], segments["v"], k_decoder=ops_["k"]["decoder"],
+            k_mean=ops_["k"]["mean"], v_decoder=ops_["v"]["decoder"], v_mean=ops_["v"]["mean"],
+            heads=shape.heads, dtype=torch.bfloat16)
+    return run
+
+
+def cpu_baseline(shape, sample_tokens: int = 2048, runs: int = 2) -> dict:
+    run = cpu_sample(shape, sample_tokens)
+    run()
+    times = []
+    for _ in range(runs):
+        t0 = time.perf_counter()
+        run()
+        times.append(time.perf_counter() - t0)
+    seconds = statistics.median(times)
+    return {"value": sample_tokens / seconds, "unit": UNIT, "cores": torch.get_num_threads(),
+            "kind": "port",
+            "sample": f"one layer, {sample_tokens}-token history subsample x {shape.queries} queries, "
+                      f"decode K+V + tiled attention; linear in history length"}
+
+
+def run_reference(args) -> dict:
+    """Reference arm: the reference's CPU arithmetic (oracle port; the reference itself is a
+    Python tree that is not present on the benchmark host) on a bounded sample per step."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return {}
+    shape = SHAPE
+    sample = 1024
+    run = cpu_sample(shape, sample)
+    for _ in range(min(args.warmup, 1)):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        run()
+    seconds = (time.perf_counter() - t0) / args.steps
+    value = sample / seconds
+    desc = (f"one layer, {sample}-token history subsample x {shape.queries} queries per step, "
+            f"decode K+V + tiled attention; linear in history length")
+    return {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT,
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps,
+        "warmup": min(args.warmup, 1), "ms_per_step": seconds * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": shape.name, "heads": shape.heads, "head_dim": shape.head_dim,
+                   "rank": shape.rank, "centers": shape.centers, "history_tokens": shape.history,
+                   "queries": shape.queries, "layers": args.layers, "sample_tokens": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=3)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--layers", type=int, default=SHAPE.layers)
+    parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = parser.parse_args()
+    line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if line:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

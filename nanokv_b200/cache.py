@@ -22,7 +22,7 @@ class CompressedHistory:
     def __init__(self, *, joint: int, rank: int, capacity: int, max_segments: int,
                  centers_per_segment: int, group: int | None = None,
                  scale_dtype: torch.dtype = torch.bfloat16, device="cuda",
-                 center_width: int | None = None):
+                 center_width: int | None = None, shared_centers: bool = False):
         if rank % 2:
             raise ValueError("rank must be even")
         self.joint, self.rank = int(joint), int(rank)
@@ -39,7 +39,10 @@ class CompressedHistory:
                                   device=device)
         self.ids = torch.zeros(self.capacity, dtype=ops.id_dtype(self.centers_per_segment),
                                device=device)
-        self.centers = torch.zeros(self.max_segments * self.centers_per_segment, width,
+        # shared_centers: one externally supplied table serves every segment (fixed-centre form)
+        self.shared_centers = bool(shared_centers)
+        table_segments = 1 if self.shared_centers else self.max_segments
+        self.centers = torch.zeros(table_segments * self.centers_per_segment, width,
                                    dtype=torch.bfloat16, device=device)
         self.seg_start = torch.zeros(self.max_segments + 1, dtype=torch.int32, device=device)
         self.seg_center_row = torch.zeros(self.max_segments, dtype=torch.int32, device=device)
@@ -64,12 +67,18 @@ class CompressedHistory:
             raise ValueError(f"history capacity {self.capacity} exceeded")
         if self.segments + 1 > self.max_segments:
             raise ValueError(f"segment capacity {self.max_segments} exceeded")
-        if self._center_used + clusters > self.centers.shape[0]:
-            raise ValueError("centre table capacity exceeded")
-        offset, row = self.tokens, self._center_used
+        if self.shared_centers:
+            if clusters > self.centers.shape[0]:
+                raise ValueError("centre table capacity exceeded")
+            offset, row = self.tokens, 0
+            self._center_used = max(self._center_used, clusters)
+        else:
+            if self._center_used + clusters > self.centers.shape[0]:
+                raise ValueError("centre table capacity exceeded")
+            offset, row = self.tokens, self._center_used
+            self._center_used += clusters
         self._starts.append(offset + count)
         self._center_rows.append(row)
-        self._center_used += clusters
         index = self.segments - 1
         # two tiny async H2D-free updates of the device segment table
         self.seg_start[index + 1].fill_(offset + count)

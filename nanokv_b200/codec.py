@@ -64,7 +64,8 @@ def encode_append(hist: CompressedHistory, rows: torch.Tensor, op: Operator,
     """Encode rows [S,J] as one new segment of ``hist``; returns its token offset.
 
     centers=None runs the online C-means (the reference's semantic_residual);
-    otherwise the given stored centres [C,J] are used as they are.
+    a tensor [C,J] is stored and used as given; "resident" uses the table already
+    in a shared-centre history (``hist.centers``) without copying it again.
     """
     if rows.dim() != 2 or rows.shape[1] != hist.joint:
         raise ValueError(f"expected rows [S,{hist.joint}], got {tuple(rows.shape)}")
@@ -72,7 +73,13 @@ def encode_append(hist: CompressedHistory, rows: torch.Tensor, op: Operator,
         raise ValueError("quantiser spec does not match the history cache")
     rows = rows.contiguous()
     S = rows.shape[0]
-    clusters = int(centers.shape[0]) if centers is not None else int(clusters)
+    resident = isinstance(centers, str)
+    if resident and (centers != "resident" or not hist.shared_centers):
+        raise ValueError('centers="resident" needs a history built with shared_centers=True')
+    if resident:
+        clusters = hist.centers_per_segment
+    else:
+        clusters = int(centers.shape[0]) if centers is not None else int(clusters)
     if clusters > hist.centers_per_segment:
         raise ValueError("more centres than the cache reserves per segment")
     offset, center_rows = hist.reserve_segment(S, clusters)
@@ -87,7 +94,8 @@ def encode_append(hist: CompressedHistory, rows: torch.Tensor, op: Operator,
                        in_coeff_dtype=quant.in_coeff_dtype and coeff.dtype == torch.bfloat16,
                        codes=codes, scales=scales)
         return offset
-    center_rows.copy_(centers.to(torch.bfloat16))
+    if not resident:
+        center_rows.copy_(centers.to(torch.bfloat16))
     workspace = torch.empty(S, op.rank, dtype=op.dtype, device=rows.device)
     lib = _lib.library()
     in_bf16 = quant.in_coeff_dtype and op.dtype == torch.bfloat16
