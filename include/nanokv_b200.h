@@ -145,6 +145,35 @@ int nkv_encode_append(const void* x, int x_dtype, const void* centers_bf16, int 
                       uint8_t* codes, void* scales, void* ids,
                       void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * nkv_encode_append without caller-provided scratch and without any device
+ * allocation.  (No counterpart in the reference: its encoder allocates
+ * temporaries freely through PyTorch.)
+ * For hosts that may not allocate where they encode -- a server that gave the
+ * whole GPU to its own memory pool at start-up, a plugin that must not risk a
+ * synchronising or failing cudaMalloc in the middle of a rollout.  The
+ * coefficient scratch (S * r values of the encoder dtype) lives in a fixed
+ * array of NKV_STATIC_SCRATCH_BYTES inside the library's device image; every
+ * GPU that loads the library holds that array until the process exits.
+ * Limits and rules:
+ *  - S * r * sizeof(encoder element) must not exceed NKV_STATIC_SCRATCH_BYTES,
+ *    else NKV_ERR_TOO_LARGE (split the chunk, or use nkv_encode_append);
+ *  - the first call on each device looks the array's address up
+ *    (cudaGetSymbolAddress, with that device current); make that first call
+ *    before any stream capture;
+ *  - all calls on a device share the one array, so two calls whose kernels can
+ *    overlap on the GPU (different streams) race: keep calls stream-ordered.
+ *    Nothing has to be cleared between calls: each call overwrites every
+ *    coefficient it later reads.
+ * Arguments and results are those of nkv_encode_append.
+ */
+#define NKV_STATIC_SCRATCH_BYTES (4 * 1024 * 1024)
+int nkv_encode_append_static(const void* x, int x_dtype, const void* centers_bf16, int C,
+                             const float* mean, const void* encoder, int encoder_dtype,
+                             int S, int J, int r, int group, float eps, int quant_mode,
+                             int scale_dtype, int id_bytes, int offset,
+                             uint8_t* codes, void* scales, void* ids, void* stream);
+
 /* ------------------------------------------------------------------- decode */
 
 /*

@@ -45,6 +45,9 @@ SIGNATURES = {
     "nkv_encode_append": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                   c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
                                   c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "nkv_encode_append_static": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                         c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                         c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nkv_decode_rows": (c_int, [POINTER(History), c_void_p, c_int, c_void_p, c_int, c_void_p,
                                 c_int, c_void_p, c_int, c_void_p]),
     "nkv_attn_codec": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int,

@@ -18,7 +18,8 @@ PACKAGE = Path(__file__).resolve().parent
 CSRC = PACKAGE / "csrc"
 BUILD = PACKAGE / "_build"
 LIBRARY = BUILD / "libnanokv_b200.so"
-SOURCES = ("nkv_api.cu", "nkv_simt.cu", "nkv_elementwise.cu", "nkv_tc_attn.cu", "nkv_tc_encode.cu")
+SOURCES = ("nkv_api.cu", "nkv_simt.cu", "nkv_elementwise.cu", "nkv_tc_attn.cu", "nkv_tc_encode.cu",
+           "nkv_static_scratch.cu")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 
