@@ -112,6 +112,10 @@ int nkv_version(void) { return NKV_ABI_VERSION; }
 
 void nkv_debug_force_simt(int on) { g_force_simt = on ? 1 : 0; }
 
+void nkv_debug_attn_profile(void* device_buckets) {
+  tc_attn_set_profile(static_cast<long long*>(device_buckets));
+}
+
 int nkv_assign(const void* x, int x_dtype, const void* centers, int centers_dtype, int S, int J,
                int C, void* ids, int id_bytes, void* stream) {
   NKV_REQUIRE(S >= 0 && J > 0 && C > 0, NKV_ERR_INVALID, "assign: S=%d J=%d C=%d", S, J, C);

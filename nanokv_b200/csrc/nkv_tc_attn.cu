@@ -5,18 +5,21 @@
 // walks the compressed history in tiles of 128 tokens.  Per tile:
 //   1. TMA streams the packed INT4 codes of the tile and the head's slice of
 //      the decoder (or reader) matrix, 64 latent columns at a time, through a
-//      two-stage ring; the compute warps expand the codes to bf16 latent rows
-//      (code * stored scale, one rounding) straight into the 128-byte-swizzled
-//      operand layout,
+//      ring of NW slots that is never aliased, so the producer runs ahead
+//      across tile boundaries; the compute warps expand the codes to bf16
+//      latent rows (code * stored scale, one rounding) straight into the
+//      128-byte-swizzled operand layout of a two-slot latent ring,
 //   2. tcgen05.mma rebuilds K[128 tok x D] and V[128 tok x D] for this head in
 //      TMEM; the compute warps add bias and the token's centre row with the
 //      reference's two bf16 roundings and park K (row-major) and V (transposed)
 //      in shared memory -- K and V never exist in global memory,
 //   3. S = Q K^T per query tile in TMEM, online softmax in registers (exp2,
-//      lazy rescaling of the O accumulator), P to shared memory as bf16,
+//      lazy rescaling of the O accumulator), P to shared memory as bf16 (over
+//      the K tile and the latent ring, both dead by then),
 //   4. O += P V in TMEM.
 // Warp roles: warps 0-7 compute (dequantise / epilogue / softmax), warp 8 lane 0
-// issues TMA, warp 9 lane 0 issues MMA.  All hand-offs are mbarriers with
+// issues TMA, warp 9 lane 0 issues MMA, warp 10 prefetches per-token metadata
+// (centre row, scales) two tiles ahead.  All hand-offs are mbarriers with
 // bounded waits (see nkv_tc.cuh).
 //
 // TMEM columns: [0,128) K accumulator then S of query tile 0; [128,256) V
@@ -33,19 +36,21 @@ constexpr int TOK = 128;          // history tokens per tile
 constexpr int QT = 128;           // queries per query tile
 constexpr int NQ = 2;             // query tiles per CTA
 constexpr int COMPUTE_THREADS = 256;
-constexpr int THREADS = COMPUTE_THREADS + 64;
+constexpr int THREADS = COMPUTE_THREADS + 96;
 constexpr int CHUNK = 64;         // latent columns per pipeline step
 constexpr int TILE_BYTES = 128 * 128;  // one [128 rows x 64 bf16] swizzled tile
+constexpr int MAX_NW = 4;
 constexpr float RESCALE_THRESHOLD = 8.0f;
 
 enum Bar {
-  Q_FULL = 0, TMA_FULL = 1, STAGE_FREE = 3, LAT_FULL = 5, ACC_DONE = 7, META_READY = 9,
-  KV_READY = 10, S_FULL = 11, P_READY = 13, PV_DONE = 15, NUM_BARS = 17
+  Q_FULL = 0, W_FULL = 1, W_FREE = 5, LAT_FULL = 9, LAT_FREE = 11, ACC_DONE = 13,
+  META_FULL = 15, META_FREE = 17, KV_READY = 19, S_FULL = 20, P_READY = 22, PV_DONE = 24,
+  NUM_BARS = 26
 };
 
 struct Params {
   int Q, heads, N, rank, nchunks, ngroups, group;
-  int scale_dtype;
+  int scale_dtype, nw;
   float scale_log2;
   nkv_history hk, hv;
   const float* bias_k;
@@ -53,7 +58,28 @@ struct Params {
   uint16_t* out;
   float* lse;
   int32_t* status;
+  long long* prof;   // optional: cycle buckets of CTA (0,0), see nkv_debug_attn_profile
 };
+
+// Same result with bf16 pair arithmetic and no int->float conversions, for bf16 scales:
+// the bit pattern 0x4300 | n is the bf16 number 128 + n; (128 + n) - 135 = n - 7 exactly, and the
+// bf16 product of two bf16 numbers is the exact product rounded once, as the reference computes it.
+__device__ __forceinline__ uint4 dequant8_bf16(uint32_t word, __nv_bfloat162 scale2) {
+  const uint32_t lo = word & 0x0F0F0F0Fu, hi = (word >> 4) & 0x0F0F0F0Fu;
+  const uint32_t t[4] = {__byte_perm(lo, hi, 0x4400), __byte_perm(lo, hi, 0x5511),
+                         __byte_perm(lo, hi, 0x6622), __byte_perm(lo, hi, 0x7733)};
+  const uint32_t bias_bits = 0x43074307u;   // bf16 pair (135, 135)
+  const __nv_bfloat162 bias2 = *reinterpret_cast<const __nv_bfloat162*>(&bias_bits);
+  uint4 r;
+  uint32_t* o = &r.x;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t bits = (t[i] & 0x00FF00FFu) | 0x43004300u;
+    const __nv_bfloat162 v = __hmul2(__hsub2(*reinterpret_cast<const __nv_bfloat162*>(&bits), bias2), scale2);
+    o[i] = *reinterpret_cast<const uint32_t*>(&v);
+  }
+  return r;
+}
 
 template <int D>
 struct Layout {
@@ -62,22 +88,27 @@ struct Layout {
   static constexpr int K_OFF = Q_OFF + NQ * DCH * TILE_BYTES;   // [DCH] tiles [128 tok x 64]
   static constexpr int VT_OFF = K_OFF + DCH * TILE_BYTES;       // [2] tiles [D rows x 64 tok]
   static constexpr int VT_TILE = D * 128;
-  static constexpr int STAGE_OFF = VT_OFF + 2 * VT_TILE;
-  static constexpr int STAGE_LAT = 0;
-  static constexpr int STAGE_W = TILE_BYTES;
-  static constexpr int STAGE_CODES = STAGE_W + D * 128;
-  static constexpr int STAGE_BYTES = STAGE_CODES + TOK * 32;
-  static constexpr int P_BYTES = NQ * 2 * TILE_BYTES;    // aliases the stage ring
-  static constexpr int RING_BYTES = 2 * STAGE_BYTES > P_BYTES ? 2 * STAGE_BYTES : P_BYTES;
-  static constexpr int META_OFF = STAGE_OFF + RING_BYTES;
-  // meta: bars, tmem slot, abort, crow_k/v [128] ints, bias_k/v [D] floats, scales (dynamic)
-  static constexpr int BARS_OFF = META_OFF;
-  static constexpr int SLOT_OFF = BARS_OFF + NUM_BARS * 8;
-  static constexpr int ABORT_OFF = SLOT_OFF + 4;
-  static constexpr int CROW_OFF = ((ABORT_OFF + 4 + 15) / 16) * 16;
-  static constexpr int BIAS_OFF = CROW_OFF + 2 * TOK * 4;
-  static constexpr int SCALES_OFF = BIAS_OFF + 2 * D * 4;
-  static size_t bytes(int ngroups) { return SCALES_OFF + 2 * TOK * ngroups * 2 + 1024; }
+  static constexpr int LAT_OFF = VT_OFF + 2 * VT_TILE;          // [2] latent tiles; P of tile 1
+  // P of query tile 0: over the K tile when that is large enough (D = 128), else its own buffer
+  static constexpr bool P0_ON_K = DCH * TILE_BYTES >= 2 * TILE_BYTES;
+  static constexpr int P0_OFF = P0_ON_K ? K_OFF : LAT_OFF + 2 * TILE_BYTES;
+  static constexpr int P1_OFF = LAT_OFF;
+  static constexpr int RING_OFF = LAT_OFF + 2 * TILE_BYTES + (P0_ON_K ? 0 : 2 * TILE_BYTES);
+  static constexpr int SLOT_W = 0;
+  static constexpr int SLOT_CODES = D * 128;
+  static constexpr int SLOT_BYTES = SLOT_CODES + TOK * 32;
+  __host__ __device__ static int meta_off(int nw) { return RING_OFF + nw * SLOT_BYTES; }
+  // meta: bars, tmem slot, abort, bias_k/v [D] floats, then per meta buffer (x2):
+  // crow [2][128] ints and scales [2][128][ngroups] u16
+  static constexpr int BARS = 0;
+  static constexpr int SLOT = NUM_BARS * 8;
+  static constexpr int ABORT = SLOT + 4;
+  static constexpr int BIAS = ((ABORT + 4 + 15) / 16) * 16;
+  static constexpr int CROW = BIAS + 2 * D * 4;
+  static constexpr int SCALES = CROW + 2 * 2 * TOK * 4;
+  static size_t bytes(int nw, int ngroups) {
+    return meta_off(nw) + SCALES + 2 * 2 * TOK * ngroups * 2 + 1024;
+  }
 };
 
 __device__ __forceinline__ float scale_to_float(uint16_t bits, int dtype) {
@@ -98,6 +129,16 @@ __device__ __forceinline__ uint4 dequant8(uint32_t word, float scale) {
   return r;
 }
 
+// Lap timer of one thread: adds the cycles since the previous lap to a bucket.
+struct Laps {
+  long long* out;
+  long long last;
+  __device__ __forceinline__ void start(long long* dst, bool on) { out = on ? dst : nullptr; last = clock64(); }
+  __device__ __forceinline__ void lap(int bucket) {
+    if (out) { long long now = clock64(); out[bucket] += now - last; last = now; }
+  }
+};
+
 template <int D>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
@@ -109,12 +150,14 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BARS_OFF);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::SLOT_OFF);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::ABORT_OFF);
-  int* crow = reinterpret_cast<int*>(smem + L::CROW_OFF);         // [2][128]
-  float* bias = reinterpret_cast<float*>(smem + L::BIAS_OFF);     // [2][D]
-  uint16_t* scales = reinterpret_cast<uint16_t*>(smem + L::SCALES_OFF);  // [2][128][ngroups]
+  const int nw = p.nw;
+  uint8_t* meta = smem + L::meta_off(nw);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(meta + L::BARS);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(meta + L::SLOT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(meta + L::ABORT);
+  float* bias = reinterpret_cast<float*>(meta + L::BIAS);            // [2][D]
+  int* crow = reinterpret_cast<int*>(meta + L::CROW);                // [2 buf][2][128]
+  uint16_t* scales = reinterpret_cast<uint16_t*>(meta + L::SCALES);  // [2 buf][2][128][ngroups]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int head = blockIdx.y;
@@ -122,19 +165,24 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
   const int nq = (q0 + QT < p.Q) ? 2 : 1;
   const int ntiles = (p.N + TOK - 1) / TOK;
   const int nchunks = p.nchunks;
+  const int ng = p.ngroups;
 
   if (tid == 0) {
     mbar_init(&bars[Q_FULL], 1);
+    for (int s = 0; s < MAX_NW; ++s) {
+      mbar_init(&bars[W_FULL + s], 1);
+      mbar_init(&bars[W_FREE + s], 1);
+    }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&bars[TMA_FULL + s], 1);
-      mbar_init(&bars[STAGE_FREE + s], 1);
       mbar_init(&bars[LAT_FULL + s], COMPUTE_THREADS);
+      mbar_init(&bars[LAT_FREE + s], 1);
       mbar_init(&bars[ACC_DONE + s], 1);
+      mbar_init(&bars[META_FULL + s], 32);
+      mbar_init(&bars[META_FREE + s], COMPUTE_THREADS);
       mbar_init(&bars[S_FULL + s], 1);
       mbar_init(&bars[P_READY + s], QT);
       mbar_init(&bars[PV_DONE + s], 1);
     }
-    mbar_init(&bars[META_READY], COMPUTE_THREADS);
     mbar_init(&bars[KV_READY], COMPUTE_THREADS);
     *abort_flag = 0;
     fence_barrier_init();
@@ -162,21 +210,19 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           tma_load_3d(smem + L::Q_OFF + (i * L::DCH + c) * TILE_BYTES, &map_q, c * 64, head,
                       q0 + i * QT, &bars[Q_FULL]);
       bool ok = true;
+      int slot = 0, use = 0;             // ring position of chunk g = it * 2 * nchunks + ...
       for (int it = 0; it < ntiles && ok; ++it) {
-        if (it > 0)
-          for (int i = 0; i < nq && ok; ++i)
-            ok = mbar_wait(&bars[PV_DONE + i], (it - 1) & 1, abort_flag, 100 + i);
         for (int which = 0; which < 2 && ok; ++which) {
           for (int c = 0; c < nchunks && ok; ++c) {
-            const int g = (it * 2 + which) * nchunks + c, s = g & 1, u = g >> 1;
-            if (u >= 1) ok = mbar_wait(&bars[STAGE_FREE + s], (u - 1) & 1, abort_flag, 110 + s);
+            if (use >= 1) ok = mbar_wait(&bars[W_FREE + slot], (use - 1) & 1, abort_flag, 110 + slot);
             if (!ok) break;
-            uint8_t* stage = smem + L::STAGE_OFF + s * L::STAGE_BYTES;
-            mbar_arrive_expect_tx(&bars[TMA_FULL + s], TOK * 32 + D * 128);
-            tma_load_2d(stage + L::STAGE_CODES, which ? &map_cv : &map_ck, c * 32, it * TOK,
-                        &bars[TMA_FULL + s]);
-            tma_load_2d(stage + L::STAGE_W, which ? &map_wv : &map_wk, c * CHUNK, head * D,
-                        &bars[TMA_FULL + s]);
+            uint8_t* dst = smem + L::RING_OFF + slot * L::SLOT_BYTES;
+            mbar_arrive_expect_tx(&bars[W_FULL + slot], TOK * 32 + D * 128);
+            tma_load_2d(dst + L::SLOT_CODES, which ? &map_cv : &map_ck, c * 32, it * TOK,
+                        &bars[W_FULL + slot]);
+            tma_load_2d(dst + L::SLOT_W, which ? &map_wv : &map_wk, c * CHUNK, head * D,
+                        &bars[W_FULL + slot]);
+            if (++slot == nw) { slot = 0; ++use; }
           }
         }
       }
@@ -193,27 +239,36 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       const uint32_t idesc_s = make_idesc_bf16(128, TOK);    // [128 q] x [128 tok]
       const uint32_t idesc_pv = make_idesc_bf16(128, D);     // [128 q] x [D]
       const uint32_t smem_base = smem_u32(smem);
+      Laps laps;
+      laps.start(p.prof + 16, p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0);
       bool ok = mbar_wait(&bars[Q_FULL], 0, abort_flag, 200);
+      int slot = 0, use = 0, g = 0;
       for (int it = 0; it < ntiles && ok; ++it) {
         for (int which = 0; which < 2 && ok; ++which) {
-          for (int c = 0; c < nchunks && ok; ++c) {
-            const int g = (it * 2 + which) * nchunks + c, s = g & 1, u = g >> 1;
-            ok = mbar_wait(&bars[TMA_FULL + s], u & 1, abort_flag, 210 + s) &&
-                 mbar_wait(&bars[LAT_FULL + s], u & 1, abort_flag, 212 + s);
+          for (int c = 0; c < nchunks && ok; ++c, ++g) {
+            const int ls = g & 1, lu = g >> 1;
+            ok = mbar_wait(&bars[W_FULL + slot], use & 1, abort_flag, 210 + slot);
+            laps.lap(0);
+            ok = ok && mbar_wait(&bars[LAT_FULL + ls], lu & 1, abort_flag, 214 + ls);
+            laps.lap(1);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t stage = smem_base + L::STAGE_OFF + s * L::STAGE_BYTES;
+            const uint32_t w = smem_base + L::RING_OFF + slot * L::SLOT_BYTES + L::SLOT_W;
+            const uint32_t lat = smem_base + L::LAT_OFF + ls * TILE_BYTES;
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-              mma_bf16(tmem_base + which * 128, make_smem_desc_sw128(stage + L::STAGE_LAT + k * 32),
-                       make_smem_desc_sw128(stage + L::STAGE_W + k * 32), idesc_dec,
-                       c > 0 || k > 0);
-            mma_commit(&bars[STAGE_FREE + s]);
+              mma_bf16(tmem_base + which * 128, make_smem_desc_sw128(lat + k * 32),
+                       make_smem_desc_sw128(w + k * 32), idesc_dec, c > 0 || k > 0);
+            mma_commit(&bars[W_FREE + slot]);
+            mma_commit(&bars[LAT_FREE + ls]);
             if (c == nchunks - 1) mma_commit(&bars[ACC_DONE + which]);
+            if (++slot == nw) { slot = 0; ++use; }
+            laps.lap(2);
           }
         }
         if (!ok) break;
         ok = mbar_wait(&bars[KV_READY], it & 1, abort_flag, 220);
+        laps.lap(3);
         if (!ok) break;
         tc_fence_after();
         for (int i = 0; i < nq; ++i) {
@@ -227,92 +282,164 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           mma_commit(&bars[S_FULL + i]);
         }
         for (int i = 0; i < nq && ok; ++i) {
+          laps.lap(4);
           ok = mbar_wait(&bars[P_READY + i], it & 1, abort_flag, 230 + i);
+          laps.lap(5);
           if (!ok) break;
           tc_fence_after();
+          const uint32_t p_tiles = smem_base + (i == 0 ? L::P0_OFF : L::P1_OFF);
 #pragma unroll
           for (int k = 0; k < TOK / 16; ++k) {
-            const uint32_t a = smem_base + L::STAGE_OFF + (i * 2 + (k >> 2)) * TILE_BYTES + (k & 3) * 32;
+            const uint32_t a = p_tiles + (k >> 2) * TILE_BYTES + (k & 3) * 32;
             const uint32_t b = smem_base + L::VT_OFF + (k >> 2) * L::VT_TILE + (k & 3) * 32;
             mma_bf16(tmem_base + 256 + i * 128, make_smem_desc_sw128(a), make_smem_desc_sw128(b),
                      idesc_pv, it > 0 || k > 0);
           }
           mma_commit(&bars[PV_DONE + i]);
         }
+        laps.lap(6);
       }
     }
     __syncwarp();
+  } else if (warp == 10) {
+    // ------------------------------------------- per-token metadata, two tiles ahead
+    bool ok = true;
+    for (int it = 0; it < ntiles && ok; ++it) {
+      const int b = it & 1, u = it >> 1;
+      if (u >= 1) ok = mbar_wait(&bars[META_FREE + b], (u - 1) & 1, abort_flag, 240 + b);
+      if (!ok) break;
+      const int t0 = it * TOK;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        const nkv_history& h = which ? p.hv : p.hk;
+        for (int r = lane; r < TOK; r += 32) {
+          const int t = t0 + r;
+          const bool in = t < p.N;
+          crow[(b * 2 + which) * TOK + r] = in ? center_row_of(h, t) : 0;
+          const uint16_t* src = static_cast<const uint16_t*>(h.scales) + static_cast<size_t>(t) * ng;
+          uint16_t* dst = scales + static_cast<size_t>((b * 2 + which) * TOK + r) * ng;
+          for (int gi = 0; gi < ng; ++gi) dst[gi] = in ? src[gi] : 0;
+        }
+      }
+      mbar_arrive(&bars[META_FULL + b]);
+    }
   } else {
     // ------------------------------------------------------------ compute warps
     const int wg = tid >> 7;                    // query tile this thread's softmax serves
     const int row = tid & 127;                  // TMEM lane == token row == query row
     const uint32_t lane_sel = static_cast<uint32_t>(32 * (warp & 3)) << 16;
-    const int ng = p.ngroups;
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
+    int slot = 0, use = 0, g = 0;
+    Laps laps;
+    laps.start(p.prof, p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0);
     for (int it = 0; it < ntiles && ok; ++it) {
       const int t0 = it * TOK;
       const int valid = min(TOK, p.N - t0);
-      if (it > 0) {
+      const int mb = it & 1;
+      if (it > 0) {  // P of the previous tile lives in the K tile and the latent ring
         for (int i = 0; i < nq && ok; ++i)
           ok = mbar_wait(&bars[PV_DONE + i], (it - 1) & 1, abort_flag, 300 + i);
         if (!ok) break;
         tc_fence_after();
       }
-      {  // per-token metadata of this tile: centre row and scales (threads 0-127: K, 128-255: V)
-        const int which = tid >> 7;
-        const nkv_history& h = which ? p.hv : p.hk;
-        const int t = t0 + row;
-        const bool in = row < valid;
-        crow[which * TOK + row] = in ? center_row_of(h, t) : 0;
-        const uint16_t* src = static_cast<const uint16_t*>(h.scales) + static_cast<size_t>(t) * ng;
-        for (int g = 0; g < ng; ++g) scales[(which * TOK + row) * ng + g] = in ? src[g] : 0;
-      }
-      mbar_arrive(&bars[META_READY]);
-      ok = mbar_wait(&bars[META_READY], it & 1, abort_flag, 310);
+      laps.lap(0);
+      ok = mbar_wait(&bars[META_FULL + mb], (it >> 1) & 1, abort_flag, 310);
+      laps.lap(1);
       if (!ok) break;
       // ---- expand codes to bf16 latent tiles, chunk by chunk
       for (int which = 0; which < 2 && ok; ++which) {
-        for (int c = 0; c < nchunks && ok; ++c) {
-          const int g = (it * 2 + which) * nchunks + c, s = g & 1, u = g >> 1;
-          ok = mbar_wait(&bars[TMA_FULL + s], u & 1, abort_flag, 320 + s);
+        for (int c = 0; c < nchunks && ok; ++c, ++g) {
+          const int ls = g & 1, lu = g >> 1;
+          ok = mbar_wait(&bars[W_FULL + slot], use & 1, abort_flag, 320 + slot);
+          laps.lap(2);
+          if (ok && lu >= 1) ok = mbar_wait(&bars[LAT_FREE + ls], (lu - 1) & 1, abort_flag, 324 + ls);
+          laps.lap(3);
           if (!ok) break;
-          uint8_t* stage = smem + L::STAGE_OFF + s * L::STAGE_BYTES;
+          const uint8_t* codes = smem + L::RING_OFF + slot * L::SLOT_BYTES + L::SLOT_CODES;
+          uint8_t* lat = smem + L::LAT_OFF + ls * TILE_BYTES;
           const int r = tid >> 1, half = tid & 1;
-          const uint4 code = *reinterpret_cast<const uint4*>(stage + L::STAGE_CODES + r * 32 + half * 16);
+          const uint4 code = *reinterpret_cast<const uint4*>(codes + r * 32 + half * 16);
           const int col0 = c * CHUNK + half * 32;
-          const float sc = scale_to_float(scales[(which * TOK + r) * ng + col0 / p.group], p.scale_dtype);
+          const uint16_t sbits =
+              scales[static_cast<size_t>((mb * 2 + which) * TOK + r) * p.ngroups + col0 / p.group];
           const uint32_t words[4] = {code.x, code.y, code.z, code.w};
+          if (p.scale_dtype == NKV_BF16) {
+            const uint32_t pair = static_cast<uint32_t>(sbits) * 0x00010001u;
+            const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&pair);
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            *reinterpret_cast<uint4*>(stage + L::STAGE_LAT + sw128_offset(r, half * 32 + j * 8)) =
-                dequant8(words[j], sc);
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint4*>(lat + sw128_offset(r, half * 32 + j * 8)) =
+                  dequant8_bf16(words[j], scale2);
+          } else {
+            const float sc = scale_to_float(sbits, p.scale_dtype);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint4*>(lat + sw128_offset(r, half * 32 + j * 8)) =
+                  dequant8(words[j], sc);
+          }
+          laps.lap(4);
           fence_proxy_async();
-          mbar_arrive(&bars[LAT_FULL + s]);
+          mbar_arrive(&bars[LAT_FULL + ls]);
+          laps.lap(5);
+          if (++slot == nw) { slot = 0; ++use; }
         }
       }
       if (!ok) break;
       // ---- K / V epilogues: bias, centre, two bf16 roundings, park in shared memory
       for (int which = 0; which < 2 && ok; ++which) {
-        ok = mbar_wait(&bars[ACC_DONE + which], it & 1, abort_flag, 330 + which);
-        if (!ok) break;
-        tc_fence_after();
         const nkv_history& h = which ? p.hv : p.hk;
         const bool in = row < valid;
         const int colhalf = warp >> 2;
-        const uint16_t* crow_ptr = static_cast<const uint16_t*>(h.centers) +
-                                   static_cast<size_t>(crow[which * TOK + row]) * h.center_width +
-                                   static_cast<size_t>(head) * D;
-#pragma unroll 1
+        const int colbase = colhalf * (D / 2);
+        // Centre rows of this warp's 32 tokens (D/2 columns each), gathered cooperatively: PIECES
+        // lanes read one row's 16-byte pieces, so a load instruction touches 32/PIECES lines
+        // instead of 32; the rows are then redistributed through a swizzled staging area in the
+        // latent ring, which is idle once both decode accumulators are complete.
+        constexpr int PIECES = D / 16, RPI = 32 / PIECES;
+        const int wrow0 = 32 * (warp & 3);
+        const uint16_t* cbase = static_cast<const uint16_t*>(h.centers) +
+                                static_cast<size_t>(head) * D + colbase;
+        uint4 cen[PIECES];
+#pragma unroll
+        for (int i = 0; i < PIECES; ++i) {
+          const int rloc = i * RPI + lane / PIECES, piece = lane % PIECES;
+          const int crow_i = crow[(mb * 2 + which) * TOK + wrow0 + rloc];
+          cen[i] = __ldg(reinterpret_cast<const uint4*>(
+              cbase + static_cast<size_t>(crow_i) * h.center_width + piece * 8));
+        }
+        laps.lap(6);
+        if (which == 0) {
+          ok = mbar_wait(&bars[ACC_DONE + 0], it & 1, abort_flag, 330) &&
+               mbar_wait(&bars[ACC_DONE + 1], it & 1, abort_flag, 331);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        laps.lap(7);
+        {
+          uint8_t* stage = smem + L::LAT_OFF + warp * (32 * PIECES * 16);
+#pragma unroll
+          for (int i = 0; i < PIECES; ++i) {
+            const int rloc = i * RPI + lane / PIECES, piece = lane % PIECES;
+            *reinterpret_cast<uint4*>(stage + rloc * (PIECES * 16) +
+                                      ((piece ^ (rloc & (PIECES - 1))) << 4)) = cen[i];
+          }
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < PIECES; ++j)
+            cen[j] = *reinterpret_cast<const uint4*>(stage + lane * (PIECES * 16) +
+                                                     ((j ^ (lane & (PIECES - 1))) << 4));
+          __syncwarp();
+        }
+#pragma unroll
         for (int cc = 0; cc < D / 64; ++cc) {
-          const int col = colhalf * (D / 2) + cc * 32;
+          const int col = colbase + cc * 32;
           float v[32];
           tmem_ld32(tmem_base + lane_sel + which * 128 + col, v);
           uint32_t packed[16];
-          const uint4* cen4 = reinterpret_cast<const uint4*>(crow_ptr + col);
 #pragma unroll
           for (int j4 = 0; j4 < 4; ++j4) {
-            const uint4 cw = __ldg(cen4 + j4);
+            const uint4 cw = cen[cc * 4 + j4];
             const uint32_t cwords[4] = {cw.x, cw.y, cw.z, cw.w};
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
@@ -342,12 +469,16 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         }
       }
       if (!ok) break;
+      laps.lap(8);
+      mbar_arrive(&bars[META_FREE + mb]);
       tc_fence_before();
       fence_proxy_async();
       mbar_arrive(&bars[KV_READY]);
+      laps.lap(9);
       // ---- online softmax of this thread's query row
       if (wg < nq) {
         ok = mbar_wait(&bars[S_FULL + wg], it & 1, abort_flag, 340 + wg);
+        laps.lap(10);
         if (!ok) break;
         tc_fence_after();
         const uint32_t s_addr = tmem_base + lane_sel + wg * 128;
@@ -357,9 +488,14 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           if (cc * 32 >= valid) break;
           float v[32];
           tmem_ld32(s_addr + cc * 32, v);
+          if (valid == TOK) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (cc * 32 + j < valid) mx = fmaxf(mx, v[j]);
+            for (int j = 0; j < 32; ++j) mx = fmaxf(mx, v[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (cc * 32 + j < valid) mx = fmaxf(mx, v[j]);
+          }
         }
         const float m_new = mx * p.scale_log2;
         const bool need = m_new > m_used + RESCALE_THRESHOLD;
@@ -380,19 +516,34 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           l_run *= alpha;
           m_used = m_next;
         }
-        uint8_t* p_tiles = smem + L::STAGE_OFF + wg * 2 * TILE_BYTES;
+        // P of tile 0 overwrites the K tile: every S = Q K^T of this history tile must be done
+        if (wg == 0 && nq == 2 && L::P0_ON_K) {
+          ok = mbar_wait(&bars[S_FULL + 1], it & 1, abort_flag, 342);
+          if (!ok) break;
+        }
+        uint8_t* p_tiles = smem + (wg == 0 ? L::P0_OFF : L::P1_OFF);
         float sum = 0.f;
 #pragma unroll 1
         for (int cc = 0; cc < TOK / 32; ++cc) {
           float v[32];
           tmem_ld32(s_addr + cc * 32, v);
           uint32_t packed[16];
+          if (valid == TOK) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            float p0 = (cc * 32 + j < valid) ? exp2f(fmaf(v[j], p.scale_log2, -m_used)) : 0.f;
-            float p1 = (cc * 32 + j + 1 < valid) ? exp2f(fmaf(v[j + 1], p.scale_log2, -m_used)) : 0.f;
-            sum += p0 + p1;
-            packed[j >> 1] = pack_bf16x2(p0, p1);
+            for (int j = 0; j < 32; j += 2) {
+              const float p0 = exp2f(fmaf(v[j], p.scale_log2, -m_used));
+              const float p1 = exp2f(fmaf(v[j + 1], p.scale_log2, -m_used));
+              sum += p0 + p1;
+              packed[j >> 1] = pack_bf16x2(p0, p1);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              float p0 = (cc * 32 + j < valid) ? exp2f(fmaf(v[j], p.scale_log2, -m_used)) : 0.f;
+              float p1 = (cc * 32 + j + 1 < valid) ? exp2f(fmaf(v[j + 1], p.scale_log2, -m_used)) : 0.f;
+              sum += p0 + p1;
+              packed[j >> 1] = pack_bf16x2(p0, p1);
+            }
           }
           uint8_t* tile = p_tiles + (cc >> 1) * TILE_BYTES;
 #pragma unroll
@@ -401,9 +552,11 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
                 make_uint4(packed[j4 * 4], packed[j4 * 4 + 1], packed[j4 * 4 + 2], packed[j4 * 4 + 3]);
         }
         l_run += sum;
+        laps.lap(11);
         tc_fence_before();
         fence_proxy_async();
         mbar_arrive(&bars[P_READY + wg]);
+        laps.lap(12);
       }
     }
     // ---- write O / l and the natural-log LSE
@@ -449,12 +602,19 @@ __global__ void fill_empty_kernel(uint16_t* out, float* lse, size_t rows, int d)
   if (i < rows) lse[i] = -INFINITY;
 }
 
+constexpr size_t SMEM_LIMIT = 232448;  // 227 KB per CTA
+long long* g_profile = nullptr;
+
 template <int D>
-int launch(const CUtensorMap maps[5], const Params& p, cudaStream_t stream) {
-  size_t smem = Layout<D>::bytes(p.ngroups);
-  NKV_REQUIRE(smem <= 232448, NKV_ERR_UNSUPPORTED,
+int launch(const CUtensorMap maps[5], Params& p, cudaStream_t stream) {
+  int nw = MAX_NW;
+  while (nw > 2 && Layout<D>::bytes(nw, p.ngroups) > SMEM_LIMIT) --nw;
+  size_t smem = Layout<D>::bytes(nw, p.ngroups);
+  NKV_REQUIRE(smem <= SMEM_LIMIT, NKV_ERR_UNSUPPORTED,
               "codec attention needs %zu bytes of shared memory (rank/group = %d too fine)", smem,
               p.ngroups);
+  p.nw = nw;
+  p.prof = g_profile;
   auto kernel = attn_codec_kernel<D>;
   NKV_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(smem)));
@@ -465,6 +625,10 @@ int launch(const CUtensorMap maps[5], const Params& p, cudaStream_t stream) {
 }
 
 }  // namespace
+
+// Development aid: 32 device int64 cycle buckets filled by CTA (0,0) of later launches
+// (compute thread 0: buckets 0-12, MMA thread: 16-22); nullptr switches it off.
+void tc_attn_set_profile(long long* device_buckets) { g_profile = device_buckets; }
 
 bool tc_attn_supported(int dk, int dv, int rank) {
   return dk == dv && (dk == 64 || dk == 128) && rank % 64 == 0 && rank > 0;
