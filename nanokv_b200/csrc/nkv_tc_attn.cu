@@ -43,9 +43,9 @@ constexpr int MAX_NW = 4;
 constexpr float RESCALE_THRESHOLD = 8.0f;
 
 enum Bar {
-  Q_FULL = 0, W_FULL = 1, W_FREE = 5, LAT_FULL = 9, LAT_FREE = 11, ACC_DONE = 13,
-  META_FULL = 15, META_FREE = 17, KV_READY = 19, S_FULL = 20, P_READY = 22, PV_DONE = 24,
-  NUM_BARS = 26
+  Q_FULL = 0, W_FULL = 1, W_FREE = 5, LAT_FULL = 9, LAT_FREE = 13, ACC_DONE = 17,
+  META_FULL = 19, META_FREE = 21, KV_READY = 23, S_FULL = 24, P_READY = 26, PV_DONE = 28,
+  KEPI_DONE = 30, NUM_BARS = 31
 };
 
 struct Params {
@@ -88,12 +88,8 @@ struct Layout {
   static constexpr int K_OFF = Q_OFF + NQ * DCH * TILE_BYTES;   // [DCH] tiles [128 tok x 64]
   static constexpr int VT_OFF = K_OFF + DCH * TILE_BYTES;       // [2] tiles [D rows x 64 tok]
   static constexpr int VT_TILE = D * 128;
-  static constexpr int LAT_OFF = VT_OFF + 2 * VT_TILE;          // [2] latent tiles; P of tile 1
-  // P of query tile 0: over the K tile when that is large enough (D = 128), else its own buffer
-  static constexpr bool P0_ON_K = DCH * TILE_BYTES >= 2 * TILE_BYTES;
-  static constexpr int P0_OFF = P0_ON_K ? K_OFF : LAT_OFF + 2 * TILE_BYTES;
-  static constexpr int P1_OFF = LAT_OFF;
-  static constexpr int RING_OFF = LAT_OFF + 2 * TILE_BYTES + (P0_ON_K ? 0 : 2 * TILE_BYTES);
+  static constexpr int SCRATCH_OFF = VT_OFF + 2 * VT_TILE;      // 8 warps x 4 KB: centre-row staging
+  static constexpr int RING_OFF = SCRATCH_OFF + 2 * TILE_BYTES;
   static constexpr int SLOT_W = 0;
   static constexpr int SLOT_CODES = D * 128;
   static constexpr int SLOT_BYTES = SLOT_CODES + TOK * 32;
@@ -172,10 +168,10 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
     for (int s = 0; s < MAX_NW; ++s) {
       mbar_init(&bars[W_FULL + s], 1);
       mbar_init(&bars[W_FREE + s], 1);
-    }
-    for (int s = 0; s < 2; ++s) {
       mbar_init(&bars[LAT_FULL + s], COMPUTE_THREADS);
       mbar_init(&bars[LAT_FREE + s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&bars[ACC_DONE + s], 1);
       mbar_init(&bars[META_FULL + s], 32);
       mbar_init(&bars[META_FREE + s], COMPUTE_THREADS);
@@ -184,6 +180,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(&bars[PV_DONE + s], 1);
     }
     mbar_init(&bars[KV_READY], COMPUTE_THREADS);
+    mbar_init(&bars[KEPI_DONE], COMPUTE_THREADS);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -246,7 +243,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       for (int it = 0; it < ntiles && ok; ++it) {
         for (int which = 0; which < 2 && ok; ++which) {
           for (int c = 0; c < nchunks && ok; ++c, ++g) {
-            const int ls = g & 1, lu = g >> 1;
+            const int ls = g & 3, lu = g >> 2;   // four latent staging slots in TMEM
             ok = mbar_wait(&bars[W_FULL + slot], use & 1, abort_flag, 210 + slot);
             laps.lap(0);
             ok = ok && mbar_wait(&bars[LAT_FULL + ls], lu & 1, abort_flag, 214 + ls);
@@ -254,11 +251,12 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
             if (!ok) break;
             tc_fence_after();
             const uint32_t w = smem_base + L::RING_OFF + slot * L::SLOT_BYTES + L::SLOT_W;
-            const uint32_t lat = smem_base + L::LAT_OFF + ls * TILE_BYTES;
+            // latent chunk: 32 TMEM columns in the other tensor's (idle) accumulator region
+            const uint32_t lat = tmem_base + (which == 0 ? 128 : 0) + ls * 32;
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-              mma_bf16(tmem_base + which * 128, make_smem_desc_sw128(lat + k * 32),
-                       make_smem_desc_sw128(w + k * 32), idesc_dec, c > 0 || k > 0);
+              mma_bf16_ts(tmem_base + which * 128, lat + k * 8, make_smem_desc_sw128(w + k * 32),
+                          idesc_dec, c > 0 || k > 0);
             mma_commit(&bars[W_FREE + slot]);
             mma_commit(&bars[LAT_FREE + ls]);
             if (c == nchunks - 1) mma_commit(&bars[ACC_DONE + which]);
@@ -287,13 +285,12 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           laps.lap(5);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t p_tiles = smem_base + (i == 0 ? L::P0_OFF : L::P1_OFF);
+          // P (bf16 pairs) sits in the first 64 columns of the S region it was computed from
 #pragma unroll
           for (int k = 0; k < TOK / 16; ++k) {
-            const uint32_t a = p_tiles + (k >> 2) * TILE_BYTES + (k & 3) * 32;
             const uint32_t b = smem_base + L::VT_OFF + (k >> 2) * L::VT_TILE + (k & 3) * 32;
-            mma_bf16(tmem_base + 256 + i * 128, make_smem_desc_sw128(a), make_smem_desc_sw128(b),
-                     idesc_pv, it > 0 || k > 0);
+            mma_bf16_ts(tmem_base + 256 + i * 128, tmem_base + i * 128 + k * 8,
+                        make_smem_desc_sw128(b), idesc_pv, it > 0 || k > 0);
           }
           mma_commit(&bars[PV_DONE + i]);
         }
@@ -347,47 +344,55 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       ok = mbar_wait(&bars[META_FULL + mb], (it >> 1) & 1, abort_flag, 310);
       laps.lap(1);
       if (!ok) break;
-      // ---- expand codes to bf16 latent tiles, chunk by chunk
+      // ---- per tensor: expand codes to bf16 latent chunks in tensor memory (the A operand of
+      // the decode MMA), then the epilogue: bias, centre, two bf16 roundings, park in shared memory
       for (int which = 0; which < 2 && ok; ++which) {
+        if (which == 1) {
+          // V's latent staging reuses K-accumulator columns: every thread must have read them
+          ok = mbar_wait(&bars[KEPI_DONE], it & 1, abort_flag, 326);
+          if (!ok) break;
+        }
         for (int c = 0; c < nchunks && ok; ++c, ++g) {
-          const int ls = g & 1, lu = g >> 1;
+          const int ls = g & 3, lu = g >> 2;   // four latent staging slots in TMEM
           ok = mbar_wait(&bars[W_FULL + slot], use & 1, abort_flag, 320 + slot);
           laps.lap(2);
           if (ok && lu >= 1) ok = mbar_wait(&bars[LAT_FREE + ls], (lu - 1) & 1, abort_flag, 324 + ls);
           laps.lap(3);
           if (!ok) break;
+          tc_fence_after();
           const uint8_t* codes = smem + L::RING_OFF + slot * L::SLOT_BYTES + L::SLOT_CODES;
-          uint8_t* lat = smem + L::LAT_OFF + ls * TILE_BYTES;
-          const int r = tid >> 1, half = tid & 1;
-          const uint4 code = *reinterpret_cast<const uint4*>(codes + r * 32 + half * 16);
+          const int half = wg;        // this thread: token `row`, latent columns half*32 .. +32
+          const uint4 code = *reinterpret_cast<const uint4*>(codes + row * 32 + half * 16);
           const int col0 = c * CHUNK + half * 32;
           const uint16_t sbits =
-              scales[static_cast<size_t>((mb * 2 + which) * TOK + r) * p.ngroups + col0 / p.group];
+              scales[static_cast<size_t>((mb * 2 + which) * TOK + row) * p.ngroups + col0 / p.group];
           const uint32_t words[4] = {code.x, code.y, code.z, code.w};
+          uint32_t packed[16];
           if (p.scale_dtype == NKV_BF16) {
             const uint32_t pair = static_cast<uint32_t>(sbits) * 0x00010001u;
             const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&pair);
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              *reinterpret_cast<uint4*>(lat + sw128_offset(r, half * 32 + j * 8)) =
-                  dequant8_bf16(words[j], scale2);
+            for (int j = 0; j < 4; ++j) {
+              const uint4 v = dequant8_bf16(words[j], scale2);
+              packed[4 * j] = v.x; packed[4 * j + 1] = v.y; packed[4 * j + 2] = v.z; packed[4 * j + 3] = v.w;
+            }
           } else {
             const float sc = scale_to_float(sbits, p.scale_dtype);
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              *reinterpret_cast<uint4*>(lat + sw128_offset(r, half * 32 + j * 8)) =
-                  dequant8(words[j], sc);
+            for (int j = 0; j < 4; ++j) {
+              const uint4 v = dequant8(words[j], sc);
+              packed[4 * j] = v.x; packed[4 * j + 1] = v.y; packed[4 * j + 2] = v.z; packed[4 * j + 3] = v.w;
+            }
           }
+          tmem_st16(tmem_base + lane_sel + (which == 0 ? 128 : 0) + ls * 32 + half * 16, packed);
+          tmem_wait_st();
           laps.lap(4);
-          fence_proxy_async();
+          tc_fence_before();
           mbar_arrive(&bars[LAT_FULL + ls]);
           laps.lap(5);
           if (++slot == nw) { slot = 0; ++use; }
         }
-      }
-      if (!ok) break;
-      // ---- K / V epilogues: bias, centre, two bf16 roundings, park in shared memory
-      for (int which = 0; which < 2 && ok; ++which) {
+        if (!ok) break;
         const nkv_history& h = which ? p.hv : p.hk;
         const bool in = row < valid;
         const int colhalf = warp >> 2;
@@ -395,7 +400,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         // Centre rows of this warp's 32 tokens (D/2 columns each), gathered cooperatively: PIECES
         // lanes read one row's 16-byte pieces, so a load instruction touches 32/PIECES lines
         // instead of 32; the rows are then redistributed through a swizzled staging area in the
-        // latent ring, which is idle once both decode accumulators are complete.
+        // scratch area of shared memory.
         constexpr int PIECES = D / 16, RPI = 32 / PIECES;
         const int wrow0 = 32 * (warp & 3);
         const uint16_t* cbase = static_cast<const uint16_t*>(h.centers) +
@@ -409,15 +414,12 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
               cbase + static_cast<size_t>(crow_i) * h.center_width + piece * 8));
         }
         laps.lap(6);
-        if (which == 0) {
-          ok = mbar_wait(&bars[ACC_DONE + 0], it & 1, abort_flag, 330) &&
-               mbar_wait(&bars[ACC_DONE + 1], it & 1, abort_flag, 331);
-          if (!ok) break;
-          tc_fence_after();
-        }
+        ok = mbar_wait(&bars[ACC_DONE + which], it & 1, abort_flag, 330 + which);
+        if (!ok) break;
+        tc_fence_after();
         laps.lap(7);
         {
-          uint8_t* stage = smem + L::LAT_OFF + warp * (32 * PIECES * 16);
+          uint8_t* stage = smem + L::SCRATCH_OFF + warp * (32 * PIECES * 16);
 #pragma unroll
           for (int i = 0; i < PIECES; ++i) {
             const int rloc = i * RPI + lane / PIECES, piece = lane % PIECES;
@@ -466,6 +468,10 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
               *reinterpret_cast<uint16_t*>(tile + sw128_offset(col + j, row & 63)) = bits;
             }
           }
+        }
+        if (which == 0) {
+          tc_fence_before();
+          mbar_arrive(&bars[KEPI_DONE]);
         }
       }
       if (!ok) break;
@@ -516,12 +522,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           l_run *= alpha;
           m_used = m_next;
         }
-        // P of tile 0 overwrites the K tile: every S = Q K^T of this history tile must be done
-        if (wg == 0 && nq == 2 && L::P0_ON_K) {
-          ok = mbar_wait(&bars[S_FULL + 1], it & 1, abort_flag, 342);
-          if (!ok) break;
-        }
-        uint8_t* p_tiles = smem + (wg == 0 ? L::P0_OFF : L::P1_OFF);
+        // P (bf16 pairs) replaces S in place: the 16 cells written per step lie below the 32 read
         float sum = 0.f;
 #pragma unroll 1
         for (int cc = 0; cc < TOK / 32; ++cc) {
@@ -545,16 +546,12 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
               packed[j >> 1] = pack_bf16x2(p0, p1);
             }
           }
-          uint8_t* tile = p_tiles + (cc >> 1) * TILE_BYTES;
-#pragma unroll
-          for (int j4 = 0; j4 < 4; ++j4)
-            *reinterpret_cast<uint4*>(tile + sw128_offset(row, (cc & 1) * 32 + j4 * 8)) =
-                make_uint4(packed[j4 * 4], packed[j4 * 4 + 1], packed[j4 * 4 + 2], packed[j4 * 4 + 3]);
+          tmem_st16(s_addr + cc * 16, packed);
         }
+        tmem_wait_st();
         l_run += sum;
         laps.lap(11);
         tc_fence_before();
-        fence_proxy_async();
         mbar_arrive(&bars[P_READY + wg]);
         laps.lap(12);
       }
