@@ -1,29 +1,35 @@
 // Fused codec-attention on tcgen05 tensor cores (bf16 operands, fp32 TMEM
-// accumulators).
+// accumulators), with the K/V reconstruction shared inside a thread-block cluster.
 //
-// One CTA owns one head and up to 256 queries (two 128-row query tiles) and
-// walks the compressed history in tiles of 128 tokens.  Per tile:
-//   1. TMA streams the packed INT4 codes of the tile and the head's slice of
-//      the decoder (or reader) matrix, 64 latent columns at a time, through a
-//      ring of NW slots that is never aliased, so the producer runs ahead
-//      across tile boundaries; the compute warps expand the codes to bf16
-//      latent rows (code * stored scale, one rounding) straight into the
-//      128-byte-swizzled operand layout of a two-slot latent ring,
-//   2. tcgen05.mma rebuilds K[128 tok x D] and V[128 tok x D] for this head in
-//      TMEM; the compute warps add bias and the token's centre row with the
-//      reference's two bf16 roundings and park K (row-major) and V (transposed)
-//      in shared memory -- K and V never exist in global memory,
-//   3. S = Q K^T per query tile in TMEM, online softmax in registers (exp2,
-//      lazy rescaling of the O accumulator), P to shared memory as bf16 (over
-//      the K tile and the latent ring, both dead by then),
-//   4. O += P V in TMEM.
+// A CTA owns one head and up to 256 queries (two 128-row query tiles) and walks
+// the compressed history in tiles of 128 tokens.  The CL CTAs of a cluster serve
+// CL consecutive query blocks of the SAME head, so they all need the same K and
+// V tile.  Each of them rebuilds one 64-column part of it (CL = 4: K columns
+// 0-63 / 64-127, V columns 0-63 / 64-127) and stores that part into the shared
+// memory of every CTA of the cluster (distributed shared memory), which divides
+// the decode GEMM, the dequantisation and the decoder-matrix traffic by CL.
+// Per tile and CTA:
+//   1. TMA streams the packed INT4 codes of the tile (of this CTA's tensor) and
+//      64 rows of the head's decoder (or reader) slice, 64 latent columns at a
+//      time, through a ring of NW slots; the compute warps expand the codes to
+//      bf16 latent rows (code * stored scale, one rounding) into tensor memory,
+//      where they are the A operand of the decode MMA,
+//   2. tcgen05.mma rebuilds the [128 tok x 64] part in TMEM; the compute warps
+//      add bias and the token's centre row with the reference's two bf16
+//      roundings and store K (row-major) or V (transposed) into all CL CTAs --
+//      K and V never exist in global memory,
+//   3. S = Q K^T per query tile in TMEM, online softmax in registers (exp2, lazy
+//      rescaling of the O accumulator); P replaces S in TMEM as bf16 pairs,
+//   4. O += P V (P from TMEM, V from shared memory) in TMEM.
 // Warp roles: warps 0-7 compute (dequantise / epilogue / softmax), warp 8 lane 0
 // issues TMA, warp 9 lane 0 issues MMA, warp 10 prefetches per-token metadata
 // (centre row, scales) two tiles ahead.  All hand-offs are mbarriers with
-// bounded waits (see nkv_tc.cuh).
+// bounded waits (see nkv_tc.cuh); peers signal each other with cluster-scope
+// arrivals and multicast commits.  No TMA load uses multicast.
 //
-// TMEM columns: [0,128) K accumulator then S of query tile 0; [128,256) V
-// accumulator then S of tile 1; [256,384) O tile 0; [384,512) O tile 1.
+// TMEM columns: [0,128) S of query tile 0 (decode accumulator in [0,64));
+// [128,256) S of tile 1 (latent staging, four 32-column slots); [256,384) O
+// tile 0; [384,512) O tile 1.
 #include "nkv_internal.h"
 #include "nkv_tc.cuh"
 
@@ -36,16 +42,19 @@ constexpr int TOK = 128;          // history tokens per tile
 constexpr int QT = 128;           // queries per query tile
 constexpr int NQ = 2;             // query tiles per CTA
 constexpr int COMPUTE_THREADS = 256;
+constexpr int COMPUTE_WARPS = COMPUTE_THREADS / 32;
 constexpr int THREADS = COMPUTE_THREADS + 96;
 constexpr int CHUNK = 64;         // latent columns per pipeline step
+constexpr int PART = 64;          // K/V columns rebuilt by one CTA
 constexpr int TILE_BYTES = 128 * 128;  // one [128 rows x 64 bf16] swizzled tile
-constexpr int MAX_NW = 4;
+constexpr int MAX_NW = 6;
+constexpr int LAT_SLOTS = 4;
 constexpr float RESCALE_THRESHOLD = 8.0f;
 
 enum Bar {
-  Q_FULL = 0, W_FULL = 1, W_FREE = 5, LAT_FULL = 9, LAT_FREE = 13, ACC_DONE = 17,
-  META_FULL = 19, META_FREE = 21, KV_READY = 23, S_FULL = 24, P_READY = 26, PV_DONE = 28,
-  KEPI_DONE = 30, NUM_BARS = 31
+  Q_FULL = 0, W_FULL = 1, W_FREE = 7, LAT_FULL = 13, LAT_FREE = 17, ACC_DONE = 21,
+  META_FULL = 22, META_FREE = 24, KV_READY = 26, KV_FREE = 27, S_FULL = 28, P_READY = 30,
+  PV_DONE = 32, EPI_LOCAL = 34, NUM_BARS = 35
 };
 
 struct Params {
@@ -61,49 +70,30 @@ struct Params {
   long long* prof;   // optional: cycle buckets of CTA (0,0), see nkv_debug_attn_profile
 };
 
-// Same result with bf16 pair arithmetic and no int->float conversions, for bf16 scales:
-// the bit pattern 0x4300 | n is the bf16 number 128 + n; (128 + n) - 135 = n - 7 exactly, and the
-// bf16 product of two bf16 numbers is the exact product rounded once, as the reference computes it.
-__device__ __forceinline__ uint4 dequant8_bf16(uint32_t word, __nv_bfloat162 scale2) {
-  const uint32_t lo = word & 0x0F0F0F0Fu, hi = (word >> 4) & 0x0F0F0F0Fu;
-  const uint32_t t[4] = {__byte_perm(lo, hi, 0x4400), __byte_perm(lo, hi, 0x5511),
-                         __byte_perm(lo, hi, 0x6622), __byte_perm(lo, hi, 0x7733)};
-  const uint32_t bias_bits = 0x43074307u;   // bf16 pair (135, 135)
-  const __nv_bfloat162 bias2 = *reinterpret_cast<const __nv_bfloat162*>(&bias_bits);
-  uint4 r;
-  uint32_t* o = &r.x;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t bits = (t[i] & 0x00FF00FFu) | 0x43004300u;
-    const __nv_bfloat162 v = __hmul2(__hsub2(*reinterpret_cast<const __nv_bfloat162*>(&bits), bias2), scale2);
-    o[i] = *reinterpret_cast<const uint32_t*>(&v);
-  }
-  return r;
-}
-
 template <int D>
 struct Layout {
+  static constexpr int CL = D / PART * 2;                // CTAs per cluster: 4 (D 128) or 2 (D 64)
   static constexpr int DCH = D / 64;                     // 64-column chunks of a head row
   static constexpr int Q_OFF = 0;                        // [NQ][DCH] tiles
   static constexpr int K_OFF = Q_OFF + NQ * DCH * TILE_BYTES;   // [DCH] tiles [128 tok x 64]
   static constexpr int VT_OFF = K_OFF + DCH * TILE_BYTES;       // [2] tiles [D rows x 64 tok]
   static constexpr int VT_TILE = D * 128;
-  static constexpr int SCRATCH_OFF = VT_OFF + 2 * VT_TILE;      // 8 warps x 4 KB: centre-row staging
-  static constexpr int RING_OFF = SCRATCH_OFF + 2 * TILE_BYTES;
-  static constexpr int SLOT_W = 0;
-  static constexpr int SLOT_CODES = D * 128;
+  static constexpr int SCRATCH_OFF = VT_OFF + 2 * VT_TILE;      // 8 warps x 2 KB: centre staging
+  static constexpr int RING_OFF = SCRATCH_OFF + TILE_BYTES;
+  static constexpr int SLOT_W = 0;                       // [64 decoder rows x 64 latent cols]
+  static constexpr int SLOT_CODES = PART * 128;          // [128 tok x 32 code bytes]
   static constexpr int SLOT_BYTES = SLOT_CODES + TOK * 32;
   __host__ __device__ static int meta_off(int nw) { return RING_OFF + nw * SLOT_BYTES; }
-  // meta: bars, tmem slot, abort, bias_k/v [D] floats, then per meta buffer (x2):
-  // crow [2][128] ints and scales [2][128][ngroups] u16
+  // meta: bars, tmem slot, abort, bias [64] floats, then two metadata buffers of
+  // crow [128] ints and scales [128][ngroups] u16
   static constexpr int BARS = 0;
   static constexpr int SLOT = NUM_BARS * 8;
   static constexpr int ABORT = SLOT + 4;
   static constexpr int BIAS = ((ABORT + 4 + 15) / 16) * 16;
-  static constexpr int CROW = BIAS + 2 * D * 4;
-  static constexpr int SCALES = CROW + 2 * 2 * TOK * 4;
+  static constexpr int CROW = BIAS + PART * 4;
+  static constexpr int SCALES = CROW + 2 * TOK * 4;
   static size_t bytes(int nw, int ngroups) {
-    return meta_off(nw) + SCALES + 2 * 2 * TOK * ngroups * 2 + 1024;
+    return meta_off(nw) + SCALES + 2 * TOK * ngroups * 2 + 1024;
   }
 };
 
@@ -125,13 +115,52 @@ __device__ __forceinline__ uint4 dequant8(uint32_t word, float scale) {
   return r;
 }
 
-// Lap timer of one thread: adds the cycles since the previous lap to a bucket.
+// Same result with bf16 pair arithmetic and no int->float conversions, for bf16 scales:
+// the bit pattern 0x4300 | n is the bf16 number 128 + n; (128 + n) - 135 = n - 7 exactly, and the
+// bf16 product of two bf16 numbers is the exact product rounded once, as the reference computes it.
+__device__ __forceinline__ uint4 dequant8_bf16(uint32_t word, __nv_bfloat162 scale2) {
+  const uint32_t lo = word & 0x0F0F0F0Fu, hi = (word >> 4) & 0x0F0F0F0Fu;
+  const uint32_t t[4] = {__byte_perm(lo, hi, 0x4400), __byte_perm(lo, hi, 0x5511),
+                         __byte_perm(lo, hi, 0x6622), __byte_perm(lo, hi, 0x7733)};
+  const uint32_t bias_bits = 0x43074307u;   // bf16 pair (135, 135)
+  const __nv_bfloat162 bias2 = *reinterpret_cast<const __nv_bfloat162*>(&bias_bits);
+  uint4 r;
+  uint32_t* o = &r.x;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t bits = (t[i] & 0x00FF00FFu) | 0x43004300u;
+    const __nv_bfloat162 v = __hmul2(__hsub2(*reinterpret_cast<const __nv_bfloat162*>(&bits), bias2), scale2);
+    o[i] = *reinterpret_cast<const uint32_t*>(&v);
+  }
+  return r;
+}
+
+// Lap timer of one thread: adds the cycles since the previous lap to a bucket kept in registers;
+// flush() adds the buckets to global memory once, at the end.
 struct Laps {
   long long* out;
-  long long last;
-  __device__ __forceinline__ void start(long long* dst, bool on) { out = on ? dst : nullptr; last = clock64(); }
+  unsigned last;
+  unsigned acc[13];
+  __device__ __forceinline__ void start(long long* dst, bool on) {
+    out = on ? dst : nullptr;
+#pragma unroll
+    for (int i = 0; i < 13; ++i) acc[i] = 0;
+    last = static_cast<unsigned>(clock64());
+  }
   __device__ __forceinline__ void lap(int bucket) {
-    if (out) { long long now = clock64(); out[bucket] += now - last; last = now; }
+    if (out) {
+      const unsigned now = static_cast<unsigned>(clock64());
+#pragma unroll
+      for (int i = 0; i < 13; ++i)
+        if (i == bucket) acc[i] += now - last;
+      last = now;
+    }
+  }
+  __device__ __forceinline__ void flush() {
+    if (out) {
+#pragma unroll
+      for (int i = 0; i < 13; ++i) out[i] += acc[i];
+    }
   }
 };
 
@@ -143,7 +172,10 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
                   const __grid_constant__ CUtensorMap map_ck,
                   const __grid_constant__ CUtensorMap map_cv, Params p) {
   using L = Layout<D>;
+  constexpr int CL = L::CL;
   extern __shared__ uint8_t smem_raw[];
+  // the dynamic shared window starts at the same offset in every CTA of the cluster, so the
+  // aligned base (and every offset from it) names the same location in each peer
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int nw = p.nw;
@@ -151,14 +183,18 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
   uint64_t* bars = reinterpret_cast<uint64_t*>(meta + L::BARS);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(meta + L::SLOT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(meta + L::ABORT);
-  float* bias = reinterpret_cast<float*>(meta + L::BIAS);            // [2][D]
-  int* crow = reinterpret_cast<int*>(meta + L::CROW);                // [2 buf][2][128]
-  uint16_t* scales = reinterpret_cast<uint16_t*>(meta + L::SCALES);  // [2 buf][2][128][ngroups]
+  float* bias = reinterpret_cast<float*>(meta + L::BIAS);            // [64] of this CTA's part
+  int* crow = reinterpret_cast<int*>(meta + L::CROW);                // [2 buf][128]
+  uint16_t* scales = reinterpret_cast<uint16_t*>(meta + L::SCALES);  // [2 buf][128][ngroups]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int head = blockIdx.y;
+  const uint32_t rank = cluster_ctarank();
+  const int tensor = static_cast<int>(rank) / (CL / 2);   // 0: this CTA rebuilds K columns, 1: V
+  const int part = static_cast<int>(rank) % (CL / 2);     // which 64-column part of the head row
+  const nkv_history& hist = tensor ? p.hv : p.hk;
   const int q0 = blockIdx.x * (NQ * QT);
-  const int nq = (q0 + QT < p.Q) ? 2 : 1;
+  const int nq = q0 >= p.Q ? 0 : ((q0 + QT < p.Q) ? 2 : 1);   // 0: decode duty only
   const int ntiles = (p.N + TOK - 1) / TOK;
   const int nchunks = p.nchunks;
   const int ng = p.ngroups;
@@ -168,59 +204,61 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
     for (int s = 0; s < MAX_NW; ++s) {
       mbar_init(&bars[W_FULL + s], 1);
       mbar_init(&bars[W_FREE + s], 1);
+    }
+    for (int s = 0; s < LAT_SLOTS; ++s) {
       mbar_init(&bars[LAT_FULL + s], COMPUTE_THREADS);
       mbar_init(&bars[LAT_FREE + s], 1);
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&bars[ACC_DONE + s], 1);
       mbar_init(&bars[META_FULL + s], 32);
       mbar_init(&bars[META_FREE + s], COMPUTE_THREADS);
       mbar_init(&bars[S_FULL + s], 1);
       mbar_init(&bars[P_READY + s], QT);
       mbar_init(&bars[PV_DONE + s], 1);
     }
-    mbar_init(&bars[KV_READY], COMPUTE_THREADS);
-    mbar_init(&bars[KEPI_DONE], COMPUTE_THREADS);
+    mbar_init(&bars[ACC_DONE], 1);
+    mbar_init(&bars[KV_READY], 1);                    // local arrival + bytes copied in by the peers
+    mbar_init(&bars[EPI_LOCAL], COMPUTE_THREADS);     // this CTA's part is in its own shared memory
+    mbar_init(&bars[KV_FREE], CL);                    // one arrival per CTA: its reads are done
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
   }
-  for (int i = tid; i < 2 * D; i += THREADS)
-    bias[i] = i < D ? p.bias_k[head * D + i] : p.bias_v[head * D + (i - D)];
+  for (int i = tid; i < PART; i += THREADS)
+    bias[i] = (tensor ? p.bias_v : p.bias_k)[head * D + part * PART + i];
   if (warp == 9) tmem_alloc(tmem_slot, 512);
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();            // every CTA's barriers exist before any peer signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 8) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      prefetch_tensormap(&map_q);
-      prefetch_tensormap(&map_wk);
-      prefetch_tensormap(&map_wv);
-      prefetch_tensormap(&map_ck);
-      prefetch_tensormap(&map_cv);
-      mbar_arrive_expect_tx(&bars[Q_FULL], nq * L::DCH * TILE_BYTES);
-      for (int i = 0; i < nq; ++i)
-        for (int c = 0; c < L::DCH; ++c)
-          tma_load_3d(smem + L::Q_OFF + (i * L::DCH + c) * TILE_BYTES, &map_q, c * 64, head,
-                      q0 + i * QT, &bars[Q_FULL]);
+      const CUtensorMap* map_w = tensor ? &map_wv : &map_wk;
+      const CUtensorMap* map_c = tensor ? &map_cv : &map_ck;
+      prefetch_tensormap(map_w);
+      prefetch_tensormap(map_c);
+      if (nq > 0) {
+        prefetch_tensormap(&map_q);
+        mbar_arrive_expect_tx(&bars[Q_FULL], nq * L::DCH * TILE_BYTES);
+        for (int i = 0; i < nq; ++i)
+          for (int c = 0; c < L::DCH; ++c)
+            tma_load_3d(smem + L::Q_OFF + (i * L::DCH + c) * TILE_BYTES, &map_q, c * 64, head,
+                        q0 + i * QT, &bars[Q_FULL]);
+      }
       bool ok = true;
-      int slot = 0, use = 0;             // ring position of chunk g = it * 2 * nchunks + ...
+      int slot = 0, use = 0;
       for (int it = 0; it < ntiles && ok; ++it) {
-        for (int which = 0; which < 2 && ok; ++which) {
-          for (int c = 0; c < nchunks && ok; ++c) {
-            if (use >= 1) ok = mbar_wait(&bars[W_FREE + slot], (use - 1) & 1, abort_flag, 110 + slot);
-            if (!ok) break;
-            uint8_t* dst = smem + L::RING_OFF + slot * L::SLOT_BYTES;
-            mbar_arrive_expect_tx(&bars[W_FULL + slot], TOK * 32 + D * 128);
-            tma_load_2d(dst + L::SLOT_CODES, which ? &map_cv : &map_ck, c * 32, it * TOK,
-                        &bars[W_FULL + slot]);
-            tma_load_2d(dst + L::SLOT_W, which ? &map_wv : &map_wk, c * CHUNK, head * D,
-                        &bars[W_FULL + slot]);
-            if (++slot == nw) { slot = 0; ++use; }
-          }
+        for (int c = 0; c < nchunks && ok; ++c) {
+          if (use >= 1) ok = mbar_wait(&bars[W_FREE + slot], (use - 1) & 1, abort_flag, 110 + slot);
+          if (!ok) break;
+          uint8_t* dst = smem + L::RING_OFF + slot * L::SLOT_BYTES;
+          mbar_arrive_expect_tx(&bars[W_FULL + slot], TOK * 32 + PART * 128);
+          tma_load_2d(dst + L::SLOT_CODES, map_c, c * 32, it * TOK, &bars[W_FULL + slot]);
+          tma_load_2d(dst + L::SLOT_W, map_w, c * CHUNK, head * D + part * PART, &bars[W_FULL + slot]);
+          if (++slot == nw) { slot = 0; ++use; }
         }
       }
       if (!ok) {  // let copies already in flight land before the CTA goes away
@@ -232,42 +270,65 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
   } else if (warp == 9) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      const uint32_t idesc_dec = make_idesc_bf16(128, D);    // [128 tok] x [D]
-      const uint32_t idesc_s = make_idesc_bf16(128, TOK);    // [128 q] x [128 tok]
-      const uint32_t idesc_pv = make_idesc_bf16(128, D);     // [128 q] x [D]
+      const uint32_t idesc_dec = make_idesc_bf16(128, PART);  // [128 tok] x [64 columns]
+      const uint32_t idesc_s = make_idesc_bf16(128, TOK);     // [128 q] x [128 tok]
+      const uint32_t idesc_pv = make_idesc_bf16(128, D);      // [128 q] x [D]
       const uint32_t smem_base = smem_u32(smem);
+      const uint16_t all_ctas = static_cast<uint16_t>((1u << CL) - 1);
       Laps laps;
       laps.start(p.prof + 16, p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0);
-      bool ok = mbar_wait(&bars[Q_FULL], 0, abort_flag, 200);
+      bool ok = nq > 0 ? mbar_wait(&bars[Q_FULL], 0, abort_flag, 200) : true;
       int slot = 0, use = 0, g = 0;
       for (int it = 0; it < ntiles && ok; ++it) {
-        for (int which = 0; which < 2 && ok; ++which) {
-          for (int c = 0; c < nchunks && ok; ++c, ++g) {
-            const int ls = g & 3, lu = g >> 2;   // four latent staging slots in TMEM
-            ok = mbar_wait(&bars[W_FULL + slot], use & 1, abort_flag, 210 + slot);
-            laps.lap(0);
-            ok = ok && mbar_wait(&bars[LAT_FULL + ls], lu & 1, abort_flag, 214 + ls);
-            laps.lap(1);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t w = smem_base + L::RING_OFF + slot * L::SLOT_BYTES + L::SLOT_W;
-            // latent chunk: 32 TMEM columns in the other tensor's (idle) accumulator region
-            const uint32_t lat = tmem_base + (which == 0 ? 128 : 0) + ls * 32;
+        for (int c = 0; c < nchunks && ok; ++c, ++g) {
+          const int ls = g & 3, lu = g >> 2;
+          ok = mbar_wait(&bars[W_FULL + slot], use & 1, abort_flag, 210 + slot);
+          laps.lap(0);
+          ok = ok && mbar_wait(&bars[LAT_FULL + ls], lu & 1, abort_flag, 216 + ls);
+          laps.lap(1);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t w = smem_base + L::RING_OFF + slot * L::SLOT_BYTES + L::SLOT_W;
+          const uint32_t lat = tmem_base + 128 + ls * 32;     // latent chunk staged in TMEM
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              mma_bf16_ts(tmem_base + which * 128, lat + k * 8, make_smem_desc_sw128(w + k * 32),
-                          idesc_dec, c > 0 || k > 0);
-            mma_commit(&bars[W_FREE + slot]);
-            mma_commit(&bars[LAT_FREE + ls]);
-            if (c == nchunks - 1) mma_commit(&bars[ACC_DONE + which]);
-            if (++slot == nw) { slot = 0; ++use; }
-            laps.lap(2);
-          }
+          for (int k = 0; k < 4; ++k)
+            mma_bf16_ts(tmem_base, lat + k * 8, make_smem_desc_sw128(w + k * 32), idesc_dec,
+                        c > 0 || k > 0);
+          mma_commit(&bars[W_FREE + slot]);
+          mma_commit(&bars[LAT_FREE + ls]);
+          if (c == nchunks - 1) mma_commit(&bars[ACC_DONE]);
+          if (++slot == nw) { slot = 0; ++use; }
+          laps.lap(2);
         }
         if (!ok) break;
-        ok = mbar_wait(&bars[KV_READY], it & 1, abort_flag, 220);
+        // exchange: once this CTA's part is complete locally and every CTA has finished reading
+        // the previous tile, copy the part into each peer (asynchronous shared-to-shared copies
+        // that report to the peer's KV_READY), then wait for the peers' parts to land here
+        ok = mbar_wait(&bars[EPI_LOCAL], it & 1, abort_flag, 218);
+        if (ok && it > 0) ok = mbar_wait_cluster(&bars[KV_FREE], (it - 1) & 1, abort_flag, 219);
+        if (!ok) break;
+        {
+          const uint32_t ready = smem_u32(&bars[KV_READY]);
+          for (uint32_t step = 1; step < CL; ++step) {
+            const uint32_t peer = (rank + step) % CL;
+            const uint32_t peer_ready = map_to_cta(ready, peer);
+            if (tensor == 0) {
+              const uint32_t src = smem_base + L::K_OFF + part * TILE_BYTES;
+              bulk_copy_to_peer(map_to_cta(src, peer), src, TILE_BYTES, peer_ready);
+            } else {
+#pragma unroll
+              for (int half = 0; half < 2; ++half) {
+                const uint32_t src = smem_base + L::VT_OFF + half * L::VT_TILE + part * PART * 128;
+                bulk_copy_to_peer(map_to_cta(src, peer), src, PART * 128, peer_ready);
+              }
+            }
+          }
+          mbar_arrive_expect_tx(&bars[KV_READY], (CL - 1) * TILE_BYTES);
+        }
+        ok = mbar_wait_cluster(&bars[KV_READY], it & 1, abort_flag, 220);
         laps.lap(3);
         if (!ok) break;
+        fence_proxy_async_all();
         tc_fence_after();
         for (int i = 0; i < nq; ++i) {
 #pragma unroll
@@ -294,8 +355,17 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           }
           mma_commit(&bars[PV_DONE + i]);
         }
+        if (!ok) break;
+        // tell every CTA of the cluster that this CTA no longer reads the tile's K / V
+        if (nq > 0) {
+          mma_commit_multicast(&bars[KV_FREE], all_ctas);
+        } else {
+          const uint32_t local = smem_u32(&bars[KV_FREE]);
+          for (uint32_t peer = 0; peer < CL; ++peer) mbar_arrive_cluster(map_to_cta(local, peer));
+        }
         laps.lap(6);
       }
+      laps.flush();
     }
     __syncwarp();
   } else if (warp == 10) {
@@ -306,23 +376,19 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       if (u >= 1) ok = mbar_wait(&bars[META_FREE + b], (u - 1) & 1, abort_flag, 240 + b);
       if (!ok) break;
       const int t0 = it * TOK;
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        const nkv_history& h = which ? p.hv : p.hk;
-        for (int r = lane; r < TOK; r += 32) {
-          const int t = t0 + r;
-          const bool in = t < p.N;
-          crow[(b * 2 + which) * TOK + r] = in ? center_row_of(h, t) : 0;
-          const uint16_t* src = static_cast<const uint16_t*>(h.scales) + static_cast<size_t>(t) * ng;
-          uint16_t* dst = scales + static_cast<size_t>((b * 2 + which) * TOK + r) * ng;
-          for (int gi = 0; gi < ng; ++gi) dst[gi] = in ? src[gi] : 0;
-        }
+      for (int r = lane; r < TOK; r += 32) {
+        const int t = t0 + r;
+        const bool in = t < p.N;
+        crow[b * TOK + r] = in ? center_row_of(hist, t) : 0;
+        const uint16_t* src = static_cast<const uint16_t*>(hist.scales) + static_cast<size_t>(t) * ng;
+        uint16_t* dst = scales + static_cast<size_t>(b * TOK + r) * ng;
+        for (int gi = 0; gi < ng; ++gi) dst[gi] = in ? src[gi] : 0;
       }
       mbar_arrive(&bars[META_FULL + b]);
     }
   } else {
     // ------------------------------------------------------------ compute warps
-    const int wg = tid >> 7;                    // query tile this thread's softmax serves
+    const int wg = tid >> 7;                    // query tile served; also the 32-column half of the part
     const int row = tid & 127;                  // TMEM lane == token row == query row
     const uint32_t lane_sel = static_cast<uint32_t>(32 * (warp & 3)) << 16;
     float m_used = -INFINITY, l_run = 0.f;
@@ -334,7 +400,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       const int t0 = it * TOK;
       const int valid = min(TOK, p.N - t0);
       const int mb = it & 1;
-      if (it > 0) {  // P of the previous tile lives in the K tile and the latent ring
+      if (it > 0) {  // P and S of the previous tile live where the accumulator and the staging go
         for (int i = 0; i < nq && ok; ++i)
           ok = mbar_wait(&bars[PV_DONE + i], (it - 1) & 1, abort_flag, 300 + i);
         if (!ok) break;
@@ -344,80 +410,69 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       ok = mbar_wait(&bars[META_FULL + mb], (it >> 1) & 1, abort_flag, 310);
       laps.lap(1);
       if (!ok) break;
-      // ---- per tensor: expand codes to bf16 latent chunks in tensor memory (the A operand of
-      // the decode MMA), then the epilogue: bias, centre, two bf16 roundings, park in shared memory
-      for (int which = 0; which < 2 && ok; ++which) {
-        if (which == 1) {
-          // V's latent staging reuses K-accumulator columns: every thread must have read them
-          ok = mbar_wait(&bars[KEPI_DONE], it & 1, abort_flag, 326);
-          if (!ok) break;
-        }
-        for (int c = 0; c < nchunks && ok; ++c, ++g) {
-          const int ls = g & 3, lu = g >> 2;   // four latent staging slots in TMEM
-          ok = mbar_wait(&bars[W_FULL + slot], use & 1, abort_flag, 320 + slot);
-          laps.lap(2);
-          if (ok && lu >= 1) ok = mbar_wait(&bars[LAT_FREE + ls], (lu - 1) & 1, abort_flag, 324 + ls);
-          laps.lap(3);
-          if (!ok) break;
-          tc_fence_after();
-          const uint8_t* codes = smem + L::RING_OFF + slot * L::SLOT_BYTES + L::SLOT_CODES;
-          const int half = wg;        // this thread: token `row`, latent columns half*32 .. +32
-          const uint4 code = *reinterpret_cast<const uint4*>(codes + row * 32 + half * 16);
-          const int col0 = c * CHUNK + half * 32;
-          const uint16_t sbits =
-              scales[static_cast<size_t>((mb * 2 + which) * TOK + row) * p.ngroups + col0 / p.group];
-          const uint32_t words[4] = {code.x, code.y, code.z, code.w};
-          uint32_t packed[16];
-          if (p.scale_dtype == NKV_BF16) {
-            const uint32_t pair = static_cast<uint32_t>(sbits) * 0x00010001u;
-            const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&pair);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint4 v = dequant8_bf16(words[j], scale2);
-              packed[4 * j] = v.x; packed[4 * j + 1] = v.y; packed[4 * j + 2] = v.z; packed[4 * j + 3] = v.w;
-            }
-          } else {
-            const float sc = scale_to_float(sbits, p.scale_dtype);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint4 v = dequant8(words[j], sc);
-              packed[4 * j] = v.x; packed[4 * j + 1] = v.y; packed[4 * j + 2] = v.z; packed[4 * j + 3] = v.w;
-            }
-          }
-          tmem_st16(tmem_base + lane_sel + (which == 0 ? 128 : 0) + ls * 32 + half * 16, packed);
-          tmem_wait_st();
-          laps.lap(4);
-          tc_fence_before();
-          mbar_arrive(&bars[LAT_FULL + ls]);
-          laps.lap(5);
-          if (++slot == nw) { slot = 0; ++use; }
-        }
+      // ---- expand this CTA's codes to bf16 latent chunks in tensor memory (A of the decode MMA)
+      for (int c = 0; c < nchunks && ok; ++c, ++g) {
+        const int ls = g & 3, lu = g >> 2;
+        ok = mbar_wait(&bars[W_FULL + slot], use & 1, abort_flag, 320 + slot);
+        laps.lap(2);
+        if (ok && lu >= 1) ok = mbar_wait(&bars[LAT_FREE + ls], (lu - 1) & 1, abort_flag, 326 + ls);
+        laps.lap(3);
         if (!ok) break;
-        const nkv_history& h = which ? p.hv : p.hk;
+        tc_fence_after();
+        const uint8_t* codes = smem + L::RING_OFF + slot * L::SLOT_BYTES + L::SLOT_CODES;
+        const uint4 code = *reinterpret_cast<const uint4*>(codes + row * 32 + wg * 16);
+        const int col0 = c * CHUNK + wg * 32;   // this thread: token `row`, latent columns col0 .. +32
+        const uint16_t sbits = scales[static_cast<size_t>(mb * TOK + row) * ng + col0 / p.group];
+        const uint32_t words[4] = {code.x, code.y, code.z, code.w};
+        uint32_t packed[16];
+        if (p.scale_dtype == NKV_BF16) {
+          const uint32_t pair = static_cast<uint32_t>(sbits) * 0x00010001u;
+          const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&pair);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint4 v = dequant8_bf16(words[j], scale2);
+            packed[4 * j] = v.x; packed[4 * j + 1] = v.y; packed[4 * j + 2] = v.z; packed[4 * j + 3] = v.w;
+          }
+        } else {
+          const float sc = scale_to_float(sbits, p.scale_dtype);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint4 v = dequant8(words[j], sc);
+            packed[4 * j] = v.x; packed[4 * j + 1] = v.y; packed[4 * j + 2] = v.z; packed[4 * j + 3] = v.w;
+          }
+        }
+        tmem_st16(tmem_base + lane_sel + 128 + ls * 32 + wg * 16, packed);
+        tmem_wait_st();
+        laps.lap(4);
+        tc_fence_before();
+        mbar_arrive(&bars[LAT_FULL + ls]);
+        laps.lap(5);
+        if (++slot == nw) { slot = 0; ++use; }
+      }
+      if (!ok) break;
+      // ---- epilogue of this CTA's part: bias, centre, two bf16 roundings, store to every CTA
+      {
         const bool in = row < valid;
-        const int colhalf = warp >> 2;
-        const int colbase = colhalf * (D / 2);
-        // Centre rows of this warp's 32 tokens (D/2 columns each), gathered cooperatively: PIECES
-        // lanes read one row's 16-byte pieces, so a load instruction touches 32/PIECES lines
-        // instead of 32; the rows are then redistributed through a swizzled staging area in the
-        // scratch area of shared memory.
-        constexpr int PIECES = D / 16, RPI = 32 / PIECES;
+        // Centre rows of this warp's 32 tokens (32 columns = 64 bytes each), gathered
+        // cooperatively: 4 lanes read one row's 16-byte pieces, so a load instruction touches
+        // 8 lines instead of 32; the rows are redistributed through a swizzled staging area.
+        constexpr int PIECES = 4, RPI = 8;
         const int wrow0 = 32 * (warp & 3);
-        const uint16_t* cbase = static_cast<const uint16_t*>(h.centers) +
-                                static_cast<size_t>(head) * D + colbase;
+        const uint16_t* cbase = static_cast<const uint16_t*>(hist.centers) +
+                                static_cast<size_t>(head) * D + part * PART + wg * 32;
         uint4 cen[PIECES];
 #pragma unroll
         for (int i = 0; i < PIECES; ++i) {
           const int rloc = i * RPI + lane / PIECES, piece = lane % PIECES;
-          const int crow_i = crow[(mb * 2 + which) * TOK + wrow0 + rloc];
+          const int crow_i = crow[mb * TOK + wrow0 + rloc];
           cen[i] = __ldg(reinterpret_cast<const uint4*>(
-              cbase + static_cast<size_t>(crow_i) * h.center_width + piece * 8));
+              cbase + static_cast<size_t>(crow_i) * hist.center_width + piece * 8));
         }
         laps.lap(6);
-        ok = mbar_wait(&bars[ACC_DONE + which], it & 1, abort_flag, 330 + which);
+        ok = mbar_wait(&bars[ACC_DONE], it & 1, abort_flag, 330);
+        laps.lap(7);
         if (!ok) break;
         tc_fence_after();
-        laps.lap(7);
         {
           uint8_t* stage = smem + L::SCRATCH_OFF + warp * (32 * PIECES * 16);
 #pragma unroll
@@ -433,53 +488,53 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
                                                      ((j ^ (lane & (PIECES - 1))) << 4));
           __syncwarp();
         }
+        float v[32];
+        tmem_ld32(tmem_base + lane_sel + wg * 32, v);
+        uint32_t packed[16];
 #pragma unroll
-        for (int cc = 0; cc < D / 64; ++cc) {
-          const int col = colbase + cc * 32;
-          float v[32];
-          tmem_ld32(tmem_base + lane_sel + which * 128 + col, v);
-          uint32_t packed[16];
+        for (int j4 = 0; j4 < 4; ++j4) {
+          const uint32_t cwords[4] = {cen[j4].x, cen[j4].y, cen[j4].z, cen[j4].w};
 #pragma unroll
-          for (int j4 = 0; j4 < 4; ++j4) {
-            const uint4 cw = cen[cc * 4 + j4];
-            const uint32_t cwords[4] = {cw.x, cw.y, cw.z, cw.w};
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-              const int j = j4 * 8 + w * 2;
-              float x0 = round_to_bf16(v[j] + bias[which * D + col + j]);
-              float x1 = round_to_bf16(v[j + 1] + bias[which * D + col + j + 1]);
-              x0 += __uint_as_float(cwords[w] << 16);
-              x1 += __uint_as_float(cwords[w] & 0xFFFF0000u);
-              packed[j4 * 4 + w] = in ? pack_bf16x2(x0, x1) : 0u;
-            }
-          }
-          if (which == 0) {
-            uint8_t* tile = smem + L::K_OFF + (col >> 6) * TILE_BYTES;
-#pragma unroll
-            for (int j4 = 0; j4 < 4; ++j4)
-              *reinterpret_cast<uint4*>(tile + sw128_offset(row, (col & 63) + j4 * 8)) =
-                  make_uint4(packed[j4 * 4], packed[j4 * 4 + 1], packed[j4 * 4 + 2], packed[j4 * 4 + 3]);
-          } else {
-            uint8_t* tile = smem + L::VT_OFF + (row >> 6) * L::VT_TILE;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const uint32_t wv = packed[j >> 1];
-              const uint16_t bits = (j & 1) ? static_cast<uint16_t>(wv >> 16) : static_cast<uint16_t>(wv & 0xFFFFu);
-              *reinterpret_cast<uint16_t*>(tile + sw128_offset(col + j, row & 63)) = bits;
-            }
+          for (int w = 0; w < 4; ++w) {
+            const int j = j4 * 8 + w * 2;
+            float x0 = round_to_bf16(v[j] + bias[wg * 32 + j]);
+            float x1 = round_to_bf16(v[j + 1] + bias[wg * 32 + j + 1]);
+            x0 += __uint_as_float(cwords[w] << 16);
+            x1 += __uint_as_float(cwords[w] & 0xFFFF0000u);
+            packed[j4 * 4 + w] = in ? pack_bf16x2(x0, x1) : 0u;
           }
         }
-        if (which == 0) {
-          tc_fence_before();
-          mbar_arrive(&bars[KEPI_DONE]);
+        tc_fence_before();
+        if (it > 0) {  // every CTA has finished reading the previous tile's K / V
+          ok = mbar_wait_cluster(&bars[KV_FREE], (it - 1) & 1, abort_flag, 332);
+          if (!ok) break;
+        }
+        if (tensor == 0) {
+          uint8_t* tile = smem + L::K_OFF + part * TILE_BYTES;
+#pragma unroll
+          for (int j4 = 0; j4 < 4; ++j4)
+            *reinterpret_cast<uint4*>(tile + sw128_offset(row, wg * 32 + j4 * 8)) =
+                make_uint4(packed[j4 * 4], packed[j4 * 4 + 1], packed[j4 * 4 + 2], packed[j4 * 4 + 3]);
+        } else {
+          // transposed store: lanes l and l^1 hold neighbouring tokens and trade halves so that
+          // each writes whole 32-bit words (token pair) of 16 of the 32 columns
+          uint8_t* tile = smem + L::VT_OFF + (row >> 6) * L::VT_TILE;
+          const bool odd = lane & 1;
+#pragma unroll
+          for (int m = 0; m < 16; ++m) {
+            const uint32_t mine = packed[m];
+            const uint32_t got = __shfl_xor_sync(0xffffffffu, odd ? (mine & 0xFFFFu) : (mine >> 16), 1);
+            const uint32_t word = odd ? ((got & 0xFFFFu) | (mine & 0xFFFF0000u))
+                                      : ((mine & 0xFFFFu) | (got << 16));
+            const int d = part * PART + wg * 32 + 2 * m + (odd ? 1 : 0);
+            *reinterpret_cast<uint32_t*>(tile + sw128_offset(d, (row & 63) & ~1)) = word;
+          }
         }
       }
-      if (!ok) break;
       laps.lap(8);
       mbar_arrive(&bars[META_FREE + mb]);
-      tc_fence_before();
       fence_proxy_async();
-      mbar_arrive(&bars[KV_READY]);
+      mbar_arrive(&bars[EPI_LOCAL]);
       laps.lap(9);
       // ---- online softmax of this thread's query row
       if (wg < nq) {
@@ -556,6 +611,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         laps.lap(12);
       }
     }
+    laps.flush();
     // ---- write O / l and the natural-log LSE
     if (ok && wg < nq && ntiles > 0) {
       ok = mbar_wait(&bars[PV_DONE + wg], (ntiles - 1) & 1, abort_flag, 350 + wg);
@@ -589,6 +645,8 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
   }
   tc_fence_before();
   __syncthreads();
+  // no CTA may leave while a peer can still store into its shared memory or signal its barriers
+  cluster_sync_all();
   if (warp == 9) tmem_dealloc(tmem_base, 512);
   if (tid == 0 && *abort_flag && p.status) atomicCAS(p.status, 0, *abort_flag);
 }
@@ -604,9 +662,10 @@ long long* g_profile = nullptr;
 
 template <int D>
 int launch(const CUtensorMap maps[5], Params& p, cudaStream_t stream) {
+  using L = Layout<D>;
   int nw = MAX_NW;
-  while (nw > 2 && Layout<D>::bytes(nw, p.ngroups) > SMEM_LIMIT) --nw;
-  size_t smem = Layout<D>::bytes(nw, p.ngroups);
+  while (nw > 2 && L::bytes(nw, p.ngroups) > SMEM_LIMIT) --nw;
+  size_t smem = L::bytes(nw, p.ngroups);
   NKV_REQUIRE(smem <= SMEM_LIMIT, NKV_ERR_UNSUPPORTED,
               "codec attention needs %zu bytes of shared memory (rank/group = %d too fine)", smem,
               p.ngroups);
@@ -615,9 +674,20 @@ int launch(const CUtensorMap maps[5], Params& p, cudaStream_t stream) {
   auto kernel = attn_codec_kernel<D>;
   NKV_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(smem)));
-  dim3 grid(ceil_div(p.Q, NQ * QT), p.heads);
-  kernel<<<grid, THREADS, smem, stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
-  NKV_LAUNCH_CHECK("attn_codec_kernel");
+  const int qblocks = ceil_div(p.Q, NQ * QT);
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(ceil_div(qblocks, L::CL) * L::CL, p.heads);   // padded: idle CTAs still decode
+  config.blockDim = dim3(THREADS);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = L::CL;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  config.attrs = &attr;
+  config.numAttrs = 1;
+  NKV_CUDA(cudaLaunchKernelEx(&config, kernel, maps[0], maps[1], maps[2], maps[3], maps[4], p));
   return NKV_OK;
 }
 
@@ -668,7 +738,7 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
   for (int w = 0; w < 2; ++w) {
     uint64_t dims[2] = {static_cast<uint64_t>(rank), static_cast<uint64_t>(heads) * dk};
     uint64_t strides[1] = {static_cast<uint64_t>(rank) * 2};
-    uint32_t box[2] = {64, static_cast<uint32_t>(dk)};
+    uint32_t box[2] = {64, PART};   // one CTA streams 64 rows of the slice
     int rc = encode_tensor_map(&maps[1 + w], 2, weights[w], 2, dims, strides, box, true);
     if (rc != NKV_OK) return rc;
   }

@@ -1,0 +1,188 @@
+"""Matrix-Game codec interface on the B200 kernels.
+
+Same function names, argument meaning, payload dictionaries and error classes
+as the reference module MGM/nanokv_codec.py (encode_tensor :334-365,
+decode_tensor :369-390, decode_value :516-539, concat_values :600-609,
+value_shape :489-513, payload_bytes :697-704), so its call sites in the
+backbone (MGM/wan_video_dit.py:493-500,710-795) can import this module
+instead.  Operators are registered explicitly (`register_operator`) rather
+than read from checkpoint directories.
+"""
+from __future__ import annotations
+
+import os
+from typing import Any
+
+import torch
+
+from . import ops
+from .cache import CompressedHistory
+from .codec import F32_EPS, Operator, kmeans_init_rows
+
+CODEC = "worldplay_c64_pca_int4_v1"
+SEGMENTS = "worldplay_segments_v1"
+RAW = "worldplay_raw_v1"
+
+_OPERATORS: dict[tuple[str, int, str], Operator] = {}
+
+
+def register_operator(kind: str, layer: int, *, mean, encoder, decoder, device="cuda") -> Operator:
+    """Make (mean [J], encoder [r,J], decoder [J,r]) resident for (kind, layer).
+    fp32 or bf16 weights select the arithmetic, as the reference's operator storage does."""
+    if kind not in {"k", "v"}:
+        raise ValueError(kind)
+    op = Operator(mean, encoder, decoder, device=device)
+    _OPERATORS[(kind, int(layer), str(torch.device(device)))] = op
+    return op
+
+
+def _operator(kind: str, layer: int, device) -> Operator:
+    device = torch.device(device)
+    for key in ((kind, int(layer), str(device)), (kind, int(layer), device.type)):
+        if key in _OPERATORS:
+            return _OPERATORS[key]
+    raise KeyError(f"no operator registered for {kind}:{int(layer):02d} on {device}")
+
+
+def _clusters() -> int:
+    return int(os.environ.get("MG35_KVCODEC_C64_CLUSTERS", "64"))
+
+
+def _iterations() -> int:
+    return int(os.environ.get("MG35_KVCODEC_C64_ITERS", "2"))
+
+
+@torch.no_grad()
+def encode_tensor(kind: str, layer: int, value: torch.Tensor) -> dict:
+    """value [1,S,J] on the GPU -> the reference's payload dictionary."""
+    if kind not in {"k", "v"}:
+        raise ValueError(kind)
+    if value.dim() != 3 or value.shape[0] != 1:
+        raise ValueError(f"expected [1,S,J], got {tuple(value.shape)}")
+    _, sequence, dim = value.shape
+    clusters = _clusters()
+    if clusters <= 0 or clusters > sequence or clusters > 256:
+        raise ValueError(f"C64 clusters must be in [1,min(S,256)], got {clusters}")
+    op = _operator(kind, layer, value.device)
+    rows = value[0].contiguous()
+    init = kmeans_init_rows(sequence, clusters, 20260804 + int(layer)).to(value.device)
+    centers, ids = ops.kmeans(rows, clusters, _iterations(), init)
+    coeff = ops.project(rows, centers, ids, op.mean, op.encoder)
+    packed, scale = ops.quant_pack(coeff, eps=F32_EPS,
+                                   in_coeff_dtype=coeff.dtype == torch.bfloat16)
+    return {
+        "codec": CODEC, "kind": kind, "layer": int(layer),
+        "shape": tuple(int(v) for v in value.shape),
+        "latent_shape": (sequence, op.rank), "latent_numel": sequence * op.rank,
+        "packed_codes": packed.reshape(-1), "scale": scale,
+        "centers": centers[None], "ids": ids[None], "semantic": True,
+        "source_dtype": str(value.dtype).replace("torch.", ""),
+    }
+
+
+def is_payload(value: Any) -> bool:
+    return isinstance(value, dict) and value.get("codec") in {RAW, CODEC, SEGMENTS}
+
+
+def _parts(value: dict) -> list[dict]:
+    return list(value["segments"]) if value.get("codec") == SEGMENTS else [value]
+
+
+def concat_values(left: Any, right: Any) -> Any:
+    if left is None:
+        return right
+    if right is None:
+        return left
+    if not is_payload(left) or not is_payload(right):
+        raise RuntimeError("WorldPlay packed-cache concat received a raw/payload mixture")
+    return {"codec": SEGMENTS, "segments": _parts(left) + _parts(right)}
+
+
+def value_shape(value: Any):
+    if value is None:
+        return None
+    if torch.is_tensor(value):
+        return tuple(int(v) for v in value.shape)
+    if value.get("codec") == RAW:
+        return tuple(int(v) for v in value["tensor"].shape)
+    if value.get("codec") == CODEC:
+        return tuple(int(v) for v in value["shape"])
+    if value.get("codec") == SEGMENTS:
+        shapes = [value_shape(item) for item in value["segments"]]
+        if not shapes:
+            return None
+        return (shapes[0][0], sum(shape[1] for shape in shapes), shapes[0][2])
+    raise RuntimeError(f"unsupported cache value {value.get('codec')}")
+
+
+def payload_bytes(value: Any) -> int:
+    if torch.is_tensor(value):
+        return value.numel() * value.element_size()
+    if isinstance(value, dict):
+        return sum(payload_bytes(v) for k, v in value.items() if not str(k).startswith("_"))
+    if isinstance(value, (list, tuple)):
+        return sum(payload_bytes(v) for v in value)
+    return 0
+
+
+def history_from_payloads(parts: list[dict], *, device) -> CompressedHistory:
+    """Stack same-layer payload segments into one struct-of-arrays history."""
+    first = parts[0]
+    kind, layer = str(first["kind"]), int(first["layer"])
+    batch, _, dim = (int(v) for v in first["shape"])
+    rank = int(first["latent_shape"][-1])
+    for part in parts:
+        if (part.get("codec") != CODEC or str(part["kind"]) != kind or int(part["layer"]) != layer
+                or int(part["shape"][0]) != batch or int(part["shape"][2]) != dim):
+            raise ValueError("incompatible WorldPlay method segments")
+    if batch != 1:
+        raise ValueError("only batch 1 payloads are supported")
+    total = sum(int(part["shape"][1]) for part in parts)
+    clusters = max(int(part["centers"].shape[1]) for part in parts)
+    hist = CompressedHistory(joint=dim, rank=rank, capacity=total, max_segments=len(parts),
+                             centers_per_segment=clusters, device=device)
+    for part in parts:
+        count = int(part["shape"][1])
+        offset, rows = hist.reserve_segment(count, int(part["centers"].shape[1]))
+        rows.copy_(part["centers"][0].to(device=device, dtype=torch.bfloat16))
+        hist.codes[offset:offset + count].copy_(part["packed_codes"].to(device).reshape(count, -1))
+        hist.scales[offset:offset + count].copy_(part["scale"].to(device).reshape(count, -1))
+        hist.ids[offset:offset + count].copy_(part["ids"].to(device).reshape(-1))
+    return hist
+
+
+@torch.no_grad()
+def decode_tensor(payload: dict, *, dtype: torch.dtype, device) -> torch.Tensor:
+    if payload.get("codec") == RAW:
+        return payload["tensor"].to(device=device, dtype=dtype)
+    if payload.get("codec") != CODEC:
+        raise RuntimeError(f"unsupported WorldPlay payload {payload.get('codec')}")
+    return _decode_parts([payload], dtype=dtype, device=device)
+
+
+def _decode_parts(parts: list[dict], *, dtype, device) -> torch.Tensor:
+    hist = history_from_payloads(parts, device=device)
+    op = _operator(str(parts[0]["kind"]), int(parts[0]["layer"]), device)
+    rows = ops.decode_rows(hist.view(), op.decoder, op.mean, dtype=dtype)
+    return rows.reshape(1, hist.tokens, hist.joint)
+
+
+@torch.no_grad()
+def decode_value(value: Any, *, dtype: torch.dtype, device):
+    if value is None:
+        return None
+    if torch.is_tensor(value):
+        return value.to(device=device, dtype=dtype)
+    if value.get("codec") == SEGMENTS:
+        parts = value["segments"]
+        if not parts:
+            return None
+        if all(part.get("codec") == CODEC for part in parts):
+            return _decode_parts(parts, dtype=dtype, device=device)
+        return torch.cat([decode_value(p, dtype=dtype, device=device) for p in parts], dim=1)
+    return decode_tensor(value, dtype=dtype, device=device)
+
+
+def decode_pair_values(key: Any, value: Any, *, dtype: torch.dtype, device):
+    return (decode_value(key, dtype=dtype, device=device),
+            decode_value(value, dtype=dtype, device=device))
