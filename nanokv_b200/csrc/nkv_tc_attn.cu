@@ -28,7 +28,7 @@
 // arrivals and multicast commits.  No TMA load uses multicast.
 //
 // TMEM columns: [0,128) S of query tile 0 (decode accumulator in [0,64));
-// [128,256) S of tile 1 (latent staging, four 32-column slots); [256,384) O
+// [128,256) S of tile 1 (latent staging slots, 32 columns each; two more in [64,128)); [256,384) O
 // tile 0; [384,512) O tile 1.
 #include "nkv_internal.h"
 #include "nkv_tc.cuh"
@@ -47,14 +47,13 @@ constexpr int THREADS = COMPUTE_THREADS + 96;
 constexpr int CHUNK = 64;         // latent columns per pipeline step
 constexpr int PART = 64;          // K/V columns rebuilt by one CTA
 constexpr int TILE_BYTES = 128 * 128;  // one [128 rows x 64 bf16] swizzled tile
-constexpr int MAX_NW = 6;
-constexpr int LAT_SLOTS = 4;
+constexpr int MAX_NW = 6;         // ring slots: operand bytes in shared memory + latent staging in TMEM
 constexpr float RESCALE_THRESHOLD = 8.0f;
 
 enum Bar {
-  Q_FULL = 0, W_FULL = 1, W_FREE = 7, LAT_FULL = 13, LAT_FREE = 17, ACC_DONE = 21,
+  Q_FULL = 0, W_FULL = 1, RING_FREE = 7, LAT_FULL = 13,
   META_FULL = 22, META_FREE = 24, KV_READY = 26, KV_FREE = 27, S_FULL = 28, P_READY = 30,
-  PV_DONE = 32, EPI_LOCAL = 34, NUM_BARS = 35
+  PV_DONE = 32, EPI_LOCAL = 34, CODES_FULL = 35, CODES_FREE = 36, NUM_BARS = 37
 };
 
 struct Params {
@@ -79,11 +78,11 @@ struct Layout {
   static constexpr int VT_OFF = K_OFF + DCH * TILE_BYTES;       // [2] tiles [D rows x 64 tok]
   static constexpr int VT_TILE = D * 128;
   static constexpr int SCRATCH_OFF = VT_OFF + 2 * VT_TILE;      // 8 warps x 2 KB: centre staging
-  static constexpr int RING_OFF = SCRATCH_OFF + TILE_BYTES;
-  static constexpr int SLOT_W = 0;                       // [64 decoder rows x 64 latent cols]
-  static constexpr int SLOT_CODES = PART * 128;          // [128 tok x 32 code bytes]
-  static constexpr int SLOT_BYTES = SLOT_CODES + TOK * 32;
-  __host__ __device__ static int meta_off(int nw) { return RING_OFF + nw * SLOT_BYTES; }
+  static constexpr int CODES_OFF = SCRATCH_OFF + TILE_BYTES;    // [128 tok][rank/2] codes of the tile
+  __host__ __device__ static int codes_bytes(int rank) { return ((TOK * rank / 2 + 1023) / 1024) * 1024; }
+  __host__ __device__ static int ring_off(int rank) { return CODES_OFF + codes_bytes(rank); }
+  static constexpr int SLOT_BYTES = PART * 128;          // [64 decoder rows x 64 latent cols]
+  __host__ __device__ static int meta_off(int nw, int rank) { return ring_off(rank) + nw * SLOT_BYTES; }
   // meta: bars, tmem slot, abort, bias [64] floats, then two metadata buffers of
   // crow [128] ints and scales [128][ngroups] u16
   static constexpr int BARS = 0;
@@ -92,8 +91,8 @@ struct Layout {
   static constexpr int BIAS = ((ABORT + 4 + 15) / 16) * 16;
   static constexpr int CROW = BIAS + PART * 4;
   static constexpr int SCALES = CROW + 2 * TOK * 4;
-  static size_t bytes(int nw, int ngroups) {
-    return meta_off(nw) + SCALES + 2 * TOK * ngroups * 2 + 1024;
+  static size_t bytes(int nw, int ngroups, int rank) {
+    return meta_off(nw, rank) + SCALES + 2 * TOK * ngroups * 2 + 1024;
   }
 };
 
@@ -135,6 +134,10 @@ __device__ __forceinline__ uint4 dequant8_bf16(uint32_t word, __nv_bfloat162 sca
   return r;
 }
 
+// TMEM column of latent staging slot s: four slots in the S region of query tile 1, two more in
+// the upper half of tile 0's (the decode accumulator only uses its first 64 columns)
+__device__ __forceinline__ uint32_t staging_col(int s) { return s < 4 ? 128 + 32 * s : 64 + 32 * (s - 4); }
+
 // Lap timer of one thread: adds the cycles since the previous lap to a bucket kept in registers;
 // flush() adds the buckets to global memory once, at the end.
 struct Laps {
@@ -168,9 +171,7 @@ template <int D>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
                   const __grid_constant__ CUtensorMap map_wk,
-                  const __grid_constant__ CUtensorMap map_wv,
-                  const __grid_constant__ CUtensorMap map_ck,
-                  const __grid_constant__ CUtensorMap map_cv, Params p) {
+                  const __grid_constant__ CUtensorMap map_wv, Params p) {
   using L = Layout<D>;
   constexpr int CL = L::CL;
   extern __shared__ uint8_t smem_raw[];
@@ -179,7 +180,9 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int nw = p.nw;
-  uint8_t* meta = smem + L::meta_off(nw);
+  uint8_t* meta = smem + L::meta_off(nw, p.rank);
+  const int ring_off = L::ring_off(p.rank);
+  const int row_bytes = p.rank / 2;          // code bytes per token
   uint64_t* bars = reinterpret_cast<uint64_t*>(meta + L::BARS);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(meta + L::SLOT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(meta + L::ABORT);
@@ -202,12 +205,9 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
   if (tid == 0) {
     mbar_init(&bars[Q_FULL], 1);
     for (int s = 0; s < MAX_NW; ++s) {
-      mbar_init(&bars[W_FULL + s], 1);
-      mbar_init(&bars[W_FREE + s], 1);
-    }
-    for (int s = 0; s < LAT_SLOTS; ++s) {
-      mbar_init(&bars[LAT_FULL + s], COMPUTE_THREADS);
-      mbar_init(&bars[LAT_FREE + s], 1);
+      mbar_init(&bars[W_FULL + s], 1);                      // TMA: codes + decoder rows landed
+      mbar_init(&bars[LAT_FULL + s], COMPUTE_THREADS);      // latent chunk staged in TMEM
+      mbar_init(&bars[RING_FREE + s], 1);                   // the chunk's MMAs are complete
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bars[META_FULL + s], 32);
@@ -216,10 +216,11 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(&bars[P_READY + s], QT);
       mbar_init(&bars[PV_DONE + s], 1);
     }
-    mbar_init(&bars[ACC_DONE], 1);
     mbar_init(&bars[KV_READY], 1);                    // local arrival + bytes copied in by the peers
     mbar_init(&bars[EPI_LOCAL], COMPUTE_THREADS);     // this CTA's part is in its own shared memory
-    mbar_init(&bars[KV_FREE], CL);                    // one arrival per CTA: its reads are done
+    mbar_init(&bars[KV_FREE], CL);
+    mbar_init(&bars[CODES_FULL], 1);                  // the tile's codes landed (one bulk copy)
+    mbar_init(&bars[CODES_FREE], COMPUTE_THREADS);    // every thread is done expanding them                    // one arrival per CTA: its reads are done
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -237,9 +238,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       const CUtensorMap* map_w = tensor ? &map_wv : &map_wk;
-      const CUtensorMap* map_c = tensor ? &map_cv : &map_ck;
       prefetch_tensormap(map_w);
-      prefetch_tensormap(map_c);
       if (nq > 0) {
         prefetch_tensormap(&map_q);
         mbar_arrive_expect_tx(&bars[Q_FULL], nq * L::DCH * TILE_BYTES);
@@ -251,13 +250,24 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       bool ok = true;
       int slot = 0, use = 0;
       for (int it = 0; it < ntiles && ok; ++it) {
+        // the tile's codes: rows are contiguous in the history, so one untiled bulk copy; it is
+        // issued as soon as the previous tile's codes are expanded and lands during that tile's
+        // epilogue / exchange / attention
+        if (it > 0) ok = mbar_wait(&bars[CODES_FREE], (it - 1) & 1, abort_flag, 108);
+        if (!ok) break;
+        {
+          const int rows = min(TOK, p.N - it * TOK);
+          const uint32_t bytes = static_cast<uint32_t>(rows) * row_bytes;
+          mbar_arrive_expect_tx(&bars[CODES_FULL], bytes);
+          bulk_load_1d(smem + L::CODES_OFF, hist.codes + static_cast<size_t>(it) * TOK * row_bytes,
+                       bytes, &bars[CODES_FULL]);
+        }
         for (int c = 0; c < nchunks && ok; ++c) {
-          if (use >= 1) ok = mbar_wait(&bars[W_FREE + slot], (use - 1) & 1, abort_flag, 110 + slot);
+          if (use >= 1) ok = mbar_wait(&bars[RING_FREE + slot], (use - 1) & 1, abort_flag, 110 + slot);
           if (!ok) break;
-          uint8_t* dst = smem + L::RING_OFF + slot * L::SLOT_BYTES;
-          mbar_arrive_expect_tx(&bars[W_FULL + slot], TOK * 32 + PART * 128);
-          tma_load_2d(dst + L::SLOT_CODES, map_c, c * 32, it * TOK, &bars[W_FULL + slot]);
-          tma_load_2d(dst + L::SLOT_W, map_w, c * CHUNK, head * D + part * PART, &bars[W_FULL + slot]);
+          mbar_arrive_expect_tx(&bars[W_FULL + slot], PART * 128);
+          tma_load_2d(smem + ring_off + slot * L::SLOT_BYTES, map_w, c * CHUNK, head * D + part * PART,
+                      &bars[W_FULL + slot]);
           if (++slot == nw) { slot = 0; ++use; }
         }
       }
@@ -278,25 +288,25 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       Laps laps;
       laps.start(p.prof + 16, p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0);
       bool ok = nq > 0 ? mbar_wait(&bars[Q_FULL], 0, abort_flag, 200) : true;
-      int slot = 0, use = 0, g = 0;
+      int slot = 0, use = 0;
       for (int it = 0; it < ntiles && ok; ++it) {
-        for (int c = 0; c < nchunks && ok; ++c, ++g) {
-          const int ls = g & 3, lu = g >> 2;
+        for (int c = 0; c < nchunks && ok; ++c) {
           ok = mbar_wait(&bars[W_FULL + slot], use & 1, abort_flag, 210 + slot);
           laps.lap(0);
-          ok = ok && mbar_wait(&bars[LAT_FULL + ls], lu & 1, abort_flag, 216 + ls);
+          ok = ok && mbar_wait(&bars[LAT_FULL + slot], use & 1, abort_flag, 216 + slot);
           laps.lap(1);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t w = smem_base + L::RING_OFF + slot * L::SLOT_BYTES + L::SLOT_W;
-          const uint32_t lat = tmem_base + 128 + ls * 32;     // latent chunk staged in TMEM
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_bf16_ts(tmem_base, lat + k * 8, make_smem_desc_sw128(w + k * 32), idesc_dec,
-                        c > 0 || k > 0);
-          mma_commit(&bars[W_FREE + slot]);
-          mma_commit(&bars[LAT_FREE + ls]);
-          if (c == nchunks - 1) mma_commit(&bars[ACC_DONE]);
+          // descriptors are built once per chunk; a K = 16 step adds 32 bytes (2 in the address
+          // field) to the shared-memory operand and 8 columns to the TMEM operand
+          const uint64_t w_desc =
+              make_smem_desc_sw128(smem_base + ring_off + slot * L::SLOT_BYTES);
+          const uint32_t lat = tmem_base + staging_col(slot);   // latent chunk staged in TMEM
+          mma_bf16_ts(tmem_base, lat, w_desc, idesc_dec, c > 0);
+          mma_bf16_ts(tmem_base, lat + 8, w_desc + 2, idesc_dec, true);
+          mma_bf16_ts(tmem_base, lat + 16, w_desc + 4, idesc_dec, true);
+          mma_bf16_ts(tmem_base, lat + 24, w_desc + 6, idesc_dec, true);
+          mma_commit(&bars[RING_FREE + slot]);   // frees the slot; on the last chunk: accumulator done
           if (++slot == nw) { slot = 0; ++use; }
           laps.lap(2);
         }
@@ -328,15 +338,16 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         ok = mbar_wait_cluster(&bars[KV_READY], it & 1, abort_flag, 220);
         laps.lap(3);
         if (!ok) break;
-        fence_proxy_async_all();
         tc_fence_after();
         for (int i = 0; i < nq; ++i) {
 #pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t a = smem_base + L::Q_OFF + (i * L::DCH + (k >> 2)) * TILE_BYTES + (k & 3) * 32;
-            const uint32_t b = smem_base + L::K_OFF + (k >> 2) * TILE_BYTES + (k & 3) * 32;
-            mma_bf16(tmem_base + i * 128, make_smem_desc_sw128(a), make_smem_desc_sw128(b),
-                     idesc_s, k > 0);
+          for (int ch = 0; ch < L::DCH; ++ch) {
+            const uint64_t a_desc = make_smem_desc_sw128(smem_base + L::Q_OFF + (i * L::DCH + ch) * TILE_BYTES);
+            const uint64_t b_desc = make_smem_desc_sw128(smem_base + L::K_OFF + ch * TILE_BYTES);
+            mma_bf16(tmem_base + i * 128, a_desc, b_desc, idesc_s, ch > 0);
+            mma_bf16(tmem_base + i * 128, a_desc + 2, b_desc + 2, idesc_s, true);
+            mma_bf16(tmem_base + i * 128, a_desc + 4, b_desc + 4, idesc_s, true);
+            mma_bf16(tmem_base + i * 128, a_desc + 6, b_desc + 6, idesc_s, true);
           }
           mma_commit(&bars[S_FULL + i]);
         }
@@ -348,10 +359,14 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           tc_fence_after();
           // P (bf16 pairs) sits in the first 64 columns of the S region it was computed from
 #pragma unroll
-          for (int k = 0; k < TOK / 16; ++k) {
-            const uint32_t b = smem_base + L::VT_OFF + (k >> 2) * L::VT_TILE + (k & 3) * 32;
-            mma_bf16_ts(tmem_base + 256 + i * 128, tmem_base + i * 128 + k * 8,
-                        make_smem_desc_sw128(b), idesc_pv, it > 0 || k > 0);
+          for (int ch = 0; ch < 2; ++ch) {
+            const uint64_t b_desc = make_smem_desc_sw128(smem_base + L::VT_OFF + ch * L::VT_TILE);
+            const uint32_t p_addr = tmem_base + i * 128 + ch * 32;
+            const uint32_t o_addr = tmem_base + 256 + i * 128;
+            mma_bf16_ts(o_addr, p_addr, b_desc, idesc_pv, it > 0 || ch > 0);
+            mma_bf16_ts(o_addr, p_addr + 8, b_desc + 2, idesc_pv, true);
+            mma_bf16_ts(o_addr, p_addr + 16, b_desc + 4, idesc_pv, true);
+            mma_bf16_ts(o_addr, p_addr + 24, b_desc + 6, idesc_pv, true);
           }
           mma_commit(&bars[PV_DONE + i]);
         }
@@ -393,7 +408,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
     const uint32_t lane_sel = static_cast<uint32_t>(32 * (warp & 3)) << 16;
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
-    int slot = 0, use = 0, g = 0;
+    int slot = 0, use = 0;
     Laps laps;
     laps.start(p.prof, p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0);
     for (int it = 0; it < ntiles && ok; ++it) {
@@ -411,18 +426,20 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       laps.lap(1);
       if (!ok) break;
       // ---- expand this CTA's codes to bf16 latent chunks in tensor memory (A of the decode MMA)
-      for (int c = 0; c < nchunks && ok; ++c, ++g) {
-        const int ls = g & 3, lu = g >> 2;
-        ok = mbar_wait(&bars[W_FULL + slot], use & 1, abort_flag, 320 + slot);
+      int last_slot = 0, last_use = 0;
+      ok = mbar_wait(&bars[CODES_FULL], it & 1, abort_flag, 318);
+      if (!ok) break;
+      const uint8_t* codes = smem + L::CODES_OFF + row * row_bytes + wg * 16;
+      for (int c = 0; c < nchunks && ok; ++c) {
+        // the TMEM staging slot is free once the MMAs of its previous use are complete
+        if (use >= 1) ok = mbar_wait(&bars[RING_FREE + slot], (use - 1) & 1, abort_flag, 320 + slot);
         laps.lap(2);
-        if (ok && lu >= 1) ok = mbar_wait(&bars[LAT_FREE + ls], (lu - 1) & 1, abort_flag, 326 + ls);
-        laps.lap(3);
         if (!ok) break;
         tc_fence_after();
-        const uint8_t* codes = smem + L::RING_OFF + slot * L::SLOT_BYTES + L::SLOT_CODES;
-        const uint4 code = *reinterpret_cast<const uint4*>(codes + row * 32 + wg * 16);
+        const uint4 code = *reinterpret_cast<const uint4*>(codes + c * 32);
         const int col0 = c * CHUNK + wg * 32;   // this thread: token `row`, latent columns col0 .. +32
-        const uint16_t sbits = scales[static_cast<size_t>(mb * TOK + row) * ng + col0 / p.group];
+        const int gi = ng == 1 ? 0 : (p.group == 32 ? 2 * c + wg : col0 / p.group);
+        const uint16_t sbits = scales[static_cast<size_t>(mb * TOK + row) * ng + gi];
         const uint32_t words[4] = {code.x, code.y, code.z, code.w};
         uint32_t packed[16];
         if (p.scale_dtype == NKV_BF16) {
@@ -441,15 +458,18 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
             packed[4 * j] = v.x; packed[4 * j + 1] = v.y; packed[4 * j + 2] = v.z; packed[4 * j + 3] = v.w;
           }
         }
-        tmem_st16(tmem_base + lane_sel + 128 + ls * 32 + wg * 16, packed);
+        tmem_st16(tmem_base + lane_sel + staging_col(slot) + wg * 16, packed);
         tmem_wait_st();
         laps.lap(4);
         tc_fence_before();
-        mbar_arrive(&bars[LAT_FULL + ls]);
+        mbar_arrive(&bars[LAT_FULL + slot]);
         laps.lap(5);
+        last_slot = slot;
+        last_use = use;
         if (++slot == nw) { slot = 0; ++use; }
       }
       if (!ok) break;
+      mbar_arrive(&bars[CODES_FREE]);
       // ---- epilogue of this CTA's part: bias, centre, two bf16 roundings, store to every CTA
       {
         const bool in = row < valid;
@@ -469,7 +489,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
               cbase + static_cast<size_t>(crow_i) * hist.center_width + piece * 8));
         }
         laps.lap(6);
-        ok = mbar_wait(&bars[ACC_DONE], it & 1, abort_flag, 330);
+        ok = mbar_wait(&bars[RING_FREE + last_slot], last_use & 1, abort_flag, 330);
         laps.lap(7);
         if (!ok) break;
         tc_fence_after();
@@ -661,14 +681,14 @@ constexpr size_t SMEM_LIMIT = 232448;  // 227 KB per CTA
 long long* g_profile = nullptr;
 
 template <int D>
-int launch(const CUtensorMap maps[5], Params& p, cudaStream_t stream) {
+int launch(const CUtensorMap maps[3], Params& p, cudaStream_t stream) {
   using L = Layout<D>;
   int nw = MAX_NW;
-  while (nw > 2 && L::bytes(nw, p.ngroups) > SMEM_LIMIT) --nw;
-  size_t smem = L::bytes(nw, p.ngroups);
+  while (nw > 2 && L::bytes(nw, p.ngroups, p.rank) > SMEM_LIMIT) --nw;
+  size_t smem = L::bytes(nw, p.ngroups, p.rank);
   NKV_REQUIRE(smem <= SMEM_LIMIT, NKV_ERR_UNSUPPORTED,
-              "codec attention needs %zu bytes of shared memory (rank/group = %d too fine)", smem,
-              p.ngroups);
+              "codec attention needs %zu bytes of shared memory (rank %d, rank/group %d)", smem,
+              p.rank, p.ngroups);
   p.nw = nw;
   p.prof = g_profile;
   auto kernel = attn_codec_kernel<D>;
@@ -687,7 +707,7 @@ int launch(const CUtensorMap maps[5], Params& p, cudaStream_t stream) {
   attr.val.clusterDim.z = 1;
   config.attrs = &attr;
   config.numAttrs = 1;
-  NKV_CUDA(cudaLaunchKernelEx(&config, kernel, maps[0], maps[1], maps[2], maps[3], maps[4], p));
+  NKV_CUDA(cudaLaunchKernelEx(&config, kernel, maps[0], maps[1], maps[2], p));
   return NKV_OK;
 }
 
@@ -726,7 +746,7 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
     NKV_LAUNCH_CHECK("fill_empty_kernel");
     return NKV_OK;
   }
-  CUtensorMap maps[5];
+  CUtensorMap maps[3];
   {
     uint64_t dims[3] = {static_cast<uint64_t>(dk), static_cast<uint64_t>(heads), static_cast<uint64_t>(Q)};
     uint64_t strides[2] = {static_cast<uint64_t>(q_stride_head) * 2, static_cast<uint64_t>(q_stride_token) * 2};
@@ -742,14 +762,9 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
     int rc = encode_tensor_map(&maps[1 + w], 2, weights[w], 2, dims, strides, box, true);
     if (rc != NKV_OK) return rc;
   }
-  const nkv_history* hists[2] = {&hk, &hv};
-  for (int w = 0; w < 2; ++w) {
-    uint64_t dims[2] = {static_cast<uint64_t>(rank / 2), static_cast<uint64_t>(N)};
-    uint64_t strides[1] = {static_cast<uint64_t>(rank / 2)};
-    uint32_t box[2] = {32, TOK};
-    int rc = encode_tensor_map(&maps[3 + w], 1, hists[w]->codes, 2, dims, strides, box, false);
-    if (rc != NKV_OK) return rc;
-  }
+  NKV_REQUIRE((reinterpret_cast<uintptr_t>(hk.codes) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(hv.codes) & 15) == 0 && (rank / 2) % 16 == 0,
+              NKV_ERR_INVALID, "code arrays must be 16-byte aligned with 16-byte multiples per token");
   Params p{};
   p.Q = Q; p.heads = heads; p.N = N; p.rank = rank; p.nchunks = rank / CHUNK;
   p.group = group; p.ngroups = rank / group; p.scale_dtype = hk.scale_dtype;
