@@ -173,6 +173,9 @@ def run_ours(args) -> dict:
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
+        # keep stdout to the one JSON line (NCCL prints its version banner there at VERSION level)
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=device)
     shape, layers = SHAPE, args.layers
     total_frames = shape.history // FRAME
