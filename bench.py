@@ -361,6 +361,124 @@ def run_reference(args) -> dict:
     }
 
 
+# ------------------------------------------------------------------ secondary workloads
+def run_fast(args) -> dict:
+    """c4: NanoKV-Fast mixed-dimensional read, one layer, one GPU.  History 32 frames; the last 2
+    are protected (decoded to full width, native attention); the older 30 are read through reader
+    projections: 18 heads at width 32, 6 heads at full width; partitions merged by LSE."""
+    from nanokv_b200 import attention, codec
+    shape = synthetic.CONFIGS["c4_fast_mixed"]
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    frames, protected = shape.history // FRAME, 2
+    old = build_layers(shape, range(frames - protected), 1, device)[0]
+    recent = build_layers(shape, range(protected), 1, device)[0]
+    (hk, ok), (hv, ov) = old["k"], old["v"]
+    (pk, _), (pv, _) = recent["k"], recent["v"]
+    gen = synthetic.generator(77)
+    reader = attention.Reader(
+        synthetic.make_reader(shape, gen, [(list(range(18)), 32), (list(range(18, 24)), 128)],
+                              k_decoder=ok.decoder.cpu(), v_decoder=ov.decoder.cpu()),
+        dtype=torch.bfloat16, device=device)
+    q = synthetic.make_queries(shape, gen).to(device)
+
+    def step():
+        native = [(codec.decode(pk, ok).view(-1, shape.heads, shape.head_dim),
+                   codec.decode(pv, ov).view(-1, shape.heads, shape.head_dim))]
+        low = [{"k": hk, "v": hv, "k_mean": ok.mean, "v_mean": ov.mean}]
+        return attention.hybrid_attention(q, q, native, low, reader)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        step()
+    stop.record()
+    torch.cuda.synchronize()
+    seconds = start.elapsed_time(stop) / 1e3 / args.steps
+    return {"metric": "fast_attention_history_tokens_per_s", "value": shape.history / seconds,
+            "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": seconds * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": shape.name, "heads": shape.heads, "rank": shape.rank,
+                       "history_tokens": shape.history, "protected_tokens": protected * FRAME,
+                       "queries": shape.queries, "low_heads": 18, "low_width": 32, "layers": 1}}
+
+
+def run_streaming(args) -> dict:
+    """c5: streaming rollout, one layer.  Per chunk: encode + append 1,560 new K and V tokens
+    (chunks are dealt round-robin to the ranks, so shards stay balanced), then 4,680-query
+    codec-attention against the grown history (each rank its shard; all-gather + LSE merge)."""
+    import torch.distributed as dist
+    from nanokv_b200 import attention, context_parallel
+    from nanokv_b200.cache import CompressedHistory
+    from nanokv_b200.codec import Operator, QuantSpec, encode_append
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
+        dist.init_process_group("nccl", device_id=device)
+    shape, chunks = synthetic.CONFIGS["c5_streaming"], args.chunks
+    mine = (chunks + world - 1 - rank) // world
+    gen = torch.Generator(device=device).manual_seed(99 + rank)
+    hists, ops_ = {}, {}
+    for kind in ("k", "v"):
+        operator = synthetic.make_operator(shape, synthetic.generator(kind == "v"))
+        ops_[kind] = Operator(operator["mean"], operator["encoder"], operator["decoder"], device=device)
+        hist = CompressedHistory(joint=shape.joint, rank=shape.rank, capacity=max(mine, 1) * FRAME,
+                                 max_segments=max(mine, 1), centers_per_segment=shape.centers,
+                                 device=device, shared_centers=True)
+        centers = torch.randn(shape.centers, shape.joint, generator=gen, device=device)
+        hist.centers.copy_(centers.to(torch.bfloat16))
+        hists[kind] = (hist, centers)
+    q = synthetic.make_queries(shape, synthetic.generator(4242)).to(device)
+    rows = {}
+    for kind in ("k", "v"):
+        centers = hists[kind][1]
+        pick = torch.randint(shape.centers, (FRAME,), generator=gen, device=device)
+        rows[kind] = (centers.index_select(0, pick) + 0.3 * torch.randn(
+            FRAME, shape.joint, generator=gen, device=device)).to(torch.bfloat16)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    attended = 0
+    for chunk in range(chunks):
+        if chunk % world == rank:
+            for kind in ("k", "v"):
+                encode_append(hists[kind][0], rows[kind], ops_[kind], QuantSpec(), centers="resident")
+        out, lse = attention.codec_attention(q, hists["k"][0], hists["v"][0], ops_["k"], ops_["v"])
+        context_parallel.gather_and_merge(out, lse)
+        attended += (chunk + 1) * FRAME
+    stop.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = torch.tensor([start.elapsed_time(stop)], device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.destroy_process_group()
+    if rank != 0:
+        return {}
+    seconds = float(ms.item()) / 1e3
+    return {"metric": "streaming_history_tokens_per_s", "value": attended / seconds, "unit": UNIT,
+            "n_gpus": world, "steps": chunks, "warmup": 0, "ms_per_step": seconds * 1e3 / chunks,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": shape.name, "heads": shape.heads, "rank": shape.rank,
+                       "chunks": chunks, "tokens_per_chunk": FRAME, "queries": shape.queries,
+                       "final_history_tokens": chunks * FRAME, "layers": 1,
+                       "sharding": "chunks round-robin over ranks"},
+            "encode_tokens_per_s_incl_attention": chunks * FRAME / seconds}
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -369,8 +487,19 @@ def main() -> None:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--layers", type=int, default=SHAPE.layers)
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    parser.add_argument("--workload", default="c3_wan_shaped",
+                        choices=["c3_wan_shaped", "c4_fast_mixed", "c5_streaming"],
+                        help="c3 is the headline; c4 / c5 are secondary measurements")
+    parser.add_argument("--chunks", type=int, default=256, help="c5: chunks streamed")
     args = parser.parse_args()
-    line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.impl == "reference":
+        line = run_reference(args)
+    elif args.workload == "c4_fast_mixed":
+        line = run_fast(args)
+    elif args.workload == "c5_streaming":
+        line = run_streaming(args)
+    else:
+        line = run_ours(args)
     if line:
         print(json.dumps(line), flush=True)
 
