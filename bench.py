@@ -274,7 +274,8 @@ def run_ours(args) -> dict:
                    "l2_policy": "inputs larger than L2 (distinct compressed history per layer)"},
         "e2e": {"value": tokens_per_step / (e2e_seconds / e2e_steps), "unit": UNIT,
                 "h2d_bytes_per_step": q_bytes * layers, "d2h_bytes_per_step": o_bytes * layers},
-        "gpu_launches": args.steps * layers * (2 if world > 1 else 1),
+        # per layer: fused attention + LSE merge of its history splits (+ the CP merge when sharded)
+        "gpu_launches": args.steps * layers * (2 + (1 if world > 1 else 0)),
         "roofline": {"bound": "tensor", "kernel": "attn_codec_kernel<128>", "achieved": achieved,
                      "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                      "peak_source": f"bf16_tflops_sustained of {peak_kind}",

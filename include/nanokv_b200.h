@@ -216,6 +216,22 @@ int nkv_attn_codec(const void* q, int dtype, int64_t q_stride_token, int64_t q_s
                    float scale, void* out, float* lse, int32_t* status_word, void* stream);
 
 /*
+ * nkv_attn_codec with the history cut into `splits` (1..16) contiguous runs of tiles that are
+ * attended by separate thread-block slices of ONE launch; their partial (O, lse) go to
+ * `workspace` (nkv_attn_codec_workspace_bytes bytes) and are merged by log-sum-exp (the merge of
+ * MGC/core.py:33-42).  More, shorter work units even out the rounds in which the GPU's resident
+ * clusters finish; results equal nkv_attn_codec up to the rounding of the partials to the output
+ * dtype.  The fp32 path ignores `splits`.
+ */
+size_t nkv_attn_codec_workspace_bytes(int Q, int heads, int dv, int splits);
+int nkv_attn_codec_split(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head,
+                         int Q, int heads, int dk, int dv,
+                         const nkv_history* hist_k, const nkv_history* hist_v,
+                         const void* wk, const float* bias_k, const void* wv, const float* bias_v,
+                         float scale, void* out, float* lse, int32_t* status_word,
+                         int splits, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Plain attention with LSE over K / V rows that are already full width (the
  * protected / current-chunk partition): O = softmax(q K^T * scale) V.
  * Reference: attention_lse, MGC/core.py:45-72;

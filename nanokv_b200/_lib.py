@@ -53,6 +53,11 @@ SIGNATURES = {
     "nkv_attn_codec": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int,
                                POINTER(History), POINTER(History), c_void_p, c_void_p, c_void_p,
                                c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nkv_attn_codec_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "nkv_attn_codec_split": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int,
+                                     POINTER(History), POINTER(History), c_void_p, c_void_p,
+                                     c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+                                     c_int, c_void_p, c_size_t, c_void_p]),
     "nkv_attention_lse": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64,
                                   c_int64, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                                   c_void_p, c_void_p]),

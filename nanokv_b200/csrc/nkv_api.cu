@@ -228,11 +228,17 @@ int nkv_decode_rows(const nkv_history* hist, const int32_t* rows_index, int n,
                           static_cast<cudaStream_t>(stream));
 }
 
-int nkv_attn_codec(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head, int Q,
-                   int heads, int dk, int dv, const nkv_history* hist_k,
-                   const nkv_history* hist_v, const void* wk, const float* bias_k, const void* wv,
-                   const float* bias_v, float scale, void* out, float* lse, int32_t* status_word,
-                   void* stream) {
+size_t nkv_attn_codec_workspace_bytes(int Q, int heads, int dv, int splits) {
+  if (splits <= 1) return 0;
+  return static_cast<size_t>(splits) * Q * heads * (static_cast<size_t>(dv) * 2 + 4);
+}
+
+int nkv_attn_codec_split(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head,
+                         int Q, int heads, int dk, int dv, const nkv_history* hist_k,
+                         const nkv_history* hist_v, const void* wk, const float* bias_k,
+                         const void* wv, const float* bias_v, float scale, void* out, float* lse,
+                         int32_t* status_word, int splits, void* workspace, size_t workspace_bytes,
+                         void* stream) {
   int rc = check_history(hist_k, "K");
   if (rc != NKV_OK) return rc;
   rc = check_history(hist_v, "V");
@@ -242,12 +248,26 @@ int nkv_attn_codec(const void* q, int dtype, int64_t q_stride_token, int64_t q_s
               NKV_ERR_INVALID, "K and V histories differ in tokens / rank / group / scale dtype");
   NKV_REQUIRE(dtype == NKV_F32 || dtype == NKV_BF16, NKV_ERR_INVALID, "attn_codec: dtype");
   NKV_REQUIRE(Q >= 0 && heads >= 0, NKV_ERR_INVALID, "attn_codec: Q=%d heads=%d", Q, heads);
+  NKV_REQUIRE(splits >= 1 && splits <= 16, NKV_ERR_INVALID, "attn_codec: splits=%d (1..16)", splits);
+  NKV_REQUIRE(workspace_bytes >= nkv_attn_codec_workspace_bytes(Q, heads, dv, splits),
+              NKV_ERR_INVALID, "attn_codec: workspace of %zu bytes is too small for %d splits",
+              workspace_bytes, splits);
   auto s = static_cast<cudaStream_t>(stream);
   if (dtype == NKV_BF16 && !simt_forced())
     return tc_attn_codec(q, q_stride_token, q_stride_head, Q, heads, dk, dv, hist_k, hist_v, wk,
-                         bias_k, wv, bias_v, scale, out, lse, status_word, s);
+                         bias_k, wv, bias_v, scale, out, lse, status_word, splits, workspace, s);
   return simt_attn(q, dtype, q_stride_token, q_stride_head, Q, heads, dk, dv, hist_k, hist_v, wk,
                    bias_k, wv, bias_v, nullptr, nullptr, 0, 0, hist_k->tokens, scale, out, lse, s);
+}
+
+int nkv_attn_codec(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head, int Q,
+                   int heads, int dk, int dv, const nkv_history* hist_k,
+                   const nkv_history* hist_v, const void* wk, const float* bias_k, const void* wv,
+                   const float* bias_v, float scale, void* out, float* lse, int32_t* status_word,
+                   void* stream) {
+  return nkv_attn_codec_split(q, dtype, q_stride_token, q_stride_head, Q, heads, dk, dv, hist_k,
+                              hist_v, wk, bias_k, wv, bias_v, scale, out, lse, status_word, 1,
+                              nullptr, 0, stream);
 }
 
 int nkv_attention_lse(const void* q, const void* k, const void* v, int dtype,

@@ -45,7 +45,7 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
                   int heads, int dk, int dv, const nkv_history* hist_k,
                   const nkv_history* hist_v, const void* wk, const float* bias_k,
                   const void* wv, const float* bias_v, float scale, void* out, float* lse,
-                  int32_t* status_word, cudaStream_t stream);
+                  int32_t* status_word, int splits, void* workspace, cudaStream_t stream);
 bool tc_attn_supported(int dk, int dv, int rank);
 void tc_attn_set_profile(long long* device_buckets);
 bool tc_project_supported(int J, int r);

@@ -59,6 +59,7 @@ enum Bar {
 struct Params {
   int Q, heads, N, rank, nchunks, ngroups, group;
   int scale_dtype, nw;
+  int tiles_per_split;   // grid.z splits the history; split z writes partial (O, lse) number z
   float scale_log2;
   nkv_history hk, hv;
   const float* bias_k;
@@ -198,7 +199,8 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
   const nkv_history& hist = tensor ? p.hv : p.hk;
   const int q0 = blockIdx.x * (NQ * QT);
   const int nq = q0 >= p.Q ? 0 : ((q0 + QT < p.Q) ? 2 : 1);   // 0: decode duty only
-  const int ntiles = (p.N + TOK - 1) / TOK;
+  const int tile0 = blockIdx.z * p.tiles_per_split;       // first history tile of this split
+  const int ntiles = max(0, min((p.N + TOK - 1) / TOK - tile0, p.tiles_per_split));
   const int nchunks = p.nchunks;
   const int ng = p.ngroups;
 
@@ -256,10 +258,10 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         if (it > 0) ok = mbar_wait(&bars[CODES_FREE], (it - 1) & 1, abort_flag, 108);
         if (!ok) break;
         {
-          const int rows = min(TOK, p.N - it * TOK);
+          const int rows = min(TOK, p.N - (tile0 + it) * TOK);
           const uint32_t bytes = static_cast<uint32_t>(rows) * row_bytes;
           mbar_arrive_expect_tx(&bars[CODES_FULL], bytes);
-          bulk_load_1d(smem + L::CODES_OFF, hist.codes + static_cast<size_t>(it) * TOK * row_bytes,
+          bulk_load_1d(smem + L::CODES_OFF, hist.codes + static_cast<size_t>(tile0 + it) * TOK * row_bytes,
                        bytes, &bars[CODES_FULL]);
         }
         for (int c = 0; c < nchunks && ok; ++c) {
@@ -390,7 +392,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       const int b = it & 1, u = it >> 1;
       if (u >= 1) ok = mbar_wait(&bars[META_FREE + b], (u - 1) & 1, abort_flag, 240 + b);
       if (!ok) break;
-      const int t0 = it * TOK;
+      const int t0 = (tile0 + it) * TOK;
       for (int r = lane; r < TOK; r += 32) {
         const int t = t0 + r;
         const bool in = t < p.N;
@@ -412,7 +414,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
     Laps laps;
     laps.start(p.prof, p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0);
     for (int it = 0; it < ntiles && ok; ++it) {
-      const int t0 = it * TOK;
+      const int t0 = (tile0 + it) * TOK;
       const int valid = min(TOK, p.N - t0);
       const int mb = it & 1;
       if (it > 0) {  // P and S of the previous tile live where the accumulator and the staging go
@@ -640,7 +642,8 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         const int qrow = q0 + wg * QT + row;
         const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
         const uint32_t o_addr = tmem_base + lane_sel + 256 + wg * 128;
-        uint16_t* dst = p.out + (static_cast<size_t>(qrow) * p.heads + head) * D;
+        const size_t split_rows = static_cast<size_t>(blockIdx.z) * p.Q * p.heads;
+        uint16_t* dst = p.out + (split_rows + static_cast<size_t>(qrow) * p.heads + head) * D;
 #pragma unroll 1
         for (int cc = 0; cc < D / 32; ++cc) {
           float v[32];
@@ -658,7 +661,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           }
         }
         if (qrow < p.Q)
-          p.lse[static_cast<size_t>(qrow) * p.heads + head] =
+          p.lse[split_rows + static_cast<size_t>(qrow) * p.heads + head] =
               l_run > 0.f ? (m_used + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
       }
     }
@@ -696,7 +699,8 @@ int launch(const CUtensorMap maps[3], Params& p, cudaStream_t stream) {
                                 static_cast<int>(smem)));
   const int qblocks = ceil_div(p.Q, NQ * QT);
   cudaLaunchConfig_t config{};
-  config.gridDim = dim3(ceil_div(qblocks, L::CL) * L::CL, p.heads);   // padded: idle CTAs still decode
+  const int splits = ceil_div(ceil_div(p.N, TOK), p.tiles_per_split);
+  config.gridDim = dim3(ceil_div(qblocks, L::CL) * L::CL, p.heads, splits);   // padded: idle CTAs still decode
   config.blockDim = dim3(THREADS);
   config.dynamicSmemBytes = smem;
   config.stream = stream;
@@ -724,8 +728,8 @@ bool tc_attn_supported(int dk, int dv, int rank) {
 int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, int Q, int heads,
                   int dk, int dv, const nkv_history* hist_k, const nkv_history* hist_v,
                   const void* wk, const float* bias_k, const void* wv, const float* bias_v,
-                  float scale, void* out, float* lse, int32_t* status_word,
-                  cudaStream_t stream) {
+                  float scale, void* out, float* lse, int32_t* status_word, int splits,
+                  void* workspace, cudaStream_t stream) {
   const nkv_history& hk = *hist_k;
   const nkv_history& hv = *hist_v;
   const int N = hk.tokens, rank = hk.rank, group = hk.group;
@@ -770,8 +774,31 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
   p.group = group; p.ngroups = rank / group; p.scale_dtype = hk.scale_dtype;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.hk = hk; p.hv = hv; p.bias_k = bias_k; p.bias_v = bias_v;
-  p.out = static_cast<uint16_t*>(out); p.lse = lse; p.status = status_word;
-  return dk == 128 ? launch<128>(maps, p, stream) : launch<64>(maps, p, stream);
+  p.status = status_word;
+  // History splits: each grid.z slice attends a contiguous run of tiles and writes a partial
+  // (O, lse); the partials are merged by log-sum-exp.  Evens out the rounds of resident clusters.
+  const int tiles = ceil_div(N, TOK);
+  splits = splits < 1 ? 1 : (splits > tiles ? tiles : splits);
+  p.tiles_per_split = ceil_div(tiles, splits);
+  splits = ceil_div(tiles, p.tiles_per_split);
+  if (splits == 1) {
+    p.out = static_cast<uint16_t*>(out); p.lse = lse;
+    return dk == 128 ? launch<128>(maps, p, stream) : launch<64>(maps, p, stream);
+  }
+  NKV_REQUIRE(workspace != nullptr, NKV_ERR_INVALID, "history splits need a workspace");
+  const size_t rows = static_cast<size_t>(Q) * heads;
+  uint16_t* part_out = static_cast<uint16_t*>(workspace);
+  float* part_lse = reinterpret_cast<float*>(part_out + static_cast<size_t>(splits) * rows * dv);
+  p.out = part_out; p.lse = part_lse;
+  int rc = dk == 128 ? launch<128>(maps, p, stream) : launch<64>(maps, p, stream);
+  if (rc != NKV_OK) return rc;
+  const void* outs[16];
+  const float* lses[16];
+  for (int z = 0; z < splits; ++z) {
+    outs[z] = part_out + static_cast<size_t>(z) * rows * dv;
+    lses[z] = part_lse + static_cast<size_t>(z) * rows;
+  }
+  return lse_merge(outs, lses, splits, static_cast<int64_t>(rows), dv, NKV_BF16, out, lse, stream);
 }
 
 }  // namespace nkv

@@ -155,11 +155,17 @@ def decode_rows(view: HistoryView, decoder, mean, *, rows=None, dtype=None) -> t
 
 
 # ------------------------------------------------------------------------ attention
+def default_splits(tokens: int) -> int:
+    """History splits of one fused launch: three once a split still spans 64 tiles."""
+    return 3 if tokens >= 3 * 64 * 128 else 1
+
+
 def attn_codec(q, view_k: HistoryView, view_v: HistoryView, wk, bias_k, wv, bias_v, *,
-               scale: float, status: torch.Tensor | None = None):
+               scale: float, status: torch.Tensor | None = None, splits: int | None = None):
     """Fused read: q [Q,H,dk] -> (O [Q,H,dv], lse f32 [Q,H]).
 
-    wk [H,dk,r], wv [H,dv,r] in q's dtype; bias f32 [H,dk] / [H,dv].
+    wk [H,dk,r], wv [H,dv,r] in q's dtype; bias f32 [H,dk] / [H,dv].  ``splits`` cuts the
+    history into that many runs attended in one launch and merged by LSE (None: automatic).
     """
     device = _require_cuda(wk, bias_k, wv, bias_v, status)
     if not q.is_cuda:
@@ -171,10 +177,15 @@ def attn_codec(q, view_k: HistoryView, view_v: HistoryView, wk, bias_k, wv, bias
     out = torch.empty(Q, H, dv, dtype=q.dtype, device=device)
     lse = torch.empty(Q, H, dtype=torch.float32, device=device)
     sk, sv = view_k.struct(), view_v.struct()
-    _lib.check(_lib.library().nkv_attn_codec(
+    lib = _lib.library()
+    if splits is None:
+        splits = default_splits(view_k.tokens) if q.dtype == torch.bfloat16 else 1
+    nbytes = lib.nkv_attn_codec_workspace_bytes(Q, H, dv, splits)
+    workspace = torch.empty(nbytes, dtype=torch.uint8, device=device) if nbytes else None
+    _lib.check(lib.nkv_attn_codec_split(
         _ptr(q), dtype_code(q.dtype), q.stride(0), q.stride(1), Q, H, dk, dv, ctypes.byref(sk),
         ctypes.byref(sv), _ptr(wk), _ptr(bias_k), _ptr(wv), _ptr(bias_v), float(scale), _ptr(out),
-        _ptr(lse), _ptr(status), _stream(device)))
+        _ptr(lse), _ptr(status), splits, _ptr(workspace), nbytes, _stream(device)))
     return out, lse
 
 

@@ -120,6 +120,24 @@ def test_codec_attention_bf16_tensor_core_vs_cuda_core_emulation():
     assert float((lse_tc - lse_sm).abs().max()) <= 5e-3
 
 
+def test_codec_attention_history_splits_agree():
+    """One launch with the history cut into runs merged by LSE equals the unsplit launch."""
+    shape = synthetic.Shape("t", 2, 128, 128, 16, 1300, 300, "bf16")
+    case = cases.CodecCase("t", shape, (600, 700), seed=43, mean_std=0.05)
+    data, segments = oracle_segments(case)
+    ops_k, ops_v = device_operator(data["k_op"]), device_operator(data["v_op"])
+    hist_k = history_from_segments(segments["k"], joint=shape.joint, rank=shape.rank)
+    hist_v = history_from_segments(segments["v"], joint=shape.joint, rank=shape.rank)
+    q = data["q"].cuda()
+    whole, whole_lse = attention.codec_attention(q, hist_k, hist_v, ops_k, ops_v, splits=1)
+    for splits in (2, 3, 16):
+        out, lse = attention.codec_attention(q, hist_k, hist_v, ops_k, ops_v, splits=splits)
+        assert rel_err(out.cpu(), whole.cpu()) <= 2.0 ** -6
+        assert float((lse - whole_lse).abs().max()) <= 1e-3
+    with pytest.raises(ValueError):
+        attention.codec_attention(q, hist_k, hist_v, ops_k, ops_v, splits=17)
+
+
 def test_codec_attention_empty_history():
     shape = synthetic.Shape("t", 2, 128, 64, 8, 0, 40, "bf16")
     gen = synthetic.generator(1)
