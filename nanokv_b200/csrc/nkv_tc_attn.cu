@@ -28,7 +28,7 @@
 // arrivals and multicast commits.  No TMA load uses multicast.
 //
 // TMEM columns: [0,128) S of query tile 0 (decode accumulator in [0,64));
-// [128,256) S of tile 1 (latent staging slots, 32 columns each; two more in [64,128)); [256,384) O
+// [128,256) S of tile 1; latent staging slots of 32 columns at 64, 96, 192, 224; [256,384) O
 // tile 0; [384,512) O tile 1.
 #include "nkv_internal.h"
 #include "nkv_tc.cuh"
@@ -47,7 +47,7 @@ constexpr int THREADS = COMPUTE_THREADS + 96;
 constexpr int CHUNK = 64;         // latent columns per pipeline step
 constexpr int PART = 64;          // K/V columns rebuilt by one CTA
 constexpr int TILE_BYTES = 128 * 128;  // one [128 rows x 64 bf16] swizzled tile
-constexpr int MAX_NW = 6;         // ring slots: operand bytes in shared memory + latent staging in TMEM
+constexpr int MAX_NW = 4;         // ring slots: decoder rows in shared memory + latent staging in TMEM
 constexpr float RESCALE_THRESHOLD = 8.0f;
 
 enum Bar {
@@ -135,9 +135,10 @@ __device__ __forceinline__ uint4 dequant8_bf16(uint32_t word, __nv_bfloat162 sca
   return r;
 }
 
-// TMEM column of latent staging slot s: four slots in the S region of query tile 1, two more in
-// the upper half of tile 0's (the decode accumulator only uses its first 64 columns)
-__device__ __forceinline__ uint32_t staging_col(int s) { return s < 4 ? 128 + 32 * s : 64 + 32 * (s - 4); }
+// TMEM column of latent staging slot s.  The four slots avoid the columns where P of the previous
+// tile may still be read by its PV MMAs (P0 in [0,64), P1 in [128,192)), so the next tile's codes
+// can be expanded while those MMAs run.
+__device__ __forceinline__ uint32_t staging_col(int s) { return s < 2 ? 64 + 32 * s : 128 + 32 * s; }
 
 // Lap timer of one thread: adds the cycles since the previous lap to a bucket kept in registers;
 // flush() adds the buckets to global memory once, at the end.
@@ -417,11 +418,10 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       const int t0 = (tile0 + it) * TOK;
       const int valid = min(TOK, p.N - t0);
       const int mb = it & 1;
-      if (it > 0) {  // P and S of the previous tile live where the accumulator and the staging go
+      if (it > 0) {  // every thread has finished reading S of the previous tile (staging reuses it)
         for (int i = 0; i < nq && ok; ++i)
-          ok = mbar_wait(&bars[PV_DONE + i], (it - 1) & 1, abort_flag, 300 + i);
+          ok = mbar_wait(&bars[P_READY + i], (it - 1) & 1, abort_flag, 300 + i);
         if (!ok) break;
-        tc_fence_after();
       }
       laps.lap(0);
       ok = mbar_wait(&bars[META_FULL + mb], (it >> 1) & 1, abort_flag, 310);
@@ -564,6 +564,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         laps.lap(10);
         if (!ok) break;
         tc_fence_after();
+        // S of this tile was issued after PV of the previous one, so O is up to date here
         const uint32_t s_addr = tmem_base + lane_sel + wg * 128;
         float mx = -INFINITY;
 #pragma unroll 1

@@ -156,8 +156,8 @@ def decode_rows(view: HistoryView, decoder, mean, *, rows=None, dtype=None) -> t
 
 # ------------------------------------------------------------------------ attention
 def default_splits(tokens: int) -> int:
-    """History splits of one fused launch: three once a split still spans 64 tiles."""
-    return 3 if tokens >= 3 * 64 * 128 else 1
+    """History splits of one fused launch: up to four, each spanning at least 48 tiles."""
+    return max(1, min(4, tokens // (48 * 128)))
 
 
 def attn_codec(q, view_k: HistoryView, view_v: HistoryView, wk, bias_k, wv, bias_v, *,
