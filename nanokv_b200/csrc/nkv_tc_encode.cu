@@ -1,7 +1,7 @@
 // Encoder GEMMs on tcgen05: nearest-centre assignment and residual projection.
 //
 // Both are [128 tokens x K=J] x [N x K]^T tiles with fp32 accumulators in TMEM,
-// K streamed 64 columns at a time through a two-stage shared-memory ring.
+// K streamed 64 columns at a time through a shared-memory ring of up to four stages.
 //   assign : A = token rows (TMA), B = centre rows (TMA), N = C <= 512.  While
 //            a stage is resident the compute warps accumulate ||x||^2 and
 //            ||c||^2 from the same tiles; the epilogue evaluates
@@ -24,10 +24,12 @@ constexpr int COMPUTE_THREADS = 256;
 constexpr int THREADS = COMPUTE_THREADS + 64;
 constexpr int A_BYTES = 128 * 128;
 
-enum Bar { TMA_FULL = 0, A_FULL = 2, STAGE_FREE = 4, ACC_DONE = 6, SIDE_READY = 7, CAND_READY = 8, NUM_BARS = 9 };
+constexpr int MAX_STAGES = 4;
+enum Bar { TMA_FULL = 0, A_FULL = 4, STAGE_FREE = 8, ACC_DONE = 12, SIDE_READY = 13, CAND_READY = 14, NUM_BARS = 15 };
 
 struct Params {
   int S, J, NB, NACC, n_total;      // n_total = r (project) or C (assign)
+  int nstages;                      // depth of the shared-memory operand ring (2..4)
   // project
   const uint16_t* x; const uint16_t* centers; const void* ids; int id_bytes;
   const float* mean; uint16_t* coeff;
@@ -56,7 +58,8 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int b_bytes = p.NB * 128;                       // one accumulator's B tile
   const int stage_bytes = A_BYTES + p.NACC * b_bytes;
-  uint8_t* meta = smem + 2 * stage_bytes;
+  const int nst = p.nstages;
+  uint8_t* meta = smem + nst * stage_bytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(meta);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(meta + NUM_BARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(meta + NUM_BARS * 8 + 4);
@@ -71,7 +74,7 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   const int nchunks = p.J / 64;
 
   if (tid == 0) {
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < MAX_STAGES; ++s) {
       mbar_init(&bars[TMA_FULL + s], 1);
       mbar_init(&bars[A_FULL + s], COMPUTE_THREADS);
       mbar_init(&bars[STAGE_FREE + s], ASSIGN ? 1 + COMPUTE_THREADS : 1);
@@ -95,7 +98,7 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       if (ASSIGN) prefetch_tensormap(&map_a);
       bool ok = true;
       for (int c = 0; c < nchunks && ok; ++c) {
-        const int s = c & 1, u = c >> 1;
+        const int s = c % nst, u = c / nst;
         if (u >= 1) ok = mbar_wait(&bars[STAGE_FREE + s], (u - 1) & 1, abort_flag, 400 + s);
         if (!ok) break;
         uint8_t* stage = smem + s * stage_bytes;
@@ -117,18 +120,20 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t smem_base = smem_u32(smem);
       bool ok = true;
       for (int c = 0; c < nchunks && ok; ++c) {
-        const int s = c & 1, u = c >> 1;
+        const int s = c % nst, u = c / nst;
         ok = mbar_wait(&bars[TMA_FULL + s], u & 1, abort_flag, 410 + s);
         if (ok && !ASSIGN) ok = mbar_wait(&bars[A_FULL + s], u & 1, abort_flag, 412 + s);
         if (!ok) break;
         tc_fence_after();
         const uint32_t stage = smem_base + s * stage_bytes;
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          for (int a = 0; a < p.NACC; ++a)
-            mma_bf16(tmem_base + a * 256, make_smem_desc_sw128(stage + k * 32),
-                     make_smem_desc_sw128(stage + A_BYTES + a * b_bytes + k * 32), idesc,
-                     c > 0 || k > 0);
+        const uint64_t a_desc = make_smem_desc_sw128(stage);
+        for (int a = 0; a < p.NACC; ++a) {
+          const uint64_t b_desc = make_smem_desc_sw128(stage + A_BYTES + a * b_bytes);
+          mma_bf16(tmem_base + a * 256, a_desc, b_desc, idesc, c > 0);
+          mma_bf16(tmem_base + a * 256, a_desc + 2, b_desc + 2, idesc, true);
+          mma_bf16(tmem_base + a * 256, a_desc + 4, b_desc + 4, idesc, true);
+          mma_bf16(tmem_base + a * 256, a_desc + 6, b_desc + 6, idesc, true);
+        }
         mma_commit(&bars[STAGE_FREE + s]);
       }
       if (ok) mma_commit(&bars[ACC_DONE]);
@@ -143,7 +148,7 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       const int C = p.n_total;
       float xs = 0.f, cs[4] = {0.f, 0.f, 0.f, 0.f};
       for (int c = 0; c < nchunks && ok; ++c) {
-        const int s = c & 1, u = c >> 1;
+        const int s = c % nst, u = c / nst;
         ok = mbar_wait(&bars[TMA_FULL + s], u & 1, abort_flag, 420 + s);
         if (!ok) break;
         const uint8_t* stage = smem + s * stage_bytes;
@@ -219,20 +224,36 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       const bool in = t < p.S;
       const uint16_t* xrow = p.x + static_cast<size_t>(in ? t : 0) * p.J;
       const uint16_t* crow = p.centers + static_cast<size_t>(in ? load_id(p.ids, p.id_bytes, t) : 0) * p.J;
+      // raw operands of one chunk for this thread: 32 columns of x and of the centre row
+      uint4 xn[4], cn[4];
+      auto fetch = [&](int c) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          xn[j] = make_uint4(0, 0, 0, 0);
+          cn[j] = make_uint4(0, 0, 0, 0);
+          if (in && c < nchunks) {
+            xn[j] = __ldg(reinterpret_cast<const uint4*>(xrow + c * 64 + half * 32) + j);
+            cn[j] = __ldg(reinterpret_cast<const uint4*>(crow + c * 64 + half * 32) + j);
+          }
+        }
+      };
+      fetch(0);
       for (int c = 0; c < nchunks && ok; ++c) {
-        const int s = c & 1, u = c >> 1;
+        const int s = c % nst, u = c / nst;
+        uint4 xc[4], cc4[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { xc[j] = xn[j]; cc4[j] = cn[j]; }
+        fetch(c + 1);                       // in flight while this chunk is formed
         if (u >= 1) ok = mbar_wait(&bars[STAGE_FREE + s], (u - 1) & 1, abort_flag, 440 + s);
         if (!ok) break;
         uint8_t* stage = smem + s * stage_bytes;
         const int j0 = c * 64 + half * 32;
-        const uint4* xs = reinterpret_cast<const uint4*>(xrow + j0);
-        const uint4* cs = reinterpret_cast<const uint4*>(crow + j0);
         const float4* ms = reinterpret_cast<const float4*>(p.mean + j0);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           uint4 out = make_uint4(0, 0, 0, 0);
           if (in) {
-            const uint4 xw = __ldg(xs + j), cw = __ldg(cs + j);
+            const uint4 xw = xc[j], cw = cc4[j];
             const float4 m0v = __ldg(ms + 2 * j), m1v = __ldg(ms + 2 * j + 1);
             const uint32_t xwords[4] = {xw.x, xw.y, xw.z, xw.w};
             const uint32_t cwords[4] = {cw.x, cw.y, cw.z, cw.w};
@@ -294,9 +315,15 @@ bool plan_columns(int n_total, int* gy, int* nacc, int* nb) {
   return false;
 }
 
-size_t smem_bytes(int nacc, int nb, int n_total) {
-  return 2 * static_cast<size_t>(A_BYTES + nacc * nb * 128) + 128 + 4 * (256 + 128 + 128) +
+size_t smem_bytes(int nacc, int nb, int n_total, int stages = 2) {
+  return stages * static_cast<size_t>(A_BYTES + nacc * nb * 128) + 128 + 4 * (256 + 128 + 128) +
          8 * static_cast<size_t>(n_total) + 1024;
+}
+
+int pick_stages(int nacc, int nb, int n_total) {
+  int stages = MAX_STAGES;
+  while (stages > 2 && smem_bytes(nacc, nb, n_total, stages) > 232448) --stages;
+  return stages;
 }
 
 }  // namespace
@@ -336,7 +363,8 @@ int tc_project(const void* x_bf16, const void* centers_bf16, const void* ids, in
   uint32_t box[2] = {64, static_cast<uint32_t>(p.NB)};
   int rc = encode_tensor_map(&map_b, 2, encoder_bf16, 2, dims, strides, box, true);
   if (rc != NKV_OK) return rc;
-  size_t smem = smem_bytes(p.NACC, p.NB, 0);
+  p.nstages = pick_stages(p.NACC, p.NB, 0);
+  size_t smem = smem_bytes(p.NACC, p.NB, 0, p.nstages);
   auto kernel = encode_gemm_kernel<false>;
   NKV_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(smem)));
@@ -369,7 +397,8 @@ int tc_assign(const void* x_bf16, const void* centers_bf16, int S, int J, int C,
     int rc = encode_tensor_map(&map_b, 2, centers_bf16, 2, dims, strides, box, true);
     if (rc != NKV_OK) return rc;
   }
-  size_t smem = smem_bytes(p.NACC, p.NB, C);
+  p.nstages = pick_stages(p.NACC, p.NB, C);
+  size_t smem = smem_bytes(p.NACC, p.NB, C, p.nstages);
   auto kernel = encode_gemm_kernel<true>;
   NKV_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(smem)));
