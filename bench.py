@@ -158,10 +158,26 @@ def time_encode(shape, device, steps: int, warmup: int, frames: int = 8):
     stop.record()
     torch.cuda.synchronize()
     seconds = start.elapsed_time(stop) / 1e3 / steps
+    # the HBM-bound stage alone: quantise + pack of 399,360 tokens' coefficients (inputs > L2)
+    from nanokv_b200 import ops
+    coeff = torch.randn(399360, shape.rank, generator=gen, device=device).to(torch.bfloat16)
+    codes = torch.empty(coeff.shape[0], shape.rank // 2, dtype=torch.uint8, device=device)
+    scales = torch.empty(coeff.shape[0], 1, dtype=torch.bfloat16, device=device)
+    q_start, q_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for index in range(3 + 5):
+        if index == 3:
+            q_start.record()
+        ops.quant_pack(coeff, codes=codes, scales=scales)
+    q_stop.record()
+    torch.cuda.synchronize()
+    quant_seconds = q_start.elapsed_time(q_stop) / 1e3 / 5
+    quant_bytes = coeff.shape[0] * (shape.rank * 2 + shape.rank // 2 + 2)
     flops = count * 2 * 2.0 * shape.joint * (shape.centers + shape.rank)
     bytes_ = count * 2 * (shape.joint * 2 + shape.rank // 2 + 2 + 2)
     return {"tokens_per_s": count / seconds, "ms": seconds * 1e3, "tokens_per_call": count,
-            "tflops": flops / seconds / 1e12, "gbs": bytes_ / seconds / 1e9}
+            "tflops": flops / seconds / 1e12, "gbs": bytes_ / seconds / 1e9,
+            "quant_pack_gbs": quant_bytes / quant_seconds / 1e9,
+            "quant_pack_tokens": int(coeff.shape[0])}
 
 
 def run_ours(args) -> dict:
