@@ -47,7 +47,8 @@ constexpr int THREADS = COMPUTE_THREADS + 96;
 constexpr int CHUNK = 64;         // latent columns per pipeline step
 constexpr int PART = 64;          // K/V columns rebuilt by one CTA
 constexpr int TILE_BYTES = 128 * 128;  // one [128 rows x 64 bf16] swizzled tile
-constexpr int MAX_NW = 4;         // ring slots: decoder rows in shared memory + latent staging in TMEM
+constexpr int MAX_NW = 2;         // ring slots; a slot holds a PAIR of 64-column latent chunks:
+                                  // their decoder rows in shared memory and their staging in TMEM
 constexpr float RESCALE_THRESHOLD = 8.0f;
 
 enum Bar {
@@ -82,7 +83,8 @@ struct Layout {
   static constexpr int CODES_OFF = SCRATCH_OFF + TILE_BYTES;    // [128 tok][rank/2] codes of the tile
   __host__ __device__ static int codes_bytes(int rank) { return ((TOK * rank / 2 + 1023) / 1024) * 1024; }
   __host__ __device__ static int ring_off(int rank) { return CODES_OFF + codes_bytes(rank); }
-  static constexpr int SLOT_BYTES = PART * 128;          // [64 decoder rows x 64 latent cols]
+  static constexpr int CHUNK_BYTES = PART * 128;         // [64 decoder rows x 64 latent cols]
+  static constexpr int SLOT_BYTES = 2 * CHUNK_BYTES;     // a pair of chunks
   __host__ __device__ static int meta_off(int nw, int rank) { return ring_off(rank) + nw * SLOT_BYTES; }
   // meta: bars, tmem slot, abort, bias [64] floats, then two metadata buffers of
   // crow [128] ints and scales [128][ngroups] u16
@@ -135,10 +137,10 @@ __device__ __forceinline__ uint4 dequant8_bf16(uint32_t word, __nv_bfloat162 sca
   return r;
 }
 
-// TMEM column of latent staging slot s.  The four slots avoid the columns where P of the previous
-// tile may still be read by its PV MMAs (P0 in [0,64), P1 in [128,192)), so the next tile's codes
-// can be expanded while those MMAs run.
-__device__ __forceinline__ uint32_t staging_col(int s) { return s < 2 ? 64 + 32 * s : 128 + 32 * s; }
+// TMEM column of the latent staging of ring slot s (a pair of chunks = 64 columns).  The two
+// slots avoid the columns where P of the previous tile may still be read by its PV MMAs (P0 in
+// [0,64), P1 in [128,192)), so the next tile's codes can be expanded while those MMAs run.
+__device__ __forceinline__ uint32_t staging_col(int s) { return s == 0 ? 64 : 192; }
 
 // Lap timer of one thread: adds the cycles since the previous lap to a bucket kept in registers;
 // flush() adds the buckets to global memory once, at the end.
@@ -265,12 +267,14 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           bulk_load_1d(smem + L::CODES_OFF, hist.codes + static_cast<size_t>(tile0 + it) * TOK * row_bytes,
                        bytes, &bars[CODES_FULL]);
         }
-        for (int c = 0; c < nchunks && ok; ++c) {
+        for (int c = 0; c < nchunks && ok; c += 2) {
+          const int n = min(2, nchunks - c);     // chunks in this pair
           if (use >= 1) ok = mbar_wait(&bars[RING_FREE + slot], (use - 1) & 1, abort_flag, 110 + slot);
           if (!ok) break;
-          mbar_arrive_expect_tx(&bars[W_FULL + slot], PART * 128);
-          tma_load_2d(smem + ring_off + slot * L::SLOT_BYTES, map_w, c * CHUNK, head * D + part * PART,
-                      &bars[W_FULL + slot]);
+          mbar_arrive_expect_tx(&bars[W_FULL + slot], n * L::CHUNK_BYTES);
+          for (int j = 0; j < n; ++j)
+            tma_load_2d(smem + ring_off + slot * L::SLOT_BYTES + j * L::CHUNK_BYTES, map_w,
+                        (c + j) * CHUNK, head * D + part * PART, &bars[W_FULL + slot]);
           if (++slot == nw) { slot = 0; ++use; }
         }
       }
@@ -293,7 +297,8 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       bool ok = nq > 0 ? mbar_wait(&bars[Q_FULL], 0, abort_flag, 200) : true;
       int slot = 0, use = 0;
       for (int it = 0; it < ntiles && ok; ++it) {
-        for (int c = 0; c < nchunks && ok; ++c) {
+        for (int c = 0; c < nchunks && ok; c += 2) {
+          const int n = min(2, nchunks - c);
           ok = mbar_wait(&bars[W_FULL + slot], use & 1, abort_flag, 210 + slot);
           laps.lap(0);
           ok = ok && mbar_wait(&bars[LAT_FULL + slot], use & 1, abort_flag, 216 + slot);
@@ -302,14 +307,16 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           tc_fence_after();
           // descriptors are built once per chunk; a K = 16 step adds 32 bytes (2 in the address
           // field) to the shared-memory operand and 8 columns to the TMEM operand
-          const uint64_t w_desc =
-              make_smem_desc_sw128(smem_base + ring_off + slot * L::SLOT_BYTES);
-          const uint32_t lat = tmem_base + staging_col(slot);   // latent chunk staged in TMEM
-          mma_bf16_ts(tmem_base, lat, w_desc, idesc_dec, c > 0);
-          mma_bf16_ts(tmem_base, lat + 8, w_desc + 2, idesc_dec, true);
-          mma_bf16_ts(tmem_base, lat + 16, w_desc + 4, idesc_dec, true);
-          mma_bf16_ts(tmem_base, lat + 24, w_desc + 6, idesc_dec, true);
-          mma_commit(&bars[RING_FREE + slot]);   // frees the slot; on the last chunk: accumulator done
+          for (int j = 0; j < n; ++j) {
+            const uint64_t w_desc = make_smem_desc_sw128(smem_base + ring_off + slot * L::SLOT_BYTES +
+                                                         j * L::CHUNK_BYTES);
+            const uint32_t lat = tmem_base + staging_col(slot) + j * 32;   // chunk staged in TMEM
+            mma_bf16_ts(tmem_base, lat, w_desc, idesc_dec, c + j > 0);
+            mma_bf16_ts(tmem_base, lat + 8, w_desc + 2, idesc_dec, true);
+            mma_bf16_ts(tmem_base, lat + 16, w_desc + 4, idesc_dec, true);
+            mma_bf16_ts(tmem_base, lat + 24, w_desc + 6, idesc_dec, true);
+          }
+          mma_commit(&bars[RING_FREE + slot]);   // frees the slot; on the last pair: accumulator done
           if (++slot == nw) { slot = 0; ++use; }
           laps.lap(2);
         }
@@ -432,35 +439,39 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       ok = mbar_wait(&bars[CODES_FULL], it & 1, abort_flag, 318);
       if (!ok) break;
       const uint8_t* codes = smem + L::CODES_OFF + row * row_bytes + wg * 16;
-      for (int c = 0; c < nchunks && ok; ++c) {
-        // the TMEM staging slot is free once the MMAs of its previous use are complete
+      for (int c0 = 0; c0 < nchunks && ok; c0 += 2) {
+        const int n = min(2, nchunks - c0);   // chunks in this pair
+        // the slot's TMEM staging is free once the MMAs of its previous use are complete
         if (use >= 1) ok = mbar_wait(&bars[RING_FREE + slot], (use - 1) & 1, abort_flag, 320 + slot);
         laps.lap(2);
         if (!ok) break;
         tc_fence_after();
-        const uint4 code = *reinterpret_cast<const uint4*>(codes + c * 32);
-        const int col0 = c * CHUNK + wg * 32;   // this thread: token `row`, latent columns col0 .. +32
-        const int gi = ng == 1 ? 0 : (p.group == 32 ? 2 * c + wg : col0 / p.group);
-        const uint16_t sbits = scales[static_cast<size_t>(mb * TOK + row) * ng + gi];
-        const uint32_t words[4] = {code.x, code.y, code.z, code.w};
-        uint32_t packed[16];
-        if (p.scale_dtype == NKV_BF16) {
-          const uint32_t pair = static_cast<uint32_t>(sbits) * 0x00010001u;
-          const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&pair);
+        for (int j = 0; j < n; ++j) {
+          const int c = c0 + j;
+          const uint4 code = *reinterpret_cast<const uint4*>(codes + c * 32);
+          const int col0 = c * CHUNK + wg * 32;   // this thread: token `row`, latent columns col0 .. +32
+          const int gi = ng == 1 ? 0 : (p.group == 32 ? 2 * c + wg : col0 / p.group);
+          const uint16_t sbits = scales[static_cast<size_t>(mb * TOK + row) * ng + gi];
+          const uint32_t words[4] = {code.x, code.y, code.z, code.w};
+          uint32_t packed[16];
+          if (p.scale_dtype == NKV_BF16) {
+            const uint32_t pair = static_cast<uint32_t>(sbits) * 0x00010001u;
+            const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&pair);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint4 v = dequant8_bf16(words[j], scale2);
-            packed[4 * j] = v.x; packed[4 * j + 1] = v.y; packed[4 * j + 2] = v.z; packed[4 * j + 3] = v.w;
-          }
-        } else {
-          const float sc = scale_to_float(sbits, p.scale_dtype);
+            for (int k = 0; k < 4; ++k) {
+              const uint4 v = dequant8_bf16(words[k], scale2);
+              packed[4 * k] = v.x; packed[4 * k + 1] = v.y; packed[4 * k + 2] = v.z; packed[4 * k + 3] = v.w;
+            }
+          } else {
+            const float sc = scale_to_float(sbits, p.scale_dtype);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint4 v = dequant8(words[j], sc);
-            packed[4 * j] = v.x; packed[4 * j + 1] = v.y; packed[4 * j + 2] = v.z; packed[4 * j + 3] = v.w;
+            for (int k = 0; k < 4; ++k) {
+              const uint4 v = dequant8(words[k], sc);
+              packed[4 * k] = v.x; packed[4 * k + 1] = v.y; packed[4 * k + 2] = v.z; packed[4 * k + 3] = v.w;
+            }
           }
+          tmem_st16(tmem_base + lane_sel + staging_col(slot) + j * 32 + wg * 16, packed);
         }
-        tmem_st16(tmem_base + lane_sel + staging_col(slot) + wg * 16, packed);
         tmem_wait_st();
         laps.lap(4);
         tc_fence_before();
@@ -688,7 +699,6 @@ template <int D>
 int launch(const CUtensorMap maps[3], Params& p, cudaStream_t stream) {
   using L = Layout<D>;
   int nw = MAX_NW;
-  while (nw > 2 && L::bytes(nw, p.ngroups, p.rank) > SMEM_LIMIT) --nw;
   size_t smem = L::bytes(nw, p.ngroups, p.rank);
   NKV_REQUIRE(smem <= SMEM_LIMIT, NKV_ERR_UNSUPPORTED,
               "codec attention needs %zu bytes of shared memory (rank %d, rank/group %d)", smem,
