@@ -32,6 +32,7 @@ SHAPE = synthetic.CONFIGS["c3_wan_shaped"]
 FRAME = 1560
 METRIC = "codec_attention_history_tokens_per_s"
 UNIT = "history-tokens/s"
+NCU_TRAFFIC_BYTES = 518.5e6   # profiles/attn_codec_kernel_c3_wan_shaped.md
 
 
 def measured_peaks() -> tuple[dict, str]:
@@ -296,7 +297,10 @@ def run_ours(args) -> dict:
                      "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                      "peak_source": f"bf16_tflops_sustained of {peak_kind}",
                      "launch_ms": kernel_s * 1e3, "flops_per_launch": flops_launch,
-                     "traffic": None},
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch over the full
+                     # 99,840-token layer (ncu capture summarised under profiles/); per-rank shards
+                     # were not captured separately
+                     "traffic": NCU_TRAFFIC_BYTES if world == 1 else None},
         "encode": encode,
         "clocks": clocks,
     }

@@ -321,6 +321,19 @@ __device__ __forceinline__ void mma_commit_multicast(uint64_t* bar, uint16_t cta
       : "memory");
 }
 
+// true in exactly one lane of a converged warp.  Issuing single-thread instructions under this
+// predicate, with the whole warp executing the surrounding (uniform) control flow, lets the
+// compiler keep descriptors and addresses in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));

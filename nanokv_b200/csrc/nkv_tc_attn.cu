@@ -286,14 +286,16 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
     __syncwarp();
   } else if (warp == 9) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // the whole warp runs the (uniform) control flow; one elected lane issues
+    {
+      const bool leader = elect_one();
       const uint32_t idesc_dec = make_idesc_bf16(128, PART);  // [128 tok] x [64 columns]
       const uint32_t idesc_s = make_idesc_bf16(128, TOK);     // [128 q] x [128 tok]
       const uint32_t idesc_pv = make_idesc_bf16(128, D);      // [128 q] x [D]
       const uint32_t smem_base = smem_u32(smem);
       const uint16_t all_ctas = static_cast<uint16_t>((1u << CL) - 1);
       Laps laps;
-      laps.start(p.prof + 16, p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0);
+      laps.start(p.prof + 16, leader && p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0);
       bool ok = nq > 0 ? mbar_wait(&bars[Q_FULL], 0, abort_flag, 200) : true;
       int slot = 0, use = 0;
       for (int it = 0; it < ntiles && ok; ++it) {
@@ -311,12 +313,12 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
             const uint64_t w_desc = make_smem_desc_sw128(smem_base + ring_off + slot * L::SLOT_BYTES +
                                                          j * L::CHUNK_BYTES);
             const uint32_t lat = tmem_base + staging_col(slot) + j * 32;   // chunk staged in TMEM
-            mma_bf16_ts(tmem_base, lat, w_desc, idesc_dec, c + j > 0);
-            mma_bf16_ts(tmem_base, lat + 8, w_desc + 2, idesc_dec, true);
-            mma_bf16_ts(tmem_base, lat + 16, w_desc + 4, idesc_dec, true);
-            mma_bf16_ts(tmem_base, lat + 24, w_desc + 6, idesc_dec, true);
+            if (leader) mma_bf16_ts(tmem_base, lat, w_desc, idesc_dec, c + j > 0);
+            if (leader) mma_bf16_ts(tmem_base, lat + 8, w_desc + 2, idesc_dec, true);
+            if (leader) mma_bf16_ts(tmem_base, lat + 16, w_desc + 4, idesc_dec, true);
+            if (leader) mma_bf16_ts(tmem_base, lat + 24, w_desc + 6, idesc_dec, true);
           }
-          mma_commit(&bars[RING_FREE + slot]);   // frees the slot; on the last pair: accumulator done
+          if (leader) mma_commit(&bars[RING_FREE + slot]);   // frees the slot; on the last pair: accumulator done
           if (++slot == nw) { slot = 0; ++use; }
           laps.lap(2);
         }
@@ -334,16 +336,16 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
             const uint32_t peer_ready = map_to_cta(ready, peer);
             if (tensor == 0) {
               const uint32_t src = smem_base + L::K_OFF + part * TILE_BYTES;
-              bulk_copy_to_peer(map_to_cta(src, peer), src, TILE_BYTES, peer_ready);
+              if (leader) bulk_copy_to_peer(map_to_cta(src, peer), src, TILE_BYTES, peer_ready);
             } else {
 #pragma unroll
               for (int half = 0; half < 2; ++half) {
                 const uint32_t src = smem_base + L::VT_OFF + half * L::VT_TILE + part * PART * 128;
-                bulk_copy_to_peer(map_to_cta(src, peer), src, PART * 128, peer_ready);
+                if (leader) bulk_copy_to_peer(map_to_cta(src, peer), src, PART * 128, peer_ready);
               }
             }
           }
-          mbar_arrive_expect_tx(&bars[KV_READY], (CL - 1) * TILE_BYTES);
+          if (leader) mbar_arrive_expect_tx(&bars[KV_READY], (CL - 1) * TILE_BYTES);
         }
         ok = mbar_wait_cluster(&bars[KV_READY], it & 1, abort_flag, 220);
         laps.lap(3);
@@ -354,12 +356,12 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           for (int ch = 0; ch < L::DCH; ++ch) {
             const uint64_t a_desc = make_smem_desc_sw128(smem_base + L::Q_OFF + (i * L::DCH + ch) * TILE_BYTES);
             const uint64_t b_desc = make_smem_desc_sw128(smem_base + L::K_OFF + ch * TILE_BYTES);
-            mma_bf16(tmem_base + i * 128, a_desc, b_desc, idesc_s, ch > 0);
-            mma_bf16(tmem_base + i * 128, a_desc + 2, b_desc + 2, idesc_s, true);
-            mma_bf16(tmem_base + i * 128, a_desc + 4, b_desc + 4, idesc_s, true);
-            mma_bf16(tmem_base + i * 128, a_desc + 6, b_desc + 6, idesc_s, true);
+            if (leader) mma_bf16(tmem_base + i * 128, a_desc, b_desc, idesc_s, ch > 0);
+            if (leader) mma_bf16(tmem_base + i * 128, a_desc + 2, b_desc + 2, idesc_s, true);
+            if (leader) mma_bf16(tmem_base + i * 128, a_desc + 4, b_desc + 4, idesc_s, true);
+            if (leader) mma_bf16(tmem_base + i * 128, a_desc + 6, b_desc + 6, idesc_s, true);
           }
-          mma_commit(&bars[S_FULL + i]);
+          if (leader) mma_commit(&bars[S_FULL + i]);
         }
         for (int i = 0; i < nq && ok; ++i) {
           laps.lap(4);
@@ -373,20 +375,20 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
             const uint64_t b_desc = make_smem_desc_sw128(smem_base + L::VT_OFF + ch * L::VT_TILE);
             const uint32_t p_addr = tmem_base + i * 128 + ch * 32;
             const uint32_t o_addr = tmem_base + 256 + i * 128;
-            mma_bf16_ts(o_addr, p_addr, b_desc, idesc_pv, it > 0 || ch > 0);
-            mma_bf16_ts(o_addr, p_addr + 8, b_desc + 2, idesc_pv, true);
-            mma_bf16_ts(o_addr, p_addr + 16, b_desc + 4, idesc_pv, true);
-            mma_bf16_ts(o_addr, p_addr + 24, b_desc + 6, idesc_pv, true);
+            if (leader) mma_bf16_ts(o_addr, p_addr, b_desc, idesc_pv, it > 0 || ch > 0);
+            if (leader) mma_bf16_ts(o_addr, p_addr + 8, b_desc + 2, idesc_pv, true);
+            if (leader) mma_bf16_ts(o_addr, p_addr + 16, b_desc + 4, idesc_pv, true);
+            if (leader) mma_bf16_ts(o_addr, p_addr + 24, b_desc + 6, idesc_pv, true);
           }
-          mma_commit(&bars[PV_DONE + i]);
+          if (leader) mma_commit(&bars[PV_DONE + i]);
         }
         if (!ok) break;
         // tell every CTA of the cluster that this CTA no longer reads the tile's K / V
         if (nq > 0) {
-          mma_commit_multicast(&bars[KV_FREE], all_ctas);
+          if (leader) mma_commit_multicast(&bars[KV_FREE], all_ctas);
         } else {
           const uint32_t local = smem_u32(&bars[KV_FREE]);
-          for (uint32_t peer = 0; peer < CL; ++peer) mbar_arrive_cluster(map_to_cta(local, peer));
+          for (uint32_t peer = 0; peer < CL; ++peer) if (leader) mbar_arrive_cluster(map_to_cta(local, peer));
         }
         laps.lap(6);
       }
