@@ -115,29 +115,32 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     }
     __syncwarp();
   } else if (warp == 9) {
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc_bf16(128, p.NB);
-      const uint32_t smem_base = smem_u32(smem);
-      bool ok = true;
-      for (int c = 0; c < nchunks && ok; ++c) {
-        const int s = c % nst, u = c / nst;
-        ok = mbar_wait(&bars[TMA_FULL + s], u & 1, abort_flag, 410 + s);
-        if (ok && !ASSIGN) ok = mbar_wait(&bars[A_FULL + s], u & 1, abort_flag, 412 + s);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t stage = smem_base + s * stage_bytes;
-        const uint64_t a_desc = make_smem_desc_sw128(stage);
-        for (int a = 0; a < p.NACC; ++a) {
-          const uint64_t b_desc = make_smem_desc_sw128(stage + A_BYTES + a * b_bytes);
+    // The whole warp walks the uniform control flow; one elected lane issues.
+    const bool leader = elect_one();
+    const uint32_t idesc = make_idesc_bf16(128, p.NB);
+    const uint32_t smem_base = smem_u32(smem);
+    bool ok = true;
+    for (int c = 0; c < nchunks && ok; ++c) {
+      const int s = c % nst, u = c / nst;
+      ok = mbar_wait(&bars[TMA_FULL + s], u & 1, abort_flag, 410 + s);
+      if (ok && !ASSIGN) ok = mbar_wait(&bars[A_FULL + s], u & 1, abort_flag, 412 + s);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t stage = smem_base + s * stage_bytes;
+      const uint64_t a_desc = make_smem_desc_sw128(stage);
+      for (int a = 0; a < p.NACC; ++a) {
+        const uint64_t b_desc = make_smem_desc_sw128(stage + A_BYTES + a * b_bytes);
+        if (leader) {
           mma_bf16(tmem_base + a * 256, a_desc, b_desc, idesc, c > 0);
           mma_bf16(tmem_base + a * 256, a_desc + 2, b_desc + 2, idesc, true);
           mma_bf16(tmem_base + a * 256, a_desc + 4, b_desc + 4, idesc, true);
           mma_bf16(tmem_base + a * 256, a_desc + 6, b_desc + 6, idesc, true);
         }
-        mma_commit(&bars[STAGE_FREE + s]);
       }
-      if (ok) mma_commit(&bars[ACC_DONE]);
+      if (leader) mma_commit(&bars[STAGE_FREE + s]);
+      __syncwarp();
     }
+    if (ok && leader) mma_commit(&bars[ACC_DONE]);
     __syncwarp();
   } else {
     const int row = tid & 127, wg = tid >> 7;
