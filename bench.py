@@ -206,14 +206,33 @@ def run_ours(args) -> dict:
     out_host = torch.empty(shape.queries, shape.heads, shape.head_dim, dtype=torch.bfloat16).pin_memory()
     lse_host = torch.empty(shape.queries, shape.heads, dtype=torch.float32).pin_memory()
     status = torch.zeros(1, dtype=torch.int32, device=device)
+    exchange = None
+    if world > 1 and args.exchange == "peer":
+        exchange = context_parallel.PeerExchange(shape.queries, shape.heads, shape.head_dim,
+                                                 torch.bfloat16, device)
+        # the fused exchange must reproduce all-gather + merge bit for bit on this workload
+        (hk, ok), (hv, ov) = built[0]["k"], built[0]["v"]
+        attention.codec_attention(q_dev, hk, hv, ok, ov, status=status, out=exchange.partial_out,
+                                  lse=exchange.partial_lse)
+        fused_out, fused_lse = exchange.merge()
+        plain_out, plain_lse = context_parallel.gather_and_merge(exchange.partial_out.clone(),
+                                                                 exchange.partial_lse.clone())
+        if not (torch.equal(fused_out.view(torch.int16), plain_out.view(torch.int16))
+                and torch.equal(fused_lse.view(torch.int32), plain_lse.view(torch.int32))):
+            raise RuntimeError("peer-memory exchange differs from all-gather + merge")
 
     def step(host_io: bool):
         merged = None
         for entry in built:
             q = q_host.to(device, non_blocking=True) if host_io else q_dev
             (hk, ok), (hv, ov) = entry["k"], entry["v"]
-            out, lse = attention.codec_attention(q, hk, hv, ok, ov, status=status)
-            merged = context_parallel.gather_and_merge(out, lse)
+            if exchange is not None:
+                attention.codec_attention(q, hk, hv, ok, ov, status=status,
+                                          out=exchange.partial_out, lse=exchange.partial_lse)
+                merged = exchange.merge()
+            else:
+                out, lse = attention.codec_attention(q, hk, hv, ok, ov, status=status)
+                merged = context_parallel.gather_and_merge(out, lse)
             if host_io:
                 out_host.copy_(merged[0], non_blocking=True)
                 lse_host.copy_(merged[1], non_blocking=True)
@@ -264,8 +283,33 @@ def run_ours(args) -> dict:
         if index >= 3:
             kernel_ms.append(start.elapsed_time(stop))
     kernel_s = statistics.mean(kernel_ms) / 1e3
+
+    # the exchange step alone (collective: every rank runs it), max over ranks
+    exchange_ms = None
+    if world > 1:
+        part_out, part_lse = attention.codec_attention(q_dev, hk, hv, ok, ov, status=status)
+        if exchange is not None:
+            exchange.partial_out.copy_(part_out)
+            exchange.partial_lse.copy_(part_lse)
+        rounds = 10
+        for index in range(2 + rounds):
+            if index == 2:
+                barrier()
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+            if exchange is not None:
+                exchange.merge()
+            else:
+                context_parallel.gather_and_merge(part_out, part_lse)
+        stop.record()
+        barrier()
+        took = torch.tensor([start.elapsed_time(stop) / rounds], device=device)
+        dist.all_reduce(took, op=dist.ReduceOp.MAX)
+        exchange_ms = float(took.item())
     encode = time_encode(shape, device, steps=5, warmup=3) if rank == 0 else None
 
+    if exchange is not None:
+        exchange.close()
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -288,11 +332,15 @@ def run_ours(args) -> dict:
                    "rank": shape.rank, "centers": shape.centers, "history_tokens": shape.history,
                    "queries": shape.queries, "layers": layers, "quant_group": shape.rank,
                    "scale_dtype": "bf16", "parallelism": f"cp{world}",
+                   "exchange": ("none" if world == 1 else
+                                "peer-memory merge + all-gather kernel" if exchange is not None else
+                                "nccl all-gather + merge kernel"),
                    "l2_policy": "inputs larger than L2 (distinct compressed history per layer)"},
         "e2e": {"value": tokens_per_step / (e2e_seconds / e2e_steps), "unit": UNIT,
                 "h2d_bytes_per_step": q_bytes * layers, "d2h_bytes_per_step": o_bytes * layers},
         # per layer: fused attention + LSE merge of its history splits (+ the CP merge when sharded)
         "gpu_launches": args.steps * layers * (2 + (1 if world > 1 else 0)),
+        "exchange_ms_per_layer": exchange_ms,
         "roofline": {"bound": "tensor", "kernel": "attn_codec_kernel<128>", "achieved": achieved,
                      "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                      "peak_source": f"bf16_tflops_sustained of {peak_kind}",
@@ -508,6 +556,8 @@ def main() -> None:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--layers", type=int, default=SHAPE.layers)
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    parser.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                        help="context-parallel exchange: fused peer-memory kernel, or NCCL all-gather + merge")
     parser.add_argument("--workload", default="c3_wan_shaped",
                         choices=["c3_wan_shaped", "c4_fast_mixed", "c5_streaming"],
                         help="c3 is the headline; c4 / c5 are secondary measurements")

@@ -257,6 +257,37 @@ int nkv_attention_lse(const void* q, const void* k, const void* v, int dtype,
 int nkv_lse_merge(const void* const* outs, const float* const* lses, int parts,
                   int64_t rows, int d, int dtype, void* out, float* lse_out, void* stream);
 
+/*
+ * Context-parallel exchange over peer memory (one process per GPU on one
+ * NVSwitch box).  The reference has no history-sharded mode -- its only
+ * multi-GPU mode shards heads by all-to-all
+ * (models/LingBot-World-2.0/fast/wan/distributed/util.py:20-30,
+ * sequence_parallel.py:464-468) -- so these entry points have no counterpart there; the arithmetic is the
+ * reference's two-way merge (MGC/core.py:33-42) folded over the ranks, the
+ * same as nkv_lse_merge.
+ *
+ * nkv_peer_alloc: device buffer on the current device plus a 64-byte handle
+ * another process of the box passes to nkv_peer_open to map the buffer
+ * (peer access is enabled on first use).  nkv_peer_close unmaps, nkv_peer_free
+ * releases the owner's buffer once every peer has closed it.
+ *
+ * nkv_cp_merge_peer: this rank merges rows [row_begin, row_end) of the
+ * `world` partials (part_out[p]: [rows, d] of dtype, part_lse[p]: f32 [rows];
+ * host arrays of device pointers, one per rank, peers' buffers as mapped by
+ * nkv_peer_open) and stores the merged rows into every rank's dst_out[p] /
+ * dst_lse[p].  Plain loads and stores only (no multicast).  The caller orders
+ * the ranks: every partial complete before the call, every rank's call complete
+ * before any result is read or any partial overwritten.
+ */
+#define NKV_PEER_HANDLE_BYTES 64
+int nkv_peer_alloc(int64_t bytes, void** ptr, uint8_t* handle);
+int nkv_peer_open(const uint8_t* handle, void** ptr);
+int nkv_peer_close(void* ptr);
+int nkv_peer_free(void* ptr);
+int nkv_cp_merge_peer(const void* const* part_out, const float* const* part_lse,
+                      void* const* dst_out, float* const* dst_lse, int world, int64_t rows,
+                      int d, int64_t row_begin, int64_t row_end, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

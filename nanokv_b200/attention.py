@@ -17,7 +17,8 @@ def _view(hist) -> HistoryView:
 
 def codec_attention(q: torch.Tensor, hist_k, hist_v, op_k: Operator, op_v: Operator, *,
                     scale: float | None = None, status: torch.Tensor | None = None,
-                    splits: int | None = None):
+                    splits: int | None = None, out: torch.Tensor | None = None,
+                    lse: torch.Tensor | None = None):
     """Full-dimensional read: q [Q,H,D] -> (O [Q,H,D], lse f32 [Q,H]).
 
     K and V of every history token are rebuilt on chip from codes, scales, the
@@ -32,7 +33,8 @@ def codec_attention(q: torch.Tensor, hist_k, hist_v, op_k: Operator, op_v: Opera
     wk = op_k.decoder.view(H, D, op_k.rank)
     wv = op_v.decoder.view(H, D, op_v.rank)
     return ops.attn_codec(q, _view(hist_k), _view(hist_v), wk, op_k.bias.view(H, D), wv,
-                          op_v.bias.view(H, D), scale=scale, status=status, splits=splits)
+                          op_v.bias.view(H, D), scale=scale, status=status, splits=splits,
+                          out=out, lse=lse)
 
 
 def merge(out_a, lse_a, out_b, lse_b):

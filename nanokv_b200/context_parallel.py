@@ -1,6 +1,11 @@
 """Context-parallel read: the compressed history is split by token range over
 the ranks of one NVSwitch box; every rank attends its shard for all queries
-and heads, the (O, lse) partials are all-gathered and merged by log-sum-exp.
+and heads, and the (O, lse) partials are merged by log-sum-exp.  Two exchanges:
+``PeerExchange`` (the default on GPUs) -- every rank merges its slice of the
+rows straight out of the peers' partial buffers over NVLink and stores the
+merged rows into every rank's result buffer, one kernel for merge and
+all-gather; and ``gather_and_merge`` -- NCCL all-gather of whole partials,
+then a P-way merge on every rank (the plain form, P times the NVLink traffic).
 
 The reference has no history-sharded mode (its only multi-GPU mode is
 head-sharding by all-to-all); the merge arithmetic is its two-way merge
@@ -52,3 +57,75 @@ def gather_and_merge(out: torch.Tensor, lse: torch.Tensor, group=None):
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         return out, lse
     return merge_partials(gather_partials(out, lse, group))
+
+
+def _aligned(nbytes: int) -> int:
+    return (nbytes + 255) // 256 * 256
+
+
+class PeerExchange:
+    """Fused merge + all-gather of context-parallel partials over peer memory.
+
+    Every rank owns one peer-visible block holding its partial (O, lse) and its
+    merged result; ``partial_out`` / ``partial_lse`` are the buffers the read
+    kernel fills.  ``merge()`` then (1) waits until every rank's partial is
+    complete (a four-byte NCCL all-reduce on the compute stream), (2) launches
+    nkv_cp_merge_peer for this rank's row slice, which loads the slice of all
+    P partials (P-1 of them over NVLink) and stores the merged rows into all P
+    result buffers, (3) waits until every rank's slice has landed.  Each rank
+    moves 2 x (P-1)/P of one partial instead of receiving P-1 whole ones.
+    The same buffers serve every layer: step (3) also guarantees nobody still
+    reads a partial when the next read overwrites it, and step (1) of the next
+    layer orders the next store into ``out`` after its last consumer.
+    """
+
+    def __init__(self, queries: int, heads: int, width: int, dtype: torch.dtype, device, group=None):
+        if not dist.is_initialized():
+            raise RuntimeError("PeerExchange needs an initialised process group")
+        self.group, self.device = group, torch.device(device)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.shape, self.dtype = (queries, heads, width), dtype
+        self.rows = queries * heads
+        itemsize = torch.empty((), dtype=dtype).element_size()
+        out_bytes, lse_bytes = _aligned(self.rows * width * itemsize), _aligned(self.rows * 4)
+        self._offsets = {"part_out": 0, "part_lse": out_bytes, "out": out_bytes + lse_bytes,
+                         "lse": 2 * out_bytes + lse_bytes}
+        self.nbytes = 2 * (out_bytes + lse_bytes)
+        self.block = ops.PeerBuffer.allocate(self.nbytes, self.device)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, self.block.handle, group=group)
+        self.blocks = [self.block if r == self.rank else
+                       ops.PeerBuffer.open(handles[r], self.nbytes, self.device)
+                       for r in range(self.world)]
+        self.partial_out = self.block.tensor(self._offsets["part_out"], self.shape, dtype)
+        self.partial_lse = self.block.tensor(self._offsets["part_lse"], (queries, heads), torch.float32)
+        self.out = self.block.tensor(self._offsets["out"], self.shape, dtype)
+        self.lse = self.block.tensor(self._offsets["lse"], (queries, heads), torch.float32)
+        self.row_begin, self.row_end = shard_bounds(self.rows, self.world)[self.rank]
+        self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._fence()   # every rank has mapped every block before anyone uses one
+
+    def _fence(self) -> None:
+        dist.all_reduce(self._token, group=self.group)
+
+    def merge(self):
+        """Partials in ``partial_out`` / ``partial_lse`` on every rank -> merged (out, lse),
+        identical on every rank.  Stream-ordered; no host synchronisation."""
+        self._fence()
+        pointers = {name: [blk.pointer + off for blk in self.blocks]
+                    for name, off in self._offsets.items()}
+        ops.cp_merge_peer(pointers["part_out"], pointers["part_lse"], pointers["out"], pointers["lse"],
+                          rows=self.rows, width=self.shape[2], row_begin=self.row_begin,
+                          row_end=self.row_end, dtype=self.dtype, device=self.device)
+        self._fence()
+        return self.out, self.lse
+
+    def close(self) -> None:
+        """Collective: unmap the peers' blocks, then free this rank's."""
+        torch.cuda.synchronize(self.device)
+        self.partial_out = self.partial_lse = self.out = self.lse = None
+        for r, blk in enumerate(self.blocks):
+            if r != self.rank:
+                blk.release()
+        dist.barrier(group=self.group)
+        self.block.release()

@@ -291,4 +291,53 @@ int nkv_lse_merge(const void* const* outs, const float* const* lses, int parts, 
                    static_cast<cudaStream_t>(stream));
 }
 
+int nkv_peer_alloc(int64_t bytes, void** ptr, uint8_t* handle) {
+  NKV_REQUIRE(bytes > 0 && ptr && handle, NKV_ERR_INVALID, "peer_alloc: bytes=%lld",
+              static_cast<long long>(bytes));
+  static_assert(sizeof(cudaIpcMemHandle_t) == NKV_PEER_HANDLE_BYTES, "handle size");
+  void* base = nullptr;
+  NKV_CUDA(cudaMalloc(&base, static_cast<size_t>(bytes)));
+  cudaIpcMemHandle_t ipc;
+  cudaError_t err = cudaIpcGetMemHandle(&ipc, base);
+  if (err != cudaSuccess) {
+    cudaFree(base);
+    return fail(NKV_ERR_CUDA, "cudaIpcGetMemHandle: %s", cudaGetErrorString(err));
+  }
+  memcpy(handle, &ipc, sizeof(ipc));
+  *ptr = base;
+  return NKV_OK;
+}
+
+int nkv_peer_open(const uint8_t* handle, void** ptr) {
+  NKV_REQUIRE(handle && ptr, NKV_ERR_INVALID, "peer_open: null argument");
+  cudaIpcMemHandle_t ipc;
+  memcpy(&ipc, handle, sizeof(ipc));
+  void* mapped = nullptr;
+  NKV_CUDA(cudaIpcOpenMemHandle(&mapped, ipc, cudaIpcMemLazyEnablePeerAccess));
+  *ptr = mapped;
+  return NKV_OK;
+}
+
+int nkv_peer_close(void* ptr) {
+  NKV_REQUIRE(ptr, NKV_ERR_INVALID, "peer_close: null pointer");
+  NKV_CUDA(cudaIpcCloseMemHandle(ptr));
+  return NKV_OK;
+}
+
+int nkv_peer_free(void* ptr) {
+  NKV_REQUIRE(ptr, NKV_ERR_INVALID, "peer_free: null pointer");
+  NKV_CUDA(cudaFree(ptr));
+  return NKV_OK;
+}
+
+int nkv_cp_merge_peer(const void* const* part_out, const float* const* part_lse,
+                      void* const* dst_out, float* const* dst_lse, int world, int64_t rows,
+                      int d, int64_t row_begin, int64_t row_end, int dtype, void* stream) {
+  NKV_REQUIRE(part_out && part_lse && dst_out && dst_lse && rows >= 0 && d > 0, NKV_ERR_INVALID,
+              "cp_merge_peer: rows=%lld d=%d", static_cast<long long>(rows), d);
+  NKV_REQUIRE(dtype == NKV_F32 || dtype == NKV_BF16, NKV_ERR_INVALID, "cp_merge_peer: dtype");
+  return cp_merge_peer(part_out, part_lse, dst_out, dst_lse, world, rows, d, row_begin, row_end,
+                       dtype, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -165,6 +165,116 @@ lse_merge_kernel(MergeArgs args, int parts, long long rows, int d, int dtype, vo
   if (col == 0) lse_out[row] = lse;
 }
 
+// ---- context-parallel merge over peer memory ---------------------------------------------
+// Rank r of `world` owns rows [row_begin, row_end) of the merged result: it reads that row range of
+// every rank's partial (its own from local memory, the others through peer mappings over NVLink),
+// folds them exactly as lse_merge_kernel does, and stores the merged rows into every rank's result
+// buffer, so the merge and the all-gather of its result are one kernel.
+struct PeerMergeArgs {
+  const void* part_out[MAX_PARTS];
+  const float* part_lse[MAX_PARTS];
+  void* dst_out[MAX_PARTS];
+  float* dst_lse[MAX_PARTS];
+};
+
+template <typename VEC>  // uint4: 8 two-byte elements; float4 pairs are handled as two uint4 halves
+__device__ __forceinline__ VEC peer_load(const void* base, size_t byte_offset) {
+  return *reinterpret_cast<const VEC*>(static_cast<const char*>(base) + byte_offset);
+}
+
+// thread = (row, 8 consecutive columns)
+template <int DTYPE>
+__global__ void __launch_bounds__(256)
+cp_merge_peer_kernel(PeerMergeArgs args, int world, long long row_begin, long long row_end, int d) {
+  const int per_row = d >> 3;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= (row_end - row_begin) * per_row) return;
+  const long long row = row_begin + idx / per_row;
+  const int col = static_cast<int>(idx % per_row) * 8;
+  const size_t elem = static_cast<size_t>(row) * d + col;
+
+  float part_lse[MAX_PARTS];
+#pragma unroll
+  for (int p = 0; p < MAX_PARTS; ++p) part_lse[p] = p < world ? args.part_lse[p][row] : 0.f;
+  float lse = part_lse[0];
+#pragma unroll
+  for (int p = 1; p < MAX_PARTS; ++p)
+    if (p < world) lse = logaddexp(lse, part_lse[p]);
+  const float origin = isfinite(lse) ? lse : 0.f;
+
+  float acc[8];
+  if (DTYPE == NKV_F32) {
+    float4 lo[MAX_PARTS], hi[MAX_PARTS];
+#pragma unroll
+    for (int p = 0; p < MAX_PARTS; ++p)
+      if (p < world) {
+        lo[p] = peer_load<float4>(args.part_out[p], elem * 4);
+        hi[p] = peer_load<float4>(args.part_out[p], elem * 4 + 16);
+      }
+#pragma unroll
+    for (int p = 0; p < MAX_PARTS; ++p)
+      if (p < world) {
+        const float w = expf(part_lse[p] - origin);
+        const float v[8] = {lo[p].x, lo[p].y, lo[p].z, lo[p].w, hi[p].x, hi[p].y, hi[p].z, hi[p].w};
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const float t = __fmul_rn(v[c], w);
+          acc[c] = p == 0 ? t : __fadd_rn(acc[c], t);
+        }
+      }
+    const float4 out_lo = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    const float4 out_hi = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    for (int r = 0; r < world; ++r) {
+      float4* dst = reinterpret_cast<float4*>(static_cast<char*>(args.dst_out[r]) + elem * 4);
+      dst[0] = out_lo;
+      dst[1] = out_hi;
+    }
+  } else {
+    uint4 raw[MAX_PARTS];
+#pragma unroll
+    for (int p = 0; p < MAX_PARTS; ++p)
+      if (p < world) raw[p] = peer_load<uint4>(args.part_out[p], elem * 2);
+#pragma unroll
+    for (int p = 0; p < MAX_PARTS; ++p)
+      if (p < world) {
+        const float w = expf(part_lse[p] - origin);
+        const uint32_t words[4] = {raw[p].x, raw[p].y, raw[p].z, raw[p].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float v0, v1;
+          if (DTYPE == NKV_BF16) {
+            v0 = __uint_as_float(words[k] << 16);
+            v1 = __uint_as_float(words[k] & 0xFFFF0000u);
+          } else {
+            v0 = __half2float(__ushort_as_half(static_cast<uint16_t>(words[k] & 0xFFFFu)));
+            v1 = __half2float(__ushort_as_half(static_cast<uint16_t>(words[k] >> 16)));
+          }
+          const float t0 = __fmul_rn(v0, w), t1 = __fmul_rn(v1, w);
+          acc[2 * k] = p == 0 ? t0 : __fadd_rn(acc[2 * k], t0);
+          acc[2 * k + 1] = p == 0 ? t1 : __fadd_rn(acc[2 * k + 1], t1);
+        }
+      }
+    uint32_t packed[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      uint32_t lo16, hi16;
+      if (DTYPE == NKV_BF16) {
+        lo16 = float_to_bf16_bits(acc[2 * k]);
+        hi16 = float_to_bf16_bits(acc[2 * k + 1]);
+      } else {
+        lo16 = __half_as_ushort(__float2half_rn(acc[2 * k]));
+        hi16 = __half_as_ushort(__float2half_rn(acc[2 * k + 1]));
+      }
+      packed[k] = lo16 | (hi16 << 16);
+    }
+    const uint4 out = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    for (int r = 0; r < world; ++r)
+      *reinterpret_cast<uint4*>(static_cast<char*>(args.dst_out[r]) + elem * 2) = out;
+  }
+  if (col == 0)
+    for (int r = 0; r < world; ++r) args.dst_lse[r][row] = lse;
+}
+
 }  // namespace
 
 int quant_pack(const void* coeff, int coeff_dtype, int S, int r, int group, float eps,
@@ -210,6 +320,39 @@ int lse_merge(const void* const* outs, const float* const* lses, int parts, int6
   lse_merge_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
       args, parts, rows, d, dtype, out, lse_out);
   NKV_LAUNCH_CHECK("lse_merge_kernel");
+  return NKV_OK;
+}
+
+int cp_merge_peer(const void* const* part_out, const float* const* part_lse, void* const* dst_out,
+                  float* const* dst_lse, int world, int64_t rows, int d, int64_t row_begin,
+                  int64_t row_end, int dtype, cudaStream_t stream) {
+  NKV_REQUIRE(world >= 1 && world <= MAX_PARTS, NKV_ERR_TOO_LARGE,
+              "peer merge takes 1..%d ranks, got %d", MAX_PARTS, world);
+  NKV_REQUIRE(d % 8 == 0, NKV_ERR_INVALID, "peer merge width %d must be a multiple of 8", d);
+  NKV_REQUIRE(0 <= row_begin && row_begin <= row_end && row_end <= rows, NKV_ERR_INVALID,
+              "peer merge rows [%lld, %lld) outside [0, %lld)", static_cast<long long>(row_begin),
+              static_cast<long long>(row_end), static_cast<long long>(rows));
+  PeerMergeArgs args{};
+  for (int p = 0; p < world; ++p) {
+    NKV_REQUIRE(part_out[p] && part_lse[p] && dst_out[p] && dst_lse[p], NKV_ERR_INVALID,
+                "peer merge: null buffer of rank %d", p);
+    NKV_REQUIRE(((reinterpret_cast<uintptr_t>(part_out[p]) | reinterpret_cast<uintptr_t>(dst_out[p])) & 15) == 0,
+                NKV_ERR_INVALID, "peer merge: buffers of rank %d are not 16-byte aligned", p);
+    args.part_out[p] = part_out[p];
+    args.part_lse[p] = part_lse[p];
+    args.dst_out[p] = dst_out[p];
+    args.dst_lse[p] = dst_lse[p];
+  }
+  if (row_end == row_begin) return NKV_OK;
+  const long long total = (row_end - row_begin) * (d >> 3);
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  if (dtype == NKV_F32)
+    cp_merge_peer_kernel<NKV_F32><<<blocks, 256, 0, stream>>>(args, world, row_begin, row_end, d);
+  else if (dtype == NKV_BF16)
+    cp_merge_peer_kernel<NKV_BF16><<<blocks, 256, 0, stream>>>(args, world, row_begin, row_end, d);
+  else
+    cp_merge_peer_kernel<NKV_F16><<<blocks, 256, 0, stream>>>(args, world, row_begin, row_end, d);
+  NKV_LAUNCH_CHECK("cp_merge_peer_kernel");
   return NKV_OK;
 }
 

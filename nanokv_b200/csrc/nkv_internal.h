@@ -34,6 +34,9 @@ int quant_pack(const void* coeff, int coeff_dtype, int S, int r, int group, floa
                cudaStream_t stream);
 int lse_merge(const void* const* outs, const float* const* lses, int parts, int64_t rows,
               int d, int dtype, void* out, float* lse_out, cudaStream_t stream);
+int cp_merge_peer(const void* const* part_out, const float* const* part_lse, void* const* dst_out,
+                  float* const* dst_lse, int world, int64_t rows, int d, int64_t row_begin,
+                  int64_t row_end, int dtype, cudaStream_t stream);
 
 // ---- tcgen05 / TMA kernels (nkv_tc_*.cu), bf16 operands, fp32 accumulation
 int tc_assign(const void* x_bf16, const void* centers_bf16, int S, int J, int C, void* ids,

@@ -161,11 +161,13 @@ def default_splits(tokens: int) -> int:
 
 
 def attn_codec(q, view_k: HistoryView, view_v: HistoryView, wk, bias_k, wv, bias_v, *,
-               scale: float, status: torch.Tensor | None = None, splits: int | None = None):
+               scale: float, status: torch.Tensor | None = None, splits: int | None = None,
+               out: torch.Tensor | None = None, lse: torch.Tensor | None = None):
     """Fused read: q [Q,H,dk] -> (O [Q,H,dv], lse f32 [Q,H]).
 
     wk [H,dk,r], wv [H,dv,r] in q's dtype; bias f32 [H,dk] / [H,dv].  ``splits`` cuts the
     history into that many runs attended in one launch and merged by LSE (None: automatic).
+    ``out`` / ``lse`` name contiguous result buffers to fill (e.g. peer-visible ones).
     """
     device = _require_cuda(wk, bias_k, wv, bias_v, status)
     if not q.is_cuda:
@@ -174,8 +176,14 @@ def attn_codec(q, view_k: HistoryView, view_v: HistoryView, wk, bias_k, wv, bias
     dv = wv.shape[1]
     if q.stride(2) != 1:
         raise ValueError("queries must be contiguous along the head dimension")
-    out = torch.empty(Q, H, dv, dtype=q.dtype, device=device)
-    lse = torch.empty(Q, H, dtype=torch.float32, device=device)
+    if out is None:
+        out = torch.empty(Q, H, dv, dtype=q.dtype, device=device)
+    if lse is None:
+        lse = torch.empty(Q, H, dtype=torch.float32, device=device)
+    if (tuple(out.shape) != (Q, H, dv) or out.dtype != q.dtype or not out.is_contiguous()
+            or tuple(lse.shape) != (Q, H) or lse.dtype != torch.float32 or not lse.is_contiguous()):
+        raise ValueError("result buffers must be contiguous [Q,H,dv] in q's dtype and f32 [Q,H]")
+    _require_cuda(out, lse)
     sk, sv = view_k.struct(), view_v.struct()
     lib = _lib.library()
     if splits is None:
@@ -202,6 +210,77 @@ def attention_lse(q, k, v, *, scale: float):
         _ptr(q), _ptr(k), _ptr(v), dtype_code(q.dtype), q.stride(0), q.stride(1), k.stride(0),
         k.stride(1), Q, N, H, d, dv, float(scale), _ptr(out), _ptr(lse), _stream(device)))
     return out, lse
+
+
+class PeerBuffer:
+    """A device buffer other processes of the box can map (nkv_peer_alloc / nkv_peer_open).
+
+    ``handle`` (64 bytes) is what a peer passes to :meth:`open`; tensors over the memory come from
+    :meth:`tensor`.  The owner frees on :meth:`release`, a peer unmaps."""
+
+    def __init__(self, pointer: int, nbytes: int, device: torch.device, handle: bytes | None):
+        self.pointer, self.nbytes, self.device, self.handle = pointer, nbytes, device, handle
+
+    @classmethod
+    def allocate(cls, nbytes: int, device) -> "PeerBuffer":
+        device = torch.device(device)
+        handle = ctypes.create_string_buffer(64)
+        pointer = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            _lib.check(_lib.library().nkv_peer_alloc(int(nbytes), ctypes.byref(pointer), handle))
+        return cls(int(pointer.value), int(nbytes), device, handle.raw)
+
+    @classmethod
+    def open(cls, handle: bytes, nbytes: int, device) -> "PeerBuffer":
+        device = torch.device(device)
+        if len(handle) != 64:
+            raise ValueError("a peer handle is 64 bytes")
+        pointer = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            _lib.check(_lib.library().nkv_peer_open(handle, ctypes.byref(pointer)))
+        return cls(int(pointer.value), int(nbytes), device, None)
+
+    def tensor(self, offset: int, shape, dtype: torch.dtype) -> torch.Tensor:
+        """Zero-copy tensor over [offset, offset + numel * itemsize) of the buffer."""
+        count = 1
+        for extent in shape:
+            count *= int(extent)
+        itemsize = torch.empty((), dtype=dtype).element_size()
+        if offset < 0 or offset + count * itemsize > self.nbytes:
+            raise ValueError("tensor window outside the peer buffer")
+        window = _CudaWindow(self.pointer + offset, count * itemsize, self)
+        flat = torch.as_tensor(window, device=self.device)
+        return flat.view(dtype).view(*shape)
+
+    def release(self) -> None:
+        if self.pointer:
+            lib = _lib.library()
+            with torch.cuda.device(self.device):
+                _lib.check(lib.nkv_peer_free(self.pointer) if self.handle is not None
+                           else lib.nkv_peer_close(self.pointer))
+            self.pointer = 0
+
+
+class _CudaWindow:
+    """__cuda_array_interface__ view (uint8) of a raw device range; keeps its owner alive."""
+
+    def __init__(self, pointer: int, nbytes: int, owner):
+        self.owner = owner
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1",
+                                         "data": (pointer, False), "version": 3, "strides": None}
+
+
+def cp_merge_peer(part_out_ptrs, part_lse_ptrs, dst_out_ptrs, dst_lse_ptrs, *, rows: int, width: int,
+                  row_begin: int, row_end: int, dtype: torch.dtype, device) -> None:
+    """Merge rows [row_begin, row_end) of every rank's partial and store them into every rank's
+    result buffer (nkv_cp_merge_peer).  The pointer lists are per rank, peers' as mapped here."""
+    world = len(part_out_ptrs)
+    arrays = [(ctypes.c_void_p * world)(*[int(v) for v in values])
+              for values in (part_out_ptrs, part_lse_ptrs, dst_out_ptrs, dst_lse_ptrs)]
+    device = torch.device(device)
+    _lib.check(_lib.library().nkv_cp_merge_peer(
+        arrays[0], arrays[1], arrays[2], arrays[3], world, int(rows), int(width), int(row_begin),
+        int(row_end), dtype_code(dtype), _stream(device)))
 
 
 def lse_merge(partials):
