@@ -221,10 +221,29 @@ def run_ours(args) -> dict:
                 and torch.equal(fused_lse.view(torch.int32), plain_lse.view(torch.int32))):
             raise RuntimeError("peer-memory exchange differs from all-gather + merge")
 
+    # end-to-end I/O of a sharded job: every rank copies in its 1/P slice of the queries (then an
+    # NVLink all-gather makes them whole on every rank) and copies out its 1/P slice of the merged
+    # rows, so the job moves each input and result byte across PCIe once
+    rows = shape.queries * shape.heads
+    per_rank_q = -(-shape.queries // world)
+    q_lo, q_hi = min(shape.queries, rank * per_rank_q), min(shape.queries, (rank + 1) * per_rank_q)
+    row_lo, row_hi = context_parallel.shard_bounds(rows, world)[rank]
+    if world > 1:
+        q_stage = torch.zeros(per_rank_q, shape.heads, shape.head_dim, dtype=torch.bfloat16, device=device)
+        q_whole = torch.empty(world * per_rank_q, shape.heads, shape.head_dim, dtype=torch.bfloat16,
+                              device=device)
+
+    def queries_from_host():
+        if world == 1:
+            return q_host.to(device, non_blocking=True)
+        q_stage[:q_hi - q_lo].copy_(q_host[q_lo:q_hi], non_blocking=True)
+        dist.all_gather_into_tensor(q_whole, q_stage)
+        return q_whole[:shape.queries]
+
     def step(host_io: bool):
         merged = None
         for entry in built:
-            q = q_host.to(device, non_blocking=True) if host_io else q_dev
+            q = queries_from_host() if host_io else q_dev
             (hk, ok), (hv, ov) = entry["k"], entry["v"]
             if exchange is not None:
                 attention.codec_attention(q, hk, hv, ok, ov, status=status,
@@ -234,8 +253,10 @@ def run_ours(args) -> dict:
                 out, lse = attention.codec_attention(q, hk, hv, ok, ov, status=status)
                 merged = context_parallel.gather_and_merge(out, lse)
             if host_io:
-                out_host.copy_(merged[0], non_blocking=True)
-                lse_host.copy_(merged[1], non_blocking=True)
+                out_host.view(rows, -1)[row_lo:row_hi].copy_(
+                    merged[0].view(rows, -1)[row_lo:row_hi], non_blocking=True)
+                lse_host.view(rows)[row_lo:row_hi].copy_(merged[1].view(rows)[row_lo:row_hi],
+                                                         non_blocking=True)
         return merged
 
     def barrier():
@@ -335,6 +356,10 @@ def run_ours(args) -> dict:
                    "exchange": ("none" if world == 1 else
                                 "peer-memory merge + all-gather kernel" if exchange is not None else
                                 "nccl all-gather + merge kernel"),
+                   "e2e_io": ("whole queries in, whole (O, lse) out" if world == 1 else
+                              "each rank copies its 1/P slice of the queries in (NVLink all-gather "
+                              "makes them whole) and its 1/P slice of the merged rows out; bytes are "
+                              "job totals"),
                    "l2_policy": "inputs larger than L2 (distinct compressed history per layer)"},
         "e2e": {"value": tokens_per_step / (e2e_seconds / e2e_steps), "unit": UNIT,
                 "h2d_bytes_per_step": q_bytes * layers, "d2h_bytes_per_step": o_bytes * layers},
