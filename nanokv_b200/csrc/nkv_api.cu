@@ -35,7 +35,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 int encode_tensor_map(CUtensorMap* map, int elem_bytes, const void* base, int rank,
                       const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
-                      bool swizzle128) {
+                      int swizzle_bytes) {
   static EncodeTiledFn encode = nullptr;
   if (!encode) {
     void* fn = nullptr;
@@ -64,7 +64,8 @@ int encode_tensor_map(CUtensorMap* map, int elem_bytes, const void* base, int ra
   CUresult rc = encode(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8,
                        static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdims, gstrides, gbox,
                        estrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                       swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                       swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                       : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE,
                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   NKV_REQUIRE(rc == CUDA_SUCCESS, NKV_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d",
               static_cast<int>(rc));

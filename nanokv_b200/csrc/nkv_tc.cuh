@@ -343,9 +343,9 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }  // namespace tc
 
 // ---- host: tensor-map encoding ---------------------------------------------------
-// dims / strides innermost first; strides in bytes for dims 1..rank-1.
+// dims / strides innermost first; strides in bytes for dims 1..rank-1; swizzle_bytes 0, 64 or 128.
 int encode_tensor_map(CUtensorMap* map, int elem_bytes, const void* base, int rank,
                       const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
-                      bool swizzle128);
+                      int swizzle_bytes);
 
 }  // namespace nkv

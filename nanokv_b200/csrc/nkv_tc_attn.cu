@@ -47,12 +47,18 @@ constexpr int THREADS = COMPUTE_THREADS + 96;
 constexpr int CHUNK = 64;         // latent columns per pipeline step
 constexpr int PART = 64;          // K/V columns rebuilt by one CTA
 constexpr int TILE_BYTES = 128 * 128;  // one [128 rows x 64 bf16] swizzled tile
-constexpr int MAX_NW = 2;         // ring slots; a slot holds a PAIR of 64-column latent chunks:
-                                  // their decoder rows in shared memory and their staging in TMEM
+constexpr int MAX_NW = 4;         // decoder-row ring slots in shared memory; a slot holds the rows of a
+                                  // PAIR of 64-column latent chunks (as many slots as fit, at least 2)
+#ifndef NKV_NSTAGE
+#define NKV_NSTAGE 2              // 3 (third slot in P1's columns) measured 2 % slower on H 40 x D 128, r 640
+#endif
+constexpr int NSTAGE = NKV_NSTAGE;  // latent staging slots in tensor memory (a pair of chunks each);
+                                    // pair i of a tile uses slot i % NSTAGE
+constexpr int NDONE = 8;          // "MMAs of pair g are complete" barriers, indexed by g % 8
 constexpr float RESCALE_THRESHOLD = 8.0f;
 
 enum Bar {
-  Q_FULL = 0, W_FULL = 1, RING_FREE = 7, LAT_FULL = 13,
+  Q_FULL = 0, W_FULL = 1, PAIR_DONE = 5, LAT_FULL = 13,
   META_FULL = 22, META_FREE = 24, KV_READY = 26, KV_FREE = 27, S_FULL = 28, P_READY = 30,
   PV_DONE = 32, EPI_LOCAL = 34, CODES_FULL = 35, CODES_FREE = 36, NUM_BARS = 37
 };
@@ -79,9 +85,18 @@ struct Layout {
   static constexpr int K_OFF = Q_OFF + NQ * DCH * TILE_BYTES;   // [DCH] tiles [128 tok x 64]
   static constexpr int VT_OFF = K_OFF + DCH * TILE_BYTES;       // [2] tiles [D rows x 64 tok]
   static constexpr int VT_TILE = D * 128;
-  static constexpr int SCRATCH_OFF = VT_OFF + 2 * VT_TILE;      // 8 warps x 2 KB: centre staging
-  static constexpr int CODES_OFF = SCRATCH_OFF + TILE_BYTES;    // [128 tok][rank/2] codes of the tile
-  __host__ __device__ static int codes_bytes(int rank) { return ((TOK * rank / 2 + 1023) / 1024) * 1024; }
+  // codes of the tile: one [128 tok x 64 byte] block per pair of latent chunks, 64-byte swizzle
+  // (rows 64 bytes apart would put a quarter-warp's 16-byte reads on two bank groups)
+  static constexpr int CODES_OFF = VT_OFF + 2 * VT_TILE;
+  static constexpr int CODE_BLOCK = TOK * 64;
+  // centre staging of the epilogue (8 warps x 2 KB) reuses the head of the code buffer: the codes
+  // of a tile are all expanded before its epilogue starts, and the next tile's codes are only
+  // requested (CODES_FREE) after the staging has been read back
+  static constexpr int SCRATCH_OFF = CODES_OFF;
+  __host__ __device__ static int codes_bytes(int rank) {
+    const int bytes = ((rank / CHUNK + 1) / 2) * CODE_BLOCK;
+    return bytes < TILE_BYTES ? TILE_BYTES : bytes;
+  }
   __host__ __device__ static int ring_off(int rank) { return CODES_OFF + codes_bytes(rank); }
   static constexpr int CHUNK_BYTES = PART * 128;         // [64 decoder rows x 64 latent cols]
   static constexpr int SLOT_BYTES = 2 * CHUNK_BYTES;     // a pair of chunks
@@ -137,10 +152,19 @@ __device__ __forceinline__ uint4 dequant8_bf16(uint32_t word, __nv_bfloat162 sca
   return r;
 }
 
-// TMEM column of the latent staging of ring slot s (a pair of chunks = 64 columns).  The two
-// slots avoid the columns where P of the previous tile may still be read by its PV MMAs (P0 in
-// [0,64), P1 in [128,192)), so the next tile's codes can be expanded while those MMAs run.
-__device__ __forceinline__ uint32_t staging_col(int s) { return s == 0 ? 64 : 192; }
+// One arrival per warp: 32 lanes arriving on the same mbarrier are 32 serialised shared-memory
+// atomics; the lanes synchronise (which orders their earlier accesses and fences before lane 0's
+// releasing arrive) and lane 0 arrives for the warp.
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
+
+// TMEM column of latent staging slot s (a pair of chunks = 64 columns).  Slots 0 and 1 avoid the
+// columns where P of the previous tile may still be read by its PV MMAs (P0 in [0,64), P1 in
+// [128,192)), so the next tile's first two pairs can be expanded while those MMAs run; slot 2 is
+// P1's place and is first written at pair 2, after a wait for PV_DONE of the second query tile.
+__device__ __forceinline__ uint32_t staging_col(int s) { return s == 0 ? 64 : (s == 1 ? 192 : 128); }
 
 // Lap timer of one thread: adds the cycles since the previous lap to a bucket kept in registers;
 // flush() adds the buckets to global memory once, at the end.
@@ -175,7 +199,9 @@ template <int D>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
                   const __grid_constant__ CUtensorMap map_wk,
-                  const __grid_constant__ CUtensorMap map_wv, Params p) {
+                  const __grid_constant__ CUtensorMap map_wv,
+                  const __grid_constant__ CUtensorMap map_ck,
+                  const __grid_constant__ CUtensorMap map_cv, Params p) {
   using L = Layout<D>;
   constexpr int CL = L::CL;
   extern __shared__ uint8_t smem_raw[];
@@ -186,7 +212,6 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
   const int nw = p.nw;
   uint8_t* meta = smem + L::meta_off(nw, p.rank);
   const int ring_off = L::ring_off(p.rank);
-  const int row_bytes = p.rank / 2;          // code bytes per token
   uint64_t* bars = reinterpret_cast<uint64_t*>(meta + L::BARS);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(meta + L::SLOT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(meta + L::ABORT);
@@ -209,23 +234,21 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
 
   if (tid == 0) {
     mbar_init(&bars[Q_FULL], 1);
-    for (int s = 0; s < MAX_NW; ++s) {
-      mbar_init(&bars[W_FULL + s], 1);                      // TMA: codes + decoder rows landed
-      mbar_init(&bars[LAT_FULL + s], COMPUTE_THREADS);      // latent chunk staged in TMEM
-      mbar_init(&bars[RING_FREE + s], 1);                   // the chunk's MMAs are complete
-    }
+    for (int s = 0; s < MAX_NW; ++s) mbar_init(&bars[W_FULL + s], 1);   // TMA: decoder rows of a pair landed
+    for (int s = 0; s < NSTAGE; ++s) mbar_init(&bars[LAT_FULL + s], COMPUTE_WARPS);  // latent pair staged in TMEM
+    for (int s = 0; s < NDONE; ++s) mbar_init(&bars[PAIR_DONE + s], 1);  // the pair's MMAs are complete
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&bars[META_FULL + s], 32);
-      mbar_init(&bars[META_FREE + s], COMPUTE_THREADS);
+      mbar_init(&bars[META_FULL + s], 1);
+      mbar_init(&bars[META_FREE + s], COMPUTE_WARPS);
       mbar_init(&bars[S_FULL + s], 1);
-      mbar_init(&bars[P_READY + s], QT);
+      mbar_init(&bars[P_READY + s], QT / 32);
       mbar_init(&bars[PV_DONE + s], 1);
     }
     mbar_init(&bars[KV_READY], 1);                    // local arrival + bytes copied in by the peers
-    mbar_init(&bars[EPI_LOCAL], COMPUTE_THREADS);     // this CTA's part is in its own shared memory
+    mbar_init(&bars[EPI_LOCAL], COMPUTE_WARPS);     // this CTA's part is in its own shared memory
     mbar_init(&bars[KV_FREE], CL);
     mbar_init(&bars[CODES_FULL], 1);                  // the tile's codes landed (one bulk copy)
-    mbar_init(&bars[CODES_FREE], COMPUTE_THREADS);    // every thread is done expanding them                    // one arrival per CTA: its reads are done
+    mbar_init(&bars[CODES_FREE], COMPUTE_WARPS);    // every thread is done expanding them                    // one arrival per CTA: its reads are done
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -243,7 +266,9 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       const CUtensorMap* map_w = tensor ? &map_wv : &map_wk;
+      const CUtensorMap* map_c = tensor ? &map_cv : &map_ck;
       prefetch_tensormap(map_w);
+      prefetch_tensormap(map_c);
       if (nq > 0) {
         prefetch_tensormap(&map_q);
         mbar_arrive_expect_tx(&bars[Q_FULL], nq * L::DCH * TILE_BYTES);
@@ -253,7 +278,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
                         q0 + i * QT, &bars[Q_FULL]);
       }
       bool ok = true;
-      int slot = 0, use = 0;
+      int slot = 0, use = 0, g = 0;   // g: running pair number over all tiles
       for (int it = 0; it < ntiles && ok; ++it) {
         // the tile's codes: rows are contiguous in the history, so one untiled bulk copy; it is
         // issued as soon as the previous tile's codes are expanded and lands during that tile's
@@ -261,20 +286,24 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         if (it > 0) ok = mbar_wait(&bars[CODES_FREE], (it - 1) & 1, abort_flag, 108);
         if (!ok) break;
         {
-          const int rows = min(TOK, p.N - (tile0 + it) * TOK);
-          const uint32_t bytes = static_cast<uint32_t>(rows) * row_bytes;
-          mbar_arrive_expect_tx(&bars[CODES_FULL], bytes);
-          bulk_load_1d(smem + L::CODES_OFF, hist.codes + static_cast<size_t>(tile0 + it) * TOK * row_bytes,
-                       bytes, &bars[CODES_FULL]);
+          const int npairs = (nchunks + 1) / 2;
+          mbar_arrive_expect_tx(&bars[CODES_FULL], npairs * L::CODE_BLOCK);
+          for (int pi = 0; pi < npairs; ++pi)   // bytes past the row or the history read as zero
+            tma_load_2d(smem + L::CODES_OFF + pi * L::CODE_BLOCK, map_c, pi * 64, (tile0 + it) * TOK,
+                        &bars[CODES_FULL]);
         }
         for (int c = 0; c < nchunks && ok; c += 2) {
           const int n = min(2, nchunks - c);     // chunks in this pair
-          if (use >= 1) ok = mbar_wait(&bars[RING_FREE + slot], (use - 1) & 1, abort_flag, 110 + slot);
+          // the slot's previous tenant was pair g - nw
+          if (g >= nw)
+            ok = mbar_wait(&bars[PAIR_DONE + ((g - nw) & (NDONE - 1))], ((g - nw) / NDONE) & 1,
+                           abort_flag, 110 + slot);
           if (!ok) break;
           mbar_arrive_expect_tx(&bars[W_FULL + slot], n * L::CHUNK_BYTES);
           for (int j = 0; j < n; ++j)
             tma_load_2d(smem + ring_off + slot * L::SLOT_BYTES + j * L::CHUNK_BYTES, map_w,
                         (c + j) * CHUNK, head * D + part * PART, &bars[W_FULL + slot]);
+          ++g;
           if (++slot == nw) { slot = 0; ++use; }
         }
       }
@@ -297,13 +326,16 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       Laps laps;
       laps.start(p.prof + 16, leader && p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0);
       bool ok = nq > 0 ? mbar_wait(&bars[Q_FULL], 0, abort_flag, 200) : true;
-      int slot = 0, use = 0;
+      int slot = 0, use = 0, g = 0;   // decoder-row ring position; running pair number
+      uint32_t lat_phase = 0;         // bit s: parity of the next completion of LAT_FULL[s]
       for (int it = 0; it < ntiles && ok; ++it) {
+        int st = 0;
         for (int c = 0; c < nchunks && ok; c += 2) {
           const int n = min(2, nchunks - c);
           ok = mbar_wait(&bars[W_FULL + slot], use & 1, abort_flag, 210 + slot);
           laps.lap(0);
-          ok = ok && mbar_wait(&bars[LAT_FULL + slot], use & 1, abort_flag, 216 + slot);
+          ok = ok && mbar_wait(&bars[LAT_FULL + st], (lat_phase >> st) & 1, abort_flag, 216 + st);
+          lat_phase ^= 1u << st;
           laps.lap(1);
           if (!ok) break;
           tc_fence_after();
@@ -312,14 +344,17 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           for (int j = 0; j < n; ++j) {
             const uint64_t w_desc = make_smem_desc_sw128(smem_base + ring_off + slot * L::SLOT_BYTES +
                                                          j * L::CHUNK_BYTES);
-            const uint32_t lat = tmem_base + staging_col(slot) + j * 32;   // chunk staged in TMEM
+            const uint32_t lat = tmem_base + staging_col(st) + j * 32;   // chunk staged in TMEM
             if (leader) mma_bf16_ts(tmem_base, lat, w_desc, idesc_dec, c + j > 0);
             if (leader) mma_bf16_ts(tmem_base, lat + 8, w_desc + 2, idesc_dec, true);
             if (leader) mma_bf16_ts(tmem_base, lat + 16, w_desc + 4, idesc_dec, true);
             if (leader) mma_bf16_ts(tmem_base, lat + 24, w_desc + 6, idesc_dec, true);
           }
-          if (leader) mma_commit(&bars[RING_FREE + slot]);   // frees the slot; on the last pair: accumulator done
+          // frees the decoder rows and the staging; on the last pair: accumulator done
+          if (leader) mma_commit(&bars[PAIR_DONE + (g & (NDONE - 1))]);
+          ++g;
           if (++slot == nw) { slot = 0; ++use; }
+          if (++st == NSTAGE) st = 0;
           laps.lap(2);
         }
         if (!ok) break;
@@ -411,7 +446,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         uint16_t* dst = scales + static_cast<size_t>(b * TOK + r) * ng;
         for (int gi = 0; gi < ng; ++gi) dst[gi] = in ? src[gi] : 0;
       }
-      mbar_arrive(&bars[META_FULL + b]);
+      warp_arrive(&bars[META_FULL + b], lane);
     }
   } else {
     // ------------------------------------------------------------ compute warps
@@ -420,7 +455,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
     const uint32_t lane_sel = static_cast<uint32_t>(32 * (warp & 3)) << 16;
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
-    int slot = 0, use = 0;
+    int g = 0;   // running pair number over all tiles
     Laps laps;
     laps.start(p.prof, p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0);
     for (int it = 0; it < ntiles && ok; ++it) {
@@ -437,54 +472,76 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       laps.lap(1);
       if (!ok) break;
       // ---- expand this CTA's codes to bf16 latent chunks in tensor memory (A of the decode MMA)
-      int last_slot = 0, last_use = 0;
       ok = mbar_wait(&bars[CODES_FULL], it & 1, abort_flag, 318);
+      laps.lap(3);
       if (!ok) break;
-      const uint8_t* codes = smem + L::CODES_OFF + row * row_bytes + wg * 16;
+      // this thread's 16 bytes of chunk j of pair pi: 16-byte unit 2 j + wg of row `row`, swizzled
+      const uint8_t* codes = smem + L::CODES_OFF + row * 64;
+      const int unit_xor = (row >> 1) & 3;
+      auto code_at = [&](int c) {
+        return *reinterpret_cast<const uint4*>(codes + (c >> 1) * L::CODE_BLOCK +
+                                               ((((c & 1) * 2 + wg) ^ unit_xor) << 4));
+      };
+      const uint16_t* my_scales = scales + static_cast<size_t>(mb * TOK + row) * ng;
+      // codes of the pair after the one being expanded are fetched ahead of the wait for its slot
+      uint4 code_next[2];
+      code_next[0] = code_at(0);
+      code_next[1] = nchunks > 1 ? code_at(1) : make_uint4(0, 0, 0, 0);
+      int st = 0;
       for (int c0 = 0; c0 < nchunks && ok; c0 += 2) {
         const int n = min(2, nchunks - c0);   // chunks in this pair
-        // the slot's TMEM staging is free once the MMAs of its previous use are complete
-        if (use >= 1) ok = mbar_wait(&bars[RING_FREE + slot], (use - 1) & 1, abort_flag, 320 + slot);
+        const uint4 code_cur[2] = {code_next[0], code_next[1]};
+        if (c0 + 2 < nchunks) code_next[0] = code_at(c0 + 2);
+        if (c0 + 3 < nchunks) code_next[1] = code_at(c0 + 3);
+        laps.lap(5);
+        // The staging slot's previous tenant in this tile is pair g - NSTAGE.  The first NSTAGE pairs
+        // of a tile follow pairs of the previous tile, all complete (its epilogue waited for the last
+        // one); slot 2 is also where P of the second query tile sat, read by that tile's PV MMAs.
+        if (c0 >= 2 * NSTAGE)
+          ok = mbar_wait(&bars[PAIR_DONE + ((g - NSTAGE) & (NDONE - 1))], ((g - NSTAGE) / NDONE) & 1,
+                         abort_flag, 320 + st);
+        else if (c0 == 4 && it > 0 && nq == 2)
+          ok = mbar_wait(&bars[PV_DONE + 1], (it - 1) & 1, abort_flag, 323);
         laps.lap(2);
         if (!ok) break;
         tc_fence_after();
-        for (int j = 0; j < n; ++j) {
-          const int c = c0 + j;
-          const uint4 code = *reinterpret_cast<const uint4*>(codes + c * 32);
-          const int col0 = c * CHUNK + wg * 32;   // this thread: token `row`, latent columns col0 .. +32
-          const int gi = ng == 1 ? 0 : (p.group == 32 ? 2 * c + wg : col0 / p.group);
-          const uint16_t sbits = scales[static_cast<size_t>(mb * TOK + row) * ng + gi];
-          const uint32_t words[4] = {code.x, code.y, code.z, code.w};
-          uint32_t packed[16];
-          if (p.scale_dtype == NKV_BF16) {
-            const uint32_t pair = static_cast<uint32_t>(sbits) * 0x00010001u;
-            const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&pair);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const uint4 v = dequant8_bf16(words[k], scale2);
-              packed[4 * k] = v.x; packed[4 * k + 1] = v.y; packed[4 * k + 2] = v.z; packed[4 * k + 3] = v.w;
-            }
-          } else {
-            const float sc = scale_to_float(sbits, p.scale_dtype);
+        for (int j = 0; j < 2; ++j) {
+          if (j < n) {
+            const int c = c0 + j;
+            const uint4 code = code_cur[j];
+            const int col0 = c * CHUNK + wg * 32;   // this thread: token `row`, latent columns col0 .. +32
+            const int gi = ng == 1 ? 0 : (p.group == 32 ? 2 * c + wg : col0 / p.group);
+            const uint16_t sbits = my_scales[gi];
+            const uint32_t words[4] = {code.x, code.y, code.z, code.w};
+            uint32_t packed[16];
+            if (p.scale_dtype == NKV_BF16) {
+              const uint32_t pair = static_cast<uint32_t>(sbits) * 0x00010001u;
+              const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&pair);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const uint4 v = dequant8(words[k], sc);
-              packed[4 * k] = v.x; packed[4 * k + 1] = v.y; packed[4 * k + 2] = v.z; packed[4 * k + 3] = v.w;
+              for (int k = 0; k < 4; ++k) {
+                const uint4 v = dequant8_bf16(words[k], scale2);
+                packed[4 * k] = v.x; packed[4 * k + 1] = v.y; packed[4 * k + 2] = v.z; packed[4 * k + 3] = v.w;
+              }
+            } else {
+              const float sc = scale_to_float(sbits, p.scale_dtype);
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const uint4 v = dequant8(words[k], sc);
+                packed[4 * k] = v.x; packed[4 * k + 1] = v.y; packed[4 * k + 2] = v.z; packed[4 * k + 3] = v.w;
+              }
             }
+            tmem_st16(tmem_base + lane_sel + staging_col(st) + j * 32 + wg * 16, packed);
           }
-          tmem_st16(tmem_base + lane_sel + staging_col(slot) + j * 32 + wg * 16, packed);
         }
         tmem_wait_st();
-        laps.lap(4);
         tc_fence_before();
-        mbar_arrive(&bars[LAT_FULL + slot]);
-        laps.lap(5);
-        last_slot = slot;
-        last_use = use;
-        if (++slot == nw) { slot = 0; ++use; }
+        warp_arrive(&bars[LAT_FULL + st], lane);
+        laps.lap(4);
+        ++g;
+        if (++st == NSTAGE) st = 0;
       }
       if (!ok) break;
-      mbar_arrive(&bars[CODES_FREE]);
       // ---- epilogue of this CTA's part: bias, centre, two bf16 roundings, store to every CTA
       {
         const bool in = row < valid;
@@ -504,7 +561,8 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
               cbase + static_cast<size_t>(crow_i) * hist.center_width + piece * 8));
         }
         laps.lap(6);
-        ok = mbar_wait(&bars[RING_FREE + last_slot], last_use & 1, abort_flag, 330);
+        // accumulator complete: the tile's last pair is pair g - 1
+        ok = mbar_wait(&bars[PAIR_DONE + ((g - 1) & (NDONE - 1))], ((g - 1) / NDONE) & 1, abort_flag, 330);
         laps.lap(7);
         if (!ok) break;
         tc_fence_after();
@@ -522,6 +580,9 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
             cen[j] = *reinterpret_cast<const uint4*>(stage + lane * (PIECES * 16) +
                                                      ((j ^ (lane & (PIECES - 1))) << 4));
           __syncwarp();
+          // the staging lived in the code buffer: only now may the next tile's codes overwrite it
+          fence_proxy_async();
+          warp_arrive(&bars[CODES_FREE], lane);
         }
         float v[32];
         tmem_ld32(tmem_base + lane_sel + wg * 32, v);
@@ -567,9 +628,9 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         }
       }
       laps.lap(8);
-      mbar_arrive(&bars[META_FREE + mb]);
+      warp_arrive(&bars[META_FREE + mb], lane);
       fence_proxy_async();
-      mbar_arrive(&bars[EPI_LOCAL]);
+      warp_arrive(&bars[EPI_LOCAL], lane);
       laps.lap(9);
       // ---- online softmax of this thread's query row
       if (wg < nq) {
@@ -643,7 +704,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         l_run += sum;
         laps.lap(11);
         tc_fence_before();
-        mbar_arrive(&bars[P_READY + wg]);
+        warp_arrive(&bars[P_READY + wg], lane);
         laps.lap(12);
       }
     }
@@ -698,9 +759,10 @@ constexpr size_t SMEM_LIMIT = 232448;  // 227 KB per CTA
 long long* g_profile = nullptr;
 
 template <int D>
-int launch(const CUtensorMap maps[3], Params& p, cudaStream_t stream) {
+int launch(const CUtensorMap maps[5], Params& p, cudaStream_t stream) {
   using L = Layout<D>;
-  int nw = MAX_NW;
+  int nw = MAX_NW;   // as many decoder-row slots as fit (at least the two staging slots' worth)
+  while (nw > NSTAGE && L::bytes(nw, p.ngroups, p.rank) > SMEM_LIMIT) --nw;
   size_t smem = L::bytes(nw, p.ngroups, p.rank);
   NKV_REQUIRE(smem <= SMEM_LIMIT, NKV_ERR_UNSUPPORTED,
               "codec attention needs %zu bytes of shared memory (rank %d, rank/group %d)", smem,
@@ -724,7 +786,7 @@ int launch(const CUtensorMap maps[3], Params& p, cudaStream_t stream) {
   attr.val.clusterDim.z = 1;
   config.attrs = &attr;
   config.numAttrs = 1;
-  NKV_CUDA(cudaLaunchKernelEx(&config, kernel, maps[0], maps[1], maps[2], p));
+  NKV_CUDA(cudaLaunchKernelEx(&config, kernel, maps[0], maps[1], maps[2], maps[3], maps[4], p));
   return NKV_OK;
 }
 
@@ -763,12 +825,12 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
     NKV_LAUNCH_CHECK("fill_empty_kernel");
     return NKV_OK;
   }
-  CUtensorMap maps[3];
+  CUtensorMap maps[5];
   {
     uint64_t dims[3] = {static_cast<uint64_t>(dk), static_cast<uint64_t>(heads), static_cast<uint64_t>(Q)};
     uint64_t strides[2] = {static_cast<uint64_t>(q_stride_head) * 2, static_cast<uint64_t>(q_stride_token) * 2};
     uint32_t box[3] = {64, 1, QT};
-    int rc = encode_tensor_map(&maps[0], 2, q, 3, dims, strides, box, true);
+    int rc = encode_tensor_map(&maps[0], 2, q, 3, dims, strides, box, 128);
     if (rc != NKV_OK) return rc;
   }
   const void* weights[2] = {wk, wv};
@@ -776,12 +838,20 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
     uint64_t dims[2] = {static_cast<uint64_t>(rank), static_cast<uint64_t>(heads) * dk};
     uint64_t strides[1] = {static_cast<uint64_t>(rank) * 2};
     uint32_t box[2] = {64, PART};   // one CTA streams 64 rows of the slice
-    int rc = encode_tensor_map(&maps[1 + w], 2, weights[w], 2, dims, strides, box, true);
+    int rc = encode_tensor_map(&maps[1 + w], 2, weights[w], 2, dims, strides, box, 128);
     if (rc != NKV_OK) return rc;
   }
   NKV_REQUIRE((reinterpret_cast<uintptr_t>(hk.codes) & 15) == 0 &&
                   (reinterpret_cast<uintptr_t>(hv.codes) & 15) == 0 && (rank / 2) % 16 == 0,
               NKV_ERR_INVALID, "code arrays must be 16-byte aligned with 16-byte multiples per token");
+  const void* code_arrays[2] = {hk.codes, hv.codes};
+  for (int w = 0; w < 2; ++w) {   // [N tokens x rank/2 bytes]; a box is 64 bytes of 128 tokens
+    uint64_t dims[2] = {static_cast<uint64_t>(rank / 2), static_cast<uint64_t>(N)};
+    uint64_t strides[1] = {static_cast<uint64_t>(rank / 2)};
+    uint32_t box[2] = {64, TOK};
+    int rc = encode_tensor_map(&maps[3 + w], 1, code_arrays[w], 2, dims, strides, box, 64);
+    if (rc != NKV_OK) return rc;
+  }
   Params p{};
   p.Q = Q; p.heads = heads; p.N = N; p.rank = rank; p.nchunks = rank / CHUNK;
   p.group = group; p.ngroups = rank / group; p.scale_dtype = hk.scale_dtype;

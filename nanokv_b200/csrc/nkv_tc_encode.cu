@@ -364,7 +364,7 @@ int tc_project(const void* x_bf16, const void* centers_bf16, const void* ids, in
   uint64_t dims[2] = {static_cast<uint64_t>(J), static_cast<uint64_t>(r)};
   uint64_t strides[1] = {static_cast<uint64_t>(J) * 2};
   uint32_t box[2] = {64, static_cast<uint32_t>(p.NB)};
-  int rc = encode_tensor_map(&map_b, 2, encoder_bf16, 2, dims, strides, box, true);
+  int rc = encode_tensor_map(&map_b, 2, encoder_bf16, 2, dims, strides, box, 128);
   if (rc != NKV_OK) return rc;
   p.nstages = pick_stages(p.NACC, p.NB, 0);
   size_t smem = smem_bytes(p.NACC, p.NB, 0, p.nstages);
@@ -390,14 +390,14 @@ int tc_assign(const void* x_bf16, const void* centers_bf16, int S, int J, int C,
     uint64_t dims[2] = {static_cast<uint64_t>(J), static_cast<uint64_t>(S)};
     uint64_t strides[1] = {static_cast<uint64_t>(J) * 2};
     uint32_t box[2] = {64, TM};
-    int rc = encode_tensor_map(&map_a, 2, x_bf16, 2, dims, strides, box, true);
+    int rc = encode_tensor_map(&map_a, 2, x_bf16, 2, dims, strides, box, 128);
     if (rc != NKV_OK) return rc;
   }
   {
     uint64_t dims[2] = {static_cast<uint64_t>(J), static_cast<uint64_t>(C)};
     uint64_t strides[1] = {static_cast<uint64_t>(J) * 2};
     uint32_t box[2] = {64, static_cast<uint32_t>(p.NB)};
-    int rc = encode_tensor_map(&map_b, 2, centers_bf16, 2, dims, strides, box, true);
+    int rc = encode_tensor_map(&map_b, 2, centers_bf16, 2, dims, strides, box, 128);
     if (rc != NKV_OK) return rc;
   }
   p.nstages = pick_stages(p.NACC, p.NB, C);
