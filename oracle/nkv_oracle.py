@@ -433,3 +433,41 @@ def hybrid_attention(q_pre, q_native, native_segments, low_segments, reader: dic
             out, lse = merge(out, lse, lifted, ll)
         result.index_copy_(1, head, out)
     return result
+
+
+# ---------------------------------------------------------------- positional restore
+def rope_table(max_len: int, head_dim: int, theta: float = 10000.0) -> torch.Tensor:
+    """complex128 [max_len, head_dim/2] rotation table of the 3-D RoPE: the columns are the
+    temporal, vertical and horizontal bands side by side
+    (wan/modules/model.py:29-36 rope_params, :426-430 the three-band concatenation)."""
+    def band(dim):
+        angles = torch.outer(torch.arange(max_len),
+                             1.0 / torch.pow(theta, torch.arange(0, dim, 2).to(torch.float64).div(dim)))
+        return torch.polar(torch.ones_like(angles), angles)
+    d = head_dim
+    return torch.cat([band(d - 4 * (d // 6)), band(2 * (d // 6)), band(2 * (d // 6))], dim=1)
+
+
+def rope_coordinates(positions: torch.Tensor, frame_seqlen: int, width: int):
+    """absolute token position -> (frame, row, column)
+    (wan/modules/lingbot_v2_cache_runtime.py:64-68)."""
+    positions = positions.long()
+    frame = torch.div(positions, frame_seqlen, rounding_mode="floor")
+    spatial = positions.remainder(frame_seqlen)
+    return frame, torch.div(spatial, width, rounding_mode="floor"), spatial.remainder(width)
+
+
+def rope_by_positions(key: torch.Tensor, positions: torch.Tensor, freqs: torch.Tensor, *,
+                      frame_seqlen: int, width: int) -> torch.Tensor:
+    """key [1,S,H,D] before RoPE -> after, each token rotated by its own absolute position:
+    adjacent element pairs are complex numbers multiplied in float64 by the table row of the
+    token's frame (temporal band), row (vertical band) and column (horizontal band), one
+    rounding back to the key's dtype (wan/modules/lingbot_v2_cache_runtime.py:19-76)."""
+    half = key.shape[-1] // 2
+    split = [half - 2 * (half // 3), half // 3, half // 3]
+    temporal, vertical, horizontal = freqs.split(split, dim=1)
+    frame, row, column = rope_coordinates(positions, frame_seqlen, width)
+    multiplier = torch.cat((temporal.index_select(0, frame), vertical.index_select(0, row),
+                            horizontal.index_select(0, column)), dim=1)[:, None]
+    pairs = torch.view_as_complex(key[0].to(torch.float64).reshape(key.shape[1], key.shape[2], -1, 2))
+    return torch.view_as_real(pairs * multiplier).flatten(2)[None].to(key.dtype)

@@ -96,3 +96,31 @@ def build_merge():
     out_a[0, 0, :4] = 0
     out_b[0, 0, 2:6] = 0
     return out_a, lse_a, out_b, lse_b
+
+
+@dataclasses.dataclass(frozen=True)
+class RopeCase:
+    name: str
+    tokens: int
+    heads: int
+    head_dim: int
+    height: int
+    width: int
+    dtype: torch.dtype
+
+
+ROPE_CASES = (RopeCase("rope_d128_bf16", 112, 3, 128, 6, 8, torch.bfloat16),
+              RopeCase("rope_d64_f32", 60, 2, 64, 5, 4, torch.float32))
+
+
+def build_rope(case: RopeCase) -> dict:
+    """Pre-RoPE keys and the absolute positions of a rolling cache: a sink run from position 0,
+    then a recent run far from it (not one contiguous interval)."""
+    gen = synthetic.generator(777 + case.head_dim)
+    key = torch.randn(1, case.tokens, case.heads, case.head_dim, generator=gen).to(case.dtype)
+    frame_seqlen = case.height * case.width
+    sink = case.tokens // 3
+    recent_start = 19 * frame_seqlen + 5
+    positions = torch.cat([torch.arange(sink), torch.arange(recent_start, recent_start + case.tokens - sink)])
+    return {"key": key, "positions": positions, "frame_seqlen": frame_seqlen,
+            "grid_sizes": torch.tensor([[32, case.height, case.width]])}

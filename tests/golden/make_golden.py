@@ -158,19 +158,55 @@ def run_merge_case(root) -> dict:
     return {"out": bits(out), "lse": lse.numpy()}
 
 
+def reference_rope_params(root):
+    """The reference's ``rope_params`` (wan/modules/model.py), taken out of its module by name and
+    executed as is: the module itself imports packages that are not installed here."""
+    import ast
+    path = root / ref_import.LB / "wan/modules/model.py"
+    tree = ast.parse(path.read_text())
+    node = next(n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == "rope_params")
+    scope = {"torch": torch}
+    exec(compile(ast.Module(body=[node], type_ignores=[]), str(path), "exec"), scope)
+    return scope["rope_params"]
+
+
+def run_rope_case(case: cases.RopeCase, root) -> dict:
+    ref_import.load_lingbot_codec(root)
+    runtime = ref_import._load("wan.modules.lingbot_v2_cache_runtime",
+                               root / ref_import.LB / "wan/modules/lingbot_v2_cache_runtime.py")
+    rope_params = reference_rope_params(root)
+    d = case.head_dim
+    freqs = torch.cat([rope_params(1024, d - 4 * (d // 6)), rope_params(1024, 2 * (d // 6)),
+                       rope_params(1024, 2 * (d // 6))], dim=1)   # model.py:426-430
+    data = cases.build_rope(case)
+    os.environ["LINGBOT_PRE_ROPE_TRITON"] = "0"
+    out = runtime.rope_pre_key_by_positions(data["key"], data["positions"],
+                                            grid_sizes=data["grid_sizes"], freqs=freqs,
+                                            frame_seqlen=data["frame_seqlen"])
+    return {"rotated": bits(out), "freqs_head": torch.view_as_real(freqs[:64]).numpy(),   # rows in use
+            "freqs_digest": np.array([checksum(torch.view_as_real(freqs).contiguous())], dtype=np.uint64),
+            "key_digest": np.array([checksum(data["key"])], dtype=np.uint64)}
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--reference", default=None)
+    parser.add_argument("--only", default="", help="regenerate only fixtures whose name starts with this")
     args = parser.parse_args()
+    global save
+    write = save
+    save = lambda name, arrays: write(name, arrays()) if name.startswith(args.only) else None
     root = ref_import.reference_root(args.reference)
     torch.set_num_threads(1)  # one thread: bit-stable reductions in the stored outputs
     for case in cases.MG_CASES:
-        save(case.name, run_mg_case(case, root))
+        save(case.name, lambda: run_mg_case(case, root))
     for case in cases.LINGBOT_CASES:
-        save(case.name, run_lingbot_case(case, root))
+        save(case.name, lambda: run_lingbot_case(case, root))
     for case in cases.FAST_CASES:
-        save(case.name, run_fast_case(case, root))
-    save("merge_edge", run_merge_case(root))
+        save(case.name, lambda: run_fast_case(case, root))
+    save("merge_edge", lambda: run_merge_case(root))
+    for case in cases.ROPE_CASES:
+        save(case.name, lambda: run_rope_case(case, root))
 
 
 if __name__ == "__main__":

@@ -136,3 +136,18 @@ def test_pack_roundtrip_and_nibble_order():
     packed, count = oracle.pack_int4(codes)
     assert packed.tolist() == [0 | (14 << 4), 7 | (10 << 4), 8 | (6 << 4), 13 | (1 << 4)]
     assert torch.equal(oracle.unpack_int4(packed, count, codes.shape), codes)
+
+
+@pytest.mark.parametrize("case", cases.ROPE_CASES, ids=lambda c: c.name)
+def test_rope_by_positions(case):
+    gold = load(case.name)
+    data = cases.build_rope(case)
+    assert int(gold["key_digest"][0]) == checksum(data["key"]), "input generator drifted"
+    freqs = oracle.rope_table(1024, case.head_dim)
+    assert np.array_equal(gold["freqs_head"], torch.view_as_real(freqs[:64]).numpy()), "rotation table"
+    assert int(gold["freqs_digest"][0]) == checksum(torch.view_as_real(freqs).contiguous())
+    got = oracle.rope_by_positions(data["key"], data["positions"], freqs,
+                                   frame_seqlen=data["frame_seqlen"], width=case.width)
+    want = from_bits(gold["rotated"], case.dtype)
+    assert torch.equal(got.view(torch.int16) if case.dtype == torch.bfloat16 else got, 
+                       want.view(torch.int16) if case.dtype == torch.bfloat16 else want)
