@@ -95,6 +95,16 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------- workload
+def rope_freqs(rows: int, head_dim: int, theta: float = 10000.0) -> torch.Tensor:
+    """complex128 [rows, head_dim/2]: temporal, vertical and horizontal bands side by side."""
+    def band(dim):
+        angles = torch.outer(torch.arange(rows),
+                             1.0 / torch.pow(theta, torch.arange(0, dim, 2).to(torch.float64).div(dim)))
+        return torch.polar(torch.ones_like(angles), angles)
+    d = head_dim
+    return torch.cat([band(d - 4 * (d // 6)), band(2 * (d // 6)), band(2 * (d // 6))], dim=1)
+
+
 def build_layers(shape, frames: range, layers: int, device, encode_frames: int = 8):
     """Encode this rank's frames of every layer into compressed histories (fixed centres).
 
@@ -206,6 +216,13 @@ def run_ours(args) -> dict:
     out_host = torch.empty(shape.queries, shape.heads, shape.head_dim, dtype=torch.bfloat16).pin_memory()
     lse_host = torch.empty(shape.queries, shape.heads, dtype=torch.float32).pin_memory()
     status = torch.zeros(1, dtype=torch.int32, device=device)
+    rope_args = {}
+    if args.rope:   # positional restore inside the read: 30 x 52 token frames, this rank's positions
+        table = attention.RopeTable(rope_freqs(1024, shape.head_dim), frame_seqlen=FRAME, width=52,
+                                    device=device)
+        start = frames.start * FRAME
+        rope_args = dict(rope=table, positions=torch.arange(start, start + local_tokens,
+                                                            dtype=torch.int32, device=device))
     exchange = None
     if world > 1 and args.exchange == "peer":
         exchange = context_parallel.PeerExchange(shape.queries, shape.heads, shape.head_dim,
@@ -213,7 +230,7 @@ def run_ours(args) -> dict:
         # the fused exchange must reproduce all-gather + merge bit for bit on this workload
         (hk, ok), (hv, ov) = built[0]["k"], built[0]["v"]
         attention.codec_attention(q_dev, hk, hv, ok, ov, status=status, out=exchange.partial_out,
-                                  lse=exchange.partial_lse)
+                                  lse=exchange.partial_lse, **rope_args)
         fused_out, fused_lse = exchange.merge()
         plain_out, plain_lse = context_parallel.gather_and_merge(exchange.partial_out.clone(),
                                                                  exchange.partial_lse.clone())
@@ -246,11 +263,11 @@ def run_ours(args) -> dict:
             q = queries_from_host() if host_io else q_dev
             (hk, ok), (hv, ov) = entry["k"], entry["v"]
             if exchange is not None:
-                attention.codec_attention(q, hk, hv, ok, ov, status=status,
+                attention.codec_attention(q, hk, hv, ok, ov, status=status, **rope_args,
                                           out=exchange.partial_out, lse=exchange.partial_lse)
                 merged = exchange.merge()
             else:
-                out, lse = attention.codec_attention(q, hk, hv, ok, ov, status=status)
+                out, lse = attention.codec_attention(q, hk, hv, ok, ov, status=status, **rope_args)
                 merged = context_parallel.gather_and_merge(out, lse)
             if host_io:
                 out_host.view(rows, -1)[row_lo:row_hi].copy_(
@@ -298,7 +315,7 @@ def run_ours(args) -> dict:
         (hk, ok), (hv, ov) = other["k"], other["v"]
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        attention.codec_attention(q_dev, hk, hv, ok, ov, status=status)
+        attention.codec_attention(q_dev, hk, hv, ok, ov, status=status, **rope_args)
         stop.record()
         torch.cuda.synchronize()
         if index >= 3:
@@ -353,6 +370,7 @@ def run_ours(args) -> dict:
                    "rank": shape.rank, "centers": shape.centers, "history_tokens": shape.history,
                    "queries": shape.queries, "layers": layers, "quant_group": shape.rank,
                    "scale_dtype": "bf16", "parallelism": f"cp{world}",
+                   "positional_restore": "3-D RoPE of the rebuilt keys inside the read" if args.rope else "none",
                    "exchange": ("none" if world == 1 else
                                 "peer-memory merge + all-gather kernel" if exchange is not None else
                                 "nccl all-gather + merge kernel"),
@@ -581,6 +599,8 @@ def main() -> None:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--layers", type=int, default=SHAPE.layers)
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    parser.add_argument("--rope", action="store_true",
+                        help="rotate the rebuilt keys by absolute position inside the read (3-D RoPE)")
     parser.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                         help="context-parallel exchange: fused peer-memory kernel, or NCCL all-gather + merge")
     parser.add_argument("--workload", default="c3_wan_shaped",

@@ -232,6 +232,45 @@ int nkv_attn_codec_split(const void* q, int dtype, int64_t q_stride_token, int64
                          int splits, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Positional restore of the reconstructed keys inside the read: 3-D RoPE by
+ * the absolute position of every history token.  A rolling cache is "sink +
+ * recent", not one contiguous interval, so positions travel with the tokens.
+ * position -> frame = pos / frame_seqlen, row = (pos % frame_seqlen) / width,
+ * column = (pos % frame_seqlen) % width; of the head_dim/2 adjacent-element
+ * pairs of a key row, the first half - 2*(half/3) are rotated by the table
+ * row of the frame, the next half/3 by that of the row, the last half/3 by
+ * that of the column (half = head_dim/2).  The reference multiplies in complex
+ * float64 and rounds once to the key dtype; here the table holds f32 (cos, sin)
+ * and the rotation runs in fp32 on the twice-rounded key, then rounds once.
+ * Coordinates beyond table_rows - 1 are clamped.
+ * Reference: rope_pre_key_by_positions
+ * models/LingBot-World-2.0/fast/wan/modules/lingbot_v2_cache_runtime.py:19-76
+ * (fused form codec_native_rope_triton.py:10-46); table rope_params
+ * wan/modules/model.py:29-36, bands :426-430.
+ */
+typedef struct nkv_rope {
+  const int32_t* positions;  /* [history tokens] absolute token positions (device) */
+  const float* cos_sin;      /* [table_rows][head_dim/2][2] (cos, sin) (device) */
+  int32_t table_rows;
+  int32_t frame_seqlen;      /* tokens per frame = height * width */
+  int32_t width;
+} nkv_rope;
+
+/*
+ * nkv_attn_codec_split with the keys rotated as above before Q K^T (queries
+ * arrive already rotated, as at the reference call site
+ * wan/modules/codec_native_attention.py:713-716).  rope == NULL is
+ * nkv_attn_codec_split.
+ */
+int nkv_attn_codec_rope(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head,
+                        int Q, int heads, int dk, int dv,
+                        const nkv_history* hist_k, const nkv_history* hist_v,
+                        const void* wk, const float* bias_k, const void* wv, const float* bias_v,
+                        const nkv_rope* rope, float scale, void* out, float* lse,
+                        int32_t* status_word, int splits, void* workspace, size_t workspace_bytes,
+                        void* stream);
+
+/*
  * Plain attention with LSE over K / V rows that are already full width (the
  * protected / current-chunk partition): O = softmax(q K^T * scale) V.
  * Reference: attention_lse, MGC/core.py:45-72;

@@ -10,6 +10,13 @@ from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t
 
 from . import build as _build
 
+
+class Rope(ctypes.Structure):
+    """struct nkv_rope"""
+    _fields_ = [("positions", c_void_p), ("cos_sin", c_void_p), ("table_rows", c_int32),
+                ("frame_seqlen", c_int32), ("width", c_int32)]
+
+
 NKV_OK = 0
 NKV_ERR_INVALID, NKV_ERR_CUDA, NKV_ERR_UNSUPPORTED, NKV_ERR_DEVICE_WAIT, NKV_ERR_TOO_LARGE = (
     -1, -2, -3, -4, -5)
@@ -58,6 +65,10 @@ SIGNATURES = {
                                      POINTER(History), POINTER(History), c_void_p, c_void_p,
                                      c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
                                      c_int, c_void_p, c_size_t, c_void_p]),
+    "nkv_attn_codec_rope": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int,
+                                    POINTER(History), POINTER(History), c_void_p, c_void_p,
+                                    c_void_p, c_void_p, POINTER(Rope), c_float, c_void_p, c_void_p,
+                                    c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
     "nkv_attention_lse": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64,
                                   c_int64, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                                   c_void_p, c_void_p]),

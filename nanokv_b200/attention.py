@@ -18,13 +18,16 @@ def _view(hist) -> HistoryView:
 def codec_attention(q: torch.Tensor, hist_k, hist_v, op_k: Operator, op_v: Operator, *,
                     scale: float | None = None, status: torch.Tensor | None = None,
                     splits: int | None = None, out: torch.Tensor | None = None,
-                    lse: torch.Tensor | None = None):
+                    lse: torch.Tensor | None = None, rope: "RopeTable | None" = None,
+                    positions: torch.Tensor | None = None):
     """Full-dimensional read: q [Q,H,D] -> (O [Q,H,D], lse f32 [Q,H]).
 
     K and V of every history token are rebuilt on chip from codes, scales, the
     decoder slice of each head and the token's centre; nothing full-width is
     written to HBM.  Replaces decode + attention of the reference
-    (MGM/nanokv_codec.py:393-455 + MGC/core.py:45-72).
+    (MGM/nanokv_codec.py:393-455 + MGC/core.py:45-72).  With ``rope`` and the history tokens'
+    absolute ``positions`` the rebuilt keys are rotated inside the kernel, which also replaces
+    rope_pre_key_by_positions (LB/lingbot_v2_cache_runtime.py:19-76); q arrives rotated.
     """
     Q, H, D = q.shape
     if H * D != op_k.joint:
@@ -32,9 +35,34 @@ def codec_attention(q: torch.Tensor, hist_k, hist_v, op_k: Operator, op_v: Opera
     scale = D ** -0.5 if scale is None else scale
     wk = op_k.decoder.view(H, D, op_k.rank)
     wv = op_v.decoder.view(H, D, op_v.rank)
+    rope_view = None
+    if rope is not None:
+        if positions is None:
+            raise ValueError("RoPE needs the absolute positions of the history tokens")
+        if positions.dim() != 1 or positions.numel() != _view(hist_k).tokens:
+            raise ValueError("RoPE position/K length mismatch")
+        rope_view = rope.view(positions)
     return ops.attn_codec(q, _view(hist_k), _view(hist_v), wk, op_k.bias.view(H, D), wv,
                           op_v.bias.view(H, D), scale=scale, status=status, splits=splits,
-                          out=out, lse=lse)
+                          out=out, lse=lse, rope=rope_view)
+
+
+class RopeTable:
+    """Device-resident rotation table of the 3-D RoPE: (cos, sin) in fp32 of the reference's
+    complex128 ``freqs`` [rows, head_dim/2] (LB/model.py:29-36, :426-430), with the frame grid
+    that maps a token position to (frame, row, column)."""
+
+    def __init__(self, freqs: torch.Tensor, *, frame_seqlen: int, width: int, device="cuda"):
+        if not freqs.is_complex() or freqs.dim() != 2:
+            raise ValueError("freqs must be a complex [rows, head_dim/2] tensor")
+        if frame_seqlen <= 0 or width <= 0 or frame_seqlen % width:
+            raise ValueError(f"frame_seqlen mismatch: width {width} does not divide {frame_seqlen}")
+        self.cos_sin = torch.view_as_real(freqs).to(device=device, dtype=torch.float32).contiguous()
+        self.frame_seqlen, self.width = int(frame_seqlen), int(width)
+
+    def view(self, positions: torch.Tensor) -> "ops.RopeView":
+        positions = positions.to(device=self.cos_sin.device, dtype=torch.int32).contiguous()
+        return ops.RopeView(positions, self.cos_sin, self.frame_seqlen, self.width)
 
 
 def merge(out_a, lse_a, out_b, lse_b):

@@ -234,12 +234,12 @@ size_t nkv_attn_codec_workspace_bytes(int Q, int heads, int dv, int splits) {
   return static_cast<size_t>(splits) * Q * heads * (static_cast<size_t>(dv) * 2 + 4);
 }
 
-int nkv_attn_codec_split(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head,
-                         int Q, int heads, int dk, int dv, const nkv_history* hist_k,
-                         const nkv_history* hist_v, const void* wk, const float* bias_k,
-                         const void* wv, const float* bias_v, float scale, void* out, float* lse,
-                         int32_t* status_word, int splits, void* workspace, size_t workspace_bytes,
-                         void* stream) {
+int nkv_attn_codec_rope(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head,
+                        int Q, int heads, int dk, int dv, const nkv_history* hist_k,
+                        const nkv_history* hist_v, const void* wk, const float* bias_k,
+                        const void* wv, const float* bias_v, const nkv_rope* rope, float scale,
+                        void* out, float* lse, int32_t* status_word, int splits, void* workspace,
+                        size_t workspace_bytes, void* stream) {
   int rc = check_history(hist_k, "K");
   if (rc != NKV_OK) return rc;
   rc = check_history(hist_v, "V");
@@ -253,12 +253,35 @@ int nkv_attn_codec_split(const void* q, int dtype, int64_t q_stride_token, int64
   NKV_REQUIRE(workspace_bytes >= nkv_attn_codec_workspace_bytes(Q, heads, dv, splits),
               NKV_ERR_INVALID, "attn_codec: workspace of %zu bytes is too small for %d splits",
               workspace_bytes, splits);
+  if (rope != nullptr) {
+    NKV_REQUIRE(rope->cos_sin != nullptr && rope->table_rows > 0 && rope->frame_seqlen > 0 &&
+                    rope->width > 0 && rope->frame_seqlen % rope->width == 0,
+                NKV_ERR_INVALID, "rope: table_rows=%d frame_seqlen=%d width=%d", rope->table_rows,
+                rope->frame_seqlen, rope->width);
+    NKV_REQUIRE(rope->positions != nullptr || hist_k->tokens == 0, NKV_ERR_INVALID,
+                "rope: positions are NULL");
+    NKV_REQUIRE(dk % 4 == 0 && (reinterpret_cast<uintptr_t>(rope->cos_sin) & 7) == 0,
+                NKV_ERR_INVALID, "rope: head width %d / table alignment", dk);
+  }
   auto s = static_cast<cudaStream_t>(stream);
   if (dtype == NKV_BF16 && !simt_forced())
     return tc_attn_codec(q, q_stride_token, q_stride_head, Q, heads, dk, dv, hist_k, hist_v, wk,
-                         bias_k, wv, bias_v, scale, out, lse, status_word, splits, workspace, s);
+                         bias_k, wv, bias_v, scale, out, lse, status_word, splits, workspace, s,
+                         rope);
   return simt_attn(q, dtype, q_stride_token, q_stride_head, Q, heads, dk, dv, hist_k, hist_v, wk,
-                   bias_k, wv, bias_v, nullptr, nullptr, 0, 0, hist_k->tokens, scale, out, lse, s);
+                   bias_k, wv, bias_v, nullptr, nullptr, 0, 0, hist_k->tokens, scale, out, lse, s,
+                   rope);
+}
+
+int nkv_attn_codec_split(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head,
+                         int Q, int heads, int dk, int dv, const nkv_history* hist_k,
+                         const nkv_history* hist_v, const void* wk, const float* bias_k,
+                         const void* wv, const float* bias_v, float scale, void* out, float* lse,
+                         int32_t* status_word, int splits, void* workspace, size_t workspace_bytes,
+                         void* stream) {
+  return nkv_attn_codec_rope(q, dtype, q_stride_token, q_stride_head, Q, heads, dk, dv, hist_k,
+                             hist_v, wk, bias_k, wv, bias_v, nullptr, scale, out, lse, status_word,
+                             splits, workspace, workspace_bytes, stream);
 }
 
 int nkv_attn_codec(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head, int Q,

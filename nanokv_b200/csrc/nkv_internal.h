@@ -20,7 +20,7 @@ int simt_attn(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride
               const void* wk, const float* bias_k, const void* wv, const float* bias_v,
               const void* k_plain, const void* v_plain, int64_t kv_stride_token,
               int64_t kv_stride_head, int N, float scale, void* out, float* lse,
-              cudaStream_t stream);
+              cudaStream_t stream, const nkv_rope* rope = nullptr);
 int kmeans_gather_init(const void* x, int x_dtype, int J, int C, const int32_t* init_rows,
                        float* centers, cudaStream_t stream);
 int kmeans_update(const void* x, int x_dtype, int S, int J, int C, const int32_t* labels,
@@ -48,7 +48,8 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
                   int heads, int dk, int dv, const nkv_history* hist_k,
                   const nkv_history* hist_v, const void* wk, const float* bias_k,
                   const void* wv, const float* bias_v, float scale, void* out, float* lse,
-                  int32_t* status_word, int splits, void* workspace, cudaStream_t stream);
+                  int32_t* status_word, int splits, void* workspace, cudaStream_t stream,
+                  const nkv_rope* rope = nullptr);
 bool tc_attn_supported(int dk, int dv, int rank);
 void tc_attn_set_profile(long long* device_buckets);
 bool tc_project_supported(int J, int r);

@@ -231,6 +231,7 @@ struct AttnArgs {
   const void* wk; const float* bias_k; const void* wv; const float* bias_v;
   const void* k_plain; const void* v_plain; int64_t kv_stride_token, kv_stride_head;
   void* out; float* lse;
+  nkv_rope rope;   // cos_sin == nullptr: no positional restore
 };
 
 template <int DK, int DV, bool CODEC>
@@ -296,12 +297,12 @@ attn_kernel(AttnArgs a) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             int m = ty * 4 + i;
+            float vals[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               int c = n0 + tx * 4 + j;
-              if (c >= D) continue;
               float v = 0.f;
-              if (t0 + m < a.N) {
+              if (c < D && t0 + m < a.N) {
                 float center = bf16_bits_to_float(
                     centers[static_cast<size_t>(crow[m]) * h.center_width +
                             static_cast<size_t>(head) * D + c]);
@@ -313,7 +314,32 @@ attn_kernel(AttnArgs a) {
                   v = __fadd_rn(__fadd_rn(acc[i][j], b), center);
                 }
               }
-              if (which == 0) Ks[c * 64 + m] = v; else Vs[m * DV + c] = v;
+              vals[j] = v;
+            }
+            if (which == 0 && a.rope.cos_sin != nullptr && t0 + m < a.N) {
+              // rotate the adjacent pairs (c, c+1) by the token's frame / row / column
+              const int half = D / 2, third = half / 3, band_a = half - 2 * third, band_b = band_a + third;
+              const int pos = max(a.rope.positions[t0 + m], 0);
+              const int frame = pos / a.rope.frame_seqlen, spatial = pos - frame * a.rope.frame_seqlen;
+              const int prow = spatial / a.rope.width, pcol = spatial - prow * a.rope.width;
+#pragma unroll
+              for (int pr = 0; pr < 2; ++pr) {
+                const int pg = (n0 + tx * 4) / 2 + pr;
+                if (pg >= half) continue;
+                int coord = pg < band_a ? frame : (pg < band_b ? prow : pcol);
+                coord = min(coord, a.rope.table_rows - 1);
+                const float2 cs = reinterpret_cast<const float2*>(a.rope.cos_sin)[static_cast<size_t>(coord) * half + pg];
+                const float x0 = vals[2 * pr], x1 = vals[2 * pr + 1];
+                float y0 = fmaf(x0, cs.x, -(x1 * cs.y)), y1 = fmaf(x0, cs.y, x1 * cs.x);
+                vals[2 * pr] = bf16 ? round_to_bf16(y0) : y0;
+                vals[2 * pr + 1] = bf16 ? round_to_bf16(y1) : y1;
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              int c = n0 + tx * 4 + j;
+              if (c >= D) continue;
+              if (which == 0) Ks[c * 64 + m] = vals[j]; else Vs[m * DV + c] = vals[j];
             }
           }
         }
@@ -509,9 +535,10 @@ int simt_attn(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride
               const void* wk, const float* bias_k, const void* wv, const float* bias_v,
               const void* k_plain, const void* v_plain, int64_t kv_stride_token,
               int64_t kv_stride_head, int N, float scale, void* out, float* lse,
-              cudaStream_t stream) {
+              cudaStream_t stream, const nkv_rope* rope) {
   if (Q == 0 || heads == 0) return NKV_OK;
   AttnArgs a{};
+  if (rope != nullptr) a.rope = *rope;
   a.q = q; a.dtype = dtype; a.q_stride_token = q_stride_token; a.q_stride_head = q_stride_head;
   a.Q = Q; a.heads = heads; a.N = N; a.scale = scale;
   const bool codec = hist_k != nullptr;

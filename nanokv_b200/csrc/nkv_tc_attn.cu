@@ -74,6 +74,7 @@ struct Params {
   uint16_t* out;
   float* lse;
   int32_t* status;
+  nkv_rope rope;     // cos_sin == nullptr: keys are used as rebuilt
   long long* prof;   // optional: cycle buckets of CTA (0,0), see nkv_debug_attn_profile
 };
 
@@ -560,6 +561,18 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           cen[i] = __ldg(reinterpret_cast<const uint4*>(
               cbase + static_cast<size_t>(crow_i) * hist.center_width + piece * 8));
         }
+        // positional restore (K parts only): this token's frame / row / column
+        const bool rotate = tensor == 0 && p.rope.cos_sin != nullptr;
+        int coord_t = 0, coord_h = 0, coord_w = 0;
+        if (rotate) {
+          const int pos = in ? max(__ldg(p.rope.positions + t0 + row), 0) : 0;
+          const int last = p.rope.table_rows - 1;
+          const int frame = pos / p.rope.frame_seqlen, spatial = pos - frame * p.rope.frame_seqlen;
+          const int prow = spatial / p.rope.width;
+          coord_t = min(frame, last);
+          coord_h = min(prow, last);
+          coord_w = min(spatial - prow * p.rope.width, last);
+        }
         laps.lap(6);
         // accumulator complete: the tile's last pair is pair g - 1
         ok = mbar_wait(&bars[PAIR_DONE + ((g - 1) & (NDONE - 1))], ((g - 1) / NDONE) & 1, abort_flag, 330);
@@ -597,6 +610,16 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
             float x1 = round_to_bf16(v[j + 1] + bias[wg * 32 + j + 1]);
             x0 += __uint_as_float(cwords[w] << 16);
             x1 += __uint_as_float(cwords[w] & 0xFFFF0000u);
+            if (rotate) {   // the pair (x0, x1) of the rebuilt bf16 key is one complex number
+              constexpr int HALF = D / 2, THIRD = HALF / 3, BAND_A = HALF - 2 * THIRD, BAND_B = BAND_A + THIRD;
+              const int pg = part * (PART / 2) + wg * 16 + (j >> 1);
+              const int coord = pg < BAND_A ? coord_t : (pg < BAND_B ? coord_h : coord_w);
+              const float2 cs = __ldg(reinterpret_cast<const float2*>(p.rope.cos_sin) +
+                                      static_cast<size_t>(coord) * HALF + pg);
+              const float k0 = round_to_bf16(x0), k1 = round_to_bf16(x1);
+              x0 = fmaf(k0, cs.x, -(k1 * cs.y));
+              x1 = fmaf(k0, cs.y, k1 * cs.x);
+            }
             packed[j4 * 4 + w] = in ? pack_bf16x2(x0, x1) : 0u;
           }
         }
@@ -804,7 +827,7 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
                   int dk, int dv, const nkv_history* hist_k, const nkv_history* hist_v,
                   const void* wk, const float* bias_k, const void* wv, const float* bias_v,
                   float scale, void* out, float* lse, int32_t* status_word, int splits,
-                  void* workspace, cudaStream_t stream) {
+                  void* workspace, cudaStream_t stream, const nkv_rope* rope) {
   const nkv_history& hk = *hist_k;
   const nkv_history& hv = *hist_v;
   const int N = hk.tokens, rank = hk.rank, group = hk.group;
@@ -858,6 +881,7 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.hk = hk; p.hv = hv; p.bias_k = bias_k; p.bias_v = bias_v;
   p.status = status_word;
+  if (rope != nullptr) p.rope = *rope;
   // History splits: each grid.z slice attends a contiguous run of tiles and writes a partial
   // (O, lse); the partials are merged by log-sum-exp.  Evens out the rounds of resident clusters.
   const int tiles = ceil_div(N, TOK);

@@ -162,12 +162,14 @@ def default_splits(tokens: int) -> int:
 
 def attn_codec(q, view_k: HistoryView, view_v: HistoryView, wk, bias_k, wv, bias_v, *,
                scale: float, status: torch.Tensor | None = None, splits: int | None = None,
-               out: torch.Tensor | None = None, lse: torch.Tensor | None = None):
+               out: torch.Tensor | None = None, lse: torch.Tensor | None = None,
+               rope: "RopeView | None" = None):
     """Fused read: q [Q,H,dk] -> (O [Q,H,dv], lse f32 [Q,H]).
 
     wk [H,dk,r], wv [H,dv,r] in q's dtype; bias f32 [H,dk] / [H,dv].  ``splits`` cuts the
     history into that many runs attended in one launch and merged by LSE (None: automatic).
     ``out`` / ``lse`` name contiguous result buffers to fill (e.g. peer-visible ones).
+    ``rope`` rotates the rebuilt keys by the absolute position of every history token.
     """
     device = _require_cuda(wk, bias_k, wv, bias_v, status)
     if not q.is_cuda:
@@ -190,11 +192,37 @@ def attn_codec(q, view_k: HistoryView, view_v: HistoryView, wk, bias_k, wv, bias
         splits = default_splits(view_k.tokens) if q.dtype == torch.bfloat16 else 1
     nbytes = lib.nkv_attn_codec_workspace_bytes(Q, H, dv, splits)
     workspace = torch.empty(nbytes, dtype=torch.uint8, device=device) if nbytes else None
-    _lib.check(lib.nkv_attn_codec_split(
+    rope_struct = None
+    if rope is not None:
+        if rope.positions.numel() < view_k.tokens:
+            raise ValueError("RoPE position/K length mismatch")
+        if rope.cos_sin.shape[1] != dk // 2:
+            raise ValueError("rotation table width does not match the head width")
+        rope_struct = ctypes.byref(rope.struct())
+    _lib.check(lib.nkv_attn_codec_rope(
         _ptr(q), dtype_code(q.dtype), q.stride(0), q.stride(1), Q, H, dk, dv, ctypes.byref(sk),
-        ctypes.byref(sv), _ptr(wk), _ptr(bias_k), _ptr(wv), _ptr(bias_v), float(scale), _ptr(out),
-        _ptr(lse), _ptr(status), splits, _ptr(workspace), nbytes, _stream(device)))
+        ctypes.byref(sv), _ptr(wk), _ptr(bias_k), _ptr(wv), _ptr(bias_v), rope_struct, float(scale),
+        _ptr(out), _ptr(lse), _ptr(status), splits, _ptr(workspace), nbytes, _stream(device)))
     return out, lse
+
+
+class RopeView:
+    """struct nkv_rope over device tensors: positions i32 [tokens], cos_sin f32 [rows, D/2, 2]."""
+
+    def __init__(self, positions: torch.Tensor, cos_sin: torch.Tensor, frame_seqlen: int, width: int):
+        _require_cuda(positions, cos_sin)
+        if positions.dtype != torch.int32 or cos_sin.dtype != torch.float32:
+            raise ValueError("positions must be int32 and the rotation table float32")
+        if cos_sin.dim() != 3 or cos_sin.shape[2] != 2:
+            raise ValueError("rotation table must be [rows, head_dim/2, 2]")
+        if frame_seqlen <= 0 or width <= 0 or frame_seqlen % width:
+            raise ValueError(f"frame_seqlen mismatch: width {width} does not divide {frame_seqlen}")
+        self.positions, self.cos_sin = positions, cos_sin
+        self.frame_seqlen, self.width = int(frame_seqlen), int(width)
+
+    def struct(self) -> "_lib.Rope":
+        return _lib.Rope(self.positions.data_ptr(), self.cos_sin.data_ptr(), int(self.cos_sin.shape[0]),
+                         self.frame_seqlen, self.width)
 
 
 def attention_lse(q, k, v, *, scale: float):

@@ -352,8 +352,11 @@ def merge_many(partials):
 
 
 def codec_attention(q, k_segments, v_segments, *, k_decoder, k_mean, v_decoder, v_mean,
-                    heads: int, dtype: torch.dtype, scale=None):
-    """Full-dimensional read: decode every segment, concatenate, attend.
+                    heads: int, dtype: torch.dtype, scale=None, rope=None):
+    """Full-dimensional read: decode every segment, concatenate, (rotate the keys,) attend.
+
+    ``rope`` = dict(positions, freqs, frame_seqlen, width): the decoded keys are rotated by
+    ``rope_by_positions`` before the attention, as LB/codec_native_attention.py:713-716 does.
 
     q [B,Q,H,D]; segments as produced by ``encode_rows``.  Read path
     MGM/nanokv_codec.py:393-455 (decode) + MGC/core.py:45-72 (attention).
@@ -363,7 +366,11 @@ def codec_attention(q, k_segments, v_segments, *, k_decoder, k_mean, v_decoder, 
     keys = [decode_rows(s, decoder=k_decoder, mean=k_mean, dtype=dtype) for s in k_segments]
     values = [decode_rows(s, decoder=v_decoder, mean=v_mean, dtype=dtype) for s in v_segments]
     if keys:
-        key = torch.cat(keys, 1).reshape(batch, -1, heads, head_dim).permute(0, 2, 1, 3)
+        key = torch.cat(keys, 1).reshape(batch, -1, heads, head_dim)
+        if rope is not None:
+            key = rope_by_positions(key, rope["positions"], rope["freqs"],
+                                    frame_seqlen=rope["frame_seqlen"], width=rope["width"])
+        key = key.permute(0, 2, 1, 3)
         value = torch.cat(values, 1).reshape(batch, -1, heads, head_dim).permute(0, 2, 1, 3)
     else:
         key = q.new_zeros(batch, heads, 0, head_dim)
