@@ -169,7 +169,16 @@ __device__ __forceinline__ uint32_t staging_col(int s) { return s == 0 ? 64 : (s
 
 // Lap timer of one thread: adds the cycles since the previous lap to a bucket kept in registers;
 // flush() adds the buckets to global memory once, at the end.
+// The PROF = false specialisation is empty, so the production kernel carries no timers.
+template <bool PROF>
 struct Laps {
+  __device__ __forceinline__ void start(long long*, bool) {}
+  __device__ __forceinline__ void lap(int) {}
+  __device__ __forceinline__ void flush() {}
+};
+
+template <>
+struct Laps<true> {
   long long* out;
   unsigned last;
   unsigned acc[13];
@@ -196,7 +205,7 @@ struct Laps {
   }
 };
 
-template <int D>
+template <int D, bool ROPE, bool PROF>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
                   const __grid_constant__ CUtensorMap map_wk,
@@ -324,7 +333,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       const uint32_t idesc_pv = make_idesc_bf16(128, D);      // [128 q] x [D]
       const uint32_t smem_base = smem_u32(smem);
       const uint16_t all_ctas = static_cast<uint16_t>((1u << CL) - 1);
-      Laps laps;
+      Laps<PROF> laps;
       laps.start(p.prof + 16, leader && p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0);
       bool ok = nq > 0 ? mbar_wait(&bars[Q_FULL], 0, abort_flag, 200) : true;
       int slot = 0, use = 0, g = 0;   // decoder-row ring position; running pair number
@@ -457,7 +466,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
     int g = 0;   // running pair number over all tiles
-    Laps laps;
+    Laps<PROF> laps;
     laps.start(p.prof, p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0);
     for (int it = 0; it < ntiles && ok; ++it) {
       const int t0 = (tile0 + it) * TOK;
@@ -562,7 +571,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
               cbase + static_cast<size_t>(crow_i) * hist.center_width + piece * 8));
         }
         // positional restore (K parts only): this token's frame / row / column
-        const bool rotate = tensor == 0 && p.rope.cos_sin != nullptr;
+        const bool rotate = ROPE && tensor == 0;
         int coord_t = 0, coord_h = 0, coord_w = 0;
         if (rotate) {
           const int pos = in ? max(__ldg(p.rope.positions + t0 + row), 0) : 0;
@@ -781,7 +790,7 @@ __global__ void fill_empty_kernel(uint16_t* out, float* lse, size_t rows, int d)
 constexpr size_t SMEM_LIMIT = 232448;  // 227 KB per CTA
 long long* g_profile = nullptr;
 
-template <int D>
+template <int D, bool ROPE, bool PROF>
 int launch(const CUtensorMap maps[5], Params& p, cudaStream_t stream) {
   using L = Layout<D>;
   int nw = MAX_NW;   // as many decoder-row slots as fit (at least the two staging slots' worth)
@@ -792,7 +801,7 @@ int launch(const CUtensorMap maps[5], Params& p, cudaStream_t stream) {
               p.rank, p.ngroups);
   p.nw = nw;
   p.prof = g_profile;
-  auto kernel = attn_codec_kernel<D>;
+  auto kernel = attn_codec_kernel<D, ROPE, PROF>;
   NKV_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(smem)));
   const int qblocks = ceil_div(p.Q, NQ * QT);
@@ -811,6 +820,14 @@ int launch(const CUtensorMap maps[5], Params& p, cudaStream_t stream) {
   config.numAttrs = 1;
   NKV_CUDA(cudaLaunchKernelEx(&config, kernel, maps[0], maps[1], maps[2], maps[3], maps[4], p));
   return NKV_OK;
+}
+
+int launch_for(int dk, bool rope, const CUtensorMap maps[5], Params& p, cudaStream_t stream) {
+  if (g_profile != nullptr && dk == 128 && !rope)   // the instrumented build exists for this case only
+    return launch<128, false, true>(maps, p, stream);
+  if (dk == 128)
+    return rope ? launch<128, true, false>(maps, p, stream) : launch<128, false, false>(maps, p, stream);
+  return rope ? launch<64, true, false>(maps, p, stream) : launch<64, false, false>(maps, p, stream);
 }
 
 }  // namespace
@@ -890,14 +907,14 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
   splits = ceil_div(tiles, p.tiles_per_split);
   if (splits == 1) {
     p.out = static_cast<uint16_t*>(out); p.lse = lse;
-    return dk == 128 ? launch<128>(maps, p, stream) : launch<64>(maps, p, stream);
+    return launch_for(dk, rope != nullptr, maps, p, stream);
   }
   NKV_REQUIRE(workspace != nullptr, NKV_ERR_INVALID, "history splits need a workspace");
   const size_t rows = static_cast<size_t>(Q) * heads;
   uint16_t* part_out = static_cast<uint16_t*>(workspace);
   float* part_lse = reinterpret_cast<float*>(part_out + static_cast<size_t>(splits) * rows * dv);
   p.out = part_out; p.lse = part_lse;
-  int rc = dk == 128 ? launch<128>(maps, p, stream) : launch<64>(maps, p, stream);
+  int rc = launch_for(dk, rope != nullptr, maps, p, stream);
   if (rc != NKV_OK) return rc;
   const void* outs[16];
   const float* lses[16];
