@@ -327,6 +327,20 @@ int nkv_cp_merge_peer(const void* const* part_out, const float* const* part_lse,
                       void* const* dst_out, float* const* dst_lse, int world, int64_t rows,
                       int d, int64_t row_begin, int64_t row_end, int dtype, void* stream);
 
+/*
+ * INT8 operator storage -> resident bf16 weights, once at load time:
+ *     out[r, c] = bf16( bf16(qweight[r, c]) * scale[r, c / group] )
+ * the expression the reference evaluates before every projection
+ * (_operator_linear MGM/nanokv_codec.py:134-152, _pack_operator :108-131,
+ * unpack_int8_weight MGM/nanokv_codec_kernels.py:76-82; LingBot per-row form
+ * _linear LB/lingbot_v2_kv_codec.py:104-108).  A B200 keeps every layer's
+ * operators resident in bf16 (about 0.5 GB for 40 layers at H 40 x D 128,
+ * rank 640), so the kernels read bf16 and nothing is dequantised per call.
+ * qweight i8 [rows, cols]; scale bf16 [rows, cols / group]; cols % 16 == 0.
+ */
+int nkv_operator_unpack_int8(const int8_t* qweight, const void* scale_bf16, int64_t rows, int cols,
+                             int group, void* out_bf16, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -74,6 +74,7 @@ SIGNATURES = {
                                   c_void_p, c_void_p]),
     "nkv_lse_merge": (c_int, [POINTER(c_void_p), POINTER(c_void_p), c_int, c_int64, c_int, c_int,
                               c_void_p, c_void_p, c_void_p]),
+    "nkv_operator_unpack_int8": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "nkv_peer_alloc": (c_int, [c_int64, POINTER(c_void_p), c_char_p]),
     "nkv_peer_open": (c_int, [c_char_p, POINTER(c_void_p)]),
     "nkv_peer_close": (c_int, [c_void_p]),

@@ -51,6 +51,19 @@ class Operator:
                      else self.mean).contiguous()
 
 
+    @classmethod
+    def from_int8(cls, mean: torch.Tensor, encoder: dict, decoder: dict, device="cuda") -> "Operator":
+        """Operator stored as INT8 (``{"qweight", "scale", "group_size"}`` per matrix: the reference's
+        deployed format, MGM/nanokv_codec.py:108-131, LB/lingbot_v2_kv_codec.py:98-108).  The weights
+        are expanded to bf16 once, here, with the reference's per-call expression; every kernel then
+        reads the resident bf16 copy."""
+        def unpack(packed):
+            q = packed["qweight"].to(device=device).contiguous()
+            scale = packed["scale"].to(device=device)
+            return ops.unpack_int8_weight(q, scale, packed.get("group_size"))
+        return cls(mean, unpack(encoder), unpack(decoder), device=device)
+
+
 def kmeans_init_rows(sequence: int, clusters: int, seed: int) -> torch.Tensor:
     """Seeded CPU permutation prefix, as the reference draws it
     (MGM/nanokv_codec.py:310-311, LB/lingbot_v2_kv_codec.py:220-221)."""

@@ -364,4 +364,12 @@ int nkv_cp_merge_peer(const void* const* part_out, const float* const* part_lse,
                        dtype, static_cast<cudaStream_t>(stream));
 }
 
+int nkv_operator_unpack_int8(const int8_t* qweight, const void* scale_bf16, int64_t rows, int cols,
+                             int group, void* out_bf16, void* stream) {
+  NKV_REQUIRE(qweight && scale_bf16 && out_bf16 && rows >= 0, NKV_ERR_INVALID,
+              "operator_unpack_int8: null argument or rows=%lld", static_cast<long long>(rows));
+  return unpack_int8(qweight, scale_bf16, rows, cols, group, out_bf16,
+                     static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -275,6 +275,37 @@ cp_merge_peer_kernel(PeerMergeArgs args, int world, long long row_begin, long lo
     for (int r = 0; r < world; ++r) args.dst_lse[r][row] = lse;
 }
 
+// ---- INT8 operator storage -> resident bf16 --------------------------------------------------
+// out[r][c] = bf16(q[r][c]) * scale[r][c / group] as one bf16 product (|q| <= 127 is exact in
+// bf16, so the fp32 product of the two is exact and is rounded once).  Thread = 16 columns.
+__global__ void __launch_bounds__(256)
+unpack_int8_kernel(const int8_t* q, const uint16_t* scale, long long rows, int cols, int group,
+                   uint16_t* out) {
+  const int per_row = cols >> 4;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= rows * per_row) return;
+  const long long r = idx / per_row;
+  const int c0 = static_cast<int>(idx % per_row) * 16;
+  const uint4 raw = *reinterpret_cast<const uint4*>(q + r * cols + c0);
+  const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+  const int groups = cols / group;
+  uint32_t packed[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int c = c0 + 2 * k;
+    const float s0 = bf16_bits_to_float(scale[r * groups + c / group]);
+    const float s1 = bf16_bits_to_float(scale[r * groups + (c + 1) / group]);
+    const int shift = (2 * k & 3) * 8;
+    const float v0 = static_cast<float>(static_cast<int8_t>((words[k >> 1] >> shift) & 0xFFu));
+    const float v1 = static_cast<float>(static_cast<int8_t>((words[k >> 1] >> (shift + 8)) & 0xFFu));
+    packed[k] = static_cast<uint32_t>(float_to_bf16_bits(v0 * s0)) |
+                (static_cast<uint32_t>(float_to_bf16_bits(v1 * s1)) << 16);
+  }
+  uint4* dst = reinterpret_cast<uint4*>(out + r * cols + c0);
+  dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+}
+
 }  // namespace
 
 int quant_pack(const void* coeff, int coeff_dtype, int S, int r, int group, float eps,
@@ -353,6 +384,22 @@ int cp_merge_peer(const void* const* part_out, const float* const* part_lse, voi
   else
     cp_merge_peer_kernel<NKV_F16><<<blocks, 256, 0, stream>>>(args, world, row_begin, row_end, d);
   NKV_LAUNCH_CHECK("cp_merge_peer_kernel");
+  return NKV_OK;
+}
+
+int unpack_int8(const int8_t* q, const void* scale_bf16, int64_t rows, int cols, int group,
+                void* out_bf16, cudaStream_t stream) {
+  NKV_REQUIRE(cols > 0 && cols % 16 == 0, NKV_ERR_INVALID,
+              "unpack_int8: %d columns (need a multiple of 16)", cols);
+  NKV_REQUIRE(group > 0 && cols % group == 0, NKV_ERR_INVALID,
+              "unpack_int8: group %d must divide %d columns", group, cols);
+  NKV_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out_bf16)) & 15) == 0,
+              NKV_ERR_INVALID, "unpack_int8: arrays must be 16-byte aligned");
+  if (rows == 0) return NKV_OK;
+  const long long total = rows * (cols >> 4);
+  unpack_int8_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+      q, static_cast<const uint16_t*>(scale_bf16), rows, cols, group, static_cast<uint16_t*>(out_bf16));
+  NKV_LAUNCH_CHECK("unpack_int8_kernel");
   return NKV_OK;
 }
 

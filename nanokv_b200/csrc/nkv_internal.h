@@ -34,6 +34,8 @@ int quant_pack(const void* coeff, int coeff_dtype, int S, int r, int group, floa
                cudaStream_t stream);
 int lse_merge(const void* const* outs, const float* const* lses, int parts, int64_t rows,
               int d, int dtype, void* out, float* lse_out, cudaStream_t stream);
+int unpack_int8(const int8_t* q, const void* scale_bf16, int64_t rows, int cols, int group,
+                void* out_bf16, cudaStream_t stream);
 int cp_merge_peer(const void* const* part_out, const float* const* part_lse, void* const* dst_out,
                   float* const* dst_lse, int world, int64_t rows, int d, int64_t row_begin,
                   int64_t row_end, int dtype, cudaStream_t stream);

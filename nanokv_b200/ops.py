@@ -240,6 +240,25 @@ def attention_lse(q, k, v, *, scale: float):
     return out, lse
 
 
+def unpack_int8_weight(qweight: torch.Tensor, scale: torch.Tensor, group_size: int | None = None):
+    """INT8 operator storage -> bf16 weight: bf16(q) * scale per (row, group), one bf16 product.
+    qweight i8 [rows, cols]; scale bf16 [rows, cols / group] (or [rows, 1] / [rows] per row)."""
+    device = _require_cuda(qweight, scale)
+    if qweight.dtype != torch.int8 or qweight.dim() != 2:
+        raise ValueError("qweight must be an int8 matrix")
+    rows, cols = qweight.shape
+    group = cols if group_size in (None, 0) else int(group_size)
+    if group <= 0 or cols % group:
+        raise ValueError(f"INT8 group size {group} must divide {cols}")
+    scale = scale.to(torch.bfloat16).reshape(rows, -1).contiguous()
+    if scale.shape[1] != cols // group:
+        raise ValueError("scale shape does not match the group size")
+    out = torch.empty(rows, cols, dtype=torch.bfloat16, device=device)
+    _lib.check(_lib.library().nkv_operator_unpack_int8(
+        _ptr(qweight), _ptr(scale), rows, cols, group, _ptr(out), _stream(device)))
+    return out
+
+
 class PeerBuffer:
     """A device buffer other processes of the box can map (nkv_peer_alloc / nkv_peer_open).
 

@@ -478,3 +478,26 @@ def rope_by_positions(key: torch.Tensor, positions: torch.Tensor, freqs: torch.T
                             horizontal.index_select(0, column)), dim=1)[:, None]
     pairs = torch.view_as_complex(key[0].to(torch.float64).reshape(key.shape[1], key.shape[2], -1, 2))
     return torch.view_as_real(pairs * multiplier).flatten(2)[None].to(key.dtype)
+
+
+# ---------------------------------------------------------------- INT8 operator storage
+def pack_int8_weight(weight: torch.Tensor, group_size: int = 0):
+    """fp32 weight [rows, in] -> (int8 codes, bf16 scale [rows, in/group], group): symmetric
+    per-(row, group) quantisation, scale = max(amax, 1e-12) / 127 (MGM/nanokv_codec.py:108-131)."""
+    weight = weight.detach().float().cpu().contiguous()
+    in_features = int(weight.shape[1])
+    group = in_features if group_size <= 0 else int(group_size)
+    if group > in_features or in_features % group:
+        raise ValueError(f"INT8 group size {group} must divide {in_features}")
+    grouped = weight.reshape(weight.shape[0], -1, group)
+    scale = grouped.abs().amax(dim=2).clamp_min(1e-12) / 127.0
+    codes = (grouped / scale[:, :, None]).round().clamp(-127, 127).to(torch.int8)
+    return codes.reshape_as(weight), scale.to(torch.bfloat16), group
+
+
+def unpack_int8_weight(qweight: torch.Tensor, scale: torch.Tensor, group_size: int) -> torch.Tensor:
+    """bf16 weight the reference multiplies with: bf16(q) * scale, a bf16 product
+    (MGM/nanokv_codec.py:147-152; LB/lingbot_v2_kv_codec.py:107 per row)."""
+    rows = qweight.shape[0]
+    return (qweight.reshape(rows, -1, group_size).to(torch.bfloat16)
+            * scale.to(torch.bfloat16).reshape(rows, -1)[:, :, None]).reshape_as(qweight)

@@ -124,3 +124,11 @@ def build_rope(case: RopeCase) -> dict:
     positions = torch.cat([torch.arange(sink), torch.arange(recent_start, recent_start + case.tokens - sink)])
     return {"key": key, "positions": positions, "frame_seqlen": frame_seqlen,
             "grid_sizes": torch.tensor([[32, case.height, case.width]])}
+
+
+def build_int8_weight() -> torch.Tensor:
+    """An operator-shaped fp32 matrix with rows of very different magnitude (and one zero row)."""
+    gen = synthetic.generator(4321)
+    weight = torch.randn(96, 256, generator=gen) * torch.logspace(-3, 1, 96)[:, None]
+    weight[17] = 0
+    return weight

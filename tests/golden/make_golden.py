@@ -170,6 +170,28 @@ def reference_rope_params(root):
     return scope["rope_params"]
 
 
+def run_int8_operator_case(root) -> dict:
+    """The reference's INT8 operator packing and the bf16 weight it multiplies with."""
+    codec = ref_import.load_mg_codec(root)
+    out = {}
+    for name, group in (("per_row", 0), ("group64", 64)):
+        weight = cases.build_int8_weight()
+        os.environ["MG35_KVCODEC_OPERATOR_WEIGHT_MODE"] = "int8"
+        os.environ["MG35_KVCODEC_INT8_WEIGHT_GROUP_SIZE"] = str(group)
+        packed = codec._pack_operator(weight, torch.device("cpu"))
+        os.environ.pop("MG35_CODEC_NATIVE_WEIGHT_DEQUANT_OPT", None)
+        # _operator_linear with an identity input returns the dequantised weight's transpose rows:
+        eye = torch.eye(weight.shape[1], dtype=torch.bfloat16)
+        dense = codec._operator_linear(eye, packed).t().contiguous()       # [rows, in] bf16
+        out[f"{name}_qweight"] = packed["qweight"].numpy()
+        out[f"{name}_scale"] = bits(packed["scale"])
+        out[f"{name}_dense"] = bits(dense)
+    os.environ["MG35_KVCODEC_OPERATOR_WEIGHT_MODE"] = "int8"
+    os.environ.pop("MG35_KVCODEC_INT8_WEIGHT_GROUP_SIZE", None)
+    out["weight_digest"] = np.array([checksum(cases.build_int8_weight())], dtype=np.uint64)
+    return out
+
+
 def run_rope_case(case: cases.RopeCase, root) -> dict:
     ref_import.load_lingbot_codec(root)
     runtime = ref_import._load("wan.modules.lingbot_v2_cache_runtime",
@@ -205,6 +227,7 @@ def main() -> None:
     for case in cases.FAST_CASES:
         save(case.name, lambda: run_fast_case(case, root))
     save("merge_edge", lambda: run_merge_case(root))
+    save("int8_operator", lambda: run_int8_operator_case(root))
     for case in cases.ROPE_CASES:
         save(case.name, lambda: run_rope_case(case, root))
 

@@ -151,3 +151,15 @@ def test_rope_by_positions(case):
     want = from_bits(gold["rotated"], case.dtype)
     assert torch.equal(got.view(torch.int16) if case.dtype == torch.bfloat16 else got, 
                        want.view(torch.int16) if case.dtype == torch.bfloat16 else want)
+
+
+@pytest.mark.parametrize("name,group", [("per_row", 0), ("group64", 64)])
+def test_int8_operator_storage(name, group):
+    gold = load("int8_operator")
+    weight = cases.build_int8_weight()
+    assert int(gold["weight_digest"][0]) == checksum(weight), "input generator drifted"
+    codes, scale, group_size = oracle.pack_int8_weight(weight, group)
+    assert np.array_equal(gold[f"{name}_qweight"], codes.numpy())
+    assert np.array_equal(gold[f"{name}_scale"], scale.view(torch.int16).numpy())
+    dense = oracle.unpack_int8_weight(codes, scale, group_size)
+    assert np.array_equal(gold[f"{name}_dense"], dense.view(torch.int16).numpy())
