@@ -102,6 +102,61 @@ class CompressedHistory:
             tokens=t1 - t0, segments=stop_segment - start_segment, rank=self.rank,
             group=self.group)
 
+    def view_tokens(self, start: int, stop: int) -> HistoryView:
+        """ABI view of the token range [start, stop), which may cut segments: the arrays are
+        offset to ``start`` and the segment table is shifted and clipped to the range, so a cut
+        segment simply starts at 0 or ends at ``stop - start``."""
+        if not 0 <= start <= stop <= self.tokens:
+            raise ValueError("bad token range")
+        if start == stop:
+            return HistoryView(codes=self.codes[start:], scales=self.scales[start:], ids=self.ids[start:],
+                               centers=self.centers, seg_start=self.seg_start,
+                               seg_center_row=self.seg_center_row, tokens=0, segments=0,
+                               rank=self.rank, group=self.group)
+        first = max(i for i in range(self.segments) if self._starts[i] <= start)
+        last = min(i for i in range(self.segments) if self._starts[i + 1] >= stop)
+        seg_start = (self.seg_start[first:last + 2] - start).clamp_(0, stop - start).to(torch.int32)
+        return HistoryView(
+            codes=self.codes[start:], scales=self.scales[start:], ids=self.ids[start:],
+            centers=self.centers, seg_start=seg_start, seg_center_row=self.seg_center_row[first:],
+            tokens=stop - start, segments=last - first + 1, rank=self.rank, group=self.group)
+
+    def retain(self, keep: list[int]) -> None:
+        """Keep only the listed segments (increasing order), moving their codes, scales, ids and
+        centre rows down in place and rebuilding the segment table.  Device copies only."""
+        keep = [int(i) for i in keep]
+        if keep != sorted(set(keep)) or any(not 0 <= i < self.segments for i in keep):
+            raise ValueError("segments to keep must be distinct, increasing and in range")
+        starts, rows, token_cursor, row_cursor = [0], [], 0, 0
+        for index in keep:
+            src, count = self._starts[index], self._starts[index + 1] - self._starts[index]
+            if src != token_cursor:   # distinct ranges may overlap when the move is short: stage a copy
+                for array in (self.codes, self.scales, self.ids):
+                    array[token_cursor:token_cursor + count].copy_(array[src:src + count].clone())
+            if self.shared_centers:
+                row = 0
+            else:
+                src_row = self._center_rows[index]
+                next_row = (self._center_rows[index + 1] if index + 1 < self.segments
+                            else self._center_used)
+                clusters = next_row - src_row
+                if src_row != row_cursor:
+                    self.centers[row_cursor:row_cursor + clusters].copy_(
+                        self.centers[src_row:src_row + clusters].clone())
+                row, row_cursor = row_cursor, row_cursor + clusters
+            rows.append(row)
+            token_cursor += count
+            starts.append(token_cursor)
+        self._starts, self._center_rows = starts, rows
+        if not self.shared_centers:
+            self._center_used = row_cursor
+        table = torch.zeros(self.max_segments + 1, dtype=torch.int32)
+        table[:len(starts)] = torch.tensor(starts, dtype=torch.int32)
+        self.seg_start.copy_(table.to(self.device), non_blocking=True)
+        row_table = torch.zeros(self.max_segments, dtype=torch.int32)
+        row_table[:len(rows)] = torch.tensor(rows, dtype=torch.int32) if rows else row_table[:0]
+        self.seg_center_row.copy_(row_table.to(self.device), non_blocking=True)
+
     def resident_bytes(self) -> int:
         """Bytes of payload actually in use (codes, scales, ids, centre tables)."""
         per_token = self.rank // 2 + 2 * (self.rank // self.group) + self.ids.element_size()

@@ -132,3 +132,21 @@ def build_int8_weight() -> torch.Tensor:
     weight = torch.randn(96, 256, generator=gen) * torch.logspace(-3, 1, 96)[:, None]
     weight[17] = 0
     return weight
+
+
+# Rolling window (LingBot lifecycle): four committed chunks, the window cuts the first and the third
+ROLLING = CodecCase("rolling_lb_bf16", Shape("rolling_lb", 2, 128, 64, 8, 250, 70, "bf16"),
+                    (70, 64, 64, 52), layer=2, seed=23, mean_std=0.05)
+ROLLING_POLICY = dict(capacity=150, sink_tokens=40)
+ROLLING_GRID = dict(height=4, width=5)      # frame_seqlen 20
+
+
+def rolling_policy_cases():
+    """(segment ranges, committed_end, capacity, sink_tokens) covering the policy's branches."""
+    uniform = [(i * 30, (i + 1) * 30) for i in range(8)]
+    ragged = [(0, 7), (7, 50), (50, 51), (51, 120), (120, 200)]
+    return [
+        (uniform, 240, 100, 30), (uniform, 240, 100, 0), (uniform, 240, 1000, 30),
+        (uniform, 240, 30, 30), (uniform, 240, 20, 30), (uniform[:1], 30, 100, 50),
+        (ragged, 200, 64, 10), (ragged, 200, 150, 49), (ragged, 200, 81, 7), ([], 0, 10, 2),
+    ]

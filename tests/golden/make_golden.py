@@ -170,6 +170,57 @@ def reference_rope_params(root):
     return scope["rope_params"]
 
 
+def load_lingbot_runtime(root):
+    ref_import.load_lingbot_codec(root)
+    return ref_import._load("wan.modules.lingbot_v2_cache_runtime",
+                            root / ref_import.LB / "wan/modules/lingbot_v2_cache_runtime.py")
+
+
+def run_rolling_case(case: cases.CodecCase, root) -> dict:
+    """LingBot lifecycle on real payloads: encode_pair per chunk, _prune_segments,
+    _decode_active_history (windowed K / V / positions), rope_pre_key_by_positions."""
+    codec = ref_import.load_lingbot_codec(root)
+    runtime = load_lingbot_runtime(root)
+    data = cases.build(case)
+    heads, dim = case.shape.heads, case.shape.head_dim
+    for kind in ("k", "v"):
+        op = data[f"{kind}_op"]
+        ref_import.inject_lingbot_operator(
+            codec, "synthetic", kind, case.layer, joint_dim=case.shape.joint,
+            rank=case.shape.rank, mean=op["mean"], encoder=op["encoder"], decoder=op["decoder"])
+    segments, start = [], 0
+    for key, value in zip(data["k_chunks"], data["v_chunks"]):
+        cache = {"codec_layer": case.layer, "codec_rank": case.shape.rank,
+                 "codec_clusters": case.shape.centers, "codec_iters": case.iters,
+                 "codec_commit_start": start, "codec_basis_root_k": "synthetic",
+                 "codec_basis_root_v": "synthetic"}
+        segments.append(codec.encode_pair(key.reshape(1, -1, heads, dim),
+                                          value.reshape(1, -1, heads, dim), cache=cache))
+        start += key.shape[0]
+    policy = dict(committed_end=start, **cases.ROLLING_POLICY)
+    kept = runtime._prune_segments(segments, **policy)
+    kept_index = [next(i for i, s in enumerate(segments) if s is k) for k in kept]
+    key, value, positions = runtime._decode_active_history(
+        kept, dtype=torch.bfloat16, device=torch.device("cpu"), **policy)
+    grid = cases.ROLLING_GRID
+    rope_params = reference_rope_params(root)
+    freqs = torch.cat([rope_params(1024, dim - 4 * (dim // 6)), rope_params(1024, 2 * (dim // 6)),
+                       rope_params(1024, 2 * (dim // 6))], dim=1)
+    os.environ["LINGBOT_PRE_ROPE_TRITON"] = "0"
+    rotated = runtime.rope_pre_key_by_positions(
+        key, positions, grid_sizes=torch.tensor([[64, grid["height"], grid["width"]]]), freqs=freqs,
+        frame_seqlen=grid["height"] * grid["width"])
+    out = {"kept": np.array(kept_index, dtype=np.int64), "positions": positions.numpy(),
+           "key": bits(key[0]), "value": bits(value[0]), "key_rotated": bits(rotated[0]),
+           "q_digest": np.array([checksum(data["q"])], dtype=np.uint64)}
+    # the policy alone, on synthetic segment tables
+    for index, (ranges, end, capacity, sink) in enumerate(cases.rolling_policy_cases()):
+        table = [{"global_start": a, "global_end": b} for a, b in ranges]
+        survivors = runtime._prune_segments(table, committed_end=end, capacity=capacity, sink_tokens=sink)
+        out[f"policy{index}_kept"] = np.array([table.index(s) for s in survivors], dtype=np.int64)
+    return out
+
+
 def run_int8_operator_case(root) -> dict:
     """The reference's INT8 operator packing and the bf16 weight it multiplies with."""
     codec = ref_import.load_mg_codec(root)
@@ -228,6 +279,7 @@ def main() -> None:
         save(case.name, lambda: run_fast_case(case, root))
     save("merge_edge", lambda: run_merge_case(root))
     save("int8_operator", lambda: run_int8_operator_case(root))
+    save(cases.ROLLING.name, lambda: run_rolling_case(cases.ROLLING, root))
     for case in cases.ROPE_CASES:
         save(case.name, lambda: run_rope_case(case, root))
 
