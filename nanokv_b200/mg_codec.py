@@ -115,6 +115,47 @@ def value_shape(value: Any):
     raise RuntimeError(f"unsupported cache value {value.get('codec')}")
 
 
+def encode_raw_tensor(tensor: torch.Tensor) -> dict:
+    """Uncompressed payload segment (the reference keeps protected frames this way)."""
+    return {"codec": RAW, "tensor": tensor.contiguous(), "shape": tuple(int(v) for v in tensor.shape)}
+
+
+def select_value(value: Any, token_idx: torch.Tensor, *, kind: str, layer: int, dtype: torch.dtype,
+                 device) -> Any:
+    """Keep the tokens listed in ``token_idx`` (sorted positions along the sequence).
+
+    Same contract as the reference's select_value (MGM/nanokv_codec.py:612-694): a segment that
+    is selected whole is reused as it is (immutable payload, no copy); a segment the selection
+    cuts is decoded, its selected rows are gathered and encoded again as a new segment; a
+    selection that takes nothing returns None.  Decode and re-encode run on the GPU kernels.
+    """
+    if torch.is_tensor(value):
+        return value.index_select(1, token_idx).contiguous()
+    parts = _parts(value)
+    lengths = [int(value_shape(part)[1]) for part in parts]
+    bounds = torch.tensor([0] + lengths).cumsum(0)
+    wanted = token_idx.detach().to(device="cpu", dtype=torch.long)
+    if wanted.numel() and (bool((wanted[1:] < wanted[:-1]).any()) or int(wanted[0]) < 0
+                           or int(wanted[-1]) >= int(bounds[-1])):
+        raise RuntimeError("segmented cache selection expects sorted in-range token indices")
+    owner = torch.bucketize(wanted, bounds[1:], right=True)      # segment of every wanted token
+    result = []
+    for index, part in enumerate(parts):
+        local = wanted[owner == index] - int(bounds[index])
+        if local.numel() == 0:
+            continue
+        if local.numel() == lengths[index] and bool((local == torch.arange(lengths[index])).all()):
+            result.append(part)                                   # whole segment: reuse
+            continue
+        rows = decode_value(part, dtype=dtype, device=device)
+        chosen = rows.index_select(1, local.to(rows.device)).contiguous()
+        result.append(encode_raw_tensor(chosen) if part.get("codec") == RAW
+                      else encode_tensor(kind, layer, chosen))
+    if not result:
+        return None
+    return result[0] if len(result) == 1 else {"codec": SEGMENTS, "segments": result}
+
+
 def payload_bytes(value: Any) -> int:
     if torch.is_tensor(value):
         return value.numel() * value.element_size()

@@ -150,3 +150,11 @@ def rolling_policy_cases():
         (uniform, 240, 30, 30), (uniform, 240, 20, 30), (uniform[:1], 30, 100, 50),
         (ragged, 200, 64, 10), (ragged, 200, 150, 49), (ragged, 200, 81, 7), ([], 0, 10, 2),
     ]
+
+
+def select_indices(case: CodecCase) -> torch.Tensor:
+    """Window compaction: drop the head of the first segment and two of its later tokens, keep the
+    rest of the history (the second segment whole)."""
+    first = case.segments[0]
+    keep = [t for t in range(40, first) if t not in (100, 101)]
+    return torch.tensor(keep + list(range(first, sum(case.segments))))

@@ -170,6 +170,32 @@ def reference_rope_params(root):
     return scope["rope_params"]
 
 
+def run_select_case(case: cases.CodecCase, root) -> dict:
+    """select_value of the MG module over two payload segments: the selection cuts the first
+    segment (decode, gather, re-encode) and takes the second whole (reused)."""
+    codec = ref_import.load_mg_codec(root)
+    data = cases.build(case)
+    os.environ["MG35_KVCODEC_C64_CLUSTERS"] = str(case.shape.centers)
+    os.environ["MG35_KVCODEC_C64_ITERS"] = str(case.iters)
+    op = data["k_op"]
+    ref_import.inject_mg_operator(codec, "k", case.layer, mean=op["mean"], encoder=op["encoder"],
+                                  decoder=op["decoder"])
+    value = None
+    for chunk in data["k_chunks"]:
+        value = codec.concat_values(value, codec.encode_tensor("k", case.layer, chunk[None]))
+    token_idx = cases.select_indices(case)
+    picked = codec.select_value(value, token_idx, kind="k", layer=case.layer, dtype=torch.bfloat16,
+                                device=torch.device("cpu"))
+    parts = picked["segments"]
+    assert len(parts) == 2 and parts[1] is value["segments"][1]
+    cut = parts[0]
+    decoded = codec.decode_value(picked, dtype=torch.bfloat16, device=torch.device("cpu"))
+    return {"cut_ids": cut["ids"].numpy(), "cut_packed": cut["packed_codes"].numpy(),
+            "cut_scale": bits(cut["scale"]), "cut_centers": bits(cut["centers"]),
+            "cut_shape": np.array(cut["shape"], dtype=np.int64), "decoded": bits(decoded[0]),
+            "input_digest": np.array([checksum(torch.cat(data["k_chunks"]))], dtype=np.uint64)}
+
+
 def load_lingbot_runtime(root):
     ref_import.load_lingbot_codec(root)
     return ref_import._load("wan.modules.lingbot_v2_cache_runtime",
@@ -278,6 +304,7 @@ def main() -> None:
     for case in cases.FAST_CASES:
         save(case.name, lambda: run_fast_case(case, root))
     save("merge_edge", lambda: run_merge_case(root))
+    save("select_mg_bf16", lambda: run_select_case(cases.MINI_BF16, root))
     save("int8_operator", lambda: run_int8_operator_case(root))
     save(cases.ROLLING.name, lambda: run_rolling_case(cases.ROLLING, root))
     for case in cases.ROPE_CASES:

@@ -62,3 +62,49 @@ def test_interface_errors_match_the_reference():
         mg_codec.concat_values({"codec": "worldplay_raw_v1", "tensor": torch.zeros(1)}, torch.zeros(1))
     with pytest.raises(RuntimeError):
         mg_codec.decode_tensor({"codec": "something_else"}, dtype=torch.float32, device="cuda")
+
+
+def test_select_value_cuts_and_reuses_segments_like_the_reference():
+    """A window compaction that cuts the first segment and keeps the second whole: the kept
+    segment is reused, the cut one is decoded, gathered and encoded again; the result is compared
+    with what the reference's select_value produced from the same inputs."""
+    from test_oracle_golden import from_bits
+    case = cases.MINI_BF16
+    gold = load("select_mg_bf16")
+    data = cases.build(case)
+    os.environ["MG35_KVCODEC_C64_CLUSTERS"] = str(case.shape.centers)
+    os.environ["MG35_KVCODEC_C64_ITERS"] = str(case.iters)
+    op = data["k_op"]
+    mg_codec.register_operator("k", case.layer, mean=op["mean"], encoder=op["encoder"],
+                               decoder=op["decoder"])
+    value = None
+    for chunk in data["k_chunks"]:
+        value = mg_codec.concat_values(value, mg_codec.encode_tensor("k", case.layer, chunk[None].cuda()))
+    token_idx = cases.select_indices(case)
+    picked = mg_codec.select_value(value, token_idx.cuda(), kind="k", layer=case.layer,
+                                   dtype=torch.bfloat16, device="cuda")
+    parts = picked["segments"]
+    assert len(parts) == 2 and parts[1] is value["segments"][1]          # whole segment reused
+    cut = parts[0]
+    assert tuple(cut["shape"]) == tuple(int(v) for v in gold["cut_shape"])
+    same_ids = float((cut["ids"].cpu().numpy() == gold["cut_ids"]).mean())
+    assert same_ids >= 0.98, same_ids
+    decoded = mg_codec.decode_value(picked, dtype=torch.bfloat16, device="cuda")[0].cpu().float()
+    want = from_bits(gold["decoded"], torch.bfloat16).float()
+    assert decoded.shape == want.shape
+    assert float((decoded - want).norm() / want.norm()) <= 2e-2
+    # selections that need no work, or nothing
+    whole = mg_codec.select_value(value, torch.arange(sum(case.segments)), kind="k", layer=case.layer,
+                                  dtype=torch.bfloat16, device="cuda")
+    assert whole["segments"][0] is value["segments"][0] and whole["segments"][1] is value["segments"][1]
+    second = mg_codec.select_value(value, torch.arange(case.segments[0], sum(case.segments)), kind="k",
+                                   layer=case.layer, dtype=torch.bfloat16, device="cuda")
+    assert second is value["segments"][1]
+    assert mg_codec.select_value(value, torch.empty(0, dtype=torch.long), kind="k", layer=case.layer,
+                                 dtype=torch.bfloat16, device="cuda") is None
+    with pytest.raises(RuntimeError):
+        mg_codec.select_value(value, torch.tensor([5, 3]), kind="k", layer=case.layer,
+                              dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError):
+        mg_codec.select_value(value, torch.tensor([5, 9999]), kind="k", layer=case.layer,
+                              dtype=torch.bfloat16, device="cuda")
