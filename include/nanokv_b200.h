@@ -250,10 +250,16 @@ int nkv_attn_codec_split(const void* q, int dtype, int64_t q_stride_token, int64
  */
 typedef struct nkv_rope {
   const int32_t* positions;  /* [history tokens] absolute token positions (device) */
-  const float* cos_sin;      /* [table_rows][head_dim/2][2] (cos, sin) (device) */
+  const float* cos_sin;      /* [table_rows][table_half][2] (cos, sin) (device) */
   int32_t table_rows;
   int32_t frame_seqlen;      /* tokens per frame = height * width */
   int32_t width;
+  int32_t table_half;        /* pairs per table row = native head_dim / 2; the bands are cut on it */
+  const int32_t* pair_index; /* NULL: pair p of the key row is native pair p (table_half = dk/2).
+                                Else [heads][dk/2]: the native pair each pair of a low-width row
+                                retains (selected RoPE of the NanoKV-Fast readers, _rope_low /
+                                _selected_multiplier wan/modules/codec_native_attention.py:416-438,
+                                rope_selected codec_native_rope_triton.py:31-47) (device) */
 } nkv_rope;
 
 /*
@@ -269,6 +275,14 @@ int nkv_attn_codec_rope(const void* q, int dtype, int64_t q_stride_token, int64_
                         const nkv_rope* rope, float scale, void* out, float* lse,
                         int32_t* status_word, int splits, void* workspace, size_t workspace_bytes,
                         void* stream);
+
+/*
+ * The same rotation applied to explicit rows (queries, the current chunk's keys):
+ * x [S, heads, d] with strides in elements -> out [S, heads, d] contiguous, same dtype;
+ * rope->positions holds the S row positions.  fp32 arithmetic, one rounding.
+ */
+int nkv_rope_rows(const void* x, int dtype, int64_t stride_row, int64_t stride_head, int S, int heads,
+                  int d, const nkv_rope* rope, void* out, void* stream);
 
 /*
  * Plain attention with LSE over K / V rows that are already full width (the

@@ -14,7 +14,8 @@ from . import build as _build
 class Rope(ctypes.Structure):
     """struct nkv_rope"""
     _fields_ = [("positions", c_void_p), ("cos_sin", c_void_p), ("table_rows", c_int32),
-                ("frame_seqlen", c_int32), ("width", c_int32)]
+                ("frame_seqlen", c_int32), ("width", c_int32), ("table_half", c_int32),
+                ("pair_index", c_void_p)]
 
 
 NKV_OK = 0
@@ -69,6 +70,8 @@ SIGNATURES = {
                                     POINTER(History), POINTER(History), c_void_p, c_void_p,
                                     c_void_p, c_void_p, POINTER(Rope), c_float, c_void_p, c_void_p,
                                     c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
+    "nkv_rope_rows": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, POINTER(Rope),
+                              c_void_p, c_void_p]),
     "nkv_attention_lse": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64,
                                   c_int64, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                                   c_void_p, c_void_p]),

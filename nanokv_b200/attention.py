@@ -60,9 +60,15 @@ class RopeTable:
         self.cos_sin = torch.view_as_real(freqs).to(device=device, dtype=torch.float32).contiguous()
         self.frame_seqlen, self.width = int(frame_seqlen), int(width)
 
-    def view(self, positions: torch.Tensor) -> "ops.RopeView":
+    def view(self, positions: torch.Tensor, pair_index: torch.Tensor | None = None) -> "ops.RopeView":
+        """``pair_index`` i32 [heads, d/2]: the native pair every pair of a low-width row retains."""
         positions = positions.to(device=self.cos_sin.device, dtype=torch.int32).contiguous()
-        return ops.RopeView(positions, self.cos_sin, self.frame_seqlen, self.width)
+        return ops.RopeView(positions, self.cos_sin, self.frame_seqlen, self.width, pair_index)
+
+    def rotate(self, rows: torch.Tensor, positions: torch.Tensor,
+               pair_index: torch.Tensor | None = None) -> torch.Tensor:
+        """rows [S,H,d] (queries, the current chunk's keys) rotated by their positions."""
+        return ops.rope_rows(rows, self.view(positions, pair_index))
 
 
 def merge(out_a, lse_a, out_b, lse_b):
@@ -98,6 +104,17 @@ class ReaderGroup:
         self.k_read = pad_rows(state["k_read"])
         self.v_read = pad_rows(state["v_read"])
         self._tables: dict = {}
+        # native pair retained by every pair of the (padded) low-width row, for the selected RoPE
+        # (LB/codec_native_attention.py:111, :271-272: indices keep native complex pairs together)
+        self.pair_index = None
+        if state.get("indices") is not None:
+            indices = state["indices"].long()
+            if (not torch.equal(indices[:, 1::2], indices[:, ::2] + 1)
+                    or bool((indices[:, ::2] % 2).any())):
+                raise ValueError("low-dimensional RoPE indices must preserve native complex pairs")
+            pairs = torch.zeros(indices.shape[0], pad_to // 2, dtype=torch.int32)
+            pairs[:, :indices.shape[1] // 2] = (indices[:, ::2] // 2).to(torch.int32)
+            self.pair_index = pairs.to(device).contiguous()
 
     def _pad_last(self, tensor):
         if tensor.shape[-1] == self.padded:
@@ -143,8 +160,12 @@ class Reader:
 
 
 def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segments,
-                     low_segments, reader: Reader):
-    """Mixed-dimensional read (MGC/core.py:278-310) with identity positional hooks.
+                     low_segments, reader: Reader, *, rope: "RopeTable | None" = None,
+                     q_positions: torch.Tensor | None = None):
+    """Mixed-dimensional read (MGC/core.py:278-310).  Positional hooks are the identity unless
+    ``rope`` is given: then the reduced query is rotated by ``q_positions`` and every low-width
+    key read by its segment's ``"positions"``, with the native pairs the group retains
+    (LB/codec_native_attention.py:757, :779); native keys and q_native arrive rotated.
 
     q_pre / q_native [Q,H,D]; native_segments [(K [n,H,D], V [n,H,D])] full
     width (protected history, current chunk); low_segments [{"k": history,
@@ -164,14 +185,19 @@ def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segment
         head = group.heads
         query = torch.einsum("nhd,hde->nhe", q_pre.index_select(1, head), group.q_reduce)
         query = group._pad_last(query)
+        if rope is not None:
+            if group.pair_index is None or q_positions is None:
+                raise ValueError("the selected RoPE needs the group's indices and the query positions")
+            query = rope.rotate(query, q_positions, group.pair_index)
         out = native_out.index_select(1, head).contiguous()
         lse = native_lse.index_select(1, head).contiguous()
         for segment in low_segments:
             view_k = group.projected_centers(segment["k"], "k")
             view_v = group.projected_centers(segment["v"], "v")
+            rope_view = (rope.view(segment["positions"], group.pair_index) if rope is not None else None)
             oo, ll = ops.attn_codec(
                 query, view_k, view_v, group.k_read, group.bias(segment["k_mean"], "k"),
-                group.v_read, group.bias(segment["v_mean"], "v"), scale=scale)
+                group.v_read, group.bias(segment["v_mean"], "v"), scale=scale, rope=rope_view)
             lifted = torch.einsum("nhe,hed->nhd", oo[..., :group.width], group.lift).contiguous()
             out, lse = ops.lse_merge([(out, lse), (lifted, ll)])
         result.index_copy_(1, head, out)

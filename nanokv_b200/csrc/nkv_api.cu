@@ -234,6 +234,32 @@ size_t nkv_attn_codec_workspace_bytes(int Q, int heads, int dv, int splits) {
   return static_cast<size_t>(splits) * Q * heads * (static_cast<size_t>(dv) * 2 + 4);
 }
 
+static int check_rope(const nkv_rope* rope, int d, int64_t rows) {
+  NKV_REQUIRE(rope->cos_sin != nullptr && rope->table_rows > 0 && rope->frame_seqlen > 0 &&
+                  rope->width > 0 && rope->frame_seqlen % rope->width == 0,
+              NKV_ERR_INVALID, "rope: table_rows=%d frame_seqlen=%d width=%d", rope->table_rows,
+              rope->frame_seqlen, rope->width);
+  NKV_REQUIRE(rope->positions != nullptr || rows == 0, NKV_ERR_INVALID, "rope: positions are NULL");
+  NKV_REQUIRE(d % 4 == 0 && (reinterpret_cast<uintptr_t>(rope->cos_sin) & 7) == 0, NKV_ERR_INVALID,
+              "rope: head width %d / table alignment", d);
+  NKV_REQUIRE(rope->table_half > 0 && (rope->pair_index != nullptr || rope->table_half == d / 2),
+              NKV_ERR_INVALID, "rope: table_half=%d for head width %d without a pair index",
+              rope->table_half, d);
+  return NKV_OK;
+}
+
+int nkv_rope_rows(const void* x, int dtype, int64_t stride_row, int64_t stride_head, int S, int heads,
+                  int d, const nkv_rope* rope, void* out, void* stream) {
+  NKV_REQUIRE(x && out && rope && S >= 0 && heads >= 0 && d > 0 && d % 2 == 0, NKV_ERR_INVALID,
+              "rope_rows: S=%d heads=%d d=%d", S, heads, d);
+  NKV_REQUIRE(dtype == NKV_F32 || dtype == NKV_BF16, NKV_ERR_INVALID, "rope_rows: dtype");
+  NKV_REQUIRE(d % 4 == 0, NKV_ERR_INVALID, "rope_rows: head width %d", d);
+  int rc = check_rope(rope, d, S);
+  if (rc != NKV_OK) return rc;
+  return rope_rows(x, dtype, stride_row, stride_head, S, heads, d, *rope, out,
+                   static_cast<cudaStream_t>(stream));
+}
+
 int nkv_attn_codec_rope(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head,
                         int Q, int heads, int dk, int dv, const nkv_history* hist_k,
                         const nkv_history* hist_v, const void* wk, const float* bias_k,
@@ -254,14 +280,8 @@ int nkv_attn_codec_rope(const void* q, int dtype, int64_t q_stride_token, int64_
               NKV_ERR_INVALID, "attn_codec: workspace of %zu bytes is too small for %d splits",
               workspace_bytes, splits);
   if (rope != nullptr) {
-    NKV_REQUIRE(rope->cos_sin != nullptr && rope->table_rows > 0 && rope->frame_seqlen > 0 &&
-                    rope->width > 0 && rope->frame_seqlen % rope->width == 0,
-                NKV_ERR_INVALID, "rope: table_rows=%d frame_seqlen=%d width=%d", rope->table_rows,
-                rope->frame_seqlen, rope->width);
-    NKV_REQUIRE(rope->positions != nullptr || hist_k->tokens == 0, NKV_ERR_INVALID,
-                "rope: positions are NULL");
-    NKV_REQUIRE(dk % 4 == 0 && (reinterpret_cast<uintptr_t>(rope->cos_sin) & 7) == 0,
-                NKV_ERR_INVALID, "rope: head width %d / table alignment", dk);
+    rc = check_rope(rope, dk, hist_k->tokens);
+    if (rc != NKV_OK) return rc;
   }
   auto s = static_cast<cudaStream_t>(stream);
   if (dtype == NKV_BF16 && !simt_forced())

@@ -21,6 +21,8 @@ int simt_attn(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride
               const void* k_plain, const void* v_plain, int64_t kv_stride_token,
               int64_t kv_stride_head, int N, float scale, void* out, float* lse,
               cudaStream_t stream, const nkv_rope* rope = nullptr);
+int rope_rows(const void* x, int dtype, int64_t stride_row, int64_t stride_head, int S, int heads,
+              int d, const nkv_rope& rope, void* out, cudaStream_t stream);
 int kmeans_gather_init(const void* x, int x_dtype, int J, int C, const int32_t* init_rows,
                        float* centers, cudaStream_t stream);
 int kmeans_update(const void* x, int x_dtype, int S, int J, int C, const int32_t* labels,

@@ -318,17 +318,19 @@ attn_kernel(AttnArgs a) {
             }
             if (which == 0 && a.rope.cos_sin != nullptr && t0 + m < a.N) {
               // rotate the adjacent pairs (c, c+1) by the token's frame / row / column
-              const int half = D / 2, third = half / 3, band_a = half - 2 * third, band_b = band_a + third;
+              const int half = D / 2, th = a.rope.table_half, third = th / 3;
+              const int band_a = th - 2 * third, band_b = band_a + third;
               const int pos = max(a.rope.positions[t0 + m], 0);
               const int frame = pos / a.rope.frame_seqlen, spatial = pos - frame * a.rope.frame_seqlen;
               const int prow = spatial / a.rope.width, pcol = spatial - prow * a.rope.width;
 #pragma unroll
               for (int pr = 0; pr < 2; ++pr) {
-                const int pg = (n0 + tx * 4) / 2 + pr;
-                if (pg >= half) continue;
+                const int pl = (n0 + tx * 4) / 2 + pr;
+                if (pl >= half) continue;
+                const int pg = a.rope.pair_index ? a.rope.pair_index[head * half + pl] : pl;
                 int coord = pg < band_a ? frame : (pg < band_b ? prow : pcol);
                 coord = min(coord, a.rope.table_rows - 1);
-                const float2 cs = reinterpret_cast<const float2*>(a.rope.cos_sin)[static_cast<size_t>(coord) * half + pg];
+                const float2 cs = reinterpret_cast<const float2*>(a.rope.cos_sin)[static_cast<size_t>(coord) * th + pg];
                 const float x0 = vals[2 * pr], x1 = vals[2 * pr + 1];
                 float y0 = fmaf(x0, cs.x, -(x1 * cs.y)), y1 = fmaf(x0, cs.y, x1 * cs.x);
                 vals[2 * pr] = bf16 ? round_to_bf16(y0) : y0;
@@ -556,6 +558,41 @@ int simt_attn(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride
   NKV_ATTN_CASE(16, 16)
 #undef NKV_ATTN_CASE
   return fail(NKV_ERR_UNSUPPORTED, "attention head widths dk=%d dv=%d (built: 16, 32, 64, 128 with dk == dv)", dk, dv);
+}
+
+// rotation of explicit rows: thread = one (row, head, pair)
+__global__ void __launch_bounds__(256)
+rope_rows_kernel(const void* x, int dtype, long long stride_row, long long stride_head, int S,
+                 int heads, int d, nkv_rope rope, void* out) {
+  const int half = d / 2;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(S) * heads * half) return;
+  const int pl = static_cast<int>(idx % half);
+  const int head = static_cast<int>((idx / half) % heads);
+  const int row = static_cast<int>(idx / (static_cast<long long>(half) * heads));
+  const int th = rope.table_half, third = th / 3, band_a = th - 2 * third, band_b = band_a + third;
+  const int pos = max(rope.positions[row], 0);
+  const int frame = pos / rope.frame_seqlen, spatial = pos - frame * rope.frame_seqlen;
+  const int prow = spatial / rope.width, pcol = spatial - prow * rope.width;
+  const int pg = rope.pair_index ? rope.pair_index[head * half + pl] : pl;
+  int coord = pg < band_a ? frame : (pg < band_b ? prow : pcol);
+  coord = min(coord, rope.table_rows - 1);
+  const float2 cs = reinterpret_cast<const float2*>(rope.cos_sin)[static_cast<size_t>(coord) * th + pg];
+  const size_t src = static_cast<size_t>(row) * stride_row + static_cast<size_t>(head) * stride_head + 2 * pl;
+  const float x0 = load_float(x, dtype, src), x1 = load_float(x, dtype, src + 1);
+  const size_t dst = (static_cast<size_t>(row) * heads + head) * d + 2 * pl;
+  store_float(out, dtype, dst, fmaf(x0, cs.x, -(x1 * cs.y)));
+  store_float(out, dtype, dst + 1, fmaf(x0, cs.y, x1 * cs.x));
+}
+
+int rope_rows(const void* x, int dtype, int64_t stride_row, int64_t stride_head, int S, int heads,
+              int d, const nkv_rope& rope, void* out, cudaStream_t stream) {
+  const long long total = static_cast<long long>(S) * heads * (d / 2);
+  if (total == 0) return NKV_OK;
+  rope_rows_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+      x, dtype, stride_row, stride_head, S, heads, d, rope, out);
+  NKV_LAUNCH_CHECK("rope_rows_kernel");
+  return NKV_OK;
 }
 
 int kmeans_gather_init(const void* x, int x_dtype, int J, int C, const int32_t* init_rows,

@@ -108,7 +108,8 @@ struct Layout {
   static constexpr int SLOT = NUM_BARS * 8;
   static constexpr int ABORT = SLOT + 4;
   static constexpr int BIAS = ((ABORT + 4 + 15) / 16) * 16;
-  static constexpr int CROW = BIAS + PART * 4;
+  static constexpr int PAIRS = BIAS + PART * 4;          // [PART / 2] native pair of each pair of the part
+  static constexpr int CROW = PAIRS + (PART / 2) * 4;
   static constexpr int SCALES = CROW + 2 * TOK * 4;
   static size_t bytes(int nw, int ngroups, int rank) {
     return meta_off(nw, rank) + SCALES + 2 * TOK * ngroups * 2 + 1024;
@@ -226,6 +227,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(meta + L::SLOT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(meta + L::ABORT);
   float* bias = reinterpret_cast<float*>(meta + L::BIAS);            // [64] of this CTA's part
+  int* pair_sel = reinterpret_cast<int*>(meta + L::PAIRS);           // [32] (positional restore)
   int* crow = reinterpret_cast<int*>(meta + L::CROW);                // [2 buf][128]
   uint16_t* scales = reinterpret_cast<uint16_t*>(meta + L::SCALES);  // [2 buf][128][ngroups]
 
@@ -265,6 +267,12 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
   }
   for (int i = tid; i < PART; i += THREADS)
     bias[i] = (tensor ? p.bias_v : p.bias_k)[head * D + part * PART + i];
+  if (ROPE) {
+    for (int i = tid; i < PART / 2; i += THREADS) {
+      const int local = part * (PART / 2) + i;
+      pair_sel[i] = p.rope.pair_index ? p.rope.pair_index[head * (D / 2) + local] : local;
+    }
+  }
   if (warp == 9) tmem_alloc(tmem_slot, 512);
   tc_fence_before();
   __syncthreads();
@@ -573,6 +581,8 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         // positional restore (K parts only): this token's frame / row / column
         const bool rotate = ROPE && tensor == 0;
         int coord_t = 0, coord_h = 0, coord_w = 0;
+        const int band_a = p.rope.table_half - 2 * (p.rope.table_half / 3);
+        const int band_b = band_a + p.rope.table_half / 3;
         if (rotate) {
           const int pos = in ? max(__ldg(p.rope.positions + t0 + row), 0) : 0;
           const int last = p.rope.table_rows - 1;
@@ -620,11 +630,10 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
             x0 += __uint_as_float(cwords[w] << 16);
             x1 += __uint_as_float(cwords[w] & 0xFFFF0000u);
             if (rotate) {   // the pair (x0, x1) of the rebuilt bf16 key is one complex number
-              constexpr int HALF = D / 2, THIRD = HALF / 3, BAND_A = HALF - 2 * THIRD, BAND_B = BAND_A + THIRD;
-              const int pg = part * (PART / 2) + wg * 16 + (j >> 1);
-              const int coord = pg < BAND_A ? coord_t : (pg < BAND_B ? coord_h : coord_w);
+              const int pg = pair_sel[wg * 16 + (j >> 1)];   // native pair this pair retains
+              const int coord = pg < band_a ? coord_t : (pg < band_b ? coord_h : coord_w);
               const float2 cs = __ldg(reinterpret_cast<const float2*>(p.rope.cos_sin) +
-                                      static_cast<size_t>(coord) * HALF + pg);
+                                      static_cast<size_t>(coord) * p.rope.table_half + pg);
               const float k0 = round_to_bf16(x0), k1 = round_to_bf16(x1);
               x0 = fmaf(k0, cs.x, -(k1 * cs.y));
               x1 = fmaf(k0, cs.y, k1 * cs.x);

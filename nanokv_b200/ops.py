@@ -196,8 +196,10 @@ def attn_codec(q, view_k: HistoryView, view_v: HistoryView, wk, bias_k, wv, bias
     if rope is not None:
         if rope.positions.numel() < view_k.tokens:
             raise ValueError("RoPE position/K length mismatch")
-        if rope.cos_sin.shape[1] != dk // 2:
+        if rope.pair_index is None and rope.cos_sin.shape[1] != dk // 2:
             raise ValueError("rotation table width does not match the head width")
+        if rope.pair_index is not None and tuple(rope.pair_index.shape) != (H, dk // 2):
+            raise ValueError("pair index must be [heads, head_dim/2]")
         rope_struct = ctypes.byref(rope.struct())
     _lib.check(lib.nkv_attn_codec_rope(
         _ptr(q), dtype_code(q.dtype), q.stride(0), q.stride(1), Q, H, dk, dv, ctypes.byref(sk),
@@ -209,8 +211,12 @@ def attn_codec(q, view_k: HistoryView, view_v: HistoryView, wk, bias_k, wv, bias
 class RopeView:
     """struct nkv_rope over device tensors: positions i32 [tokens], cos_sin f32 [rows, D/2, 2]."""
 
-    def __init__(self, positions: torch.Tensor, cos_sin: torch.Tensor, frame_seqlen: int, width: int):
-        _require_cuda(positions, cos_sin)
+    def __init__(self, positions: torch.Tensor, cos_sin: torch.Tensor, frame_seqlen: int, width: int,
+                 pair_index: torch.Tensor | None = None):
+        _require_cuda(positions, cos_sin, pair_index)
+        if pair_index is not None and pair_index.dtype != torch.int32:
+            raise ValueError("pair index must be int32")
+        self.pair_index = pair_index
         if positions.dtype != torch.int32 or cos_sin.dtype != torch.float32:
             raise ValueError("positions must be int32 and the rotation table float32")
         if cos_sin.dim() != 3 or cos_sin.shape[2] != 2:
@@ -222,7 +228,27 @@ class RopeView:
 
     def struct(self) -> "_lib.Rope":
         return _lib.Rope(self.positions.data_ptr(), self.cos_sin.data_ptr(), int(self.cos_sin.shape[0]),
-                         self.frame_seqlen, self.width)
+                         self.frame_seqlen, self.width, int(self.cos_sin.shape[1]),
+                         None if self.pair_index is None else self.pair_index.data_ptr())
+
+
+def rope_rows(x: torch.Tensor, rope: RopeView) -> torch.Tensor:
+    """Rotate explicit rows x [S,H,d] by rope.positions (nkv_rope_rows) -> contiguous [S,H,d]."""
+    device = _require_cuda(rope.positions)
+    if not x.is_cuda or x.dim() != 3 or x.stride(2) != 1:
+        raise ValueError("rows must be a CUDA [S,H,d] tensor, contiguous along d")
+    S, H, d = x.shape
+    if rope.positions.numel() != S:
+        raise ValueError("RoPE position/row length mismatch")
+    if rope.pair_index is None and rope.cos_sin.shape[1] != d // 2:
+        raise ValueError("rotation table width does not match the head width")
+    if rope.pair_index is not None and tuple(rope.pair_index.shape) != (H, d // 2):
+        raise ValueError("pair index must be [heads, head_dim/2]")
+    out = torch.empty(S, H, d, dtype=x.dtype, device=device)
+    struct = rope.struct()
+    _lib.check(_lib.library().nkv_rope_rows(_ptr(x), dtype_code(x.dtype), x.stride(0), x.stride(1), S, H,
+                                            d, ctypes.byref(struct), _ptr(out), _stream(device)))
+    return out
 
 
 def attention_lse(q, k, v, *, scale: float):

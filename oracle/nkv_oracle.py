@@ -367,7 +367,11 @@ def codec_attention(q, k_segments, v_segments, *, k_decoder, k_mean, v_decoder, 
     values = [decode_rows(s, decoder=v_decoder, mean=v_mean, dtype=dtype) for s in v_segments]
     if keys:
         key = torch.cat(keys, 1).reshape(batch, -1, heads, head_dim)
-        if rope is not None:
+        if rope is not None and rope.get("indices") is not None:
+            key = rope_selected(key.permute(0, 2, 1, 3), rope["positions"], rope["freqs"],
+                                frame_seqlen=rope["frame_seqlen"], width=rope["width"],
+                                indices=rope["indices"]).permute(0, 2, 1, 3)
+        elif rope is not None:
             key = rope_by_positions(key, rope["positions"], rope["freqs"],
                                     frame_seqlen=rope["frame_seqlen"], width=rope["width"])
         key = key.permute(0, 2, 1, 3)
@@ -409,8 +413,12 @@ def reader_read(group: dict, latent, centers, ids, mean, *, target: str, dtype,
     return output + assigned
 
 
-def hybrid_attention(q_pre, q_native, native_segments, low_segments, reader: dict):
-    """Mixed-dimensional read with identity positional hooks.
+def hybrid_attention(q_pre, q_native, native_segments, low_segments, reader: dict, rope=None):
+    """Mixed-dimensional read; positional hooks are the identity unless ``rope`` is given.
+
+    ``rope`` = dict(freqs, frame_seqlen, width, q_positions): the reduced query and every
+    low-width key read are rotated with the native pairs the group retains (group["indices"]),
+    by q_positions and segment["positions"] (LB/codec_native_attention.py:757, :779).
 
     q_* [B,H,Q,D]; native_segments [(K,V)] full-width [B,H,n,D]; low_segments
     [{"k": (latent, centers, ids, mean), "v": (...)}]; reader {"native_dim",
@@ -430,11 +438,19 @@ def hybrid_attention(q_pre, q_native, native_segments, low_segments, reader: dic
         head = group["heads"].long()
         query = torch.einsum("bhnd,hde->bhne", q_pre.index_select(1, head),
                              group["q_reduce"].to(dtype))
+        if rope is not None:
+            query = rope_selected(query, rope["q_positions"], rope["freqs"],
+                                  frame_seqlen=rope["frame_seqlen"], width=rope["width"],
+                                  indices=group["indices"])
         out = native_out.index_select(1, head)
         lse = native_lse.index_select(1, head)
         for segment in low_segments:
             kk = reader_read(group, *segment["k"], target="k", dtype=dtype, native_dim=native_dim)
             vv = reader_read(group, *segment["v"], target="v", dtype=dtype, native_dim=native_dim)
+            if rope is not None:
+                kk = rope_selected(kk, segment["positions"], rope["freqs"],
+                                   frame_seqlen=rope["frame_seqlen"], width=rope["width"],
+                                   indices=group["indices"])
             oo, ll = attention_lse(query, kk, vv, scale=scale)
             lifted = torch.einsum("bhne,hed->bhnd", oo, group["lift"].to(dtype))
             out, lse = merge(out, lse, lifted, ll)
@@ -478,6 +494,22 @@ def rope_by_positions(key: torch.Tensor, positions: torch.Tensor, freqs: torch.T
                             horizontal.index_select(0, column)), dim=1)[:, None]
     pairs = torch.view_as_complex(key[0].to(torch.float64).reshape(key.shape[1], key.shape[2], -1, 2))
     return torch.view_as_real(pairs * multiplier).flatten(2)[None].to(key.dtype)
+
+
+def rope_selected(value: torch.Tensor, positions: torch.Tensor, freqs: torch.Tensor, *,
+                  frame_seqlen: int, width: int, indices: torch.Tensor) -> torch.Tensor:
+    """value [B,h,S,e] of a low-width reader -> rotated: pair p of head h is the native pair
+    indices[h, 2p] // 2, and is multiplied by that column of the token's full multiplier row
+    (wan/modules/codec_native_attention.py:416-438 _selected_multiplier / _rope_low)."""
+    original_half = freqs.shape[1]
+    split = [original_half - 2 * (original_half // 3), original_half // 3, original_half // 3]
+    temporal, vertical, horizontal = freqs.split(split, dim=1)
+    frame, row, column = rope_coordinates(positions, frame_seqlen, width)
+    multiplier = torch.cat((temporal[frame], vertical[row], horizontal[column]), 1)   # [S, native half]
+    pair = indices.long()[:, ::2] // 2                                                # [h, e/2]
+    selected = multiplier[:, pair].permute(1, 0, 2)                                   # [h, S, e/2]
+    pairs = torch.view_as_complex(value.double().reshape(*value.shape[:-1], -1, 2).contiguous())
+    return torch.view_as_real(pairs * selected[None]).flatten(-2).to(value.dtype)
 
 
 # ---------------------------------------------------------------- INT8 operator storage

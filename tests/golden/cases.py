@@ -158,3 +158,16 @@ def select_indices(case: CodecCase) -> torch.Tensor:
     first = case.segments[0]
     keep = [t for t in range(40, first) if t not in (100, 101)]
     return torch.tensor(keep + list(range(first, sum(case.segments))))
+
+
+def build_rope_selected():
+    """A low-width reader's rows [1, heads, tokens, 32] with the native pairs (of 64) each head keeps."""
+    gen = synthetic.generator(901)
+    heads, tokens, width, native = 3, 90, 32, 128
+    value = torch.randn(1, heads, tokens, width, generator=gen).to(torch.bfloat16)
+    pairs = torch.stack([torch.randperm(native // 2, generator=gen)[:width // 2].sort().values
+                         for _ in range(heads)])
+    indices = torch.stack((2 * pairs, 2 * pairs + 1), dim=2).reshape(heads, width)
+    positions = torch.cat([torch.arange(25), torch.arange(700, 765)])
+    return {"value": value, "indices": indices, "positions": positions, "frame_seqlen": 35,
+            "grid_sizes": torch.tensor([[40, 5, 7]]), "native_dim": native}

@@ -247,6 +247,25 @@ def run_rolling_case(case: cases.CodecCase, root) -> dict:
     return out
 
 
+def run_rope_selected_case(root) -> dict:
+    """_rope_low of the LingBot Fast attention module (selected native pairs per head)."""
+    import types
+    ref_import.load_lingbot_codec(root)
+    load_lingbot_runtime(root)
+    fast = ref_import._load("wan.modules.codec_native_attention",
+                            root / ref_import.LB / "wan/modules/codec_native_attention.py")
+    data = cases.build_rope_selected()
+    rope_params = reference_rope_params(root)
+    d = data["native_dim"]
+    freqs = torch.cat([rope_params(1024, d - 4 * (d // 6)), rope_params(1024, 2 * (d // 6)),
+                       rope_params(1024, 2 * (d // 6))], dim=1)
+    os.environ["LINGBOT_CODEC_NATIVE_TRITON_ROPE"] = "0"
+    out = fast._rope_low(data["value"], data["positions"], data["grid_sizes"], freqs,
+                         data["frame_seqlen"], types.SimpleNamespace(indices=data["indices"]))
+    return {"rotated": bits(out), "value_digest": np.array([checksum(data["value"])], dtype=np.uint64),
+            "indices": data["indices"].numpy()}
+
+
 def run_int8_operator_case(root) -> dict:
     """The reference's INT8 operator packing and the bf16 weight it multiplies with."""
     codec = ref_import.load_mg_codec(root)
@@ -305,6 +324,7 @@ def main() -> None:
         save(case.name, lambda: run_fast_case(case, root))
     save("merge_edge", lambda: run_merge_case(root))
     save("select_mg_bf16", lambda: run_select_case(cases.MINI_BF16, root))
+    save("rope_selected_bf16", lambda: run_rope_selected_case(root))
     save("int8_operator", lambda: run_int8_operator_case(root))
     save(cases.ROLLING.name, lambda: run_rolling_case(cases.ROLLING, root))
     for case in cases.ROPE_CASES:

@@ -98,3 +98,131 @@ def test_rope_argument_errors():
                                   positions=positions[:-1].cuda())
     with pytest.raises(ValueError):
         attention.codec_attention(q.cuda(), hist_k, hist_v, ops_k, ops_v, rope=table)
+
+
+def pair_index_of(indices: torch.Tensor) -> torch.Tensor:
+    """reader indices [h, e] (retained native dimensions) -> native pair of every pair, i32 [h, e/2]."""
+    return (indices[:, ::2] // 2).to(torch.int32)
+
+
+def test_rope_rows_against_the_reference_fixtures():
+    from test_oracle_golden import from_bits, load
+    # full-width rows: rope_pre_key_by_positions
+    case = cases.ROPE_CASES[0]
+    gold, data = load(case.name), cases.build_rope(case)
+    freqs = oracle.rope_table(1024, case.head_dim)
+    table = attention.RopeTable(freqs, frame_seqlen=data["frame_seqlen"], width=case.width)
+    got = table.rotate(data["key"][0].cuda(), data["positions"].cuda()).cpu()
+    want = from_bits(gold["rotated"], torch.bfloat16)[0]
+    assert float((got.float() - want.float()).abs().max()) <= 2.0 ** -7 * float(want.float().abs().max())
+    assert float((got != want).float().mean()) < 0.01          # fp32 instead of fp64: rare last-bit ties
+    # a low-width reader's rows: _rope_low with selected native pairs
+    gold, data = load("rope_selected_bf16"), cases.build_rope_selected()
+    freqs = oracle.rope_table(1024, data["native_dim"])
+    table = attention.RopeTable(freqs, frame_seqlen=data["frame_seqlen"], width=int(data["grid_sizes"][0, 2]))
+    rows = data["value"][0].permute(1, 0, 2).contiguous()       # [S, h, e]
+    got = table.rotate(rows.cuda(), data["positions"].cuda(), pair_index_of(data["indices"]).cuda()).cpu()
+    want = from_bits(gold["rotated"], torch.bfloat16)[0].permute(1, 0, 2)
+    assert float((got.float() - want.float()).abs().max()) <= 2.0 ** -7 * float(want.float().abs().max())
+    assert float((got != want).float().mean()) < 0.01
+    # fp32 rows, strided input
+    x = torch.randn(50, 4, 2 * 64, generator=torch.Generator().manual_seed(3))[:, :, :64]
+    positions = torch.arange(100, 150)
+    freqs = oracle.rope_table(1024, 64)
+    table = attention.RopeTable(freqs, frame_seqlen=12, width=4)
+    got = table.rotate(x.cuda(), positions.cuda()).cpu()
+    want = oracle.rope_by_positions(x[None].contiguous(), positions, freqs, frame_seqlen=12, width=4)[0]
+    assert torch.allclose(got, want, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("simt", [False, True], ids=["tcgen05", "cuda-core"])
+def test_selected_pair_rope_inside_the_low_width_read(simt):
+    """A 64-wide reader whose pairs are 32 selected native pairs of a 128-wide head."""
+    heads, width, native = 3, 64, 128
+    built = build(heads, width, 128, 400, 150, "bf16", 5, 6)
+    case, data, segments, positions, frame_seqlen, q = built
+    gen = torch.Generator().manual_seed(11)
+    pairs = torch.stack([torch.randperm(native // 2, generator=gen)[:width // 2].sort().values
+                         for _ in range(heads)])
+    indices = torch.stack((2 * pairs, 2 * pairs + 1), dim=2).reshape(heads, width)
+    ops_k, ops_v = device_operator(data["k_op"]), device_operator(data["v_op"])
+    hist_k = history_from_segments(segments["k"], joint=case.shape.joint, rank=case.shape.rank)
+    hist_v = history_from_segments(segments["v"], joint=case.shape.joint, rank=case.shape.rank)
+    freqs = oracle.rope_table(1024, native)
+    table = attention.RopeTable(freqs, frame_seqlen=frame_seqlen, width=6)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    view = table.view(positions.cuda(), pair_index_of(indices).cuda())
+    ops.force_simt(simt)
+    try:
+        out, lse = ops.attn_codec(
+            q.cuda(), hist_k.view(), hist_v.view(), ops_k.decoder.view(heads, width, -1),
+            ops_k.bias.view(heads, width), ops_v.decoder.view(heads, width, -1),
+            ops_v.bias.view(heads, width), scale=width ** -0.5, status=status, rope=view)
+        torch.cuda.synchronize()
+    finally:
+        ops.force_simt(False)
+    assert int(status.item()) == 0
+    k_op, v_op = data["k_op"], data["v_op"]
+    want, want_lse = oracle.codec_attention(
+        q[None], segments["k"], segments["v"], k_decoder=k_op["decoder"], k_mean=k_op["mean"],
+        v_decoder=v_op["decoder"], v_mean=v_op["mean"], heads=heads, dtype=torch.bfloat16,
+        rope=dict(positions=positions, freqs=freqs, frame_seqlen=frame_seqlen, width=6, indices=indices))
+    assert rel_err(out.cpu(), want[0]) <= BF16_REL_TOL
+    assert float((lse.cpu() - want_lse[0].t()).abs().max()) <= BF16_REL_TOL
+
+
+@pytest.mark.parametrize("case", cases.FAST_CASES, ids=lambda c: c.name)
+def test_hybrid_attention_with_selected_rope(case):
+    """NanoKV-Fast with real positional hooks: the reduced query and the low-width keys are
+    rotated with the native pairs each reader group keeps (LingBot's attend loop)."""
+    from helpers import F32_REL_TOL
+    from nanokv_b200 import codec
+    from test_oracle_golden import encode_all
+    data = cases.build(case.codec)
+    shape = case.codec.shape
+    dtype = shape.torch_dtype
+    segments = encode_all(case.codec, data)
+    frame_seqlen, width = 24, 6
+    freqs = oracle.rope_table(1024, shape.head_dim)
+    q_positions = torch.arange(5000, 5000 + shape.queries)
+    starts = [0]
+    for count in case.codec.segments:
+        starts.append(starts[-1] + count)
+    # oracle inputs (as in the fixture test) plus positions
+    low, native = [], []
+    for index in range(len(case.codec.segments)):
+        seg_k, seg_v = segments["k"][index], segments["v"][index]
+        if index < case.low_segments:
+            entry = {"positions": torch.arange(starts[index], starts[index + 1]) + 300}
+            for kind, seg in (("k", seg_k), ("v", seg_v)):
+                latent = oracle.dequantize_rows(seg["codes"], seg["scale"])[None]
+                entry[kind] = (latent, seg["centers"].float(), seg["ids"].long(), data[f"{kind}_op"]["mean"])
+            low.append(entry)
+        else:
+            pair = []
+            for kind, seg in (("k", seg_k), ("v", seg_v)):
+                op = data[f"{kind}_op"]
+                rows = oracle.decode_rows(seg, decoder=op["decoder"], mean=op["mean"], dtype=dtype)
+                pair.append(rows.reshape(1, -1, shape.heads, shape.head_dim).permute(0, 2, 1, 3))
+            native.append(tuple(pair))
+    reader_payload = cases.build_reader(case, data)
+    q = data["q"][None].permute(0, 2, 1, 3).contiguous()
+    want = oracle.hybrid_attention(q, q, native, low, reader_payload,
+                                   rope=dict(freqs=freqs, frame_seqlen=frame_seqlen, width=width,
+                                             q_positions=q_positions))[0]
+    # product path
+    ops_k, ops_v = device_operator(data["k_op"]), device_operator(data["v_op"])
+    n_low = case.low_segments
+    low_k = history_from_segments(segments["k"][:n_low], joint=shape.joint, rank=shape.rank)
+    low_v = history_from_segments(segments["v"][:n_low], joint=shape.joint, rank=shape.rank)
+    native_dev = [(k[0].permute(1, 0, 2).contiguous().cuda(), v[0].permute(1, 0, 2).contiguous().cuda())
+                  for k, v in native]
+    reader = attention.Reader(reader_payload, dtype=dtype)
+    table = attention.RopeTable(freqs, frame_seqlen=frame_seqlen, width=width)
+    low_positions = torch.cat([entry["positions"] for entry in low]).cuda()
+    got = attention.hybrid_attention(
+        data["q"].cuda(), data["q"].cuda(), native_dev,
+        [{"k": low_k, "v": low_v, "k_mean": ops_k.mean, "v_mean": ops_v.mean, "positions": low_positions}],
+        reader, rope=table, q_positions=q_positions.cuda())
+    tol = F32_REL_TOL if dtype == torch.float32 else BF16_REL_TOL
+    assert rel_err(got.cpu().permute(1, 0, 2), want) <= tol

@@ -163,3 +163,14 @@ def test_int8_operator_storage(name, group):
     assert np.array_equal(gold[f"{name}_scale"], scale.view(torch.int16).numpy())
     dense = oracle.unpack_int8_weight(codes, scale, group_size)
     assert np.array_equal(gold[f"{name}_dense"], dense.view(torch.int16).numpy())
+
+
+def test_rope_selected_pairs():
+    gold = load("rope_selected_bf16")
+    data = cases.build_rope_selected()
+    assert int(gold["value_digest"][0]) == checksum(data["value"]), "input generator drifted"
+    assert np.array_equal(gold["indices"], data["indices"].numpy())
+    freqs = oracle.rope_table(1024, data["native_dim"])
+    got = oracle.rope_selected(data["value"], data["positions"], freqs, frame_seqlen=data["frame_seqlen"],
+                               width=int(data["grid_sizes"][0, 2]), indices=data["indices"])
+    assert torch.equal(got.view(torch.int16), from_bits(gold["rotated"], torch.bfloat16).view(torch.int16))
