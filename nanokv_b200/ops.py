@@ -251,11 +251,54 @@ def rope_rows(x: torch.Tensor, rope: RopeView) -> torch.Tensor:
     return out
 
 
+_PLAIN_CACHE: dict = {}
+
+
+def _plain_history(k: torch.Tensor) -> HistoryView:
+    """Full-width rows [N,H,D] dressed as a compressed history the fused kernel rebuilds exactly:
+    rank-64 codes that all mean zero with zero scales (latent = 0), and the rows themselves as the
+    centre table with ids 0, 1, 2 ... (segments of 32,768 tokens keep the ids in 16 bits), so that
+    bf16(bf16(0 + 0) + centre) is the row."""
+    N, H, D = k.shape
+    key = (k.device, N)
+    if key not in _PLAIN_CACHE:
+        span = 32768
+        segments = max(1, -(-N // span))
+        index = torch.arange(N, device=k.device)
+        for stale in [name for name in _PLAIN_CACHE if isinstance(name[0], torch.device)][:-7]:
+            del _PLAIN_CACHE[stale]   # keep a handful of history lengths
+        _PLAIN_CACHE[key] = dict(
+            codes=torch.full((max(N, 1), 32), 0x77, dtype=torch.uint8, device=k.device),
+            scales=torch.zeros(max(N, 1), 1, dtype=torch.bfloat16, device=k.device),
+            ids=(index % span).to(torch.int16),
+            seg_start=torch.tensor([min(s * span, N) for s in range(segments + 1)], dtype=torch.int32,
+                                   device=k.device),
+            seg_center_row=torch.arange(segments, dtype=torch.int32, device=k.device) * span,
+            segments=segments)
+    c = _PLAIN_CACHE[key]
+    return HistoryView(codes=c["codes"], scales=c["scales"], ids=c["ids"], centers=k.view(N, H * D),
+                       seg_start=c["seg_start"], seg_center_row=c["seg_center_row"], tokens=N,
+                       segments=c["segments"], rank=64, group=64)
+
+
 def attention_lse(q, k, v, *, scale: float):
-    """Plain attention: q [Q,H,d], k [N,H,d], v [N,H,dv] -> (O [Q,H,dv], lse [Q,H])."""
+    """Plain attention: q [Q,H,d], k [N,H,d], v [N,H,dv] -> (O [Q,H,dv], lse [Q,H]).
+
+    bf16 rows of width 64 or 128 run on the tcgen05 kernel of the fused read (the rows enter as
+    its centre table, see ``_plain_history``); everything else on the fp32 CUDA-core kernel."""
     device = _require_cuda(q, k, v)
     Q, H, d = q.shape
     N, dv = k.shape[0], v.shape[2]
+    if (q.dtype == torch.bfloat16 and k.dtype == v.dtype == torch.bfloat16 and d == dv
+            and d in (64, 128) and N > 0 and k.is_contiguous() and v.is_contiguous()
+            and q.stride(2) == 1 and q.stride(0) % 8 == 0 and q.stride(1) % 8 == 0):
+        zero_w = _PLAIN_CACHE.setdefault(("w", device, H, d),
+                                         torch.zeros(H, d, 64, dtype=torch.bfloat16, device=device))
+        zero_b = _PLAIN_CACHE.setdefault(("b", device, H, d),
+                                         torch.zeros(H, d, dtype=torch.float32, device=device))
+        view_k = _plain_history(k)
+        view_v = _plain_history(v)
+        return attn_codec(q, view_k, view_v, zero_w, zero_b, zero_w, zero_b, scale=scale)
     out = torch.empty(Q, H, dv, dtype=q.dtype, device=device)
     lse = torch.empty(Q, H, dtype=torch.float32, device=device)
     if k.stride() != v.stride() and d == dv:
@@ -264,96 +307,6 @@ def attention_lse(q, k, v, *, scale: float):
         _ptr(q), _ptr(k), _ptr(v), dtype_code(q.dtype), q.stride(0), q.stride(1), k.stride(0),
         k.stride(1), Q, N, H, d, dv, float(scale), _ptr(out), _ptr(lse), _stream(device)))
     return out, lse
-
-
-def unpack_int8_weight(qweight: torch.Tensor, scale: torch.Tensor, group_size: int | None = None):
-    """INT8 operator storage -> bf16 weight: bf16(q) * scale per (row, group), one bf16 product.
-    qweight i8 [rows, cols]; scale bf16 [rows, cols / group] (or [rows, 1] / [rows] per row)."""
-    device = _require_cuda(qweight, scale)
-    if qweight.dtype != torch.int8 or qweight.dim() != 2:
-        raise ValueError("qweight must be an int8 matrix")
-    rows, cols = qweight.shape
-    group = cols if group_size in (None, 0) else int(group_size)
-    if group <= 0 or cols % group:
-        raise ValueError(f"INT8 group size {group} must divide {cols}")
-    scale = scale.to(torch.bfloat16).reshape(rows, -1).contiguous()
-    if scale.shape[1] != cols // group:
-        raise ValueError("scale shape does not match the group size")
-    out = torch.empty(rows, cols, dtype=torch.bfloat16, device=device)
-    _lib.check(_lib.library().nkv_operator_unpack_int8(
-        _ptr(qweight), _ptr(scale), rows, cols, group, _ptr(out), _stream(device)))
-    return out
-
-
-class PeerBuffer:
-    """A device buffer other processes of the box can map (nkv_peer_alloc / nkv_peer_open).
-
-    ``handle`` (64 bytes) is what a peer passes to :meth:`open`; tensors over the memory come from
-    :meth:`tensor`.  The owner frees on :meth:`release`, a peer unmaps."""
-
-    def __init__(self, pointer: int, nbytes: int, device: torch.device, handle: bytes | None):
-        self.pointer, self.nbytes, self.device, self.handle = pointer, nbytes, device, handle
-
-    @classmethod
-    def allocate(cls, nbytes: int, device) -> "PeerBuffer":
-        device = torch.device(device)
-        handle = ctypes.create_string_buffer(64)
-        pointer = ctypes.c_void_p()
-        with torch.cuda.device(device):
-            _lib.check(_lib.library().nkv_peer_alloc(int(nbytes), ctypes.byref(pointer), handle))
-        return cls(int(pointer.value), int(nbytes), device, handle.raw)
-
-    @classmethod
-    def open(cls, handle: bytes, nbytes: int, device) -> "PeerBuffer":
-        device = torch.device(device)
-        if len(handle) != 64:
-            raise ValueError("a peer handle is 64 bytes")
-        pointer = ctypes.c_void_p()
-        with torch.cuda.device(device):
-            _lib.check(_lib.library().nkv_peer_open(handle, ctypes.byref(pointer)))
-        return cls(int(pointer.value), int(nbytes), device, None)
-
-    def tensor(self, offset: int, shape, dtype: torch.dtype) -> torch.Tensor:
-        """Zero-copy tensor over [offset, offset + numel * itemsize) of the buffer."""
-        count = 1
-        for extent in shape:
-            count *= int(extent)
-        itemsize = torch.empty((), dtype=dtype).element_size()
-        if offset < 0 or offset + count * itemsize > self.nbytes:
-            raise ValueError("tensor window outside the peer buffer")
-        window = _CudaWindow(self.pointer + offset, count * itemsize, self)
-        flat = torch.as_tensor(window, device=self.device)
-        return flat.view(dtype).view(*shape)
-
-    def release(self) -> None:
-        if self.pointer:
-            lib = _lib.library()
-            with torch.cuda.device(self.device):
-                _lib.check(lib.nkv_peer_free(self.pointer) if self.handle is not None
-                           else lib.nkv_peer_close(self.pointer))
-            self.pointer = 0
-
-
-class _CudaWindow:
-    """__cuda_array_interface__ view (uint8) of a raw device range; keeps its owner alive."""
-
-    def __init__(self, pointer: int, nbytes: int, owner):
-        self.owner = owner
-        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1",
-                                         "data": (pointer, False), "version": 3, "strides": None}
-
-
-def cp_merge_peer(part_out_ptrs, part_lse_ptrs, dst_out_ptrs, dst_lse_ptrs, *, rows: int, width: int,
-                  row_begin: int, row_end: int, dtype: torch.dtype, device) -> None:
-    """Merge rows [row_begin, row_end) of every rank's partial and store them into every rank's
-    result buffer (nkv_cp_merge_peer).  The pointer lists are per rank, peers' as mapped here."""
-    world = len(part_out_ptrs)
-    arrays = [(ctypes.c_void_p * world)(*[int(v) for v in values])
-              for values in (part_out_ptrs, part_lse_ptrs, dst_out_ptrs, dst_lse_ptrs)]
-    device = torch.device(device)
-    _lib.check(_lib.library().nkv_cp_merge_peer(
-        arrays[0], arrays[1], arrays[2], arrays[3], world, int(rows), int(width), int(row_begin),
-        int(row_end), dtype_code(dtype), _stream(device)))
 
 
 def lse_merge(partials):

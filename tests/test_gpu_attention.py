@@ -220,3 +220,29 @@ def test_hybrid_attention_against_reference_fixture(case):
     want = from_bits(gold["hybrid"], dtype)                  # [H, Q, D]
     tol = F32_REL_TOL if dtype == torch.float32 else BF16_REL_TOL
     assert rel_err(got.cpu().permute(1, 0, 2), want) <= tol
+
+
+@pytest.mark.parametrize("heads,dim,tokens,queries", [(3, 128, 517, 300), (2, 64, 1, 1), (2, 128, 33000, 40)])
+def test_plain_attention_bf16_runs_on_the_fused_kernel(heads, dim, tokens, queries):
+    """bf16 plain attention (the Fast path's protected / current branch) enters the tcgen05 kernel
+    with the rows as an exact centre table; it must agree with the oracle and with the fp32
+    CUDA-core kernel, also past the 32,768-token segment boundary of the 16-bit ids."""
+    gen = torch.Generator().manual_seed(tokens)
+    q = torch.randn(queries, heads, dim, generator=gen).to(torch.bfloat16)
+    k = torch.randn(tokens, heads, dim, generator=gen).to(torch.bfloat16)
+    v = torch.randn(tokens, heads, dim, generator=gen).to(torch.bfloat16)
+    scale = dim ** -0.5
+    out, lse = ops.attention_lse(q.cuda(), k.cuda(), v.cuda(), scale=scale)
+    ops.force_simt(True)
+    try:
+        ref_out, ref_lse = ops.attention_lse(q.cuda(), k.cuda(), v.cuda(), scale=scale)
+    finally:
+        ops.force_simt(False)
+    torch.cuda.synchronize()
+    assert rel_err(out.cpu(), ref_out.cpu()) <= BF16_REL_TOL
+    assert float((lse - ref_lse).abs().max()) <= BF16_REL_TOL
+    if tokens <= 1000:
+        want, want_lse = oracle.attention_lse(q.permute(1, 0, 2)[None], k.permute(1, 0, 2)[None],
+                                              v.permute(1, 0, 2)[None], scale=scale)
+        assert rel_err(out.cpu(), want[0].permute(1, 0, 2)) <= BF16_REL_TOL
+        assert float((lse.cpu() - want_lse[0].t()).abs().max()) <= BF16_REL_TOL
