@@ -309,6 +309,96 @@ def attention_lse(q, k, v, *, scale: float):
     return out, lse
 
 
+def unpack_int8_weight(qweight: torch.Tensor, scale: torch.Tensor, group_size: int | None = None):
+    """INT8 operator storage -> bf16 weight: bf16(q) * scale per (row, group), one bf16 product.
+    qweight i8 [rows, cols]; scale bf16 [rows, cols / group] (or [rows, 1] / [rows] per row)."""
+    device = _require_cuda(qweight, scale)
+    if qweight.dtype != torch.int8 or qweight.dim() != 2:
+        raise ValueError("qweight must be an int8 matrix")
+    rows, cols = qweight.shape
+    group = cols if group_size in (None, 0) else int(group_size)
+    if group <= 0 or cols % group:
+        raise ValueError(f"INT8 group size {group} must divide {cols}")
+    scale = scale.to(torch.bfloat16).reshape(rows, -1).contiguous()
+    if scale.shape[1] != cols // group:
+        raise ValueError("scale shape does not match the group size")
+    out = torch.empty(rows, cols, dtype=torch.bfloat16, device=device)
+    _lib.check(_lib.library().nkv_operator_unpack_int8(
+        _ptr(qweight), _ptr(scale), rows, cols, group, _ptr(out), _stream(device)))
+    return out
+
+
+class PeerBuffer:
+    """A device buffer other processes of the box can map (nkv_peer_alloc / nkv_peer_open).
+
+    ``handle`` (64 bytes) is what a peer passes to :meth:`open`; tensors over the memory come from
+    :meth:`tensor`.  The owner frees on :meth:`release`, a peer unmaps."""
+
+    def __init__(self, pointer: int, nbytes: int, device: torch.device, handle: bytes | None):
+        self.pointer, self.nbytes, self.device, self.handle = pointer, nbytes, device, handle
+
+    @classmethod
+    def allocate(cls, nbytes: int, device) -> "PeerBuffer":
+        device = torch.device(device)
+        handle = ctypes.create_string_buffer(64)
+        pointer = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            _lib.check(_lib.library().nkv_peer_alloc(int(nbytes), ctypes.byref(pointer), handle))
+        return cls(int(pointer.value), int(nbytes), device, handle.raw)
+
+    @classmethod
+    def open(cls, handle: bytes, nbytes: int, device) -> "PeerBuffer":
+        device = torch.device(device)
+        if len(handle) != 64:
+            raise ValueError("a peer handle is 64 bytes")
+        pointer = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            _lib.check(_lib.library().nkv_peer_open(handle, ctypes.byref(pointer)))
+        return cls(int(pointer.value), int(nbytes), device, None)
+
+    def tensor(self, offset: int, shape, dtype: torch.dtype) -> torch.Tensor:
+        """Zero-copy tensor over [offset, offset + numel * itemsize) of the buffer."""
+        count = 1
+        for extent in shape:
+            count *= int(extent)
+        itemsize = torch.empty((), dtype=dtype).element_size()
+        if offset < 0 or offset + count * itemsize > self.nbytes:
+            raise ValueError("tensor window outside the peer buffer")
+        window = _CudaWindow(self.pointer + offset, count * itemsize, self)
+        flat = torch.as_tensor(window, device=self.device)
+        return flat.view(dtype).view(*shape)
+
+    def release(self) -> None:
+        if self.pointer:
+            lib = _lib.library()
+            with torch.cuda.device(self.device):
+                _lib.check(lib.nkv_peer_free(self.pointer) if self.handle is not None
+                           else lib.nkv_peer_close(self.pointer))
+            self.pointer = 0
+
+
+class _CudaWindow:
+    """__cuda_array_interface__ view (uint8) of a raw device range; keeps its owner alive."""
+
+    def __init__(self, pointer: int, nbytes: int, owner):
+        self.owner = owner
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1",
+                                         "data": (pointer, False), "version": 3, "strides": None}
+
+
+def cp_merge_peer(part_out_ptrs, part_lse_ptrs, dst_out_ptrs, dst_lse_ptrs, *, rows: int, width: int,
+                  row_begin: int, row_end: int, dtype: torch.dtype, device) -> None:
+    """Merge rows [row_begin, row_end) of every rank's partial and store them into every rank's
+    result buffer (nkv_cp_merge_peer).  The pointer lists are per rank, peers' as mapped here."""
+    world = len(part_out_ptrs)
+    arrays = [(ctypes.c_void_p * world)(*[int(v) for v in values])
+              for values in (part_out_ptrs, part_lse_ptrs, dst_out_ptrs, dst_lse_ptrs)]
+    device = torch.device(device)
+    _lib.check(_lib.library().nkv_cp_merge_peer(
+        arrays[0], arrays[1], arrays[2], arrays[3], world, int(rows), int(width), int(row_begin),
+        int(row_end), dtype_code(dtype), _stream(device)))
+
+
 def lse_merge(partials):
     """[(O [rows..., d], lse [rows...])] -> merged (O, lse); an empty partition is (0, -inf)."""
     outs = [o for o, _ in partials]

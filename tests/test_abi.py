@@ -59,3 +59,23 @@ def test_product_never_imports_the_oracle():
     for path in (ROOT / "nanokv_b200").rglob("*.py"):
         text = path.read_text()
         assert "oracle" not in text.replace("no CPU", ""), f"{path} mentions the oracle"
+
+
+def test_host_layer_exposes_a_wrapper_for_every_entry_point():
+    """Each C entry point has its host-side caller (an edit that drops one must fail here, on CPU)."""
+    from nanokv_b200 import attention, codec, context_parallel, lifecycle, mg_codec, ops
+    expected = {
+        ops: ["assign", "kmeans", "project", "quant_pack", "decode_rows", "attn_codec", "attention_lse",
+              "lse_merge", "rope_rows", "RopeView", "HistoryView", "unpack_int8_weight", "PeerBuffer",
+              "cp_merge_peer", "force_simt", "default_splits"],
+        attention: ["codec_attention", "merge", "RopeTable", "ReaderGroup", "Reader", "hybrid_attention"],
+        codec: ["Operator", "QuantSpec", "encode_append", "decode", "kmeans_init_rows"],
+        context_parallel: ["shard_bounds", "gather_partials", "merge_partials", "gather_and_merge",
+                           "PeerExchange"],
+        lifecycle: ["active_intervals", "kept_segments", "active_pieces", "RollingHistory"],
+        mg_codec: ["register_operator", "encode_tensor", "decode_tensor", "decode_value", "concat_values",
+                   "select_value", "value_shape", "payload_bytes", "history_from_payloads"],
+    }
+    for module, names in expected.items():
+        missing = [name for name in names if not hasattr(module, name)]
+        assert not missing, f"{module.__name__} lost {missing}"
