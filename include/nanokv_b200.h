@@ -355,6 +355,21 @@ int nkv_cp_merge_peer(const void* const* part_out, const float* const* part_lse,
 int nkv_operator_unpack_int8(const int8_t* qweight, const void* scale_bf16, int64_t rows, int cols,
                              int group, void* out_bf16, void* stream);
 
+/*
+ * First moments of a compressed history, without decoding it:
+ *   latent_sum[j]      = sum over tokens of the bf16 latent coefficient j (f32 [rank])
+ *   center_counts[row] = tokens assigned to centre row `row` (i32 [center_rows])
+ * from which the mean decoded value follows by linearity,
+ *   mean V = decoder (latent_sum / n) + bf16(mean) + (counts^T centres) / n,
+ * as the reference forms it for the value-mean residual of the NanoKV-Fast read
+ * (_compressed_value_mean wan/modules/codec_native_attention.py:465-501).
+ * Deterministic (fixed summation order).  workspace:
+ * nkv_history_moments_workspace_bytes(tokens, rank) bytes.
+ */
+size_t nkv_history_moments_workspace_bytes(int tokens, int rank);
+int nkv_history_moments(const nkv_history* hist, float* latent_sum, int32_t* center_counts,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

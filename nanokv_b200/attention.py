@@ -159,13 +159,40 @@ class Reader:
             raise ValueError("Reader groups must partition heads exactly once")
 
 
+def history_moments(low_segments):
+    """[(latent_sum f32 [r], centre counts f32 [rows], tokens)] of every low segment's V history."""
+    moments = []
+    for segment in low_segments:
+        view = _view(segment["v"])
+        latent_sum, counts = ops.history_moments(view)
+        moments.append((latent_sum, counts.float(), view.tokens))
+    return moments
+
+
+def compressed_value_mean(low_segments, moments, *, heads: int, native_dim: int) -> torch.Tensor:
+    """Mean decoded V over the low history, f32 [heads, native_dim], from the latent sums and centre
+    counts (never from decoded rows): decoder (sum latent / n) + bf16(mean) + (counts^T centres) / n
+    (LB/codec_native_attention.py:465-501)."""
+    first = low_segments[0]
+    total = sum(n for _, _, n in moments)
+    latent_sum = sum(ls for ls, _, _ in moments)
+    center_sum = sum(counts @ _view(seg["v"]).centers.float() for seg, (_, counts, _) in zip(low_segments, moments))
+    value = (torch.mv(first["v_decoder"].float(), latent_sum / total)
+             + first["v_mean"].to(torch.bfloat16).float() + center_sum / total)
+    return value.view(heads, native_dim)
+
+
 def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segments,
                      low_segments, reader: Reader, *, rope: "RopeTable | None" = None,
-                     q_positions: torch.Tensor | None = None):
+                     q_positions: torch.Tensor | None = None, value_mean_residual: bool = False):
     """Mixed-dimensional read (MGC/core.py:278-310).  Positional hooks are the identity unless
     ``rope`` is given: then the reduced query is rotated by ``q_positions`` and every low-width
     key read by its segment's ``"positions"``, with the native pairs the group retains
     (LB/codec_native_attention.py:757, :779); native keys and q_native arrive rotated.
+    ``value_mean_residual`` adds, for groups narrower than the head, the mean decoded V of the low
+    history minus the lifted mean of its low-width read (a first-moment correction, :726, :793-796);
+    every low segment then also carries ``"v_decoder"`` [J, r].  The low-width mean follows from the
+    same moments by linearity rather than from materialised rows.
 
     q_pre / q_native [Q,H,D]; native_segments [(K [n,H,D], V [n,H,D])] full
     width (protected history, current chunk); low_segments [{"k": history,
@@ -181,6 +208,10 @@ def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segment
                                      scale=scale)
         native_out, native_lse = ops.lse_merge([(native_out, native_lse), (out, lse)])
     result = torch.empty_like(q_native)
+    moments = value_mean = None
+    if value_mean_residual and low_segments:
+        moments = history_moments(low_segments)
+        value_mean = compressed_value_mean(low_segments, moments, heads=H, native_dim=reader.native_dim)
     for group in reader.groups:
         head = group.heads
         query = torch.einsum("nhd,hde->nhe", q_pre.index_select(1, head), group.q_reduce)
@@ -191,6 +222,19 @@ def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segment
             query = rope.rotate(query, q_positions, group.pair_index)
         out = native_out.index_select(1, head).contiguous()
         lse = native_lse.index_select(1, head).contiguous()
+        correction = None
+        if value_mean is not None and group.width < reader.native_dim:
+            # mean over the low tokens of the group's low-width V read, by linearity
+            total = sum(n for _, _, n in moments)
+            mean_low = torch.zeros(head.numel(), group.padded, device=q_native.device)
+            for segment, (latent_sum, counts, n) in zip(low_segments, moments):
+                table = group.projected_centers(segment["v"], "v").centers.float()
+                mean_low += (torch.einsum("her,r->he", group.v_read.float(), latent_sum)
+                             + n * group.bias(segment["v_mean"], "v")
+                             + (counts @ table).view(head.numel(), group.padded))
+            mean_low = (mean_low / total)[:, :group.width]
+            projected = torch.einsum("he,hed->hd", mean_low, group.lift.float())
+            correction = (value_mean.index_select(0, head) - projected)[None]
         for segment in low_segments:
             view_k = group.projected_centers(segment["k"], "k")
             view_v = group.projected_centers(segment["v"], "v")
@@ -199,6 +243,9 @@ def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segment
                 query, view_k, view_v, group.k_read, group.bias(segment["k_mean"], "k"),
                 group.v_read, group.bias(segment["v_mean"], "v"), scale=scale, rope=rope_view)
             lifted = torch.einsum("nhe,hed->nhd", oo[..., :group.width], group.lift).contiguous()
-            out, lse = ops.lse_merge([(out, lse), (lifted, ll)])
-        result.index_copy_(1, head, out)
+            if correction is not None:   # fp32 blend, one rounding, as the reference merges it
+                out, lse = ops.lse_merge([(out.float(), lse), (lifted.float() + correction, ll)])
+            else:
+                out, lse = ops.lse_merge([(out, lse), (lifted, ll)])
+        result.index_copy_(1, head, out.to(result.dtype))
     return result

@@ -392,4 +392,20 @@ int nkv_operator_unpack_int8(const int8_t* qweight, const void* scale_bf16, int6
                      static_cast<cudaStream_t>(stream));
 }
 
+size_t nkv_history_moments_workspace_bytes(int tokens, int rank) {
+  return history_moments_workspace_bytes(tokens, rank);
+}
+
+int nkv_history_moments(const nkv_history* hist, float* latent_sum, int32_t* center_counts,
+                        void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_history(hist, "moments");
+  if (rc != NKV_OK) return rc;
+  NKV_REQUIRE(latent_sum && center_counts, NKV_ERR_INVALID, "history_moments: null output");
+  NKV_REQUIRE(workspace_bytes >= history_moments_workspace_bytes(hist->tokens, hist->rank) &&
+                  (workspace != nullptr || hist->tokens == 0),
+              NKV_ERR_INVALID, "history_moments: workspace of %zu bytes is too small", workspace_bytes);
+  return history_moments(*hist, latent_sum, center_counts, workspace,
+                         static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -306,6 +306,44 @@ unpack_int8_kernel(const int8_t* q, const uint16_t* scale, long long rows, int c
   dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
 }
 
+// ---- first moments of a compressed history ---------------------------------------------------
+// latent_sum[j] = sum_t bf16((code[t][j] - 7) * scale[t][j / group]) and, per centre row, how many
+// tokens were assigned to it.  Stage 1: a block sums a slab of MOMENT_SLAB tokens, thread = one
+// code byte (two latent columns), and writes its partial row; counts are integer atomics (exact
+// in any order).  Stage 2 adds the partial rows in slab order, so the result is deterministic.
+constexpr int MOMENT_SLAB = 512;
+
+__global__ void __launch_bounds__(256)
+moments_partial_kernel(nkv_history h, float* partial, int* counts) {
+  const int slab = blockIdx.x;
+  const int t0 = slab * MOMENT_SLAB, t1 = min(h.tokens, t0 + MOMENT_SLAB);
+  const int row_bytes = h.rank >> 1, groups = h.rank / h.group;
+  for (int b = threadIdx.x; b < row_bytes; b += blockDim.x) {
+    float lo = 0.f, hi = 0.f;
+    const int g_lo = (2 * b) / h.group, g_hi = (2 * b + 1) / h.group;
+    for (int t = t0; t < t1; ++t) {
+      const uint8_t byte = h.codes[static_cast<size_t>(t) * row_bytes + b];
+      const float s_lo = load_float(h.scales, h.scale_dtype, static_cast<size_t>(t) * groups + g_lo);
+      const float s_hi = g_hi == g_lo ? s_lo
+                                      : load_float(h.scales, h.scale_dtype, static_cast<size_t>(t) * groups + g_hi);
+      lo += round_to_bf16(static_cast<float>(static_cast<int>(byte & 15u) - 7) * s_lo);
+      hi += round_to_bf16(static_cast<float>(static_cast<int>(byte >> 4) - 7) * s_hi);
+    }
+    partial[static_cast<size_t>(slab) * h.rank + 2 * b] = lo;
+    partial[static_cast<size_t>(slab) * h.rank + 2 * b + 1] = hi;
+  }
+  for (int t = t0 + threadIdx.x; t < t1; t += blockDim.x) atomicAdd(&counts[center_row_of(h, t)], 1);
+}
+
+__global__ void __launch_bounds__(256)
+moments_reduce_kernel(const float* partial, int slabs, int rank, float* latent_sum) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= rank) return;
+  float sum = 0.f;
+  for (int s = 0; s < slabs; ++s) sum += partial[static_cast<size_t>(s) * rank + j];
+  latent_sum[j] = sum;
+}
+
 }  // namespace
 
 int quant_pack(const void* coeff, int coeff_dtype, int S, int r, int group, float eps,
@@ -400,6 +438,27 @@ int unpack_int8(const int8_t* q, const void* scale_bf16, int64_t rows, int cols,
   unpack_int8_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
       q, static_cast<const uint16_t*>(scale_bf16), rows, cols, group, static_cast<uint16_t*>(out_bf16));
   NKV_LAUNCH_CHECK("unpack_int8_kernel");
+  return NKV_OK;
+}
+
+size_t history_moments_workspace_bytes(int tokens, int rank) {
+  const size_t slabs = (static_cast<size_t>(tokens > 0 ? tokens : 0) + MOMENT_SLAB - 1) / MOMENT_SLAB;
+  return slabs * static_cast<size_t>(rank) * sizeof(float);
+}
+
+int history_moments(const nkv_history& h, float* latent_sum, int32_t* center_counts, void* workspace,
+                    cudaStream_t stream) {
+  NKV_CUDA(cudaMemsetAsync(center_counts, 0, sizeof(int32_t) * static_cast<size_t>(h.center_rows), stream));
+  if (h.tokens == 0) {
+    NKV_CUDA(cudaMemsetAsync(latent_sum, 0, sizeof(float) * static_cast<size_t>(h.rank), stream));
+    return NKV_OK;
+  }
+  const int slabs = (h.tokens + MOMENT_SLAB - 1) / MOMENT_SLAB;
+  moments_partial_kernel<<<slabs, 256, 0, stream>>>(h, static_cast<float*>(workspace), center_counts);
+  NKV_LAUNCH_CHECK("moments_partial_kernel");
+  moments_reduce_kernel<<<(h.rank + 255) / 256, 256, 0, stream>>>(static_cast<const float*>(workspace),
+                                                                   slabs, h.rank, latent_sum);
+  NKV_LAUNCH_CHECK("moments_reduce_kernel");
   return NKV_OK;
 }
 

@@ -36,6 +36,9 @@ int quant_pack(const void* coeff, int coeff_dtype, int S, int r, int group, floa
                cudaStream_t stream);
 int lse_merge(const void* const* outs, const float* const* lses, int parts, int64_t rows,
               int d, int dtype, void* out, float* lse_out, cudaStream_t stream);
+size_t history_moments_workspace_bytes(int tokens, int rank);
+int history_moments(const nkv_history& h, float* latent_sum, int32_t* center_counts, void* workspace,
+                    cudaStream_t stream);
 int unpack_int8(const int8_t* q, const void* scale_bf16, int64_t rows, int cols, int group,
                 void* out_bf16, cudaStream_t stream);
 int cp_merge_peer(const void* const* part_out, const float* const* part_lse, void* const* dst_out,

@@ -309,6 +309,20 @@ def attention_lse(q, k, v, *, scale: float):
     return out, lse
 
 
+def history_moments(view: HistoryView):
+    """(latent_sum f32 [rank], center_counts i32 [centre rows]) of a history (nkv_history_moments)."""
+    device = _require_cuda(view.codes)
+    lib = _lib.library()
+    latent_sum = torch.empty(view.rank, dtype=torch.float32, device=device)
+    counts = torch.empty(view.centers.shape[0], dtype=torch.int32, device=device)
+    nbytes = lib.nkv_history_moments_workspace_bytes(view.tokens, view.rank)
+    workspace = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
+    struct = view.struct()
+    _lib.check(lib.nkv_history_moments(ctypes.byref(struct), _ptr(latent_sum), _ptr(counts),
+                                       _ptr(workspace), nbytes, _stream(device)))
+    return latent_sum, counts
+
+
 def unpack_int8_weight(qweight: torch.Tensor, scale: torch.Tensor, group_size: int | None = None):
     """INT8 operator storage -> bf16 weight: bf16(q) * scale per (row, group), one bf16 product.
     qweight i8 [rows, cols]; scale bf16 [rows, cols / group] (or [rows, 1] / [rows] per row)."""

@@ -413,12 +413,35 @@ def reader_read(group: dict, latent, centers, ids, mean, *, target: str, dtype,
     return output + assigned
 
 
-def hybrid_attention(q_pre, q_native, native_segments, low_segments, reader: dict, rope=None):
+def compressed_value_mean(low_segments, *, decoder: torch.Tensor, heads: int, native_dim: int):
+    """Mean decoded V over the low history from latent sums and centre counts, fp32
+    (LB/codec_native_attention.py:465-501): decoder (sum latent / n) + bf16(mean) + (counts^T
+    centres) / n, as [B, heads, 1, native_dim]."""
+    latent_sum = center_sum = None
+    count = 0
+    for item in low_segments:
+        latent, centers, ids, mean = item["v"]
+        counts = torch.zeros(centers.shape[:2], dtype=torch.float32)
+        counts.scatter_add_(1, ids, torch.ones_like(ids, dtype=torch.float32))
+        ls = latent.float().sum(1)
+        cs = torch.einsum("bc,bcd->bd", counts, centers.float())
+        latent_sum = ls if latent_sum is None else latent_sum + ls
+        center_sum = cs if center_sum is None else center_sum + cs
+        count += latent.shape[1]
+    value = F.linear(latent_sum / count, decoder.float(), mean.to(torch.bfloat16).float()) + center_sum / count
+    return value.reshape(latent_sum.shape[0], heads, 1, native_dim)
+
+
+def hybrid_attention(q_pre, q_native, native_segments, low_segments, reader: dict, rope=None,
+                     value_mean=None):
     """Mixed-dimensional read; positional hooks are the identity unless ``rope`` is given.
 
     ``rope`` = dict(freqs, frame_seqlen, width, q_positions): the reduced query and every
     low-width key read are rotated with the native pairs the group retains (group["indices"]),
     by q_positions and segment["positions"] (LB/codec_native_attention.py:757, :779).
+    ``value_mean`` [B,H,1,D] switches on the value-mean residual of groups narrower than the head:
+    lifted + value_mean[heads] - lift(mean over tokens of the low-width V), in fp32 (:793-796); it
+    applies to the single joined low partition, as the reference concatenates its segments.
 
     q_* [B,H,Q,D]; native_segments [(K,V)] full-width [B,H,n,D]; low_segments
     [{"k": (latent, centers, ids, mean), "v": (...)}]; reader {"native_dim",
@@ -444,6 +467,24 @@ def hybrid_attention(q_pre, q_native, native_segments, low_segments, reader: dic
                                   indices=group["indices"])
         out = native_out.index_select(1, head)
         lse = native_lse.index_select(1, head)
+        if value_mean is not None:   # LingBot's form: one joined low partition per group
+            kk = torch.cat([reader_read(group, *seg["k"], target="k", dtype=dtype, native_dim=native_dim)
+                            for seg in low_segments], dim=2)
+            vv = torch.cat([reader_read(group, *seg["v"], target="v", dtype=dtype, native_dim=native_dim)
+                            for seg in low_segments], dim=2)
+            if rope is not None:
+                kk = rope_selected(kk, torch.cat([seg["positions"] for seg in low_segments]),
+                                   rope["freqs"], frame_seqlen=rope["frame_seqlen"],
+                                   width=rope["width"], indices=group["indices"])
+            oo, ll = attention_lse(query, kk, vv, scale=scale)
+            lifted = torch.einsum("bhne,hed->bhnd", oo, group["lift"].to(dtype))
+            if group["lift"].shape[1] < native_dim:
+                projected = torch.einsum("bhse,hed->bhsd", vv.float().mean(2, keepdim=True),
+                                         group["lift"].to(dtype).float())
+                lifted = lifted.float() + value_mean.index_select(1, head) - projected
+            out, lse = merge(out, lse, lifted, ll)
+            result.index_copy_(1, head, out.to(dtype))
+            continue
         for segment in low_segments:
             kk = reader_read(group, *segment["k"], target="k", dtype=dtype, native_dim=native_dim)
             vv = reader_read(group, *segment["v"], target="v", dtype=dtype, native_dim=native_dim)

@@ -171,3 +171,9 @@ def build_rope_selected():
     positions = torch.cat([torch.arange(25), torch.arange(700, 765)])
     return {"value": value, "indices": indices, "positions": positions, "frame_seqlen": 35,
             "grid_sizes": torch.tensor([[40, 5, 7]]), "native_dim": native}
+
+
+def value_mean_interval(case: CodecCase, index: int) -> tuple[int, int]:
+    """Local token interval of segment ``index`` that belongs to the low history."""
+    count = case.segments[index]
+    return (17, count) if index == 0 else (0, count)

@@ -266,6 +266,32 @@ def run_rope_selected_case(root) -> dict:
             "indices": data["indices"].numpy()}
 
 
+def run_value_mean_case(case: cases.CodecCase, root) -> dict:
+    """_compressed_value_mean of the LingBot Fast module over the V payloads of a rolling case:
+    the first segment cut to an interval, the others whole."""
+    codec = ref_import.load_lingbot_codec(root)
+    load_lingbot_runtime(root)
+    fast = ref_import._load("wan.modules.codec_native_attention",
+                            root / ref_import.LB / "wan/modules/codec_native_attention.py")
+    data = cases.build(case)
+    heads, dim = case.shape.heads, case.shape.head_dim
+    op = data["v_op"]
+    ref_import.inject_lingbot_operator(
+        codec, "synthetic", "v", case.layer, joint_dim=case.shape.joint, rank=case.shape.rank,
+        mean=op["mean"], encoder=op["encoder"], decoder=op["decoder"])
+    low = []
+    for index, chunk in enumerate(data["v_chunks"]):
+        payload = codec.encode_tensor(
+            chunk.reshape(1, -1, heads, dim), target="v", layer=case.layer, sp_rank=0,
+            basis_root="synthetic", rank=case.shape.rank, clusters=case.shape.centers, iters=case.iters)
+        lo, hi = cases.value_mean_interval(case, index)
+        low.append({"v": codec.direct_latent_slice(payload, lo, hi, device=torch.device("cpu")),
+                    "v_payload": payload, "bounds": (lo, hi)})
+    value = fast._compressed_value_mean(low, torch.device("cpu"), None)
+    return {"value_mean": value.numpy(),
+            "input_digest": np.array([checksum(torch.cat(data["v_chunks"]))], dtype=np.uint64)}
+
+
 def run_int8_operator_case(root) -> dict:
     """The reference's INT8 operator packing and the bf16 weight it multiplies with."""
     codec = ref_import.load_mg_codec(root)
@@ -325,6 +351,7 @@ def main() -> None:
     save("merge_edge", lambda: run_merge_case(root))
     save("select_mg_bf16", lambda: run_select_case(cases.MINI_BF16, root))
     save("rope_selected_bf16", lambda: run_rope_selected_case(root))
+    save("value_mean_lb_bf16", lambda: run_value_mean_case(cases.ROLLING, root))
     save("int8_operator", lambda: run_int8_operator_case(root))
     save(cases.ROLLING.name, lambda: run_rolling_case(cases.ROLLING, root))
     for case in cases.ROPE_CASES:

@@ -246,3 +246,62 @@ def test_plain_attention_bf16_runs_on_the_fused_kernel(heads, dim, tokens, queri
                                               v.permute(1, 0, 2)[None], scale=scale)
         assert rel_err(out.cpu(), want[0].permute(1, 0, 2)) <= BF16_REL_TOL
         assert float((lse.cpu() - want_lse[0].t()).abs().max()) <= BF16_REL_TOL
+
+
+def test_history_moments_match_the_oracle():
+    case = cases.MINI_BF16
+    data, segments = oracle_segments(case)
+    hist = history_from_segments(segments["v"], joint=case.shape.joint, rank=case.shape.rank)
+    latent_sum, counts = ops.history_moments(hist.view())
+    want_sum = sum(oracle.dequantize_rows(s["codes"], s["scale"]).float().sum(0) for s in segments["v"])
+    assert torch.allclose(latent_sum.cpu(), want_sum.reshape(-1), rtol=1e-5, atol=1e-4)
+    want_counts = torch.cat([torch.bincount(s["ids"].reshape(-1).long(), minlength=case.shape.centers)
+                             for s in segments["v"]])
+    assert torch.equal(counts.cpu()[:want_counts.numel()].long(), want_counts)
+    again, _ = ops.history_moments(hist.view())
+    assert torch.equal(again, latent_sum)                      # fixed summation order
+
+
+@pytest.mark.parametrize("case", cases.FAST_CASES, ids=lambda c: c.name)
+def test_hybrid_attention_value_mean_residual(case):
+    """First-moment correction of the groups narrower than the head (LingBot's opt-in residual)."""
+    codec_case = case.codec
+    shape = codec_case.shape
+    dtype = shape.torch_dtype
+    data, segments = oracle_segments(codec_case)
+    n_low = case.low_segments
+    low, native = [], []
+    for index in range(len(codec_case.segments)):
+        seg_k, seg_v = segments["k"][index], segments["v"][index]
+        if index < n_low:
+            entry = {}
+            for kind, seg in (("k", seg_k), ("v", seg_v)):
+                latent = oracle.dequantize_rows(seg["codes"], seg["scale"])[None]
+                entry[kind] = (latent, seg["centers"].float(), seg["ids"].long(), data[f"{kind}_op"]["mean"])
+            low.append(entry)
+        else:
+            pair = []
+            for kind, seg in (("k", seg_k), ("v", seg_v)):
+                op = data[f"{kind}_op"]
+                rows = oracle.decode_rows(seg, decoder=op["decoder"], mean=op["mean"], dtype=dtype)
+                pair.append(rows.reshape(1, -1, shape.heads, shape.head_dim).permute(0, 2, 1, 3))
+            native.append(tuple(pair))
+    reader_payload = cases.build_reader(case, data)
+    q = data["q"][None].permute(0, 2, 1, 3).contiguous()
+    value_mean = oracle.compressed_value_mean(low, decoder=data["v_op"]["decoder"].to(dtype),
+                                              heads=shape.heads, native_dim=shape.head_dim)
+    want = oracle.hybrid_attention(q, q, native, low, reader_payload, value_mean=value_mean)[0]
+    plain = oracle.hybrid_attention(q, q, native, low, reader_payload)[0]
+    ops_k, ops_v = device_operator(data["k_op"]), device_operator(data["v_op"])
+    low_k = history_from_segments(segments["k"][:n_low], joint=shape.joint, rank=shape.rank)
+    low_v = history_from_segments(segments["v"][:n_low], joint=shape.joint, rank=shape.rank)
+    native_dev = [(k[0].permute(1, 0, 2).contiguous().cuda(), v[0].permute(1, 0, 2).contiguous().cuda())
+                  for k, v in native]
+    reader = attention.Reader(reader_payload, dtype=dtype)
+    got = attention.hybrid_attention(
+        data["q"].cuda(), data["q"].cuda(), native_dev,
+        [{"k": low_k, "v": low_v, "k_mean": ops_k.mean, "v_mean": ops_v.mean, "v_decoder": ops_v.decoder}],
+        reader, value_mean_residual=True)
+    tol = F32_REL_TOL if dtype == torch.float32 else BF16_REL_TOL
+    assert rel_err(got.cpu().permute(1, 0, 2), want) <= tol
+    assert rel_err(plain, want) > 2 * tol, "the correction must matter in this case"

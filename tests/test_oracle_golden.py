@@ -174,3 +174,20 @@ def test_rope_selected_pairs():
     got = oracle.rope_selected(data["value"], data["positions"], freqs, frame_seqlen=data["frame_seqlen"],
                                width=int(data["grid_sizes"][0, 2]), indices=data["indices"])
     assert torch.equal(got.view(torch.int16), from_bits(gold["rotated"], torch.bfloat16).view(torch.int16))
+
+
+def test_compressed_value_mean():
+    gold = load("value_mean_lb_bf16")
+    case = cases.ROLLING
+    data = cases.build(case)
+    assert int(gold["input_digest"][0]) == checksum(torch.cat(data["v_chunks"])), "input generator drifted"
+    segments = encode_all(case, data, lingbot=True)["v"]
+    low = []
+    for index, seg in enumerate(segments):
+        lo, hi = cases.value_mean_interval(case, index)
+        latent = oracle.dequantize_rows(seg["codes"], seg["scale"])[None][:, lo:hi]
+        low.append({"v": (latent, seg["centers"][None] if seg["centers"].dim() == 2 else seg["centers"],
+                          seg["ids"].long().reshape(1, -1)[:, lo:hi], data["v_op"]["mean"])})
+    got = oracle.compressed_value_mean(low, decoder=data["v_op"]["decoder"], heads=case.shape.heads,
+                                       native_dim=case.shape.head_dim)
+    assert np.array_equal(gold["value_mean"], got.numpy())
