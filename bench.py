@@ -591,6 +591,77 @@ def run_streaming(args) -> dict:
             "encode_tokens_per_s_incl_attention": chunks * FRAME / seconds}
 
 
+def run_aux(args) -> dict:
+    """The HBM-bound helpers around the read, one GPU, c3 shapes: INT8 operator expansion, first
+    moments of a 99,840-token history, rotation of the 4,680 query rows, the P-way merge, and the
+    rolling-window prune.  Each is timed alone with CUDA events (inputs larger than L2 or an L2
+    flush between iterations) and reported in GB/s of its algorithmic bytes against the measured
+    copy bandwidth."""
+    from nanokv_b200 import attention, ops
+    shape = SHAPE
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    peaks, peak_kind = measured_peaks()
+    hbm = float(peaks["hbm_gbs"])
+    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=device)
+    gen = torch.Generator(device=device).manual_seed(5)
+
+    def timed(fn, steps=args.steps, warmup=max(args.warmup, 3)):
+        times = []
+        for index in range(warmup + steps):
+            flush.fill_(index & 255)                      # evict L2 between iterations
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            stop.record()
+            torch.cuda.synchronize()
+            if index >= warmup:
+                times.append(start.elapsed_time(stop))
+        return statistics.mean(times) / 1e3
+
+    results = {}
+
+    def report(name, seconds, nbytes):
+        results[name] = {"ms": seconds * 1e3, "gbs": nbytes / seconds / 1e9,
+                         "frac_of_hbm": nbytes / seconds / 1e9 / hbm, "bytes": nbytes}
+
+    # INT8 operator -> bf16: one decoder [J, r]
+    q8 = torch.randint(-127, 128, (shape.joint, shape.rank), generator=gen, device=device, dtype=torch.int8)
+    scale = torch.rand(shape.joint, 1, generator=gen, device=device).to(torch.bfloat16)
+    report("operator_unpack_int8", timed(lambda: ops.unpack_int8_weight(q8, scale)),
+           q8.numel() * 3 + scale.numel() * 2)
+    # first moments of one layer's V history
+    layer = build_layers(shape, range(shape.history // FRAME), 1, device)[0]
+    (hk, ok), (hv, ov) = layer["k"], layer["v"]
+    view = hv.view()
+    per_token = shape.rank // 2 + 2 + hv.ids.element_size()
+    report("history_moments", timed(lambda: ops.history_moments(view)), view.tokens * per_token)
+    # rotation of the query rows
+    table = attention.RopeTable(rope_freqs(1024, shape.head_dim), frame_seqlen=FRAME, width=52, device=device)
+    q = synthetic.make_queries(shape, synthetic.generator(1)).to(device)
+    positions = torch.arange(90000, 90000 + shape.queries, dtype=torch.int32, device=device)
+    report("rope_rows", timed(lambda: table.rotate(q, positions)), q.numel() * 2 * 2)
+    # four-way merge of (O, lse) partials
+    parts = [(torch.randn(shape.queries, shape.heads, shape.head_dim, generator=gen, device=device)
+              .to(torch.bfloat16), torch.randn(shape.queries, shape.heads, generator=gen, device=device))
+             for _ in range(4)]
+    report("lse_merge_4way", timed(lambda: ops.lse_merge(parts)),
+           5 * parts[0][0].numel() * 2 + 5 * parts[0][1].numel() * 4)
+    # rolling-window prune: drop the oldest non-sink segments of the history (device copies only)
+    keep = [0] + list(range(3, hk.segments))
+    moved = (hk.tokens - hk._starts[3]) * per_token
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    hk.retain(keep)
+    stop.record()
+    torch.cuda.synchronize()
+    report("prune_retain", start.elapsed_time(stop) / 1e3, 2 * moved)
+    return {"metric": "aux_kernels", "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "dtype": "u8/bf16", "data": "synthetic",
+            "config": {"workload": "aux", "shape": shape.name, "l2_policy": "192 MiB flush between iterations"},
+            "peak": hbm, "peak_source": f"hbm_gbs of {peak_kind}", "kernels": results}
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -604,8 +675,8 @@ def main() -> None:
     parser.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                         help="context-parallel exchange: fused peer-memory kernel, or NCCL all-gather + merge")
     parser.add_argument("--workload", default="c3_wan_shaped",
-                        choices=["c3_wan_shaped", "c4_fast_mixed", "c5_streaming"],
-                        help="c3 is the headline; c4 / c5 are secondary measurements")
+                        choices=["c3_wan_shaped", "c4_fast_mixed", "c5_streaming", "aux"],
+                        help="c3 is the headline; c4 / c5 / aux are secondary measurements")
     parser.add_argument("--chunks", type=int, default=256, help="c5: chunks streamed")
     args = parser.parse_args()
     if args.impl == "reference":
@@ -614,6 +685,8 @@ def main() -> None:
         line = run_fast(args)
     elif args.workload == "c5_streaming":
         line = run_streaming(args)
+    elif args.workload == "aux":
+        line = run_aux(args)
     else:
         line = run_ours(args)
     if line:

@@ -182,10 +182,11 @@ __device__ __forceinline__ VEC peer_load(const void* base, size_t byte_offset) {
   return *reinterpret_cast<const VEC*>(static_cast<const char*>(base) + byte_offset);
 }
 
-// thread = (row, 8 consecutive columns)
-template <int DTYPE>
+// thread = (row, 8 consecutive columns); MAXP bounds the unrolled part loops (registers)
+template <int DTYPE, int MAXP>
 __global__ void __launch_bounds__(256)
-cp_merge_peer_kernel(PeerMergeArgs args, int world, long long row_begin, long long row_end, int d) {
+cp_merge_peer_kernel(PeerMergeArgs args, int world, int dests, long long row_begin, long long row_end,
+                     int d) {
   const int per_row = d >> 3;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= (row_end - row_begin) * per_row) return;
@@ -193,67 +194,63 @@ cp_merge_peer_kernel(PeerMergeArgs args, int world, long long row_begin, long lo
   const int col = static_cast<int>(idx % per_row) * 8;
   const size_t elem = static_cast<size_t>(row) * d + col;
 
-  float part_lse[MAX_PARTS];
+  // every load is issued before the transcendental arithmetic of the fold
+  constexpr int VECS = DTYPE == NKV_F32 ? 2 : 1;
+  uint4 raw[MAXP][VECS];
+  float part_lse[MAXP];
 #pragma unroll
-  for (int p = 0; p < MAX_PARTS; ++p) part_lse[p] = p < world ? args.part_lse[p][row] : 0.f;
+  for (int p = 0; p < MAXP; ++p)
+    if (p < world) {
+      part_lse[p] = args.part_lse[p][row];
+#pragma unroll
+      for (int v = 0; v < VECS; ++v)
+        raw[p][v] = peer_load<uint4>(args.part_out[p], elem * (DTYPE == NKV_F32 ? 4 : 2) + 16 * v);
+    }
   float lse = part_lse[0];
 #pragma unroll
-  for (int p = 1; p < MAX_PARTS; ++p)
+  for (int p = 1; p < MAXP; ++p)
     if (p < world) lse = logaddexp(lse, part_lse[p]);
   const float origin = isfinite(lse) ? lse : 0.f;
 
   float acc[8];
-  if (DTYPE == NKV_F32) {
-    float4 lo[MAX_PARTS], hi[MAX_PARTS];
 #pragma unroll
-    for (int p = 0; p < MAX_PARTS; ++p)
-      if (p < world) {
-        lo[p] = peer_load<float4>(args.part_out[p], elem * 4);
-        hi[p] = peer_load<float4>(args.part_out[p], elem * 4 + 16);
-      }
+  for (int p = 0; p < MAXP; ++p)
+    if (p < world) {
+      const float w = expf(part_lse[p] - origin);
+      float v[8];
+      if (DTYPE == NKV_F32) {
+        const uint32_t words[8] = {raw[p][0].x, raw[p][0].y, raw[p][0].z, raw[p][0].w,
+                                   raw[p][VECS - 1].x, raw[p][VECS - 1].y, raw[p][VECS - 1].z, raw[p][VECS - 1].w};
 #pragma unroll
-    for (int p = 0; p < MAX_PARTS; ++p)
-      if (p < world) {
-        const float w = expf(part_lse[p] - origin);
-        const float v[8] = {lo[p].x, lo[p].y, lo[p].z, lo[p].w, hi[p].x, hi[p].y, hi[p].z, hi[p].w};
+        for (int c = 0; c < 8; ++c) v[c] = __uint_as_float(words[c]);
+      } else {
+        const uint32_t words[4] = {raw[p][0].x, raw[p][0].y, raw[p][0].z, raw[p][0].w};
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const float t = __fmul_rn(v[c], w);
-          acc[c] = p == 0 ? t : __fadd_rn(acc[c], t);
+        for (int k = 0; k < 4; ++k) {
+          if (DTYPE == NKV_BF16) {
+            v[2 * k] = __uint_as_float(words[k] << 16);
+            v[2 * k + 1] = __uint_as_float(words[k] & 0xFFFF0000u);
+          } else {
+            v[2 * k] = __half2float(__ushort_as_half(static_cast<uint16_t>(words[k] & 0xFFFFu)));
+            v[2 * k + 1] = __half2float(__ushort_as_half(static_cast<uint16_t>(words[k] >> 16)));
+          }
         }
       }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float t = __fmul_rn(v[c], w);
+        acc[c] = p == 0 ? t : __fadd_rn(acc[c], t);
+      }
+    }
+  if (DTYPE == NKV_F32) {
     const float4 out_lo = make_float4(acc[0], acc[1], acc[2], acc[3]);
     const float4 out_hi = make_float4(acc[4], acc[5], acc[6], acc[7]);
-    for (int r = 0; r < world; ++r) {
+    for (int r = 0; r < dests; ++r) {
       float4* dst = reinterpret_cast<float4*>(static_cast<char*>(args.dst_out[r]) + elem * 4);
       dst[0] = out_lo;
       dst[1] = out_hi;
     }
   } else {
-    uint4 raw[MAX_PARTS];
-#pragma unroll
-    for (int p = 0; p < MAX_PARTS; ++p)
-      if (p < world) raw[p] = peer_load<uint4>(args.part_out[p], elem * 2);
-#pragma unroll
-    for (int p = 0; p < MAX_PARTS; ++p)
-      if (p < world) {
-        const float w = expf(part_lse[p] - origin);
-        const uint32_t words[4] = {raw[p].x, raw[p].y, raw[p].z, raw[p].w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          float v0, v1;
-          if (DTYPE == NKV_BF16) {
-            v0 = __uint_as_float(words[k] << 16);
-            v1 = __uint_as_float(words[k] & 0xFFFF0000u);
-          } else {
-            v0 = __half2float(__ushort_as_half(static_cast<uint16_t>(words[k] & 0xFFFFu)));
-            v1 = __half2float(__ushort_as_half(static_cast<uint16_t>(words[k] >> 16)));
-          }
-          const float t0 = __fmul_rn(v0, w), t1 = __fmul_rn(v1, w);
-          acc[2 * k] = p == 0 ? t0 : __fadd_rn(acc[2 * k], t0);
-          acc[2 * k + 1] = p == 0 ? t1 : __fadd_rn(acc[2 * k + 1], t1);
-        }
-      }
     uint32_t packed[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -268,11 +265,24 @@ cp_merge_peer_kernel(PeerMergeArgs args, int world, long long row_begin, long lo
       packed[k] = lo16 | (hi16 << 16);
     }
     const uint4 out = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-    for (int r = 0; r < world; ++r)
+    for (int r = 0; r < dests; ++r)
       *reinterpret_cast<uint4*>(static_cast<char*>(args.dst_out[r]) + elem * 2) = out;
   }
   if (col == 0)
-    for (int r = 0; r < world; ++r) args.dst_lse[r][row] = lse;
+    for (int r = 0; r < dests; ++r) args.dst_lse[r][row] = lse;
+}
+
+template <int DTYPE>
+void launch_merge(const PeerMergeArgs& args, int parts, int dests, long long row_begin, long long row_end,
+                  int d, cudaStream_t stream) {
+  const long long total = (row_end - row_begin) * (d >> 3);
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  if (parts <= 4)
+    cp_merge_peer_kernel<DTYPE, 4><<<blocks, 256, 0, stream>>>(args, parts, dests, row_begin, row_end, d);
+  else if (parts <= 8)
+    cp_merge_peer_kernel<DTYPE, 8><<<blocks, 256, 0, stream>>>(args, parts, dests, row_begin, row_end, d);
+  else
+    cp_merge_peer_kernel<DTYPE, MAX_PARTS><<<blocks, 256, 0, stream>>>(args, parts, dests, row_begin, row_end, d);
 }
 
 // ---- INT8 operator storage -> resident bf16 --------------------------------------------------
@@ -311,7 +321,7 @@ unpack_int8_kernel(const int8_t* q, const uint16_t* scale, long long rows, int c
 // tokens were assigned to it.  Stage 1: a block sums a slab of MOMENT_SLAB tokens, thread = one
 // code byte (two latent columns), and writes its partial row; counts are integer atomics (exact
 // in any order).  Stage 2 adds the partial rows in slab order, so the result is deterministic.
-constexpr int MOMENT_SLAB = 512;
+constexpr int MOMENT_SLAB = 128;
 
 __global__ void __launch_bounds__(256)
 moments_partial_kernel(nkv_history h, float* partial, int* counts) {
@@ -321,6 +331,7 @@ moments_partial_kernel(nkv_history h, float* partial, int* counts) {
   for (int b = threadIdx.x; b < row_bytes; b += blockDim.x) {
     float lo = 0.f, hi = 0.f;
     const int g_lo = (2 * b) / h.group, g_hi = (2 * b + 1) / h.group;
+#pragma unroll 8
     for (int t = t0; t < t1; ++t) {
       const uint8_t byte = h.codes[static_cast<size_t>(t) * row_bytes + b];
       const float s_lo = load_float(h.scales, h.scale_dtype, static_cast<size_t>(t) * groups + g_lo);
@@ -335,13 +346,22 @@ moments_partial_kernel(nkv_history h, float* partial, int* counts) {
   for (int t = t0 + threadIdx.x; t < t1; t += blockDim.x) atomicAdd(&counts[center_row_of(h, t)], 1);
 }
 
+// block = 8 latent columns; 32 thread groups stride over the slabs, then a fixed-order tree
 __global__ void __launch_bounds__(256)
 moments_reduce_kernel(const float* partial, int slabs, int rank, float* latent_sum) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= rank) return;
+  __shared__ float tree[32][8];
+  const int c = threadIdx.x & 7, lane = threadIdx.x >> 3;
+  const int j = blockIdx.x * 8 + c;
   float sum = 0.f;
-  for (int s = 0; s < slabs; ++s) sum += partial[static_cast<size_t>(s) * rank + j];
-  latent_sum[j] = sum;
+  if (j < rank)
+    for (int s = lane; s < slabs; s += 32) sum += partial[static_cast<size_t>(s) * rank + j];
+  tree[lane][c] = sum;
+  __syncthreads();
+  for (int width = 16; width >= 1; width >>= 1) {
+    if (lane < width) tree[lane][c] += tree[lane + width][c];
+    __syncthreads();
+  }
+  if (lane == 0 && j < rank) latent_sum[j] = tree[0][c];
 }
 
 }  // namespace
@@ -383,6 +403,19 @@ int lse_merge(const void* const* outs, const float* const* lses, int parts, int6
               "lse merge takes 1..%d partitions, got %d", MAX_PARTS, parts);
   NKV_REQUIRE(d % 4 == 0, NKV_ERR_INVALID, "merge width %d must be a multiple of 4", d);
   if (rows == 0) return NKV_OK;
+  bool vector = d % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+                (dtype == NKV_F32 || dtype == NKV_BF16);
+  for (int p = 0; p < parts; ++p) vector = vector && (reinterpret_cast<uintptr_t>(outs[p]) & 15) == 0;
+  if (vector) {   // 16-byte loads and stores: the peer-merge kernel with one local destination
+    PeerMergeArgs wide{};
+    for (int p = 0; p < parts; ++p) { wide.part_out[p] = outs[p]; wide.part_lse[p] = lses[p]; }
+    wide.dst_out[0] = out;
+    wide.dst_lse[0] = lse_out;
+    if (dtype == NKV_F32) launch_merge<NKV_F32>(wide, parts, 1, 0, rows, d, stream);
+    else launch_merge<NKV_BF16>(wide, parts, 1, 0, rows, d, stream);
+    NKV_LAUNCH_CHECK("cp_merge_peer_kernel");
+    return NKV_OK;
+  }
   MergeArgs args{};
   for (int p = 0; p < parts; ++p) { args.outs[p] = outs[p]; args.lses[p] = lses[p]; }
   long long total = rows * (d >> 2);
@@ -413,14 +446,9 @@ int cp_merge_peer(const void* const* part_out, const float* const* part_lse, voi
     args.dst_lse[p] = dst_lse[p];
   }
   if (row_end == row_begin) return NKV_OK;
-  const long long total = (row_end - row_begin) * (d >> 3);
-  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
-  if (dtype == NKV_F32)
-    cp_merge_peer_kernel<NKV_F32><<<blocks, 256, 0, stream>>>(args, world, row_begin, row_end, d);
-  else if (dtype == NKV_BF16)
-    cp_merge_peer_kernel<NKV_BF16><<<blocks, 256, 0, stream>>>(args, world, row_begin, row_end, d);
-  else
-    cp_merge_peer_kernel<NKV_F16><<<blocks, 256, 0, stream>>>(args, world, row_begin, row_end, d);
+  if (dtype == NKV_F32) launch_merge<NKV_F32>(args, world, world, row_begin, row_end, d, stream);
+  else if (dtype == NKV_BF16) launch_merge<NKV_BF16>(args, world, world, row_begin, row_end, d, stream);
+  else launch_merge<NKV_F16>(args, world, world, row_begin, row_end, d, stream);
   NKV_LAUNCH_CHECK("cp_merge_peer_kernel");
   return NKV_OK;
 }
@@ -456,7 +484,7 @@ int history_moments(const nkv_history& h, float* latent_sum, int32_t* center_cou
   const int slabs = (h.tokens + MOMENT_SLAB - 1) / MOMENT_SLAB;
   moments_partial_kernel<<<slabs, 256, 0, stream>>>(h, static_cast<float*>(workspace), center_counts);
   NKV_LAUNCH_CHECK("moments_partial_kernel");
-  moments_reduce_kernel<<<(h.rank + 255) / 256, 256, 0, stream>>>(static_cast<const float*>(workspace),
+  moments_reduce_kernel<<<(h.rank + 7) / 8, 256, 0, stream>>>(static_cast<const float*>(workspace),
                                                                    slabs, h.rank, latent_sum);
   NKV_LAUNCH_CHECK("moments_reduce_kernel");
   return NKV_OK;

@@ -560,37 +560,69 @@ int simt_attn(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride
   return fail(NKV_ERR_UNSUPPORTED, "attention head widths dk=%d dv=%d (built: 16, 32, 64, 128 with dk == dv)", dk, dv);
 }
 
-// rotation of explicit rows: thread = one (row, head, pair)
+// rotation of explicit rows: thread = four adjacent pairs (8 elements) of one (row, head)
 __global__ void __launch_bounds__(256)
 rope_rows_kernel(const void* x, int dtype, long long stride_row, long long stride_head, int S,
-                 int heads, int d, nkv_rope rope, void* out) {
-  const int half = d / 2;
+                 int heads, int d, nkv_rope rope, void* out, int vector) {
+  const int half = d / 2, quads = half / 4 + (half % 4 ? 1 : 0);
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= static_cast<long long>(S) * heads * half) return;
-  const int pl = static_cast<int>(idx % half);
-  const int head = static_cast<int>((idx / half) % heads);
-  const int row = static_cast<int>(idx / (static_cast<long long>(half) * heads));
+  if (idx >= static_cast<long long>(S) * heads * quads) return;
+  const int pl0 = static_cast<int>(idx % quads) * 4;
+  const int head = static_cast<int>((idx / quads) % heads);
+  const int row = static_cast<int>(idx / (static_cast<long long>(quads) * heads));
   const int th = rope.table_half, third = th / 3, band_a = th - 2 * third, band_b = band_a + third;
   const int pos = max(rope.positions[row], 0);
   const int frame = pos / rope.frame_seqlen, spatial = pos - frame * rope.frame_seqlen;
   const int prow = spatial / rope.width, pcol = spatial - prow * rope.width;
-  const int pg = rope.pair_index ? rope.pair_index[head * half + pl] : pl;
-  int coord = pg < band_a ? frame : (pg < band_b ? prow : pcol);
-  coord = min(coord, rope.table_rows - 1);
-  const float2 cs = reinterpret_cast<const float2*>(rope.cos_sin)[static_cast<size_t>(coord) * th + pg];
-  const size_t src = static_cast<size_t>(row) * stride_row + static_cast<size_t>(head) * stride_head + 2 * pl;
-  const float x0 = load_float(x, dtype, src), x1 = load_float(x, dtype, src + 1);
-  const size_t dst = (static_cast<size_t>(row) * heads + head) * d + 2 * pl;
-  store_float(out, dtype, dst, fmaf(x0, cs.x, -(x1 * cs.y)));
-  store_float(out, dtype, dst + 1, fmaf(x0, cs.y, x1 * cs.x));
+  const size_t src = static_cast<size_t>(row) * stride_row + static_cast<size_t>(head) * stride_head + 2 * pl0;
+  const size_t dst = (static_cast<size_t>(row) * heads + head) * d + 2 * pl0;
+  float v[8];
+  const int count = min(4, half - pl0);
+  if (vector && dtype == NKV_BF16) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + src);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      v[2 * k] = __uint_as_float(w[k] << 16);
+      v[2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u);
+    }
+  } else {
+    for (int k = 0; k < 2 * count; ++k) v[k] = load_float(x, dtype, src + k);
+  }
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    if (k >= count) break;
+    const int pl = pl0 + k;
+    const int pg = rope.pair_index ? rope.pair_index[head * half + pl] : pl;
+    int coord = pg < band_a ? frame : (pg < band_b ? prow : pcol);
+    coord = min(coord, rope.table_rows - 1);
+    const float2 cs = reinterpret_cast<const float2*>(rope.cos_sin)[static_cast<size_t>(coord) * th + pg];
+    const float x0 = v[2 * k], x1 = v[2 * k + 1];
+    v[2 * k] = fmaf(x0, cs.x, -(x1 * cs.y));
+    v[2 * k + 1] = fmaf(x0, cs.y, x1 * cs.x);
+  }
+  if (vector && dtype == NKV_BF16) {
+    uint4 packed;
+    packed.x = float_to_bf16_bits(v[0]) | (static_cast<uint32_t>(float_to_bf16_bits(v[1])) << 16);
+    packed.y = float_to_bf16_bits(v[2]) | (static_cast<uint32_t>(float_to_bf16_bits(v[3])) << 16);
+    packed.z = float_to_bf16_bits(v[4]) | (static_cast<uint32_t>(float_to_bf16_bits(v[5])) << 16);
+    packed.w = float_to_bf16_bits(v[6]) | (static_cast<uint32_t>(float_to_bf16_bits(v[7])) << 16);
+    *reinterpret_cast<uint4*>(static_cast<uint16_t*>(out) + dst) = packed;
+  } else {
+    for (int k = 0; k < 2 * count; ++k) store_float(out, dtype, dst + k, v[k]);
+  }
 }
 
 int rope_rows(const void* x, int dtype, int64_t stride_row, int64_t stride_head, int S, int heads,
               int d, const nkv_rope& rope, void* out, cudaStream_t stream) {
-  const long long total = static_cast<long long>(S) * heads * (d / 2);
+  const int half = d / 2, quads = half / 4 + (half % 4 ? 1 : 0);
+  const long long total = static_cast<long long>(S) * heads * quads;
   if (total == 0) return NKV_OK;
+  // 16-byte path: whole groups of 8 elements, every row and head start 16-byte aligned
+  const int vector = d % 8 == 0 && stride_row % 8 == 0 && stride_head % 8 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
   rope_rows_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
-      x, dtype, stride_row, stride_head, S, heads, d, rope, out);
+      x, dtype, stride_row, stride_head, S, heads, d, rope, out, vector);
   NKV_LAUNCH_CHECK("rope_rows_kernel");
   return NKV_OK;
 }
