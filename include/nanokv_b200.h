@@ -252,7 +252,10 @@ typedef struct nkv_rope {
   const int32_t* positions;  /* [history tokens] absolute token positions (device) */
   const float* cos_sin;      /* [table_rows][table_half][2] (cos, sin) (device) */
   int32_t table_rows;
-  int32_t frame_seqlen;      /* tokens per frame = height * width */
+  int32_t frame_seqlen;      /* tokens per frame = height * width; 0: the table has one row per
+                                token position (every band reads row `position`), the form in which
+                                Matrix-Game hands its multipliers over (rope_selected
+                                models/Matrix-Game-3.5/fast/codec_native/core.py:75-91) */
   int32_t width;
   int32_t table_half;        /* pairs per table row = native head_dim / 2; the bands are cut on it */
   const int32_t* pair_index; /* NULL: pair p of the key row is native pair p (table_half = dk/2).

@@ -55,10 +55,16 @@ class RopeTable:
     def __init__(self, freqs: torch.Tensor, *, frame_seqlen: int, width: int, device="cuda"):
         if not freqs.is_complex() or freqs.dim() != 2:
             raise ValueError("freqs must be a complex [rows, head_dim/2] tensor")
-        if frame_seqlen <= 0 or width <= 0 or frame_seqlen % width:
+        if frame_seqlen != 0 and (frame_seqlen < 0 or width <= 0 or frame_seqlen % width):
             raise ValueError(f"frame_seqlen mismatch: width {width} does not divide {frame_seqlen}")
         self.cos_sin = torch.view_as_real(freqs).to(device=device, dtype=torch.float32).contiguous()
         self.frame_seqlen, self.width = int(frame_seqlen), int(width)
+
+    @classmethod
+    def per_token(cls, multiplier: torch.Tensor, device="cuda") -> "RopeTable":
+        """Table with one row per token: ``multiplier`` complex [S, native half] as Matrix-Game
+        passes it (MGC/core.py:75-91); ``positions`` then index its rows."""
+        return cls(multiplier, frame_seqlen=0, width=0, device=device)
 
     def view(self, positions: torch.Tensor, pair_index: torch.Tensor | None = None) -> "ops.RopeView":
         """``pair_index`` i32 [heads, d/2]: the native pair every pair of a low-width row retains."""

@@ -235,8 +235,9 @@ size_t nkv_attn_codec_workspace_bytes(int Q, int heads, int dv, int splits) {
 }
 
 static int check_rope(const nkv_rope* rope, int d, int64_t rows) {
-  NKV_REQUIRE(rope->cos_sin != nullptr && rope->table_rows > 0 && rope->frame_seqlen > 0 &&
-                  rope->width > 0 && rope->frame_seqlen % rope->width == 0,
+  NKV_REQUIRE(rope->cos_sin != nullptr && rope->table_rows > 0 &&
+                  (rope->frame_seqlen == 0 ||
+                   (rope->frame_seqlen > 0 && rope->width > 0 && rope->frame_seqlen % rope->width == 0)),
               NKV_ERR_INVALID, "rope: table_rows=%d frame_seqlen=%d width=%d", rope->table_rows,
               rope->frame_seqlen, rope->width);
   NKV_REQUIRE(rope->positions != nullptr || rows == 0, NKV_ERR_INVALID, "rope: positions are NULL");

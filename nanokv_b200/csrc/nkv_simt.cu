@@ -321,8 +321,13 @@ attn_kernel(AttnArgs a) {
               const int half = D / 2, th = a.rope.table_half, third = th / 3;
               const int band_a = th - 2 * third, band_b = band_a + third;
               const int pos = max(a.rope.positions[t0 + m], 0);
-              const int frame = pos / a.rope.frame_seqlen, spatial = pos - frame * a.rope.frame_seqlen;
-              const int prow = spatial / a.rope.width, pcol = spatial - prow * a.rope.width;
+              int frame = pos, prow = pos, pcol = pos;   // frame_seqlen 0: one table row per token
+              if (a.rope.frame_seqlen > 0) {
+                frame = pos / a.rope.frame_seqlen;
+                const int spatial = pos - frame * a.rope.frame_seqlen;
+                prow = spatial / a.rope.width;
+                pcol = spatial - prow * a.rope.width;
+              }
 #pragma unroll
               for (int pr = 0; pr < 2; ++pr) {
                 const int pl = (n0 + tx * 4) / 2 + pr;
@@ -572,8 +577,13 @@ rope_rows_kernel(const void* x, int dtype, long long stride_row, long long strid
   const int row = static_cast<int>(idx / (static_cast<long long>(quads) * heads));
   const int th = rope.table_half, third = th / 3, band_a = th - 2 * third, band_b = band_a + third;
   const int pos = max(rope.positions[row], 0);
-  const int frame = pos / rope.frame_seqlen, spatial = pos - frame * rope.frame_seqlen;
-  const int prow = spatial / rope.width, pcol = spatial - prow * rope.width;
+  int frame = pos, prow = pos, pcol = pos;   // frame_seqlen 0: one table row per token
+  if (rope.frame_seqlen > 0) {
+    frame = pos / rope.frame_seqlen;
+    const int spatial = pos - frame * rope.frame_seqlen;
+    prow = spatial / rope.width;
+    pcol = spatial - prow * rope.width;
+  }
   const size_t src = static_cast<size_t>(row) * stride_row + static_cast<size_t>(head) * stride_head + 2 * pl0;
   const size_t dst = (static_cast<size_t>(row) * heads + head) * d + 2 * pl0;
   float v[8];

@@ -275,6 +275,15 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr) {
          (1ull << 46) | (2ull << 61);
 }
 
+// The same tiles read as an MN-major operand (the 64 contiguous elements of a row run along M / N,
+// rows along K): 8-row groups 1024 bytes apart are the stride offset, the next 64-column tile
+// (`tile_stride` bytes away) is the leading offset.  A K step of 16 rows adds 2048 bytes.
+__device__ __forceinline__ uint64_t make_smem_desc_sw128_mn(uint32_t smem_addr, uint32_t tile_stride) {
+  return static_cast<uint64_t>((smem_addr >> 4) & 0x3FFF) |
+         (static_cast<uint64_t>((tile_stride >> 4) & 0x3FFF) << 16) | (64ull << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+
 // byte offset of element (row, col) inside such a tile (col < 64)
 __device__ __forceinline__ uint32_t sw128_offset(int row, int col) {
   return static_cast<uint32_t>(row) * 128u +

@@ -84,8 +84,8 @@ struct Layout {
   static constexpr int DCH = D / 64;                     // 64-column chunks of a head row
   static constexpr int Q_OFF = 0;                        // [NQ][DCH] tiles
   static constexpr int K_OFF = Q_OFF + NQ * DCH * TILE_BYTES;   // [DCH] tiles [128 tok x 64]
-  static constexpr int VT_OFF = K_OFF + DCH * TILE_BYTES;       // [2] tiles [D rows x 64 tok]
-  static constexpr int VT_TILE = D * 128;
+  static constexpr int VT_OFF = K_OFF + DCH * TILE_BYTES;       // V: [DCH] tiles [128 tok x 64], like K
+  static constexpr int VT_TILE = D * 128;                       // (2 * VT_TILE == DCH * TILE_BYTES)
   // codes of the tile: one [128 tok x 64 byte] block per pair of latent chunks, 64-byte swizzle
   // (rows 64 bytes apart would put a quarter-warp's 16-byte reads on two bank groups)
   static constexpr int CODES_OFF = VT_OFF + 2 * VT_TILE;
@@ -338,7 +338,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       const bool leader = elect_one();
       const uint32_t idesc_dec = make_idesc_bf16(128, PART);  // [128 tok] x [64 columns]
       const uint32_t idesc_s = make_idesc_bf16(128, TOK);     // [128 q] x [128 tok]
-      const uint32_t idesc_pv = make_idesc_bf16(128, D);      // [128 q] x [D]
+      const uint32_t idesc_pv = make_idesc_bf16(128, D) | (1u << 16);   // [128 q] x [D], B (V) MN-major
       const uint32_t smem_base = smem_u32(smem);
       const uint16_t all_ctas = static_cast<uint16_t>((1u << CL) - 1);
       Laps<PROF> laps;
@@ -387,16 +387,9 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           for (uint32_t step = 1; step < CL; ++step) {
             const uint32_t peer = (rank + step) % CL;
             const uint32_t peer_ready = map_to_cta(ready, peer);
-            if (tensor == 0) {
-              const uint32_t src = smem_base + L::K_OFF + part * TILE_BYTES;
-              if (leader) bulk_copy_to_peer(map_to_cta(src, peer), src, TILE_BYTES, peer_ready);
-            } else {
-#pragma unroll
-              for (int half = 0; half < 2; ++half) {
-                const uint32_t src = smem_base + L::VT_OFF + half * L::VT_TILE + part * PART * 128;
-                if (leader) bulk_copy_to_peer(map_to_cta(src, peer), src, PART * 128, peer_ready);
-              }
-            }
+            // K and V are both stored token-major, one [128 tok x 64 col] tile per part
+            const uint32_t src = smem_base + (tensor == 0 ? L::K_OFF : L::VT_OFF) + part * TILE_BYTES;
+            if (leader) bulk_copy_to_peer(map_to_cta(src, peer), src, TILE_BYTES, peer_ready);
           }
           if (leader) mbar_arrive_expect_tx(&bars[KV_READY], (CL - 1) * TILE_BYTES);
         }
@@ -423,15 +416,16 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           if (!ok) break;
           tc_fence_after();
           // P (bf16 pairs) sits in the first 64 columns of the S region it was computed from
-#pragma unroll
-          for (int ch = 0; ch < 2; ++ch) {
-            const uint64_t b_desc = make_smem_desc_sw128(smem_base + L::VT_OFF + ch * L::VT_TILE);
-            const uint32_t p_addr = tmem_base + i * 128 + ch * 32;
+          // V is the B operand in MN-major form: [tokens (K) x d (N)] with d contiguous, 64-column
+          // tiles 16 KB apart (leading offset), 8-token groups 1 KB apart (stride offset); a K step
+          // of 16 tokens moves the start by 2 KB (128 in the address field)
+          {
+            const uint64_t b_desc = make_smem_desc_sw128_mn(smem_base + L::VT_OFF, TILE_BYTES);
+            const uint32_t p_addr = tmem_base + i * 128;
             const uint32_t o_addr = tmem_base + 256 + i * 128;
-            if (leader) mma_bf16_ts(o_addr, p_addr, b_desc, idesc_pv, it > 0 || ch > 0);
-            if (leader) mma_bf16_ts(o_addr, p_addr + 8, b_desc + 2, idesc_pv, true);
-            if (leader) mma_bf16_ts(o_addr, p_addr + 16, b_desc + 4, idesc_pv, true);
-            if (leader) mma_bf16_ts(o_addr, p_addr + 24, b_desc + 6, idesc_pv, true);
+#pragma unroll
+            for (int ks = 0; ks < TOK / 16; ++ks)
+              if (leader) mma_bf16_ts(o_addr, p_addr + 8 * ks, b_desc + 128 * ks, idesc_pv, it > 0 || ks > 0);
           }
           if (leader) mma_commit(&bars[PV_DONE + i]);
         }
@@ -586,11 +580,15 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         if (rotate) {
           const int pos = in ? max(__ldg(p.rope.positions + t0 + row), 0) : 0;
           const int last = p.rope.table_rows - 1;
-          const int frame = pos / p.rope.frame_seqlen, spatial = pos - frame * p.rope.frame_seqlen;
-          const int prow = spatial / p.rope.width;
-          coord_t = min(frame, last);
-          coord_h = min(prow, last);
-          coord_w = min(spatial - prow * p.rope.width, last);
+          if (p.rope.frame_seqlen == 0) {   // one table row per token: every band reads row `pos`
+            coord_t = coord_h = coord_w = min(pos, last);
+          } else {
+            const int frame = pos / p.rope.frame_seqlen, spatial = pos - frame * p.rope.frame_seqlen;
+            const int prow = spatial / p.rope.width;
+            coord_t = min(frame, last);
+            coord_h = min(prow, last);
+            coord_w = min(spatial - prow * p.rope.width, last);
+          }
         }
         laps.lap(6);
         // accumulator complete: the tile's last pair is pair g - 1
@@ -646,26 +644,12 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           ok = mbar_wait_cluster(&bars[KV_FREE], (it - 1) & 1, abort_flag, 332);
           if (!ok) break;
         }
-        if (tensor == 0) {
-          uint8_t* tile = smem + L::K_OFF + part * TILE_BYTES;
+        {   // K and V alike: token-major, this thread's 32 columns of its token row
+          uint8_t* tile = smem + (tensor == 0 ? L::K_OFF : L::VT_OFF) + part * TILE_BYTES;
 #pragma unroll
           for (int j4 = 0; j4 < 4; ++j4)
             *reinterpret_cast<uint4*>(tile + sw128_offset(row, wg * 32 + j4 * 8)) =
                 make_uint4(packed[j4 * 4], packed[j4 * 4 + 1], packed[j4 * 4 + 2], packed[j4 * 4 + 3]);
-        } else {
-          // transposed store: lanes l and l^1 hold neighbouring tokens and trade halves so that
-          // each writes whole 32-bit words (token pair) of 16 of the 32 columns
-          uint8_t* tile = smem + L::VT_OFF + (row >> 6) * L::VT_TILE;
-          const bool odd = lane & 1;
-#pragma unroll
-          for (int m = 0; m < 16; ++m) {
-            const uint32_t mine = packed[m];
-            const uint32_t got = __shfl_xor_sync(0xffffffffu, odd ? (mine & 0xFFFFu) : (mine >> 16), 1);
-            const uint32_t word = odd ? ((got & 0xFFFFu) | (mine & 0xFFFF0000u))
-                                      : ((mine & 0xFFFFu) | (got << 16));
-            const int d = part * PART + wg * 32 + 2 * m + (odd ? 1 : 0);
-            *reinterpret_cast<uint32_t*>(tile + sw128_offset(d, (row & 63) & ~1)) = word;
-          }
         }
       }
       laps.lap(8);

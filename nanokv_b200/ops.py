@@ -221,7 +221,7 @@ class RopeView:
             raise ValueError("positions must be int32 and the rotation table float32")
         if cos_sin.dim() != 3 or cos_sin.shape[2] != 2:
             raise ValueError("rotation table must be [rows, head_dim/2, 2]")
-        if frame_seqlen <= 0 or width <= 0 or frame_seqlen % width:
+        if frame_seqlen != 0 and (frame_seqlen < 0 or width <= 0 or frame_seqlen % width):
             raise ValueError(f"frame_seqlen mismatch: width {width} does not divide {frame_seqlen}")
         self.positions, self.cos_sin = positions, cos_sin
         self.frame_seqlen, self.width = int(frame_seqlen), int(width)

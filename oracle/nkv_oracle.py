@@ -553,6 +553,15 @@ def rope_selected(value: torch.Tensor, positions: torch.Tensor, freqs: torch.Ten
     return torch.view_as_real(pairs * selected[None]).flatten(-2).to(value.dtype)
 
 
+def rope_per_token(value: torch.Tensor, multiplier: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+    """Matrix-Game's form: value [B,h,S,e], multiplier complex [S, native half] given per token,
+    indices [h,e] the native dimensions each head retains (whole pairs); float64 complex product,
+    one rounding (MGC/core.py:75-91 rope_selected)."""
+    chosen = multiplier[:, indices.long()[:, ::2] // 2].permute(1, 0, 2)
+    pairs = torch.view_as_complex(value.double().reshape(*value.shape[:-1], -1, 2).contiguous())
+    return torch.view_as_real(pairs * chosen[None]).flatten(-2).to(value.dtype)
+
+
 # ---------------------------------------------------------------- INT8 operator storage
 def pack_int8_weight(weight: torch.Tensor, group_size: int = 0):
     """fp32 weight [rows, in] -> (int8 codes, bf16 scale [rows, in/group], group): symmetric

@@ -177,3 +177,11 @@ def value_mean_interval(case: CodecCase, index: int) -> tuple[int, int]:
     """Local token interval of segment ``index`` that belongs to the low history."""
     count = case.segments[index]
     return (17, count) if index == 0 else (0, count)
+
+
+def per_token_multiplier(data: dict) -> torch.Tensor:
+    """complex128 [tokens, native half]: unit-modulus multipliers with seeded angles, one row per token."""
+    gen = synthetic.generator(902)
+    tokens = data["value"].shape[2]
+    angles = (torch.rand(tokens, data["native_dim"] // 2, generator=gen, dtype=torch.float64) - 0.5) * 40.0
+    return torch.polar(torch.ones_like(angles), angles)

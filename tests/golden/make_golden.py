@@ -292,6 +292,14 @@ def run_value_mean_case(case: cases.CodecCase, root) -> dict:
             "input_digest": np.array([checksum(torch.cat(data["v_chunks"]))], dtype=np.uint64)}
 
 
+def run_rope_per_token_case(root) -> dict:
+    """rope_selected of the MG core module: multipliers handed over per token."""
+    core = ref_import.load_mg_core(root)
+    data = cases.build_rope_selected()
+    out = core.rope_selected(data["value"], cases.per_token_multiplier(data), data["indices"])
+    return {"rotated": bits(out), "value_digest": np.array([checksum(data["value"])], dtype=np.uint64)}
+
+
 def run_int8_operator_case(root) -> dict:
     """The reference's INT8 operator packing and the bf16 weight it multiplies with."""
     codec = ref_import.load_mg_codec(root)
@@ -351,6 +359,7 @@ def main() -> None:
     save("merge_edge", lambda: run_merge_case(root))
     save("select_mg_bf16", lambda: run_select_case(cases.MINI_BF16, root))
     save("rope_selected_bf16", lambda: run_rope_selected_case(root))
+    save("rope_per_token_bf16", lambda: run_rope_per_token_case(root))
     save("value_mean_lb_bf16", lambda: run_value_mean_case(cases.ROLLING, root))
     save("int8_operator", lambda: run_int8_operator_case(root))
     save(cases.ROLLING.name, lambda: run_rolling_case(cases.ROLLING, root))

@@ -226,3 +226,45 @@ def test_hybrid_attention_with_selected_rope(case):
         reader, rope=table, q_positions=q_positions.cuda())
     tol = F32_REL_TOL if dtype == torch.float32 else BF16_REL_TOL
     assert rel_err(got.cpu().permute(1, 0, 2), want) <= tol
+
+
+def test_per_token_multipliers_matrix_game_form():
+    """One table row per token (Matrix-Game hands its multipliers over that way): rows through
+    nkv_rope_rows against the reference fixture, and the same table inside the fused read."""
+    from test_oracle_golden import from_bits, load
+    gold, data = load("rope_per_token_bf16"), cases.build_rope_selected()
+    multiplier = cases.per_token_multiplier(data)
+    table = attention.RopeTable.per_token(multiplier)
+    rows = data["value"][0].permute(1, 0, 2).contiguous()
+    tokens = rows.shape[0]
+    got = table.rotate(rows.cuda(), torch.arange(tokens).cuda(), pair_index_of(data["indices"]).cuda()).cpu()
+    want = from_bits(gold["rotated"], torch.bfloat16)[0].permute(1, 0, 2)
+    assert float((got.float() - want.float()).abs().max()) <= 2.0 ** -7 * float(want.float().abs().max())
+    assert float((got != want).float().mean()) < 0.01
+    # inside the read: a 64-wide reader over 128-wide heads, multipliers per history token
+    heads, width, native = 2, 64, 128
+    built = build(heads, width, 64, 300, 130, "bf16", 5, 6)
+    case, bdata, segments, _, _, q = built
+    gen = torch.Generator().manual_seed(13)
+    angles = (torch.rand(300, native // 2, generator=gen, dtype=torch.float64) - 0.5) * 30.0
+    mult = torch.polar(torch.ones_like(angles), angles)
+    pairs = torch.stack([torch.randperm(native // 2, generator=gen)[:width // 2].sort().values
+                         for _ in range(heads)])
+    indices = torch.stack((2 * pairs, 2 * pairs + 1), dim=2).reshape(heads, width)
+    ops_k, ops_v = device_operator(bdata["k_op"]), device_operator(bdata["v_op"])
+    hist_k = history_from_segments(segments["k"], joint=case.shape.joint, rank=case.shape.rank)
+    hist_v = history_from_segments(segments["v"], joint=case.shape.joint, rank=case.shape.rank)
+    view = attention.RopeTable.per_token(mult).view(torch.arange(300).cuda(), pair_index_of(indices).cuda())
+    out, lse = ops.attn_codec(
+        q.cuda(), hist_k.view(), hist_v.view(), ops_k.decoder.view(heads, width, -1),
+        ops_k.bias.view(heads, width), ops_v.decoder.view(heads, width, -1),
+        ops_v.bias.view(heads, width), scale=width ** -0.5, rope=view)
+    k_op, v_op = bdata["k_op"], bdata["v_op"]
+    keys = torch.cat([oracle.decode_rows(s, decoder=k_op["decoder"], mean=k_op["mean"], dtype=torch.bfloat16)
+                      for s in segments["k"]], 1).reshape(1, -1, heads, width).permute(0, 2, 1, 3)
+    values = torch.cat([oracle.decode_rows(s, decoder=v_op["decoder"], mean=v_op["mean"], dtype=torch.bfloat16)
+                        for s in segments["v"]], 1).reshape(1, -1, heads, width).permute(0, 2, 1, 3)
+    keys = oracle.rope_per_token(keys, mult, indices)
+    want, want_lse = oracle.attention_lse(q.permute(1, 0, 2)[None], keys, values, scale=width ** -0.5)
+    assert rel_err(out.cpu(), want[0].permute(1, 0, 2)) <= BF16_REL_TOL
+    assert float((lse.cpu() - want_lse[0].t()).abs().max()) <= BF16_REL_TOL

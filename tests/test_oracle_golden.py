@@ -191,3 +191,11 @@ def test_compressed_value_mean():
     got = oracle.compressed_value_mean(low, decoder=data["v_op"]["decoder"], heads=case.shape.heads,
                                        native_dim=case.shape.head_dim)
     assert np.array_equal(gold["value_mean"], got.numpy())
+
+
+def test_rope_per_token_multipliers():
+    gold = load("rope_per_token_bf16")
+    data = cases.build_rope_selected()
+    assert int(gold["value_digest"][0]) == checksum(data["value"]), "input generator drifted"
+    got = oracle.rope_per_token(data["value"], cases.per_token_multiplier(data), data["indices"])
+    assert torch.equal(got.view(torch.int16), from_bits(gold["rotated"], torch.bfloat16).view(torch.int16))
