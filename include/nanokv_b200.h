@@ -280,6 +280,40 @@ int nkv_attn_codec_rope(const void* q, int dtype, int64_t q_stride_token, int64_
                         void* stream);
 
 /*
+ * PRoPE camera transform of the rebuilt rows (Matrix-Game / HY): a row is made of 8-wide blocks,
+ * a block of four two-element slots; output slot i of a block is sum_j M[i][j] * input slot j,
+ * with M = matrices[frame][camera] (4 x 4), camera = cam_index[head][block] (the native block id
+ * modulo 4 for the blocks a low-width reader retains) and frame = token / tokens_per_frame
+ * (equal-sized frames, clamped to frames - 1).  Operands are bf16 values (the matrices are
+ * rounded to bf16 on load), fp32 accumulation, one rounding; it follows the rotation.
+ * Reference: camera_selected models/Matrix-Game-3.5/fast/codec_native/core.py:110-137, fused
+ * form codec_native/camera_kernel.py:9-80; call sites codec_native/mg35.py:321, :339-346.
+ */
+typedef struct nkv_camera {
+  const float* matrices;     /* [frames][4][4][4] f32 (device) */
+  const int32_t* cam_index;  /* [heads][head_dim / 8] camera 0..3 of every block (device) */
+  int32_t frames;
+  int32_t tokens_per_frame;
+} nkv_camera;
+
+/*
+ * nkv_attn_codec_rope plus the camera transform of the rebuilt keys (camera_k) and values
+ * (camera_v); any of rope / camera_k / camera_v may be NULL.
+ */
+int nkv_attn_codec_pos(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head,
+                       int Q, int heads, int dk, int dv,
+                       const nkv_history* hist_k, const nkv_history* hist_v,
+                       const void* wk, const float* bias_k, const void* wv, const float* bias_v,
+                       const nkv_rope* rope, const nkv_camera* camera_k, const nkv_camera* camera_v,
+                       float scale, void* out, float* lse, int32_t* status_word, int splits,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
+/* The camera transform applied to explicit rows x [S, heads, d] (reduced queries with P^T,
+ * attention outputs with P): out [S, heads, d] contiguous, same dtype. */
+int nkv_camera_rows(const void* x, int dtype, int64_t stride_row, int64_t stride_head, int S,
+                    int heads, int d, const nkv_camera* camera, void* out, void* stream);
+
+/*
  * The same rotation applied to explicit rows (queries, the current chunk's keys):
  * x [S, heads, d] with strides in elements -> out [S, heads, d] contiguous, same dtype;
  * rope->positions holds the S row positions.  fp32 arithmetic, one rounding.

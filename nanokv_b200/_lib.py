@@ -18,6 +18,12 @@ class Rope(ctypes.Structure):
                 ("pair_index", c_void_p)]
 
 
+class Camera(ctypes.Structure):
+    """struct nkv_camera"""
+    _fields_ = [("matrices", c_void_p), ("cam_index", c_void_p), ("frames", c_int32),
+                ("tokens_per_frame", c_int32)]
+
+
 NKV_OK = 0
 NKV_ERR_INVALID, NKV_ERR_CUDA, NKV_ERR_UNSUPPORTED, NKV_ERR_DEVICE_WAIT, NKV_ERR_TOO_LARGE = (
     -1, -2, -3, -4, -5)
@@ -70,6 +76,13 @@ SIGNATURES = {
                                     POINTER(History), POINTER(History), c_void_p, c_void_p,
                                     c_void_p, c_void_p, POINTER(Rope), c_float, c_void_p, c_void_p,
                                     c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
+    "nkv_attn_codec_pos": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int,
+                                   POINTER(History), POINTER(History), c_void_p, c_void_p,
+                                   c_void_p, c_void_p, POINTER(Rope), POINTER(Camera), POINTER(Camera),
+                                   c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_size_t,
+                                   c_void_p]),
+    "nkv_camera_rows": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, POINTER(Camera),
+                                c_void_p, c_void_p]),
     "nkv_rope_rows": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, POINTER(Rope),
                               c_void_p, c_void_p]),
     "nkv_attention_lse": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64,

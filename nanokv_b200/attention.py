@@ -77,6 +77,28 @@ class RopeTable:
         return ops.rope_rows(rows, self.view(positions, pair_index))
 
 
+def camera_index(indices: torch.Tensor, device="cuda") -> torch.Tensor:
+    """reader indices [h, e] that retain whole 8-wide native blocks -> camera of every block,
+    i32 [h, e/8]: native block id modulo 4 (MGC/core.py:119-127)."""
+    blocks = indices.long().reshape(indices.shape[0], -1, 8)
+    if (not torch.equal(blocks, blocks[..., :1] + torch.arange(8, device=blocks.device))
+            or bool((blocks[..., 0] % 8).any())):
+        raise ValueError("Invalid MG camera blocks")
+    return ((blocks[..., 0] // 8) % 4).to(device=device, dtype=torch.int32).contiguous()
+
+
+def camera_view(matrix: torch.Tensor, indices: torch.Tensor, tokens: int, device="cuda") -> "ops.CameraView":
+    """matrix [1, frames, 4, 4, 4] (already the role's: P^T for queries, P^-1 for keys and values,
+    P for outputs) over ``tokens`` rows split evenly over its frames."""
+    if matrix.dim() != 5 or matrix.shape[0] != 1 or tuple(matrix.shape[2:]) != (4, 4, 4):
+        raise ValueError("camera matrix must be [1, frames, 4, 4, 4]")
+    frames = int(matrix.shape[1])
+    if tokens % frames:
+        raise ValueError("PRoPE frame count must divide the token sequence")
+    return ops.CameraView(matrix[0].to(device=device, dtype=torch.float32).contiguous(),
+                          camera_index(indices, device), tokens // frames)
+
+
 def merge(out_a, lse_a, out_b, lse_b):
     """Two-partition softmax merge (MGC/core.py:33-42)."""
     return ops.lse_merge([(out_a.contiguous(), lse_a.contiguous()),

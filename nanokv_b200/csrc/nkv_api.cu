@@ -261,12 +261,44 @@ int nkv_rope_rows(const void* x, int dtype, int64_t stride_row, int64_t stride_h
                    static_cast<cudaStream_t>(stream));
 }
 
+static int check_camera(const nkv_camera* cam, int d) {
+  NKV_REQUIRE(cam->matrices != nullptr && cam->cam_index != nullptr && cam->frames > 0 &&
+                  cam->tokens_per_frame > 0,
+              NKV_ERR_INVALID, "camera: frames=%d tokens_per_frame=%d", cam->frames, cam->tokens_per_frame);
+  NKV_REQUIRE(d % 8 == 0 && (reinterpret_cast<uintptr_t>(cam->matrices) & 15) == 0, NKV_ERR_INVALID,
+              "camera: head width %d must be a multiple of 8 and the matrices 16-byte aligned", d);
+  return NKV_OK;
+}
+
+int nkv_camera_rows(const void* x, int dtype, int64_t stride_row, int64_t stride_head, int S,
+                    int heads, int d, const nkv_camera* camera, void* out, void* stream) {
+  NKV_REQUIRE(x && out && camera && S >= 0 && heads >= 0 && d > 0, NKV_ERR_INVALID,
+              "camera_rows: S=%d heads=%d d=%d", S, heads, d);
+  NKV_REQUIRE(dtype == NKV_F32 || dtype == NKV_BF16, NKV_ERR_INVALID, "camera_rows: dtype");
+  int rc = check_camera(camera, d);
+  if (rc != NKV_OK) return rc;
+  return camera_rows(x, dtype, stride_row, stride_head, S, heads, d, *camera, out,
+                     static_cast<cudaStream_t>(stream));
+}
+
 int nkv_attn_codec_rope(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head,
                         int Q, int heads, int dk, int dv, const nkv_history* hist_k,
                         const nkv_history* hist_v, const void* wk, const float* bias_k,
                         const void* wv, const float* bias_v, const nkv_rope* rope, float scale,
                         void* out, float* lse, int32_t* status_word, int splits, void* workspace,
                         size_t workspace_bytes, void* stream) {
+  return nkv_attn_codec_pos(q, dtype, q_stride_token, q_stride_head, Q, heads, dk, dv, hist_k, hist_v,
+                            wk, bias_k, wv, bias_v, rope, nullptr, nullptr, scale, out, lse,
+                            status_word, splits, workspace, workspace_bytes, stream);
+}
+
+int nkv_attn_codec_pos(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head,
+                       int Q, int heads, int dk, int dv, const nkv_history* hist_k,
+                       const nkv_history* hist_v, const void* wk, const float* bias_k,
+                       const void* wv, const float* bias_v, const nkv_rope* rope,
+                       const nkv_camera* camera_k, const nkv_camera* camera_v, float scale,
+                       void* out, float* lse, int32_t* status_word, int splits, void* workspace,
+                       size_t workspace_bytes, void* stream) {
   int rc = check_history(hist_k, "K");
   if (rc != NKV_OK) return rc;
   rc = check_history(hist_v, "V");
@@ -284,14 +316,22 @@ int nkv_attn_codec_rope(const void* q, int dtype, int64_t q_stride_token, int64_
     rc = check_rope(rope, dk, hist_k->tokens);
     if (rc != NKV_OK) return rc;
   }
+  if (camera_k != nullptr) {
+    rc = check_camera(camera_k, dk);
+    if (rc != NKV_OK) return rc;
+  }
+  if (camera_v != nullptr) {
+    rc = check_camera(camera_v, dv);
+    if (rc != NKV_OK) return rc;
+  }
   auto s = static_cast<cudaStream_t>(stream);
   if (dtype == NKV_BF16 && !simt_forced())
     return tc_attn_codec(q, q_stride_token, q_stride_head, Q, heads, dk, dv, hist_k, hist_v, wk,
                          bias_k, wv, bias_v, scale, out, lse, status_word, splits, workspace, s,
-                         rope);
+                         rope, camera_k, camera_v);
   return simt_attn(q, dtype, q_stride_token, q_stride_head, Q, heads, dk, dv, hist_k, hist_v, wk,
                    bias_k, wv, bias_v, nullptr, nullptr, 0, 0, hist_k->tokens, scale, out, lse, s,
-                   rope);
+                   rope, camera_k, camera_v);
 }
 
 int nkv_attn_codec_split(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head,

@@ -20,7 +20,10 @@ int simt_attn(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride
               const void* wk, const float* bias_k, const void* wv, const float* bias_v,
               const void* k_plain, const void* v_plain, int64_t kv_stride_token,
               int64_t kv_stride_head, int N, float scale, void* out, float* lse,
-              cudaStream_t stream, const nkv_rope* rope = nullptr);
+              cudaStream_t stream, const nkv_rope* rope = nullptr, const nkv_camera* cam_k = nullptr,
+              const nkv_camera* cam_v = nullptr);
+int camera_rows(const void* x, int dtype, int64_t stride_row, int64_t stride_head, int S, int heads,
+                int d, const nkv_camera& camera, void* out, cudaStream_t stream);
 int rope_rows(const void* x, int dtype, int64_t stride_row, int64_t stride_head, int S, int heads,
               int d, const nkv_rope& rope, void* out, cudaStream_t stream);
 int kmeans_gather_init(const void* x, int x_dtype, int J, int C, const int32_t* init_rows,
@@ -56,7 +59,8 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
                   const nkv_history* hist_v, const void* wk, const float* bias_k,
                   const void* wv, const float* bias_v, float scale, void* out, float* lse,
                   int32_t* status_word, int splits, void* workspace, cudaStream_t stream,
-                  const nkv_rope* rope = nullptr);
+                  const nkv_rope* rope = nullptr, const nkv_camera* cam_k = nullptr,
+                  const nkv_camera* cam_v = nullptr);
 bool tc_attn_supported(int dk, int dv, int rank);
 void tc_attn_set_profile(long long* device_buckets);
 bool tc_project_supported(int J, int r);

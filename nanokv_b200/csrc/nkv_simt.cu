@@ -232,6 +232,7 @@ struct AttnArgs {
   const void* k_plain; const void* v_plain; int64_t kv_stride_token, kv_stride_head;
   void* out; float* lse;
   nkv_rope rope;   // cos_sin == nullptr: no positional restore
+  nkv_camera cam_k, cam_v;   // matrices == nullptr: no camera transform
 };
 
 template <int DK, int DV, bool CODEC>
@@ -367,6 +368,40 @@ attn_kernel(AttnArgs a) {
           v = load_float(a.v_plain, a.dtype, static_cast<size_t>(t0 + j) * a.kv_stride_token +
                                                  static_cast<size_t>(head) * a.kv_stride_head + d);
         Vs[j * DV + d] = v;
+      }
+    }
+    if (CODEC && (a.cam_k.matrices != nullptr || a.cam_v.matrices != nullptr)) {
+      // camera transform of the finished tiles: thread = one (token, 8-wide block)
+      __syncthreads();
+      for (int which = 0; which < 2; ++which) {
+        const nkv_camera& cam = which == 0 ? a.cam_k : a.cam_v;
+        if (cam.matrices == nullptr) continue;
+        const int D = which == 0 ? DK : DV;
+        for (int idx = tid; idx < 64 * (D / 8); idx += THREADS) {
+          const int m = idx % 64, g = idx / 64;
+          if (t0 + m >= a.N) continue;
+          const int frame = min((t0 + m) / cam.tokens_per_frame, cam.frames - 1);
+          const float* mat = cam.matrices + (static_cast<size_t>(frame) * 4 + (cam.cam_index[head * (D / 8) + g] & 3)) * 16;
+          float x[8], y[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) x[k] = which == 0 ? Ks[(g * 8 + k) * 64 + m] : Vs[m * DV + g * 8 + k];
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+              float acc = 0.f;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float mij = bf16 ? round_to_bf16(mat[i * 4 + j]) : mat[i * 4 + j];
+                acc = fmaf(mij, x[2 * j + r], acc);
+              }
+              y[2 * i + r] = bf16 ? round_to_bf16(acc) : acc;
+            }
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            if (which == 0) Ks[(g * 8 + k) * 64 + m] = y[k]; else Vs[m * DV + g * 8 + k] = y[k];
+          }
+        }
       }
     }
     __syncthreads();
@@ -542,10 +577,13 @@ int simt_attn(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride
               const void* wk, const float* bias_k, const void* wv, const float* bias_v,
               const void* k_plain, const void* v_plain, int64_t kv_stride_token,
               int64_t kv_stride_head, int N, float scale, void* out, float* lse,
-              cudaStream_t stream, const nkv_rope* rope) {
+              cudaStream_t stream, const nkv_rope* rope, const nkv_camera* cam_k,
+              const nkv_camera* cam_v) {
   if (Q == 0 || heads == 0) return NKV_OK;
   AttnArgs a{};
   if (rope != nullptr) a.rope = *rope;
+  if (cam_k != nullptr) a.cam_k = *cam_k;
+  if (cam_v != nullptr) a.cam_v = *cam_v;
   a.q = q; a.dtype = dtype; a.q_stride_token = q_stride_token; a.q_stride_head = q_stride_head;
   a.Q = Q; a.heads = heads; a.N = N; a.scale = scale;
   const bool codec = hist_k != nullptr;
@@ -563,6 +601,46 @@ int simt_attn(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride
   NKV_ATTN_CASE(16, 16)
 #undef NKV_ATTN_CASE
   return fail(NKV_ERR_UNSUPPORTED, "attention head widths dk=%d dv=%d (built: 16, 32, 64, 128 with dk == dv)", dk, dv);
+}
+
+// camera transform of explicit rows: thread = one (row, head, 8-wide block)
+__global__ void __launch_bounds__(256)
+camera_rows_kernel(const void* x, int dtype, long long stride_row, long long stride_head, int S,
+                   int heads, int d, nkv_camera cam, void* out) {
+  const int blocks = d / 8;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(S) * heads * blocks) return;
+  const int g = static_cast<int>(idx % blocks);
+  const int head = static_cast<int>((idx / blocks) % heads);
+  const int row = static_cast<int>(idx / (static_cast<long long>(blocks) * heads));
+  const int frame = min(row / cam.tokens_per_frame, cam.frames - 1);
+  const float* mat = cam.matrices + (static_cast<size_t>(frame) * 4 + (cam.cam_index[head * blocks + g] & 3)) * 16;
+  const bool bf16 = dtype == NKV_BF16;
+  const size_t src = static_cast<size_t>(row) * stride_row + static_cast<size_t>(head) * stride_head + g * 8;
+  const size_t dst = (static_cast<size_t>(row) * heads + head) * d + g * 8;
+  float v[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) v[k] = load_float(x, dtype, src + k);
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        acc = fmaf(bf16 ? round_to_bf16(mat[i * 4 + j]) : mat[i * 4 + j], v[2 * j + r], acc);
+      store_float(out, dtype, dst + 2 * i + r, acc);
+    }
+}
+
+int camera_rows(const void* x, int dtype, int64_t stride_row, int64_t stride_head, int S, int heads,
+                int d, const nkv_camera& camera, void* out, cudaStream_t stream) {
+  const long long total = static_cast<long long>(S) * heads * (d / 8);
+  if (total == 0) return NKV_OK;
+  camera_rows_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+      x, dtype, stride_row, stride_head, S, heads, d, camera, out);
+  NKV_LAUNCH_CHECK("camera_rows_kernel");
+  return NKV_OK;
 }
 
 // rotation of explicit rows: thread = four adjacent pairs (8 elements) of one (row, head)

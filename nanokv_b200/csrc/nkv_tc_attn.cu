@@ -75,6 +75,7 @@ struct Params {
   float* lse;
   int32_t* status;
   nkv_rope rope;     // cos_sin == nullptr: keys are used as rebuilt
+  nkv_camera cam_k, cam_v;   // matrices == nullptr: no camera transform of that tensor
   long long* prof;   // optional: cycle buckets of CTA (0,0), see nkv_debug_attn_profile
 };
 
@@ -109,7 +110,8 @@ struct Layout {
   static constexpr int ABORT = SLOT + 4;
   static constexpr int BIAS = ((ABORT + 4 + 15) / 16) * 16;
   static constexpr int PAIRS = BIAS + PART * 4;          // [PART / 2] native pair of each pair of the part
-  static constexpr int CROW = PAIRS + (PART / 2) * 4;
+  static constexpr int CAMS = PAIRS + (PART / 2) * 4;   // [PART / 8] camera of each block of the part
+  static constexpr int CROW = CAMS + (PART / 8) * 4;
   static constexpr int SCALES = CROW + 2 * TOK * 4;
   static size_t bytes(int nw, int ngroups, int rank) {
     return meta_off(nw, rank) + SCALES + 2 * TOK * ngroups * 2 + 1024;
@@ -206,7 +208,7 @@ struct Laps<true> {
   }
 };
 
-template <int D, bool ROPE, bool PROF>
+template <int D, bool ROPE, bool CAM, bool PROF>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
                   const __grid_constant__ CUtensorMap map_wk,
@@ -228,6 +230,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
   volatile int* abort_flag = reinterpret_cast<volatile int*>(meta + L::ABORT);
   float* bias = reinterpret_cast<float*>(meta + L::BIAS);            // [64] of this CTA's part
   int* pair_sel = reinterpret_cast<int*>(meta + L::PAIRS);           // [32] (positional restore)
+  int* cam_sel = reinterpret_cast<int*>(meta + L::CAMS);             // [8] (camera transform)
   int* crow = reinterpret_cast<int*>(meta + L::CROW);                // [2 buf][128]
   uint16_t* scales = reinterpret_cast<uint16_t*>(meta + L::SCALES);  // [2 buf][128][ngroups]
 
@@ -267,6 +270,11 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
   }
   for (int i = tid; i < PART; i += THREADS)
     bias[i] = (tensor ? p.bias_v : p.bias_k)[head * D + part * PART + i];
+  if (CAM) {
+    const nkv_camera& cam = tensor ? p.cam_v : p.cam_k;
+    for (int i = tid; i < PART / 8; i += THREADS)
+      cam_sel[i] = cam.matrices ? (cam.cam_index[head * (D / 8) + part * (PART / 8) + i] & 3) : 0;
+  }
   if (ROPE) {
     for (int i = tid; i < PART / 2; i += THREADS) {
       const int local = part * (PART / 2) + i;
@@ -573,7 +581,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
               cbase + static_cast<size_t>(crow_i) * hist.center_width + piece * 8));
         }
         // positional restore (K parts only): this token's frame / row / column
-        const bool rotate = ROPE && tensor == 0;
+        const bool rotate = ROPE && tensor == 0 && p.rope.cos_sin != nullptr;
         int coord_t = 0, coord_h = 0, coord_w = 0;
         const int band_a = p.rope.table_half - 2 * (p.rope.table_half / 3);
         const int band_b = band_a + p.rope.table_half / 3;
@@ -590,6 +598,13 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
             coord_w = min(spatial - prow * p.rope.width, last);
           }
         }
+        // camera transform: this token's frame picks the 4 x 4 matrices
+        const nkv_camera& cam = tensor ? p.cam_v : p.cam_k;
+        const bool transform = CAM && cam.matrices != nullptr;
+        const float* cam_frame = nullptr;
+        if (transform)
+          cam_frame = cam.matrices +
+                      static_cast<size_t>(min((t0 + row) / cam.tokens_per_frame, cam.frames - 1)) * 64;
         laps.lap(6);
         // accumulator complete: the tile's last pair is pair g - 1
         ok = mbar_wait(&bars[PAIR_DONE + ((g - 1) & (NDONE - 1))], ((g - 1) / NDONE) & 1, abort_flag, 330);
@@ -620,6 +635,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
         for (int j4 = 0; j4 < 4; ++j4) {
           const uint32_t cwords[4] = {cen[j4].x, cen[j4].y, cen[j4].z, cen[j4].w};
+          float block[8];   // the 8-wide block j4 of this thread's columns (camera transform only)
 #pragma unroll
           for (int w = 0; w < 4; ++w) {
             const int j = j4 * 8 + w * 2;
@@ -636,7 +652,25 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
               x0 = fmaf(k0, cs.x, -(k1 * cs.y));
               x1 = fmaf(k0, cs.y, k1 * cs.x);
             }
+            if (CAM) {
+              block[2 * w] = x0;
+              block[2 * w + 1] = x1;
+            }
             packed[j4 * 4 + w] = in ? pack_bf16x2(x0, x1) : 0u;
+          }
+          if (transform) {   // slots (w) of the block are mixed by the token's 4 x 4 camera matrix
+            const float4* m = reinterpret_cast<const float4*>(cam_frame + cam_sel[wg * 4 + j4] * 16);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) block[k] = round_to_bf16(block[k]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float4 mi = __ldg(m + i);
+              const float m0 = round_to_bf16(mi.x), m1 = round_to_bf16(mi.y);
+              const float m2 = round_to_bf16(mi.z), m3 = round_to_bf16(mi.w);
+              const float y0 = fmaf(m3, block[6], fmaf(m2, block[4], fmaf(m1, block[2], m0 * block[0])));
+              const float y1 = fmaf(m3, block[7], fmaf(m2, block[5], fmaf(m1, block[3], m0 * block[1])));
+              packed[j4 * 4 + i] = in ? pack_bf16x2(y0, y1) : 0u;
+            }
           }
         }
         tc_fence_before();
@@ -783,7 +817,7 @@ __global__ void fill_empty_kernel(uint16_t* out, float* lse, size_t rows, int d)
 constexpr size_t SMEM_LIMIT = 232448;  // 227 KB per CTA
 long long* g_profile = nullptr;
 
-template <int D, bool ROPE, bool PROF>
+template <int D, bool ROPE, bool CAM, bool PROF>
 int launch(const CUtensorMap maps[5], Params& p, cudaStream_t stream) {
   using L = Layout<D>;
   int nw = MAX_NW;   // as many decoder-row slots as fit (at least the two staging slots' worth)
@@ -794,7 +828,7 @@ int launch(const CUtensorMap maps[5], Params& p, cudaStream_t stream) {
               p.rank, p.ngroups);
   p.nw = nw;
   p.prof = g_profile;
-  auto kernel = attn_codec_kernel<D, ROPE, PROF>;
+  auto kernel = attn_codec_kernel<D, ROPE, CAM, PROF>;
   NKV_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(smem)));
   const int qblocks = ceil_div(p.Q, NQ * QT);
@@ -815,12 +849,17 @@ int launch(const CUtensorMap maps[5], Params& p, cudaStream_t stream) {
   return NKV_OK;
 }
 
-int launch_for(int dk, bool rope, const CUtensorMap maps[5], Params& p, cudaStream_t stream) {
-  if (g_profile != nullptr && dk == 128 && !rope)   // the instrumented build exists for this case only
-    return launch<128, false, true>(maps, p, stream);
+int launch_for(int dk, bool rope, bool cam, const CUtensorMap maps[5], Params& p, cudaStream_t stream) {
+  if (g_profile != nullptr && dk == 128 && !rope && !cam)   // the instrumented build exists for this case only
+    return launch<128, false, false, true>(maps, p, stream);
+  if (cam)   // camera builds always carry the rotation code (a NULL table switches it off at run time)
+    return dk == 128 ? launch<128, true, true, false>(maps, p, stream)
+                     : launch<64, true, true, false>(maps, p, stream);
   if (dk == 128)
-    return rope ? launch<128, true, false>(maps, p, stream) : launch<128, false, false>(maps, p, stream);
-  return rope ? launch<64, true, false>(maps, p, stream) : launch<64, false, false>(maps, p, stream);
+    return rope ? launch<128, true, false, false>(maps, p, stream)
+                : launch<128, false, false, false>(maps, p, stream);
+  return rope ? launch<64, true, false, false>(maps, p, stream)
+              : launch<64, false, false, false>(maps, p, stream);
 }
 
 }  // namespace
@@ -837,7 +876,8 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
                   int dk, int dv, const nkv_history* hist_k, const nkv_history* hist_v,
                   const void* wk, const float* bias_k, const void* wv, const float* bias_v,
                   float scale, void* out, float* lse, int32_t* status_word, int splits,
-                  void* workspace, cudaStream_t stream, const nkv_rope* rope) {
+                  void* workspace, cudaStream_t stream, const nkv_rope* rope,
+                  const nkv_camera* cam_k, const nkv_camera* cam_v) {
   const nkv_history& hk = *hist_k;
   const nkv_history& hv = *hist_v;
   const int N = hk.tokens, rank = hk.rank, group = hk.group;
@@ -892,6 +932,8 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
   p.hk = hk; p.hv = hv; p.bias_k = bias_k; p.bias_v = bias_v;
   p.status = status_word;
   if (rope != nullptr) p.rope = *rope;
+  if (cam_k != nullptr) p.cam_k = *cam_k;
+  if (cam_v != nullptr) p.cam_v = *cam_v;
   // History splits: each grid.z slice attends a contiguous run of tiles and writes a partial
   // (O, lse); the partials are merged by log-sum-exp.  Evens out the rounds of resident clusters.
   const int tiles = ceil_div(N, TOK);
@@ -900,14 +942,14 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
   splits = ceil_div(tiles, p.tiles_per_split);
   if (splits == 1) {
     p.out = static_cast<uint16_t*>(out); p.lse = lse;
-    return launch_for(dk, rope != nullptr, maps, p, stream);
+    return launch_for(dk, rope != nullptr, cam_k != nullptr || cam_v != nullptr, maps, p, stream);
   }
   NKV_REQUIRE(workspace != nullptr, NKV_ERR_INVALID, "history splits need a workspace");
   const size_t rows = static_cast<size_t>(Q) * heads;
   uint16_t* part_out = static_cast<uint16_t*>(workspace);
   float* part_lse = reinterpret_cast<float*>(part_out + static_cast<size_t>(splits) * rows * dv);
   p.out = part_out; p.lse = part_lse;
-  int rc = launch_for(dk, rope != nullptr, maps, p, stream);
+  int rc = launch_for(dk, rope != nullptr, cam_k != nullptr || cam_v != nullptr, maps, p, stream);
   if (rc != NKV_OK) return rc;
   const void* outs[16];
   const float* lses[16];

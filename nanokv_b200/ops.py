@@ -163,13 +163,15 @@ def default_splits(tokens: int) -> int:
 def attn_codec(q, view_k: HistoryView, view_v: HistoryView, wk, bias_k, wv, bias_v, *,
                scale: float, status: torch.Tensor | None = None, splits: int | None = None,
                out: torch.Tensor | None = None, lse: torch.Tensor | None = None,
-               rope: "RopeView | None" = None):
+               rope: "RopeView | None" = None, camera_k: "CameraView | None" = None,
+               camera_v: "CameraView | None" = None):
     """Fused read: q [Q,H,dk] -> (O [Q,H,dv], lse f32 [Q,H]).
 
     wk [H,dk,r], wv [H,dv,r] in q's dtype; bias f32 [H,dk] / [H,dv].  ``splits`` cuts the
     history into that many runs attended in one launch and merged by LSE (None: automatic).
     ``out`` / ``lse`` name contiguous result buffers to fill (e.g. peer-visible ones).
-    ``rope`` rotates the rebuilt keys by the absolute position of every history token.
+    ``rope`` rotates the rebuilt keys by the absolute position of every history token;
+    ``camera_k`` / ``camera_v`` apply the PRoPE camera transform to the rebuilt keys / values.
     """
     device = _require_cuda(wk, bias_k, wv, bias_v, status)
     if not q.is_cuda:
@@ -201,11 +203,51 @@ def attn_codec(q, view_k: HistoryView, view_v: HistoryView, wk, bias_k, wv, bias
         if rope.pair_index is not None and tuple(rope.pair_index.shape) != (H, dk // 2):
             raise ValueError("pair index must be [heads, head_dim/2]")
         rope_struct = ctypes.byref(rope.struct())
-    _lib.check(lib.nkv_attn_codec_rope(
+    cameras = []
+    for camera, width in ((camera_k, dk), (camera_v, dv)):
+        if camera is not None and tuple(camera.cam_index.shape) != (H, width // 8):
+            raise ValueError("camera index must be [heads, head_dim/8]")
+        cameras.append(None if camera is None else ctypes.byref(camera.struct()))
+    _lib.check(lib.nkv_attn_codec_pos(
         _ptr(q), dtype_code(q.dtype), q.stride(0), q.stride(1), Q, H, dk, dv, ctypes.byref(sk),
-        ctypes.byref(sv), _ptr(wk), _ptr(bias_k), _ptr(wv), _ptr(bias_v), rope_struct, float(scale),
-        _ptr(out), _ptr(lse), _ptr(status), splits, _ptr(workspace), nbytes, _stream(device)))
+        ctypes.byref(sv), _ptr(wk), _ptr(bias_k), _ptr(wv), _ptr(bias_v), rope_struct, cameras[0],
+        cameras[1], float(scale), _ptr(out), _ptr(lse), _ptr(status), splits, _ptr(workspace), nbytes,
+        _stream(device)))
     return out, lse
+
+
+class CameraView:
+    """struct nkv_camera over device tensors: matrices f32 [frames, 4, 4, 4], cam_index i32
+    [heads, head_dim/8]; tokens are split evenly over the frames."""
+
+    def __init__(self, matrices: torch.Tensor, cam_index: torch.Tensor, tokens_per_frame: int):
+        _require_cuda(matrices, cam_index)
+        if matrices.dtype != torch.float32 or matrices.dim() != 4 or tuple(matrices.shape[1:]) != (4, 4, 4):
+            raise ValueError("camera matrices must be float32 [frames, 4, 4, 4]")
+        if cam_index.dtype != torch.int32 or cam_index.dim() != 2:
+            raise ValueError("camera index must be int32 [heads, head_dim/8]")
+        if tokens_per_frame <= 0:
+            raise ValueError("tokens_per_frame must be positive")
+        self.matrices, self.cam_index, self.tokens_per_frame = matrices, cam_index, int(tokens_per_frame)
+
+    def struct(self) -> "_lib.Camera":
+        return _lib.Camera(self.matrices.data_ptr(), self.cam_index.data_ptr(),
+                           int(self.matrices.shape[0]), self.tokens_per_frame)
+
+
+def camera_rows(x: torch.Tensor, camera: CameraView) -> torch.Tensor:
+    """PRoPE camera transform of explicit rows x [S,H,d] (nkv_camera_rows) -> contiguous [S,H,d]."""
+    device = _require_cuda(camera.matrices)
+    if not x.is_cuda or x.dim() != 3 or x.stride(2) != 1:
+        raise ValueError("rows must be a CUDA [S,H,d] tensor, contiguous along d")
+    S, H, d = x.shape
+    if d % 8 or tuple(camera.cam_index.shape) != (H, d // 8):
+        raise ValueError("camera index must be [heads, head_dim/8]")
+    out = torch.empty(S, H, d, dtype=x.dtype, device=device)
+    struct = camera.struct()
+    _lib.check(_lib.library().nkv_camera_rows(_ptr(x), dtype_code(x.dtype), x.stride(0), x.stride(1), S,
+                                              H, d, ctypes.byref(struct), _ptr(out), _stream(device)))
+    return out
 
 
 class RopeView:

@@ -562,6 +562,25 @@ def rope_per_token(value: torch.Tensor, multiplier: torch.Tensor, indices: torch
     return torch.view_as_real(pairs * chosen[None]).flatten(-2).to(value.dtype)
 
 
+def camera_selected(x: torch.Tensor, matrix: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+    """PRoPE camera transform of rows x [B,h,S,e] that retain whole 8-wide native blocks:
+    a block holds four (j) two-element (r) slots; slot j of the output block is sum_j' M[i, j'] of
+    the input slots, with M = matrix[b, frame, camera] (4 x 4), camera = native block id % 4 and
+    the S tokens split evenly over the matrix's frames; operands in x's dtype
+    (MGC/core.py:110-137 camera_selected, full layout)."""
+    blocks = indices.long().reshape(indices.shape[0], -1, 8)
+    if not torch.equal(blocks, blocks[..., :1] + torch.arange(8)) or bool((blocks[..., 0] % 8).any()):
+        raise ValueError("Invalid MG camera blocks")
+    cams = (blocks[..., 0] // 8) % 4                                     # [h, G]
+    frames = int(matrix.shape[1])
+    if x.shape[-2] % frames:
+        raise ValueError("PRoPE frame count must divide the token sequence")
+    selected = matrix[:, :, cams].permute(0, 2, 1, 3, 4, 5)             # B, h, F, G, 4, 4
+    values = x.reshape(x.shape[0], x.shape[1], frames, -1, blocks.shape[1], 4, 2)
+    out = torch.einsum("bhfgij,bhftgjr->bhftgir", selected.to(x.dtype), values)
+    return out.reshape(x.shape)
+
+
 # ---------------------------------------------------------------- INT8 operator storage
 def pack_int8_weight(weight: torch.Tensor, group_size: int = 0):
     """fp32 weight [rows, in] -> (int8 codes, bf16 scale [rows, in/group], group): symmetric

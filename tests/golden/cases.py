@@ -185,3 +185,15 @@ def per_token_multiplier(data: dict) -> torch.Tensor:
     tokens = data["value"].shape[2]
     angles = (torch.rand(tokens, data["native_dim"] // 2, generator=gen, dtype=torch.float64) - 0.5) * 40.0
     return torch.polar(torch.ones_like(angles), angles)
+
+
+def build_camera():
+    """Low-width rows [1, heads, tokens, 32] that retain four of the sixteen native 8-wide blocks,
+    and per-frame camera matrices [1, frames, 4 cameras, 4, 4]."""
+    gen = synthetic.generator(903)
+    heads, frames, per_frame, width = 3, 5, 18, 32
+    value = torch.randn(1, heads, frames * per_frame, width, generator=gen).to(torch.bfloat16)
+    blocks = torch.stack([torch.randperm(16, generator=gen)[:width // 8].sort().values for _ in range(heads)])
+    indices = (blocks[:, :, None] * 8 + torch.arange(8)).reshape(heads, width)
+    matrix = torch.randn(1, frames, 4, 4, 4, generator=gen)
+    return {"value": value, "indices": indices, "matrix": matrix}

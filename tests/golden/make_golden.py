@@ -300,6 +300,16 @@ def run_rope_per_token_case(root) -> dict:
     return {"rotated": bits(out), "value_digest": np.array([checksum(data["value"])], dtype=np.uint64)}
 
 
+def run_camera_case(root) -> dict:
+    """camera_selected of the MG core module (torch path)."""
+    core = ref_import.load_mg_core(root)
+    data = cases.build_camera()
+    os.environ.pop("MG35_CODEC_NATIVE_FUSED_CAMERA", None)
+    os.environ.pop("MG35_CODEC_NATIVE_RUNTIME_OPT", None)
+    out = core.camera_selected(data["value"], data["matrix"], data["indices"])
+    return {"transformed": bits(out), "value_digest": np.array([checksum(data["value"])], dtype=np.uint64)}
+
+
 def run_int8_operator_case(root) -> dict:
     """The reference's INT8 operator packing and the bf16 weight it multiplies with."""
     codec = ref_import.load_mg_codec(root)
@@ -360,6 +370,7 @@ def main() -> None:
     save("select_mg_bf16", lambda: run_select_case(cases.MINI_BF16, root))
     save("rope_selected_bf16", lambda: run_rope_selected_case(root))
     save("rope_per_token_bf16", lambda: run_rope_per_token_case(root))
+    save("camera_bf16", lambda: run_camera_case(root))
     save("value_mean_lb_bf16", lambda: run_value_mean_case(cases.ROLLING, root))
     save("int8_operator", lambda: run_int8_operator_case(root))
     save(cases.ROLLING.name, lambda: run_rolling_case(cases.ROLLING, root))

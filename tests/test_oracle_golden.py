@@ -199,3 +199,11 @@ def test_rope_per_token_multipliers():
     assert int(gold["value_digest"][0]) == checksum(data["value"]), "input generator drifted"
     got = oracle.rope_per_token(data["value"], cases.per_token_multiplier(data), data["indices"])
     assert torch.equal(got.view(torch.int16), from_bits(gold["rotated"], torch.bfloat16).view(torch.int16))
+
+
+def test_camera_selected():
+    gold = load("camera_bf16")
+    data = cases.build_camera()
+    assert int(gold["value_digest"][0]) == checksum(data["value"]), "input generator drifted"
+    got = oracle.camera_selected(data["value"], data["matrix"], data["indices"])
+    assert torch.equal(got.view(torch.int16), from_bits(gold["transformed"], torch.bfloat16).view(torch.int16))
