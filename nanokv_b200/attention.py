@@ -99,6 +99,15 @@ def camera_view(matrix: torch.Tensor, indices: torch.Tensor, tokens: int, device
                           camera_index(indices, device), tokens // frames)
 
 
+def _camera(matrix: torch.Tensor, cam_index: torch.Tensor, tokens: int) -> "ops.CameraView":
+    if matrix.dim() != 5 or matrix.shape[0] != 1 or tuple(matrix.shape[2:]) != (4, 4, 4):
+        raise ValueError("camera matrix must be [1, frames, 4, 4, 4]")
+    if tokens % int(matrix.shape[1]):
+        raise ValueError("PRoPE frame count must divide the token sequence")
+    return ops.CameraView(matrix[0].to(device=cam_index.device, dtype=torch.float32).contiguous(),
+                          cam_index, tokens // int(matrix.shape[1]))
+
+
 def merge(out_a, lse_a, out_b, lse_b):
     """Two-partition softmax merge (MGC/core.py:33-42)."""
     return ops.lse_merge([(out_a.contiguous(), lse_a.contiguous()),
@@ -143,6 +152,19 @@ class ReaderGroup:
             pairs = torch.zeros(indices.shape[0], pad_to // 2, dtype=torch.int32)
             pairs[:, :indices.shape[1] // 2] = (indices[:, ::2] // 2).to(torch.int32)
             self.pair_index = pairs.to(device).contiguous()
+        # camera of every 8-wide block of the (padded) row, for the PRoPE transform (K / Q and V / output)
+        self.cam_index_k = self.cam_index_v = None
+        if state.get("indices") is not None and self.width % 8 == 0:
+            def cams(indices):
+                try:
+                    index = camera_index(indices, "cpu")
+                except ValueError:
+                    return None   # this reader does not keep whole native blocks: no camera transform
+                padded = torch.zeros(index.shape[0], pad_to // 8, dtype=torch.int32)
+                padded[:, :index.shape[1]] = index
+                return padded.to(device).contiguous()
+            self.cam_index_k = cams(state["indices"])
+            self.cam_index_v = cams(state.get("v_indices", state["indices"]))
 
     def _pad_last(self, tensor):
         if tensor.shape[-1] == self.padded:
@@ -212,7 +234,8 @@ def compressed_value_mean(low_segments, moments, *, heads: int, native_dim: int)
 
 def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segments,
                      low_segments, reader: Reader, *, rope: "RopeTable | None" = None,
-                     q_positions: torch.Tensor | None = None, value_mean_residual: bool = False):
+                     q_positions: torch.Tensor | None = None, value_mean_residual: bool = False,
+                     camera: dict | None = None):
     """Mixed-dimensional read (MGC/core.py:278-310).  Positional hooks are the identity unless
     ``rope`` is given: then the reduced query is rotated by ``q_positions`` and every low-width
     key read by its segment's ``"positions"``, with the native pairs the group retains
@@ -221,6 +244,10 @@ def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segment
     history minus the lifted mean of its low-width read (a first-moment correction, :726, :793-796);
     every low segment then also carries ``"v_decoder"`` [J, r].  The low-width mean follows from the
     same moments by linearity rather than from materialised rows.
+    ``camera`` = {"q": P^T, "out": P} ([1, frames, 4, 4, 4] over the query rows) with a ``"camera"``
+    entry (P^-1 over the segment's tokens) in every low segment switches on Matrix-Game's PRoPE: the
+    reduced query, the low-width keys and values (inside the kernel) and the low-width output are
+    transformed block-wise (MGC/mg35.py:318-347).
 
     q_pre / q_native [Q,H,D]; native_segments [(K [n,H,D], V [n,H,D])] full
     width (protected history, current chunk); low_segments [{"k": history,
@@ -248,6 +275,10 @@ def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segment
             if group.pair_index is None or q_positions is None:
                 raise ValueError("the selected RoPE needs the group's indices and the query positions")
             query = rope.rotate(query, q_positions, group.pair_index)
+        if camera is not None:
+            if group.cam_index_k is None:
+                raise ValueError("the camera transform needs reader indices that keep whole 8-wide blocks")
+            query = ops.camera_rows(query, _camera(camera["q"], group.cam_index_k, Q))
         out = native_out.index_select(1, head).contiguous()
         lse = native_lse.index_select(1, head).contiguous()
         correction = None
@@ -267,9 +298,16 @@ def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segment
             view_k = group.projected_centers(segment["k"], "k")
             view_v = group.projected_centers(segment["v"], "v")
             rope_view = (rope.view(segment["positions"], group.pair_index) if rope is not None else None)
+            cam_k = cam_v = None
+            if camera is not None:
+                cam_k = _camera(segment["camera"], group.cam_index_k, view_k.tokens)
+                cam_v = _camera(segment["camera"], group.cam_index_v, view_v.tokens)
             oo, ll = ops.attn_codec(
                 query, view_k, view_v, group.k_read, group.bias(segment["k_mean"], "k"),
-                group.v_read, group.bias(segment["v_mean"], "v"), scale=scale, rope=rope_view)
+                group.v_read, group.bias(segment["v_mean"], "v"), scale=scale, rope=rope_view,
+                camera_k=cam_k, camera_v=cam_v)
+            if camera is not None:
+                oo = ops.camera_rows(oo, _camera(camera["out"], group.cam_index_v, Q))
             lifted = torch.einsum("nhe,hed->nhd", oo[..., :group.width], group.lift).contiguous()
             if correction is not None:   # fp32 blend, one rounding, as the reference merges it
                 out, lse = ops.lse_merge([(out.float(), lse), (lifted.float() + correction, ll)])

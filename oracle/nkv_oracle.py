@@ -433,7 +433,7 @@ def compressed_value_mean(low_segments, *, decoder: torch.Tensor, heads: int, na
 
 
 def hybrid_attention(q_pre, q_native, native_segments, low_segments, reader: dict, rope=None,
-                     value_mean=None):
+                     value_mean=None, camera=None):
     """Mixed-dimensional read; positional hooks are the identity unless ``rope`` is given.
 
     ``rope`` = dict(freqs, frame_seqlen, width, q_positions): the reduced query and every
@@ -442,6 +442,9 @@ def hybrid_attention(q_pre, q_native, native_segments, low_segments, reader: dic
     ``value_mean`` [B,H,1,D] switches on the value-mean residual of groups narrower than the head:
     lifted + value_mean[heads] - lift(mean over tokens of the low-width V), in fp32 (:793-796); it
     applies to the single joined low partition, as the reference concatenates its segments.
+    ``camera`` = dict(q=P^T, out=P) with segment["camera"] = P^-1 (each [1, frames, 4, 4, 4]) is
+    Matrix-Game's PRoPE: query, low-width keys and values and the low-width output are transformed
+    block-wise after the rotation (MGC/mg35.py:318-347).
 
     q_* [B,H,Q,D]; native_segments [(K,V)] full-width [B,H,n,D]; low_segments
     [{"k": (latent, centers, ids, mean), "v": (...)}]; reader {"native_dim",
@@ -465,6 +468,8 @@ def hybrid_attention(q_pre, q_native, native_segments, low_segments, reader: dic
             query = rope_selected(query, rope["q_positions"], rope["freqs"],
                                   frame_seqlen=rope["frame_seqlen"], width=rope["width"],
                                   indices=group["indices"])
+        if camera is not None:
+            query = camera_selected(query, camera["q"], group["indices"])
         out = native_out.index_select(1, head)
         lse = native_lse.index_select(1, head)
         if value_mean is not None:   # LingBot's form: one joined low partition per group
@@ -492,7 +497,12 @@ def hybrid_attention(q_pre, q_native, native_segments, low_segments, reader: dic
                 kk = rope_selected(kk, segment["positions"], rope["freqs"],
                                    frame_seqlen=rope["frame_seqlen"], width=rope["width"],
                                    indices=group["indices"])
+            if camera is not None:
+                kk = camera_selected(kk, segment["camera"], group["indices"])
+                vv = camera_selected(vv, segment["camera"], group.get("v_indices", group["indices"]))
             oo, ll = attention_lse(query, kk, vv, scale=scale)
+            if camera is not None:
+                oo = camera_selected(oo, camera["out"], group.get("v_indices", group["indices"]))
             lifted = torch.einsum("bhne,hed->bhnd", oo, group["lift"].to(dtype))
             out, lse = merge(out, lse, lifted, ll)
         result.index_copy_(1, head, out)

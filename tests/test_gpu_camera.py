@@ -74,3 +74,51 @@ def test_camera_inside_the_read(heads, head_dim, rank, history, queries, frames,
     tol = F32_REL_TOL if dtype == torch.float32 else BF16_REL_TOL
     assert rel_err(out.cpu(), want[0].permute(1, 0, 2)) <= tol
     assert float((lse.cpu() - want_lse[0].t()).abs().max()) <= tol * max(1.0, float(want_lse.abs().max()))
+
+
+def test_hybrid_attention_with_camera_hooks():
+    """Matrix-Game's PRoPE around the low-width read: query (P^T), keys / values (P^-1, inside the
+    kernel) and the low-width output (P)."""
+    from test_oracle_golden import encode_all
+    case = cases.FAST_CASES[1]                                   # bf16
+    data = cases.build(case.codec)
+    shape = case.codec.shape
+    dtype = shape.torch_dtype
+    segments = encode_all(case.codec, data)
+    gen = torch.Generator().manual_seed(29)
+    q_frames, low_frames = 2, 4
+    cam = {"q": torch.randn(1, q_frames, 4, 4, 4, generator=gen) * 0.5,
+           "out": torch.randn(1, q_frames, 4, 4, 4, generator=gen) * 0.5}
+    low, native = [], []
+    for index in range(len(case.codec.segments)):
+        seg_k, seg_v = segments["k"][index], segments["v"][index]
+        if index < case.low_segments:
+            entry = {"camera": torch.randn(1, low_frames, 4, 4, 4, generator=gen) * 0.5}
+            for kind, seg in (("k", seg_k), ("v", seg_v)):
+                latent = oracle.dequantize_rows(seg["codes"], seg["scale"])[None]
+                entry[kind] = (latent, seg["centers"].float(), seg["ids"].long(), data[f"{kind}_op"]["mean"])
+            low.append(entry)
+        else:
+            pair = []
+            for kind, seg in (("k", seg_k), ("v", seg_v)):
+                op = data[f"{kind}_op"]
+                rows = oracle.decode_rows(seg, decoder=op["decoder"], mean=op["mean"], dtype=dtype)
+                pair.append(rows.reshape(1, -1, shape.heads, shape.head_dim).permute(0, 2, 1, 3))
+            native.append(tuple(pair))
+    reader_payload = cases.build_reader(case, data)
+    q = data["q"][None].permute(0, 2, 1, 3).contiguous()
+    want = oracle.hybrid_attention(q, q, native, low, reader_payload, camera=cam)[0]
+    plain = oracle.hybrid_attention(q, q, native, low, reader_payload)[0]
+    ops_k, ops_v = device_operator(data["k_op"]), device_operator(data["v_op"])
+    native_dev = [(k[0].permute(1, 0, 2).contiguous().cuda(), v[0].permute(1, 0, 2).contiguous().cuda())
+                  for k, v in native]
+    reader = attention.Reader(reader_payload, dtype=dtype)
+    low_dev = []
+    for index, entry in enumerate(low):
+        low_dev.append({"k": history_from_segments([segments["k"][index]], joint=shape.joint, rank=shape.rank),
+                        "v": history_from_segments([segments["v"][index]], joint=shape.joint, rank=shape.rank),
+                        "k_mean": ops_k.mean, "v_mean": ops_v.mean, "camera": entry["camera"]})
+    got = attention.hybrid_attention(data["q"].cuda(), data["q"].cuda(), native_dev, low_dev, reader,
+                                     camera=cam)
+    assert rel_err(got.cpu().permute(1, 0, 2), want) <= BF16_REL_TOL
+    assert rel_err(plain, want) > 2 * BF16_REL_TOL, "the transform must matter in this case"
