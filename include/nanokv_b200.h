@@ -297,13 +297,27 @@ typedef struct nkv_camera {
 } nkv_camera;
 
 /*
+ * Decoder / reader rows in the order the tensor-core kernel expands a code word: within every
+ * group of 8 latent columns, 0 2 4 6 1 3 5 7 (even elements are the low nibbles of four code
+ * bytes, odd ones the high nibbles, so each bf16 pair comes from one byte permute).  Done once
+ * per operator at load time, like the INT8 expansion; w [rows, rank] bf16 -> out [rows, rank].
+ * The result is only valid as wk / wv of nkv_attn_codec_pos with NKV_WEIGHTS_KERNEL_ORDER and
+ * dtype NKV_BF16.  No counterpart in the reference.
+ */
+#define NKV_WEIGHTS_NATURAL 0
+#define NKV_WEIGHTS_KERNEL_ORDER 1
+int nkv_decoder_prepare(const void* w_bf16, int64_t rows, int rank, void* out_bf16, void* stream);
+
+/*
  * nkv_attn_codec_rope plus the camera transform of the rebuilt keys (camera_k) and values
- * (camera_v); any of rope / camera_k / camera_v may be NULL.
+ * (camera_v); any of rope / camera_k / camera_v may be NULL.  weight_order says whether wk / wv
+ * are as stored (NKV_WEIGHTS_NATURAL) or came from nkv_decoder_prepare.
  */
 int nkv_attn_codec_pos(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head,
                        int Q, int heads, int dk, int dv,
                        const nkv_history* hist_k, const nkv_history* hist_v,
                        const void* wk, const float* bias_k, const void* wv, const float* bias_v,
+                       int weight_order,
                        const nkv_rope* rope, const nkv_camera* camera_k, const nkv_camera* camera_v,
                        float scale, void* out, float* lse, int32_t* status_word, int splits,
                        void* workspace, size_t workspace_bytes, void* stream);

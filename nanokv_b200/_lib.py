@@ -78,9 +78,10 @@ SIGNATURES = {
                                     c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
     "nkv_attn_codec_pos": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int,
                                    POINTER(History), POINTER(History), c_void_p, c_void_p,
-                                   c_void_p, c_void_p, POINTER(Rope), POINTER(Camera), POINTER(Camera),
+                                   c_void_p, c_void_p, c_int, POINTER(Rope), POINTER(Camera), POINTER(Camera),
                                    c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_size_t,
                                    c_void_p]),
+    "nkv_decoder_prepare": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "nkv_camera_rows": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, POINTER(Camera),
                                 c_void_p, c_void_p]),
     "nkv_rope_rows": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, POINTER(Rope),

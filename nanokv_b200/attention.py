@@ -33,8 +33,10 @@ def codec_attention(q: torch.Tensor, hist_k, hist_v, op_k: Operator, op_v: Opera
     if H * D != op_k.joint:
         raise ValueError("query heads do not match the operator's joint width")
     scale = D ** -0.5 if scale is None else scale
-    wk = op_k.decoder.view(H, D, op_k.rank)
-    wv = op_v.decoder.view(H, D, op_v.rank)
+    prepared = (ops.tensor_core_read(q.dtype, D, D, op_k.rank) and op_k.decoder_tc is not None
+                and op_v.decoder_tc is not None)
+    wk = (op_k.decoder_tc if prepared else op_k.decoder).view(H, D, op_k.rank)
+    wv = (op_v.decoder_tc if prepared else op_v.decoder).view(H, D, op_v.rank)
     rope_view = None
     if rope is not None:
         if positions is None:
@@ -44,7 +46,7 @@ def codec_attention(q: torch.Tensor, hist_k, hist_v, op_k: Operator, op_v: Opera
         rope_view = rope.view(positions)
     return ops.attn_codec(q, _view(hist_k), _view(hist_v), wk, op_k.bias.view(H, D), wv,
                           op_v.bias.view(H, D), scale=scale, status=status, splits=splits,
-                          out=out, lse=lse, rope=rope_view)
+                          out=out, lse=lse, rope=rope_view, prepared=prepared)
 
 
 class RopeTable:
@@ -140,6 +142,12 @@ class ReaderGroup:
             return out.contiguous()
         self.k_read = pad_rows(state["k_read"])
         self.v_read = pad_rows(state["v_read"])
+        # the same rows in the order the tensor-core read expands code words
+        self.rank = int(self.k_read.shape[2])
+        self.prepared = (dtype == torch.bfloat16 and pad_to in (64, 128) and self.rank % 64 == 0
+                         and self.k_read.is_cuda)
+        self.k_read_tc = ops.prepare_decoder(self.k_read) if self.prepared else None
+        self.v_read_tc = ops.prepare_decoder(self.v_read) if self.prepared else None
         self._tables: dict = {}
         # native pair retained by every pair of the (padded) low-width row, for the selected RoPE
         # (LB/codec_native_attention.py:111, :271-272: indices keep native complex pairs together)
@@ -302,10 +310,13 @@ def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segment
             if camera is not None:
                 cam_k = _camera(segment["camera"], group.cam_index_k, view_k.tokens)
                 cam_v = _camera(segment["camera"], group.cam_index_v, view_v.tokens)
+            prepared = group.prepared and ops.tensor_core_read(query.dtype, group.padded, group.padded,
+                                                               group.rank)
             oo, ll = ops.attn_codec(
-                query, view_k, view_v, group.k_read, group.bias(segment["k_mean"], "k"),
-                group.v_read, group.bias(segment["v_mean"], "v"), scale=scale, rope=rope_view,
-                camera_k=cam_k, camera_v=cam_v)
+                query, view_k, view_v, group.k_read_tc if prepared else group.k_read,
+                group.bias(segment["k_mean"], "k"), group.v_read_tc if prepared else group.v_read,
+                group.bias(segment["v_mean"], "v"), scale=scale, rope=rope_view,
+                camera_k=cam_k, camera_v=cam_v, prepared=prepared)
             if camera is not None:
                 oo = ops.camera_rows(oo, _camera(camera["out"], group.cam_index_v, Q))
             lifted = torch.einsum("nhe,hed->nhd", oo[..., :group.width], group.lift).contiguous()

@@ -49,6 +49,10 @@ class Operator:
         # bias as the decoder GEMM sees it: the bf16 path rounds the mean to bf16 first
         self.bias = (self.mean.to(torch.bfloat16).float() if self.dtype == torch.bfloat16
                      else self.mean).contiguous()
+        # decoder rows in the order the tensor-core read expands code words (one-time copy)
+        self.decoder_tc = (ops.prepare_decoder(self.decoder)
+                           if self.dtype == torch.bfloat16 and self.decoder.is_cuda and self.rank % 8 == 0
+                           else None)
 
 
     @classmethod

@@ -270,6 +270,12 @@ static int check_camera(const nkv_camera* cam, int d) {
   return NKV_OK;
 }
 
+int nkv_decoder_prepare(const void* w_bf16, int64_t rows, int rank, void* out_bf16, void* stream) {
+  NKV_REQUIRE(w_bf16 && out_bf16 && rows >= 0 && rank > 0, NKV_ERR_INVALID,
+              "decoder_prepare: rows=%lld rank=%d", static_cast<long long>(rows), rank);
+  return tc_prepare_decoder(w_bf16, rows, rank, out_bf16, static_cast<cudaStream_t>(stream));
+}
+
 int nkv_camera_rows(const void* x, int dtype, int64_t stride_row, int64_t stride_head, int S,
                     int heads, int d, const nkv_camera* camera, void* out, void* stream) {
   NKV_REQUIRE(x && out && camera && S >= 0 && heads >= 0 && d > 0, NKV_ERR_INVALID,
@@ -288,14 +294,14 @@ int nkv_attn_codec_rope(const void* q, int dtype, int64_t q_stride_token, int64_
                         void* out, float* lse, int32_t* status_word, int splits, void* workspace,
                         size_t workspace_bytes, void* stream) {
   return nkv_attn_codec_pos(q, dtype, q_stride_token, q_stride_head, Q, heads, dk, dv, hist_k, hist_v,
-                            wk, bias_k, wv, bias_v, rope, nullptr, nullptr, scale, out, lse,
-                            status_word, splits, workspace, workspace_bytes, stream);
+                            wk, bias_k, wv, bias_v, NKV_WEIGHTS_NATURAL, rope, nullptr, nullptr, scale,
+                            out, lse, status_word, splits, workspace, workspace_bytes, stream);
 }
 
 int nkv_attn_codec_pos(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head,
                        int Q, int heads, int dk, int dv, const nkv_history* hist_k,
                        const nkv_history* hist_v, const void* wk, const float* bias_k,
-                       const void* wv, const float* bias_v, const nkv_rope* rope,
+                       const void* wv, const float* bias_v, int weight_order, const nkv_rope* rope,
                        const nkv_camera* camera_k, const nkv_camera* camera_v, float scale,
                        void* out, float* lse, int32_t* status_word, int splits, void* workspace,
                        size_t workspace_bytes, void* stream) {
@@ -312,6 +318,12 @@ int nkv_attn_codec_pos(const void* q, int dtype, int64_t q_stride_token, int64_t
   NKV_REQUIRE(workspace_bytes >= nkv_attn_codec_workspace_bytes(Q, heads, dv, splits),
               NKV_ERR_INVALID, "attn_codec: workspace of %zu bytes is too small for %d splits",
               workspace_bytes, splits);
+  const bool prepared = weight_order == NKV_WEIGHTS_KERNEL_ORDER;
+  NKV_REQUIRE(weight_order == NKV_WEIGHTS_NATURAL || prepared, NKV_ERR_INVALID,
+              "attn_codec: weight_order=%d", weight_order);
+  NKV_REQUIRE(!prepared || (dtype == NKV_BF16 && !simt_forced() && tc_attn_supported(dk, dv, hist_k->rank)),
+              NKV_ERR_INVALID,
+              "attn_codec: kernel-order weights are only valid on the bf16 tensor-core path");
   if (rope != nullptr) {
     rc = check_rope(rope, dk, hist_k->tokens);
     if (rc != NKV_OK) return rc;
@@ -328,7 +340,7 @@ int nkv_attn_codec_pos(const void* q, int dtype, int64_t q_stride_token, int64_t
   if (dtype == NKV_BF16 && !simt_forced())
     return tc_attn_codec(q, q_stride_token, q_stride_head, Q, heads, dk, dv, hist_k, hist_v, wk,
                          bias_k, wv, bias_v, scale, out, lse, status_word, splits, workspace, s,
-                         rope, camera_k, camera_v);
+                         rope, camera_k, camera_v, prepared);
   return simt_attn(q, dtype, q_stride_token, q_stride_head, Q, heads, dk, dv, hist_k, hist_v, wk,
                    bias_k, wv, bias_v, nullptr, nullptr, 0, 0, hist_k->tokens, scale, out, lse, s,
                    rope, camera_k, camera_v);

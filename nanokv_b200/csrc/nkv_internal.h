@@ -60,7 +60,8 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
                   const void* wv, const float* bias_v, float scale, void* out, float* lse,
                   int32_t* status_word, int splits, void* workspace, cudaStream_t stream,
                   const nkv_rope* rope = nullptr, const nkv_camera* cam_k = nullptr,
-                  const nkv_camera* cam_v = nullptr);
+                  const nkv_camera* cam_v = nullptr, bool prepared_weights = false);
+int tc_prepare_decoder(const void* w_bf16, int64_t rows, int rank, void* out_bf16, cudaStream_t stream);
 bool tc_attn_supported(int dk, int dv, int rank);
 void tc_attn_set_profile(long long* device_buckets);
 bool tc_project_supported(int J, int r);

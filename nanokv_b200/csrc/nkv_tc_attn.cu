@@ -66,6 +66,7 @@ enum Bar {
 struct Params {
   int Q, heads, N, rank, nchunks, ngroups, group;
   int scale_dtype, nw;
+  int w_perm;            // decoder rows are in kernel order (tc_prepare_decoder)
   int tiles_per_split;   // grid.z splits the history; split z writes partial (O, lse) number z
   float scale_log2;
   nkv_history hk, hv;
@@ -162,6 +163,39 @@ __device__ __forceinline__ uint4 dequant8_bf16(uint32_t word, __nv_bfloat162 sca
 __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
   __syncwarp();
   if (lane == 0) mbar_arrive(bar);
+}
+
+// Kernel-order variants: the decoder rows were prepared (tc_prepare_decoder) so that within every
+// group of 8 latent columns the order is e0 e2 e4 e6 e1 e3 e5 e7.  The even elements are the low
+// nibbles of a code word and the odd ones its high nibbles, so a byte permute against the constant
+// 0x43 builds each bf16 pair directly (4 PRMT per 8 elements instead of 4 PRMT + 4 LOP3: the
+// integer pipe is what bounds the expansion).
+__device__ __forceinline__ uint4 dequant8_bf16_perm(uint32_t word, __nv_bfloat162 scale2) {
+  const uint32_t lo = word & 0x0F0F0F0Fu, hi = (word >> 4) & 0x0F0F0F0Fu, magic = 0x43434343u;
+  const uint32_t t[4] = {__byte_perm(lo, magic, 0x4140), __byte_perm(lo, magic, 0x4342),
+                         __byte_perm(hi, magic, 0x4140), __byte_perm(hi, magic, 0x4342)};
+  const uint32_t bias_bits = 0x43074307u;   // bf16 pair (135, 135)
+  const __nv_bfloat162 bias2 = *reinterpret_cast<const __nv_bfloat162*>(&bias_bits);
+  uint4 r;
+  uint32_t* o = &r.x;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 v = __hmul2(__hsub2(*reinterpret_cast<const __nv_bfloat162*>(&t[i]), bias2), scale2);
+    o[i] = *reinterpret_cast<const uint32_t*>(&v);
+  }
+  return r;
+}
+
+__device__ __forceinline__ uint4 dequant8_perm(uint32_t word, float scale) {
+  float e[8];
+#pragma unroll
+  for (int b = 0; b < 4; ++b) {
+    const uint32_t byte = (word >> (8 * b)) & 0xFFu;
+    e[2 * b] = static_cast<float>(static_cast<int>(byte & 15u) - 7) * scale;
+    e[2 * b + 1] = static_cast<float>(static_cast<int>(byte >> 4) - 7) * scale;
+  }
+  return make_uint4(pack_bf16x2(e[0], e[2]), pack_bf16x2(e[4], e[6]), pack_bf16x2(e[1], e[3]),
+                    pack_bf16x2(e[5], e[7]));
 }
 
 // TMEM column of latent staging slot s (a pair of chunks = 64 columns).  Slots 0 and 1 avoid the
@@ -540,14 +574,14 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
               const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&pair);
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
-                const uint4 v = dequant8_bf16(words[k], scale2);
+                const uint4 v = p.w_perm ? dequant8_bf16_perm(words[k], scale2) : dequant8_bf16(words[k], scale2);
                 packed[4 * k] = v.x; packed[4 * k + 1] = v.y; packed[4 * k + 2] = v.z; packed[4 * k + 3] = v.w;
               }
             } else {
               const float sc = scale_to_float(sbits, p.scale_dtype);
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
-                const uint4 v = dequant8(words[k], sc);
+                const uint4 v = p.w_perm ? dequant8_perm(words[k], sc) : dequant8(words[k], sc);
                 packed[4 * k] = v.x; packed[4 * k + 1] = v.y; packed[4 * k + 2] = v.z; packed[4 * k + 3] = v.w;
               }
             }
@@ -864,6 +898,32 @@ int launch_for(int dk, bool rope, bool cam, const CUtensorMap maps[5], Params& p
 
 }  // namespace
 
+// out[row][8 g + i] = w[row][8 g + perm[i]], perm = 0 2 4 6 1 3 5 7: the order in which the kernel
+// expands a code word (dequant8_bf16_perm).  Thread = one group of 8 columns (16 bytes).
+__global__ void __launch_bounds__(256)
+prepare_decoder_kernel(const uint4* w, long long groups, uint4* out) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= groups) return;
+  const uint4 v = w[idx];   // (e0 e1) (e2 e3) (e4 e5) (e6 e7)
+  uint4 r;
+  r.x = __byte_perm(v.x, v.y, 0x5410);   // e0 e2
+  r.y = __byte_perm(v.z, v.w, 0x5410);   // e4 e6
+  r.z = __byte_perm(v.x, v.y, 0x7632);   // e1 e3
+  r.w = __byte_perm(v.z, v.w, 0x7632);   // e5 e7
+  out[idx] = r;
+}
+
+int tc_prepare_decoder(const void* w_bf16, int64_t rows, int rank, void* out_bf16, cudaStream_t stream) {
+  NKV_REQUIRE(rank % 8 == 0 && ((reinterpret_cast<uintptr_t>(w_bf16) | reinterpret_cast<uintptr_t>(out_bf16)) & 15) == 0,
+              NKV_ERR_INVALID, "prepare_decoder: rank %d must be a multiple of 8, arrays 16-byte aligned", rank);
+  const long long groups = rows * (rank / 8);
+  if (groups == 0) return NKV_OK;
+  prepare_decoder_kernel<<<static_cast<unsigned>((groups + 255) / 256), 256, 0, stream>>>(
+      static_cast<const uint4*>(w_bf16), groups, static_cast<uint4*>(out_bf16));
+  NKV_LAUNCH_CHECK("prepare_decoder_kernel");
+  return NKV_OK;
+}
+
 // Development aid: 32 device int64 cycle buckets filled by CTA (0,0) of later launches
 // (compute thread 0: buckets 0-12, MMA thread: 16-22); nullptr switches it off.
 void tc_attn_set_profile(long long* device_buckets) { g_profile = device_buckets; }
@@ -877,7 +937,7 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
                   const void* wk, const float* bias_k, const void* wv, const float* bias_v,
                   float scale, void* out, float* lse, int32_t* status_word, int splits,
                   void* workspace, cudaStream_t stream, const nkv_rope* rope,
-                  const nkv_camera* cam_k, const nkv_camera* cam_v) {
+                  const nkv_camera* cam_k, const nkv_camera* cam_v, bool prepared_weights) {
   const nkv_history& hk = *hist_k;
   const nkv_history& hv = *hist_v;
   const int N = hk.tokens, rank = hk.rank, group = hk.group;
@@ -931,6 +991,7 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.hk = hk; p.hv = hv; p.bias_k = bias_k; p.bias_v = bias_v;
   p.status = status_word;
+  p.w_perm = prepared_weights ? 1 : 0;
   if (rope != nullptr) p.rope = *rope;
   if (cam_k != nullptr) p.cam_k = *cam_k;
   if (cam_v != nullptr) p.cam_v = *cam_v;

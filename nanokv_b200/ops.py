@@ -164,7 +164,7 @@ def attn_codec(q, view_k: HistoryView, view_v: HistoryView, wk, bias_k, wv, bias
                scale: float, status: torch.Tensor | None = None, splits: int | None = None,
                out: torch.Tensor | None = None, lse: torch.Tensor | None = None,
                rope: "RopeView | None" = None, camera_k: "CameraView | None" = None,
-               camera_v: "CameraView | None" = None):
+               camera_v: "CameraView | None" = None, prepared: bool = False):
     """Fused read: q [Q,H,dk] -> (O [Q,H,dv], lse f32 [Q,H]).
 
     wk [H,dk,r], wv [H,dv,r] in q's dtype; bias f32 [H,dk] / [H,dv].  ``splits`` cuts the
@@ -172,6 +172,7 @@ def attn_codec(q, view_k: HistoryView, view_v: HistoryView, wk, bias_k, wv, bias
     ``out`` / ``lse`` name contiguous result buffers to fill (e.g. peer-visible ones).
     ``rope`` rotates the rebuilt keys by the absolute position of every history token;
     ``camera_k`` / ``camera_v`` apply the PRoPE camera transform to the rebuilt keys / values.
+    ``prepared``: wk / wv came from :func:`prepare_decoder` (kernel order; bf16 tensor-core path only).
     """
     device = _require_cuda(wk, bias_k, wv, bias_v, status)
     if not q.is_cuda:
@@ -210,10 +211,34 @@ def attn_codec(q, view_k: HistoryView, view_v: HistoryView, wk, bias_k, wv, bias
         cameras.append(None if camera is None else ctypes.byref(camera.struct()))
     _lib.check(lib.nkv_attn_codec_pos(
         _ptr(q), dtype_code(q.dtype), q.stride(0), q.stride(1), Q, H, dk, dv, ctypes.byref(sk),
-        ctypes.byref(sv), _ptr(wk), _ptr(bias_k), _ptr(wv), _ptr(bias_v), rope_struct, cameras[0],
+        ctypes.byref(sv), _ptr(wk), _ptr(bias_k), _ptr(wv), _ptr(bias_v), 1 if prepared else 0,
+        rope_struct, cameras[0],
         cameras[1], float(scale), _ptr(out), _ptr(lse), _ptr(status), splits, _ptr(workspace), nbytes,
         _stream(device)))
     return out, lse
+
+
+def prepare_decoder(weight: torch.Tensor) -> torch.Tensor:
+    """bf16 decoder / reader rows [..., rank] in the order the tensor-core kernel expands code words
+    (nkv_decoder_prepare): a one-time copy per operator; pass it with ``prepared=True``."""
+    device = _require_cuda(weight)
+    if weight.dtype != torch.bfloat16 or weight.shape[-1] % 8:
+        raise ValueError("prepare_decoder takes bf16 rows whose length is a multiple of 8")
+    out = torch.empty_like(weight)
+    rank = weight.shape[-1]
+    _lib.check(_lib.library().nkv_decoder_prepare(_ptr(weight), weight.numel() // rank, rank, _ptr(out),
+                                                  _stream(device)))
+    return out
+
+
+def tensor_core_read(dtype: torch.dtype, dk: int, dv: int, rank: int) -> bool:
+    """Whether nkv_attn_codec runs this shape on the tcgen05 kernel (and may take prepared weights)."""
+    import os
+    return (dtype == torch.bfloat16 and dk == dv and dk in (64, 128) and rank % 64 == 0
+            and not _SIMT_FORCED[0] and os.environ.get("NKV_FORCE_SIMT", "0") in ("", "0"))
+
+
+_SIMT_FORCED = [False]
 
 
 class CameraView:
@@ -340,7 +365,9 @@ def attention_lse(q, k, v, *, scale: float):
                                          torch.zeros(H, d, dtype=torch.float32, device=device))
         view_k = _plain_history(k)
         view_v = _plain_history(v)
-        return attn_codec(q, view_k, view_v, zero_w, zero_b, zero_w, zero_b, scale=scale)
+        # all-zero weights are their own kernel-order copy
+        return attn_codec(q, view_k, view_v, zero_w, zero_b, zero_w, zero_b, scale=scale,
+                          prepared=tensor_core_read(q.dtype, d, dv, 64))
     out = torch.empty(Q, H, dv, dtype=q.dtype, device=device)
     lse = torch.empty(Q, H, dtype=torch.float32, device=device)
     if k.stride() != v.stride() and d == dv:
@@ -476,4 +503,5 @@ def lse_merge(partials):
 
 def force_simt(on: bool) -> None:
     """Triage hook: run bf16 work on the fp32 CUDA-core kernels (same rounding points)."""
+    _SIMT_FORCED[0] = bool(on)
     _lib.library().nkv_debug_force_simt(1 if on else 0)
