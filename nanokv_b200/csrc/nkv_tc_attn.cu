@@ -423,6 +423,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         // that report to the peer's KV_READY), then wait for the peers' parts to land here
         ok = mbar_wait(&bars[EPI_LOCAL], it & 1, abort_flag, 218);
         if (ok && it > 0) ok = mbar_wait_cluster(&bars[KV_FREE], (it - 1) & 1, abort_flag, 219);
+        laps.lap(7);
         if (!ok) break;
         {
           const uint32_t ready = smem_u32(&bars[KV_READY]);
