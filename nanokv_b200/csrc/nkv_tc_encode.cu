@@ -30,6 +30,7 @@ enum Bar { TMA_FULL = 0, A_FULL = 4, STAGE_FREE = 8, ACC_DONE = 12, SIDE_READY =
 struct Params {
   int S, J, NB, NACC, n_total;      // n_total = r (project) or C (assign)
   int nstages;                      // depth of the shared-memory operand ring (2..4)
+  int rows;                         // tokens owned by one CTA (<= TM)
   // project
   const uint16_t* x; const uint16_t* centers; const void* ids; int id_bytes;
   const float* mean; uint16_t* coeff;
@@ -69,7 +70,8 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   float* cn_part = reinterpret_cast<float*>(cand_i + 128);        // [C][2]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int m0 = blockIdx.x * TM;
+  const int m0 = blockIdx.x * p.rows;                   // this CTA's tokens: [m0, m_end)
+  const int m_end = min(p.S, m0 + p.rows);
   const int n_base = blockIdx.y * p.NACC * p.NB;
   const int nchunks = p.J / 64;
 
@@ -213,7 +215,7 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           if (ok) {
             if (cand_d[row] < best) { best = cand_d[row]; best_i = cand_i[row]; }
             const int t = m0 + row;
-            if (t < p.S) {
+            if (t < m_end) {
               if (p.id_bytes == 1) static_cast<uint8_t*>(p.ids_out)[t] = static_cast<uint8_t>(best_i);
               else static_cast<uint16_t*>(p.ids_out)[t] = static_cast<uint16_t>(best_i);
             }
@@ -224,7 +226,7 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       // ---- residual operand: bf16((x - centre[id]) - mean), 32 columns per thread
       const int r = tid >> 1, half = tid & 1;
       const int t = m0 + r;
-      const bool in = t < p.S;
+      const bool in = t < m_end;
       const uint16_t* xrow = p.x + static_cast<size_t>(in ? t : 0) * p.J;
       const uint16_t* crow = p.centers + static_cast<size_t>(in ? load_id(p.ids, p.id_bytes, t) : 0) * p.J;
       // raw operands of one chunk for this thread: 32 columns of x and of the centre row
@@ -286,7 +288,7 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           const int col = cc * 32, acc = col / p.NB;
           float v[32];
           tmem_ld32(tmem_base + lane_sel + acc * 256 + (col - acc * p.NB), v);
-          if (tok < p.S) {
+          if (tok < m_end) {
             uint16_t* dst = p.coeff + static_cast<size_t>(tok) * p.n_total + n_base + col;
 #pragma unroll
             for (int j4 = 0; j4 < 4; ++j4) {
@@ -337,6 +339,27 @@ bool tc_project_supported(int J, int r) {
          smem_bytes(nacc, nb, 0) <= 232448;
 }
 
+// Tokens per CTA (<= TM): the MMA always spans TM rows, but the operand build, the loads and the
+// epilogue scale with the rows a CTA owns, so the token tiles are sized to fill whole rounds of the
+// SMs instead of leaving the last round mostly empty (12,480 tokens: 147 CTAs of 85 rows instead
+// of 98 of 128).  Not below 64 rows: every CTA streams the whole B operand from L2.
+int pick_rows(int S, int column_parts) {
+  static int sms = 0;
+  if (sms == 0) {
+    int device = 0;
+    cudaDeviceProp prop{};
+    if (cudaGetDevice(&device) == cudaSuccess && cudaGetDeviceProperties(&prop, device) == cudaSuccess)
+      sms = prop.multiProcessorCount;
+    if (sms <= 0) sms = 148;
+  }
+  const long long units = static_cast<long long>(ceil_div(S, TM)) * column_parts;
+  const long long waves = (units + sms - 1) / sms;
+  const long long tiles = waves * sms / column_parts;
+  long long rows = (S + tiles - 1) / (tiles > 0 ? tiles : 1);
+  rows = rows < 64 ? 64 : (rows > TM ? TM : rows);
+  return static_cast<int>(rows);
+}
+
 bool tc_assign_supported(int J, int C) {
   if (J % 64 || C % 16 || C > 512) return false;
   return C <= 256 || C % 64 == 0;
@@ -371,7 +394,8 @@ int tc_project(const void* x_bf16, const void* centers_bf16, const void* ids, in
   auto kernel = encode_gemm_kernel<false>;
   NKV_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(smem)));
-  dim3 grid(ceil_div(S, TM), gy);
+  p.rows = pick_rows(S, gy);
+  dim3 grid(ceil_div(S, p.rows), gy);
   kernel<<<grid, THREADS, smem, stream>>>(map_b, map_b, p);
   NKV_LAUNCH_CHECK("encode_gemm_kernel<project>");
   return NKV_OK;
@@ -405,7 +429,8 @@ int tc_assign(const void* x_bf16, const void* centers_bf16, int S, int J, int C,
   auto kernel = encode_gemm_kernel<true>;
   NKV_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(smem)));
-  dim3 grid(ceil_div(S, TM), 1);
+  p.rows = pick_rows(S, 1);
+  dim3 grid(ceil_div(S, p.rows), 1);
   kernel<<<grid, THREADS, smem, stream>>>(map_a, map_b, p);
   NKV_LAUNCH_CHECK("encode_gemm_kernel<assign>");
   return NKV_OK;
