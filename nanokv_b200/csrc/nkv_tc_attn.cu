@@ -198,6 +198,14 @@ __device__ __forceinline__ uint4 dequant8_perm(uint32_t word, float scale) {
                     pack_bf16x2(e[5], e[7]));
 }
 
+// 2^x as the bare exponential-unit instruction (results below 2^-126 flush to zero, which is
+// what a softmax weight that small is worth)
+__device__ __forceinline__ float exp2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // TMEM column of latent staging slot s (a pair of chunks = 64 columns).  Slots 0 and 1 avoid the
 // columns where P of the previous tile may still be read by its PV MMAs (P0 in [0,64), P1 in
 // [128,192)), so the next tile's first two pairs can be expanded while those MMAs run; slot 2 is
@@ -735,18 +743,29 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         // S of this tile was issued after PV of the previous one, so O is up to date here
         const uint32_t s_addr = tmem_base + lane_sel + wg * 128;
         float mx = -INFINITY;
-#pragma unroll 1
-        for (int cc = 0; cc < TOK / 32; ++cc) {
-          if (cc * 32 >= valid) break;
-          float v[32];
-          tmem_ld32(s_addr + cc * 32, v);
-          if (valid == TOK) {
+        {
+          uint32_t raw[2][32];
+          tmem_ld32_issue(s_addr, raw[0]);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) mx = fmaxf(mx, v[j]);
-          } else {
+          for (int cc = 0; cc < TOK / 32; ++cc) {
+            uint32_t (&cur)[32] = raw[cc & 1];
+            tmem_ld32_wait(cur);
+            if (cc + 1 < TOK / 32) tmem_ld32_issue(s_addr + (cc + 1) * 32, raw[(cc + 1) & 1]);
+            if (valid == TOK) {   // four chains instead of one
+              float ma = -INFINITY, mb_ = -INFINITY, mc = -INFINITY, md = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (cc * 32 + j < valid) mx = fmaxf(mx, v[j]);
+              for (int j = 0; j < 32; j += 4) {
+                ma = fmaxf(ma, __uint_as_float(cur[j]));
+                mb_ = fmaxf(mb_, __uint_as_float(cur[j + 1]));
+                mc = fmaxf(mc, __uint_as_float(cur[j + 2]));
+                md = fmaxf(md, __uint_as_float(cur[j + 3]));
+              }
+              mx = fmaxf(mx, fmaxf(fmaxf(ma, mb_), fmaxf(mc, md)));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (cc * 32 + j < valid) mx = fmaxf(mx, __uint_as_float(cur[j]));
+            }
           }
         }
         const float m_new = mx * p.scale_log2;
@@ -768,26 +787,33 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           l_run *= alpha;
           m_used = m_next;
         }
-        // P (bf16 pairs) replaces S in place: the 16 cells written per step lie below the 32 read
-        float sum = 0.f;
-#pragma unroll 1
+        // P (bf16 pairs) replaces S in place: the 16 cells written per step lie below the 32 read.
+        // The load of the next 32 scores stays in flight under the exponentials of the current ones.
+        float sum = 0.f, sum_b = 0.f, sum_c = 0.f, sum_d = 0.f;   // four chains instead of one
+        uint32_t raw[2][32];
+        tmem_ld32_issue(s_addr, raw[0]);
+#pragma unroll
         for (int cc = 0; cc < TOK / 32; ++cc) {
-          float v[32];
-          tmem_ld32(s_addr + cc * 32, v);
+          uint32_t (&cur)[32] = raw[cc & 1];
+          tmem_ld32_wait(cur);
+          if (cc + 1 < TOK / 32) tmem_ld32_issue(s_addr + (cc + 1) * 32, raw[(cc + 1) & 1]);
           uint32_t packed[16];
           if (valid == TOK) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              const float p0 = exp2f(fmaf(v[j], p.scale_log2, -m_used));
-              const float p1 = exp2f(fmaf(v[j + 1], p.scale_log2, -m_used));
-              sum += p0 + p1;
+            for (int j = 0; j < 32; j += 4) {
+              const float p0 = exp2_approx(fmaf(__uint_as_float(cur[j]), p.scale_log2, -m_used));
+              const float p1 = exp2_approx(fmaf(__uint_as_float(cur[j + 1]), p.scale_log2, -m_used));
+              const float p2 = exp2_approx(fmaf(__uint_as_float(cur[j + 2]), p.scale_log2, -m_used));
+              const float p3 = exp2_approx(fmaf(__uint_as_float(cur[j + 3]), p.scale_log2, -m_used));
+              sum += p0; sum_b += p1; sum_c += p2; sum_d += p3;
               packed[j >> 1] = pack_bf16x2(p0, p1);
+              packed[(j >> 1) + 1] = pack_bf16x2(p2, p3);
             }
           } else {
 #pragma unroll
             for (int j = 0; j < 32; j += 2) {
-              float p0 = (cc * 32 + j < valid) ? exp2f(fmaf(v[j], p.scale_log2, -m_used)) : 0.f;
-              float p1 = (cc * 32 + j + 1 < valid) ? exp2f(fmaf(v[j + 1], p.scale_log2, -m_used)) : 0.f;
+              float p0 = (cc * 32 + j < valid) ? exp2f(fmaf(__uint_as_float(cur[j]), p.scale_log2, -m_used)) : 0.f;
+              float p1 = (cc * 32 + j + 1 < valid) ? exp2f(fmaf(__uint_as_float(cur[j + 1]), p.scale_log2, -m_used)) : 0.f;
               sum += p0 + p1;
               packed[j >> 1] = pack_bf16x2(p0, p1);
             }
@@ -795,7 +821,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           tmem_st16(s_addr + cc * 16, packed);
         }
         tmem_wait_st();
-        l_run += sum;
+        l_run += (sum + sum_b) + (sum_c + sum_d);
         laps.lap(11);
         tc_fence_before();
         warp_arrive(&bars[P_READY + wg], lane);
