@@ -654,6 +654,9 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         laps.lap(7);
         if (!ok) break;
         tc_fence_after();
+        // the accumulator read stays in flight under the centre staging
+        uint32_t acc_raw[32];
+        tmem_ld32_issue(tmem_base + lane_sel + wg * 32, acc_raw);
         {
           uint8_t* stage = smem + L::SCRATCH_OFF + warp * (32 * PIECES * 16);
 #pragma unroll
@@ -672,8 +675,10 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
           fence_proxy_async();
           warp_arrive(&bars[CODES_FREE], lane);
         }
+        tmem_ld32_wait(acc_raw);
         float v[32];
-        tmem_ld32(tmem_base + lane_sel + wg * 32, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc_raw[i]);
         uint32_t packed[16];
 #pragma unroll
         for (int j4 = 0; j4 < 4; ++j4) {
