@@ -23,7 +23,10 @@ LB = "models/LingBot-World-2.0/fast"
 
 
 def reference_root(root: str | os.PathLike | None = None) -> Path:
-    root = Path(root or os.environ.get("NANOKV_REFERENCE_ROOT", "/root/reference"))
+    root = root or os.environ.get("NANOKV_REFERENCE_ROOT")
+    if not root:
+        raise FileNotFoundError("pass the reference checkout's root or set NANOKV_REFERENCE_ROOT")
+    root = Path(root)
     if not (root / MG / "diffsynth/models/nanokv_codec.py").exists():
         raise FileNotFoundError(f"no reference checkout at {root}")
     return root

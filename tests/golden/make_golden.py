@@ -1,6 +1,6 @@
 """Generate the golden fixtures by running the UNMODIFIED reference on CPU.
 
-    python tests/golden/make_golden.py [--reference /path/to/NanoKV]
+    python tests/golden/make_golden.py --reference /path/to/NanoKV   (or NANOKV_REFERENCE_ROOT)
 
 Needs a checkout of the reference project (it is imported, never copied).
 Inputs are regenerated from seeds by ``tests/golden/cases.py``; only the
