@@ -684,6 +684,20 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         for (int j4 = 0; j4 < 4; ++j4) {
           const uint32_t cwords[4] = {cen[j4].x, cen[j4].y, cen[j4].z, cen[j4].w};
           float block[8];   // the 8-wide block j4 of this thread's columns (camera transform only)
+          if (!ROPE && !CAM) {
+            // plain rebuild in packed bf16 arithmetic: bf16x2(acc + bias) then one bf16x2 add of the
+            // centre word -- the same two roundings (the sum of two bf16 numbers is exact in fp32
+            // unless the smaller one lies below the rounding step of the larger either way)
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              const int j = j4 * 8 + w * 2;
+              const uint32_t first = pack_bf16x2(v[j] + bias[wg * 32 + j], v[j + 1] + bias[wg * 32 + j + 1]);
+              const __nv_bfloat162 sum = __hadd2(*reinterpret_cast<const __nv_bfloat162*>(&first),
+                                                 *reinterpret_cast<const __nv_bfloat162*>(&cwords[w]));
+              packed[j4 * 4 + w] = in ? *reinterpret_cast<const uint32_t*>(&sum) : 0u;
+            }
+            continue;
+          }
 #pragma unroll
           for (int w = 0; w < 4; ++w) {
             const int j = j4 * 8 + w * 2;
