@@ -30,6 +30,8 @@
 // TMEM columns: [0,128) S of query tile 0 (decode accumulator in [0,64));
 // [128,256) S of tile 1; latent staging slots of 32 columns at 64, 96, 192, 224; [256,384) O
 // tile 0; [384,512) O tile 1.
+#include <type_traits>
+
 #include "nkv_internal.h"
 #include "nkv_tc.cuh"
 
@@ -551,59 +553,69 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       code_next[0] = code_at(0);
       code_next[1] = nchunks > 1 ? code_at(1) : make_uint4(0, 0, 0, 0);
       int st = 0;
-      for (int c0 = 0; c0 < nchunks && ok; c0 += 2) {
-        const int n = min(2, nchunks - c0);   // chunks in this pair
-        const uint4 code_cur[2] = {code_next[0], code_next[1]};
-        if (c0 + 2 < nchunks) code_next[0] = code_at(c0 + 2);
-        if (c0 + 3 < nchunks) code_next[1] = code_at(c0 + 3);
-        laps.lap(5);
-        // The staging slot's previous tenant in this tile is pair g - NSTAGE.  The first NSTAGE pairs
-        // of a tile follow pairs of the previous tile, all complete (its epilogue waited for the last
-        // one); slot 2 is also where P of the second query tile sat, read by that tile's PV MMAs.
-        if (c0 >= 2 * NSTAGE)
-          ok = mbar_wait(&bars[PAIR_DONE + ((g - NSTAGE) & (NDONE - 1))], ((g - NSTAGE) / NDONE) & 1,
-                         abort_flag, 320 + st);
-        else if (c0 == 4 && it > 0 && nq == 2)
-          ok = mbar_wait(&bars[PV_DONE + 1], (it - 1) & 1, abort_flag, 323);
-        laps.lap(2);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          if (j < n) {
-            const int c = c0 + j;
-            const uint4 code = code_cur[j];
-            const int col0 = c * CHUNK + wg * 32;   // this thread: token `row`, latent columns col0 .. +32
-            const int gi = ng == 1 ? 0 : (p.group == 32 ? 2 * c + wg : col0 / p.group);
-            const uint16_t sbits = my_scales[gi];
-            const uint32_t words[4] = {code.x, code.y, code.z, code.w};
-            uint32_t packed[16];
-            if (p.scale_dtype == NKV_BF16) {
-              const uint32_t pair = static_cast<uint32_t>(sbits) * 0x00010001u;
-              const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&pair);
-#pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                const uint4 v = p.w_perm ? dequant8_bf16_perm(words[k], scale2) : dequant8_bf16(words[k], scale2);
-                packed[4 * k] = v.x; packed[4 * k + 1] = v.y; packed[4 * k + 2] = v.z; packed[4 * k + 3] = v.w;
+      // The pair loop exists twice: FASTQ is the common deployment (one bf16 scale per token,
+      // decoder rows in kernel order) with every choice made at compile time; the other copy keeps
+      // the run-time choices (grouped or fp16 scales, natural-order rows).  Picking between them
+      // inside the loop instead costs 7 % of the kernel.
+      auto expand_pairs = [&](auto fast_tag) {
+        constexpr bool FASTQ = decltype(fast_tag)::value;
+        for (int c0 = 0; c0 < nchunks && ok; c0 += 2) {
+          const int n = min(2, nchunks - c0);   // chunks in this pair
+          const uint4 code_cur[2] = {code_next[0], code_next[1]};
+          if (c0 + 2 < nchunks) code_next[0] = code_at(c0 + 2);
+          if (c0 + 3 < nchunks) code_next[1] = code_at(c0 + 3);
+          laps.lap(5);
+          // The staging slot's previous tenant in this tile is pair g - NSTAGE.  The first NSTAGE pairs
+          // of a tile follow pairs of the previous tile, all complete (its epilogue waited for the last
+          // one); slot 2 is also where P of the second query tile sat, read by that tile's PV MMAs.
+          if (c0 >= 2 * NSTAGE)
+            ok = mbar_wait(&bars[PAIR_DONE + ((g - NSTAGE) & (NDONE - 1))], ((g - NSTAGE) / NDONE) & 1,
+                           abort_flag, 320 + st);
+          else if (c0 == 4 && it > 0 && nq == 2)
+            ok = mbar_wait(&bars[PV_DONE + 1], (it - 1) & 1, abort_flag, 323);
+          laps.lap(2);
+          if (!ok) break;
+          tc_fence_after();
+  #pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            if (j < n) {
+              const int c = c0 + j;
+              const uint4 code = code_cur[j];
+              const int col0 = c * CHUNK + wg * 32;   // this thread: token `row`, latent columns col0 .. +32
+              const int gi = (FASTQ || ng == 1) ? 0 : (p.group == 32 ? 2 * c + wg : col0 / p.group);
+              const uint16_t sbits = my_scales[gi];
+              const uint32_t words[4] = {code.x, code.y, code.z, code.w};
+              uint32_t packed[16];
+              if (FASTQ || p.scale_dtype == NKV_BF16) {
+                const uint32_t pair = static_cast<uint32_t>(sbits) * 0x00010001u;
+                const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&pair);
+  #pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  const uint4 v = (FASTQ || p.w_perm) ? dequant8_bf16_perm(words[k], scale2)
+                                                       : dequant8_bf16(words[k], scale2);
+                  packed[4 * k] = v.x; packed[4 * k + 1] = v.y; packed[4 * k + 2] = v.z; packed[4 * k + 3] = v.w;
+                }
+              } else {
+                const float sc = scale_to_float(sbits, p.scale_dtype);
+  #pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  const uint4 v = p.w_perm ? dequant8_perm(words[k], sc) : dequant8(words[k], sc);
+                  packed[4 * k] = v.x; packed[4 * k + 1] = v.y; packed[4 * k + 2] = v.z; packed[4 * k + 3] = v.w;
+                }
               }
-            } else {
-              const float sc = scale_to_float(sbits, p.scale_dtype);
-#pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                const uint4 v = p.w_perm ? dequant8_perm(words[k], sc) : dequant8(words[k], sc);
-                packed[4 * k] = v.x; packed[4 * k + 1] = v.y; packed[4 * k + 2] = v.z; packed[4 * k + 3] = v.w;
-              }
+              tmem_st16(tmem_base + lane_sel + staging_col(st) + j * 32 + wg * 16, packed);
             }
-            tmem_st16(tmem_base + lane_sel + staging_col(st) + j * 32 + wg * 16, packed);
           }
+          tmem_wait_st();
+          tc_fence_before();
+          warp_arrive(&bars[LAT_FULL + st], lane);
+          laps.lap(4);
+          ++g;
+          if (++st == NSTAGE) st = 0;
         }
-        tmem_wait_st();
-        tc_fence_before();
-        warp_arrive(&bars[LAT_FULL + st], lane);
-        laps.lap(4);
-        ++g;
-        if (++st == NSTAGE) st = 0;
-      }
+      };
+      if (p.w_perm && p.scale_dtype == NKV_BF16 && ng == 1) expand_pairs(std::true_type{});
+      else expand_pairs(std::false_type{});
       if (!ok) break;
       // ---- epilogue of this CTA's part: bias, centre, two bf16 roundings, store to every CTA
       {
