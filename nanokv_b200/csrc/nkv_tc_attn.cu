@@ -660,6 +660,20 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         if (transform)
           cam_frame = cam.matrices +
                       static_cast<size_t>(min((t0 + row) / cam.tokens_per_frame, cam.frames - 1)) * 64;
+        // rotation entries of this thread's 16 pairs, requested before the accumulator wait
+        float2 rot[16];
+        if (ROPE) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            rot[i] = make_float2(1.f, 0.f);
+            if (rotate) {
+              const int pg = pair_sel[wg * 16 + i];   // native pair this pair retains
+              const int coord = pg < band_a ? coord_t : (pg < band_b ? coord_h : coord_w);
+              rot[i] = __ldg(reinterpret_cast<const float2*>(p.rope.cos_sin) +
+                             static_cast<size_t>(coord) * p.rope.table_half + pg);
+            }
+          }
+        }
         laps.lap(6);
         // accumulator complete: the tile's last pair is pair g - 1
         ok = mbar_wait(&bars[PAIR_DONE + ((g - 1) & (NDONE - 1))], ((g - 1) / NDONE) & 1, abort_flag, 330);
@@ -713,16 +727,15 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
           for (int w = 0; w < 4; ++w) {
             const int j = j4 * 8 + w * 2;
-            float x0 = round_to_bf16(v[j] + bias[wg * 32 + j]);
-            float x1 = round_to_bf16(v[j + 1] + bias[wg * 32 + j + 1]);
-            x0 += __uint_as_float(cwords[w] << 16);
-            x1 += __uint_as_float(cwords[w] & 0xFFFF0000u);
+            // the rebuilt pair in packed bf16 arithmetic (as above), then widened for the transforms
+            const uint32_t first = pack_bf16x2(v[j] + bias[wg * 32 + j], v[j + 1] + bias[wg * 32 + j + 1]);
+            const __nv_bfloat162 sum = __hadd2(*reinterpret_cast<const __nv_bfloat162*>(&first),
+                                               *reinterpret_cast<const __nv_bfloat162*>(&cwords[w]));
+            const uint32_t rebuilt = *reinterpret_cast<const uint32_t*>(&sum);
+            float x0 = __uint_as_float(rebuilt << 16), x1 = __uint_as_float(rebuilt & 0xFFFF0000u);
             if (rotate) {   // the pair (x0, x1) of the rebuilt bf16 key is one complex number
-              const int pg = pair_sel[wg * 16 + (j >> 1)];   // native pair this pair retains
-              const int coord = pg < band_a ? coord_t : (pg < band_b ? coord_h : coord_w);
-              const float2 cs = __ldg(reinterpret_cast<const float2*>(p.rope.cos_sin) +
-                                      static_cast<size_t>(coord) * p.rope.table_half + pg);
-              const float k0 = round_to_bf16(x0), k1 = round_to_bf16(x1);
+              const float2 cs = rot[j >> 1];
+              const float k0 = x0, k1 = x1;
               x0 = fmaf(k0, cs.x, -(k1 * cs.y));
               x1 = fmaf(k0, cs.y, k1 * cs.x);
             }
