@@ -593,8 +593,8 @@ def run_streaming(args) -> dict:
 
 def run_aux(args) -> dict:
     """The HBM-bound helpers around the read, one GPU, c3 shapes: INT8 operator expansion, first
-    moments of a 99,840-token history, rotation of the 4,680 query rows, the P-way merge, and the
-    rolling-window prune.  Each is timed alone with CUDA events (inputs larger than L2 or an L2
+    moments of a 99,840-token history, rotation of the 4,680 query rows, the P-way merge, the finish of the
+    mixed-dimensional read, and the rolling-window prune.  Each is timed alone with CUDA events (inputs larger than L2 or an L2
     flush between iterations) and reported in GB/s of its algorithmic bytes against the measured
     copy bandwidth."""
     from nanokv_b200 import attention, ops
@@ -647,6 +647,17 @@ def run_aux(args) -> dict:
              for _ in range(4)]
     report("lse_merge_4way", timed(lambda: ops.lse_merge(parts)),
            5 * parts[0][0].numel() * 2 + 5 * parts[0][1].numel() * 4)
+    # finish of the mixed-dimensional read: 18 of 24 heads corrected, merged and scattered in one launch
+    fin_heads = torch.arange(18, dtype=torch.int32, device=device)
+    native = torch.randn(shape.queries, 24, shape.head_dim, generator=gen, device=device).to(torch.bfloat16)
+    native_lse = torch.randn(shape.queries, 24, generator=gen, device=device)
+    lifted = native[:, :18].contiguous()
+    low_lse = native_lse[:, :18].contiguous()
+    mean = torch.randn(24, shape.head_dim, generator=gen, device=device)
+    finished = torch.empty_like(native)
+    report("fast_finish", timed(lambda: ops.fast_finish(native, native_lse, lifted, low_lse, fin_heads, finished,
+                                                        value_mean=mean, projected_mean=mean[:18].contiguous())),
+           3 * lifted.numel() * 2 + 2 * low_lse.numel() * 4)
     # rolling-window prune: drop the oldest non-sink segments of the history (device copies only)
     keep = [0] + list(range(3, hk.segments))
     moved = (hk.tokens - hk._starts[3]) * per_token

@@ -421,6 +421,26 @@ size_t nkv_history_moments_workspace_bytes(int tokens, int rank);
 int nkv_history_moments(const nkv_history* hist, float* latent_sum, int32_t* center_counts,
                         void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * Finish of the mixed-dimensional (NanoKV-Fast) read for one head group, one launch:
+ * the value-mean correction, the log-sum-exp merge of the full-width partial with the
+ * lifted low-width partial, and the scatter of the group's heads to their places
+ * (finish wan/modules/codec_native_finish_triton.py:10-46, LingBot fast tree):
+ *     l      = logaddexp(native_lse[n, head], low_lse[n, g]),  origin = l if finite else 0
+ *     low    = (lifted[n, g, :] + value_mean[head, :]) - projected_mean[g, :]
+ *     out[n, head, :] = native[n, head, :] * exp(native_lse - origin) + low * exp(low_lse - origin)
+ * fp32 in this order, one rounding to `dtype`; head = heads[g].
+ * native, out [rows, total_heads, d]; lifted [rows, group_heads, d] in `dtype` (NKV_BF16 /
+ * NKV_F32); native_lse [rows, total_heads], low_lse [rows, group_heads] f32; heads i32
+ * [group_heads]; value_mean f32 [total_heads, d] and projected_mean f32 [group_heads, d]
+ * both NULL to skip the correction; out_lse f32 [rows, total_heads] or NULL.  out may alias
+ * native (each element is read and written by the same thread).  d % 8 == 0.
+ */
+int nkv_fast_finish(const void* native, const float* native_lse, const void* lifted, const float* low_lse,
+                    const int32_t* heads, const float* value_mean, const float* projected_mean,
+                    int64_t rows, int total_heads, int group_heads, int d, int dtype, void* out,
+                    float* out_lse, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -93,6 +93,8 @@ SIGNATURES = {
                               c_void_p, c_void_p, c_void_p]),
     "nkv_history_moments_workspace_bytes": (c_size_t, [c_int, c_int]),
     "nkv_history_moments": (c_int, [POINTER(History), c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "nkv_fast_finish": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "nkv_operator_unpack_int8": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "nkv_peer_alloc": (c_int, [c_int64, POINTER(c_void_p), c_char_p]),
     "nkv_peer_open": (c_int, [c_char_p, POINTER(c_void_p)]),

@@ -271,6 +271,7 @@ def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segment
                                      scale=scale)
         native_out, native_lse = ops.lse_merge([(native_out, native_lse), (out, lse)])
     result = torch.empty_like(q_native)
+    running_lse = torch.empty_like(native_lse)
     moments = value_mean = None
     if value_mean_residual and low_segments:
         moments = history_moments(low_segments)
@@ -287,9 +288,7 @@ def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segment
             if group.cam_index_k is None:
                 raise ValueError("the camera transform needs reader indices that keep whole 8-wide blocks")
             query = ops.camera_rows(query, _camera(camera["q"], group.cam_index_k, Q))
-        out = native_out.index_select(1, head).contiguous()
-        lse = native_lse.index_select(1, head).contiguous()
-        correction = None
+        mean_rows = projected = None
         if value_mean is not None and group.width < reader.native_dim:
             # mean over the low tokens of the group's low-width V read, by linearity
             total = sum(n for _, _, n in moments)
@@ -301,7 +300,8 @@ def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segment
                              + (counts @ table).view(head.numel(), group.padded))
             mean_low = (mean_low / total)[:, :group.width]
             projected = torch.einsum("he,hed->hd", mean_low, group.lift.float())
-            correction = (value_mean.index_select(0, head) - projected)[None]
+            mean_rows = value_mean
+        partials = []
         for segment in low_segments:
             view_k = group.projected_centers(segment["k"], "k")
             view_v = group.projected_centers(segment["v"], "v")
@@ -319,10 +319,18 @@ def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segment
                 camera_k=cam_k, camera_v=cam_v, prepared=prepared)
             if camera is not None:
                 oo = ops.camera_rows(oo, _camera(camera["out"], group.cam_index_v, Q))
+            partials.append((oo, ll))
+        if value_mean is not None and len(partials) > 1:
+            # LingBot's form attends the joined low history once: one low partial per group
+            partials = [ops.lse_merge(partials)]
+        # value-mean correction, log-sum-exp merge and head scatter in one launch per partial;
+        # the running (O, lse) of the group's heads lives in ``result`` / ``running_lse``
+        source, source_lse = native_out, native_lse
+        for oo, ll in partials:
             lifted = torch.einsum("nhe,hed->nhd", oo[..., :group.width], group.lift).contiguous()
-            if correction is not None:   # fp32 blend, one rounding, as the reference merges it
-                out, lse = ops.lse_merge([(out.float(), lse), (lifted.float() + correction, ll)])
-            else:
-                out, lse = ops.lse_merge([(out, lse), (lifted, ll)])
-        result.index_copy_(1, head, out.to(result.dtype))
+            ops.fast_finish(source, source_lse, lifted, ll, head, result, value_mean=mean_rows,
+                            projected_mean=projected, out_lse=running_lse)
+            source, source_lse = result, running_lse
+        if not partials:
+            result.index_copy_(1, head, native_out.index_select(1, head))
     return result

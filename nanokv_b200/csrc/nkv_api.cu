@@ -445,6 +445,16 @@ int nkv_operator_unpack_int8(const int8_t* qweight, const void* scale_bf16, int6
                      static_cast<cudaStream_t>(stream));
 }
 
+int nkv_fast_finish(const void* native, const float* native_lse, const void* lifted, const float* low_lse,
+                    const int32_t* heads, const float* value_mean, const float* projected_mean,
+                    int64_t rows, int total_heads, int group_heads, int d, int dtype, void* out,
+                    float* out_lse, void* stream) {
+  NKV_REQUIRE(native && native_lse && lifted && low_lse && heads && out && rows >= 0, NKV_ERR_INVALID,
+              "fast_finish: null argument or rows=%lld", static_cast<long long>(rows));
+  return fast_finish(native, native_lse, lifted, low_lse, heads, value_mean, projected_mean, rows,
+                     total_heads, group_heads, d, dtype, out, out_lse, static_cast<cudaStream_t>(stream));
+}
+
 size_t nkv_history_moments_workspace_bytes(int tokens, int rank) {
   return history_moments_workspace_bytes(tokens, rank);
 }

@@ -285,6 +285,77 @@ void launch_merge(const PeerMergeArgs& args, int parts, int dests, long long row
     cp_merge_peer_kernel<DTYPE, MAX_PARTS><<<blocks, 256, 0, stream>>>(args, parts, dests, row_begin, row_end, d);
 }
 
+// ---- finish of the mixed-dimensional read ------------------------------------------------------
+// For query row n and group head g (real head = heads[g]):
+//     l      = logaddexp(native_lse, low_lse),  origin = l where finite else 0
+//     low    = (lifted + mean[head]) - projected[g]          (only with the value-mean residual)
+//     out[n, head, :] = native * exp(native_lse - origin) + low * exp(low_lse - origin)
+// in fp32 in exactly this order with one rounding to the output type, scattered to the head's
+// place.  thread = (row, group head, 8 columns); every operand is read once, the result written once.
+template <int DTYPE>
+__device__ __forceinline__ void load8(const void* base, size_t elem, float (&v)[8]) {
+  if (DTYPE == NKV_F32) {
+    const float4 a = *reinterpret_cast<const float4*>(static_cast<const char*>(base) + elem * 4);
+    const float4 b = *reinterpret_cast<const float4*>(static_cast<const char*>(base) + elem * 4 + 16);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    const uint4 raw = *reinterpret_cast<const uint4*>(static_cast<const char*>(base) + elem * 2);
+    const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      v[2 * k] = __uint_as_float(words[k] << 16);
+      v[2 * k + 1] = __uint_as_float(words[k] & 0xFFFF0000u);
+    }
+  }
+}
+
+template <int DTYPE, bool CORRECT>
+__global__ void __launch_bounds__(256)
+fast_finish_kernel(const void* native, const float* native_lse, const void* lifted, const float* low_lse,
+                   const int32_t* heads, const float* mean, const float* projected, long long rows,
+                   int total_heads, int group_heads, int d, void* out, float* out_lse) {
+  const int per_row = d >> 3;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= rows * group_heads * per_row) return;
+  const int col = static_cast<int>(idx % per_row) * 8;
+  const long long pair = idx / per_row;              // row * group_heads + g
+  const int g = static_cast<int>(pair % group_heads);
+  const long long row = pair / group_heads;
+  const int head = heads[g];
+  const size_t wide = (static_cast<size_t>(row) * total_heads + head);
+  float a[8], b[8];
+  load8<DTYPE>(native, wide * d + col, a);
+  load8<DTYPE>(lifted, static_cast<size_t>(pair) * d + col, b);
+  const float x = native_lse[wide], z = low_lse[pair];
+  const float l = logaddexp(x, z);
+  const float origin = isfinite(l) ? l : 0.f;
+  const float wa = expf(x - origin), wb = expf(z - origin);
+  if (CORRECT) {
+    float m[8], q[8];
+    load8<NKV_F32>(mean, static_cast<size_t>(head) * d + col, m);
+    load8<NKV_F32>(projected, static_cast<size_t>(g) * d + col, q);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) b[c] = __fsub_rn(__fadd_rn(b[c], m[c]), q[c]);
+  }
+  float y[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) y[c] = __fadd_rn(__fmul_rn(a[c], wa), __fmul_rn(b[c], wb));
+  if (DTYPE == NKV_F32) {
+    float4* dst = reinterpret_cast<float4*>(static_cast<char*>(out) + (wide * d + col) * 4);
+    dst[0] = make_float4(y[0], y[1], y[2], y[3]);
+    dst[1] = make_float4(y[4], y[5], y[6], y[7]);
+  } else {
+    uint32_t packed[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      packed[k] = static_cast<uint32_t>(float_to_bf16_bits(y[2 * k])) |
+                  (static_cast<uint32_t>(float_to_bf16_bits(y[2 * k + 1])) << 16);
+    *reinterpret_cast<uint4*>(static_cast<char*>(out) + (wide * d + col) * 2) =
+        make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  }
+  if (out_lse != nullptr && col == 0) out_lse[wide] = l;
+}
+
 // ---- INT8 operator storage -> resident bf16 --------------------------------------------------
 // out[r][c] = bf16(q[r][c]) * scale[r][c / group] as one bf16 product (|q| <= 127 is exact in
 // bf16, so the fp32 product of the two is exact and is rounded once).  Thread = 16 columns.
@@ -466,6 +537,33 @@ int unpack_int8(const int8_t* q, const void* scale_bf16, int64_t rows, int cols,
   unpack_int8_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
       q, static_cast<const uint16_t*>(scale_bf16), rows, cols, group, static_cast<uint16_t*>(out_bf16));
   NKV_LAUNCH_CHECK("unpack_int8_kernel");
+  return NKV_OK;
+}
+
+int fast_finish(const void* native, const float* native_lse, const void* lifted, const float* low_lse,
+                const int32_t* heads, const float* mean, const float* projected, int64_t rows,
+                int total_heads, int group_heads, int d, int dtype, void* out, float* out_lse,
+                cudaStream_t stream) {
+  NKV_REQUIRE(dtype == NKV_BF16 || dtype == NKV_F32, NKV_ERR_UNSUPPORTED, "fast_finish: dtype %d", dtype);
+  NKV_REQUIRE(d > 0 && d % 8 == 0, NKV_ERR_UNSUPPORTED, "fast_finish: width %d (need a multiple of 8)", d);
+  NKV_REQUIRE(group_heads > 0 && group_heads <= total_heads, NKV_ERR_INVALID,
+              "fast_finish: %d group heads of %d", group_heads, total_heads);
+  NKV_REQUIRE((mean == nullptr) == (projected == nullptr), NKV_ERR_INVALID,
+              "fast_finish: the value mean and its projected part come together");
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(native) | reinterpret_cast<uintptr_t>(lifted) |
+                         reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(mean) |
+                         reinterpret_cast<uintptr_t>(projected);
+  NKV_REQUIRE(bits % 16 == 0, NKV_ERR_INVALID, "fast_finish: arrays must be 16-byte aligned");
+  if (rows == 0) return NKV_OK;
+  const long long total = rows * group_heads * (d >> 3);
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+#define NKV_FINISH(DT, CORRECT)                                                                     \
+  fast_finish_kernel<DT, CORRECT><<<blocks, 256, 0, stream>>>(native, native_lse, lifted, low_lse,  \
+      heads, mean, projected, rows, total_heads, group_heads, d, out, out_lse)
+  if (dtype == NKV_F32) { if (mean) NKV_FINISH(NKV_F32, true); else NKV_FINISH(NKV_F32, false); }
+  else                  { if (mean) NKV_FINISH(NKV_BF16, true); else NKV_FINISH(NKV_BF16, false); }
+#undef NKV_FINISH
+  NKV_LAUNCH_CHECK("fast_finish_kernel");
   return NKV_OK;
 }
 

@@ -39,6 +39,10 @@ int quant_pack(const void* coeff, int coeff_dtype, int S, int r, int group, floa
                cudaStream_t stream);
 int lse_merge(const void* const* outs, const float* const* lses, int parts, int64_t rows,
               int d, int dtype, void* out, float* lse_out, cudaStream_t stream);
+int fast_finish(const void* native, const float* native_lse, const void* lifted, const float* low_lse,
+                const int32_t* heads, const float* mean, const float* projected, int64_t rows,
+                int total_heads, int group_heads, int d, int dtype, void* out, float* out_lse,
+                cudaStream_t stream);
 size_t history_moments_workspace_bytes(int tokens, int rank);
 int history_moments(const nkv_history& h, float* latent_sum, int32_t* center_counts, void* workspace,
                     cudaStream_t stream);

@@ -412,6 +412,47 @@ def unpack_int8_weight(qweight: torch.Tensor, scale: torch.Tensor, group_size: i
     return out
 
 
+def fast_finish(native: torch.Tensor, native_lse: torch.Tensor, lifted: torch.Tensor,
+                low_lse: torch.Tensor, heads: torch.Tensor, out: torch.Tensor, *,
+                value_mean: torch.Tensor | None = None, projected_mean: torch.Tensor | None = None,
+                out_lse: torch.Tensor | None = None) -> torch.Tensor:
+    """Finish of the mixed-dimensional read for one head group in one launch: value-mean
+    correction, log-sum-exp merge of the full-width with the lifted low-width partial, scatter to
+    the group's heads (finish, LingBot fast tree wan/modules/codec_native_finish_triton.py:37-46).
+
+    native, out [Q, H, D]; lifted [Q, Hg, D]; native_lse [Q, H]; low_lse [Q, Hg] f32; heads i32 [Hg];
+    value_mean f32 [H, D] with projected_mean f32 [Hg, D], or neither."""
+    device = _require_cuda(native, native_lse, lifted, low_lse, heads, out)
+    Q, H, D = native.shape
+    G = heads.numel()
+    if lifted.shape != (Q, G, D) or out.shape != native.shape or lifted.dtype != native.dtype \
+            or out.dtype != native.dtype:
+        raise ValueError("fast_finish: native/out [Q,H,D] and lifted [Q,Hg,D] of one dtype")
+    if native_lse.shape != (Q, H) or low_lse.shape != (Q, G):
+        raise ValueError("fast_finish: lse shapes do not match")
+    if (value_mean is None) != (projected_mean is None):
+        raise ValueError("fast_finish: the value mean and its projected part come together")
+    for t in (native, lifted, out, native_lse, low_lse):
+        if not t.is_contiguous():
+            raise ValueError("fast_finish: contiguous tensors are required")
+    if native_lse.dtype != torch.float32 or low_lse.dtype != torch.float32:
+        raise ValueError("fast_finish: lse tensors are float32")
+    heads = heads.to(torch.int32).contiguous()
+    if value_mean is not None:
+        if value_mean.shape != (H, D) or projected_mean.shape != (G, D):
+            raise ValueError("fast_finish: value_mean [H,D], projected_mean [Hg,D]")
+        value_mean = value_mean.float().contiguous()
+        projected_mean = projected_mean.float().contiguous()
+    if out_lse is not None and (out_lse.shape != (Q, H) or out_lse.dtype != torch.float32
+                                or not out_lse.is_contiguous()):
+        raise ValueError("fast_finish: out_lse is a contiguous float32 [Q,H]")
+    _lib.check(_lib.library().nkv_fast_finish(
+        _ptr(native), _ptr(native_lse), _ptr(lifted), _ptr(low_lse), _ptr(heads), _ptr(value_mean),
+        _ptr(projected_mean), Q, H, G, D, dtype_code(native.dtype), _ptr(out), _ptr(out_lse),
+        _stream(device)))
+    return out
+
+
 class PeerBuffer:
     """A device buffer other processes of the box can map (nkv_peer_alloc / nkv_peer_open).
 

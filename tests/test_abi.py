@@ -67,7 +67,8 @@ def test_host_layer_exposes_a_wrapper_for_every_entry_point():
     expected = {
         ops: ["assign", "kmeans", "project", "quant_pack", "decode_rows", "attn_codec", "attention_lse",
               "lse_merge", "rope_rows", "RopeView", "HistoryView", "unpack_int8_weight", "PeerBuffer",
-              "cp_merge_peer", "force_simt", "default_splits"],
+              "cp_merge_peer", "force_simt", "default_splits", "fast_finish", "history_moments",
+              "camera_rows", "prepare_decoder"],
         attention: ["codec_attention", "merge", "RopeTable", "ReaderGroup", "Reader", "hybrid_attention"],
         codec: ["Operator", "QuantSpec", "encode_append", "decode", "kmeans_init_rows"],
         context_parallel: ["shard_bounds", "gather_partials", "merge_partials", "gather_and_merge",

@@ -305,3 +305,70 @@ def test_hybrid_attention_value_mean_residual(case):
     tol = F32_REL_TOL if dtype == torch.float32 else BF16_REL_TOL
     assert rel_err(got.cpu().permute(1, 0, 2), want) <= tol
     assert rel_err(plain, want) > 2 * tol, "the correction must matter in this case"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("correct", [False, True])
+def test_fast_finish_is_the_reference_blend_bit_for_bit(dtype, correct):
+    """One launch = value-mean correction + LSE merge + head scatter, in the reference's fp32 order
+    (finish, LingBot fast tree wan/modules/codec_native_finish_triton.py:21-35): compared bit for bit
+    with the same expression evaluated by torch in fp32, infinite LSEs included."""
+    gen = torch.Generator().manual_seed(11)
+    Q, H, D = 37, 6, 64
+    heads = torch.tensor([4, 0, 3], dtype=torch.int32)
+    G = heads.numel()
+    native = torch.randn(Q, H, D, generator=gen).to(dtype)
+    lifted = torch.randn(Q, G, D, generator=gen).to(dtype)
+    native_lse = torch.randn(Q, H, generator=gen) * 3
+    low_lse = torch.randn(Q, G, generator=gen) * 3
+    native_lse[0], low_lse[0] = -math.inf, -math.inf            # both partitions empty
+    native_lse[1] = -math.inf                                    # only the low partition
+    low_lse[2] = -math.inf                                       # only the native partition
+    mean = torch.randn(H, D, generator=gen) if correct else None
+    projected = torch.randn(G, D, generator=gen) if correct else None
+
+    dev = torch.device("cuda", 0)
+    pick = heads.long().to(dev)
+    x, z = native_lse.to(dev)[:, pick], low_lse.to(dev)
+    lse = torch.logaddexp(x, z)
+    origin = torch.where(torch.isfinite(lse), lse, torch.zeros_like(lse))
+    low = lifted.to(dev).float()
+    if correct:
+        low = (low + mean.to(dev)[pick][None]) - projected.to(dev)[None]
+    want = (native.to(dev)[:, pick].float() * (x - origin).exp()[..., None]
+            + low * (z - origin).exp()[..., None]).to(dtype).cpu()
+    lse = lse.cpu()
+
+    out = torch.full((Q, H, D), 7.0, dtype=dtype, device=dev)
+    out_lse = torch.full((Q, H), 7.0, device=dev)
+    ops.fast_finish(native.to(dev), native_lse.to(dev), lifted.to(dev), low_lse.to(dev), heads.to(dev), out,
+                    value_mean=None if mean is None else mean.to(dev),
+                    projected_mean=None if projected is None else projected.to(dev), out_lse=out_lse)
+    got = out.cpu()
+    assert torch.equal(got[:, heads.long()].view(torch.int16 if dtype == torch.bfloat16 else torch.int32),
+                       want.view(torch.int16 if dtype == torch.bfloat16 else torch.int32))
+    untouched = [h for h in range(H) if h not in heads.tolist()]
+    assert torch.all(got[:, untouched].float() == 7.0) and torch.all(out_lse.cpu()[:, untouched] == 7.0)
+    got_lse = out_lse.cpu()[:, heads.long()]
+    finite = torch.isfinite(lse)
+    assert torch.equal(torch.isfinite(got_lse), finite)
+    assert torch.allclose(got_lse[finite], lse[finite], rtol=0, atol=2e-6)
+
+    # in place: the running output may be the full-width input itself
+    running = native.to(dev).clone()
+    ops.fast_finish(running, native_lse.to(dev), lifted.to(dev), low_lse.to(dev), heads.to(dev), running,
+                    value_mean=None if mean is None else mean.to(dev),
+                    projected_mean=None if projected is None else projected.to(dev))
+    assert torch.equal(running.cpu()[:, heads.long()].float(), want.float())
+
+
+def test_fast_finish_rejects_bad_arguments():
+    dev = torch.device("cuda", 0)
+    native = torch.zeros(4, 2, 16, dtype=torch.bfloat16, device=dev)
+    lse = torch.zeros(4, 2, device=dev)
+    heads = torch.tensor([1], dtype=torch.int32, device=dev)
+    with pytest.raises(ValueError):
+        ops.fast_finish(native, lse, native[:, :1].contiguous().float(), lse[:, :1].contiguous(), heads, native)
+    with pytest.raises(ValueError):
+        ops.fast_finish(native, lse, native[:, :1].contiguous(), lse[:, :1].contiguous(), heads, native,
+                        value_mean=torch.zeros(2, 16, device=dev))
