@@ -243,7 +243,7 @@ def compressed_value_mean(low_segments, moments, *, heads: int, native_dim: int)
 def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segments,
                      low_segments, reader: Reader, *, rope: "RopeTable | None" = None,
                      q_positions: torch.Tensor | None = None, value_mean_residual: bool = False,
-                     camera: dict | None = None):
+                     camera: dict | None = None, query_groups: torch.Tensor | None = None):
     """Mixed-dimensional read (MGC/core.py:278-310).  Positional hooks are the identity unless
     ``rope`` is given: then the reduced query is rotated by ``q_positions`` and every low-width
     key read by its segment's ``"positions"``, with the native pairs the group retains
@@ -257,16 +257,27 @@ def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segment
     reduced query, the low-width keys and values (inside the kernel) and the low-width output are
     transformed block-wise (MGC/mg35.py:318-347).
 
+    Visibility (Matrix-Game's boolean masks, MGC/core.py:55-65, :94-108, :290-291, :303): a native
+    segment may be (K, V, mask) and a low segment may carry ``"mask"``, bool [G, tokens]; query row n
+    sees the keys ``mask[query_groups[n]]`` (G = 1 without ``query_groups``).  Queries of one group
+    share their visible keys, so each group attends the gathered keys (codes, scales and ids of a
+    compressed segment are gathered, not decoded) with the unmasked kernels.
+
     q_pre / q_native [Q,H,D]; native_segments [(K [n,H,D], V [n,H,D])] full
     width (protected history, current chunk); low_segments [{"k": history,
     "v": history, "k_mean": f32 [J], "v_mean": f32 [J]}] read through the
     reader projections.  Returns O [Q,H,D].
     """
+    if any(len(segment) > 2 and segment[2] is not None for segment in native_segments) or \
+            any(segment.get("mask") is not None for segment in low_segments):
+        return _hybrid_visible(q_pre, q_native, native_segments, low_segments, reader, rope=rope,
+                               q_positions=q_positions, value_mean_residual=value_mean_residual,
+                               camera=camera, query_groups=query_groups)
     Q, H, D = q_native.shape
     scale = reader.native_dim ** -0.5
     native_out = torch.zeros_like(q_native)
     native_lse = torch.full((Q, H), -math.inf, device=q_native.device)
-    for key, value in native_segments:
+    for key, value, *_ in native_segments:
         out, lse = ops.attention_lse(q_native.contiguous(), key.contiguous(), value.contiguous(),
                                      scale=scale)
         native_out, native_lse = ops.lse_merge([(native_out, native_lse), (out, lse)])
@@ -305,7 +316,13 @@ def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segment
         for segment in low_segments:
             view_k = group.projected_centers(segment["k"], "k")
             view_v = group.projected_centers(segment["v"], "v")
-            rope_view = (rope.view(segment["positions"], group.pair_index) if rope is not None else None)
+            positions = segment.get("positions")
+            if segment.get("visible") is not None:
+                view_k = ops.gather_view(view_k, segment["visible"])
+                view_v = ops.gather_view(view_v, segment["visible"])
+                if positions is not None:
+                    positions = positions.index_select(0, segment["visible"])
+            rope_view = rope.view(positions, group.pair_index) if rope is not None else None
             cam_k = cam_v = None
             if camera is not None:
                 cam_k = _camera(segment["camera"], group.cam_index_k, view_k.tokens)
@@ -333,4 +350,53 @@ def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segment
             source, source_lse = result, running_lse
         if not partials:
             result.index_copy_(1, head, native_out.index_select(1, head))
+    return result
+
+
+def _hybrid_visible(q_pre, q_native, native_segments, low_segments, reader, *, rope, q_positions,
+                    value_mean_residual, camera, query_groups):
+    """hybrid_attention under boolean visibility: one unmasked read per query group over the keys
+    the group sees (attention_grouped_mask MGC/core.py:94-108, applied to every segment)."""
+    if camera is not None or value_mean_residual:
+        raise ValueError("visibility masks combine with the rotation only: the camera transform and "
+                         "the value-mean residual index tokens by their place in the segment")
+    masks = [segment[2] for segment in native_segments if len(segment) > 2 and segment[2] is not None]
+    masks += [segment["mask"] for segment in low_segments if segment.get("mask") is not None]
+    groups = masks[0].shape[0]
+    if any(mask.dtype != torch.bool or mask.dim() != 2 or mask.shape[0] != groups for mask in masks):
+        raise ValueError("Only boolean visibility masks [groups, tokens] are supported")
+    if query_groups is None and groups != 1:
+        raise ValueError("several visibility rows need query_groups")
+    if query_groups is not None and (query_groups.numel() != q_native.shape[0] or
+                                     int(query_groups.min()) < 0 or int(query_groups.max()) >= groups):
+        raise ValueError("query_groups holds one visibility row index per query")
+    result = torch.empty_like(q_native)
+    for g in range(groups):
+        rows = None
+        if query_groups is not None:
+            rows = torch.nonzero(query_groups == g).flatten()
+            if rows.numel() == 0:
+                continue
+        native = []
+        for key, value, *visible in native_segments:
+            if visible and visible[0] is not None:
+                index = torch.nonzero(visible[0][g]).flatten()
+                if index.numel() == 0:
+                    continue
+                key, value = key.index_select(0, index), value.index_select(0, index)
+            native.append((key, value))
+        low = []
+        for segment in low_segments:
+            entry = {name: item for name, item in segment.items() if name != "mask"}
+            if segment.get("mask") is not None:
+                entry["visible"] = torch.nonzero(segment["mask"][g]).flatten()
+                if entry["visible"].numel() == 0:
+                    continue
+            low.append(entry)
+        pick = (lambda t: t) if rows is None else (lambda t: t.index_select(0, rows).contiguous())
+        part = hybrid_attention(pick(q_pre), pick(q_native), native, low, reader, rope=rope,
+                                q_positions=None if q_positions is None else pick(q_positions))
+        if rows is None:
+            return part
+        result.index_copy_(0, rows, part)
     return result

@@ -138,6 +138,22 @@ class HistoryView:
             self.ids.element_size(), self.centers.shape[0], self.centers.shape[1])
 
 
+def gather_view(view: HistoryView, index: torch.Tensor) -> HistoryView:
+    """The history restricted to the tokens listed in ``index`` (increasing, device i64): codes,
+    scales and ids are gathered, every segment keeps its centre rows and shrinks to its listed
+    tokens (a segment none of whose tokens is listed becomes empty).  This is how a boolean
+    visibility mask over the keys is applied to a compressed history: nothing is decoded."""
+    _require_cuda(view.codes, index)
+    index = index.to(torch.int64)
+    starts = view.seg_start[:view.segments + 1].to(torch.int64)
+    seg_start = torch.searchsorted(index, starts).to(torch.int32)
+    return HistoryView(
+        codes=view.codes.index_select(0, index), scales=view.scales.index_select(0, index),
+        ids=view.ids.index_select(0, index), centers=view.centers, seg_start=seg_start,
+        seg_center_row=view.seg_center_row, tokens=int(index.numel()), segments=view.segments,
+        rank=view.rank, group=view.group)
+
+
 def decode_rows(view: HistoryView, decoder, mean, *, rows=None, dtype=None) -> torch.Tensor:
     """Reconstruct rows (all, or those listed in ``rows``) -> [n, J]."""
     device = _require_cuda(decoder, mean, rows)

@@ -446,8 +446,9 @@ def hybrid_attention(q_pre, q_native, native_segments, low_segments, reader: dic
     Matrix-Game's PRoPE: query, low-width keys and values and the low-width output are transformed
     block-wise after the rotation (MGC/mg35.py:318-347).
 
-    q_* [B,H,Q,D]; native_segments [(K,V)] full-width [B,H,n,D]; low_segments
-    [{"k": (latent, centers, ids, mean), "v": (...)}]; reader {"native_dim",
+    q_* [B,H,Q,D]; native_segments [(K,V) or (K,V,mask)] full-width [B,H,n,D]; low_segments
+    [{"k": (latent, centers, ids, mean), "v": (...), optional "mask"}]; a mask is a boolean
+    visibility [1,1,Q or 1,n] (MGC/core.py:55-65, :290-291, :303); reader {"native_dim",
     "groups": [...]}.  Per group the low-width partitions are merged into the
     native (protected) partition by LSE.  MGC/core.py:278-310.
     """
@@ -456,8 +457,8 @@ def hybrid_attention(q_pre, q_native, native_segments, low_segments, reader: dic
     dtype = q_native.dtype
     native_out = torch.zeros_like(q_native)
     native_lse = torch.full(q_native.shape[:-1], -math.inf)
-    for key, value in native_segments:
-        out, lse = attention_lse(q_native, key, value, scale=scale)
+    for key, value, *visible in native_segments:
+        out, lse = attention_lse(q_native, key, value, visible[0] if visible else None, scale=scale)
         native_out, native_lse = merge(native_out, native_lse, out, lse)
     result = torch.zeros_like(q_native)
     for group in reader["groups"]:
@@ -500,7 +501,7 @@ def hybrid_attention(q_pre, q_native, native_segments, low_segments, reader: dic
             if camera is not None:
                 kk = camera_selected(kk, segment["camera"], group["indices"])
                 vv = camera_selected(vv, segment["camera"], group.get("v_indices", group["indices"]))
-            oo, ll = attention_lse(query, kk, vv, scale=scale)
+            oo, ll = attention_lse(query, kk, vv, segment.get("mask"), scale=scale)
             if camera is not None:
                 oo = camera_selected(oo, camera["out"], group.get("v_indices", group["indices"]))
             lifted = torch.einsum("bhne,hed->bhnd", oo, group["lift"].to(dtype))

@@ -83,6 +83,19 @@ def build_reader(case: FastCase, data: dict) -> dict:
                                  v_decoder=data["v_op"]["decoder"])
 
 
+def build_visibility(case: FastCase):
+    """Matrix-Game style visibility: three query groups, each seeing its own subset of every
+    segment (the first token of a segment is visible to all, so no partition is empty).
+    Returns (query_groups i64 [Q], [bool [3, tokens of segment s]])."""
+    gen = synthetic.generator(case.codec.seed + 2000)
+    queries = case.codec.shape.queries
+    groups = torch.arange(queries) * 3 // queries
+    masks = [torch.rand(3, n, generator=gen) < 0.7 for n in case.codec.segments]
+    for mask in masks:
+        mask[:, 0] = True
+    return groups, masks
+
+
 def build_merge():
     """Two partitions with every -inf combination among the rows."""
     gen = synthetic.generator(99)

@@ -116,8 +116,9 @@ def run_lingbot_case(case: cases.CodecCase, root) -> dict:
     return out
 
 
-def run_fast_case(case: cases.FastCase, root) -> dict:
-    """hybrid_attention of codec_native/core.py over MG payloads."""
+def run_fast_case(case: cases.FastCase, root, masked: bool = False) -> dict:
+    """hybrid_attention of codec_native/core.py over MG payloads; ``masked`` hands every segment
+    a boolean visibility mask [1, 1, Q, tokens] that is constant within a query group."""
     codec = ref_import.load_mg_codec(root)
     core = ref_import.load_mg_core(root)
     os.environ["MG35_KVCODEC_C64_CLUSTERS"] = str(case.codec.shape.centers)
@@ -141,6 +142,12 @@ def run_fast_case(case: cases.FastCase, root) -> dict:
         value = codec.decode_tensor(pv, dtype=dtype, device=device)
         native.append((key.reshape(1, -1, heads, dim).permute(0, 2, 1, 3),
                        value.reshape(1, -1, heads, dim).permute(0, 2, 1, 3), None))
+    if masked:
+        groups, visible = cases.build_visibility(case)
+        full = [mask[groups][None, None] for mask in visible]           # [1, 1, Q, tokens]
+        for segment, mask in zip(low, full[:case.low_segments]):
+            segment["mask"] = mask
+        native = [(key, value, mask) for (key, value, _), mask in zip(native, full[case.low_segments:])]
     reader_payload = cases.build_reader(case, data)
     reader = core.ReaderLayer(reader_payload)
     q = data["q"][None].permute(0, 2, 1, 3).contiguous()
@@ -366,6 +373,7 @@ def main() -> None:
         save(case.name, lambda: run_lingbot_case(case, root))
     for case in cases.FAST_CASES:
         save(case.name, lambda: run_fast_case(case, root))
+    save("fast_masked_bf16", lambda: run_fast_case(cases.FAST_CASES[1], root, masked=True))
     save("merge_edge", lambda: run_merge_case(root))
     save("select_mg_bf16", lambda: run_select_case(cases.MINI_BF16, root))
     save("rope_selected_bf16", lambda: run_rope_selected_case(root))

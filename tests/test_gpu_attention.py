@@ -222,6 +222,59 @@ def test_hybrid_attention_against_reference_fixture(case):
     assert rel_err(got.cpu().permute(1, 0, 2), want) <= tol
 
 
+def test_hybrid_attention_with_visibility_masks_against_reference_fixture():
+    """Boolean visibility per query group on every segment: the compressed segments are gathered
+    (codes, scales, ids), not decoded, and read by the unmasked kernels; against the reference's
+    masked hybrid_attention (MGC/core.py:278-310 with masks, :55-65)."""
+    case = cases.FAST_CASES[1]
+    gold = load("fast_masked_bf16")
+    codec_case, shape = case.codec, case.codec.shape
+    dtype = shape.torch_dtype
+    data, segments = oracle_segments(codec_case)
+    low = case.low_segments
+    ops_k, ops_v = device_operator(data["k_op"]), device_operator(data["v_op"])
+    low_k = history_from_segments(segments["k"][:low], joint=shape.joint, rank=shape.rank)
+    low_v = history_from_segments(segments["v"][:low], joint=shape.joint, rank=shape.rank)
+    groups, visible = cases.build_visibility(case)
+    native = []
+    for sk, sv, mask in zip(segments["k"][low:], segments["v"][low:], visible[low:]):
+        hk = history_from_segments([sk], joint=shape.joint, rank=shape.rank)
+        hv = history_from_segments([sv], joint=shape.joint, rank=shape.rank)
+        native.append((codec.decode(hk, ops_k, dtype=dtype).view(-1, shape.heads, shape.head_dim),
+                       codec.decode(hv, ops_v, dtype=dtype).view(-1, shape.heads, shape.head_dim),
+                       mask.cuda()))
+    reader = attention.Reader(cases.build_reader(case, data), dtype=dtype)
+    q = data["q"].cuda()
+    got = attention.hybrid_attention(
+        q, q, native, [{"k": low_k, "v": low_v, "k_mean": ops_k.mean, "v_mean": ops_v.mean,
+                        "mask": torch.cat(visible[:low], dim=1).cuda()}],
+        reader, query_groups=groups.cuda())
+    want = from_bits(gold["hybrid"], dtype)                  # [H, Q, D]
+    assert rel_err(got.cpu().permute(1, 0, 2), want) <= BF16_REL_TOL
+    # the masks matter: the unmasked read of the same inputs is far from the masked fixture
+    plain = attention.hybrid_attention(
+        q, q, [pair[:2] for pair in native],
+        [{"k": low_k, "v": low_v, "k_mean": ops_k.mean, "v_mean": ops_v.mean}], reader)
+    assert rel_err(plain.cpu().permute(1, 0, 2), want) > 4 * BF16_REL_TOL
+
+
+def test_gather_view_keeps_the_segment_of_every_token():
+    """Gathered tokens decode to the same rows as the same tokens of the whole history, across
+    segment boundaries and with a segment that loses all its tokens."""
+    case = cases.MINI_BF16
+    shape = case.shape
+    data, segments = oracle_segments(case)
+    op = device_operator(data["k_op"])
+    hist = history_from_segments(segments["k"] + segments["k"][:1], joint=shape.joint, rank=shape.rank)
+    whole = codec.decode(hist, op, dtype=torch.bfloat16)
+    first, second = case.segments
+    index = torch.tensor([0, 5, first - 1, first + second, first + second + 7, hist.tokens - 1], device="cuda")
+    view = ops.gather_view(hist.view(), index)                     # the middle segment is empty
+    assert view.tokens == index.numel() and view.seg_start[:4].tolist() == [0, 3, 3, 6]
+    rows = ops.decode_rows(view, op.decoder, op.mean, dtype=torch.bfloat16)
+    assert torch.equal(rows, whole.index_select(0, index))
+
+
 @pytest.mark.parametrize("heads,dim,tokens,queries", [(3, 128, 517, 300), (2, 64, 1, 1), (2, 128, 33000, 40)])
 def test_plain_attention_bf16_runs_on_the_fused_kernel(heads, dim, tokens, queries):
     """bf16 plain attention (the Fast path's protected / current branch) enters the tcgen05 kernel

@@ -93,9 +93,9 @@ def test_lingbot_codec(case):
 
 
 @pytest.mark.parametrize("case", cases.FAST_CASES, ids=lambda c: c.name)
-def test_hybrid_attention(case):
+def test_hybrid_attention(case, masked=False):
     torch.set_num_threads(1)
-    gold = load(case.name)
+    gold = load("fast_masked_bf16" if masked else case.name)
     data = cases.build(case.codec)
     shape = case.codec.shape
     dtype = shape.torch_dtype
@@ -117,11 +117,22 @@ def test_hybrid_attention(case):
                 rows = oracle.decode_rows(seg, decoder=op["decoder"], mean=op["mean"], dtype=dtype)
                 pair.append(rows.reshape(1, -1, shape.heads, shape.head_dim).permute(0, 2, 1, 3))
             native.append(tuple(pair))
+    if masked:
+        groups, visible = cases.build_visibility(case)
+        full = [mask[groups][None, None] for mask in visible]
+        for entry, mask in zip(low, full):
+            entry["mask"] = mask
+        native = [pair + (mask,) for pair, mask in zip(native, full[case.low_segments:])]
     reader = cases.build_reader(case, data)
     q = data["q"][None].permute(0, 2, 1, 3).contiguous()
     result = oracle.hybrid_attention(q, q, native, low, reader)
     want = from_bits(gold["hybrid"], dtype)
     assert torch.equal(result[0], want)
+
+
+def test_hybrid_attention_with_visibility_masks():
+    """Boolean visibility per query group on every segment, against the reference's masked read."""
+    test_hybrid_attention(cases.FAST_CASES[1], masked=True)
 
 
 def test_merge_edge_cases():
