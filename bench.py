@@ -476,7 +476,7 @@ def run_reference(args) -> dict:
 # ------------------------------------------------------------------ secondary workloads
 def run_fast(args) -> dict:
     """c4: NanoKV-Fast mixed-dimensional read, one layer, one GPU.  History 32 frames; the last 2
-    are protected (decoded to full width, native attention); the older 30 are read through reader
+    are protected (rebuilt at full width inside the fused kernel); the older 30 are read through reader
     projections: 18 heads at width 32, 6 heads at full width; partitions merged by LSE."""
     from nanokv_b200 import attention, codec
     shape = synthetic.CONFIGS["c4_fast_mixed"]
@@ -495,8 +495,7 @@ def run_fast(args) -> dict:
     q = synthetic.make_queries(shape, gen).to(device)
 
     def step():
-        native = [(codec.decode(pk, ok).view(-1, shape.heads, shape.head_dim),
-                   codec.decode(pv, ov).view(-1, shape.heads, shape.head_dim))]
+        native = [{"k": pk, "v": pv, "op_k": ok, "op_v": ov}]    # protected rows rebuilt inside the kernel
         low = [{"k": hk, "v": hv, "k_mean": ok.mean, "v_mean": ov.mean}]
         return attention.hybrid_attention(q, q, native, low, reader)
 

@@ -264,23 +264,36 @@ def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segment
     compressed segment are gathered, not decoded) with the unmasked kernels.
 
     q_pre / q_native [Q,H,D]; native_segments [(K [n,H,D], V [n,H,D])] full
-    width (protected history, current chunk); low_segments [{"k": history,
+    width (protected history, current chunk), or {"k", "v": compressed histories, "op_k", "op_v":
+    operators} for protected tokens that stay compressed and are rebuilt at full width inside the
+    fused kernel instead of being decoded to rows first (_decode_active_history
+    LB/lingbot_v2_cache_runtime.py:139-163 followed by the native attention); low_segments [{"k": history,
     "v": history, "k_mean": f32 [J], "v_mean": f32 [J]}] read through the
     reader projections.  Returns O [Q,H,D].
     """
-    if any(len(segment) > 2 and segment[2] is not None for segment in native_segments) or \
+    if any(not isinstance(segment, dict) and len(segment) > 2 and segment[2] is not None
+           for segment in native_segments) or \
             any(segment.get("mask") is not None for segment in low_segments):
         return _hybrid_visible(q_pre, q_native, native_segments, low_segments, reader, rope=rope,
                                q_positions=q_positions, value_mean_residual=value_mean_residual,
                                camera=camera, query_groups=query_groups)
     Q, H, D = q_native.shape
     scale = reader.native_dim ** -0.5
-    native_out = torch.zeros_like(q_native)
-    native_lse = torch.full((Q, H), -math.inf, device=q_native.device)
-    for key, value, *_ in native_segments:
-        out, lse = ops.attention_lse(q_native.contiguous(), key.contiguous(), value.contiguous(),
-                                     scale=scale)
-        native_out, native_lse = ops.lse_merge([(native_out, native_lse), (out, lse)])
+    native_out = native_lse = None
+    for segment in native_segments:
+        if isinstance(segment, dict):      # protected tokens kept compressed: rebuilt inside the kernel
+            out, lse = codec_attention(q_native.contiguous(), segment["k"], segment["v"], segment["op_k"],
+                                       segment["op_v"], scale=scale)
+        else:
+            key, value = segment[0], segment[1]
+            out, lse = ops.attention_lse(q_native.contiguous(), key.contiguous(), value.contiguous(),
+                                         scale=scale)
+        # merging into the empty partition (0, -inf) returns the partial unchanged
+        native_out, native_lse = (out, lse) if native_out is None else \
+            ops.lse_merge([(native_out, native_lse), (out, lse)])
+    if native_out is None:
+        native_out = torch.zeros_like(q_native)
+        native_lse = torch.full((Q, H), -math.inf, device=q_native.device)
     result = torch.empty_like(q_native)
     running_lse = torch.empty_like(native_lse)
     moments = value_mean = None
@@ -360,7 +373,8 @@ def _hybrid_visible(q_pre, q_native, native_segments, low_segments, reader, *, r
     if camera is not None or value_mean_residual:
         raise ValueError("visibility masks combine with the rotation only: the camera transform and "
                          "the value-mean residual index tokens by their place in the segment")
-    masks = [segment[2] for segment in native_segments if len(segment) > 2 and segment[2] is not None]
+    masks = [segment[2] for segment in native_segments
+             if not isinstance(segment, dict) and len(segment) > 2 and segment[2] is not None]
     masks += [segment["mask"] for segment in low_segments if segment.get("mask") is not None]
     groups = masks[0].shape[0]
     if any(mask.dtype != torch.bool or mask.dim() != 2 or mask.shape[0] != groups for mask in masks):
@@ -378,7 +392,11 @@ def _hybrid_visible(q_pre, q_native, native_segments, low_segments, reader, *, r
             if rows.numel() == 0:
                 continue
         native = []
-        for key, value, *visible in native_segments:
+        for segment in native_segments:
+            if isinstance(segment, dict):          # compressed protected tokens carry no mask
+                native.append(segment)
+                continue
+            key, value, *visible = segment
             if visible and visible[0] is not None:
                 index = torch.nonzero(visible[0][g]).flatten()
                 if index.numel() == 0:

@@ -220,6 +220,14 @@ def test_hybrid_attention_against_reference_fixture(case):
     want = from_bits(gold["hybrid"], dtype)                  # [H, Q, D]
     tol = F32_REL_TOL if dtype == torch.float32 else BF16_REL_TOL
     assert rel_err(got.cpu().permute(1, 0, 2), want) <= tol
+    # protected tokens left compressed and rebuilt inside the fused kernel: same result
+    compressed = [{"k": history_from_segments([sk], joint=shape.joint, rank=shape.rank),
+                   "v": history_from_segments([sv], joint=shape.joint, rank=shape.rank),
+                   "op_k": ops_k, "op_v": ops_v}
+                  for sk, sv in zip(segments["k"][low:], segments["v"][low:])]
+    fused = attention.hybrid_attention(
+        q, q, compressed, [{"k": low_k, "v": low_v, "k_mean": ops_k.mean, "v_mean": ops_v.mean}], reader)
+    assert rel_err(fused.cpu().permute(1, 0, 2), want) <= tol
 
 
 def test_hybrid_attention_with_visibility_masks_against_reference_fixture():
