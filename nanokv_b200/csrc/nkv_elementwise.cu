@@ -417,6 +417,40 @@ moments_partial_kernel(nkv_history h, float* partial, int* counts) {
   for (int t = t0 + threadIdx.x; t < t1; t += blockDim.x) atomicAdd(&counts[center_row_of(h, t)], 1);
 }
 
+// Vector form for rank % 8 == 0, group % 8 == 0, rank <= 2048: thread = (token sub-lane, one
+// 4-byte word of a code row = 8 latent columns sharing one scale); a warp reads 128 contiguous
+// bytes of a row.  The sub-lanes' sums are added in sub-lane order, so the result is deterministic.
+__global__ void __launch_bounds__(256)
+moments_partial_vec_kernel(nkv_history h, float* partial, int* counts) {
+  __shared__ float lanes[2048];
+  const int slab = blockIdx.x;
+  const int t0 = slab * MOMENT_SLAB, t1 = min(h.tokens, t0 + MOMENT_SLAB);
+  const int words = h.rank >> 3, groups = h.rank / h.group;
+  const int sublanes = blockDim.x / words;
+  const int word = threadIdx.x % words, sub = threadIdx.x / words;
+  if (sub < sublanes) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const int g = (word * 8) / h.group;
+#pragma unroll 4
+    for (int t = t0 + sub; t < t1; t += sublanes) {
+      const uint32_t packed = reinterpret_cast<const uint32_t*>(h.codes)[static_cast<size_t>(t) * words + word];
+      const float scale = load_float(h.scales, h.scale_dtype, static_cast<size_t>(t) * groups + g);
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        acc[c] += round_to_bf16(static_cast<float>(static_cast<int>((packed >> (4 * c)) & 15u) - 7) * scale);
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) lanes[(sub * words + word) * 8 + c] = acc[c];
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < h.rank; j += blockDim.x) {
+    float sum = 0.f;
+    for (int s = 0; s < sublanes; ++s) sum += lanes[s * h.rank + j];
+    partial[static_cast<size_t>(slab) * h.rank + j] = sum;
+  }
+  for (int t = t0 + threadIdx.x; t < t1; t += blockDim.x) atomicAdd(&counts[center_row_of(h, t)], 1);
+}
+
 // block = 8 latent columns; 32 thread groups stride over the slabs, then a fixed-order tree
 __global__ void __launch_bounds__(256)
 moments_reduce_kernel(const float* partial, int slabs, int rank, float* latent_sum) {
@@ -580,7 +614,10 @@ int history_moments(const nkv_history& h, float* latent_sum, int32_t* center_cou
     return NKV_OK;
   }
   const int slabs = (h.tokens + MOMENT_SLAB - 1) / MOMENT_SLAB;
-  moments_partial_kernel<<<slabs, 256, 0, stream>>>(h, static_cast<float*>(workspace), center_counts);
+  const bool vec = h.rank % 8 == 0 && h.group % 8 == 0 && h.rank <= 2048 &&
+                   reinterpret_cast<uintptr_t>(h.codes) % 4 == 0;
+  if (vec) moments_partial_vec_kernel<<<slabs, 256, 0, stream>>>(h, static_cast<float*>(workspace), center_counts);
+  else moments_partial_kernel<<<slabs, 256, 0, stream>>>(h, static_cast<float*>(workspace), center_counts);
   NKV_LAUNCH_CHECK("moments_partial_kernel");
   moments_reduce_kernel<<<(h.rank + 7) / 8, 256, 0, stream>>>(static_cast<const float*>(workspace),
                                                                    slabs, h.rank, latent_sum);
