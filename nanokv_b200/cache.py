@@ -123,30 +123,41 @@ class CompressedHistory:
 
     def retain(self, keep: list[int]) -> None:
         """Keep only the listed segments (increasing order), moving their codes, scales, ids and
-        centre rows down in place and rebuilding the segment table.  Device copies only."""
+        centre rows down in place and rebuilding the segment table.  Device copies only: one per
+        array and run of consecutive kept segments."""
         keep = [int(i) for i in keep]
         if keep != sorted(set(keep)) or any(not 0 <= i < self.segments for i in keep):
             raise ValueError("segments to keep must be distinct, increasing and in range")
         starts, rows, token_cursor, row_cursor = [0], [], 0, 0
-        for index in keep:
-            src, count = self._starts[index], self._starts[index + 1] - self._starts[index]
-            if src != token_cursor:   # distinct ranges may overlap when the move is short: stage a copy
+
+        def move(array, dst, src, count):
+            """array[dst:dst+count] = array[src:src+count] with dst < src; staged when they overlap."""
+            source = array[src:src + count]
+            array[dst:dst + count].copy_(source.clone() if dst + count > src else source)
+
+        runs, position = [], 0                     # runs of consecutive kept segments move as one block
+        while position < len(keep):
+            end = position
+            while end + 1 < len(keep) and keep[end + 1] == keep[end] + 1:
+                end += 1
+            runs.append((keep[position], keep[end]))
+            position = end + 1
+        for first, last in runs:
+            src, count = self._starts[first], self._starts[last + 1] - self._starts[first]
+            if src != token_cursor and count:
                 for array in (self.codes, self.scales, self.ids):
-                    array[token_cursor:token_cursor + count].copy_(array[src:src + count].clone())
-            if self.shared_centers:
-                row = 0
-            else:
-                src_row = self._center_rows[index]
-                next_row = (self._center_rows[index + 1] if index + 1 < self.segments
-                            else self._center_used)
-                clusters = next_row - src_row
-                if src_row != row_cursor:
-                    self.centers[row_cursor:row_cursor + clusters].copy_(
-                        self.centers[src_row:src_row + clusters].clone())
-                row, row_cursor = row_cursor, row_cursor + clusters
-            rows.append(row)
+                    move(array, token_cursor, src, count)
+            if not self.shared_centers:
+                src_row = self._center_rows[first]
+                next_row = self._center_rows[last + 1] if last + 1 < self.segments else self._center_used
+                if src_row != row_cursor and next_row > src_row:
+                    move(self.centers, row_cursor, src_row, next_row - src_row)
+            for index in range(first, last + 1):
+                rows.append(0 if self.shared_centers else self._center_rows[index] - src_row + row_cursor)
+                starts.append(token_cursor + self._starts[index + 1] - src)
             token_cursor += count
-            starts.append(token_cursor)
+            if not self.shared_centers:
+                row_cursor += next_row - src_row
         self._starts, self._center_rows = starts, rows
         if not self.shared_centers:
             self._center_used = row_cursor

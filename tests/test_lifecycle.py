@@ -116,7 +116,56 @@ def test_retain_and_token_views():
     assert hist.tokens == 70 + 64 + 52 and hist.segments == 3
     kept = codec.decode(hist, op, dtype=torch.bfloat16)
     assert torch.equal(kept, torch.cat([whole[:70], whole[134:]]))
+    hist.retain([0, 2])                                        # two single-segment runs
+    assert hist.tokens == 70 + 52 and hist.segments == 2
+    assert torch.equal(codec.decode(hist, op, dtype=torch.bfloat16), torch.cat([whole[:70], whole[198:]]))
     with pytest.raises(ValueError):
         hist.retain([1, 0])
     with pytest.raises(ValueError):
         hist.view_tokens(10, 500)
+
+
+def test_retain_bookkeeping_on_random_histories():
+    """Host logic of the in-place prune (tensors on the CPU, arrays filled directly): for random
+    segment sizes and random kept subsets the moved codes, scales, ids, centre rows and both segment
+    tables equal the concatenation of the kept segments."""
+    import random
+    from nanokv_b200.cache import CompressedHistory
+    rng = random.Random(1)
+    for _ in range(60):
+        segments = rng.randint(1, 7)
+        counts = [rng.randint(1, 40) for _ in range(segments)]
+        clusters = [rng.randint(1, 5) for _ in range(segments)]
+        hist = CompressedHistory(joint=8, rank=8, capacity=sum(counts) + 5, max_segments=8,
+                                 centers_per_segment=5, device="cpu")
+        tokens = rows = 0
+        hist._starts, hist._center_rows = [0], []
+        for count, k in zip(counts, clusters):
+            hist.codes[tokens:tokens + count] = torch.randint(0, 255, (count, hist.codes.shape[1])).to(hist.codes.dtype)
+            hist.scales[tokens:tokens + count] = torch.randn(count, hist.scales.shape[1]).to(hist.scales.dtype)
+            hist.ids[tokens:tokens + count] = torch.randint(0, k, (count,)).to(hist.ids.dtype)
+            hist.centers[rows:rows + k] = torch.randn(k, hist.centers.shape[1]).to(hist.centers.dtype)
+            hist._center_rows.append(rows)
+            tokens, rows = tokens + count, rows + k
+            hist._starts.append(tokens)
+        hist._center_used = rows
+        keep = sorted(rng.sample(range(segments), rng.randint(0, segments)))
+
+        def kept(array, bounds):
+            parts = [array[bounds[i]:bounds[i + 1]].clone() for i in keep]
+            return torch.cat(parts) if parts else array[:0].clone()
+        row_bounds = hist._center_rows + [rows]
+        want = {name: kept(getattr(hist, name), hist._starts) for name in ("codes", "scales", "ids")}
+        want_centers = kept(hist.centers, row_bounds)
+        starts, first_rows = [0], [0]
+        for i in keep:
+            starts.append(starts[-1] + counts[i])
+            first_rows.append(first_rows[-1] + clusters[i])
+        hist.retain(keep)
+        assert hist._starts == starts and hist._center_rows == first_rows[:-1]
+        assert hist.tokens == starts[-1] and hist.segments == len(keep)
+        for name, expected in want.items():
+            assert torch.equal(getattr(hist, name)[:starts[-1]], expected), name
+        assert torch.equal(hist.centers[:first_rows[-1]], want_centers)
+        assert hist.seg_start[:len(starts)].tolist() == starts
+        assert hist.seg_center_row[:len(keep)].tolist() == first_rows[:-1]
