@@ -528,6 +528,88 @@ def run_reference(args) -> dict:
     }
 
 
+
+# ------------------------------------------------------------------ GPU comparison arm
+def gpu_reference(shape, entry, q, steps: int = 3, warmup: int = 2) -> dict:
+    """The reference's own GPU arithmetic for one layer with stock torch operators, per stage:
+    nibble unpack x bf16 scale, F.linear with the decoder and the bf16 mean, centre add (K and V
+    rows of history size written to HBM), then scaled-dot-product attention by the library kernel
+    torch picks (MGM/nanokv_codec.py:393-455, MGC/core.py:50-53).  A comparison arm: it calls
+    library kernels and is never part of the product path."""
+    import torch.nn.functional as F
+    (hk, ok), (hv, ov) = entry["k"], entry["v"]
+    H, D = shape.heads, shape.head_dim
+
+    def rebuild(hist, op):
+        n = hist.tokens
+        codes = hist.codes[:n]
+        nibbles = torch.stack((codes & 0x0F, codes >> 4), dim=-1).reshape(n, hist.rank)
+        latent = (nibbles.to(torch.bfloat16) - 7) * hist.scales[:n]
+        rows = F.linear(latent, op.decoder, op.mean.to(torch.bfloat16))
+        ids = hist.ids[:n].long() & 0xFFFF
+        rows += hist.centers.index_select(0, ids)
+        return rows.view(n, H, D)
+
+    def attend(k, v, backend):
+        qq, kk, vv = (t.permute(1, 0, 2)[None] for t in (q, k, v))
+        if backend == "aten_flash":
+            res = torch.ops.aten._scaled_dot_product_flash_attention(qq, kk, vv, 0.0, False, False,
+                                                                     scale=D ** -0.5)
+            return res[0], res[1]
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+        with sdpa_kernel(SDPBackend.CUDNN_ATTENTION):
+            return F.scaled_dot_product_attention(qq, kk, vv, scale=D ** -0.5), None
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            out = fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps, out
+
+    result = {"layer_tokens": hk.tokens}
+    decode_ms, kv = timed(lambda: (rebuild(hk, ok), rebuild(hv, ov)))
+    result["decode_ms"] = decode_ms
+    best = None
+    for backend in ("aten_flash", "cudnn"):
+        try:
+            ms, (out, _) = timed(lambda: attend(kv[0], kv[1], backend))
+        except Exception as exc:   # the backend is not built for this GPU / shape
+            result[backend + "_error"] = str(exc).splitlines()[0][:120]
+            continue
+        result[backend + "_attention_ms"] = ms
+        if best is None or ms < best[0]:
+            best = (ms, backend, out)
+    if best is not None:
+        result.update(attention_ms=best[0], backend=best[1], total_ms=decode_ms + best[0])
+        result["out"] = best[2][0].permute(1, 0, 2)      # [Q, H, D], dropped before printing
+    result["kv_hbm_bytes"] = 2 * hk.tokens * shape.joint * 2
+    return result
+
+
+def run_torch_gpu(args) -> dict:
+    """bench.py --impl torch_gpu: one c3 layer through stock torch operators on one GPU."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return {}
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    shape = SHAPE
+    built = build_layers(shape, range(shape.history // FRAME), 1, device)
+    q = synthetic.make_queries(shape, synthetic.generator(4242)).to(device)
+    ref = gpu_reference(shape, built[0], q, steps=args.steps, warmup=max(args.warmup, 1))
+    ref.pop("out", None)
+    total = ref.get("total_ms")
+    return {"impl": "torch_gpu", "metric": METRIC, "unit": UNIT,
+            "value": (shape.history / (total / 1e3)) if total else None, "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic", "config": {"workload": shape.name, "layers": 1},
+            "gpu_reference": ref}
+
 # ------------------------------------------------------------------ secondary workloads
 def run_fast(args) -> dict:
     """c4: NanoKV-Fast mixed-dimensional read, one layer, one GPU.  History 32 frames; the last 2
@@ -732,7 +814,7 @@ def main() -> None:
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=3)
     parser.add_argument("--warmup", type=int, default=3)
-    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference", "torch_gpu"])
     parser.add_argument("--layers", type=int, default=SHAPE.layers)
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--rope", action="store_true",
@@ -746,6 +828,8 @@ def main() -> None:
     args = parser.parse_args()
     if args.impl == "reference":
         line = run_reference(args)
+    elif args.impl == "torch_gpu":
+        line = run_torch_gpu(args)
     elif args.workload == "c4_fast_mixed":
         line = run_fast(args)
     elif args.workload == "c5_streaming":

@@ -52,3 +52,23 @@ def code_flip_report(got_codes: torch.Tensor, want_codes: torch.Tensor) -> dict:
     return {"total": int(diff.numel()), "flips": int((diff > 0).sum()),
             "max_step": int(diff.max()) if diff.numel() else 0,
             "rows_touched": int((diff > 0).any(-1).sum())}
+
+
+def oracle_segments_of(hist: CompressedHistory, joint: int) -> list[dict]:
+    """Device cache -> the oracle's segment dicts (what ``oracle.encode_rows`` returns, minus the
+    encoder-side extras), so that a history encoded on the GPU can be read by the CPU oracle."""
+    starts = list(hist._starts)
+    segments = []
+    for index in range(hist.segments):
+        a, b = starts[index], starts[index + 1]
+        first = 0 if hist.shared_centers else hist._center_rows[index]
+        table = hist.centers[first:first + hist.centers_per_segment].cpu()
+        codes = hist.codes[a:b].cpu()
+        segments.append({
+            "shape": (1, b - a, joint), "rank": hist.rank,
+            "packed": codes.reshape(-1), "count": (b - a) * hist.rank,
+            "codes": oracle.unpack_int4(codes.reshape(-1), (b - a) * hist.rank, (b - a, hist.rank)),
+            "scale": hist.scales[a:b].cpu(), "centers": table[None],
+            "ids": hist.ids[a:b].cpu().to(torch.int64).bitwise_and(0xFFFF)[None],
+        })
+    return segments
