@@ -76,6 +76,28 @@ typedef struct nkv_history {
   int32_t center_width;          /* row pitch of `centers` in elements */
 } nkv_history;
 
+/*
+ * Which kernels serve bf16 inputs, process-wide: the tcgen05 tensor-core kernels (default) or the
+ * fp32 CUDA-core kernels run with the bf16 path's rounding points.  The second form is the
+ * triage aid for a suspected tensor-core discrepancy (same arithmetic contract, independent
+ * code) and is what the parity tests cross-check the tensor-core kernels against at sizes a CPU
+ * oracle cannot reach; it is far slower.  No counterpart in the reference.
+ */
+#define NKV_PATH_TENSOR_CORES 0
+#define NKV_PATH_CUDA_CORES   1
+int nkv_set_bf16_path(int path);
+
+/*
+ * Self-test of the bounded device-side waits: launches one tiny kernel whose only thread waits
+ * on (kind 0) a shared-memory barrier on which nobody arrives, or (kind 1) a global counter that
+ * nobody advances.  After `budget_cycles` SM cycles (1 .. 2^28) the wait must give up, exactly as
+ * the waits inside the fused read do after their budget of about a second; the wait-site code
+ * (990 / 991) is then stored in *status_word (device int32, cleared by the caller) and the kernel
+ * returns.  Nothing faults or hangs: this exercises the give-up path, not an error of the GPU.
+ * No counterpart in the reference.
+ */
+int nkv_selftest_bounded_wait(int kind, long long budget_cycles, int32_t* status_word, void* stream);
+
 /* ------------------------------------------------------------------ encode */
 
 /*

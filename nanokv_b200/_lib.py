@@ -97,6 +97,8 @@ SIGNATURES = {
                                 c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "nkv_operator_unpack_int8": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "nkv_peer_alloc": (c_int, [c_int64, POINTER(c_void_p), c_char_p]),
+    "nkv_set_bf16_path": (c_int, [c_int]),
+    "nkv_selftest_bounded_wait": (c_int, [c_int, ctypes.c_longlong, c_void_p, c_void_p]),
     "nkv_peer_open": (c_int, [c_char_p, POINTER(c_void_p)]),
     "nkv_peer_close": (c_int, [c_void_p]),
     "nkv_peer_free": (c_int, [c_void_p]),
@@ -120,8 +122,6 @@ def library() -> ctypes.CDLL:
             fn = getattr(lib, name)   # AttributeError if the library lacks a declared symbol
             fn.restype = restype
             fn.argtypes = argtypes
-        lib.nkv_debug_force_simt.restype = None
-        lib.nkv_debug_force_simt.argtypes = [c_int]
         _lib = lib
     return _lib
 

@@ -1,4 +1,5 @@
 // extern "C" surface of libnanokv_b200: argument checks and kernel dispatch.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -10,7 +11,7 @@
 namespace nkv {
 
 static thread_local char g_error[512] = "";
-static int g_force_simt = -1;
+static std::atomic<int> g_bf16_path{NKV_PATH_TENSOR_CORES};
 
 int fail(int status, const char* fmt, ...) {
   va_list args;
@@ -20,13 +21,7 @@ int fail(int status, const char* fmt, ...) {
   return status;
 }
 
-bool simt_forced() {
-  if (g_force_simt < 0) {
-    const char* env = getenv("NKV_FORCE_SIMT");
-    g_force_simt = (env && env[0] == '1') ? 1 : 0;
-  }
-  return g_force_simt == 1;
-}
+bool simt_forced() { return g_bf16_path.load(std::memory_order_relaxed) == NKV_PATH_CUDA_CORES; }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -111,10 +106,15 @@ const char* nkv_last_error(void) { return g_error; }
 
 int nkv_version(void) { return NKV_ABI_VERSION; }
 
-void nkv_debug_force_simt(int on) { g_force_simt = on ? 1 : 0; }
+int nkv_set_bf16_path(int path) {
+  NKV_REQUIRE(path == NKV_PATH_TENSOR_CORES || path == NKV_PATH_CUDA_CORES, NKV_ERR_INVALID,
+              "set_bf16_path: %d", path);
+  g_bf16_path.store(path, std::memory_order_relaxed);
+  return NKV_OK;
+}
 
-void nkv_debug_attn_profile(void* device_buckets) {
-  tc_attn_set_profile(static_cast<long long*>(device_buckets));
+int nkv_selftest_bounded_wait(int kind, long long budget_cycles, int32_t* status_word, void* stream) {
+  return tc_wait_expiry_selftest(kind, budget_cycles, status_word, static_cast<cudaStream_t>(stream));
 }
 
 int nkv_assign(const void* x, int x_dtype, const void* centers, int centers_dtype, int S, int J,

@@ -67,7 +67,7 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
                   const nkv_camera* cam_v = nullptr, bool prepared_weights = false);
 int tc_prepare_decoder(const void* w_bf16, int64_t rows, int rank, void* out_bf16, cudaStream_t stream);
 bool tc_attn_supported(int dk, int dv, int rank);
-void tc_attn_set_profile(long long* device_buckets);
+int tc_wait_expiry_selftest(int kind, long long budget_cycles, int32_t* status_word, cudaStream_t stream);
 bool tc_project_supported(int J, int r);
 bool tc_assign_supported(int J, int C);
 

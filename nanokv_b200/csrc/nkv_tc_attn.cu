@@ -1,35 +1,38 @@
-// Fused codec-attention on tcgen05 tensor cores (bf16 operands, fp32 TMEM
-// accumulators), with the K/V reconstruction shared inside a thread-block cluster.
+// Fused codec-attention on tcgen05 tensor cores (bf16 operands, fp32 TMEM accumulators):
+// ONE persistent, cooperative launch in which some CTAs rebuild K / V tiles from the
+// compressed history and the others attend to them.
 //
-// A CTA owns one head and up to 256 queries (two 128-row query tiles) and walks
-// the compressed history in tiles of 128 tokens.  The CL CTAs of a cluster serve
-// CL consecutive query blocks of the SAME head, so they all need the same K and
-// V tile.  Each of them rebuilds one 64-column part of it (CL = 4: K columns
-// 0-63 / 64-127, V columns 0-63 / 64-127) and stores that part into the shared
-// memory of every CTA of the cluster (distributed shared memory), which divides
-// the decode GEMM, the dequantisation and the decoder-matrix traffic by CL.
-// Per tile and CTA:
-//   1. TMA streams the packed INT4 codes of the tile (of this CTA's tensor) and
-//      64 rows of the head's decoder (or reader) slice, 64 latent columns at a
-//      time, through a ring of NW slots; the compute warps expand the codes to
-//      bf16 latent rows (code * stored scale, one rounding) into tensor memory,
-//      where they are the A operand of the decode MMA,
-//   2. tcgen05.mma rebuilds the [128 tok x 64] part in TMEM; the compute warps
-//      add bias and the token's centre row with the reference's two bf16
-//      roundings and store K (row-major) or V (transposed) into all CL CTAs --
-//      K and V never exist in global memory,
-//   3. S = Q K^T per query tile in TMEM, online softmax in registers (exp2, lazy
-//      rescaling of the O accumulator); P replaces S in TMEM as bf16 pairs,
-//   4. O += P V (P from TMEM, V from shared memory) in TMEM.
-// Warp roles: warps 0-7 compute (dequantise / epilogue / softmax), warp 8 lane 0
-// issues TMA, warp 9 lane 0 issues MMA, warp 10 prefetches per-token metadata
-// (centre row, scales) two tiles ahead.  All hand-offs are mbarriers with
-// bounded waits (see nkv_tc.cuh); peers signal each other with cluster-scope
-// arrivals and multicast commits.  No TMA load uses multicast.
+// The grid is cut into `groups`; a group owns `cons` consumer CTAs and `prod` producer
+// CTAs (one CTA per SM) and walks a list of work units (head, history split, block of
+// query tiles).  Inside a unit
+//   * a producer owns one tensor (K or V) and every (prod/2)-th 128-token tile of it:
+//     TMA brings the tile's packed INT4 codes and the head's decoder (or reader) rows
+//     into shared memory -- the rows stay resident for the whole unit when they fit --
+//     the compute warps expand codes to bf16 latents (code * stored scale, one rounding)
+//     straight into tensor memory, tcgen05.mma (A from TMEM) rebuilds the [128 tok x D]
+//     tile in TMEM, the epilogue adds bias and the token's centre row with the
+//     reference's two bf16 roundings (plus the positional restore) and stores the tile
+//     into a slot of the group's tile ring;
+//   * a consumer owns up to 256 queries (two 128-row query tiles): TMA brings ring slots
+//     into a two-stage K / V buffer, S = Q K^T per query tile in TMEM, online softmax in
+//     registers (exp2, lazy rescaling of the O accumulator), P replaces S in TMEM as bf16
+//     pairs, O += P V with P from TMEM and V (token-major, read as an MN-major operand)
+//     from shared memory.
+// The ring is a few MB of device memory (slots of 128 tokens x D for K and for V, `ring`
+// slots per group) that is rewritten continuously and stays in the 126 MB L2: every K / V
+// tile is rebuilt ONCE per head and read by all of the head's consumers from L2; no K or V
+// array of history size exists anywhere and DRAM sees the compressed history only.
+// Producers and consumers of a group meet through release / acquire counters in global
+// memory (tile published, tile consumed); inside a CTA every hand-off is an mbarrier.
+// Every wait, local or global, is bounded: when its cycle budget runs out the CTA raises
+// its own abort flag and the launch-wide one, every other wait returns at once, all CTAs
+// drain and leave, and the wait-site code lands in the caller's status word.
+// No TMA load uses multicast; there are no clusters.
 //
-// TMEM columns: [0,128) S of query tile 0 (decode accumulator in [0,64));
-// [128,256) S of tile 1; latent staging slots of 32 columns at 64, 96, 192, 224; [256,384) O
-// tile 0; [384,512) O tile 1.
+// TMEM columns, consumer: [0,128) S / P of query tile 0, [128,256) of tile 1, [256,384) O
+// tile 0, [384,512) O tile 1.  Producer: [0,D) the tile accumulator, [256,512) four latent
+// staging slots of 64 columns (a pair of 64-column latent chunks each).
+#include <mutex>
 #include <type_traits>
 
 #include "nkv_internal.h"
@@ -42,35 +45,47 @@ using namespace tc;
 
 constexpr int TOK = 128;          // history tokens per tile
 constexpr int QT = 128;           // queries per query tile
-constexpr int NQ = 2;             // query tiles per CTA
+constexpr int NQ = 2;             // query tiles per consumer CTA
 constexpr int COMPUTE_THREADS = 256;
 constexpr int COMPUTE_WARPS = COMPUTE_THREADS / 32;
 constexpr int THREADS = COMPUTE_THREADS + 96;
-constexpr int CHUNK = 64;         // latent columns per pipeline step
-constexpr int PART = 64;          // K/V columns rebuilt by one CTA
+constexpr int CHUNK = 64;         // latent columns per MMA group
 constexpr int TILE_BYTES = 128 * 128;  // one [128 rows x 64 bf16] swizzled tile
-constexpr int MAX_NW = 4;         // decoder-row ring slots in shared memory; a slot holds the rows of a
-                                  // PAIR of 64-column latent chunks (as many slots as fit, at least 2)
-#ifndef NKV_NSTAGE
-#define NKV_NSTAGE 2              // 3 (third slot in P1's columns) measured 2 % slower on H 40 x D 128, r 640
-#endif
-constexpr int NSTAGE = NKV_NSTAGE;  // latent staging slots in tensor memory (a pair of chunks each);
-                                    // pair i of a tile uses slot i % NSTAGE
+constexpr int CODE_BLOCK = TOK * 64;   // codes of a pair of chunks: [128 tok x 64 bytes], 64-byte swizzle
+constexpr int MAX_NW = 8;         // decoder-row slots (a pair of chunks each) in shared memory
+constexpr int NSTAGE = 4;         // latent staging slots in tensor memory
 constexpr int NDONE = 8;          // "MMAs of pair g are complete" barriers, indexed by g % 8
+constexpr int KVS = 2;            // K / V stages of a consumer
+constexpr int META_BYTES = 3072;  // barriers, flags and per-token metadata at the head of shared memory
+constexpr int MAX_RING = 8;       // ring slots per group
 constexpr float RESCALE_THRESHOLD = 8.0f;
 
 enum Bar {
-  Q_FULL = 0, W_FULL = 1, PAIR_DONE = 5, LAT_FULL = 13,
-  META_FULL = 22, META_FREE = 24, KV_READY = 26, KV_FREE = 27, S_FULL = 28, P_READY = 30,
-  PV_DONE = 32, EPI_LOCAL = 34, CODES_FULL = 35, CODES_FREE = 36, NUM_BARS = 37
+  // consumer
+  Q_FULL = 0, Q_FREE = 1, K_FULL = 2, K_FREE = 4, V_FULL = 6, V_FREE = 8, S_FULL = 10, P_READY = 12,
+  PV_DONE = 14, O_FREE = 16,
+  // producer
+  W_FULL = 18, PAIR_DONE = 26, LAT_FULL = 34, META_FULL = 38, META_FREE = 40, CODES_FULL = 42,
+  CODES_FREE = 43, OUT_DONE = 44, NUM_BARS = 45
 };
 
+// meta block
+constexpr int M_SLOT = NUM_BARS * 8;              // TMEM base address
+constexpr int M_ABORT = M_SLOT + 4;
+constexpr int M_CROW = 512;                       // [2][128] centre row of every token of a tile
+static_assert(M_ABORT + 4 <= M_CROW && M_CROW + 2 * TOK * 4 <= META_BYTES, "meta block layout");
+
+// global flag words
+constexpr int F_ABORT = 0;        // launch-wide abort (wait-site code)
+constexpr int F_SLOTS = 32;       // then [groups][ring][4]: K published, V published, K consumed, V consumed
+
 struct Params {
-  int Q, heads, N, rank, nchunks, ngroups, group;
-  int scale_dtype, nw;
-  int w_perm;            // decoder rows are in kernel order (tc_prepare_decoder)
-  int tiles_per_split;   // grid.z splits the history; split z writes partial (O, lse) number z
+  int Q, heads, N, rank, nchunks, npairs, ngroups, group;
+  int scale_dtype, nw, w_perm;
+  int tiles, tiles_per_split, splits, qchunks;
+  int groups, cons, prod, ring, units;
   float scale_log2;
+  long long wait_budget;
   nkv_history hk, hv;
   const float* bias_k;
   const float* bias_v;
@@ -79,47 +94,95 @@ struct Params {
   int32_t* status;
   nkv_rope rope;     // cos_sin == nullptr: keys are used as rebuilt
   nkv_camera cam_k, cam_v;   // matrices == nullptr: no camera transform of that tensor
-  long long* prof;   // optional: cycle buckets of CTA (0,0), see nkv_debug_attn_profile
+  uint16_t* ring_k;  // [groups * ring * 128][D]
+  uint16_t* ring_v;
+  int32_t* flags;
 };
 
-template <int D>
-struct Layout {
-  static constexpr int CL = D / PART * 2;                // CTAs per cluster: 4 (D 128) or 2 (D 64)
-  static constexpr int DCH = D / 64;                     // 64-column chunks of a head row
-  static constexpr int Q_OFF = 0;                        // [NQ][DCH] tiles
-  static constexpr int K_OFF = Q_OFF + NQ * DCH * TILE_BYTES;   // [DCH] tiles [128 tok x 64]
-  static constexpr int VT_OFF = K_OFF + DCH * TILE_BYTES;       // V: [DCH] tiles [128 tok x 64], like K
-  static constexpr int VT_TILE = D * 128;                       // (2 * VT_TILE == DCH * TILE_BYTES)
-  // codes of the tile: one [128 tok x 64 byte] block per pair of latent chunks, 64-byte swizzle
-  // (rows 64 bytes apart would put a quarter-warp's 16-byte reads on two bank groups)
-  static constexpr int CODES_OFF = VT_OFF + 2 * VT_TILE;
-  static constexpr int CODE_BLOCK = TOK * 64;
-  // centre staging of the epilogue (8 warps x 2 KB) reuses the head of the code buffer: the codes
-  // of a tile are all expanded before its epilogue starts, and the next tile's codes are only
-  // requested (CODES_FREE) after the staging has been read back
-  static constexpr int SCRATCH_OFF = CODES_OFF;
-  __host__ __device__ static int codes_bytes(int rank) {
-    const int bytes = ((rank / CHUNK + 1) / 2) * CODE_BLOCK;
-    return bytes < TILE_BYTES ? TILE_BYTES : bytes;
-  }
-  __host__ __device__ static int ring_off(int rank) { return CODES_OFF + codes_bytes(rank); }
-  static constexpr int CHUNK_BYTES = PART * 128;         // [64 decoder rows x 64 latent cols]
-  static constexpr int SLOT_BYTES = 2 * CHUNK_BYTES;     // a pair of chunks
-  __host__ __device__ static int meta_off(int nw, int rank) { return ring_off(rank) + nw * SLOT_BYTES; }
-  // meta: bars, tmem slot, abort, bias [64] floats, then two metadata buffers of
-  // crow [128] ints and scales [128][ngroups] u16
-  static constexpr int BARS = 0;
-  static constexpr int SLOT = NUM_BARS * 8;
-  static constexpr int ABORT = SLOT + 4;
-  static constexpr int BIAS = ((ABORT + 4 + 15) / 16) * 16;
-  static constexpr int PAIRS = BIAS + PART * 4;          // [PART / 2] native pair of each pair of the part
-  static constexpr int CAMS = PAIRS + (PART / 2) * 4;   // [PART / 8] camera of each block of the part
-  static constexpr int CROW = CAMS + (PART / 8) * 4;
-  static constexpr int SCALES = CROW + 2 * TOK * 4;
-  static size_t bytes(int nw, int ngroups, int rank) {
-    return meta_off(nw, rank) + SCALES + 2 * TOK * ngroups * 2 + 1024;
-  }
+struct Unit { int head, z, qc, tile0, nt; };
+
+__device__ __forceinline__ Unit unit_of(const Params& p, int u) {
+  Unit r;
+  r.z = u % p.splits;
+  const int rest = u / p.splits;
+  r.head = rest % p.heads;
+  r.qc = rest / p.heads;
+  r.tile0 = r.z * p.tiles_per_split;
+  r.nt = min(p.tiles_per_split, p.tiles - r.tile0);
+  return r;
+}
+
+// ---- bounded waits ------------------------------------------------------------------------------
+struct Ctx {
+  volatile int* abort_flag;   // this CTA's (shared memory)
+  int32_t* gabort;            // the launch's (global memory)
+  long long budget;           // SM cycles per wait
 };
+
+__device__ __forceinline__ int ld_relaxed(const int32_t* p) {
+  int v;
+  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_acquire(const int32_t* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release(int32_t* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_add(int32_t* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __noinline__ void raise_abort(const Ctx& c, int code) {
+  atomicCAS(const_cast<int*>(c.abort_flag), 0, code);
+  atomicCAS(c.gabort, 0, code);
+}
+
+// slow path of both waits: true = give up
+__device__ __forceinline__ bool wait_expired(const Ctx& c, long long start, int code) {
+  if (ld_relaxed(c.gabort) != 0) {   // another CTA gave up: leave too
+    atomicCAS(const_cast<int*>(c.abort_flag), 0, 900);
+    return true;
+  }
+  if (clock64() - start > c.budget) {
+    raise_abort(c, code);
+    return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ bool mwait(uint64_t* bar, uint32_t parity, const Ctx& c, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  unsigned spins = 0;
+  while (true) {
+    if (*c.abort_flag) return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 63u) == 0 && wait_expired(c, start, code)) return false;
+  }
+}
+
+// The same for a whole (converged) warp: every lane waits, and the answer is made uniform so that
+// a wait that gives up in some lanes only cannot split the warp in front of a warp-wide barrier.
+__device__ __forceinline__ bool mwait_all(uint64_t* bar, uint32_t parity, const Ctx& c, int code) {
+  return __all_sync(0xffffffffu, mwait(bar, parity, c, code) ? 1 : 0) != 0;
+}
+
+// wait until a global counter (written by other CTAs with release semantics) reaches `target`
+__device__ __forceinline__ bool fwait(const int32_t* flag, int target, const Ctx& c, int code) {
+  if (ld_acquire(flag) >= target) return true;
+  const long long start = clock64();
+  unsigned spins = 0;
+  while (true) {
+    if (*c.abort_flag) return false;
+    if (ld_acquire(flag) >= target) return true;
+    if ((++spins & 31u) == 0 && wait_expired(c, start, code)) return false;
+    __nanosleep(40);
+  }
+}
 
 __device__ __forceinline__ float scale_to_float(uint16_t bits, int dtype) {
   return dtype == NKV_BF16 ? bf16_bits_to_float(bits) : __half2float(__ushort_as_half(bits));
@@ -208,173 +271,119 @@ __device__ __forceinline__ float exp2_approx(float x) {
   return y;
 }
 
-// TMEM column of latent staging slot s (a pair of chunks = 64 columns).  Slots 0 and 1 avoid the
-// columns where P of the previous tile may still be read by its PV MMAs (P0 in [0,64), P1 in
-// [128,192)), so the next tile's first two pairs can be expanded while those MMAs run; slot 2 is
-// P1's place and is first written at pair 2, after a wait for PV_DONE of the second query tile.
-__device__ __forceinline__ uint32_t staging_col(int s) { return s == 0 ? 64 : (s == 1 ? 192 : 128); }
-
-// Lap timer of one thread: adds the cycles since the previous lap to a bucket kept in registers;
-// flush() adds the buckets to global memory once, at the end.
-// The PROF = false specialisation is empty, so the production kernel carries no timers.
-template <bool PROF>
-struct Laps {
-  __device__ __forceinline__ void start(long long*, bool) {}
-  __device__ __forceinline__ void lap(int) {}
-  __device__ __forceinline__ void flush() {}
-};
-
-template <>
-struct Laps<true> {
-  long long* out;
-  unsigned last;
-  unsigned acc[13];
-  __device__ __forceinline__ void start(long long* dst, bool on) {
-    out = on ? dst : nullptr;
-#pragma unroll
-    for (int i = 0; i < 13; ++i) acc[i] = 0;
-    last = static_cast<unsigned>(clock64());
+template <int D>
+struct Layout {
+  static constexpr int DCH = D / 64;                      // 64-column tiles of a head row
+  // consumer
+  static constexpr int Q_OFF = META_BYTES;                // [NQ][DCH] tiles
+  static constexpr int K_OFF = Q_OFF + NQ * DCH * TILE_BYTES;    // [KVS][DCH] tiles [128 tok x 64]
+  static constexpr int V_OFF = K_OFF + KVS * DCH * TILE_BYTES;   // [KVS][DCH] tiles, token-major like K
+  static constexpr int CONSUMER_BYTES = V_OFF + KVS * DCH * TILE_BYTES;
+  // producer: the tile's codes (one block per pair of latent chunks; its head doubles as the centre
+  // staging of the epilogue, 8 warps x 2 KB), the decoder-row slots, the tokens' scales
+  static constexpr int CODES_OFF = META_BYTES;
+  __host__ __device__ static int codes_bytes(int npairs) {
+    const int bytes = npairs * CODE_BLOCK;
+    return bytes < TILE_BYTES ? TILE_BYTES : bytes;
   }
-  __device__ __forceinline__ void lap(int bucket) {
-    if (out) {
-      const unsigned now = static_cast<unsigned>(clock64());
-#pragma unroll
-      for (int i = 0; i < 13; ++i)
-        if (i == bucket) acc[i] += now - last;
-      last = now;
-    }
-  }
-  __device__ __forceinline__ void flush() {
-    if (out) {
-#pragma unroll
-      for (int i = 0; i < 13; ++i) out[i] += acc[i];
-    }
+  static constexpr int SLOT_BYTES = 2 * D * 128;          // a pair of [D rows x 64 latent cols] tiles
+  __host__ __device__ static int ring_off(int npairs) { return CODES_OFF + codes_bytes(npairs); }
+  __host__ __device__ static int scales_off(int npairs, int nw) { return ring_off(npairs) + nw * SLOT_BYTES; }
+  __host__ __device__ static int producer_bytes(int npairs, int nw, int ngroups) {
+    return scales_off(npairs, nw) + 2 * TOK * ngroups * 2;
   }
 };
 
-template <int D, bool ROPE, bool CAM, bool PROF>
-__global__ void __launch_bounds__(THREADS, 1)
-attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
-                  const __grid_constant__ CUtensorMap map_wk,
-                  const __grid_constant__ CUtensorMap map_wv,
-                  const __grid_constant__ CUtensorMap map_ck,
-                  const __grid_constant__ CUtensorMap map_cv, Params p) {
+// ================================================================================ consumer
+template <int D>
+__device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uint32_t tmem_base,
+                                              const CUtensorMap* map_q, const CUtensorMap* map_rk,
+                                              const CUtensorMap* map_rv, const Params& p, const Ctx& ctx,
+                                              int g, int c) {
   using L = Layout<D>;
-  constexpr int CL = L::CL;
-  extern __shared__ uint8_t smem_raw[];
-  // the dynamic shared window starts at the same offset in every CTA of the cluster, so the
-  // aligned base (and every offset from it) names the same location in each peer
-  uint8_t* smem = reinterpret_cast<uint8_t*>(
-      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  const int nw = p.nw;
-  uint8_t* meta = smem + L::meta_off(nw, p.rank);
-  const int ring_off = L::ring_off(p.rank);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(meta + L::BARS);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(meta + L::SLOT);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(meta + L::ABORT);
-  float* bias = reinterpret_cast<float*>(meta + L::BIAS);            // [64] of this CTA's part
-  int* pair_sel = reinterpret_cast<int*>(meta + L::PAIRS);           // [32] (positional restore)
-  int* cam_sel = reinterpret_cast<int*>(meta + L::CAMS);             // [8] (camera transform)
-  int* crow = reinterpret_cast<int*>(meta + L::CROW);                // [2 buf][128]
-  uint16_t* scales = reinterpret_cast<uint16_t*>(meta + L::SCALES);  // [2 buf][128][ngroups]
-
+  constexpr int DCH = L::DCH;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int head = blockIdx.y;
-  const uint32_t rank = cluster_ctarank();
-  const int tensor = static_cast<int>(rank) / (CL / 2);   // 0: this CTA rebuilds K columns, 1: V
-  const int part = static_cast<int>(rank) % (CL / 2);     // which 64-column part of the head row
-  const nkv_history& hist = tensor ? p.hv : p.hk;
-  const int q0 = blockIdx.x * (NQ * QT);
-  const int nq = q0 >= p.Q ? 0 : ((q0 + QT < p.Q) ? 2 : 1);   // 0: decode duty only
-  const int tile0 = blockIdx.z * p.tiles_per_split;       // first history tile of this split
-  const int ntiles = max(0, min((p.N + TOK - 1) / TOK - tile0, p.tiles_per_split));
-  const int nchunks = p.nchunks;
-  const int ng = p.ngroups;
-
-  if (tid == 0) {
-    mbar_init(&bars[Q_FULL], 1);
-    for (int s = 0; s < MAX_NW; ++s) mbar_init(&bars[W_FULL + s], 1);   // TMA: decoder rows of a pair landed
-    for (int s = 0; s < NSTAGE; ++s) mbar_init(&bars[LAT_FULL + s], COMPUTE_WARPS);  // latent pair staged in TMEM
-    for (int s = 0; s < NDONE; ++s) mbar_init(&bars[PAIR_DONE + s], 1);  // the pair's MMAs are complete
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&bars[META_FULL + s], 1);
-      mbar_init(&bars[META_FREE + s], COMPUTE_WARPS);
-      mbar_init(&bars[S_FULL + s], 1);
-      mbar_init(&bars[P_READY + s], QT / 32);
-      mbar_init(&bars[PV_DONE + s], 1);
-    }
-    mbar_init(&bars[KV_READY], 1);                    // local arrival + bytes copied in by the peers
-    mbar_init(&bars[EPI_LOCAL], COMPUTE_WARPS);     // this CTA's part is in its own shared memory
-    mbar_init(&bars[KV_FREE], CL);
-    mbar_init(&bars[CODES_FULL], 1);                  // the tile's codes landed (one bulk copy)
-    mbar_init(&bars[CODES_FREE], COMPUTE_WARPS);    // every thread is done expanding them                    // one arrival per CTA: its reads are done
-    *abort_flag = 0;
-    fence_barrier_init();
-    fence_proxy_async();
-  }
-  for (int i = tid; i < PART; i += THREADS)
-    bias[i] = (tensor ? p.bias_v : p.bias_k)[head * D + part * PART + i];
-  if (CAM) {
-    const nkv_camera& cam = tensor ? p.cam_v : p.cam_k;
-    for (int i = tid; i < PART / 8; i += THREADS)
-      cam_sel[i] = cam.matrices ? (cam.cam_index[head * (D / 8) + part * (PART / 8) + i] & 3) : 0;
-  }
-  if (ROPE) {
-    for (int i = tid; i < PART / 2; i += THREADS) {
-      const int local = part * (PART / 2) + i;
-      pair_sel[i] = p.rope.pair_index ? p.rope.pair_index[head * (D / 2) + local] : local;
-    }
-  }
-  if (warp == 9) tmem_alloc(tmem_slot, 512);
-  tc_fence_before();
-  __syncthreads();
-  cluster_sync_all();            // every CTA's barriers exist before any peer signals them
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const int R = p.ring;
+  int32_t* gflags = p.flags + F_SLOTS + g * R * 4;
+  auto queries_of = [&](const Unit& un, int& q0) {
+    q0 = (un.qc * p.cons + c) * (NQ * QT);
+    return q0 >= p.Q ? 0 : ((q0 + QT < p.Q) ? 2 : 1);
+  };
 
   if (warp == 8) {
-    // ------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------ TMA: queries, ring -> K / V stages
     if (lane == 0) {
-      const CUtensorMap* map_w = tensor ? &map_wv : &map_wk;
-      const CUtensorMap* map_c = tensor ? &map_cv : &map_ck;
-      prefetch_tensormap(map_w);
-      prefetch_tensormap(map_c);
-      if (nq > 0) {
-        prefetch_tensormap(&map_q);
-        mbar_arrive_expect_tx(&bars[Q_FULL], nq * L::DCH * TILE_BYTES);
-        for (int i = 0; i < nq; ++i)
-          for (int c = 0; c < L::DCH; ++c)
-            tma_load_3d(smem + L::Q_OFF + (i * L::DCH + c) * TILE_BYTES, &map_q, c * 64, head,
-                        q0 + i * QT, &bars[Q_FULL]);
-      }
+      prefetch_tensormap(map_q);
+      prefetch_tensormap(map_rk);
+      prefetch_tensormap(map_rv);
       bool ok = true;
-      int slot = 0, use = 0, g = 0;   // g: running pair number over all tiles
-      for (int it = 0; it < ntiles && ok; ++it) {
-        // the tile's codes: rows are contiguous in the history, so one untiled bulk copy; it is
-        // issued as soon as the previous tile's codes are expanded and lands during that tile's
-        // epilogue / exchange / attention
-        if (it > 0) ok = mbar_wait(&bars[CODES_FREE], (it - 1) & 1, abort_flag, 108);
-        if (!ok) break;
-        {
-          const int npairs = (nchunks + 1) / 2;
-          mbar_arrive_expect_tx(&bars[CODES_FULL], npairs * L::CODE_BLOCK);
-          for (int pi = 0; pi < npairs; ++pi)   // bytes past the row or the history read as zero
-            tma_load_2d(smem + L::CODES_OFF + pi * L::CODE_BLOCK, map_c, pi * 64, (tile0 + it) * TOK,
-                        &bars[CODES_FULL]);
-        }
-        for (int c = 0; c < nchunks && ok; c += 2) {
-          const int n = min(2, nchunks - c);     // chunks in this pair
-          // the slot's previous tenant was pair g - nw
-          if (g >= nw)
-            ok = mbar_wait(&bars[PAIR_DONE + ((g - nw) & (NDONE - 1))], ((g - nw) / NDONE) & 1,
-                           abort_flag, 110 + slot);
+      int seq = 0, cseq = 0, ucount = 0;
+      int pend_slot = -1, pend_stage = 0, pend_phase = 0;
+      for (int u = g; u < p.units && ok; u += p.groups) {
+        const Unit un = unit_of(p, u);
+        int q0;
+        const int nq = queries_of(un, q0);
+        if (nq > 0) {
+          if (ucount > 0) ok = mwait(&bars[Q_FREE], (ucount - 1) & 1, ctx, 101);
           if (!ok) break;
-          mbar_arrive_expect_tx(&bars[W_FULL + slot], n * L::CHUNK_BYTES);
-          for (int j = 0; j < n; ++j)
-            tma_load_2d(smem + ring_off + slot * L::SLOT_BYTES + j * L::CHUNK_BYTES, map_w,
-                        (c + j) * CHUNK, head * D + part * PART, &bars[W_FULL + slot]);
-          ++g;
-          if (++slot == nw) { slot = 0; ++use; }
+          mbar_arrive_expect_tx(&bars[Q_FULL], nq * DCH * TILE_BYTES);
+          for (int i = 0; i < nq; ++i)
+            for (int ch = 0; ch < DCH; ++ch)
+              tma_load_3d(smem + L::Q_OFF + (i * DCH + ch) * TILE_BYTES, map_q, ch * 64, un.head,
+                          q0 + i * QT, &bars[Q_FULL]);
+          ++ucount;
+        }
+        for (int t = 0; t < un.nt && ok; ++t, ++seq) {
+          const int slot = seq % R;
+          int32_t* f = gflags + slot * 4;
+          const int stage = cseq % KVS, use = cseq / KVS;
+          const int row = (g * R + slot) * TOK;
+          ok = fwait(f + 0, seq + 1, ctx, 102);
+          if (!ok) break;
+          fence_proxy_async_all();   // the tile was written with ordinary stores, TMA reads it
+          if (nq > 0) {
+            if (use >= 1) ok = mwait(&bars[K_FREE + stage], (use - 1) & 1, ctx, 103);
+            if (!ok) break;
+            mbar_arrive_expect_tx(&bars[K_FULL + stage], DCH * TILE_BYTES);
+            for (int ch = 0; ch < DCH; ++ch)
+              tma_load_2d(smem + L::K_OFF + (stage * DCH + ch) * TILE_BYTES, map_rk, ch * 64, row,
+                          &bars[K_FULL + stage]);
+          }
+          ok = fwait(f + 1, seq + 1, ctx, 104);
+          if (!ok) break;
+          fence_proxy_async_all();
+          if (nq > 0) {
+            if (use >= 1) ok = mwait(&bars[V_FREE + stage], (use - 1) & 1, ctx, 105);
+            if (!ok) break;
+            mbar_arrive_expect_tx(&bars[V_FULL + stage], DCH * TILE_BYTES);
+            for (int ch = 0; ch < DCH; ++ch)
+              tma_load_2d(smem + L::V_OFF + (stage * DCH + ch) * TILE_BYTES, map_rv, ch * 64, row,
+                          &bars[V_FULL + stage]);
+          }
+          // the previous tile has landed in shared memory by now: hand its ring slot back
+          if (pend_slot >= 0) {
+            ok = mwait(&bars[K_FULL + pend_stage], pend_phase, ctx, 106) &&
+                 mwait(&bars[V_FULL + pend_stage], pend_phase, ctx, 107);
+            if (!ok) break;
+            red_release_add(gflags + pend_slot * 4 + 2, 1);
+            red_release_add(gflags + pend_slot * 4 + 3, 1);
+            pend_slot = -1;
+          }
+          if (nq > 0) {
+            pend_slot = slot; pend_stage = stage; pend_phase = use & 1;
+            ++cseq;
+          } else {   // nothing to load for this block of queries: the slot is not needed here
+            red_release_add(f + 2, 1);
+            red_release_add(f + 3, 1);
+          }
+        }
+      }
+      if (ok && pend_slot >= 0) {
+        ok = mwait(&bars[K_FULL + pend_stage], pend_phase, ctx, 106) &&
+             mwait(&bars[V_FULL + pend_stage], pend_phase, ctx, 107);
+        if (ok) {
+          red_release_add(gflags + pend_slot * 4 + 2, 1);
+          red_release_add(gflags + pend_slot * 4 + 3, 1);
         }
       }
       if (!ok) {  // let copies already in flight land before the CTA goes away
@@ -386,405 +395,104 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
   } else if (warp == 9) {
     // -------------------------------------------------------------- MMA issuer
     // the whole warp runs the (uniform) control flow; one elected lane issues
-    {
-      const bool leader = elect_one();
-      const uint32_t idesc_dec = make_idesc_bf16(128, PART);  // [128 tok] x [64 columns]
-      const uint32_t idesc_s = make_idesc_bf16(128, TOK);     // [128 q] x [128 tok]
-      const uint32_t idesc_pv = make_idesc_bf16(128, D) | (1u << 16);   // [128 q] x [D], B (V) MN-major
-      const uint32_t smem_base = smem_u32(smem);
-      const uint16_t all_ctas = static_cast<uint16_t>((1u << CL) - 1);
-      Laps<PROF> laps;
-      laps.start(p.prof + 16, leader && p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0);
-      bool ok = nq > 0 ? mbar_wait(&bars[Q_FULL], 0, abort_flag, 200) : true;
-      int slot = 0, use = 0, g = 0;   // decoder-row ring position; running pair number
-      uint32_t lat_phase = 0;         // bit s: parity of the next completion of LAT_FULL[s]
-      for (int it = 0; it < ntiles && ok; ++it) {
-        int st = 0;
-        for (int c = 0; c < nchunks && ok; c += 2) {
-          const int n = min(2, nchunks - c);
-          ok = mbar_wait(&bars[W_FULL + slot], use & 1, abort_flag, 210 + slot);
-          laps.lap(0);
-          ok = ok && mbar_wait(&bars[LAT_FULL + st], (lat_phase >> st) & 1, abort_flag, 216 + st);
-          lat_phase ^= 1u << st;
-          laps.lap(1);
-          if (!ok) break;
-          tc_fence_after();
-          // descriptors are built once per chunk; a K = 16 step adds 32 bytes (2 in the address
-          // field) to the shared-memory operand and 8 columns to the TMEM operand
-          for (int j = 0; j < n; ++j) {
-            const uint64_t w_desc = make_smem_desc_sw128(smem_base + ring_off + slot * L::SLOT_BYTES +
-                                                         j * L::CHUNK_BYTES);
-            const uint32_t lat = tmem_base + staging_col(st) + j * 32;   // chunk staged in TMEM
-            if (leader) mma_bf16_ts(tmem_base, lat, w_desc, idesc_dec, c + j > 0);
-            if (leader) mma_bf16_ts(tmem_base, lat + 8, w_desc + 2, idesc_dec, true);
-            if (leader) mma_bf16_ts(tmem_base, lat + 16, w_desc + 4, idesc_dec, true);
-            if (leader) mma_bf16_ts(tmem_base, lat + 24, w_desc + 6, idesc_dec, true);
-          }
-          // frees the decoder rows and the staging; on the last pair: accumulator done
-          if (leader) mma_commit(&bars[PAIR_DONE + (g & (NDONE - 1))]);
-          ++g;
-          if (++slot == nw) { slot = 0; ++use; }
-          if (++st == NSTAGE) st = 0;
-          laps.lap(2);
-        }
-        if (!ok) break;
-        // exchange: once this CTA's part is complete locally and every CTA has finished reading
-        // the previous tile, copy the part into each peer (asynchronous shared-to-shared copies
-        // that report to the peer's KV_READY), then wait for the peers' parts to land here
-        ok = mbar_wait(&bars[EPI_LOCAL], it & 1, abort_flag, 218);
-        if (ok && it > 0) ok = mbar_wait_cluster(&bars[KV_FREE], (it - 1) & 1, abort_flag, 219);
-        laps.lap(7);
-        if (!ok) break;
-        {
-          const uint32_t ready = smem_u32(&bars[KV_READY]);
-          for (uint32_t step = 1; step < CL; ++step) {
-            const uint32_t peer = (rank + step) % CL;
-            const uint32_t peer_ready = map_to_cta(ready, peer);
-            // K and V are both stored token-major, one [128 tok x 64 col] tile per part
-            const uint32_t src = smem_base + (tensor == 0 ? L::K_OFF : L::VT_OFF) + part * TILE_BYTES;
-            if (leader) bulk_copy_to_peer(map_to_cta(src, peer), src, TILE_BYTES, peer_ready);
-          }
-          if (leader) mbar_arrive_expect_tx(&bars[KV_READY], (CL - 1) * TILE_BYTES);
-        }
-        ok = mbar_wait_cluster(&bars[KV_READY], it & 1, abort_flag, 220);
-        laps.lap(3);
+    const bool leader = elect_one();
+    const uint32_t idesc_s = make_idesc_bf16(128, TOK);                // [128 q] x [128 tok]
+    const uint32_t idesc_pv = make_idesc_bf16(128, D) | (1u << 16);    // [128 q] x [D], B (V) MN-major
+    const uint32_t smem_base = smem_u32(smem);
+    auto issue_s = [&](int i, int stage) {
+#pragma unroll
+      for (int ch = 0; ch < DCH; ++ch) {
+        const uint64_t a_desc = make_smem_desc_sw128(smem_base + L::Q_OFF + (i * DCH + ch) * TILE_BYTES);
+        const uint64_t b_desc = make_smem_desc_sw128(smem_base + L::K_OFF + (stage * DCH + ch) * TILE_BYTES);
+        if (leader) mma_bf16(tmem_base + i * 128, a_desc, b_desc, idesc_s, ch > 0);
+        if (leader) mma_bf16(tmem_base + i * 128, a_desc + 2, b_desc + 2, idesc_s, true);
+        if (leader) mma_bf16(tmem_base + i * 128, a_desc + 4, b_desc + 4, idesc_s, true);
+        if (leader) mma_bf16(tmem_base + i * 128, a_desc + 6, b_desc + 6, idesc_s, true);
+      }
+      if (leader) mma_commit(&bars[S_FULL + i]);
+    };
+    // P (bf16 pairs) sits in the first 64 columns of the S region it was computed from.  V is the B
+    // operand in MN-major form: [tokens (K) x d (N)] with d contiguous, 64-column tiles 16 KB apart
+    // (leading offset), 8-token groups 1 KB apart (stride offset); a K step of 16 tokens moves the
+    // start by 2 KB (128 in the address field)
+    auto issue_pv = [&](int i, int stage, bool accumulate) {
+      const uint64_t b_desc = make_smem_desc_sw128_mn(smem_base + L::V_OFF + stage * DCH * TILE_BYTES, TILE_BYTES);
+      const uint32_t p_addr = tmem_base + i * 128;
+      const uint32_t o_addr = tmem_base + 256 + i * 128;
+#pragma unroll
+      for (int ks = 0; ks < TOK / 16; ++ks)
+        if (leader) mma_bf16_ts(o_addr, p_addr + 8 * ks, b_desc + 128 * ks, idesc_pv, accumulate || ks > 0);
+      if (leader) mma_commit(&bars[PV_DONE + i]);
+    };
+    bool ok = true;
+    int cseq = 0, ucount = 0;
+    int ctile[NQ] = {0, 0}, cunit[NQ] = {0, 0};   // tiles / units each query tile's chain has done
+    for (int u = g; u < p.units && ok; u += p.groups) {
+      const Unit un = unit_of(p, u);
+      int q0;
+      const int nq = queries_of(un, q0);
+      if (nq == 0) continue;
+      ok = mwait_all(&bars[Q_FULL], ucount & 1, ctx, 200);
+      if (!ok) break;
+      {
+        const int stage = cseq % KVS;
+        ok = mwait_all(&bars[K_FULL + stage], (cseq / KVS) & 1, ctx, 201);
         if (!ok) break;
         tc_fence_after();
-        for (int i = 0; i < nq; ++i) {
-#pragma unroll
-          for (int ch = 0; ch < L::DCH; ++ch) {
-            const uint64_t a_desc = make_smem_desc_sw128(smem_base + L::Q_OFF + (i * L::DCH + ch) * TILE_BYTES);
-            const uint64_t b_desc = make_smem_desc_sw128(smem_base + L::K_OFF + ch * TILE_BYTES);
-            if (leader) mma_bf16(tmem_base + i * 128, a_desc, b_desc, idesc_s, ch > 0);
-            if (leader) mma_bf16(tmem_base + i * 128, a_desc + 2, b_desc + 2, idesc_s, true);
-            if (leader) mma_bf16(tmem_base + i * 128, a_desc + 4, b_desc + 4, idesc_s, true);
-            if (leader) mma_bf16(tmem_base + i * 128, a_desc + 6, b_desc + 6, idesc_s, true);
-          }
-          if (leader) mma_commit(&bars[S_FULL + i]);
-        }
+        for (int i = 0; i < nq; ++i) issue_s(i, stage);
+        if (leader) mma_commit(&bars[K_FREE + stage]);
+      }
+      for (int t = 0; t < un.nt && ok; ++t) {
+        const int cur = cseq + t, stage = cur % KVS, phase = (cur / KVS) & 1;
+        const int nstage = (cur + 1) % KVS;
         for (int i = 0; i < nq && ok; ++i) {
-          laps.lap(4);
-          ok = mbar_wait(&bars[P_READY + i], it & 1, abort_flag, 230 + i);
-          laps.lap(5);
+          const int ci = ctile[i] + t;
+          ok = mwait_all(&bars[P_READY + i], ci & 1, ctx, 210 + i);
+          if (ok && i == 0) ok = mwait_all(&bars[V_FULL + stage], phase, ctx, 212);
+          // the first PV of a unit overwrites O: the previous unit's rows must have been read out
+          if (ok && t == 0 && cunit[i] > 0) ok = mwait_all(&bars[O_FREE + i], (cunit[i] - 1) & 1, ctx, 214 + i);
           if (!ok) break;
           tc_fence_after();
-          // P (bf16 pairs) sits in the first 64 columns of the S region it was computed from
-          // V is the B operand in MN-major form: [tokens (K) x d (N)] with d contiguous, 64-column
-          // tiles 16 KB apart (leading offset), 8-token groups 1 KB apart (stride offset); a K step
-          // of 16 tokens moves the start by 2 KB (128 in the address field)
-          {
-            const uint64_t b_desc = make_smem_desc_sw128_mn(smem_base + L::VT_OFF, TILE_BYTES);
-            const uint32_t p_addr = tmem_base + i * 128;
-            const uint32_t o_addr = tmem_base + 256 + i * 128;
-#pragma unroll
-            for (int ks = 0; ks < TOK / 16; ++ks)
-              if (leader) mma_bf16_ts(o_addr, p_addr + 8 * ks, b_desc + 128 * ks, idesc_pv, it > 0 || ks > 0);
+          issue_pv(i, stage, t > 0);
+          if (i == nq - 1 && leader) mma_commit(&bars[V_FREE + stage]);
+          if (t + 1 < un.nt) {
+            if (i == 0) ok = mwait_all(&bars[K_FULL + nstage], ((cur + 1) / KVS) & 1, ctx, 216);
+            // S of the next tile overwrites P of this one: PV must have finished reading it
+            if (ok) ok = mwait_all(&bars[PV_DONE + i], ci & 1, ctx, 218 + i);
+            if (!ok) break;
+            tc_fence_after();
+            issue_s(i, nstage);
+            if (i == nq - 1 && leader) mma_commit(&bars[K_FREE + nstage]);
           }
-          if (leader) mma_commit(&bars[PV_DONE + i]);
         }
-        if (!ok) break;
-        // tell every CTA of the cluster that this CTA no longer reads the tile's K / V
-        if (nq > 0) {
-          if (leader) mma_commit_multicast(&bars[KV_FREE], all_ctas);
-        } else {
-          const uint32_t local = smem_u32(&bars[KV_FREE]);
-          for (uint32_t peer = 0; peer < CL; ++peer) if (leader) mbar_arrive_cluster(map_to_cta(local, peer));
-        }
-        laps.lap(6);
       }
-      laps.flush();
+      if (!ok) break;
+      if (leader) mma_commit(&bars[Q_FREE]);   // every S MMA of the unit is done: Q may be replaced
+      cseq += un.nt;
+      ++ucount;
+      for (int i = 0; i < nq; ++i) { ctile[i] += un.nt; ++cunit[i]; }
     }
     __syncwarp();
-  } else if (warp == 10) {
-    // ------------------------------------------- per-token metadata, two tiles ahead
-    bool ok = true;
-    for (int it = 0; it < ntiles && ok; ++it) {
-      const int b = it & 1, u = it >> 1;
-      if (u >= 1) ok = mbar_wait(&bars[META_FREE + b], (u - 1) & 1, abort_flag, 240 + b);
-      if (!ok) break;
-      const int t0 = (tile0 + it) * TOK;
-      for (int r = lane; r < TOK; r += 32) {
-        const int t = t0 + r;
-        const bool in = t < p.N;
-        crow[b * TOK + r] = in ? center_row_of(hist, t) : 0;
-        const uint16_t* src = static_cast<const uint16_t*>(hist.scales) + static_cast<size_t>(t) * ng;
-        uint16_t* dst = scales + static_cast<size_t>(b * TOK + r) * ng;
-        for (int gi = 0; gi < ng; ++gi) dst[gi] = in ? src[gi] : 0;
-      }
-      warp_arrive(&bars[META_FULL + b], lane);
-    }
-  } else {
-    // ------------------------------------------------------------ compute warps
-    const int wg = tid >> 7;                    // query tile served; also the 32-column half of the part
-    const int row = tid & 127;                  // TMEM lane == token row == query row
+  } else if (warp < COMPUTE_WARPS) {
+    // ------------------------------------------------------------ softmax: one thread per query row
+    const int wg = tid >> 7;                    // query tile served
+    const int row = tid & 127;                  // TMEM lane == query row
     const uint32_t lane_sel = static_cast<uint32_t>(32 * (warp & 3)) << 16;
-    float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
-    int g = 0;   // running pair number over all tiles
-    Laps<PROF> laps;
-    laps.start(p.prof, p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0);
-    for (int it = 0; it < ntiles && ok; ++it) {
-      const int t0 = (tile0 + it) * TOK;
-      const int valid = min(TOK, p.N - t0);
-      const int mb = it & 1;
-      if (it > 0) {  // every thread has finished reading S of the previous tile (staging reuses it)
-        for (int i = 0; i < nq && ok; ++i)
-          ok = mbar_wait(&bars[P_READY + i], (it - 1) & 1, abort_flag, 300 + i);
-        if (!ok) break;
-      }
-      laps.lap(0);
-      ok = mbar_wait(&bars[META_FULL + mb], (it >> 1) & 1, abort_flag, 310);
-      laps.lap(1);
-      if (!ok) break;
-      // ---- expand this CTA's codes to bf16 latent chunks in tensor memory (A of the decode MMA)
-      ok = mbar_wait(&bars[CODES_FULL], it & 1, abort_flag, 318);
-      laps.lap(3);
-      if (!ok) break;
-      // this thread's 16 bytes of chunk j of pair pi: 16-byte unit 2 j + wg of row `row`, swizzled
-      const uint8_t* codes = smem + L::CODES_OFF + row * 64;
-      const int unit_xor = (row >> 1) & 3;
-      auto code_at = [&](int c) {
-        return *reinterpret_cast<const uint4*>(codes + (c >> 1) * L::CODE_BLOCK +
-                                               ((((c & 1) * 2 + wg) ^ unit_xor) << 4));
-      };
-      const uint16_t* my_scales = scales + static_cast<size_t>(mb * TOK + row) * ng;
-      // codes of the pair after the one being expanded are fetched ahead of the wait for its slot
-      uint4 code_next[2];
-      code_next[0] = code_at(0);
-      code_next[1] = nchunks > 1 ? code_at(1) : make_uint4(0, 0, 0, 0);
-      int st = 0;
-      // The pair loop exists twice: FASTQ is the common deployment (one bf16 scale per token,
-      // decoder rows in kernel order) with every choice made at compile time; the other copy keeps
-      // the run-time choices (grouped or fp16 scales, natural-order rows).  Picking between them
-      // inside the loop instead costs 7 % of the kernel.
-      auto expand_pairs = [&](auto fast_tag) {
-        constexpr bool FASTQ = decltype(fast_tag)::value;
-        for (int c0 = 0; c0 < nchunks && ok; c0 += 2) {
-          const int n = min(2, nchunks - c0);   // chunks in this pair
-          const uint4 code_cur[2] = {code_next[0], code_next[1]};
-          if (c0 + 2 < nchunks) code_next[0] = code_at(c0 + 2);
-          if (c0 + 3 < nchunks) code_next[1] = code_at(c0 + 3);
-          laps.lap(5);
-          // The staging slot's previous tenant in this tile is pair g - NSTAGE.  The first NSTAGE pairs
-          // of a tile follow pairs of the previous tile, all complete (its epilogue waited for the last
-          // one); slot 2 is also where P of the second query tile sat, read by that tile's PV MMAs.
-          if (c0 >= 2 * NSTAGE)
-            ok = mbar_wait(&bars[PAIR_DONE + ((g - NSTAGE) & (NDONE - 1))], ((g - NSTAGE) / NDONE) & 1,
-                           abort_flag, 320 + st);
-          else if (c0 == 4 && it > 0 && nq == 2)
-            ok = mbar_wait(&bars[PV_DONE + 1], (it - 1) & 1, abort_flag, 323);
-          laps.lap(2);
-          if (!ok) break;
-          tc_fence_after();
-  #pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            if (j < n) {
-              const int c = c0 + j;
-              const uint4 code = code_cur[j];
-              const int col0 = c * CHUNK + wg * 32;   // this thread: token `row`, latent columns col0 .. +32
-              const int gi = (FASTQ || ng == 1) ? 0 : (p.group == 32 ? 2 * c + wg : col0 / p.group);
-              const uint16_t sbits = my_scales[gi];
-              const uint32_t words[4] = {code.x, code.y, code.z, code.w};
-              uint32_t packed[16];
-              if (FASTQ || p.scale_dtype == NKV_BF16) {
-                const uint32_t pair = static_cast<uint32_t>(sbits) * 0x00010001u;
-                const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&pair);
-  #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                  const uint4 v = (FASTQ || p.w_perm) ? dequant8_bf16_perm(words[k], scale2)
-                                                       : dequant8_bf16(words[k], scale2);
-                  packed[4 * k] = v.x; packed[4 * k + 1] = v.y; packed[4 * k + 2] = v.z; packed[4 * k + 3] = v.w;
-                }
-              } else {
-                const float sc = scale_to_float(sbits, p.scale_dtype);
-  #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                  const uint4 v = p.w_perm ? dequant8_perm(words[k], sc) : dequant8(words[k], sc);
-                  packed[4 * k] = v.x; packed[4 * k + 1] = v.y; packed[4 * k + 2] = v.z; packed[4 * k + 3] = v.w;
-                }
-              }
-              tmem_st16(tmem_base + lane_sel + staging_col(st) + j * 32 + wg * 16, packed);
-            }
-          }
-          tmem_wait_st();
-          tc_fence_before();
-          warp_arrive(&bars[LAT_FULL + st], lane);
-          laps.lap(4);
-          ++g;
-          if (++st == NSTAGE) st = 0;
-        }
-      };
-      if (p.w_perm && p.scale_dtype == NKV_BF16 && ng == 1) expand_pairs(std::true_type{});
-      else expand_pairs(std::false_type{});
-      if (!ok) break;
-      // ---- epilogue of this CTA's part: bias, centre, two bf16 roundings, store to every CTA
-      {
-        const bool in = row < valid;
-        // Centre rows of this warp's 32 tokens (32 columns = 64 bytes each), gathered
-        // cooperatively: 4 lanes read one row's 16-byte pieces, so a load instruction touches
-        // 8 lines instead of 32; the rows are redistributed through a swizzled staging area.
-        constexpr int PIECES = 4, RPI = 8;
-        const int wrow0 = 32 * (warp & 3);
-        const uint16_t* cbase = static_cast<const uint16_t*>(hist.centers) +
-                                static_cast<size_t>(head) * D + part * PART + wg * 32;
-        uint4 cen[PIECES];
-#pragma unroll
-        for (int i = 0; i < PIECES; ++i) {
-          const int rloc = i * RPI + lane / PIECES, piece = lane % PIECES;
-          const int crow_i = crow[mb * TOK + wrow0 + rloc];
-          cen[i] = __ldg(reinterpret_cast<const uint4*>(
-              cbase + static_cast<size_t>(crow_i) * hist.center_width + piece * 8));
-        }
-        // positional restore (K parts only): this token's frame / row / column
-        const bool rotate = ROPE && tensor == 0 && p.rope.cos_sin != nullptr;
-        int coord_t = 0, coord_h = 0, coord_w = 0;
-        const int band_a = p.rope.table_half - 2 * (p.rope.table_half / 3);
-        const int band_b = band_a + p.rope.table_half / 3;
-        if (rotate) {
-          const int pos = in ? max(__ldg(p.rope.positions + t0 + row), 0) : 0;
-          const int last = p.rope.table_rows - 1;
-          if (p.rope.frame_seqlen == 0) {   // one table row per token: every band reads row `pos`
-            coord_t = coord_h = coord_w = min(pos, last);
-          } else {
-            const int frame = pos / p.rope.frame_seqlen, spatial = pos - frame * p.rope.frame_seqlen;
-            const int prow = spatial / p.rope.width;
-            coord_t = min(frame, last);
-            coord_h = min(prow, last);
-            coord_w = min(spatial - prow * p.rope.width, last);
-          }
-        }
-        // camera transform: this token's frame picks the 4 x 4 matrices
-        const nkv_camera& cam = tensor ? p.cam_v : p.cam_k;
-        const bool transform = CAM && cam.matrices != nullptr;
-        const float* cam_frame = nullptr;
-        if (transform)
-          cam_frame = cam.matrices +
-                      static_cast<size_t>(min((t0 + row) / cam.tokens_per_frame, cam.frames - 1)) * 64;
-        // rotation entries of this thread's 16 pairs, requested before the accumulator wait
-        float2 rot[16];
-        if (ROPE) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            rot[i] = make_float2(1.f, 0.f);
-            if (rotate) {
-              const int pg = pair_sel[wg * 16 + i];   // native pair this pair retains
-              const int coord = pg < band_a ? coord_t : (pg < band_b ? coord_h : coord_w);
-              rot[i] = __ldg(reinterpret_cast<const float2*>(p.rope.cos_sin) +
-                             static_cast<size_t>(coord) * p.rope.table_half + pg);
-            }
-          }
-        }
-        laps.lap(6);
-        // accumulator complete: the tile's last pair is pair g - 1
-        ok = mbar_wait(&bars[PAIR_DONE + ((g - 1) & (NDONE - 1))], ((g - 1) / NDONE) & 1, abort_flag, 330);
-        laps.lap(7);
+    int ci = 0;
+    int u = g;
+    for (; u < p.units && ok; u += p.groups) {
+      const Unit un = unit_of(p, u);
+      int q0;
+      const int nq = queries_of(un, q0);
+      if (wg >= nq) continue;
+      float m_used = -INFINITY, l_run = 0.f;
+      for (int t = 0; t < un.nt && ok; ++t, ++ci) {
+        const int valid = min(TOK, p.N - (un.tile0 + t) * TOK);
+        ok = mwait_all(&bars[S_FULL + wg], ci & 1, ctx, 300 + wg);
         if (!ok) break;
         tc_fence_after();
-        // the accumulator read stays in flight under the centre staging
-        uint32_t acc_raw[32];
-        tmem_ld32_issue(tmem_base + lane_sel + wg * 32, acc_raw);
-        {
-          uint8_t* stage = smem + L::SCRATCH_OFF + warp * (32 * PIECES * 16);
-#pragma unroll
-          for (int i = 0; i < PIECES; ++i) {
-            const int rloc = i * RPI + lane / PIECES, piece = lane % PIECES;
-            *reinterpret_cast<uint4*>(stage + rloc * (PIECES * 16) +
-                                      ((piece ^ (rloc & (PIECES - 1))) << 4)) = cen[i];
-          }
-          __syncwarp();
-#pragma unroll
-          for (int j = 0; j < PIECES; ++j)
-            cen[j] = *reinterpret_cast<const uint4*>(stage + lane * (PIECES * 16) +
-                                                     ((j ^ (lane & (PIECES - 1))) << 4));
-          __syncwarp();
-          // the staging lived in the code buffer: only now may the next tile's codes overwrite it
-          fence_proxy_async();
-          warp_arrive(&bars[CODES_FREE], lane);
-        }
-        tmem_ld32_wait(acc_raw);
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc_raw[i]);
-        uint32_t packed[16];
-#pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          const uint32_t cwords[4] = {cen[j4].x, cen[j4].y, cen[j4].z, cen[j4].w};
-          float block[8];   // the 8-wide block j4 of this thread's columns (camera transform only)
-          if (!ROPE && !CAM) {
-            // plain rebuild in packed bf16 arithmetic: bf16x2(acc + bias) then one bf16x2 add of the
-            // centre word -- the same two roundings (the sum of two bf16 numbers is exact in fp32
-            // unless the smaller one lies below the rounding step of the larger either way)
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-              const int j = j4 * 8 + w * 2;
-              const uint32_t first = pack_bf16x2(v[j] + bias[wg * 32 + j], v[j + 1] + bias[wg * 32 + j + 1]);
-              const __nv_bfloat162 sum = __hadd2(*reinterpret_cast<const __nv_bfloat162*>(&first),
-                                                 *reinterpret_cast<const __nv_bfloat162*>(&cwords[w]));
-              packed[j4 * 4 + w] = in ? *reinterpret_cast<const uint32_t*>(&sum) : 0u;
-            }
-            continue;
-          }
-#pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            const int j = j4 * 8 + w * 2;
-            // the rebuilt pair in packed bf16 arithmetic (as above), then widened for the transforms
-            const uint32_t first = pack_bf16x2(v[j] + bias[wg * 32 + j], v[j + 1] + bias[wg * 32 + j + 1]);
-            const __nv_bfloat162 sum = __hadd2(*reinterpret_cast<const __nv_bfloat162*>(&first),
-                                               *reinterpret_cast<const __nv_bfloat162*>(&cwords[w]));
-            const uint32_t rebuilt = *reinterpret_cast<const uint32_t*>(&sum);
-            float x0 = __uint_as_float(rebuilt << 16), x1 = __uint_as_float(rebuilt & 0xFFFF0000u);
-            if (rotate) {   // the pair (x0, x1) of the rebuilt bf16 key is one complex number
-              const float2 cs = rot[j >> 1];
-              const float k0 = x0, k1 = x1;
-              x0 = fmaf(k0, cs.x, -(k1 * cs.y));
-              x1 = fmaf(k0, cs.y, k1 * cs.x);
-            }
-            if (CAM) {
-              block[2 * w] = x0;
-              block[2 * w + 1] = x1;
-            }
-            packed[j4 * 4 + w] = in ? pack_bf16x2(x0, x1) : 0u;
-          }
-          if (transform) {   // slots (w) of the block are mixed by the token's 4 x 4 camera matrix
-            const float4* m = reinterpret_cast<const float4*>(cam_frame + cam_sel[wg * 4 + j4] * 16);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) block[k] = round_to_bf16(block[k]);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float4 mi = __ldg(m + i);
-              const float m0 = round_to_bf16(mi.x), m1 = round_to_bf16(mi.y);
-              const float m2 = round_to_bf16(mi.z), m3 = round_to_bf16(mi.w);
-              const float y0 = fmaf(m3, block[6], fmaf(m2, block[4], fmaf(m1, block[2], m0 * block[0])));
-              const float y1 = fmaf(m3, block[7], fmaf(m2, block[5], fmaf(m1, block[3], m0 * block[1])));
-              packed[j4 * 4 + i] = in ? pack_bf16x2(y0, y1) : 0u;
-            }
-          }
-        }
-        tc_fence_before();
-        if (it > 0) {  // every CTA has finished reading the previous tile's K / V
-          ok = mbar_wait_cluster(&bars[KV_FREE], (it - 1) & 1, abort_flag, 332);
-          if (!ok) break;
-        }
-        {   // K and V alike: token-major, this thread's 32 columns of its token row
-          uint8_t* tile = smem + (tensor == 0 ? L::K_OFF : L::VT_OFF) + part * TILE_BYTES;
-#pragma unroll
-          for (int j4 = 0; j4 < 4; ++j4)
-            *reinterpret_cast<uint4*>(tile + sw128_offset(row, wg * 32 + j4 * 8)) =
-                make_uint4(packed[j4 * 4], packed[j4 * 4 + 1], packed[j4 * 4 + 2], packed[j4 * 4 + 3]);
-        }
-      }
-      laps.lap(8);
-      warp_arrive(&bars[META_FREE + mb], lane);
-      fence_proxy_async();
-      warp_arrive(&bars[EPI_LOCAL], lane);
-      laps.lap(9);
-      // ---- online softmax of this thread's query row
-      if (wg < nq) {
-        ok = mbar_wait(&bars[S_FULL + wg], it & 1, abort_flag, 340 + wg);
-        laps.lap(10);
-        if (!ok) break;
-        tc_fence_after();
-        // S of this tile was issued after PV of the previous one, so O is up to date here
+        // S of this tile was issued after PV of the previous one completed, so O is up to date here
         const uint32_t s_addr = tmem_base + lane_sel + wg * 128;
         float mx = -INFINITY;
         {
@@ -817,7 +525,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         if (__any_sync(0xffffffffu, need)) {
           const float m_next = fmaxf(m_used, m_new);
           const float alpha = exp2f(m_used - m_next);   // 0 on the first tile (m_used = -inf)
-          if (it > 0) {
+          if (t > 0) {
             const uint32_t o_addr = tmem_base + lane_sel + 256 + wg * 128;
 #pragma unroll 1
             for (int cc = 0; cc < D / 32; ++cc) {
@@ -866,49 +574,543 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         tmem_wait_st();
         l_run += (sum + sum_b) + (sum_c + sum_d);
-        laps.lap(11);
         tc_fence_before();
         warp_arrive(&bars[P_READY + wg], lane);
-        laps.lap(12);
+      }
+      if (!ok) break;
+      // ---- the unit's rows: O / l and the natural-log LSE (partial number z when the history is split)
+      ok = mwait_all(&bars[PV_DONE + wg], (ci - 1) & 1, ctx, 310 + wg);
+      if (!ok) break;
+      tc_fence_after();
+      const int qrow = q0 + wg * QT + row;
+      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      const uint32_t o_addr = tmem_base + lane_sel + 256 + wg * 128;
+      const size_t split_rows = static_cast<size_t>(un.z) * p.Q * p.heads;
+      uint16_t* dst = p.out + (split_rows + static_cast<size_t>(qrow) * p.heads + un.head) * D;
+#pragma unroll 1
+      for (int cc = 0; cc < D / 32; ++cc) {
+        float v[32];
+        tmem_ld32(o_addr + cc * 32, v);
+        if (qrow < p.Q) {
+#pragma unroll
+          for (int j4 = 0; j4 < 4; ++j4) {
+            uint4 w;
+            w.x = pack_bf16x2(v[j4 * 8 + 0] * inv, v[j4 * 8 + 1] * inv);
+            w.y = pack_bf16x2(v[j4 * 8 + 2] * inv, v[j4 * 8 + 3] * inv);
+            w.z = pack_bf16x2(v[j4 * 8 + 4] * inv, v[j4 * 8 + 5] * inv);
+            w.w = pack_bf16x2(v[j4 * 8 + 6] * inv, v[j4 * 8 + 7] * inv);
+            *reinterpret_cast<uint4*>(dst + cc * 32 + j4 * 8) = w;
+          }
+        }
+      }
+      if (qrow < p.Q)
+        p.lse[split_rows + static_cast<size_t>(qrow) * p.heads + un.head] =
+            l_run > 0.f ? (m_used + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+      tc_fence_before();
+      warp_arrive(&bars[O_FREE + wg], lane);
+    }
+    // a launch that gave up must not hand back rows that look like results: the unit it stopped in
+    // and every later one get NaN in their LSE
+    if (!ok) {
+      for (; u < p.units; u += p.groups) {
+        const Unit un = unit_of(p, u);
+        int q0;
+        const int nq = queries_of(un, q0);
+        const int qrow = q0 + wg * QT + row;
+        if (wg < nq && qrow < p.Q)
+          p.lse[static_cast<size_t>(un.z) * p.Q * p.heads + static_cast<size_t>(qrow) * p.heads + un.head] =
+              __int_as_float(0x7fc00000);
       }
     }
-    laps.flush();
-    // ---- write O / l and the natural-log LSE
-    if (ok && wg < nq && ntiles > 0) {
-      ok = mbar_wait(&bars[PV_DONE + wg], (ntiles - 1) & 1, abort_flag, 350 + wg);
-      if (ok) {
-        tc_fence_after();
-        const int qrow = q0 + wg * QT + row;
-        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-        const uint32_t o_addr = tmem_base + lane_sel + 256 + wg * 128;
-        const size_t split_rows = static_cast<size_t>(blockIdx.z) * p.Q * p.heads;
-        uint16_t* dst = p.out + (split_rows + static_cast<size_t>(qrow) * p.heads + head) * D;
-#pragma unroll 1
-        for (int cc = 0; cc < D / 32; ++cc) {
-          float v[32];
-          tmem_ld32(o_addr + cc * 32, v);
-          if (qrow < p.Q) {
+  }
+}
+
+// ================================================================================ producer
+template <int D, bool ROPE, bool CAM>
+__device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uint32_t tmem_base,
+                                              const CUtensorMap* map_w, const CUtensorMap* map_c,
+                                              const Params& p, const Ctx& ctx, int g, int pidx) {
+  using L = Layout<D>;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int R = p.ring, PH = p.prod / 2;
+  const int tensor = pidx / PH;            // 0: this CTA rebuilds K tiles, 1: V tiles
+  const int mine = pidx % PH;              // it takes the tiles with seq % PH == mine
+  const nkv_history& hist = tensor ? p.hv : p.hk;
+  const int nchunks = p.nchunks, npairs = p.npairs, ng = p.ngroups, nw = p.nw;
+  const bool resident = npairs <= nw;      // the head's decoder rows stay in shared memory for a whole unit
+  const int ring_off = L::ring_off(npairs);
+  int32_t* gflags = p.flags + F_SLOTS + g * R * 4;
+  int* crow = reinterpret_cast<int*>(smem + M_CROW);                                        // [2 buf][128]
+  uint16_t* scales = reinterpret_cast<uint16_t*>(smem + L::scales_off(npairs, nw));         // [2 buf][128][ng]
+  uint16_t* ring = tensor ? p.ring_v : p.ring_k;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------ TMA: codes and decoder rows
+    if (lane == 0) {
+      prefetch_tensormap(map_w);
+      prefetch_tensormap(map_c);
+      bool ok = true;
+      int seq = 0, jobs = 0, gp = 0;   // gp: running pair number over all jobs of this CTA
+      for (int u = g; u < p.units && ok; u += p.groups) {
+        const Unit un = unit_of(p, u);
+        bool first = true;
+        for (int t = 0; t < un.nt && ok; ++t, ++seq) {
+          if (seq % PH != mine) continue;
+          // the tile's codes: issued as soon as the previous job's codes are expanded (and its centre
+          // staging, which lives in the same buffer, has been read back)
+          if (jobs > 0) ok = mwait(&bars[CODES_FREE], (jobs - 1) & 1, ctx, 401);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&bars[CODES_FULL], npairs * CODE_BLOCK);
+          for (int pi = 0; pi < npairs; ++pi)   // bytes past the row or the history read as zero
+            tma_load_2d(smem + L::CODES_OFF + pi * CODE_BLOCK, map_c, pi * 64, (un.tile0 + t) * TOK,
+                        &bars[CODES_FULL]);
+          for (int pi = 0; pi < npairs && ok; ++pi) {
+            const int n = min(2, nchunks - 2 * pi);
+            int slot;
+            if (resident) {
+              if (!first) continue;
+              slot = pi;
+              // the slot's last reader was pair pi of this CTA's previous job
+              if (jobs > 0) {
+                const int last = gp - npairs + pi;
+                ok = mwait(&bars[PAIR_DONE + (last & (NDONE - 1))], (last / NDONE) & 1, ctx, 402);
+              }
+            } else {
+              const int load = gp + pi;
+              slot = load % nw;
+              if (load >= nw)
+                ok = mwait(&bars[PAIR_DONE + ((load - nw) & (NDONE - 1))], ((load - nw) / NDONE) & 1, ctx, 403);
+            }
+            if (!ok) break;
+            mbar_arrive_expect_tx(&bars[W_FULL + slot], n * D * 128);
+            for (int j = 0; j < n; ++j)
+              tma_load_2d(smem + ring_off + slot * L::SLOT_BYTES + j * D * 128, map_w, (2 * pi + j) * CHUNK,
+                          un.head * D, &bars[W_FULL + slot]);
+          }
+          gp += npairs;
+          ++jobs;
+          first = false;
+        }
+      }
+      if (!ok) {
+        const long long start = clock64();
+        while (clock64() - start < (1ll << 21)) {}
+      }
+    }
+    __syncwarp();
+  } else if (warp == 9) {
+    // -------------------------------------------------------------- MMA issuer
+    const bool leader = elect_one();
+    const uint32_t idesc_dec = make_idesc_bf16(128, D);   // [128 tok] x [D columns]
+    const uint32_t smem_base = smem_u32(smem);
+    bool ok = true;
+    int seq = 0, gp = 0, wgen = 0;   // wgen: units whose rows this CTA has loaded (resident form)
+    for (int u = g; u < p.units && ok; u += p.groups) {
+      const Unit un = unit_of(p, u);
+      bool first = true;
+      for (int t = 0; t < un.nt && ok; ++t, ++seq) {
+        if (seq % PH != mine) continue;
+        for (int pi = 0; pi < npairs && ok; ++pi, ++gp) {
+          const int n = min(2, nchunks - 2 * pi);
+          int slot;
+          if (resident) {
+            slot = pi;
+            if (first) ok = mwait_all(&bars[W_FULL + slot], wgen & 1, ctx, 410);
+          } else {
+            slot = gp % nw;
+            ok = mwait_all(&bars[W_FULL + slot], (gp / nw) & 1, ctx, 411);
+          }
+          const int st = gp % NSTAGE;
+          ok = ok && mwait_all(&bars[LAT_FULL + st], (gp / NSTAGE) & 1, ctx, 412);
+          if (!ok) break;
+          tc_fence_after();
+          // descriptors are built once per chunk; a K = 16 step adds 32 bytes (2 in the address
+          // field) to the shared-memory operand and 8 columns to the TMEM operand
+          for (int j = 0; j < n; ++j) {
+            const uint64_t w_desc = make_smem_desc_sw128(smem_base + ring_off + slot * L::SLOT_BYTES + j * D * 128);
+            const uint32_t lat = tmem_base + 256 + st * 64 + j * 32;   // chunk staged in TMEM
+            if (leader) mma_bf16_ts(tmem_base, lat, w_desc, idesc_dec, pi + j > 0);
+            if (leader) mma_bf16_ts(tmem_base, lat + 8, w_desc + 2, idesc_dec, true);
+            if (leader) mma_bf16_ts(tmem_base, lat + 16, w_desc + 4, idesc_dec, true);
+            if (leader) mma_bf16_ts(tmem_base, lat + 24, w_desc + 6, idesc_dec, true);
+          }
+          // frees the staging slot (and the decoder rows); on the last pair: accumulator done
+          if (leader) mma_commit(&bars[PAIR_DONE + (gp & (NDONE - 1))]);
+        }
+        if (first && resident) ++wgen;
+        first = false;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 10) {
+    // ------------------------------------------- per-token metadata, up to two jobs ahead
+    bool ok = true;
+    int seq = 0, jobs = 0;
+    for (int u = g; u < p.units && ok; u += p.groups) {
+      const Unit un = unit_of(p, u);
+      for (int t = 0; t < un.nt && ok; ++t, ++seq) {
+        if (seq % PH != mine) continue;
+        const int b = jobs & 1, use = jobs >> 1;
+        if (use >= 1) ok = mwait_all(&bars[META_FREE + b], (use - 1) & 1, ctx, 420 + b);
+        if (!ok) break;
+        const int t0 = (un.tile0 + t) * TOK;
+        for (int r = lane; r < TOK; r += 32) {
+          const int tok = t0 + r;
+          const bool in = tok < p.N;
+          crow[b * TOK + r] = in ? center_row_of(hist, tok) : 0;
+          const uint16_t* src = static_cast<const uint16_t*>(hist.scales) + static_cast<size_t>(tok) * ng;
+          uint16_t* dst = scales + static_cast<size_t>(b * TOK + r) * ng;
+          for (int gi = 0; gi < ng; ++gi) dst[gi] = in ? src[gi] : 0;
+        }
+        warp_arrive(&bars[META_FULL + b], lane);
+        ++jobs;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ compute warps: expand, epilogue
+    const int wg = tid >> 7;                    // which half of the columns (of a chunk / of the tile)
+    const int row = tid & 127;                  // TMEM lane == token row
+    const uint32_t lane_sel = static_cast<uint32_t>(32 * (warp & 3)) << 16;
+    const nkv_camera& cam = tensor ? p.cam_v : p.cam_k;
+    bool ok = true;
+    int seq = 0, jobs = 0, gp = 0;
+    for (int u = g; u < p.units && ok; u += p.groups) {
+      const Unit un = unit_of(p, u);
+      const int head = un.head;
+      for (int t = 0; t < un.nt && ok; ++t, ++seq) {
+        if (seq % PH != mine) continue;
+        const int t0 = (un.tile0 + t) * TOK;
+        const int valid = min(TOK, p.N - t0);
+        const int mb = jobs & 1;
+        ok = mwait_all(&bars[META_FULL + mb], (jobs >> 1) & 1, ctx, 500);
+        ok = ok && mwait_all(&bars[CODES_FULL], jobs & 1, ctx, 501);
+        if (!ok) break;
+        // ---- expand the tile's codes to bf16 latent chunks in tensor memory (A of the decode MMA)
+        // this thread's 16 bytes of chunk j of pair pi: 16-byte unit 2 j + wg of row `row`, swizzled
+        const uint8_t* codes = smem + L::CODES_OFF + row * 64;
+        const int unit_xor = (row >> 1) & 3;
+        auto code_at = [&](int c) {
+          return *reinterpret_cast<const uint4*>(codes + (c >> 1) * CODE_BLOCK +
+                                                 ((((c & 1) * 2 + wg) ^ unit_xor) << 4));
+        };
+        const uint16_t* my_scales = scales + static_cast<size_t>(mb * TOK + row) * ng;
+        // codes of the pair after the one being expanded are fetched ahead of the wait for its slot
+        uint4 code_next[2];
+        code_next[0] = code_at(0);
+        code_next[1] = nchunks > 1 ? code_at(1) : make_uint4(0, 0, 0, 0);
+        // The pair loop exists twice: FASTQ is the common deployment (one bf16 scale per token,
+        // decoder rows in kernel order) with every choice made at compile time; the other copy keeps
+        // the run-time choices (grouped or fp16 scales, natural-order rows).
+        auto expand_pairs = [&](auto fast_tag) {
+          constexpr bool FASTQ = decltype(fast_tag)::value;
+          for (int c0 = 0; c0 < nchunks && ok; c0 += 2, ++gp) {
+            const int n = min(2, nchunks - c0);   // chunks in this pair
+            const uint4 code_cur[2] = {code_next[0], code_next[1]};
+            if (c0 + 2 < nchunks) code_next[0] = code_at(c0 + 2);
+            if (c0 + 3 < nchunks) code_next[1] = code_at(c0 + 3);
+            const int st = gp % NSTAGE;
+            // the staging slot's previous tenant is pair gp - NSTAGE
+            if (gp >= NSTAGE)
+              ok = mwait_all(&bars[PAIR_DONE + ((gp - NSTAGE) & (NDONE - 1))], ((gp - NSTAGE) / NDONE) & 1, ctx, 502);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              if (j < n) {
+                const int c = c0 + j;
+                const uint4 code = code_cur[j];
+                const int col0 = c * CHUNK + wg * 32;   // this thread: token `row`, latent columns col0 .. +32
+                const int gi = (FASTQ || ng == 1) ? 0 : (p.group == 32 ? 2 * c + wg : col0 / p.group);
+                const uint16_t sbits = my_scales[gi];
+                const uint32_t words[4] = {code.x, code.y, code.z, code.w};
+                uint32_t packed[16];
+                if (FASTQ || p.scale_dtype == NKV_BF16) {
+                  const uint32_t pair = static_cast<uint32_t>(sbits) * 0x00010001u;
+                  const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&pair);
+#pragma unroll
+                  for (int k = 0; k < 4; ++k) {
+                    const uint4 v = (FASTQ || p.w_perm) ? dequant8_bf16_perm(words[k], scale2)
+                                                         : dequant8_bf16(words[k], scale2);
+                    packed[4 * k] = v.x; packed[4 * k + 1] = v.y; packed[4 * k + 2] = v.z; packed[4 * k + 3] = v.w;
+                  }
+                } else {
+                  const float sc = scale_to_float(sbits, p.scale_dtype);
+#pragma unroll
+                  for (int k = 0; k < 4; ++k) {
+                    const uint4 v = p.w_perm ? dequant8_perm(words[k], sc) : dequant8(words[k], sc);
+                    packed[4 * k] = v.x; packed[4 * k + 1] = v.y; packed[4 * k + 2] = v.z; packed[4 * k + 3] = v.w;
+                  }
+                }
+                tmem_st16(tmem_base + lane_sel + 256 + st * 64 + j * 32 + wg * 16, packed);
+              }
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            warp_arrive(&bars[LAT_FULL + st], lane);
+          }
+        };
+        if (p.w_perm && p.scale_dtype == NKV_BF16 && ng == 1) expand_pairs(std::true_type{});
+        else expand_pairs(std::false_type{});
+        if (!ok) break;
+        // ---- epilogue: bias, centre, two bf16 roundings, positional restore; D / 2 columns per thread
+        // in rounds of 32
+        const bool in = row < valid;
+        constexpr int ROUNDS = D / 64;
+        uint32_t outp[ROUNDS][16];
+        {
+          // positional restore (K tiles only): this token's frame / row / column
+          const bool rotate = ROPE && tensor == 0 && p.rope.cos_sin != nullptr;
+          int coord_t = 0, coord_h = 0, coord_w = 0;
+          const int band_a = p.rope.table_half - 2 * (p.rope.table_half / 3);
+          const int band_b = band_a + p.rope.table_half / 3;
+          if (rotate) {
+            const int pos = in ? max(__ldg(p.rope.positions + t0 + row), 0) : 0;
+            const int last = p.rope.table_rows - 1;
+            if (p.rope.frame_seqlen == 0) {   // one table row per token: every band reads row `pos`
+              coord_t = coord_h = coord_w = min(pos, last);
+            } else {
+              const int frame = pos / p.rope.frame_seqlen, spatial = pos - frame * p.rope.frame_seqlen;
+              const int prow = spatial / p.rope.width;
+              coord_t = min(frame, last);
+              coord_h = min(prow, last);
+              coord_w = min(spatial - prow * p.rope.width, last);
+            }
+          }
+          // camera transform: this token's frame picks the 4 x 4 matrices
+          const bool transform = CAM && cam.matrices != nullptr;
+          const float* cam_frame = nullptr;
+          if (transform)
+            cam_frame = cam.matrices +
+                        static_cast<size_t>(min((t0 + row) / cam.tokens_per_frame, cam.frames - 1)) * 64;
+          const float* bias_head = (tensor ? p.bias_v : p.bias_k) + head * D;
+          // accumulator complete: the tile's last pair is pair gp - 1
+          bool waited = false;
+#pragma unroll
+          for (int sub = 0; sub < ROUNDS; ++sub) {
+            const int col0 = wg * (D / 2) + sub * 32;   // this thread's columns col0 .. col0 + 32
+            // Centre rows of this warp's 32 tokens (32 columns = 64 bytes each), gathered
+            // cooperatively: 4 lanes read one row's 16-byte pieces, so a load instruction touches
+            // 8 lines instead of 32; the rows are redistributed through a swizzled staging area.
+            constexpr int PIECES = 4, RPI = 8;
+            const int wrow0 = 32 * (warp & 3);
+            const uint16_t* cbase = static_cast<const uint16_t*>(hist.centers) +
+                                    static_cast<size_t>(head) * D + col0;
+            uint4 cen[PIECES];
+#pragma unroll
+            for (int i = 0; i < PIECES; ++i) {
+              const int rloc = i * RPI + lane / PIECES, piece = lane % PIECES;
+              const int crow_i = crow[mb * TOK + wrow0 + rloc];
+              cen[i] = __ldg(reinterpret_cast<const uint4*>(
+                  cbase + static_cast<size_t>(crow_i) * hist.center_width + piece * 8));
+            }
+            // rotation entries of this thread's 16 pairs, requested before the accumulator wait
+            float2 rot[16];
+            if (ROPE) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                rot[i] = make_float2(1.f, 0.f);
+                if (rotate) {
+                  const int local = col0 / 2 + i;   // pair of the head row
+                  const int pg = p.rope.pair_index ? __ldg(p.rope.pair_index + head * (D / 2) + local) : local;
+                  const int coord = pg < band_a ? coord_t : (pg < band_b ? coord_h : coord_w);
+                  rot[i] = __ldg(reinterpret_cast<const float2*>(p.rope.cos_sin) +
+                                 static_cast<size_t>(coord) * p.rope.table_half + pg);
+                }
+              }
+            }
+            float bias[32];
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const float4 b4 = __ldg(reinterpret_cast<const float4*>(bias_head + col0 + j));
+              bias[j] = b4.x; bias[j + 1] = b4.y; bias[j + 2] = b4.z; bias[j + 3] = b4.w;
+            }
+            if (!waited) {
+              ok = mwait_all(&bars[PAIR_DONE + ((gp - 1) & (NDONE - 1))], ((gp - 1) / NDONE) & 1, ctx, 503);
+              waited = true;
+              tc_fence_after();
+            }
+            // the accumulator read stays in flight under the centre staging
+            uint32_t acc_raw[32];
+            tmem_ld32_issue(tmem_base + lane_sel + col0, acc_raw);
+            {
+              uint8_t* stage = smem + L::CODES_OFF + warp * (32 * PIECES * 16);
+#pragma unroll
+              for (int i = 0; i < PIECES; ++i) {
+                const int rloc = i * RPI + lane / PIECES, piece = lane % PIECES;
+                *reinterpret_cast<uint4*>(stage + rloc * (PIECES * 16) +
+                                          ((piece ^ (rloc & (PIECES - 1))) << 4)) = cen[i];
+              }
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < PIECES; ++j)
+                cen[j] = *reinterpret_cast<const uint4*>(stage + lane * (PIECES * 16) +
+                                                         ((j ^ (lane & (PIECES - 1))) << 4));
+              __syncwarp();
+            }
+            tmem_ld32_wait(acc_raw);
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc_raw[i]);
+            uint32_t* packed = outp[sub];
 #pragma unroll
             for (int j4 = 0; j4 < 4; ++j4) {
-              uint4 w;
-              w.x = pack_bf16x2(v[j4 * 8 + 0] * inv, v[j4 * 8 + 1] * inv);
-              w.y = pack_bf16x2(v[j4 * 8 + 2] * inv, v[j4 * 8 + 3] * inv);
-              w.z = pack_bf16x2(v[j4 * 8 + 4] * inv, v[j4 * 8 + 5] * inv);
-              w.w = pack_bf16x2(v[j4 * 8 + 6] * inv, v[j4 * 8 + 7] * inv);
-              *reinterpret_cast<uint4*>(dst + cc * 32 + j4 * 8) = w;
+              const uint32_t cwords[4] = {cen[j4].x, cen[j4].y, cen[j4].z, cen[j4].w};
+              float block[8];   // the 8-wide block j4 of this thread's columns (camera transform only)
+              if (!ROPE && !CAM) {
+                // plain rebuild in packed bf16 arithmetic: bf16x2(acc + bias) then one bf16x2 add of the
+                // centre word -- the same two roundings (the sum of two bf16 numbers is exact in fp32
+                // unless the smaller one lies below the rounding step of the larger either way)
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                  const int j = j4 * 8 + w * 2;
+                  const uint32_t first = pack_bf16x2(v[j] + bias[j], v[j + 1] + bias[j + 1]);
+                  const __nv_bfloat162 sum = __hadd2(*reinterpret_cast<const __nv_bfloat162*>(&first),
+                                                     *reinterpret_cast<const __nv_bfloat162*>(&cwords[w]));
+                  packed[j4 * 4 + w] = in ? *reinterpret_cast<const uint32_t*>(&sum) : 0u;
+                }
+                continue;
+              }
+#pragma unroll
+              for (int w = 0; w < 4; ++w) {
+                const int j = j4 * 8 + w * 2;
+                // the rebuilt pair in packed bf16 arithmetic (as above), then widened for the transforms
+                const uint32_t first = pack_bf16x2(v[j] + bias[j], v[j + 1] + bias[j + 1]);
+                const __nv_bfloat162 sum = __hadd2(*reinterpret_cast<const __nv_bfloat162*>(&first),
+                                                   *reinterpret_cast<const __nv_bfloat162*>(&cwords[w]));
+                const uint32_t rebuilt = *reinterpret_cast<const uint32_t*>(&sum);
+                float x0 = __uint_as_float(rebuilt << 16), x1 = __uint_as_float(rebuilt & 0xFFFF0000u);
+                if (rotate) {   // the pair (x0, x1) of the rebuilt bf16 key is one complex number
+                  const float2 cs = rot[j >> 1];
+                  const float k0 = x0, k1 = x1;
+                  x0 = fmaf(k0, cs.x, -(k1 * cs.y));
+                  x1 = fmaf(k0, cs.y, k1 * cs.x);
+                }
+                if (CAM) {
+                  block[2 * w] = x0;
+                  block[2 * w + 1] = x1;
+                }
+                packed[j4 * 4 + w] = in ? pack_bf16x2(x0, x1) : 0u;
+              }
+              if (transform) {   // slots (w) of the block are mixed by the token's 4 x 4 camera matrix
+                const int which = __ldg(cam.cam_index + head * (D / 8) + col0 / 8 + j4) & 3;
+                const float4* m = reinterpret_cast<const float4*>(cam_frame + which * 16);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) block[k] = round_to_bf16(block[k]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float4 mi = __ldg(m + i);
+                  const float m0 = round_to_bf16(mi.x), m1 = round_to_bf16(mi.y);
+                  const float m2 = round_to_bf16(mi.z), m3 = round_to_bf16(mi.w);
+                  const float y0 = fmaf(m3, block[6], fmaf(m2, block[4], fmaf(m1, block[2], m0 * block[0])));
+                  const float y1 = fmaf(m3, block[7], fmaf(m2, block[5], fmaf(m1, block[3], m0 * block[1])));
+                  packed[j4 * 4 + i] = in ? pack_bf16x2(y0, y1) : 0u;
+                }
+              }
             }
           }
         }
-        if (qrow < p.Q)
-          p.lse[split_rows + static_cast<size_t>(qrow) * p.heads + head] =
-              l_run > 0.f ? (m_used + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+        if (!ok) break;
+        // the centre staging lived in the code buffer: only now may the next job's codes overwrite it;
+        // the accumulator has been read, the metadata buffer is free
+        fence_proxy_async();
+        warp_arrive(&bars[CODES_FREE], lane);
+        warp_arrive(&bars[META_FREE + mb], lane);
+        tc_fence_before();
+        // ---- publish: wait until every consumer of the group has taken the slot's previous tile
+        const int slot = seq % R, use = seq / R;
+        int32_t* f = gflags + slot * 4;
+        {
+          int okf = 1;
+          if (lane == 0) okf = fwait(f + 2 + tensor, p.cons * use, ctx, 504) ? 1 : 0;
+          ok = __shfl_sync(0xffffffffu, okf, 0) != 0;
+        }
+        if (!ok) break;
+        {
+          uint16_t* dst = ring + (static_cast<size_t>(g * R + slot) * TOK + row) * D + wg * (D / 2);
+#pragma unroll
+          for (int sub = 0; sub < ROUNDS; ++sub)
+#pragma unroll
+            for (int j4 = 0; j4 < 4; ++j4)
+              *reinterpret_cast<uint4*>(dst + sub * 32 + j4 * 8) =
+                  make_uint4(outp[sub][j4 * 4], outp[sub][j4 * 4 + 1], outp[sub][j4 * 4 + 2], outp[sub][j4 * 4 + 3]);
+        }
+        __threadfence();
+        fence_proxy_async_all();   // the consumers read the tile with TMA
+        warp_arrive(&bars[OUT_DONE], lane);
+        if (tid == 0) {
+          ok = mwait(&bars[OUT_DONE], jobs & 1, ctx, 505);
+          if (ok) st_release(f + tensor, seq + 1);
+        }
+        if (warp == 0) ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        ++jobs;
       }
+    }
+  }
+}
+
+template <int D, bool ROPE, bool CAM>
+__global__ void __launch_bounds__(THREADS, 1)
+attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
+                  const __grid_constant__ CUtensorMap map_wk,
+                  const __grid_constant__ CUtensorMap map_wv,
+                  const __grid_constant__ CUtensorMap map_ck,
+                  const __grid_constant__ CUtensorMap map_cv,
+                  const __grid_constant__ CUtensorMap map_rk,
+                  const __grid_constant__ CUtensorMap map_rv, Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + M_SLOT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + M_ABORT);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int per_group = p.cons + p.prod;
+  const int g = blockIdx.x / per_group, role = blockIdx.x % per_group;
+
+  if (tid == 0) {
+    mbar_init(&bars[Q_FULL], 1);
+    mbar_init(&bars[Q_FREE], 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars[K_FULL + s], 1);
+      mbar_init(&bars[K_FREE + s], 1);
+      mbar_init(&bars[V_FULL + s], 1);
+      mbar_init(&bars[V_FREE + s], 1);
+      mbar_init(&bars[S_FULL + s], 1);
+      mbar_init(&bars[P_READY + s], QT / 32);
+      mbar_init(&bars[PV_DONE + s], 1);
+      mbar_init(&bars[O_FREE + s], QT / 32);
+      mbar_init(&bars[META_FULL + s], 1);
+      mbar_init(&bars[META_FREE + s], COMPUTE_WARPS);
+    }
+    for (int s = 0; s < MAX_NW; ++s) mbar_init(&bars[W_FULL + s], 1);     // TMA: decoder rows of a pair landed
+    for (int s = 0; s < NDONE; ++s) mbar_init(&bars[PAIR_DONE + s], 1);   // the pair's MMAs are complete
+    for (int s = 0; s < NSTAGE; ++s) mbar_init(&bars[LAT_FULL + s], COMPUTE_WARPS);   // latent pair staged in TMEM
+    mbar_init(&bars[CODES_FULL], 1);                 // the tile's codes landed
+    mbar_init(&bars[CODES_FREE], COMPUTE_WARPS);     // every warp is done with codes and centre staging
+    mbar_init(&bars[OUT_DONE], COMPUTE_WARPS);       // every warp's part of the tile is in the ring
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 9) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const Ctx ctx{abort_flag, p.flags + F_ABORT, p.wait_budget};
+
+  if (g < p.groups) {
+    if (role < p.cons) {
+      consumer_role<D>(smem, bars, tmem_base, &map_q, &map_rk, &map_rv, p, ctx, g, role);
+    } else {
+      const int pidx = role - p.cons;
+      const bool value = pidx >= p.prod / 2;
+      producer_role<D, ROPE, CAM>(smem, bars, tmem_base, value ? &map_wv : &map_wk,
+                                  value ? &map_cv : &map_ck, p, ctx, g, pidx);
     }
   }
   tc_fence_before();
   __syncthreads();
-  // no CTA may leave while a peer can still store into its shared memory or signal its barriers
-  cluster_sync_all();
   if (warp == 9) tmem_dealloc(tmem_base, 512);
   if (tid == 0 && *abort_flag && p.status) atomicCAS(p.status, 0, *abort_flag);
 }
@@ -919,52 +1121,166 @@ __global__ void fill_empty_kernel(uint16_t* out, float* lse, size_t rows, int d)
   if (i < rows) lse[i] = -INFINITY;
 }
 
-constexpr size_t SMEM_LIMIT = 232448;  // 227 KB per CTA
-long long* g_profile = nullptr;
+// ---- the bounded waits on their own: nobody ever arrives, the wait must give up --------------------
+__global__ void wait_expiry_kernel(int kind, long long budget, int32_t* gabort, int32_t* status) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  const Ctx ctx{&abort_flag, gabort, budget};
+  if (threadIdx.x == 0) {
+    const bool ok = kind == 0 ? mwait(&bar, 0, ctx, 990) : fwait(gabort + 1, 1, ctx, 991);
+    if (!ok && abort_flag) atomicCAS(status, 0, abort_flag);
+  }
+}
 
-template <int D, bool ROPE, bool CAM, bool PROF>
-int launch(const CUtensorMap maps[5], Params& p, cudaStream_t stream) {
+constexpr size_t SMEM_LIMIT = 232448;  // 227 KB per CTA
+
+// ---- per-device state: the tile ring and the flag words live in the library's own device image ------
+constexpr size_t FLAG_BYTES = 65536;
+constexpr size_t RING_BYTES = 24u << 20;
+static __device__ __align__(1024) unsigned char g_ring[FLAG_BYTES + RING_BYTES];
+
+constexpr int MAX_DEVICES = 64;
+struct DeviceState {
+  unsigned char* base = nullptr;
+  int sms = 0;
+  cudaEvent_t last = nullptr;
+  cudaStream_t last_stream = nullptr;
+  bool used = false;
+};
+std::mutex g_mutex;
+DeviceState g_state[MAX_DEVICES];
+
+int device_state(DeviceState** out) {
+  int device = 0;
+  NKV_CUDA(cudaGetDevice(&device));
+  NKV_REQUIRE(device >= 0 && device < MAX_DEVICES, NKV_ERR_UNSUPPORTED,
+              "device ordinal %d beyond the %d the fused read tracks", device, MAX_DEVICES);
+  DeviceState& s = g_state[device];
+  if (s.base == nullptr) {
+    void* resolved = nullptr;
+    NKV_CUDA(cudaGetSymbolAddress(&resolved, g_ring));
+    NKV_REQUIRE(resolved != nullptr, NKV_ERR_CUDA, "tile ring has no device address");
+    NKV_CUDA(cudaDeviceGetAttribute(&s.sms, cudaDevAttrMultiProcessorCount, device));
+    int cooperative = 0;
+    NKV_CUDA(cudaDeviceGetAttribute(&cooperative, cudaDevAttrCooperativeLaunch, device));
+    NKV_REQUIRE(cooperative != 0, NKV_ERR_UNSUPPORTED, "device %d cannot launch cooperative kernels", device);
+    NKV_CUDA(cudaEventCreateWithFlags(&s.last, cudaEventDisableTiming));
+    s.base = static_cast<unsigned char*>(resolved);
+  }
+  *out = &s;
+  return NKV_OK;
+}
+
+int tuning(const char* name, int fallback) {
+#ifdef NKV_DEV
+  const char* env = getenv(name);
+  if (env && env[0]) return atoi(env);
+#else
+  (void)name;
+#endif
+  return fallback;
+}
+
+template <int D, bool ROPE, bool CAM>
+int launch(const CUtensorMap maps[7], Params& p, DeviceState& dev, cudaStream_t stream) {
   using L = Layout<D>;
-  int nw = MAX_NW;   // as many decoder-row slots as fit (at least the two staging slots' worth)
-  while (nw > NSTAGE && L::bytes(nw, p.ngroups, p.rank) > SMEM_LIMIT) --nw;
-  size_t smem = L::bytes(nw, p.ngroups, p.rank);
+  int nw = MAX_NW;   // as many decoder-row slots as fit
+  while (nw > 2 && static_cast<size_t>(L::producer_bytes(p.npairs, nw, p.ngroups)) + 1024 > SMEM_LIMIT) --nw;
+  if (nw > p.npairs) nw = p.npairs;
+  if (nw < 2 && p.npairs >= 2) nw = 2;
+  size_t smem = static_cast<size_t>(L::producer_bytes(p.npairs, nw, p.ngroups));
+  if (smem < static_cast<size_t>(L::CONSUMER_BYTES)) smem = L::CONSUMER_BYTES;
+  smem += 1024;
   NKV_REQUIRE(smem <= SMEM_LIMIT, NKV_ERR_UNSUPPORTED,
               "codec attention needs %zu bytes of shared memory (rank %d, rank/group %d)", smem,
               p.rank, p.ngroups);
   p.nw = nw;
-  p.prof = g_profile;
-  auto kernel = attn_codec_kernel<D, ROPE, CAM, PROF>;
+  auto kernel = attn_codec_kernel<D, ROPE, CAM>;
   NKV_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(smem)));
-  const int qblocks = ceil_div(p.Q, NQ * QT);
+  // the flag words start every launch at zero
+  NKV_CUDA(cudaMemsetAsync(p.flags, 0, static_cast<size_t>(F_SLOTS + p.groups * p.ring * 4) * 4, stream));
   cudaLaunchConfig_t config{};
-  const int splits = ceil_div(ceil_div(p.N, TOK), p.tiles_per_split);
-  config.gridDim = dim3(ceil_div(qblocks, L::CL) * L::CL, p.heads, splits);   // padded: idle CTAs still decode
+  config.gridDim = dim3(p.groups * (p.cons + p.prod));
   config.blockDim = dim3(THREADS);
   config.dynamicSmemBytes = smem;
   config.stream = stream;
   cudaLaunchAttribute attr{};
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = L::CL;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
+  attr.id = cudaLaunchAttributeCooperative;   // producers and consumers wait on one another: all CTAs resident
+  attr.val.cooperative = 1;
   config.attrs = &attr;
   config.numAttrs = 1;
-  NKV_CUDA(cudaLaunchKernelEx(&config, kernel, maps[0], maps[1], maps[2], maps[3], maps[4], p));
+  NKV_CUDA(cudaLaunchKernelEx(&config, kernel, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5],
+                              maps[6], p));
+  (void)dev;
   return NKV_OK;
 }
 
-int launch_for(int dk, bool rope, bool cam, const CUtensorMap maps[5], Params& p, cudaStream_t stream) {
-  if (g_profile != nullptr && dk == 128 && !rope && !cam)   // the instrumented build exists for this case only
-    return launch<128, false, false, true>(maps, p, stream);
+int launch_for(int dk, bool rope, bool cam, const CUtensorMap maps[7], Params& p, DeviceState& dev,
+               cudaStream_t stream) {
   if (cam)   // camera builds always carry the rotation code (a NULL table switches it off at run time)
-    return dk == 128 ? launch<128, true, true, false>(maps, p, stream)
-                     : launch<64, true, true, false>(maps, p, stream);
+    return dk == 128 ? launch<128, true, true>(maps, p, dev, stream)
+                     : launch<64, true, true>(maps, p, dev, stream);
   if (dk == 128)
-    return rope ? launch<128, true, false, false>(maps, p, stream)
-                : launch<128, false, false, false>(maps, p, stream);
-  return rope ? launch<64, true, false, false>(maps, p, stream)
-              : launch<64, false, false, false>(maps, p, stream);
+    return rope ? launch<128, true, false>(maps, p, dev, stream)
+                : launch<128, false, false>(maps, p, dev, stream);
+  return rope ? launch<64, true, false>(maps, p, dev, stream)
+              : launch<64, false, false>(maps, p, dev, stream);
+}
+
+// Work decomposition of one launch: consumers and producers per group, groups, history splits.
+struct Plan { int cons, prod, groups, qchunks, splits, tiles_per_split, ring; };
+
+Plan make_plan(int sms, int Q, int heads, int tiles, int rank, int dk, int max_splits) {
+  Plan plan{};
+  // a producer needs roughly rank-proportional time per tile; one pair of producers (K, V) per
+  // tensor keeps up with the consumers at small ranks, two pairs at the codec's ranks
+  int prod = rank >= 256 ? 4 : 2;
+  prod = tuning("NKV_ATTN_PROD", prod);
+  if (prod < 2) prod = 2;
+  prod &= ~1;
+  const int qblocks = ceil_div(Q, NQ * QT);
+  int cons = qblocks < sms - prod ? qblocks : sms - prod;
+  const int qchunks = ceil_div(qblocks, cons);
+  cons = ceil_div(qblocks, qchunks);
+  const int ring_slots = static_cast<int>(RING_BYTES / (2u * TOK * dk * 2u));
+  int wmax = sms / (cons + prod);
+  if (wmax > ring_slots / 4) wmax = ring_slots / 4;
+  if (wmax < 1) wmax = 1;
+  const int forced = tuning("NKV_ATTN_SPLITS", 0);
+  long long best_cost = -1;
+  for (int s = 1; s <= max_splits; ++s) {
+    if (forced > 0 && s != forced && forced <= max_splits) continue;
+    const int tps = ceil_div(tiles, s);
+    const int eff = ceil_div(tiles, tps);
+    if (eff != s && forced == 0) continue;
+    const int units = qchunks * heads * eff;
+    const int groups = units < wmax ? units : wmax;
+    const int rounds = ceil_div(units, groups);
+    // a unit costs its tiles plus a fill / drain of a few tile times; split partials cost a merge
+    const long long cost = static_cast<long long>(rounds) * (tps + 6) + (eff > 1 ? 4 + eff : 0);
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      plan.splits = eff;
+      plan.tiles_per_split = tps;
+      plan.groups = groups;
+    }
+  }
+  plan.cons = cons;
+  plan.prod = prod;
+  plan.qchunks = qchunks;
+  int ring = ring_slots / plan.groups;
+  plan.ring = ring > MAX_RING ? MAX_RING : ring;
+  plan.ring = tuning("NKV_ATTN_RING", plan.ring);
+  if (plan.ring > ring) plan.ring = ring;
+  if (plan.ring < 2) plan.ring = 2;
+  return plan;
 }
 
 }  // namespace
@@ -995,12 +1311,25 @@ int tc_prepare_decoder(const void* w_bf16, int64_t rows, int rank, void* out_bf1
   return NKV_OK;
 }
 
-// Development aid: 32 device int64 cycle buckets filled by CTA (0,0) of later launches
-// (compute thread 0: buckets 0-12, MMA thread: 16-22); nullptr switches it off.
-void tc_attn_set_profile(long long* device_buckets) { g_profile = device_buckets; }
-
 bool tc_attn_supported(int dk, int dv, int rank) {
   return dk == dv && (dk == 64 || dk == 128) && rank % 64 == 0 && rank > 0;
+}
+
+// kind 0: an mbarrier nobody arrives on; kind 1: a global counter nobody advances.  The kernel's
+// single waiting thread must give up after `budget_cycles` and report the wait site (990 / 991).
+int tc_wait_expiry_selftest(int kind, long long budget_cycles, int32_t* status_word, cudaStream_t stream) {
+  NKV_REQUIRE((kind == 0 || kind == 1) && budget_cycles > 0 && budget_cycles <= (1ll << 28) && status_word,
+              NKV_ERR_INVALID, "wait self-test: kind=%d budget=%lld", kind, budget_cycles);
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState* dev = nullptr;
+  int rc = device_state(&dev);
+  if (rc != NKV_OK) return rc;
+  // two private flag words behind the ones the fused read uses
+  int32_t* words = reinterpret_cast<int32_t*>(dev->base + FLAG_BYTES - 64);
+  NKV_CUDA(cudaMemsetAsync(words, 0, 8, stream));
+  wait_expiry_kernel<<<1, 32, 0, stream>>>(kind, budget_cycles, words, status_word);
+  NKV_LAUNCH_CHECK("wait_expiry_kernel");
+  return NKV_OK;
 }
 
 int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, int Q, int heads,
@@ -1021,6 +1350,8 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
               "centre row pitch must be a multiple of 8 elements");
   NKV_REQUIRE(q_stride_head % 8 == 0 && q_stride_token % 8 == 0, NKV_ERR_INVALID,
               "query strides must be multiples of 8 elements (16 bytes)");
+  NKV_REQUIRE(((reinterpret_cast<uintptr_t>(bias_k) | reinterpret_cast<uintptr_t>(bias_v)) & 15) == 0,
+              NKV_ERR_INVALID, "bias arrays must be 16-byte aligned");
   if (Q == 0 || heads == 0) return NKV_OK;
   if (N == 0) {
     size_t rows = static_cast<size_t>(Q) * heads;
@@ -1029,7 +1360,18 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
     NKV_LAUNCH_CHECK("fill_empty_kernel");
     return NKV_OK;
   }
-  CUtensorMap maps[5];
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState* dev = nullptr;
+  {
+    int rc = device_state(&dev);
+    if (rc != NKV_OK) return rc;
+  }
+  const int tiles = ceil_div(N, TOK);
+  splits = splits < 1 ? 1 : (splits > tiles ? tiles : splits);
+  if (workspace == nullptr) splits = 1;
+  const Plan plan = make_plan(dev->sms, Q, heads, tiles, rank, dk, splits);
+
+  CUtensorMap maps[7];
   {
     uint64_t dims[3] = {static_cast<uint64_t>(dk), static_cast<uint64_t>(heads), static_cast<uint64_t>(Q)};
     uint64_t strides[2] = {static_cast<uint64_t>(q_stride_head) * 2, static_cast<uint64_t>(q_stride_token) * 2};
@@ -1041,7 +1383,7 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
   for (int w = 0; w < 2; ++w) {
     uint64_t dims[2] = {static_cast<uint64_t>(rank), static_cast<uint64_t>(heads) * dk};
     uint64_t strides[1] = {static_cast<uint64_t>(rank) * 2};
-    uint32_t box[2] = {64, PART};   // one CTA streams 64 rows of the slice
+    uint32_t box[2] = {64, static_cast<uint32_t>(dk)};   // a producer streams all rows of the head's slice
     int rc = encode_tensor_map(&maps[1 + w], 2, weights[w], 2, dims, strides, box, 128);
     if (rc != NKV_OK) return rc;
   }
@@ -1057,7 +1399,20 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
     if (rc != NKV_OK) return rc;
   }
   Params p{};
+  const size_t ring_rows = static_cast<size_t>(plan.groups) * plan.ring * TOK;
+  p.flags = reinterpret_cast<int32_t*>(dev->base);
+  p.ring_k = reinterpret_cast<uint16_t*>(dev->base + FLAG_BYTES);
+  p.ring_v = p.ring_k + ring_rows * dk;
+  const void* rings[2] = {p.ring_k, p.ring_v};
+  for (int w = 0; w < 2; ++w) {   // a consumer loads a slot as [128 tok x 64 col] boxes
+    uint64_t dims[2] = {static_cast<uint64_t>(dk), static_cast<uint64_t>(ring_rows)};
+    uint64_t strides[1] = {static_cast<uint64_t>(dk) * 2};
+    uint32_t box[2] = {64, TOK};
+    int rc = encode_tensor_map(&maps[5 + w], 2, rings[w], 2, dims, strides, box, 128);
+    if (rc != NKV_OK) return rc;
+  }
   p.Q = Q; p.heads = heads; p.N = N; p.rank = rank; p.nchunks = rank / CHUNK;
+  p.npairs = (p.nchunks + 1) / 2;
   p.group = group; p.ngroups = rank / group; p.scale_dtype = hk.scale_dtype;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.hk = hk; p.hv = hv; p.bias_k = bias_k; p.bias_v = bias_v;
@@ -1066,30 +1421,44 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
   if (rope != nullptr) p.rope = *rope;
   if (cam_k != nullptr) p.cam_k = *cam_k;
   if (cam_v != nullptr) p.cam_v = *cam_v;
-  // History splits: each grid.z slice attends a contiguous run of tiles and writes a partial
-  // (O, lse); the partials are merged by log-sum-exp.  Evens out the rounds of resident clusters.
-  const int tiles = ceil_div(N, TOK);
-  splits = splits < 1 ? 1 : (splits > tiles ? tiles : splits);
-  p.tiles_per_split = ceil_div(tiles, splits);
-  splits = ceil_div(tiles, p.tiles_per_split);
-  if (splits == 1) {
+  p.tiles = tiles;
+  p.tiles_per_split = plan.tiles_per_split;
+  p.splits = plan.splits;
+  p.qchunks = plan.qchunks;
+  p.groups = plan.groups; p.cons = plan.cons; p.prod = plan.prod; p.ring = plan.ring;
+  p.units = plan.qchunks * heads * plan.splits;
+  p.wait_budget = 1ll << 31;   // about a second of SM cycles per wait
+  // launches of the fused read share the ring: one that is enqueued on another stream than the
+  // previous one waits for it
+  if (dev->used && dev->last_stream != stream) NKV_CUDA(cudaStreamWaitEvent(stream, dev->last, 0));
+  const bool rope_on = rope != nullptr, cam_on = cam_k != nullptr || cam_v != nullptr;
+  int rc;
+  if (plan.splits == 1) {
     p.out = static_cast<uint16_t*>(out); p.lse = lse;
-    return launch_for(dk, rope != nullptr, cam_k != nullptr || cam_v != nullptr, maps, p, stream);
+    rc = launch_for(dk, rope_on, cam_on, maps, p, *dev, stream);
+  } else {
+    // History splits: each unit attends a contiguous run of tiles and writes a partial (O, lse) in
+    // the output dtype; the partials are merged by log-sum-exp.
+    const size_t rows = static_cast<size_t>(Q) * heads;
+    uint16_t* part_out = static_cast<uint16_t*>(workspace);
+    float* part_lse = reinterpret_cast<float*>(part_out + static_cast<size_t>(plan.splits) * rows * dv);
+    p.out = part_out; p.lse = part_lse;
+    rc = launch_for(dk, rope_on, cam_on, maps, p, *dev, stream);
+    if (rc == NKV_OK) {
+      const void* outs[16];
+      const float* lses[16];
+      for (int z = 0; z < plan.splits; ++z) {
+        outs[z] = part_out + static_cast<size_t>(z) * rows * dv;
+        lses[z] = part_lse + static_cast<size_t>(z) * rows;
+      }
+      rc = lse_merge(outs, lses, plan.splits, static_cast<int64_t>(rows), dv, NKV_BF16, out, lse, stream);
+    }
   }
-  NKV_REQUIRE(workspace != nullptr, NKV_ERR_INVALID, "history splits need a workspace");
-  const size_t rows = static_cast<size_t>(Q) * heads;
-  uint16_t* part_out = static_cast<uint16_t*>(workspace);
-  float* part_lse = reinterpret_cast<float*>(part_out + static_cast<size_t>(splits) * rows * dv);
-  p.out = part_out; p.lse = part_lse;
-  int rc = launch_for(dk, rope != nullptr, cam_k != nullptr || cam_v != nullptr, maps, p, stream);
   if (rc != NKV_OK) return rc;
-  const void* outs[16];
-  const float* lses[16];
-  for (int z = 0; z < splits; ++z) {
-    outs[z] = part_out + static_cast<size_t>(z) * rows * dv;
-    lses[z] = part_lse + static_cast<size_t>(z) * rows;
-  }
-  return lse_merge(outs, lses, splits, static_cast<int64_t>(rows), dv, NKV_BF16, out, lse, stream);
+  NKV_CUDA(cudaEventRecord(dev->last, stream));
+  dev->last_stream = stream;
+  dev->used = true;
+  return NKV_OK;
 }
 
 }  // namespace nkv

@@ -250,9 +250,8 @@ def prepare_decoder(weight: torch.Tensor) -> torch.Tensor:
 
 def tensor_core_read(dtype: torch.dtype, dk: int, dv: int, rank: int) -> bool:
     """Whether nkv_attn_codec runs this shape on the tcgen05 kernel (and may take prepared weights)."""
-    import os
     return (dtype == torch.bfloat16 and dk == dv and dk in (64, 128) and rank % 64 == 0
-            and not _SIMT_FORCED[0] and os.environ.get("NKV_FORCE_SIMT", "0") in ("", "0"))
+            and not _SIMT_FORCED[0])
 
 
 _SIMT_FORCED = [False]
@@ -562,4 +561,4 @@ def lse_merge(partials):
 def force_simt(on: bool) -> None:
     """Triage hook: run bf16 work on the fp32 CUDA-core kernels (same rounding points)."""
     _SIMT_FORCED[0] = bool(on)
-    _lib.library().nkv_debug_force_simt(1 if on else 0)
+    _lib.check(_lib.library().nkv_set_bf16_path(1 if on else 0))
