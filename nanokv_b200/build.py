@@ -24,6 +24,13 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 
 
+def flags() -> list[str]:
+    """NKV_DEV=1 in the environment adds -DNKV_DEV: tuning knobs read from the environment by the
+    fused read's planner (development builds only; the default build has none)."""
+    extra = ["-DNKV_DEV"] if os.environ.get("NKV_DEV", "0") not in ("", "0") else []
+    return NVCC_FLAGS + extra
+
+
 def nvcc() -> str:
     found = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not Path(found).exists():
@@ -38,6 +45,9 @@ def sources() -> list[Path]:
 def stale() -> bool:
     if not LIBRARY.exists():
         return True
+    stamp = BUILD / "flags.txt"
+    if not stamp.exists() or stamp.read_text() != " ".join(flags()):
+        return True
     built = LIBRARY.stat().st_mtime
     deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))
     deps.append(PACKAGE.parent / "include" / "nanokv_b200.h")
@@ -46,7 +56,7 @@ def stale() -> bool:
 
 def compile_one(source: Path) -> Path:
     obj = BUILD / (source.stem + ".o")
-    cmd = [nvcc(), *NVCC_FLAGS, "-c", str(source), "-o", str(obj)]
+    cmd = [nvcc(), *flags(), "-c", str(source), "-o", str(obj)]
     result = subprocess.run(cmd, capture_output=True, text=True)
     (BUILD / (source.stem + ".ptxas.log")).write_text(result.stderr)
     if result.returncode:
@@ -64,6 +74,7 @@ def build(force: bool = False) -> Path:
     result = subprocess.run(cmd, capture_output=True, text=True)
     if result.returncode:
         raise RuntimeError(f"link failed:\n{result.stderr[-4000:]}")
+    (BUILD / "flags.txt").write_text(" ".join(flags()))
     return LIBRARY
 
 

@@ -57,7 +57,7 @@ constexpr int NSTAGE = 4;         // latent staging slots in tensor memory
 constexpr int NDONE = 8;          // "MMAs of pair g are complete" barriers, indexed by g % 8
 constexpr int KVS = 2;            // K / V stages of a consumer
 constexpr int META_BYTES = 3072;  // barriers, flags and per-token metadata at the head of shared memory
-constexpr int MAX_RING = 8;       // ring slots per group
+constexpr int MAX_RING = 8;       // ring slots per group (GF - GF_DONE flag words)
 constexpr float RESCALE_THRESHOLD = 8.0f;
 
 enum Bar {
@@ -66,7 +66,7 @@ enum Bar {
   PV_DONE = 14, O_FREE = 16,
   // producer
   W_FULL = 18, PAIR_DONE = 26, LAT_FULL = 34, META_FULL = 38, META_FREE = 40, CODES_FULL = 42,
-  CODES_FREE = 43, OUT_DONE = 44, NUM_BARS = 45
+  CODES_FREE = 43, OUT_DONE = 44, NUM_BARS = 46
 };
 
 // meta block
@@ -77,7 +77,10 @@ static_assert(M_ABORT + 4 <= M_CROW && M_CROW + 2 * TOK * 4 <= META_BYTES, "meta
 
 // global flag words
 constexpr int F_ABORT = 0;        // launch-wide abort (wait-site code)
-constexpr int F_SLOTS = 32;       // then [groups][ring][4]: K published, V published, K consumed, V consumed
+constexpr int F_GROUPS = 32;      // then per group GF words:
+constexpr int GF = 16;            //   [0, 8): tiles published by producer p of the group (K producers first)
+constexpr int GF_DONE = 8;        //   [8, 16): per ring slot, consumers that have taken the slot's tiles
+constexpr int MAX_PROD = 8;
 
 struct Params {
   int Q, heads, N, rank, nchunks, npairs, ngroups, group;
@@ -97,6 +100,7 @@ struct Params {
   uint16_t* ring_k;  // [groups * ring * 128][D]
   uint16_t* ring_v;
   int32_t* flags;
+  long long* prof;   // development builds: cycle buckets of group 0's first consumer and first producer
 };
 
 struct Unit { int head, z, qc, tile0, nt; };
@@ -128,6 +132,15 @@ __device__ __forceinline__ int ld_acquire(const int32_t* p) {
   int v;
   asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
+}
+__device__ __forceinline__ int4 ld_acquire_v4(const int32_t* p) {
+  int4 v;
+  asm volatile("ld.acquire.gpu.global.v4.s32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_relaxed_add(int32_t* p, int v) {
+  asm volatile("red.relaxed.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ void st_release(int32_t* p, int v) {
   asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -271,6 +284,43 @@ __device__ __forceinline__ float exp2_approx(float x) {
   return y;
 }
 
+// Lap timer of one thread (development builds only): adds the cycles since the previous lap to a
+// bucket kept in registers; flush() adds the buckets to global memory once, at the end.
+#ifdef NKV_DEV
+struct Laps {
+  long long* out;
+  unsigned last;
+  unsigned acc[8];
+  __device__ __forceinline__ void start(long long* dst, bool on) {
+    out = on ? dst : nullptr;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0;
+    last = static_cast<unsigned>(clock64());
+  }
+  __device__ __forceinline__ void lap(int bucket) {
+    if (out) {
+      const unsigned now = static_cast<unsigned>(clock64());
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (i == bucket) acc[i] += now - last;
+      last = now;
+    }
+  }
+  __device__ __forceinline__ void flush() {
+    if (out) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) out[i] += acc[i];
+    }
+  }
+};
+#else
+struct Laps {
+  __device__ __forceinline__ void start(long long*, bool) {}
+  __device__ __forceinline__ void lap(int) {}
+  __device__ __forceinline__ void flush() {}
+};
+#endif
+
 template <int D>
 struct Layout {
   static constexpr int DCH = D / 64;                      // 64-column tiles of a head row
@@ -279,15 +329,13 @@ struct Layout {
   static constexpr int K_OFF = Q_OFF + NQ * DCH * TILE_BYTES;    // [KVS][DCH] tiles [128 tok x 64]
   static constexpr int V_OFF = K_OFF + KVS * DCH * TILE_BYTES;   // [KVS][DCH] tiles, token-major like K
   static constexpr int CONSUMER_BYTES = V_OFF + KVS * DCH * TILE_BYTES;
-  // producer: the tile's codes (one block per pair of latent chunks; its head doubles as the centre
-  // staging of the epilogue, 8 warps x 2 KB), the decoder-row slots, the tokens' scales
+  // producer: the tile's codes (one block per pair of latent chunks), the centre staging of the
+  // epilogue (8 warps x 2 KB), the decoder-row slots, the tokens' scales
   static constexpr int CODES_OFF = META_BYTES;
-  __host__ __device__ static int codes_bytes(int npairs) {
-    const int bytes = npairs * CODE_BLOCK;
-    return bytes < TILE_BYTES ? TILE_BYTES : bytes;
-  }
+  static constexpr int SCRATCH_BYTES = COMPUTE_WARPS * 2048;
+  __host__ __device__ static int scratch_off(int npairs) { return CODES_OFF + npairs * CODE_BLOCK; }
   static constexpr int SLOT_BYTES = 2 * D * 128;          // a pair of [D rows x 64 latent cols] tiles
-  __host__ __device__ static int ring_off(int npairs) { return CODES_OFF + codes_bytes(npairs); }
+  __host__ __device__ static int ring_off(int npairs) { return scratch_off(npairs) + SCRATCH_BYTES; }
   __host__ __device__ static int scales_off(int npairs, int nw) { return ring_off(npairs) + nw * SLOT_BYTES; }
   __host__ __device__ static int producer_bytes(int npairs, int nw, int ngroups) {
     return scales_off(npairs, nw) + 2 * TOK * ngroups * 2;
@@ -304,7 +352,7 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
   constexpr int DCH = L::DCH;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int R = p.ring;
-  int32_t* gflags = p.flags + F_SLOTS + g * R * 4;
+  int32_t* gflags = p.flags + F_GROUPS + g * GF;
   auto queries_of = [&](const Unit& un, int& q0) {
     q0 = (un.qc * p.cons + c) * (NQ * QT);
     return q0 >= p.Q ? 0 : ((q0 + QT < p.Q) ? 2 : 1);
@@ -319,6 +367,10 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
       bool ok = true;
       int seq = 0, cseq = 0, ucount = 0;
       int pend_slot = -1, pend_stage = 0, pend_phase = 0;
+      int pub[MAX_PROD] = {0, 0, 0, 0, 0, 0, 0, 0};   // cached copy of the producers' counters
+      const int PH = p.prod / 2;
+      Laps laps;
+      laps.start(p.prof, p.prof != nullptr && g == 0 && c == 0);
       for (int u = g; u < p.units && ok; u += p.groups) {
         const Unit un = unit_of(p, u);
         int q0;
@@ -335,12 +387,33 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
         }
         for (int t = 0; t < un.nt && ok; ++t, ++seq) {
           const int slot = seq % R;
-          int32_t* f = gflags + slot * 4;
           const int stage = cseq % KVS, use = cseq / KVS;
           const int row = (g * R + slot) * TOK;
-          ok = fwait(f + 0, seq + 1, ctx, 102);
-          if (!ok) break;
-          fence_proxy_async_all();   // the tile was written with ordinary stores, TMA reads it
+          laps.lap(7);
+          // tile `seq` of K comes from producer seq % PH as its job number seq / PH, V from
+          // producer PH + seq % PH; the counters are re-read only when the cached copy falls short
+          {
+            const int who = seq % PH, need = seq / PH + 1;
+            if (pub[who] < need || pub[PH + who] < need) {
+              const long long start = clock64();
+              unsigned spins = 0;
+              while (true) {
+                const int4 lo = ld_acquire_v4(gflags);
+                pub[0] = lo.x; pub[1] = lo.y; pub[2] = lo.z; pub[3] = lo.w;
+                if (p.prod > 4) {
+                  const int4 hi = ld_acquire_v4(gflags + 4);
+                  pub[4] = hi.x; pub[5] = hi.y; pub[6] = hi.z; pub[7] = hi.w;
+                }
+                if (pub[who] >= need && pub[PH + who] >= need) break;
+                if (*ctx.abort_flag) { ok = false; break; }
+                if ((++spins & 31u) == 0 && wait_expired(ctx, start, 102)) { ok = false; break; }
+                __nanosleep(40);
+              }
+              if (!ok) break;
+              fence_proxy_async_all();   // the tiles were written with ordinary stores, TMA reads them
+            }
+          }
+          laps.lap(0);
           if (nq > 0) {
             if (use >= 1) ok = mwait(&bars[K_FREE + stage], (use - 1) & 1, ctx, 103);
             if (!ok) break;
@@ -348,11 +421,7 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
             for (int ch = 0; ch < DCH; ++ch)
               tma_load_2d(smem + L::K_OFF + (stage * DCH + ch) * TILE_BYTES, map_rk, ch * 64, row,
                           &bars[K_FULL + stage]);
-          }
-          ok = fwait(f + 1, seq + 1, ctx, 104);
-          if (!ok) break;
-          fence_proxy_async_all();
-          if (nq > 0) {
+            laps.lap(1);
             if (use >= 1) ok = mwait(&bars[V_FREE + stage], (use - 1) & 1, ctx, 105);
             if (!ok) break;
             mbar_arrive_expect_tx(&bars[V_FULL + stage], DCH * TILE_BYTES);
@@ -360,32 +429,32 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
               tma_load_2d(smem + L::V_OFF + (stage * DCH + ch) * TILE_BYTES, map_rv, ch * 64, row,
                           &bars[V_FULL + stage]);
           }
-          // the previous tile has landed in shared memory by now: hand its ring slot back
+          laps.lap(3);
+          // the previous tile has landed in shared memory by now: hand its ring slot back.  The
+          // slot's data has been read (the copies are complete), so a relaxed add is enough.
           if (pend_slot >= 0) {
             ok = mwait(&bars[K_FULL + pend_stage], pend_phase, ctx, 106) &&
                  mwait(&bars[V_FULL + pend_stage], pend_phase, ctx, 107);
             if (!ok) break;
-            red_release_add(gflags + pend_slot * 4 + 2, 1);
-            red_release_add(gflags + pend_slot * 4 + 3, 1);
+            laps.lap(4);
+            red_relaxed_add(gflags + GF_DONE + pend_slot, 1);
             pend_slot = -1;
+            laps.lap(5);
           }
           if (nq > 0) {
             pend_slot = slot; pend_stage = stage; pend_phase = use & 1;
             ++cseq;
           } else {   // nothing to load for this block of queries: the slot is not needed here
-            red_release_add(f + 2, 1);
-            red_release_add(f + 3, 1);
+            red_relaxed_add(gflags + GF_DONE + slot, 1);
           }
         }
       }
       if (ok && pend_slot >= 0) {
         ok = mwait(&bars[K_FULL + pend_stage], pend_phase, ctx, 106) &&
              mwait(&bars[V_FULL + pend_stage], pend_phase, ctx, 107);
-        if (ok) {
-          red_release_add(gflags + pend_slot * 4 + 2, 1);
-          red_release_add(gflags + pend_slot * 4 + 3, 1);
-        }
+        if (ok) red_relaxed_add(gflags + GF_DONE + pend_slot, 1);
       }
+      laps.flush();
       if (!ok) {  // let copies already in flight land before the CTA goes away
         const long long start = clock64();
         while (clock64() - start < (1ll << 21)) {}
@@ -427,6 +496,8 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
     bool ok = true;
     int cseq = 0, ucount = 0;
     int ctile[NQ] = {0, 0}, cunit[NQ] = {0, 0};   // tiles / units each query tile's chain has done
+    Laps laps;
+    laps.start(p.prof + 8, p.prof != nullptr && g == 0 && c == 0 && leader);
     for (int u = g; u < p.units && ok; u += p.groups) {
       const Unit un = unit_of(p, u);
       int q0;
@@ -447,21 +518,26 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
         const int nstage = (cur + 1) % KVS;
         for (int i = 0; i < nq && ok; ++i) {
           const int ci = ctile[i] + t;
+          laps.lap(7);
           ok = mwait_all(&bars[P_READY + i], ci & 1, ctx, 210 + i);
+          laps.lap(i);
           if (ok && i == 0) ok = mwait_all(&bars[V_FULL + stage], phase, ctx, 212);
+          laps.lap(2);
           // the first PV of a unit overwrites O: the previous unit's rows must have been read out
           if (ok && t == 0 && cunit[i] > 0) ok = mwait_all(&bars[O_FREE + i], (cunit[i] - 1) & 1, ctx, 214 + i);
           if (!ok) break;
           tc_fence_after();
           issue_pv(i, stage, t > 0);
           if (i == nq - 1 && leader) mma_commit(&bars[V_FREE + stage]);
+          laps.lap(3);
           if (t + 1 < un.nt) {
+            // S of the next tile overwrites P of this one.  It is issued right behind the PV that
+            // reads P: the tensor core executes the MMAs of one issuing thread in order
             if (i == 0) ok = mwait_all(&bars[K_FULL + nstage], ((cur + 1) / KVS) & 1, ctx, 216);
-            // S of the next tile overwrites P of this one: PV must have finished reading it
-            if (ok) ok = mwait_all(&bars[PV_DONE + i], ci & 1, ctx, 218 + i);
             if (!ok) break;
-            tc_fence_after();
+            laps.lap(4);
             issue_s(i, nstage);
+            laps.lap(5);
             if (i == nq - 1 && leader) mma_commit(&bars[K_FREE + nstage]);
           }
         }
@@ -472,6 +548,7 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
       ++ucount;
       for (int i = 0; i < nq; ++i) { ctile[i] += un.nt; ++cunit[i]; }
     }
+    laps.flush();
     __syncwarp();
   } else if (warp < COMPUTE_WARPS) {
     // ------------------------------------------------------------ softmax: one thread per query row
@@ -481,6 +558,8 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
     bool ok = true;
     int ci = 0;
     int u = g;
+    Laps laps;
+    laps.start(p.prof + 16, p.prof != nullptr && g == 0 && c == 0 && tid == 0);
     for (; u < p.units && ok; u += p.groups) {
       const Unit un = unit_of(p, u);
       int q0;
@@ -489,44 +568,22 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
       float m_used = -INFINITY, l_run = 0.f;
       for (int t = 0; t < un.nt && ok; ++t, ++ci) {
         const int valid = min(TOK, p.N - (un.tile0 + t) * TOK);
+        laps.lap(2);
         ok = mwait_all(&bars[S_FULL + wg], ci & 1, ctx, 300 + wg);
         if (!ok) break;
         tc_fence_after();
-        // S of this tile was issued after PV of the previous one completed, so O is up to date here
+        laps.lap(0);
+        // S of this tile was issued behind PV of the previous one and its commit covers both, so O is
+        // up to date here
         const uint32_t s_addr = tmem_base + lane_sel + wg * 128;
-        float mx = -INFINITY;
-        {
-          uint32_t raw[2][32];
-          tmem_ld32_issue(s_addr, raw[0]);
-#pragma unroll
-          for (int cc = 0; cc < TOK / 32; ++cc) {
-            uint32_t (&cur)[32] = raw[cc & 1];
-            tmem_ld32_wait(cur);
-            if (cc + 1 < TOK / 32) tmem_ld32_issue(s_addr + (cc + 1) * 32, raw[(cc + 1) & 1]);
-            if (valid == TOK) {   // four chains instead of one
-              float ma = -INFINITY, mb_ = -INFINITY, mc = -INFINITY, md = -INFINITY;
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                ma = fmaxf(ma, __uint_as_float(cur[j]));
-                mb_ = fmaxf(mb_, __uint_as_float(cur[j + 1]));
-                mc = fmaxf(mc, __uint_as_float(cur[j + 2]));
-                md = fmaxf(md, __uint_as_float(cur[j + 3]));
-              }
-              mx = fmaxf(mx, fmaxf(fmaxf(ma, mb_), fmaxf(mc, md)));
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (cc * 32 + j < valid) mx = fmaxf(mx, __uint_as_float(cur[j]));
-            }
-          }
-        }
-        const float m_new = mx * p.scale_log2;
-        const bool need = m_new > m_used + RESCALE_THRESHOLD;
-        if (__any_sync(0xffffffffu, need)) {
+        const uint32_t o_addr = tmem_base + lane_sel + 256 + wg * 128;
+        float sum = 0.f, sum_b = 0.f, sum_c = 0.f, sum_d = 0.f;   // four chains instead of one
+        // moves the reference point of the row: O, the running sum and whatever of this tile is
+        // already summed or stored as P (chunks [0, done)) are scaled by alpha = 2^(old - new)
+        auto move_reference = [&](float m_new, int done) {
           const float m_next = fmaxf(m_used, m_new);
           const float alpha = exp2f(m_used - m_next);   // 0 on the first tile (m_used = -inf)
           if (t > 0) {
-            const uint32_t o_addr = tmem_base + lane_sel + 256 + wg * 128;
 #pragma unroll 1
             for (int cc = 0; cc < D / 32; ++cc) {
               float v[32];
@@ -536,44 +593,96 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
               tmem_st32(o_addr + cc * 32, v);
             }
           }
-          l_run *= alpha;
-          m_used = m_next;
-        }
-        // P (bf16 pairs) replaces S in place: the 16 cells written per step lie below the 32 read.
-        // The load of the next 32 scores stays in flight under the exponentials of the current ones.
-        float sum = 0.f, sum_b = 0.f, sum_c = 0.f, sum_d = 0.f;   // four chains instead of one
-        uint32_t raw[2][32];
-        tmem_ld32_issue(s_addr, raw[0]);
+#pragma unroll 1
+          for (int cc = 0; cc < done; ++cc) {   // P chunks already written: 16 cells of bf16 pairs each
+            float v[32];
+            tmem_ld32(s_addr + cc * 16 - (cc & 1) * 16, v);   // aligned 32-cell read around the chunk
+            // (only this chunk's 16 cells are rewritten; the other half belongs to its neighbour)
+            uint32_t cells[16];
 #pragma unroll
-        for (int cc = 0; cc < TOK / 32; ++cc) {
-          uint32_t (&cur)[32] = raw[cc & 1];
-          tmem_ld32_wait(cur);
-          if (cc + 1 < TOK / 32) tmem_ld32_issue(s_addr + (cc + 1) * 32, raw[(cc + 1) & 1]);
-          uint32_t packed[16];
-          if (valid == TOK) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              const float p0 = exp2_approx(fmaf(__uint_as_float(cur[j]), p.scale_log2, -m_used));
-              const float p1 = exp2_approx(fmaf(__uint_as_float(cur[j + 1]), p.scale_log2, -m_used));
-              const float p2 = exp2_approx(fmaf(__uint_as_float(cur[j + 2]), p.scale_log2, -m_used));
-              const float p3 = exp2_approx(fmaf(__uint_as_float(cur[j + 3]), p.scale_log2, -m_used));
-              sum += p0; sum_b += p1; sum_c += p2; sum_d += p3;
-              packed[j >> 1] = pack_bf16x2(p0, p1);
-              packed[(j >> 1) + 1] = pack_bf16x2(p2, p3);
+            for (int j = 0; j < 16; ++j) {
+              const uint32_t w = __float_as_uint((cc & 1) ? v[16 + j] : v[j]);
+              cells[j] = pack_bf16x2(__uint_as_float(w << 16) * alpha, __uint_as_float(w & 0xFFFF0000u) * alpha);
             }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              float p0 = (cc * 32 + j < valid) ? exp2f(fmaf(__uint_as_float(cur[j]), p.scale_log2, -m_used)) : 0.f;
-              float p1 = (cc * 32 + j + 1 < valid) ? exp2f(fmaf(__uint_as_float(cur[j + 1]), p.scale_log2, -m_used)) : 0.f;
-              sum += p0 + p1;
-              packed[j >> 1] = pack_bf16x2(p0, p1);
-            }
+            tmem_st16(s_addr + cc * 16, cells);
+            tmem_wait_st();
           }
-          tmem_st16(s_addr + cc * 16, packed);
+          l_run *= alpha;
+          sum *= alpha; sum_b *= alpha; sum_c *= alpha; sum_d *= alpha;
+          m_used = m_next;
+        };
+        if (t == 0 || valid != TOK) {
+          // first tile of a unit (no reference point yet) and the ragged last tile: row maximum first
+          float mx = -INFINITY;
+          uint32_t raw[2][32];
+          tmem_ld32_issue(s_addr, raw[0]);
+#pragma unroll
+          for (int cc = 0; cc < TOK / 32; ++cc) {
+            uint32_t (&cur)[32] = raw[cc & 1];
+            tmem_ld32_wait(cur);
+            if (cc + 1 < TOK / 32) tmem_ld32_issue(s_addr + (cc + 1) * 32, raw[(cc + 1) & 1]);
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (cc * 32 + j < valid) mx = fmaxf(mx, __uint_as_float(cur[j]));
+          }
+          const float m_new = mx * p.scale_log2;
+          if (__any_sync(0xffffffffu, m_new > m_used + RESCALE_THRESHOLD)) move_reference(m_new, 0);
+        }
+        // One pass over the scores: exponentials against the current reference point (lazy
+        // rescaling: it only moves when a score exceeds it by more than the threshold, so P stays
+        // below 2^threshold), P (bf16 pairs) replaces S in place -- the 16 cells written per step lie
+        // below the 32 read -- and the load of the next 32 scores stays in flight under the
+        // exponentials of the current ones.
+        {
+          uint32_t raw[2][32];
+          tmem_ld32_issue(s_addr, raw[0]);
+#pragma unroll
+          for (int cc = 0; cc < TOK / 32; ++cc) {
+            uint32_t (&cur)[32] = raw[cc & 1];
+            tmem_ld32_wait(cur);
+            if (cc + 1 < TOK / 32) tmem_ld32_issue(s_addr + (cc + 1) * 32, raw[(cc + 1) & 1]);
+            uint32_t packed[16];
+            if (valid == TOK) {
+              if (t > 0) {   // does a score of this chunk leave the window of the reference point?
+                float ma = -INFINITY, mb_ = -INFINITY, mc = -INFINITY, md = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                  ma = fmaxf(ma, __uint_as_float(cur[j]));
+                  mb_ = fmaxf(mb_, __uint_as_float(cur[j + 1]));
+                  mc = fmaxf(mc, __uint_as_float(cur[j + 2]));
+                  md = fmaxf(md, __uint_as_float(cur[j + 3]));
+                }
+                const float m_new = fmaxf(fmaxf(ma, mb_), fmaxf(mc, md)) * p.scale_log2;
+                if (__any_sync(0xffffffffu, m_new > m_used + RESCALE_THRESHOLD)) {
+                  if (cc + 1 < TOK / 32) tmem_ld32_wait(raw[(cc + 1) & 1]);   // no load in flight in there
+                  move_reference(m_new, cc);
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                const float p0 = exp2_approx(fmaf(__uint_as_float(cur[j]), p.scale_log2, -m_used));
+                const float p1 = exp2_approx(fmaf(__uint_as_float(cur[j + 1]), p.scale_log2, -m_used));
+                const float p2 = exp2_approx(fmaf(__uint_as_float(cur[j + 2]), p.scale_log2, -m_used));
+                const float p3 = exp2_approx(fmaf(__uint_as_float(cur[j + 3]), p.scale_log2, -m_used));
+                sum += p0; sum_b += p1; sum_c += p2; sum_d += p3;
+                packed[j >> 1] = pack_bf16x2(p0, p1);
+                packed[(j >> 1) + 1] = pack_bf16x2(p2, p3);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                float p0 = (cc * 32 + j < valid) ? exp2f(fmaf(__uint_as_float(cur[j]), p.scale_log2, -m_used)) : 0.f;
+                float p1 = (cc * 32 + j + 1 < valid) ? exp2f(fmaf(__uint_as_float(cur[j + 1]), p.scale_log2, -m_used)) : 0.f;
+                sum += p0 + p1;
+                packed[j >> 1] = pack_bf16x2(p0, p1);
+              }
+            }
+            tmem_st16(s_addr + cc * 16, packed);
+          }
         }
         tmem_wait_st();
         l_run += (sum + sum_b) + (sum_c + sum_d);
+        laps.lap(1);
         tc_fence_before();
         warp_arrive(&bars[P_READY + wg], lane);
       }
@@ -608,7 +717,9 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
             l_run > 0.f ? (m_used + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
       tc_fence_before();
       warp_arrive(&bars[O_FREE + wg], lane);
+      laps.lap(3);
     }
+    laps.flush();
     // a launch that gave up must not hand back rows that look like results: the unit it stopped in
     // and every later one get NaN in their LSE
     if (!ok) {
@@ -639,7 +750,7 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
   const int nchunks = p.nchunks, npairs = p.npairs, ng = p.ngroups, nw = p.nw;
   const bool resident = npairs <= nw;      // the head's decoder rows stay in shared memory for a whole unit
   const int ring_off = L::ring_off(npairs);
-  int32_t* gflags = p.flags + F_SLOTS + g * R * 4;
+  int32_t* gflags = p.flags + F_GROUPS + g * GF;
   int* crow = reinterpret_cast<int*>(smem + M_CROW);                                        // [2 buf][128]
   uint16_t* scales = reinterpret_cast<uint16_t*>(smem + L::scales_off(npairs, nw));         // [2 buf][128][ng]
   uint16_t* ring = tensor ? p.ring_v : p.ring_k;
@@ -656,8 +767,8 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
         bool first = true;
         for (int t = 0; t < un.nt && ok; ++t, ++seq) {
           if (seq % PH != mine) continue;
-          // the tile's codes: issued as soon as the previous job's codes are expanded (and its centre
-          // staging, which lives in the same buffer, has been read back)
+          // the tile's codes: issued as soon as the previous job's codes are expanded, so that they
+          // land during that job's epilogue
           if (jobs > 0) ok = mwait(&bars[CODES_FREE], (jobs - 1) & 1, ctx, 401);
           if (!ok) break;
           mbar_arrive_expect_tx(&bars[CODES_FULL], npairs * CODE_BLOCK);
@@ -743,29 +854,65 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
     }
     __syncwarp();
   } else if (warp == 10) {
-    // ------------------------------------------- per-token metadata, up to two jobs ahead
+    // ------------------------------------------- everything that waits on global memory, off the
+    // compute warps' path: per-token metadata two jobs ahead, the ring slot's release by the
+    // consumers (META_FULL also says "the slot is free"), and the publication of finished tiles
     bool ok = true;
     int seq = 0, jobs = 0;
+    // Tile of job j: its stores happen before this release by the OUT_DONE barrier, and a release
+    // is cumulative, so a consumer that sees the counter sees the tile.
+    auto publish = [&](int j) {
+      const bool done = mwait_all(&bars[OUT_DONE + (j & 1)], (j >> 1) & 1, ctx, 505);
+      if (done && lane == 0) st_release(gflags + pidx, j + 1);
+      return done;
+    };
     for (int u = g; u < p.units && ok; u += p.groups) {
       const Unit un = unit_of(p, u);
       for (int t = 0; t < un.nt && ok; ++t, ++seq) {
         if (seq % PH != mine) continue;
         const int b = jobs & 1, use = jobs >> 1;
-        if (use >= 1) ok = mwait_all(&bars[META_FREE + b], (use - 1) & 1, ctx, 420 + b);
-        if (!ok) break;
+        // the job's metadata is fetched into registers while job jobs - 2 is still running
         const int t0 = (un.tile0 + t) * TOK;
-        for (int r = lane; r < TOK; r += 32) {
-          const int tok = t0 + r;
+        int crow_reg[TOK / 32];
+        uint16_t scale_reg[TOK / 32];
+#pragma unroll
+        for (int k = 0; k < TOK / 32; ++k) {
+          const int tok = t0 + lane + 32 * k;
           const bool in = tok < p.N;
-          crow[b * TOK + r] = in ? center_row_of(hist, tok) : 0;
-          const uint16_t* src = static_cast<const uint16_t*>(hist.scales) + static_cast<size_t>(tok) * ng;
-          uint16_t* dst = scales + static_cast<size_t>(b * TOK + r) * ng;
-          for (int gi = 0; gi < ng; ++gi) dst[gi] = in ? src[gi] : 0;
+          crow_reg[k] = in ? center_row_of(hist, tok) : 0;
+          scale_reg[k] = (in && ng == 1) ? __ldg(static_cast<const uint16_t*>(hist.scales) + tok) : uint16_t(0);
+        }
+        if (use >= 1) {   // job jobs - 2 is finished: its metadata buffer is free, its tile is stored
+          ok = mwait_all(&bars[META_FREE + b], (use - 1) & 1, ctx, 420 + b);
+          ok = ok && publish(jobs - 2);
+        }
+        if (!ok) break;
+        {   // every consumer of the group must have taken the previous tiles of this job's ring slot
+          int okf = 1;
+          if (lane == 0) okf = fwait(gflags + GF_DONE + seq % R, p.cons * (seq / R), ctx, 504) ? 1 : 0;
+          ok = __shfl_sync(0xffffffffu, okf, 0) != 0;
+        }
+        if (!ok) break;
+#pragma unroll
+        for (int k = 0; k < TOK / 32; ++k) {
+          const int r = lane + 32 * k;
+          crow[b * TOK + r] = crow_reg[k];
+          if (ng == 1) scales[b * TOK + r] = scale_reg[k];
+        }
+        if (ng > 1) {
+          for (int r = lane; r < TOK; r += 32) {
+            const int tok = t0 + r;
+            const bool in = tok < p.N;
+            const uint16_t* src = static_cast<const uint16_t*>(hist.scales) + static_cast<size_t>(tok) * ng;
+            uint16_t* dst = scales + static_cast<size_t>(b * TOK + r) * ng;
+            for (int gi = 0; gi < ng; ++gi) dst[gi] = in ? src[gi] : 0;
+          }
         }
         warp_arrive(&bars[META_FULL + b], lane);
         ++jobs;
       }
     }
+    for (int j = jobs >= 2 ? jobs - 2 : 0; j < jobs && ok; ++j) ok = publish(j);
   } else {
     // ------------------------------------------------------------ compute warps: expand, epilogue
     const int wg = tid >> 7;                    // which half of the columns (of a chunk / of the tile)
@@ -774,6 +921,8 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
     const nkv_camera& cam = tensor ? p.cam_v : p.cam_k;
     bool ok = true;
     int seq = 0, jobs = 0, gp = 0;
+    Laps laps;
+    laps.start(p.prof + 24, p.prof != nullptr && g == 0 && pidx == 0 && tid == 0);
     for (int u = g; u < p.units && ok; u += p.groups) {
       const Unit un = unit_of(p, u);
       const int head = un.head;
@@ -782,9 +931,12 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
         const int t0 = (un.tile0 + t) * TOK;
         const int valid = min(TOK, p.N - t0);
         const int mb = jobs & 1;
+        laps.lap(7);
         ok = mwait_all(&bars[META_FULL + mb], (jobs >> 1) & 1, ctx, 500);
+        laps.lap(6);
         ok = ok && mwait_all(&bars[CODES_FULL], jobs & 1, ctx, 501);
         if (!ok) break;
+        laps.lap(0);
         // ---- expand the tile's codes to bf16 latent chunks in tensor memory (A of the decode MMA)
         // this thread's 16 bytes of chunk j of pair pi: 16-byte unit 2 j + wg of row `row`, swizzled
         const uint8_t* codes = smem + L::CODES_OFF + row * 64;
@@ -852,11 +1004,15 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
         if (p.w_perm && p.scale_dtype == NKV_BF16 && ng == 1) expand_pairs(std::true_type{});
         else expand_pairs(std::false_type{});
         if (!ok) break;
+        laps.lap(1);
+        fence_proxy_async();   // the codes were read; TMA may overwrite them
+        warp_arrive(&bars[CODES_FREE], lane);
+        const int slot = seq % R;   // free: the metadata warp has checked that before META_FULL
         // ---- epilogue: bias, centre, two bf16 roundings, positional restore; D / 2 columns per thread
         // in rounds of 32
         const bool in = row < valid;
         constexpr int ROUNDS = D / 64;
-        uint32_t outp[ROUNDS][16];
+        uint16_t* const slot_rows = ring + static_cast<size_t>(g * R + slot) * TOK * D;
         {
           // positional restore (K tiles only): this token's frame / row / column
           const bool rotate = ROPE && tensor == 0 && p.rope.cos_sin != nullptr;
@@ -884,25 +1040,34 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
                         static_cast<size_t>(min((t0 + row) / cam.tokens_per_frame, cam.frames - 1)) * 64;
           const float* bias_head = (tensor ? p.bias_v : p.bias_k) + head * D;
           // accumulator complete: the tile's last pair is pair gp - 1
+          // Centre rows of this warp's 32 tokens (32 columns = 64 bytes per round), gathered
+          // cooperatively: 4 lanes read one row's 16-byte pieces, so a load instruction touches
+          // 8 lines instead of 32; the rows are redistributed through a swizzled staging area.
+          // All rounds are requested here, ahead of the accumulator wait.
+          constexpr int PIECES = 4, RPI = 8;
+          uint4 cen_all[ROUNDS][PIECES];
+          {
+            const int wrow0 = 32 * (warp & 3);
+#pragma unroll
+            for (int sub = 0; sub < ROUNDS; ++sub) {
+              const uint16_t* cbase = static_cast<const uint16_t*>(hist.centers) +
+                                      static_cast<size_t>(head) * D + wg * (D / 2) + sub * 32;
+#pragma unroll
+              for (int i = 0; i < PIECES; ++i) {
+                const int rloc = i * RPI + lane / PIECES, piece = lane % PIECES;
+                const int crow_i = crow[mb * TOK + wrow0 + rloc];
+                cen_all[sub][i] = __ldg(reinterpret_cast<const uint4*>(
+                    cbase + static_cast<size_t>(crow_i) * hist.center_width + piece * 8));
+              }
+            }
+          }
           bool waited = false;
 #pragma unroll
           for (int sub = 0; sub < ROUNDS; ++sub) {
             const int col0 = wg * (D / 2) + sub * 32;   // this thread's columns col0 .. col0 + 32
-            // Centre rows of this warp's 32 tokens (32 columns = 64 bytes each), gathered
-            // cooperatively: 4 lanes read one row's 16-byte pieces, so a load instruction touches
-            // 8 lines instead of 32; the rows are redistributed through a swizzled staging area.
-            constexpr int PIECES = 4, RPI = 8;
-            const int wrow0 = 32 * (warp & 3);
-            const uint16_t* cbase = static_cast<const uint16_t*>(hist.centers) +
-                                    static_cast<size_t>(head) * D + col0;
             uint4 cen[PIECES];
 #pragma unroll
-            for (int i = 0; i < PIECES; ++i) {
-              const int rloc = i * RPI + lane / PIECES, piece = lane % PIECES;
-              const int crow_i = crow[mb * TOK + wrow0 + rloc];
-              cen[i] = __ldg(reinterpret_cast<const uint4*>(
-                  cbase + static_cast<size_t>(crow_i) * hist.center_width + piece * 8));
-            }
+            for (int i = 0; i < PIECES; ++i) cen[i] = cen_all[sub][i];
             // rotation entries of this thread's 16 pairs, requested before the accumulator wait
             float2 rot[16];
             if (ROPE) {
@@ -928,12 +1093,13 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
               ok = mwait_all(&bars[PAIR_DONE + ((gp - 1) & (NDONE - 1))], ((gp - 1) / NDONE) & 1, ctx, 503);
               waited = true;
               tc_fence_after();
+              laps.lap(2);
             }
             // the accumulator read stays in flight under the centre staging
             uint32_t acc_raw[32];
             tmem_ld32_issue(tmem_base + lane_sel + col0, acc_raw);
             {
-              uint8_t* stage = smem + L::CODES_OFF + warp * (32 * PIECES * 16);
+              uint8_t* stage = smem + L::scratch_off(npairs) + warp * (32 * PIECES * 16);
 #pragma unroll
               for (int i = 0; i < PIECES; ++i) {
                 const int rloc = i * RPI + lane / PIECES, piece = lane % PIECES;
@@ -951,7 +1117,7 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
             float v[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc_raw[i]);
-            uint32_t* packed = outp[sub];
+            uint32_t packed[16];
 #pragma unroll
             for (int j4 = 0; j4 < 4; ++j4) {
               const uint32_t cwords[4] = {cen[j4].x, cen[j4].y, cen[j4].z, cen[j4].w};
@@ -1007,44 +1173,41 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
                 }
               }
             }
+            // Into the ring through the warp's staging area, so that a store instruction writes whole
+            // 64-byte row pieces (4 lanes per row, 8 rows) instead of 16 bytes of 32 different rows.
+            {
+              uint8_t* stage = smem + L::scratch_off(npairs) + warp * (32 * PIECES * 16);
+#pragma unroll
+              for (int j = 0; j < PIECES; ++j)
+                *reinterpret_cast<uint4*>(stage + lane * (PIECES * 16) + ((j ^ (lane & (PIECES - 1))) << 4)) =
+                    make_uint4(packed[j * 4], packed[j * 4 + 1], packed[j * 4 + 2], packed[j * 4 + 3]);
+              __syncwarp();
+              const int wrow0 = 32 * (warp & 3);
+#pragma unroll
+              for (int i = 0; i < PIECES; ++i) {
+                const int rloc = i * RPI + lane / PIECES, piece = lane % PIECES;
+                const uint4 v4 = *reinterpret_cast<const uint4*>(stage + rloc * (PIECES * 16) +
+                                                                 ((piece ^ (rloc & (PIECES - 1))) << 4));
+                *reinterpret_cast<uint4*>(slot_rows + static_cast<size_t>(wrow0 + rloc) * D + col0 + piece * 8) = v4;
+              }
+              __syncwarp();
+            }
           }
         }
         if (!ok) break;
-        // the centre staging lived in the code buffer: only now may the next job's codes overwrite it;
+        laps.lap(3);
         // the accumulator has been read, the metadata buffer is free
-        fence_proxy_async();
-        warp_arrive(&bars[CODES_FREE], lane);
         warp_arrive(&bars[META_FREE + mb], lane);
         tc_fence_before();
-        // ---- publish: wait until every consumer of the group has taken the slot's previous tile
-        const int slot = seq % R, use = seq / R;
-        int32_t* f = gflags + slot * 4;
-        {
-          int okf = 1;
-          if (lane == 0) okf = fwait(f + 2 + tensor, p.cons * use, ctx, 504) ? 1 : 0;
-          ok = __shfl_sync(0xffffffffu, okf, 0) != 0;
-        }
-        if (!ok) break;
-        {
-          uint16_t* dst = ring + (static_cast<size_t>(g * R + slot) * TOK + row) * D + wg * (D / 2);
-#pragma unroll
-          for (int sub = 0; sub < ROUNDS; ++sub)
-#pragma unroll
-            for (int j4 = 0; j4 < 4; ++j4)
-              *reinterpret_cast<uint4*>(dst + sub * 32 + j4 * 8) =
-                  make_uint4(outp[sub][j4 * 4], outp[sub][j4 * 4 + 1], outp[sub][j4 * 4 + 2], outp[sub][j4 * 4 + 3]);
-        }
-        __threadfence();
-        fence_proxy_async_all();   // the consumers read the tile with TMA
-        warp_arrive(&bars[OUT_DONE], lane);
-        if (tid == 0) {
-          ok = mwait(&bars[OUT_DONE], jobs & 1, ctx, 505);
-          if (ok) st_release(f + tensor, seq + 1);
-        }
-        if (warp == 0) ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        // ---- the metadata warp publishes the tile once every warp has stored its part
+        // (the consumers read the tile with TMA; the fence between the two proxies is on their side,
+        // behind the acquire that shows them the tile)
+        warp_arrive(&bars[OUT_DONE + (jobs & 1)], lane);
+        laps.lap(5);
         ++jobs;
       }
     }
+    laps.flush();
   }
 }
 
@@ -1087,7 +1250,8 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
     for (int s = 0; s < NSTAGE; ++s) mbar_init(&bars[LAT_FULL + s], COMPUTE_WARPS);   // latent pair staged in TMEM
     mbar_init(&bars[CODES_FULL], 1);                 // the tile's codes landed
     mbar_init(&bars[CODES_FREE], COMPUTE_WARPS);     // every warp is done with codes and centre staging
-    mbar_init(&bars[OUT_DONE], COMPUTE_WARPS);       // every warp's part of the tile is in the ring
+    for (int s = 0; s < 2; ++s)
+      mbar_init(&bars[OUT_DONE + s], COMPUTE_WARPS);   // every warp's part of the tile is in the ring
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -1177,6 +1341,10 @@ int device_state(DeviceState** out) {
   return NKV_OK;
 }
 
+#ifdef NKV_DEV
+long long* g_profile = nullptr;
+#endif
+
 int tuning(const char* name, int fallback) {
 #ifdef NKV_DEV
   const char* env = getenv(name);
@@ -1205,7 +1373,7 @@ int launch(const CUtensorMap maps[7], Params& p, DeviceState& dev, cudaStream_t 
   NKV_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(smem)));
   // the flag words start every launch at zero
-  NKV_CUDA(cudaMemsetAsync(p.flags, 0, static_cast<size_t>(F_SLOTS + p.groups * p.ring * 4) * 4, stream));
+  NKV_CUDA(cudaMemsetAsync(p.flags, 0, static_cast<size_t>(F_GROUPS + p.groups * GF) * 4, stream));
   cudaLaunchConfig_t config{};
   config.gridDim = dim3(p.groups * (p.cons + p.prod));
   config.blockDim = dim3(THREADS);
@@ -1244,14 +1412,18 @@ Plan make_plan(int sms, int Q, int heads, int tiles, int rank, int dk, int max_s
   int prod = rank >= 256 ? 4 : 2;
   prod = tuning("NKV_ATTN_PROD", prod);
   if (prod < 2) prod = 2;
+  if (prod > MAX_PROD) prod = MAX_PROD;
   prod &= ~1;
   const int qblocks = ceil_div(Q, NQ * QT);
   int cons = qblocks < sms - prod ? qblocks : sms - prod;
   const int qchunks = ceil_div(qblocks, cons);
   cons = ceil_div(qblocks, qchunks);
   const int ring_slots = static_cast<int>(RING_BYTES / (2u * TOK * dk * 2u));
+  // a group needs more ring slots than producers per tensor (a producer publishes its previous
+  // tile only when it prepares the next but one, so the consumers must be able to get that far)
+  const int min_ring = prod > 4 ? prod : 4;
   int wmax = sms / (cons + prod);
-  if (wmax > ring_slots / 4) wmax = ring_slots / 4;
+  if (wmax > ring_slots / min_ring) wmax = ring_slots / min_ring;
   if (wmax < 1) wmax = 1;
   const int forced = tuning("NKV_ATTN_SPLITS", 0);
   long long best_cost = -1;
@@ -1279,7 +1451,7 @@ Plan make_plan(int sms, int Q, int heads, int tiles, int rank, int dk, int max_s
   plan.ring = ring > MAX_RING ? MAX_RING : ring;
   plan.ring = tuning("NKV_ATTN_RING", plan.ring);
   if (plan.ring > ring) plan.ring = ring;
-  if (plan.ring < 2) plan.ring = 2;
+  if (plan.ring < min_ring) plan.ring = min_ring;
   return plan;
 }
 
@@ -1310,6 +1482,10 @@ int tc_prepare_decoder(const void* w_bf16, int64_t rows, int rank, void* out_bf1
   NKV_LAUNCH_CHECK("prepare_decoder_kernel");
   return NKV_OK;
 }
+
+#ifdef NKV_DEV
+extern "C" void nkv_dev_attn_profile(void* device_buckets) { g_profile = static_cast<long long*>(device_buckets); }
+#endif
 
 bool tc_attn_supported(int dk, int dv, int rank) {
   return dk == dv && (dk == 64 || dk == 128) && rank % 64 == 0 && rank > 0;
@@ -1428,6 +1604,9 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
   p.groups = plan.groups; p.cons = plan.cons; p.prod = plan.prod; p.ring = plan.ring;
   p.units = plan.qchunks * heads * plan.splits;
   p.wait_budget = 1ll << 31;   // about a second of SM cycles per wait
+#ifdef NKV_DEV
+  p.prof = g_profile;
+#endif
   // launches of the fused read share the ring: one that is enqueued on another stream than the
   // previous one waits for it
   if (dev->used && dev->last_stream != stream) NKV_CUDA(cudaStreamWaitEvent(stream, dev->last, 0));
