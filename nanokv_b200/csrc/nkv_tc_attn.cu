@@ -59,6 +59,8 @@ constexpr int KVS = 2;            // K / V stages of a consumer
 constexpr int META_BYTES = 3072;  // barriers, flags and per-token metadata at the head of shared memory
 constexpr int MAX_RING = 8;       // ring slots per group (GF - GF_DONE flag words)
 constexpr float RESCALE_THRESHOLD = 8.0f;
+constexpr float SCORE_WINDOW = 96.0f;   // log2 units a score may exceed the row's reference point by
+constexpr int STATUS_SCORE_RANGE = 950; // status word: a row's scores left that window (its LSE is NaN)
 
 enum Bar {
   // consumer
@@ -321,6 +323,12 @@ struct Laps {
 };
 #endif
 
+__device__ __forceinline__ uint32_t bf16x2_max(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 m = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a),
+                                   *reinterpret_cast<const __nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&m);
+}
+
 template <int D>
 struct Layout {
   static constexpr int DCH = D / 64;                      // 64-column tiles of a head row
@@ -565,7 +573,8 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
       int q0;
       const int nq = queries_of(un, q0);
       if (wg >= nq) continue;
-      float m_used = -INFINITY, l_run = 0.f;
+      float m_used = -INFINITY, l_run = 0.f, m_seen = -INFINITY;
+      bool saturated = false;
       for (int t = 0; t < un.nt && ok; ++t, ++ci) {
         const int valid = min(TOK, p.N - (un.tile0 + t) * TOK);
         laps.lap(2);
@@ -577,10 +586,8 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
         // up to date here
         const uint32_t s_addr = tmem_base + lane_sel + wg * 128;
         const uint32_t o_addr = tmem_base + lane_sel + 256 + wg * 128;
-        float sum = 0.f, sum_b = 0.f, sum_c = 0.f, sum_d = 0.f;   // four chains instead of one
-        // moves the reference point of the row: O, the running sum and whatever of this tile is
-        // already summed or stored as P (chunks [0, done)) are scaled by alpha = 2^(old - new)
-        auto move_reference = [&](float m_new, int done) {
+        // moves the reference point of the row: O and the running sum are scaled by 2^(old - new)
+        auto move_reference = [&](float m_new) {
           const float m_next = fmaxf(m_used, m_new);
           const float alpha = exp2f(m_used - m_next);   // 0 on the first tile (m_used = -inf)
           if (t > 0) {
@@ -593,26 +600,15 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
               tmem_st32(o_addr + cc * 32, v);
             }
           }
-#pragma unroll 1
-          for (int cc = 0; cc < done; ++cc) {   // P chunks already written: 16 cells of bf16 pairs each
-            float v[32];
-            tmem_ld32(s_addr + cc * 16 - (cc & 1) * 16, v);   // aligned 32-cell read around the chunk
-            // (only this chunk's 16 cells are rewritten; the other half belongs to its neighbour)
-            uint32_t cells[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const uint32_t w = __float_as_uint((cc & 1) ? v[16 + j] : v[j]);
-              cells[j] = pack_bf16x2(__uint_as_float(w << 16) * alpha, __uint_as_float(w & 0xFFFF0000u) * alpha);
-            }
-            tmem_st16(s_addr + cc * 16, cells);
-            tmem_wait_st();
-          }
           l_run *= alpha;
-          sum *= alpha; sum_b *= alpha; sum_c *= alpha; sum_d *= alpha;
           m_used = m_next;
         };
+        // The reference point (the exponent every weight of the row is taken against) is exact on
+        // the first tile of a unit and on a ragged tile: row maximum first, then the weights.  On
+        // every other tile it moves BETWEEN tiles, by the maximum the previous tile saw, so that no
+        // exponential ever waits for a maximum; a tile's weights may then exceed 1 by the factor its
+        // scores exceed the reference, which fp32 sums and bf16 weights hold up to 2^SCORE_WINDOW.
         if (t == 0 || valid != TOK) {
-          // first tile of a unit (no reference point yet) and the ragged last tile: row maximum first
           float mx = -INFINITY;
           uint32_t raw[2][32];
           tmem_ld32_issue(s_addr, raw[0]);
@@ -625,14 +621,14 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
             for (int j = 0; j < 32; ++j)
               if (cc * 32 + j < valid) mx = fmaxf(mx, __uint_as_float(cur[j]));
           }
-          const float m_new = mx * p.scale_log2;
-          if (__any_sync(0xffffffffu, m_new > m_used + RESCALE_THRESHOLD)) move_reference(m_new, 0);
+          m_seen = fmaxf(m_seen, mx * p.scale_log2);
         }
-        // One pass over the scores: exponentials against the current reference point (lazy
-        // rescaling: it only moves when a score exceeds it by more than the threshold, so P stays
-        // below 2^threshold), P (bf16 pairs) replaces S in place -- the 16 cells written per step lie
-        // below the 32 read -- and the load of the next 32 scores stays in flight under the
+        if (__any_sync(0xffffffffu, m_seen > m_used + RESCALE_THRESHOLD)) move_reference(m_seen);
+        // One pass over the scores: P (bf16 pairs) replaces S in place -- the 16 cells written per
+        // step lie below the 32 read -- and the load of the next 32 scores stays in flight under the
         // exponentials of the current ones.
+        float sum = 0.f, sum_b = 0.f, sum_c = 0.f, sum_d = 0.f;   // four chains instead of one
+        uint32_t pmax_a = 0u, pmax_b = 0u;
         {
           uint32_t raw[2][32];
           tmem_ld32_issue(s_addr, raw[0]);
@@ -643,21 +639,6 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
             if (cc + 1 < TOK / 32) tmem_ld32_issue(s_addr + (cc + 1) * 32, raw[(cc + 1) & 1]);
             uint32_t packed[16];
             if (valid == TOK) {
-              if (t > 0) {   // does a score of this chunk leave the window of the reference point?
-                float ma = -INFINITY, mb_ = -INFINITY, mc = -INFINITY, md = -INFINITY;
-#pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                  ma = fmaxf(ma, __uint_as_float(cur[j]));
-                  mb_ = fmaxf(mb_, __uint_as_float(cur[j + 1]));
-                  mc = fmaxf(mc, __uint_as_float(cur[j + 2]));
-                  md = fmaxf(md, __uint_as_float(cur[j + 3]));
-                }
-                const float m_new = fmaxf(fmaxf(ma, mb_), fmaxf(mc, md)) * p.scale_log2;
-                if (__any_sync(0xffffffffu, m_new > m_used + RESCALE_THRESHOLD)) {
-                  if (cc + 1 < TOK / 32) tmem_ld32_wait(raw[(cc + 1) & 1]);   // no load in flight in there
-                  move_reference(m_new, cc);
-                }
-              }
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
                 const float p0 = exp2_approx(fmaf(__uint_as_float(cur[j]), p.scale_log2, -m_used));
@@ -667,6 +648,13 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
                 sum += p0; sum_b += p1; sum_c += p2; sum_d += p3;
                 packed[j >> 1] = pack_bf16x2(p0, p1);
                 packed[(j >> 1) + 1] = pack_bf16x2(p2, p3);
+              }
+              // the largest weight of the chunk, on the packed pairs (weights are positive, so the
+              // bf16 bit patterns order like the numbers): half an instruction per score
+#pragma unroll
+              for (int j = 0; j < 16; j += 2) {
+                pmax_a = bf16x2_max(pmax_a, packed[j]);
+                pmax_b = bf16x2_max(pmax_b, packed[j + 1]);
               }
             } else {
 #pragma unroll
@@ -679,6 +667,14 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
             }
             tmem_st16(s_addr + cc * 16, packed);
           }
+        }
+        if (valid == TOK) {
+          // largest weight 2^(score - reference) -> the largest score the tile saw (to 2^-8)
+          const uint32_t pm = bf16x2_max(pmax_a, pmax_b);
+          const float wmax = fmaxf(__uint_as_float(pm << 16), __uint_as_float(pm & 0xFFFF0000u));
+          m_seen = fmaxf(m_seen, m_used + log2f(wmax));
+          // a weight beyond the window has overflowed or lost its meaning: the row cannot be trusted
+          saturated = saturated || !(wmax < exp2f(SCORE_WINDOW));
         }
         tmem_wait_st();
         l_run += (sum + sum_b) + (sum_c + sum_d);
@@ -712,9 +708,12 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
           }
         }
       }
-      if (qrow < p.Q)
+      if (qrow < p.Q) {
         p.lse[split_rows + static_cast<size_t>(qrow) * p.heads + un.head] =
-            l_run > 0.f ? (m_used + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+            saturated ? __int_as_float(0x7fc00000)
+                      : (l_run > 0.f ? (m_used + log2f(l_run)) * 0.6931471805599453f : -INFINITY);
+        if (saturated && p.status) atomicCAS(p.status, 0, STATUS_SCORE_RANGE);
+      }
       tc_fence_before();
       warp_arrive(&bars[O_FREE + wg], lane);
       laps.lap(3);
