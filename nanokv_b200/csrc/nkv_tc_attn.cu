@@ -57,7 +57,8 @@ constexpr int NSTAGE = 4;         // latent staging slots in tensor memory
 constexpr int NDONE = 8;          // "MMAs of pair g are complete" barriers, indexed by g % 8
 constexpr int KVS = 2;            // K / V stages of a consumer
 constexpr int META_BYTES = 3072;  // barriers, flags and per-token metadata at the head of shared memory
-constexpr int MAX_RING = 8;       // ring slots per group (GF - GF_DONE flag words)
+constexpr int MAX_RING = 16;      // ring slots per group (GF - GF_DONE flag words)
+constexpr int NMETA = 4;          // metadata buffers of a producer (it prepares up to four jobs ahead)
 constexpr float RESCALE_THRESHOLD = 8.0f;
 constexpr float SCORE_WINDOW = 96.0f;   // log2 units a score may exceed the row's reference point by
 constexpr int STATUS_SCORE_RANGE = 950; // status word: a row's scores left that window (its LSE is NaN)
@@ -67,21 +68,21 @@ enum Bar {
   Q_FULL = 0, Q_FREE = 1, K_FULL = 2, K_FREE = 4, V_FULL = 6, V_FREE = 8, S_FULL = 10, P_READY = 12,
   PV_DONE = 14, O_FREE = 16,
   // producer
-  W_FULL = 18, PAIR_DONE = 26, LAT_FULL = 34, META_FULL = 38, META_FREE = 40, CODES_FULL = 42,
-  CODES_FREE = 43, OUT_DONE = 44, NUM_BARS = 46
+  W_FULL = 18, PAIR_DONE = 26, LAT_FULL = 34, META_FULL = 38, META_FREE = 42, CODES_FULL = 46,
+  CODES_FREE = 47, OUT_DONE = 48, NUM_BARS = 52
 };
 
 // meta block
 constexpr int M_SLOT = NUM_BARS * 8;              // TMEM base address
 constexpr int M_ABORT = M_SLOT + 4;
-constexpr int M_CROW = 512;                       // [2][128] centre row of every token of a tile
-static_assert(M_ABORT + 4 <= M_CROW && M_CROW + 2 * TOK * 4 <= META_BYTES, "meta block layout");
+constexpr int M_CROW = 512;                       // [NMETA][128] centre row of every token of a tile
+static_assert(M_ABORT + 4 <= M_CROW && M_CROW + NMETA * TOK * 4 <= META_BYTES, "meta block layout");
 
 // global flag words
 constexpr int F_ABORT = 0;        // launch-wide abort (wait-site code)
 constexpr int F_GROUPS = 32;      // then per group GF words:
-constexpr int GF = 16;            //   [0, 8): tiles published by producer p of the group (K producers first)
-constexpr int GF_DONE = 8;        //   [8, 16): per ring slot, consumers that have taken the slot's tiles
+constexpr int GF = 32;            //   [0, 8): tiles published by producer p of the group (K producers first)
+constexpr int GF_DONE = 8;        //   [8, 24): per ring slot, consumers that have taken the slot's tiles
 constexpr int MAX_PROD = 8;
 
 struct Params {
@@ -346,7 +347,7 @@ struct Layout {
   __host__ __device__ static int ring_off(int npairs) { return scratch_off(npairs) + SCRATCH_BYTES; }
   __host__ __device__ static int scales_off(int npairs, int nw) { return ring_off(npairs) + nw * SLOT_BYTES; }
   __host__ __device__ static int producer_bytes(int npairs, int nw, int ngroups) {
-    return scales_off(npairs, nw) + 2 * TOK * ngroups * 2;
+    return scales_off(npairs, nw) + NMETA * TOK * ngroups * 2;
   }
 };
 
@@ -750,8 +751,8 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
   const bool resident = npairs <= nw;      // the head's decoder rows stay in shared memory for a whole unit
   const int ring_off = L::ring_off(npairs);
   int32_t* gflags = p.flags + F_GROUPS + g * GF;
-  int* crow = reinterpret_cast<int*>(smem + M_CROW);                                        // [2 buf][128]
-  uint16_t* scales = reinterpret_cast<uint16_t*>(smem + L::scales_off(npairs, nw));         // [2 buf][128][ng]
+  int* crow = reinterpret_cast<int*>(smem + M_CROW);                                        // [NMETA buf][128]
+  uint16_t* scales = reinterpret_cast<uint16_t*>(smem + L::scales_off(npairs, nw));         // [NMETA buf][128][ng]
   uint16_t* ring = tensor ? p.ring_v : p.ring_k;
 
   if (warp == 8) {
@@ -814,12 +815,14 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
     const uint32_t idesc_dec = make_idesc_bf16(128, D);   // [128 tok] x [D columns]
     const uint32_t smem_base = smem_u32(smem);
     bool ok = true;
-    int seq = 0, gp = 0, wgen = 0;   // wgen: units whose rows this CTA has loaded (resident form)
+    int seq = 0, gp = 0, wgen = 0, jobs = 0;   // wgen: units whose rows this CTA has loaded (resident form)
     for (int u = g; u < p.units && ok; u += p.groups) {
       const Unit un = unit_of(p, u);
       bool first = true;
       for (int t = 0; t < un.nt && ok; ++t, ++seq) {
         if (seq % PH != mine) continue;
+        const uint32_t acc = tmem_base + (jobs & 1) * 128;   // two accumulators: the epilogue of a job runs
+        ++jobs;                                              // under the MMAs of the next one
         for (int pi = 0; pi < npairs && ok; ++pi, ++gp) {
           const int n = min(2, nchunks - 2 * pi);
           int slot;
@@ -839,10 +842,10 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
           for (int j = 0; j < n; ++j) {
             const uint64_t w_desc = make_smem_desc_sw128(smem_base + ring_off + slot * L::SLOT_BYTES + j * D * 128);
             const uint32_t lat = tmem_base + 256 + st * 64 + j * 32;   // chunk staged in TMEM
-            if (leader) mma_bf16_ts(tmem_base, lat, w_desc, idesc_dec, pi + j > 0);
-            if (leader) mma_bf16_ts(tmem_base, lat + 8, w_desc + 2, idesc_dec, true);
-            if (leader) mma_bf16_ts(tmem_base, lat + 16, w_desc + 4, idesc_dec, true);
-            if (leader) mma_bf16_ts(tmem_base, lat + 24, w_desc + 6, idesc_dec, true);
+            if (leader) mma_bf16_ts(acc, lat, w_desc, idesc_dec, pi + j > 0);
+            if (leader) mma_bf16_ts(acc, lat + 8, w_desc + 2, idesc_dec, true);
+            if (leader) mma_bf16_ts(acc, lat + 16, w_desc + 4, idesc_dec, true);
+            if (leader) mma_bf16_ts(acc, lat + 24, w_desc + 6, idesc_dec, true);
           }
           // frees the staging slot (and the decoder rows); on the last pair: accumulator done
           if (leader) mma_commit(&bars[PAIR_DONE + (gp & (NDONE - 1))]);
@@ -854,14 +857,15 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
     __syncwarp();
   } else if (warp == 10) {
     // ------------------------------------------- everything that waits on global memory, off the
-    // compute warps' path: per-token metadata two jobs ahead, the ring slot's release by the
+    // compute warps' path: per-token metadata up to four jobs ahead, the ring slot's release by the
     // consumers (META_FULL also says "the slot is free"), and the publication of finished tiles
     bool ok = true;
     int seq = 0, jobs = 0;
     // Tile of job j: its stores happen before this release by the OUT_DONE barrier, and a release
     // is cumulative, so a consumer that sees the counter sees the tile.
     auto publish = [&](int j) {
-      const bool done = mwait_all(&bars[OUT_DONE + (j & 1)], (j >> 1) & 1, ctx, 505);
+      // (job j + NMETA cannot start before job j is published, so the barrier never runs a phase ahead)
+      const bool done = mwait_all(&bars[OUT_DONE + j % NMETA], (j / NMETA) & 1, ctx, 505);
       if (done && lane == 0) st_release(gflags + pidx, j + 1);
       return done;
     };
@@ -869,8 +873,8 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
       const Unit un = unit_of(p, u);
       for (int t = 0; t < un.nt && ok; ++t, ++seq) {
         if (seq % PH != mine) continue;
-        const int b = jobs & 1, use = jobs >> 1;
-        // the job's metadata is fetched into registers while job jobs - 2 is still running
+        const int b = jobs % NMETA, use = jobs / NMETA;
+        // the job's metadata is fetched into registers while job jobs - NMETA is still running
         const int t0 = (un.tile0 + t) * TOK;
         int crow_reg[TOK / 32];
         uint16_t scale_reg[TOK / 32];
@@ -881,9 +885,9 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
           crow_reg[k] = in ? center_row_of(hist, tok) : 0;
           scale_reg[k] = (in && ng == 1) ? __ldg(static_cast<const uint16_t*>(hist.scales) + tok) : uint16_t(0);
         }
-        if (use >= 1) {   // job jobs - 2 is finished: its metadata buffer is free, its tile is stored
+        if (use >= 1) {   // job jobs - NMETA is finished: its metadata buffer is free, its tile is stored
           ok = mwait_all(&bars[META_FREE + b], (use - 1) & 1, ctx, 420 + b);
-          ok = ok && publish(jobs - 2);
+          ok = ok && publish(jobs - NMETA);
         }
         if (!ok) break;
         {   // every consumer of the group must have taken the previous tiles of this job's ring slot
@@ -911,7 +915,7 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
         ++jobs;
       }
     }
-    for (int j = jobs >= 2 ? jobs - 2 : 0; j < jobs && ok; ++j) ok = publish(j);
+    for (int j = jobs >= NMETA ? jobs - NMETA : 0; j < jobs && ok; ++j) ok = publish(j);
   } else {
     // ------------------------------------------------------------ compute warps: expand, epilogue
     const int wg = tid >> 7;                    // which half of the columns (of a chunk / of the tile)
@@ -922,19 +926,19 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
     int seq = 0, jobs = 0, gp = 0;
     Laps laps;
     laps.start(p.prof + 24, p.prof != nullptr && g == 0 && pidx == 0 && tid == 0);
-    for (int u = g; u < p.units && ok; u += p.groups) {
-      const Unit un = unit_of(p, u);
-      const int head = un.head;
-      for (int t = 0; t < un.nt && ok; ++t, ++seq) {
-        if (seq % PH != mine) continue;
-        const int t0 = (un.tile0 + t) * TOK;
-        const int valid = min(TOK, p.N - t0);
-        const int mb = jobs & 1;
+    // A job runs in two stages: the codes are expanded (and the MMAs started) right away, its
+    // epilogue follows after the NEXT job's expansion, so that the MMAs' tail, the accumulator read
+    // and the ring stores of one job hide under the expansion of the following one.
+    struct Job { int head, t0, valid, slot, num, last_pair; };
+    Job prev{};
+    bool have_prev = false;
+    auto expand = [&](const Job& job) {
+        const int mb = job.num % NMETA;
         laps.lap(7);
-        ok = mwait_all(&bars[META_FULL + mb], (jobs >> 1) & 1, ctx, 500);
+        ok = mwait_all(&bars[META_FULL + mb], (job.num / NMETA) & 1, ctx, 500);
         laps.lap(6);
-        ok = ok && mwait_all(&bars[CODES_FULL], jobs & 1, ctx, 501);
-        if (!ok) break;
+        ok = ok && mwait_all(&bars[CODES_FULL], job.num & 1, ctx, 501);
+        if (!ok) return;
         laps.lap(0);
         // ---- expand the tile's codes to bf16 latent chunks in tensor memory (A of the decode MMA)
         // this thread's 16 bytes of chunk j of pair pi: 16-byte unit 2 j + wg of row `row`, swizzled
@@ -1002,11 +1006,15 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
         };
         if (p.w_perm && p.scale_dtype == NKV_BF16 && ng == 1) expand_pairs(std::true_type{});
         else expand_pairs(std::false_type{});
-        if (!ok) break;
+        if (!ok) return;
         laps.lap(1);
         fence_proxy_async();   // the codes were read; TMA may overwrite them
         warp_arrive(&bars[CODES_FREE], lane);
-        const int slot = seq % R;   // free: the metadata warp has checked that before META_FULL
+    };
+    auto epilogue = [&](const Job& job) {
+        const int head = job.head, t0 = job.t0, valid = job.valid, mb = job.num % NMETA;
+        const int slot = job.slot;   // free: the metadata warp has checked that before META_FULL
+        const uint32_t acc = tmem_base + (job.num & 1) * 128;
         // ---- epilogue: bias, centre, two bf16 roundings, positional restore; D / 2 columns per thread
         // in rounds of 32
         const bool in = row < valid;
@@ -1089,14 +1097,14 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
               bias[j] = b4.x; bias[j + 1] = b4.y; bias[j + 2] = b4.z; bias[j + 3] = b4.w;
             }
             if (!waited) {
-              ok = mwait_all(&bars[PAIR_DONE + ((gp - 1) & (NDONE - 1))], ((gp - 1) / NDONE) & 1, ctx, 503);
+              ok = mwait_all(&bars[PAIR_DONE + (job.last_pair & (NDONE - 1))], (job.last_pair / NDONE) & 1, ctx, 503);
               waited = true;
               tc_fence_after();
               laps.lap(2);
             }
             // the accumulator read stays in flight under the centre staging
             uint32_t acc_raw[32];
-            tmem_ld32_issue(tmem_base + lane_sel + col0, acc_raw);
+            tmem_ld32_issue(acc + lane_sel + col0, acc_raw);
             {
               uint8_t* stage = smem + L::scratch_off(npairs) + warp * (32 * PIECES * 16);
 #pragma unroll
@@ -1193,7 +1201,7 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
             }
           }
         }
-        if (!ok) break;
+        if (!ok) return;
         laps.lap(3);
         // the accumulator has been read, the metadata buffer is free
         warp_arrive(&bars[META_FREE + mb], lane);
@@ -1201,11 +1209,27 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
         // ---- the metadata warp publishes the tile once every warp has stored its part
         // (the consumers read the tile with TMA; the fence between the two proxies is on their side,
         // behind the acquire that shows them the tile)
-        warp_arrive(&bars[OUT_DONE + (jobs & 1)], lane);
+        warp_arrive(&bars[OUT_DONE + job.num % NMETA], lane);
         laps.lap(5);
-        ++jobs;
+    };
+    for (int u = g; u < p.units && ok; u += p.groups) {
+      const Unit un = unit_of(p, u);
+      for (int t = 0; t < un.nt && ok; ++t, ++seq) {
+        if (seq % PH != mine) continue;
+        Job job;
+        job.head = un.head;
+        job.t0 = (un.tile0 + t) * TOK;
+        job.valid = min(TOK, p.N - job.t0);
+        job.slot = seq % R;
+        job.num = jobs++;
+        expand(job);
+        job.last_pair = gp - 1;
+        if (ok && have_prev) epilogue(prev);
+        prev = job;
+        have_prev = true;
       }
     }
+    if (ok && have_prev) epilogue(prev);
     laps.flush();
   }
 }
@@ -1241,6 +1265,8 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(&bars[P_READY + s], QT / 32);
       mbar_init(&bars[PV_DONE + s], 1);
       mbar_init(&bars[O_FREE + s], QT / 32);
+    }
+    for (int s = 0; s < NMETA; ++s) {
       mbar_init(&bars[META_FULL + s], 1);
       mbar_init(&bars[META_FREE + s], COMPUTE_WARPS);
     }
@@ -1249,7 +1275,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
     for (int s = 0; s < NSTAGE; ++s) mbar_init(&bars[LAT_FULL + s], COMPUTE_WARPS);   // latent pair staged in TMEM
     mbar_init(&bars[CODES_FULL], 1);                 // the tile's codes landed
     mbar_init(&bars[CODES_FREE], COMPUTE_WARPS);     // every warp is done with codes and centre staging
-    for (int s = 0; s < 2; ++s)
+    for (int s = 0; s < NMETA; ++s)
       mbar_init(&bars[OUT_DONE + s], COMPUTE_WARPS);   // every warp's part of the tile is in the ring
     *abort_flag = 0;
     fence_barrier_init();
@@ -1418,9 +1444,10 @@ Plan make_plan(int sms, int Q, int heads, int tiles, int rank, int dk, int max_s
   const int qchunks = ceil_div(qblocks, cons);
   cons = ceil_div(qblocks, qchunks);
   const int ring_slots = static_cast<int>(RING_BYTES / (2u * TOK * dk * 2u));
-  // a group needs more ring slots than producers per tensor (a producer publishes its previous
-  // tile only when it prepares the next but one, so the consumers must be able to get that far)
-  const int min_ring = prod > 4 ? prod : 4;
+  // A producer prepares its jobs up to NMETA ahead and checks the ring slot of a job at that
+  // point, with up to NMETA - 1 of its own earlier tiles not yet published; the slot's previous
+  // tile must be older than those, which takes more than (NMETA - 1) * prod / 2 slots.
+  const int min_ring = (NMETA - 1) * (prod / 2) + 1 > 4 ? (NMETA - 1) * (prod / 2) + 1 : 4;
   int wmax = sms / (cons + prod);
   if (wmax > ring_slots / min_ring) wmax = ring_slots / min_ring;
   if (wmax < 1) wmax = 1;
