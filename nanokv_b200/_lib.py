@@ -134,3 +134,22 @@ def check(status: int) -> None:
     detail = lib.nkv_last_error().decode()
     kind = lib.nkv_status_string(status).decode()
     raise _EXCEPTIONS.get(status, RuntimeError)(f"nanokv_b200: {kind}: {detail}")
+
+
+STATUS_SCORE_RANGE = 950
+
+
+def check_device_status(word: int) -> None:
+    """Raise for a non-zero status word that a kernel left behind.
+
+    The fused read writes the site code of a bounded wait that gave up (its rows are then not
+    results: their LSE is NaN), or STATUS_SCORE_RANGE when a row's scores left the window of the
+    online softmax (that row's LSE is NaN).  NKV_OK from the launching call only says that the
+    launch was accepted; the word is valid once the stream has been synchronised."""
+    if word == 0:
+        return
+    if word == STATUS_SCORE_RANGE:
+        raise RuntimeError("nanokv_b200: attention scores of a row rose more than 2^96 above the "
+                           "maximum of the tiles before them; that row's LSE is NaN")
+    kind = library().nkv_status_string(NKV_ERR_DEVICE_WAIT).decode()
+    raise RuntimeError(f"nanokv_b200: {kind}: wait site {word}")

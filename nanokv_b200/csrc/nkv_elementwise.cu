@@ -96,8 +96,8 @@ quant_pack_vec_kernel(const uint16_t* coeff, int S, int r, float eps, int scale_
     else scale = __fdiv_rn(fmaxf(amax[j], eps), 7.0f);
     const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
     uint32_t out = 0;
+    const float inv = IN_BF16 ? 0.f : __frcp_rn(scale);
 #pragma unroll
-    const float inv = __frcp_rn(scale);
     for (int k = 0; k < 4; ++k) {
       const float z0 = __uint_as_float(w[k] << 16), z1 = __uint_as_float(w[k] & 0xFFFF0000u);
       float q0, q1;

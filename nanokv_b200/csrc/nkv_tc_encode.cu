@@ -11,6 +11,8 @@
 //            rounds once to bf16.
 // A CTA covers up to 512 output columns as 1 or 2 accumulators of NB <= 256.
 // Warps 0-7 compute, warp 8 lane 0 issues TMA, warp 9 lane 0 issues MMA.
+#include <atomic>
+
 #include "nkv_internal.h"
 #include "nkv_tc.cuh"
 
@@ -344,13 +346,16 @@ bool tc_project_supported(int J, int r) {
 // SMs instead of leaving the last round mostly empty (12,480 tokens: 147 CTAs of 85 rows instead
 // of 98 of 128).  Not below 64 rows: every CTA streams the whole B operand from L2.
 int pick_rows(int S, int column_parts) {
-  static int sms = 0;
+  // SM count of the current device, cached per device ordinal
+  static std::atomic<int> cached[64];
+  int device = 0, sms = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) device = -1;
+  if (device >= 0) sms = cached[device].load(std::memory_order_relaxed);
   if (sms == 0) {
-    int device = 0;
-    cudaDeviceProp prop{};
-    if (cudaGetDevice(&device) == cudaSuccess && cudaGetDeviceProperties(&prop, device) == cudaSuccess)
-      sms = prop.multiProcessorCount;
-    if (sms <= 0) sms = 148;
+    if (device < 0 ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+      sms = 148;
+    if (device >= 0) cached[device].store(sms, std::memory_order_relaxed);
   }
   const long long units = static_cast<long long>(ceil_div(S, TM)) * column_parts;
   const long long waves = (units + sms - 1) / sms;

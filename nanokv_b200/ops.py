@@ -172,9 +172,33 @@ def decode_rows(view: HistoryView, decoder, mean, *, rows=None, dtype=None) -> t
 
 # ------------------------------------------------------------------------ attention
 def default_splits(tokens: int) -> int:
-    """History splits of one fused launch: up to four, each spanning at least 24 tiles
-    (measured on 12,480 to 49,920 tokens: four splits are 1.3 to 3 % faster than two)."""
-    return max(1, min(4, tokens // (24 * 128)))
+    """Upper bound on the history splits of one fused launch; the library picks the count below it
+    that fills its groups of thread blocks most evenly (runs of at least 24 tiles)."""
+    return max(1, min(8, tokens // (24 * 128)))
+
+
+_STATUS_WORDS: dict = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """The per-device int32 word the fused read reports into when the caller passes none."""
+    key = torch.device(device)
+    if key not in _STATUS_WORDS:
+        _STATUS_WORDS[key] = torch.zeros(1, dtype=torch.int32, device=key)
+    return _STATUS_WORDS[key]
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if a fused read on ``device`` (default: every device used so far) left a
+    status behind: a bounded device-side wait that gave up, or a row whose scores left the softmax
+    window.  The word is cleared.  Results of launches since the last check are only to be trusted
+    after this returns."""
+    words = [status_word(device)] if device is not None else list(_STATUS_WORDS.values())
+    for word in words:
+        value = int(word.item())      # synchronises the device
+        if value:
+            word.zero_()
+            _lib.check_device_status(value)
 
 
 def attn_codec(q, view_k: HistoryView, view_v: HistoryView, wk, bias_k, wv, bias_v, *,
@@ -206,6 +230,8 @@ def attn_codec(q, view_k: HistoryView, view_v: HistoryView, wk, bias_k, wv, bias
             or tuple(lse.shape) != (Q, H) or lse.dtype != torch.float32 or not lse.is_contiguous()):
         raise ValueError("result buffers must be contiguous [Q,H,dv] in q's dtype and f32 [Q,H]")
     _require_cuda(out, lse)
+    if status is None:   # a launch always has somewhere to report a wait that gave up: check_status()
+        status = status_word(device)
     sk, sv = view_k.struct(), view_v.struct()
     lib = _lib.library()
     if splits is None:

@@ -60,7 +60,10 @@ def test_peer_merge_rejects_bad_arguments():
     with pytest.raises(ValueError):
         ops.cp_merge_peer(*ptrs, rows=4, width=12, row_begin=0, row_end=4, dtype=torch.bfloat16,
                           device=device)
-    with pytest.raises(ValueError):
+    with pytest.raises(ValueError, match="not 16-byte aligned"):   # partial / result pointers off by 2 bytes
+        ops.cp_merge_peer(*[[v + 2 for v in p] for p in ptrs], rows=4, width=8, row_begin=0, row_end=4,
+                          dtype=torch.bfloat16, device=device)
+    with pytest.raises(ValueError):                                  # more ranks than the kernel folds
         ops.cp_merge_peer(*[p * 17 for p in ptrs], rows=4, width=8, row_begin=0, row_end=4,
                           dtype=torch.bfloat16, device=device)
 

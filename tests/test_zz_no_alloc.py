@@ -75,3 +75,31 @@ def test_static_scratch_encoder_rejects_oversized_chunks():
     assert b"coefficient scratch" in lib.nkv_last_error()
     with pytest.raises(ValueError):
         _lib.check(status)
+
+
+def test_static_scratch_encoder_takes_no_device_memory():
+    """With every buffer allocated beforehand and one warmed call behind it, a call of the static
+    entry point leaves the device's free memory exactly where it was: nothing inside allocates."""
+    lib = _lib.library()
+    shape = synthetic.Shape("s", 2, 128, 64, 16, 0, 0, "bf16")
+    gen = synthetic.generator(7)
+    op = synthetic.make_operator(shape, gen, mean_std=0.05)
+    centers = synthetic.make_centers(shape, gen)
+    mean, encoder = op["mean"].cuda(), op["encoder"].cuda()
+    stored = centers.to(torch.bfloat16).cuda()
+    rows = synthetic.make_rows(512, centers, gen, dtype=torch.bfloat16).cuda()
+    S, J = rows.shape
+    r, C = encoder.shape[0], stored.shape[0]
+    codes = torch.zeros(S, r // 2, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(S, 1, dtype=torch.bfloat16, device="cuda")
+    ids = torch.zeros(S, dtype=torch.uint8, device="cuda")
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    args = (_ptr(rows), ops.dtype_code(rows.dtype), _ptr(stored), C, _ptr(mean), _ptr(encoder),
+            ops.dtype_code(encoder.dtype), S, J, r, r, 1e-12, _lib.NKV_QUANT_F32, _lib.NKV_BF16, 1, 0,
+            _ptr(codes), _ptr(scales), _ptr(ids), stream)
+    _lib.check(lib.nkv_encode_append_static(*args))    # first call: symbol look-up, module load
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    _lib.check(lib.nkv_encode_append_static(*args))
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
