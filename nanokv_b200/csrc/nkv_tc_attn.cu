@@ -816,6 +816,8 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
     const uint32_t smem_base = smem_u32(smem);
     bool ok = true;
     int seq = 0, gp = 0, wgen = 0, jobs = 0;   // wgen: units whose rows this CTA has loaded (resident form)
+    Laps laps;
+    laps.start(p.prof + 32, p.prof != nullptr && g == 0 && pidx == 0 && leader);
     for (int u = g; u < p.units && ok; u += p.groups) {
       const Unit un = unit_of(p, u);
       bool first = true;
@@ -834,9 +836,11 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
             ok = mwait_all(&bars[W_FULL + slot], (gp / nw) & 1, ctx, 411);
           }
           const int st = gp % NSTAGE;
+          laps.lap(0);
           ok = ok && mwait_all(&bars[LAT_FULL + st], (gp / NSTAGE) & 1, ctx, 412);
           if (!ok) break;
           tc_fence_after();
+          laps.lap(1);
           // descriptors are built once per chunk; a K = 16 step adds 32 bytes (2 in the address
           // field) to the shared-memory operand and 8 columns to the TMEM operand
           for (int j = 0; j < n; ++j) {
@@ -849,11 +853,13 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
           }
           // frees the staging slot (and the decoder rows); on the last pair: accumulator done
           if (leader) mma_commit(&bars[PAIR_DONE + (gp & (NDONE - 1))]);
+          laps.lap(2);
         }
         if (first && resident) ++wgen;
         first = false;
       }
     }
+    laps.flush();
     __syncwarp();
   } else if (warp == 10) {
     // ------------------------------------------- everything that waits on global memory, off the
