@@ -32,7 +32,20 @@ SHAPE = synthetic.CONFIGS["c3_wan_shaped"]
 FRAME = 1560
 METRIC = "codec_attention_history_tokens_per_s"
 UNIT = "history-tokens/s"
-NCU_TRAFFIC_BYTES = 521.8e6   # profiles/attn_codec_kernel_c3_wan_shaped.md
+
+
+def measured_traffic(kernel: str, workload: str):
+    """DRAM bytes per launch of `kernel` on `workload`, from the figures file written next to the ncu
+    summary of that kernel (dram__bytes_read.sum + dram__bytes_write.sum of one launch); None when
+    no capture of the kernel as built is on record."""
+    path = ROOT / "profiles" / "ncu_figures.json"
+    if not path.exists():
+        return None
+    try:
+        entry = json.loads(path.read_text()).get(f"{kernel}:{workload}")
+    except (ValueError, AttributeError):
+        return None
+    return None if entry is None else entry.get("dram_bytes_per_launch")
 
 
 def measured_peaks() -> tuple[dict, str]:
@@ -205,7 +218,8 @@ def run_ours(args) -> dict:
             os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=device)
     shape, layers = SHAPE, args.layers
-    total_frames = shape.history // FRAME
+    total_frames = args.history_frames or shape.history // FRAME
+    history_tokens = total_frames * FRAME
     bounds = context_parallel.shard_bounds(total_frames, world)
     frames = range(*bounds[rank])
     built = build_layers(shape, frames, layers, device)
@@ -400,15 +414,64 @@ def run_ours(args) -> dict:
         exchange_ms = float(took.item())
     encode = time_encode(shape, device, steps=5, warmup=3) if rank == 0 else None
 
+    # the same end-to-end step with the copies IN LINE on the compute stream: queries in, attention,
+    # rows out, layer after layer -- what a layer stack whose next queries depend on this layer's
+    # output pays (the overlapped form above is the upper bound a pipelined caller can reach)
+    def step_inline():
+        merged = None
+        for entry in built:
+            if world > 1:
+                q_stage[0][:q_hi - q_lo].copy_(q_host[q_lo:q_hi], non_blocking=True)
+                dist.all_gather_into_tensor(q_whole[0], q_stage[0])
+                q = q_whole[0][:shape.queries]
+            else:
+                q_slots[0].copy_(q_host, non_blocking=True)
+                q = q_slots[0]
+            merged = merge_layer(attend_layer(entry, q))
+            out_host.view(rows, -1)[row_lo:row_hi].copy_(merged[0].view(rows, -1)[row_lo:row_hi],
+                                                         non_blocking=True)
+            lse_host.view(rows)[row_lo:row_hi].copy_(merged[1].view(rows)[row_lo:row_hi], non_blocking=True)
+        return merged
+
+    step_inline()
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(e2e_steps):
+        step_inline()
+    stop.record()
+    barrier()
+    inline_ms = torch.tensor([start.elapsed_time(stop)], device=device)
+    if world > 1:
+        dist.all_reduce(inline_ms, op=dist.ReduceOp.MAX)
+    inline_seconds = float(inline_ms.item()) / 1e3
+
+    # parity of what was timed, on rank 0: the first frames of layer 0's history through the fused
+    # read against the CPU oracle on a strided subset of the query rows, and (one GPU) the stock
+    # torch GPU path on the whole layer as the comparison arm
+    parity, gpu_ref = None, None
+    if rank == 0 and not args.no_cpu:
+        parity = parity_sample(shape, built[0], q_dev, q_host)
+    if rank == 0 and world == 1 and not args.no_gpu_reference:
+        gpu_ref = gpu_reference(shape, built[0], q_dev)
+        ours = attention.codec_attention(q_dev, built[0]["k"][0], built[0]["v"][0], built[0]["k"][1],
+                                         built[0]["v"][1])[0]
+        theirs = gpu_ref.pop("out", None)
+        if theirs is not None:
+            gpu_ref["rel_diff_vs_fused"] = float((ours.float() - theirs.float()).abs().max() /
+                                                 theirs.float().abs().max())
+        del ours, theirs
+        torch.cuda.empty_cache()
+
     if exchange is not None:
         exchange.close()
+    del built
+    torch.cuda.empty_cache()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
         return {}
     peaks, peak_kind = measured_peaks()
     step_ms = seconds / args.steps * 1e3
-    tokens_per_step = shape.history * layers
+    tokens_per_step = history_tokens * layers
     flops_launch = attention_flops(local_tokens, shape.queries, shape.joint, shape.rank)
     achieved = flops_launch / kernel_s / 1e12
     peak = float(peaks["bf16_tflops_sustained"])
@@ -421,7 +484,7 @@ def run_ours(args) -> dict:
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
         "config": {"workload": shape.name, "heads": shape.heads, "head_dim": shape.head_dim,
-                   "rank": shape.rank, "centers": shape.centers, "history_tokens": shape.history,
+                   "rank": shape.rank, "centers": shape.centers, "history_tokens": history_tokens,
                    "queries": shape.queries, "layers": layers, "quant_group": shape.rank,
                    "scale_dtype": "bf16", "parallelism": f"cp{world}",
                    "positional_restore": "3-D RoPE of the rebuilt keys inside the read" if args.rope else "none",
@@ -436,6 +499,8 @@ def run_ours(args) -> dict:
                    "l2_policy": "inputs larger than L2 (distinct compressed history per layer)"},
         "e2e": {"value": tokens_per_step / (e2e_seconds / e2e_steps), "unit": UNIT,
                 "h2d_bytes_per_step": q_bytes * layers, "d2h_bytes_per_step": o_bytes * layers},
+        "e2e_inline": {"value": tokens_per_step / (inline_seconds / e2e_steps), "unit": UNIT,
+                       "note": "copies in line on the compute stream, no overlap with other layers"},
         # per layer: fused attention + LSE merge of its history splits (+ the CP merge when sharded)
         "gpu_launches": args.steps * layers * (2 + (1 if world > 1 else 0)),
         "exchange_ms_per_layer": exchange_ms,
@@ -443,17 +508,19 @@ def run_ours(args) -> dict:
                      "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                      "peak_source": f"bf16_tflops_sustained of {peak_kind}",
                      "launch_ms": kernel_s * 1e3, "flops_per_launch": flops_launch,
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch over the full
-                     # 99,840-token layer (ncu capture summarised under profiles/); per-rank shards
-                     # were not captured separately
-                     "traffic": NCU_TRAFFIC_BYTES if world == 1 else None},
+                     # DRAM bytes of one launch over the full layer from an ncu capture of this
+                     # kernel, when one is on record (per-rank shards are not captured separately)
+                     "traffic": (measured_traffic("attn_codec_kernel", shape.name)
+                                 if world == 1 and not args.history_frames else None)},
         "encode": encode,
         "clocks": clocks,
     }
     if cpu:
         line["cpu_baseline"] = cpu
-    if world > 1:
-        dist.destroy_process_group()
+    if parity:
+        line["parity"] = parity
+    if gpu_ref:
+        line["gpu_reference"] = gpu_ref
     return line
 
 
@@ -527,6 +594,39 @@ def run_reference(args) -> dict:
         "gpu_launches": 0,
     }
 
+
+
+# ------------------------------------------------------------------ parity of the timed path
+def parity_sample(shape, entry, q_dev, q_host, frames: int = 4, stride: int = 73) -> dict:
+    """The fused read over the first `frames` frames of a layer's history (a view of the cache the
+    bench times) against the CPU oracle reading the same codes, on every `stride`-th query row."""
+    from nanokv_b200 import attention
+    from oracle import nkv_oracle as oracle
+    (hk, ok), (hv, ov) = entry["k"], entry["v"]
+    tokens = min(frames * FRAME, hk.tokens)
+    out, lse = attention.codec_attention(q_dev, hk.view_tokens(0, tokens), hv.view_tokens(0, tokens), ok, ov)
+    torch.cuda.synchronize()
+    rows = torch.arange(0, shape.queries, stride)
+
+    def segment(hist):
+        codes = hist.codes[:tokens].cpu()
+        return {"shape": (1, tokens, shape.joint), "rank": hist.rank, "packed": codes.reshape(-1),
+                "count": tokens * hist.rank, "scale": hist.scales[:tokens].cpu(),
+                "centers": hist.centers[:hist.centers_per_segment].cpu()[None],
+                "ids": hist.ids[:tokens].cpu().to(torch.int64).bitwise_and(0xFFFF)[None]}
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    want, want_lse = oracle.codec_attention(
+        q_host[rows][None], [segment(hk)], [segment(hv)], k_decoder=ok.decoder.cpu(), k_mean=ok.mean.cpu(),
+        v_decoder=ov.decoder.cpu(), v_mean=ov.mean.cpu(), heads=shape.heads, dtype=torch.bfloat16)
+    got = out.cpu()[rows].float()
+    rel = float((got - want[0].float()).abs().max() / want[0].float().abs().max())
+    lse_err = float((lse.cpu()[rows] - want_lse[0].t()).abs().max())
+    if not (rel <= 2e-2 and lse_err <= 2e-2):
+        raise RuntimeError(f"fused read differs from the oracle: rel {rel:.3e}, lse {lse_err:.3e}")
+    return {"parity_rel_err": rel, "lse_abs_err": lse_err, "tolerance": 2e-2,
+            "sample": f"layer 0, first {tokens} history tokens, {rows.numel()} of {shape.queries} query "
+                      f"rows x {shape.heads} heads, against the CPU oracle"}
 
 
 # ------------------------------------------------------------------ GPU comparison arm
@@ -646,7 +746,19 @@ def run_fast(args) -> dict:
     stop.record()
     torch.cuda.synchronize()
     seconds = start.elapsed_time(stop) / 1e3 / args.steps
-    return {"metric": "fast_attention_history_tokens_per_s", "value": shape.history / seconds,
+    peaks, peak_kind = measured_peaks()
+    Q, r, D = shape.queries, shape.rank, shape.head_dim
+    low_tokens, prot_tokens = (frames - protected) * FRAME, protected * FRAME
+    # algorithmic flops: per low-width token and head group 4 Q d + 4 r d, per protected token the full read
+    flops = (low_tokens * (18 * (4.0 * Q * 32 + 4.0 * r * 32) + 6 * (4.0 * Q * D + 4.0 * r * D)) +
+             prot_tokens * (4.0 * Q * shape.joint + 4.0 * r * shape.joint))
+    roofline = {"bound": "tensor", "kernel": "attn_codec_kernel<64> + attn_codec_kernel<128>",
+                "achieved": flops / seconds / 1e12, "peak": float(peaks["bf16_tflops_sustained"]),
+                "unit": "TFLOP/s", "frac": flops / seconds / 1e12 / float(peaks["bf16_tflops_sustained"]),
+                "peak_source": f"bf16_tflops_sustained of {peak_kind}", "flops_per_layer": flops,
+                "traffic": None}
+    return {"roofline": roofline,
+            "metric": "fast_attention_history_tokens_per_s", "value": shape.history / seconds,
             "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": seconds * 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -655,10 +767,12 @@ def run_fast(args) -> dict:
                        "queries": shape.queries, "low_heads": 18, "low_width": 32, "layers": 1}}
 
 
-def run_streaming(args) -> dict:
+def run_streaming(args, standalone: bool = True) -> dict:
     """c5: streaming rollout, one layer.  Per chunk: encode + append 1,560 new K and V tokens
-    (chunks are dealt round-robin to the ranks, so shards stay balanced), then 4,680-query
-    codec-attention against the grown history (each rank its shard; all-gather + LSE merge)."""
+    (chunk c belongs to rank c % world, which encodes it into its own shard: ownership is
+    round-robin by chunk, so shards stay balanced as the history grows), then 4,680-query
+    codec-attention against the grown history (each rank its shard; the partials are merged by the
+    peer-memory exchange, or by NCCL all-gather + merge with --exchange nccl)."""
     import torch.distributed as dist
     from nanokv_b200 import attention, context_parallel
     from nanokv_b200.cache import CompressedHistory
@@ -668,11 +782,15 @@ def run_streaming(args) -> dict:
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    if world > 1:
+    if world > 1 and standalone:
         if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=device)
     shape, chunks = synthetic.CONFIGS["c5_streaming"], args.chunks
+    exchange = None
+    if world > 1 and args.exchange == "peer":
+        exchange = context_parallel.PeerExchange(shape.queries, shape.heads, shape.head_dim,
+                                                 torch.bfloat16, device)
     mine = (chunks + world - 1 - rank) // world
     gen = torch.Generator(device=device).manual_seed(99 + rank)
     hists, ops_ = {}, {}
@@ -702,8 +820,13 @@ def run_streaming(args) -> dict:
         if chunk % world == rank:
             for kind in ("k", "v"):
                 encode_append(hists[kind][0], rows[kind], ops_[kind], QuantSpec(), centers="resident")
-        out, lse = attention.codec_attention(q, hists["k"][0], hists["v"][0], ops_["k"], ops_["v"])
-        context_parallel.gather_and_merge(out, lse)
+        if exchange is not None:
+            attention.codec_attention(q, hists["k"][0], hists["v"][0], ops_["k"], ops_["v"],
+                                      out=exchange.partial_out, lse=exchange.partial_lse)
+            exchange.merge()
+        else:
+            out, lse = attention.codec_attention(q, hists["k"][0], hists["v"][0], ops_["k"], ops_["v"])
+            context_parallel.gather_and_merge(out, lse)
         attended += (chunk + 1) * FRAME
     stop.record()
     if world > 1:
@@ -712,6 +835,9 @@ def run_streaming(args) -> dict:
     ms = torch.tensor([start.elapsed_time(stop)], device=device)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if exchange is not None:
+        exchange.close()
+    if world > 1 and standalone:
         dist.destroy_process_group()
     if rank != 0:
         return {}
@@ -723,7 +849,10 @@ def run_streaming(args) -> dict:
             "config": {"workload": shape.name, "heads": shape.heads, "rank": shape.rank,
                        "chunks": chunks, "tokens_per_chunk": FRAME, "queries": shape.queries,
                        "final_history_tokens": chunks * FRAME, "layers": 1,
-                       "sharding": "chunks round-robin over ranks"},
+                       "sharding": "chunk c is encoded into and owned by rank c % world (round-robin)",
+                       "exchange": ("none" if world == 1 else
+                                    "peer-memory merge + all-gather kernel" if args.exchange == "peer" else
+                                    "nccl all-gather + merge kernel")},
             "encode_tokens_per_s_incl_attention": chunks * FRAME / seconds}
 
 
@@ -809,6 +938,66 @@ def run_aux(args) -> dict:
             "peak": hbm, "peak_source": f"hbm_gbs of {peak_kind}", "kernels": results}
 
 
+def time_rope(shape, device, layers: int = 2, launches: int = 4) -> dict:
+    """Positional restore inside the read: ms per layer launch with the rebuilt keys rotated (3-D RoPE
+    by absolute position), one GPU, whole c3 history."""
+    from nanokv_b200 import attention
+    built = build_layers(shape, range(shape.history // FRAME), layers, device)
+    q = synthetic.make_queries(shape, synthetic.generator(4242)).to(device)
+    table = attention.RopeTable(rope_freqs(1024, shape.head_dim), frame_seqlen=FRAME, width=52, device=device)
+    positions = torch.arange(shape.history, dtype=torch.int32, device=device)
+    times = []
+    for index in range(2 + launches):
+        (hk, ok), (hv, ov) = built[index % layers]["k"], built[index % layers]["v"]
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        attention.codec_attention(q, hk, hv, ok, ov, rope=table, positions=positions)
+        stop.record()
+        torch.cuda.synchronize()
+        if index >= 2:
+            times.append(start.elapsed_time(stop))
+    ms = statistics.mean(times)
+    peaks, peak_kind = measured_peaks()
+    flops = attention_flops(shape.history, shape.queries, shape.joint, shape.rank)
+    return {"ms_per_layer": ms, "history_tokens_per_s": shape.history / (ms / 1e3),
+            "roofline": {"bound": "tensor", "kernel": "attn_codec_kernel<128, rope>",
+                         "achieved": flops / (ms / 1e3) / 1e12, "peak": float(peaks["bf16_tflops_sustained"]),
+                         "unit": "TFLOP/s",
+                         "frac": flops / (ms / 1e3) / 1e12 / float(peaks["bf16_tflops_sustained"]),
+                         "peak_source": f"bf16_tflops_sustained of {peak_kind}", "traffic": None}}
+
+
+def run_secondary(args) -> dict:
+    """Short versions of the secondary workloads, after the headline: c5 on every rank; c4 and the
+    positional restore on one GPU only.  A failure is reported in place and does not void the headline."""
+    import copy
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    result = {}
+
+    def attempt(name, fn):
+        try:
+            value = fn()
+            if rank == 0:
+                result[name] = value
+        except Exception as exc:   # keep the headline line
+            if rank == 0:
+                result[name] = {"error": f"{type(exc).__name__}: {str(exc).splitlines()[0][:160]}"}
+
+    stream_args = copy.copy(args)
+    stream_args.chunks = args.secondary_chunks
+    attempt("c5_streaming", lambda: {k: v for k, v in run_streaming(stream_args, standalone=False).items()
+                                     if k in ("metric", "value", "unit", "ms_per_step", "config",
+                                              "encode_tokens_per_s_incl_attention")})
+    if world == 1:
+        fast_args = copy.copy(args)
+        fast_args.steps, fast_args.warmup = 3, 2
+        attempt("c4_fast_mixed", lambda: {k: v for k, v in run_fast(fast_args).items()
+                                          if k in ("metric", "value", "unit", "ms_per_step", "config", "roofline")})
+        attempt("c3_positional_restore", lambda: time_rope(SHAPE, torch.device("cuda", 0)))
+    return result
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -816,7 +1005,14 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference", "torch_gpu"])
     parser.add_argument("--layers", type=int, default=SHAPE.layers)
-    parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg and the oracle parity sample")
+    parser.add_argument("--no-gpu-reference", action="store_true",
+                        help="skip the stock-torch GPU comparison arm (one GPU only)")
+    parser.add_argument("--no-secondary", action="store_true",
+                        help="skip the short secondary workloads (c4, c5, positional restore)")
+    parser.add_argument("--history-frames", type=int, default=0,
+                        help="history frames per layer (default: the workload's 64); smaller values are "
+                             "for profiler captures")
     parser.add_argument("--rope", action="store_true",
                         help="rotate the rebuilt keys by absolute position inside the read (3-D RoPE)")
     parser.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
@@ -825,6 +1021,8 @@ def main() -> None:
                         choices=["c3_wan_shaped", "c4_fast_mixed", "c5_streaming", "aux"],
                         help="c3 is the headline; c4 / c5 / aux are secondary measurements")
     parser.add_argument("--chunks", type=int, default=256, help="c5: chunks streamed")
+    parser.add_argument("--secondary-chunks", type=int, default=256,
+                        help="c5 chunks of the short secondary run behind the headline")
     args = parser.parse_args()
     if args.impl == "reference":
         line = run_reference(args)
@@ -838,6 +1036,13 @@ def main() -> None:
         line = run_aux(args)
     else:
         line = run_ours(args)
+        if not args.no_secondary and not args.history_frames:
+            secondary = run_secondary(args)
+            if line:
+                line["secondary"] = secondary
+        import torch.distributed as dist
+        if dist.is_initialized():
+            dist.destroy_process_group()
     if line:
         print(json.dumps(line), flush=True)
 
