@@ -1024,6 +1024,11 @@ def main() -> None:
     parser.add_argument("--secondary-chunks", type=int, default=256,
                         help="c5 chunks of the short secondary run behind the headline")
     args = parser.parse_args()
+    # stdout carries the one JSON line and nothing else: whatever a library prints there while
+    # the workloads run (the NCCL version banner, for one) goes to stderr instead
+    sys.stdout.flush()
+    json_out = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         line = run_reference(args)
     elif args.impl == "torch_gpu":
@@ -1043,6 +1048,9 @@ def main() -> None:
         import torch.distributed as dist
         if dist.is_initialized():
             dist.destroy_process_group()
+    sys.stdout.flush()
+    os.dup2(json_out, 1)
+    os.close(json_out)
     if line:
         print(json.dumps(line), flush=True)
 
