@@ -238,9 +238,10 @@ def run_ours(args) -> dict:
         rope_args = dict(rope=table, positions=torch.arange(start, start + local_tokens,
                                                             dtype=torch.int32, device=device))
     exchange = None
-    if world > 1 and args.exchange == "peer":
+    if world > 1 and args.exchange != "nccl":
         exchange = context_parallel.PeerExchange(shape.queries, shape.heads, shape.head_dim,
-                                                 torch.bfloat16, device)
+                                                 torch.bfloat16, device,
+                                                 ordering="flags" if args.exchange == "peer" else "nccl")
         # the fused exchange must reproduce all-gather + merge bit for bit on this workload
         (hk, ok), (hv, ov) = built[0]["k"], built[0]["v"]
         attention.codec_attention(q_dev, hk, hv, ok, ov, status=status, out=exchange.partial_out,
@@ -489,8 +490,10 @@ def run_ours(args) -> dict:
                    "scale_dtype": "bf16", "parallelism": f"cp{world}",
                    "positional_restore": "3-D RoPE of the rebuilt keys inside the read" if args.rope else "none",
                    "exchange": ("none" if world == 1 else
-                                "peer-memory merge + all-gather kernel" if exchange is not None else
-                                "nccl all-gather + merge kernel"),
+                                "peer-memory merge + all-gather kernel, ranks ordered by flag words in peer memory"
+                                if exchange is not None and args.exchange == "peer" else
+                                "peer-memory merge + all-gather kernel between two NCCL all-reduces"
+                                if exchange is not None else "nccl all-gather + merge kernel"),
                    "e2e_io": (("whole queries in, whole (O, lse) out" if world == 1 else
                                "each rank copies its 1/P slice of the queries in (NVLink all-gather "
                                "makes them whole) and its 1/P slice of the merged rows out; bytes are "
@@ -788,9 +791,10 @@ def run_streaming(args, standalone: bool = True) -> dict:
         dist.init_process_group("nccl", device_id=device)
     shape, chunks = synthetic.CONFIGS["c5_streaming"], args.chunks
     exchange = None
-    if world > 1 and args.exchange == "peer":
+    if world > 1 and args.exchange != "nccl":
         exchange = context_parallel.PeerExchange(shape.queries, shape.heads, shape.head_dim,
-                                                 torch.bfloat16, device)
+                                                 torch.bfloat16, device,
+                                                 ordering="flags" if args.exchange == "peer" else "nccl")
     mine = (chunks + world - 1 - rank) // world
     gen = torch.Generator(device=device).manual_seed(99 + rank)
     hists, ops_ = {}, {}
@@ -851,7 +855,7 @@ def run_streaming(args, standalone: bool = True) -> dict:
                        "final_history_tokens": chunks * FRAME, "layers": 1,
                        "sharding": "chunk c is encoded into and owned by rank c % world (round-robin)",
                        "exchange": ("none" if world == 1 else
-                                    "peer-memory merge + all-gather kernel" if args.exchange == "peer" else
+                                    "peer-memory merge + all-gather kernel" if args.exchange != "nccl" else
                                     "nccl all-gather + merge kernel")},
             "encode_tokens_per_s_incl_attention": chunks * FRAME / seconds}
 
@@ -1015,8 +1019,9 @@ def main() -> None:
                              "for profiler captures")
     parser.add_argument("--rope", action="store_true",
                         help="rotate the rebuilt keys by absolute position inside the read (3-D RoPE)")
-    parser.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
-                        help="context-parallel exchange: fused peer-memory kernel, or NCCL all-gather + merge")
+    parser.add_argument("--exchange", default="peer", choices=["peer", "peer_nccl_fences", "nccl"],
+                        help="context-parallel exchange: fused peer-memory kernel ordered by flag words in peer "
+                             "memory, the same kernel between two 4-byte NCCL all-reduces, or NCCL all-gather + merge")
     parser.add_argument("--workload", default="c3_wan_shaped",
                         choices=["c3_wan_shaped", "c4_fast_mixed", "c5_streaming", "aux"],
                         help="c3 is the headline; c4 / c5 / aux are secondary measurements")

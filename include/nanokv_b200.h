@@ -415,6 +415,28 @@ int nkv_cp_merge_peer(const void* const* part_out, const float* const* part_lse,
                       int d, int64_t row_begin, int64_t row_end, int dtype, void* stream);
 
 /*
+ * nkv_cp_merge_peer with the ordering of the ranks inside the kernel, so that the exchange of a
+ * layer is ONE launch per rank and no collective: every rank owns NKV_PEER_FLAG_WORDS int32 of
+ * peer-visible memory, zero at the start (flags[p]: rank p's words as mapped on this rank).  The
+ * kernel tells every rank that this rank's partial of `epoch` is complete (a release store at
+ * system scope; the partial was written by earlier work of the same stream), waits until every rank
+ * has said so here, merges and stores this rank's row slice into every rank's result, tells every
+ * rank that the slice has landed and waits until all slices have landed here -- after which every
+ * result row is in place and nobody still reads this rank's partial.  `epoch` counts the calls of a
+ * communicator from 1 upwards, the same on every rank.  Waits are bounded by `budget_cycles` SM
+ * cycles (<= 0: about a second); one that runs out stores its site (980: a partial never came,
+ * 981: a slice never landed) in *status_word and ends the kernel -- NKV_ERR_DEVICE_WAIT for the host
+ * that checks the word.  Plain loads and stores over peer mappings only (no multicast); the ranks'
+ * kernels run on different GPUs.  No counterpart in the reference.
+ */
+#define NKV_PEER_FLAG_WORDS 64
+int nkv_cp_exchange_peer(const void* const* part_out, const float* const* part_lse,
+                         void* const* dst_out, float* const* dst_lse, int32_t* const* flags,
+                         int world, int rank, int64_t rows, int d, int64_t row_begin,
+                         int64_t row_end, int dtype, int epoch, long long budget_cycles,
+                         int32_t* status_word, void* stream);
+
+/*
  * INT8 operator storage -> resident bf16 weights, once at load time:
  *     out[r, c] = bf16( bf16(qweight[r, c]) * scale[r, c / group] )
  * the expression the reference evaluates before every projection

@@ -66,32 +66,41 @@ def _aligned(nbytes: int) -> int:
 class PeerExchange:
     """Fused merge + all-gather of context-parallel partials over peer memory.
 
-    Every rank owns one peer-visible block holding its partial (O, lse) and its
-    merged result; ``partial_out`` / ``partial_lse`` are the buffers the read
-    kernel fills.  ``merge()`` then (1) waits until every rank's partial is
-    complete (a four-byte NCCL all-reduce on the compute stream), (2) launches
-    nkv_cp_merge_peer for this rank's row slice, which loads the slice of all
-    P partials (P-1 of them over NVLink) and stores the merged rows into all P
-    result buffers, (3) waits until every rank's slice has landed.  Each rank
-    moves 2 x (P-1)/P of one partial instead of receiving P-1 whole ones.
-    The same buffers serve every layer: step (3) also guarantees nobody still
-    reads a partial when the next read overwrites it, and step (1) of the next
-    layer orders the next store into ``out`` after its last consumer.
+    Every rank owns one peer-visible block holding its partial (O, lse), its
+    merged result and a few flag words; ``partial_out`` / ``partial_lse`` are the
+    buffers the read kernel fills.  ``merge()`` is ONE launch per rank
+    (nkv_cp_exchange_peer): the kernel tells every rank that this rank's partial
+    is complete, waits until every rank has said so, loads its row slice of all P
+    partials (P-1 of them over NVLink), stores the merged rows into all P result
+    buffers, tells every rank that its slice has landed and waits for all slices
+    to land here.  No collective, no host synchronisation; each rank moves
+    2 x (P-1)/P of one partial instead of receiving P-1 whole ones.
+    The same buffers serve every layer: the kernel's last wait also means that
+    nobody still reads this rank's partial when the next read overwrites it.
+    ``ordering="nccl"`` keeps the earlier form (nkv_cp_merge_peer between two
+    four-byte all-reduces) for comparison.
     """
 
-    def __init__(self, queries: int, heads: int, width: int, dtype: torch.dtype, device, group=None):
+    def __init__(self, queries: int, heads: int, width: int, dtype: torch.dtype, device, group=None,
+                 ordering: str = "flags"):
         if not dist.is_initialized():
             raise RuntimeError("PeerExchange needs an initialised process group")
-        self.group, self.device = group, torch.device(device)
+        if ordering not in ("flags", "nccl"):
+            raise ValueError("ordering is 'flags' or 'nccl'")
+        self.group, self.device, self.ordering = group, torch.device(device), ordering
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.shape, self.dtype = (queries, heads, width), dtype
         self.rows = queries * heads
         itemsize = torch.empty((), dtype=dtype).element_size()
         out_bytes, lse_bytes = _aligned(self.rows * width * itemsize), _aligned(self.rows * 4)
+        flag_bytes = _aligned(ops.PEER_FLAG_WORDS * 4)
         self._offsets = {"part_out": 0, "part_lse": out_bytes, "out": out_bytes + lse_bytes,
-                         "lse": 2 * out_bytes + lse_bytes}
-        self.nbytes = 2 * (out_bytes + lse_bytes)
+                         "lse": 2 * out_bytes + lse_bytes, "flags": 2 * (out_bytes + lse_bytes)}
+        self.nbytes = 2 * (out_bytes + lse_bytes) + flag_bytes
         self.block = ops.PeerBuffer.allocate(self.nbytes, self.device)
+        self.flags = self.block.tensor(self._offsets["flags"], (ops.PEER_FLAG_WORDS,), torch.int32)
+        self.flags.zero_()
+        torch.cuda.synchronize(self.device)
         handles = [None] * self.world
         dist.all_gather_object(handles, self.block.handle, group=group)
         self.blocks = [self.block if r == self.rank else
@@ -102,28 +111,36 @@ class PeerExchange:
         self.out = self.block.tensor(self._offsets["out"], self.shape, dtype)
         self.lse = self.block.tensor(self._offsets["lse"], (queries, heads), torch.float32)
         self.row_begin, self.row_end = shard_bounds(self.rows, self.world)[self.rank]
+        self.epoch = 0
         self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self._fence()   # every rank has mapped every block before anyone uses one
+        self._fence()   # every rank has mapped every block (and cleared its flags) before anyone uses one
 
     def _fence(self) -> None:
         dist.all_reduce(self._token, group=self.group)
 
-    def merge(self):
+    def merge(self, status: torch.Tensor | None = None):
         """Partials in ``partial_out`` / ``partial_lse`` on every rank -> merged (out, lse),
         identical on every rank.  Stream-ordered; no host synchronisation."""
-        self._fence()
         pointers = {name: [blk.pointer + off for blk in self.blocks]
                     for name, off in self._offsets.items()}
-        ops.cp_merge_peer(pointers["part_out"], pointers["part_lse"], pointers["out"], pointers["lse"],
-                          rows=self.rows, width=self.shape[2], row_begin=self.row_begin,
-                          row_end=self.row_end, dtype=self.dtype, device=self.device)
-        self._fence()
+        if self.ordering == "nccl":
+            self._fence()
+            ops.cp_merge_peer(pointers["part_out"], pointers["part_lse"], pointers["out"], pointers["lse"],
+                              rows=self.rows, width=self.shape[2], row_begin=self.row_begin,
+                              row_end=self.row_end, dtype=self.dtype, device=self.device)
+            self._fence()
+            return self.out, self.lse
+        self.epoch += 1
+        ops.cp_exchange_peer(pointers["part_out"], pointers["part_lse"], pointers["out"], pointers["lse"],
+                             pointers["flags"], rank=self.rank, rows=self.rows, width=self.shape[2],
+                             row_begin=self.row_begin, row_end=self.row_end, dtype=self.dtype,
+                             epoch=self.epoch, device=self.device, status=status)
         return self.out, self.lse
 
     def close(self) -> None:
         """Collective: unmap the peers' blocks, then free this rank's."""
         torch.cuda.synchronize(self.device)
-        self.partial_out = self.partial_lse = self.out = self.lse = None
+        self.partial_out = self.partial_lse = self.out = self.lse = self.flags = None
         for r, blk in enumerate(self.blocks):
             if r != self.rank:
                 blk.release()

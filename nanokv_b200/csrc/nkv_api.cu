@@ -437,6 +437,18 @@ int nkv_cp_merge_peer(const void* const* part_out, const float* const* part_lse,
                        dtype, static_cast<cudaStream_t>(stream));
 }
 
+int nkv_cp_exchange_peer(const void* const* part_out, const float* const* part_lse,
+                         void* const* dst_out, float* const* dst_lse, int32_t* const* flags, int world,
+                         int rank, int64_t rows, int d, int64_t row_begin, int64_t row_end, int dtype,
+                         int epoch, long long budget_cycles, int32_t* status_word, void* stream) {
+  NKV_REQUIRE(part_out && part_lse && dst_out && dst_lse && flags && rows >= 0 && d > 0, NKV_ERR_INVALID,
+              "cp_exchange_peer: rows=%lld d=%d", static_cast<long long>(rows), d);
+  NKV_REQUIRE(dtype == NKV_F32 || dtype == NKV_BF16, NKV_ERR_INVALID, "cp_exchange_peer: dtype");
+  if (budget_cycles <= 0) budget_cycles = 1ll << 31;
+  return cp_merge_peer(part_out, part_lse, dst_out, dst_lse, world, rows, d, row_begin, row_end, dtype,
+                       static_cast<cudaStream_t>(stream), flags, rank, epoch, budget_cycles, status_word);
+}
+
 int nkv_operator_unpack_int8(const int8_t* qweight, const void* scale_bf16, int64_t rows, int cols,
                              int group, void* out_bf16, void* stream) {
   NKV_REQUIRE(qweight && scale_bf16 && out_bf16 && rows >= 0, NKV_ERR_INVALID,

@@ -177,19 +177,97 @@ struct PeerMergeArgs {
   float* dst_lse[MAX_PARTS];
 };
 
+// Ordering of the ranks without a collective: every rank owns a block of flag words that its peers
+// can write (NKV_PEER_FLAG_WORDS int32: [0, 16) "rank r's partial of epoch e is complete",
+// [16, 32) "rank r has stored its merged slice of epoch e here", [32] a ticket counter of this
+// rank's own blocks).  epoch == 0 switches the protocol off (local merges).
+struct PeerSync {
+  int32_t* flags[MAX_PARTS];   // flag block of every rank, as mapped on this rank
+  int rank, epoch;
+  long long budget;            // SM cycles a wait may take before the kernel gives up
+  int32_t* status;             // receives the wait-site code (980 / 981) when it does
+};
+
+__device__ __forceinline__ void st_release_sys(int32_t* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int32_t* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// bounded: true when the word reached `target`, false (status set) when the budget ran out
+__device__ __forceinline__ bool wait_flag_sys(const int32_t* flag, int target, long long budget,
+                                              int32_t* status, int code) {
+  if (ld_acquire_sys(flag) >= target) return true;
+  const long long start = clock64();
+  while (ld_acquire_sys(flag) < target) {
+    if (clock64() - start > budget) {
+      if (status) atomicCAS(status, 0, code);
+      return false;
+    }
+    __nanosleep(100);
+  }
+  return true;
+}
+
 template <typename VEC>  // uint4: 8 two-byte elements; float4 pairs are handled as two uint4 halves
 __device__ __forceinline__ VEC peer_load(const void* base, size_t byte_offset) {
   return *reinterpret_cast<const VEC*>(static_cast<const char*>(base) + byte_offset);
 }
 
+template <int DTYPE, int MAXP>
+__device__ __forceinline__ void cp_merge_rows(const PeerMergeArgs& args, int world, int dests,
+                                              long long row_begin, int d, long long idx);
+
 // thread = (row, 8 consecutive columns); MAXP bounds the unrolled part loops (registers)
 template <int DTYPE, int MAXP>
 __global__ void __launch_bounds__(256)
-cp_merge_peer_kernel(PeerMergeArgs args, int world, int dests, long long row_begin, long long row_end,
-                     int d) {
+cp_merge_peer_kernel(PeerMergeArgs args, PeerSync sync, int world, int dests, long long row_begin,
+                     long long row_end, int d) {
+  __shared__ int gate;
+  if (sync.epoch > 0) {
+    // this rank's partial is complete (it was written by earlier kernels of this stream): tell every
+    // rank, then wait until every rank has said the same here
+    if (blockIdx.x == 0 && threadIdx.x < world) st_release_sys(sync.flags[threadIdx.x] + sync.rank, sync.epoch);
+    if (threadIdx.x == 0) gate = 1;
+    __syncthreads();
+    if (threadIdx.x < world &&
+        !wait_flag_sys(sync.flags[sync.rank] + threadIdx.x, sync.epoch, sync.budget, sync.status, 980))
+      gate = 0;
+    __syncthreads();
+    if (!gate) return;   // a peer never arrived: nothing is merged, the status word says so
+  }
   const int per_row = d >> 3;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= (row_end - row_begin) * per_row) return;
+  if (idx < (row_end - row_begin) * per_row)
+    cp_merge_rows<DTYPE, MAXP>(args, world, dests, row_begin, d, idx);
+  if (sync.epoch > 0) {
+    // every block's stores are out; the last block to get here tells every rank that this rank's
+    // slice has landed and waits until all slices have landed here (which also means that every
+    // rank is done reading this rank's partial)
+    __threadfence_system();
+    __syncthreads();
+    int32_t* mine = sync.flags[sync.rank];
+    if (threadIdx.x == 0) {
+      const int ticket = atomicAdd(mine + 32, 1);
+      __threadfence();
+      gate = ticket == static_cast<int>(gridDim.x) - 1;
+    }
+    __syncthreads();
+    if (!gate) return;
+    if (threadIdx.x < world) {
+      st_release_sys(sync.flags[threadIdx.x] + 16 + sync.rank, sync.epoch);
+      wait_flag_sys(mine + 16 + threadIdx.x, sync.epoch, sync.budget, sync.status, 981);
+    }
+    if (threadIdx.x == 0) mine[32] = 0;
+  }
+}
+
+template <int DTYPE, int MAXP>
+__device__ __forceinline__ void cp_merge_rows(const PeerMergeArgs& args, int world, int dests,
+                                              long long row_begin, int d, long long idx) {
+  const int per_row = d >> 3;
   const long long row = row_begin + idx / per_row;
   const int col = static_cast<int>(idx % per_row) * 8;
   const size_t elem = static_cast<size_t>(row) * d + col;
@@ -273,16 +351,17 @@ cp_merge_peer_kernel(PeerMergeArgs args, int world, int dests, long long row_beg
 }
 
 template <int DTYPE>
-void launch_merge(const PeerMergeArgs& args, int parts, int dests, long long row_begin, long long row_end,
-                  int d, cudaStream_t stream) {
+void launch_merge(const PeerMergeArgs& args, const PeerSync& sync, int parts, int dests, long long row_begin,
+                  long long row_end, int d, cudaStream_t stream) {
   const long long total = (row_end - row_begin) * (d >> 3);
-  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  // with the flag protocol even a rank without rows takes part (one block)
+  const unsigned blocks = static_cast<unsigned>(total > 0 ? (total + 255) / 256 : 1);
   if (parts <= 4)
-    cp_merge_peer_kernel<DTYPE, 4><<<blocks, 256, 0, stream>>>(args, parts, dests, row_begin, row_end, d);
+    cp_merge_peer_kernel<DTYPE, 4><<<blocks, 256, 0, stream>>>(args, sync, parts, dests, row_begin, row_end, d);
   else if (parts <= 8)
-    cp_merge_peer_kernel<DTYPE, 8><<<blocks, 256, 0, stream>>>(args, parts, dests, row_begin, row_end, d);
+    cp_merge_peer_kernel<DTYPE, 8><<<blocks, 256, 0, stream>>>(args, sync, parts, dests, row_begin, row_end, d);
   else
-    cp_merge_peer_kernel<DTYPE, MAX_PARTS><<<blocks, 256, 0, stream>>>(args, parts, dests, row_begin, row_end, d);
+    cp_merge_peer_kernel<DTYPE, MAX_PARTS><<<blocks, 256, 0, stream>>>(args, sync, parts, dests, row_begin, row_end, d);
 }
 
 // ---- finish of the mixed-dimensional read ------------------------------------------------------
@@ -516,8 +595,9 @@ int lse_merge(const void* const* outs, const float* const* lses, int parts, int6
     for (int p = 0; p < parts; ++p) { wide.part_out[p] = outs[p]; wide.part_lse[p] = lses[p]; }
     wide.dst_out[0] = out;
     wide.dst_lse[0] = lse_out;
-    if (dtype == NKV_F32) launch_merge<NKV_F32>(wide, parts, 1, 0, rows, d, stream);
-    else launch_merge<NKV_BF16>(wide, parts, 1, 0, rows, d, stream);
+    const PeerSync none{};
+    if (dtype == NKV_F32) launch_merge<NKV_F32>(wide, none, parts, 1, 0, rows, d, stream);
+    else launch_merge<NKV_BF16>(wide, none, parts, 1, 0, rows, d, stream);
     NKV_LAUNCH_CHECK("cp_merge_peer_kernel");
     return NKV_OK;
   }
@@ -532,7 +612,8 @@ int lse_merge(const void* const* outs, const float* const* lses, int parts, int6
 
 int cp_merge_peer(const void* const* part_out, const float* const* part_lse, void* const* dst_out,
                   float* const* dst_lse, int world, int64_t rows, int d, int64_t row_begin,
-                  int64_t row_end, int dtype, cudaStream_t stream) {
+                  int64_t row_end, int dtype, cudaStream_t stream, int32_t* const* flags, int rank,
+                  int epoch, long long budget_cycles, int32_t* status) {
   NKV_REQUIRE(world >= 1 && world <= MAX_PARTS, NKV_ERR_TOO_LARGE,
               "peer merge takes 1..%d ranks, got %d", MAX_PARTS, world);
   NKV_REQUIRE(d % 8 == 0, NKV_ERR_INVALID, "peer merge width %d must be a multiple of 8", d);
@@ -540,6 +621,7 @@ int cp_merge_peer(const void* const* part_out, const float* const* part_lse, voi
               "peer merge rows [%lld, %lld) outside [0, %lld)", static_cast<long long>(row_begin),
               static_cast<long long>(row_end), static_cast<long long>(rows));
   PeerMergeArgs args{};
+  PeerSync sync{};
   for (int p = 0; p < world; ++p) {
     NKV_REQUIRE(part_out[p] && part_lse[p] && dst_out[p] && dst_lse[p], NKV_ERR_INVALID,
                 "peer merge: null buffer of rank %d", p);
@@ -550,10 +632,21 @@ int cp_merge_peer(const void* const* part_out, const float* const* part_lse, voi
     args.dst_out[p] = dst_out[p];
     args.dst_lse[p] = dst_lse[p];
   }
-  if (row_end == row_begin) return NKV_OK;
-  if (dtype == NKV_F32) launch_merge<NKV_F32>(args, world, world, row_begin, row_end, d, stream);
-  else if (dtype == NKV_BF16) launch_merge<NKV_BF16>(args, world, world, row_begin, row_end, d, stream);
-  else launch_merge<NKV_F16>(args, world, world, row_begin, row_end, d, stream);
+  if (flags != nullptr) {
+    NKV_REQUIRE(rank >= 0 && rank < world && epoch > 0 && budget_cycles > 0, NKV_ERR_INVALID,
+                "peer exchange: rank=%d of %d, epoch=%d, budget=%lld", rank, world, epoch, budget_cycles);
+    for (int p = 0; p < world; ++p) {
+      NKV_REQUIRE(flags[p] != nullptr && (reinterpret_cast<uintptr_t>(flags[p]) & 3) == 0, NKV_ERR_INVALID,
+                  "peer exchange: flag block of rank %d", p);
+      sync.flags[p] = flags[p];
+    }
+    sync.rank = rank; sync.epoch = epoch; sync.budget = budget_cycles; sync.status = status;
+  } else if (row_end == row_begin) {
+    return NKV_OK;
+  }
+  if (dtype == NKV_F32) launch_merge<NKV_F32>(args, sync, world, world, row_begin, row_end, d, stream);
+  else if (dtype == NKV_BF16) launch_merge<NKV_BF16>(args, sync, world, world, row_begin, row_end, d, stream);
+  else launch_merge<NKV_F16>(args, sync, world, world, row_begin, row_end, d, stream);
   NKV_LAUNCH_CHECK("cp_merge_peer_kernel");
   return NKV_OK;
 }

@@ -50,7 +50,8 @@ int unpack_int8(const int8_t* q, const void* scale_bf16, int64_t rows, int cols,
                 void* out_bf16, cudaStream_t stream);
 int cp_merge_peer(const void* const* part_out, const float* const* part_lse, void* const* dst_out,
                   float* const* dst_lse, int world, int64_t rows, int d, int64_t row_begin,
-                  int64_t row_end, int dtype, cudaStream_t stream);
+                  int64_t row_end, int dtype, cudaStream_t stream, int32_t* const* flags = nullptr,
+                  int rank = 0, int epoch = 0, long long budget_cycles = 0, int32_t* status = nullptr);
 
 // ---- tcgen05 / TMA kernels (nkv_tc_*.cu), bf16 operands, fp32 accumulation
 int tc_assign(const void* x_bf16, const void* centers_bf16, int S, int J, int C, void* ids,

@@ -565,6 +565,26 @@ def cp_merge_peer(part_out_ptrs, part_lse_ptrs, dst_out_ptrs, dst_lse_ptrs, *, r
         int(row_end), dtype_code(dtype), _stream(device)))
 
 
+PEER_FLAG_WORDS = 64
+
+
+def cp_exchange_peer(part_out_ptrs, part_lse_ptrs, dst_out_ptrs, dst_lse_ptrs, flag_ptrs, *, rank: int,
+                     rows: int, width: int, row_begin: int, row_end: int, dtype: torch.dtype, epoch: int,
+                     device, status: torch.Tensor | None = None, budget_cycles: int = 0) -> None:
+    """cp_merge_peer with the ranks ordered by flag words in peer memory instead of collectives
+    (nkv_cp_exchange_peer): one launch per rank and layer."""
+    world = len(part_out_ptrs)
+    arrays = [(ctypes.c_void_p * world)(*[int(v) for v in values])
+              for values in (part_out_ptrs, part_lse_ptrs, dst_out_ptrs, dst_lse_ptrs, flag_ptrs)]
+    device = torch.device(device)
+    if status is None:
+        status = status_word(device)
+    _lib.check(_lib.library().nkv_cp_exchange_peer(
+        arrays[0], arrays[1], arrays[2], arrays[3], arrays[4], world, int(rank), int(rows), int(width),
+        int(row_begin), int(row_end), dtype_code(dtype), int(epoch), int(budget_cycles), _ptr(status),
+        _stream(device)))
+
+
 def lse_merge(partials):
     """[(O [rows..., d], lse [rows...])] -> merged (O, lse); an empty partition is (0, -inf)."""
     outs = [o for o, _ in partials]

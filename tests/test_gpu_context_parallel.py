@@ -95,3 +95,50 @@ def test_two_ranks_exchange_over_peer_memory():
          str(ROOT / "tests" / "cp_peer_worker.py")],
         env=env, capture_output=True, text=True, timeout=600)
     assert run.returncode == 0, run.stdout[-2000:] + run.stderr[-2000:]
+
+
+def test_flag_ordered_exchange_of_one_rank_matches_the_merge():
+    """world = 1: the flag protocol is satisfied by the rank itself; the result is the plain merge's."""
+    from nanokv_b200 import ops
+    device = torch.device("cuda", 0)
+    gen = torch.Generator().manual_seed(3)
+    out = torch.randn(50, 2, 64, generator=gen).to(torch.bfloat16).to(device)
+    lse = torch.randn(50, 2, generator=gen).to(device)
+    got_out, got_lse = torch.full_like(out, float("nan")), torch.full_like(lse, float("nan"))
+    flags = torch.zeros(ops.PEER_FLAG_WORDS, dtype=torch.int32, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    for epoch in (1, 2, 3):                                   # the same buffers, call after call
+        ops.cp_exchange_peer([out.data_ptr()], [lse.data_ptr()], [got_out.data_ptr()], [got_lse.data_ptr()],
+                             [flags.data_ptr()], rank=0, rows=100, width=64, row_begin=0, row_end=100,
+                             dtype=torch.bfloat16, epoch=epoch, device=device, status=status)
+    torch.cuda.synchronize()
+    want_out, want_lse = ops.lse_merge([(out, lse)])
+    assert int(status.item()) == 0
+    assert torch.equal(got_out.view(torch.int16), want_out.view(torch.int16))
+    assert torch.equal(got_lse, want_lse)
+    assert flags[:1].tolist() == [3] and flags[16:17].tolist() == [3] and int(flags[32]) == 0
+
+
+def test_exchange_gives_up_when_a_peer_never_arrives():
+    """Two ranks' buffers on one GPU, only rank 0's kernel runs: rank 1 never reports its partial, so
+    rank 0's wait runs out of its (short) budget, the kernel returns without merging and the status
+    word names the wait site.  Nothing hangs or faults; the context stays usable."""
+    from nanokv_b200 import _lib, ops
+    device = torch.device("cuda", 0)
+    parts = [(torch.ones(8, 1, 8, dtype=torch.bfloat16, device=device), torch.zeros(8, 1, device=device))
+             for _ in range(2)]
+    results = [(torch.full((8, 1, 8), 5.0, dtype=torch.bfloat16, device=device),
+                torch.full((8, 1), 5.0, device=device)) for _ in range(2)]
+    flags = [torch.zeros(ops.PEER_FLAG_WORDS, dtype=torch.int32, device=device) for _ in range(2)]
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    ops.cp_exchange_peer([o.data_ptr() for o, _ in parts], [l.data_ptr() for _, l in parts],
+                         [o.data_ptr() for o, _ in results], [l.data_ptr() for _, l in results],
+                         [f.data_ptr() for f in flags], rank=0, rows=8, width=8, row_begin=0, row_end=4,
+                         dtype=torch.bfloat16, epoch=1, device=device, status=status, budget_cycles=1 << 17)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 980
+    assert all(bool((o == 5.0).all()) and bool((l == 5.0).all()) for o, l in results)   # nothing merged
+    assert flags[1][0].item() == 1                      # rank 0 did announce its partial to rank 1
+    with pytest.raises(RuntimeError, match="device-side wait"):
+        _lib.check_device_status(int(status.item()))
+    assert float(torch.ones(3, device=device).sum()) == 3.0
