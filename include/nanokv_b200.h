@@ -466,6 +466,20 @@ int nkv_history_moments(const nkv_history* hist, float* latent_sum, int32_t* cen
                         void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The two small per-head linear maps of a reader group of the mixed-dimensional read:
+ *     out[n, g, e] = sum_d x[n, head(g), d] * w[g, d, e],   head(g) = heads[g] (g when heads is NULL)
+ * fp32 accumulation, one rounding to `dtype`; columns [dout, dout_pad) of out are zero.  With
+ * w = q_reduce [h, D, d] and x the pre-positional queries [Q, H, D] this is the reduced query
+ * (query MGC/core.py:164-166, LB/codec_native_attention.py:115-116), with w = lift [h, d, D] and x
+ * the low-width attention output the lifted value (lift_value MGC/core.py:202-204,
+ * LB/codec_native_attention.py:210-211).  x strides in elements; w [group_heads, din, dout] and
+ * out [rows, group_heads, dout_pad] contiguous; dtype NKV_BF16 | NKV_F32 for x, w and out.
+ */
+int nkv_head_linear(const void* x, int dtype, int64_t stride_row, int64_t stride_head,
+                    const int32_t* heads, const void* w, int64_t rows, int group_heads, int din,
+                    int dout, int dout_pad, void* out, void* stream);
+
+/*
  * Finish of the mixed-dimensional (NanoKV-Fast) read for one head group, one launch:
  * the value-mean correction, the log-sum-exp merge of the full-width partial with the
  * lifted low-width partial, and the scatter of the group's heads to their places

@@ -100,6 +100,8 @@ SIGNATURES = {
     "nkv_cp_exchange_peer": (c_int, [POINTER(c_void_p), POINTER(c_void_p), POINTER(c_void_p),
                                      POINTER(c_void_p), POINTER(c_void_p), c_int, c_int, c_int64, c_int,
                                      c_int64, c_int64, c_int, c_int, ctypes.c_longlong, c_void_p, c_void_p]),
+    "nkv_head_linear": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int,
+                                c_int, c_int, c_void_p, c_void_p]),
     "nkv_set_bf16_path": (c_int, [c_int]),
     "nkv_selftest_bounded_wait": (c_int, [c_int, ctypes.c_longlong, c_void_p, c_void_p]),
     "nkv_peer_open": (c_int, [c_char_p, POINTER(c_void_p)]),

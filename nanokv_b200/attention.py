@@ -302,8 +302,8 @@ def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segment
         value_mean = compressed_value_mean(low_segments, moments, heads=H, native_dim=reader.native_dim)
     for group in reader.groups:
         head = group.heads
-        query = torch.einsum("nhd,hde->nhe", q_pre.index_select(1, head), group.q_reduce)
-        query = group._pad_last(query)
+        # reduced query of the group's heads, zero-padded to the kernel's tile width (own kernel)
+        query = ops.head_linear(q_pre, group.q_reduce, heads=head, pad_to=group.padded)
         if rope is not None:
             if group.pair_index is None or q_positions is None:
                 raise ValueError("the selected RoPE needs the group's indices and the query positions")
@@ -357,7 +357,7 @@ def hybrid_attention(q_pre: torch.Tensor, q_native: torch.Tensor, native_segment
         # the running (O, lse) of the group's heads lives in ``result`` / ``running_lse``
         source, source_lse = native_out, native_lse
         for oo, ll in partials:
-            lifted = torch.einsum("nhe,hed->nhd", oo[..., :group.width], group.lift).contiguous()
+            lifted = ops.head_linear(oo, group.lift, din=group.width)   # [Q, h, D]
             ops.fast_finish(source, source_lse, lifted, ll, head, result, value_mean=mean_rows,
                             projected_mean=projected, out_lse=running_lse)
             source, source_lse = result, running_lse

@@ -457,6 +457,15 @@ int nkv_operator_unpack_int8(const int8_t* qweight, const void* scale_bf16, int6
                      static_cast<cudaStream_t>(stream));
 }
 
+int nkv_head_linear(const void* x, int dtype, int64_t stride_row, int64_t stride_head,
+                    const int32_t* heads, const void* w, int64_t rows, int group_heads, int din, int dout,
+                    int dout_pad, void* out, void* stream) {
+  NKV_REQUIRE(x && w && out && rows >= 0, NKV_ERR_INVALID, "head_linear: null argument or rows=%lld",
+              static_cast<long long>(rows));
+  return head_linear(x, dtype, stride_row, stride_head, heads, w, rows, group_heads, din, dout, dout_pad,
+                     out, static_cast<cudaStream_t>(stream));
+}
+
 int nkv_fast_finish(const void* native, const float* native_lse, const void* lifted, const float* low_lse,
                     const int32_t* heads, const float* value_mean, const float* projected_mean,
                     int64_t rows, int total_heads, int group_heads, int d, int dtype, void* out,

@@ -694,6 +694,70 @@ int fast_finish(const void* native, const float* native_lse, const void* lifted,
   return NKV_OK;
 }
 
+// ---- per-head small linear maps of the mixed-dimensional read -----------------------------------
+// out[n, g, e] = sum_d x[n, head(g), d] * w[g, d, e]  (fp32 accumulation, one rounding):
+// the query reduction q_reduce [h, D, d] and the value lift [h, d, D] of a reader group.
+// Block = 32 rows of one group head; the head's matrix sits in shared memory as fp32; a thread owns
+// one row and every eighth output column.
+template <int DTYPE>
+__global__ void __launch_bounds__(256)
+head_linear_kernel(const void* x, long long stride_row, long long stride_head, const int32_t* heads,
+                   const void* w, long long rows, int din, int dout, int dout_pad, void* out) {
+  extern __shared__ float head_linear_smem[];
+  float* ws = head_linear_smem;                 // [din][dout]
+  float* xs = head_linear_smem + din * dout;    // [32][din + 1]
+  const int g = blockIdx.y;
+  const int head = heads ? heads[g] : g;
+  const long long row0 = static_cast<long long>(blockIdx.x) * 32;
+  for (int i = threadIdx.x; i < din * dout; i += 256)
+    ws[i] = load_float(w, DTYPE, static_cast<size_t>(g) * din * dout + i);
+  for (int i = threadIdx.x; i < 32 * din; i += 256) {
+    const int r = i / din, d = i - r * din;
+    const long long row = row0 + r;
+    xs[r * (din + 1) + d] = row < rows
+        ? load_float(x, DTYPE, static_cast<size_t>(row * stride_row + head * stride_head + d)) : 0.f;
+  }
+  __syncthreads();
+  const int r = threadIdx.x >> 3, c0 = threadIdx.x & 7;
+  const long long row = row0 + r;
+  if (row >= rows) return;
+  const size_t base = (static_cast<size_t>(row) * gridDim.y + g) * dout_pad;
+  for (int e = c0; e < dout_pad; e += 8) {
+    float acc = 0.f;
+    if (e < dout) {
+      const float* xr = xs + r * (din + 1);
+      for (int d = 0; d < din; ++d) acc = fmaf(xr[d], ws[d * dout + e], acc);
+    }
+    store_float(out, DTYPE, base + e, acc);
+  }
+}
+
+int head_linear(const void* x, int dtype, int64_t stride_row, int64_t stride_head, const int32_t* heads,
+                const void* w, int64_t rows, int group_heads, int din, int dout, int dout_pad, void* out,
+                cudaStream_t stream) {
+  NKV_REQUIRE(dtype == NKV_BF16 || dtype == NKV_F32, NKV_ERR_UNSUPPORTED, "head_linear: dtype %d", dtype);
+  NKV_REQUIRE(group_heads > 0 && din > 0 && dout > 0 && dout_pad >= dout, NKV_ERR_INVALID,
+              "head_linear: heads=%d din=%d dout=%d pad=%d", group_heads, din, dout, dout_pad);
+  const size_t smem = (static_cast<size_t>(din) * dout + 32 * (din + 1)) * sizeof(float);
+  NKV_REQUIRE(smem <= 200 * 1024, NKV_ERR_UNSUPPORTED, "head_linear: a %d x %d map does not fit shared memory",
+              din, dout);
+  if (rows == 0) return NKV_OK;
+  dim3 grid(static_cast<unsigned>((rows + 31) / 32), static_cast<unsigned>(group_heads));
+  if (dtype == NKV_F32) {
+    NKV_CUDA(cudaFuncSetAttribute(head_linear_kernel<NKV_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(smem)));
+    head_linear_kernel<NKV_F32><<<grid, 256, smem, stream>>>(x, stride_row, stride_head, heads, w, rows, din,
+                                                             dout, dout_pad, out);
+  } else {
+    NKV_CUDA(cudaFuncSetAttribute(head_linear_kernel<NKV_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(smem)));
+    head_linear_kernel<NKV_BF16><<<grid, 256, smem, stream>>>(x, stride_row, stride_head, heads, w, rows, din,
+                                                              dout, dout_pad, out);
+  }
+  NKV_LAUNCH_CHECK("head_linear_kernel");
+  return NKV_OK;
+}
+
 size_t history_moments_workspace_bytes(int tokens, int rank) {
   const size_t slabs = (static_cast<size_t>(tokens > 0 ? tokens : 0) + MOMENT_SLAB - 1) / MOMENT_SLAB;
   return slabs * static_cast<size_t>(rank) * sizeof(float);

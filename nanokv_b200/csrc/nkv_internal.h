@@ -43,6 +43,9 @@ int fast_finish(const void* native, const float* native_lse, const void* lifted,
                 const int32_t* heads, const float* mean, const float* projected, int64_t rows,
                 int total_heads, int group_heads, int d, int dtype, void* out, float* out_lse,
                 cudaStream_t stream);
+int head_linear(const void* x, int dtype, int64_t stride_row, int64_t stride_head, const int32_t* heads,
+                const void* w, int64_t rows, int group_heads, int din, int dout, int dout_pad, void* out,
+                cudaStream_t stream);
 size_t history_moments_workspace_bytes(int tokens, int rank);
 int history_moments(const nkv_history& h, float* latent_sum, int32_t* center_counts, void* workspace,
                     cudaStream_t stream);

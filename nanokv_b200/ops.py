@@ -565,6 +565,29 @@ def cp_merge_peer(part_out_ptrs, part_lse_ptrs, dst_out_ptrs, dst_lse_ptrs, *, r
         int(row_end), dtype_code(dtype), _stream(device)))
 
 
+def head_linear(x: torch.Tensor, w: torch.Tensor, *, heads: torch.Tensor | None = None,
+                din: int | None = None, pad_to: int | None = None) -> torch.Tensor:
+    """out[n, g, :] = x[n, head(g), :din] @ w[g]  (nkv_head_linear): the query reduction and the value
+    lift of a reader group.  x [S, H, >= din] (last dimension contiguous), w [h, din, dout] in x's dtype,
+    ``heads`` i32 [h] picks the heads of x (default: head g), ``pad_to`` zero-pads the output columns."""
+    device = _require_cuda(w)
+    if not x.is_cuda or x.device != device:
+        raise RuntimeError("nanokv_b200 runs on CUDA tensors only (there is no CPU path)")
+    if x.stride(2) != 1 or x.dtype != w.dtype:
+        raise ValueError("head_linear takes rows contiguous along the last dimension, in the weights' dtype")
+    h, w_in, dout = w.shape
+    din = w_in if din is None else int(din)
+    if din != w_in or x.shape[2] < din:
+        raise ValueError("head_linear: input width does not match the weights")
+    pad = dout if pad_to is None else int(pad_to)
+    out = torch.empty(x.shape[0], h, pad, dtype=x.dtype, device=device)
+    index = None if heads is None else heads.to(device=device, dtype=torch.int32).contiguous()
+    _lib.check(_lib.library().nkv_head_linear(
+        _ptr(x), dtype_code(x.dtype), x.stride(0), x.stride(1), _ptr(index), _ptr(w.contiguous()),
+        x.shape[0], h, din, dout, pad, _ptr(out), _stream(device)))
+    return out
+
+
 PEER_FLAG_WORDS = 64
 
 

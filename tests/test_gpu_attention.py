@@ -433,3 +433,23 @@ def test_fast_finish_rejects_bad_arguments():
     with pytest.raises(ValueError):
         ops.fast_finish(native, lse, native[:, :1].contiguous(), lse[:, :1].contiguous(), heads, native,
                         value_mean=torch.zeros(2, 16, device=dev))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("din,dout,pad", [(128, 32, 64), (32, 128, 128), (128, 128, 128), (24, 40, 48)])
+def test_head_linear_is_the_per_head_matrix_product(dtype, din, dout, pad):
+    """q_reduce / lift of a reader group on the library's own kernel against fp64 arithmetic."""
+    gen = torch.Generator().manual_seed(din * 1000 + dout)
+    x = torch.randn(77, 6, max(din, 64), generator=gen).to(dtype).cuda()
+    w = (torch.randn(3, din, dout, generator=gen) / din ** 0.5).to(dtype).cuda()
+    heads = torch.tensor([4, 0, 5])
+    got = ops.head_linear(x, w, heads=heads.cuda(), din=din, pad_to=pad)
+    want = torch.einsum("nhd,hde->nhe", x.cpu().double()[:, heads, :din], w.cpu().double())
+    assert got.shape == (77, 3, pad) and got.dtype == dtype
+    assert bool((got[..., dout:] == 0).all())
+    tol = 2.0 ** -7 if dtype == torch.bfloat16 else 1e-5
+    assert float((got[..., :dout].cpu().double() - want).abs().max()) <= tol * float(want.abs().max())
+    # without a head list: head g of x goes with matrix g
+    same = ops.head_linear(x[:, :3], w, din=din)
+    plain = torch.einsum("nhd,hde->nhe", x.cpu().double()[:, :3, :din], w.cpu().double())
+    assert float((same.cpu().double() - plain).abs().max()) <= tol * float(plain.abs().max())
