@@ -206,11 +206,12 @@ class ReaderGroup:
 
 class Reader:
     """All groups of one layer; groups partition the heads (MGC/core.py:207-224)."""
+    group_class = ReaderGroup
 
     def __init__(self, payload: dict, *, dtype: torch.dtype, device="cuda"):
         self.heads, self.native_dim = int(payload["heads"]), int(payload["native_dim"])
         self.rank = int(payload["rank"])
-        self.groups = [ReaderGroup(s, dtype=dtype, device=device, native_dim=self.native_dim)
+        self.groups = [self.group_class(s, dtype=dtype, device=device, native_dim=self.native_dim)
                        for s in payload["groups"]]
         listed = sorted(int(h) for g in self.groups for h in g.heads.tolist())
         if listed != list(range(self.heads)):

@@ -172,3 +172,17 @@ class CompressedHistory:
         """Bytes of payload actually in use (codes, scales, ids, centre tables)."""
         per_token = self.rank // 2 + 2 * (self.rank // self.group) + self.ids.element_size()
         return self.tokens * per_token + self._center_used * self.centers.shape[1] * 2
+
+
+class PackedRows:
+    """Rows of one payload segment as the kernels read them (codes, scales, centre ids and table in
+    the payload's packed form) with the operator mean f32 [J]; after a token selection ``visible``
+    lists the kept rows.  It stands where the reference hands a dequantised latent tensor to its
+    readers (MGM/nanokv_codec.py direct_latent_pair_segments): here no latent row exists in HBM."""
+
+    def __init__(self, history: CompressedHistory, mean: torch.Tensor, visible: torch.Tensor | None = None):
+        self.history, self.mean, self.visible = history, mean, visible
+
+    @property
+    def tokens(self) -> int:
+        return self.history.tokens if self.visible is None else int(self.visible.numel())

@@ -1,0 +1,195 @@
+"""LingBot rolling-cache attention on the B200 kernels.
+
+Two entry points over the same cache dictionary the reference keeps per layer
+(LB/lingbot_v2_cache_runtime.py:337-352, ``configure_cache``):
+
+* ``codec_cache_attention_inputs`` has the reference's name, argument list, return value and side
+  effects (LB/lingbot_v2_cache_runtime.py:263-334): windowed history K / V / positions with the
+  current chunk appended, cut to ``max_attention_size``; commit + prune when the cache asks for it.
+  It is the import-swap form: the caller still runs its own RoPE and attention on the returned
+  rows, so K and V of the window are written to HBM once by the decode kernel.
+* ``codec_cache_attention`` does the whole step and returns the attention output: the window is
+  read straight from the packed payloads by the fused kernel (keys rotated in-kernel by their
+  absolute positions), the current chunk is attended as plain rows, and the partial results are
+  merged by log-sum-exp.  No history row is materialised.  Same cache side effects.
+
+The window policy (sink + recent, pruning, pieces of a cut segment) is ``lifecycle``'s.
+"""
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+
+from . import attention, lifecycle, ops
+from .lingbot_codec import decode_segments, encode_pair, history_from_payloads, operator_of
+
+
+def configure_cache(cache: dict[str, Any], *, layer: int, sp_rank: int, options: dict[str, Any]) -> None:
+    """Attach the run's options and the empty per-layer codec state."""
+    cache.update(options)
+    cache.update({"codec_layer": int(layer), "codec_sp_rank": int(sp_rank), "codec_segments": [],
+                  "codec_committed_end": 0, "codec_commit": False, "codec_chunk_id": 0})
+
+
+def _ranges(segments: list[dict]) -> list[tuple[int, int]]:
+    return [(int(s["global_start"]), int(s["global_end"])) for s in segments]
+
+
+def _prune_segments(segments: list[dict], *, committed_end: int, capacity: int, sink_tokens: int) -> list[dict]:
+    keep = lifecycle.kept_segments(_ranges(segments), committed_end=committed_end, capacity=capacity,
+                                   sink_tokens=sink_tokens)
+    return [segments[i] for i in keep]
+
+
+def _window(segments: list[dict], *, committed_end: int, capacity: int, sink_tokens: int):
+    """(active segments, [(row start, row stop, position start)] over their stacked rows)."""
+    if not segments or committed_end <= 0:
+        return [], []
+    ranges = _ranges(segments)
+    pieces = lifecycle.active_pieces(ranges, committed_end=committed_end, capacity=capacity,
+                                     sink_tokens=sink_tokens)
+    used = sorted({index for index, _, _ in pieces})
+    base, total = {}, 0
+    for index in used:
+        base[index] = total
+        total += ranges[index][1] - ranges[index][0]
+    runs = [(base[i] + begin - ranges[i][0], base[i] + end - ranges[i][0], begin) for i, begin, end in pieces]
+    return [segments[i] for i in used], runs
+
+
+def _positions(runs, device, dtype=torch.long) -> torch.Tensor:
+    return torch.cat([torch.arange(p, p + (b - a), device=device, dtype=dtype) for a, b, p in runs])
+
+
+def _decode_active_history(segments: list[dict], *, committed_end: int, capacity: int, sink_tokens: int,
+                           dtype: torch.dtype, device, cache: dict | None = None):
+    """(K [1,N,H,D], V [1,N,H,D], positions [N]) of the window, or None when it is empty: one
+    decode launch per target over the rows the window shows (LB/lingbot_v2_cache_runtime.py:122-191)."""
+    if cache is not None and cache.get("a1_controller") is not None:
+        raise NotImplementedError("the A1 training controller is not part of the inference path")
+    active, runs = _window(segments, committed_end=committed_end, capacity=capacity, sink_tokens=sink_tokens)
+    if not runs:
+        return None
+    rows = torch.cat([torch.arange(a, b, device=device, dtype=torch.int32) for a, b, _ in runs])
+    key, value = decode_segments(active, dtype=dtype, device=device, rows=rows)
+    return key, value, _positions(runs, device)
+
+
+def _cut(runs, current: int, *, protected: int, limit: int):
+    """The reference's overflow rule on the concatenation [window rows..., current chunk]: keep the
+    first ``protected`` rows and the newest ``limit - protected`` ones
+    (LB/lingbot_v2_cache_runtime.py:301-314).  ``protected`` never exceeds the sink rows the window
+    starts with, so the prefix lies in the history.  Returns (history runs, rows cut from the front
+    of the current chunk)."""
+    total = sum(b - a for a, b, _ in runs) + current
+    if total <= limit:
+        return runs, 0
+    keep = ((0, protected), (max(protected, total - (limit - protected)), total))
+    out, cursor = [], 0
+    for a, b, p in runs:
+        for low, high in keep:
+            begin, end = max(cursor, low), min(cursor + b - a, high)
+            if begin < end:
+                out.append((a + begin - cursor, a + end - cursor, p + begin - cursor))
+        cursor += b - a
+    return out, min(current, max(0, keep[1][0] - cursor))
+
+
+def _commit(cache: dict, key: torch.Tensor, value: torch.Tensor, *, current_start: int, capacity: int,
+            sink_tokens: int) -> None:
+    committed_end = int(cache.get("codec_committed_end", 0))
+    current_end = current_start + int(key.shape[1])
+    if cache.get("codec_commit", False):
+        if current_start != committed_end:
+            raise RuntimeError(f"non-causal codec commit: start={current_start}, committed={committed_end}")
+        cache["codec_commit_start"] = current_start
+        segments = cache.setdefault("codec_segments", [])
+        segments.append(encode_pair(key, value, cache=cache))
+        cache["codec_committed_end"] = current_end
+        cache["codec_segments"] = _prune_segments(segments, committed_end=current_end, capacity=capacity,
+                                                  sink_tokens=sink_tokens)
+    for name, end in (("global_end_index", current_end), ("local_end_index", min(current_end, capacity))):
+        if torch.is_tensor(cache.get(name)):
+            cache[name].fill_(end)
+
+
+@torch.no_grad()
+def codec_cache_attention_inputs(cache: dict[str, Any], key: torch.Tensor, value: torch.Tensor, *,
+                                 current_start: int, capacity: int, sink_tokens: int,
+                                 max_attention_size: int):
+    """history + current K / V [1,N,H,D] and positions [N]; commits the chunk when
+    ``cache["codec_commit"]``.  ``key`` is pre-RoPE, ``value`` the raw projection."""
+    segments = cache.setdefault("codec_segments", [])
+    committed_end = int(cache.get("codec_committed_end", 0))
+    device, current = key.device, int(key.shape[1])
+    active, runs = _window(segments, committed_end=committed_end, capacity=capacity, sink_tokens=sink_tokens)
+    protected = min(sink_tokens, committed_end, max_attention_size)
+    kept, lead = _cut(runs, current, protected=protected, limit=max_attention_size)
+    stop = current
+    now = torch.arange(current_start + lead, current_start + stop, device=device)
+    if kept:
+        rows = torch.cat([torch.arange(a, b, device=device, dtype=torch.int32) for a, b, _ in kept])
+        hist_k, hist_v = decode_segments(active, dtype=value.dtype, device=device, rows=rows)
+        key_cache = torch.cat((hist_k, key[:, lead:stop]), dim=1)
+        value_cache = torch.cat((hist_v, value[:, lead:stop]), dim=1)
+        positions = torch.cat((_positions(kept, device), now))
+    else:
+        key_cache, value_cache, positions = key[:, lead:stop], value[:, lead:stop], now
+    _commit(cache, key, value, current_start=current_start, capacity=capacity, sink_tokens=sink_tokens)
+    return key_cache, value_cache, positions
+
+
+@torch.no_grad()
+def codec_cache_attention(cache: dict[str, Any], query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, *,
+                          current_start: int, capacity: int, sink_tokens: int, max_attention_size: int,
+                          rope: "attention.RopeTable | None" = None, scale: float | None = None,
+                          status: torch.Tensor | None = None):
+    """Attention output [1,S,H,D] (and lse f32 [S,H]) of ``query`` over the window and the current chunk.
+
+    ``query`` arrives rotated; ``key`` is pre-RoPE and is rotated here by ``rope`` at positions
+    ``current_start + i``; the history's keys are rotated inside the fused kernel.  Replaces
+    codec_cache_attention_inputs + rope_pre_key_by_positions + flash attention at the reference's
+    call site (LB/model_fast.py:170-195) without writing a history row to HBM."""
+    if query.ndim != 4 or query.shape[0] != 1:
+        raise ValueError(f"expected [1,S,H,D], got {tuple(query.shape)}")
+    segments = cache.setdefault("codec_segments", [])
+    committed_end = int(cache.get("codec_committed_end", 0))
+    device, current = key.device, int(key.shape[1])
+    head_dim = int(query.shape[-1])
+    scale = head_dim ** -0.5 if scale is None else scale
+    active, runs = _window(segments, committed_end=committed_end, capacity=capacity, sink_tokens=sink_tokens)
+    protected = min(sink_tokens, committed_end, max_attention_size)
+    kept, lead = _cut(runs, current, protected=protected, limit=max_attention_size)
+    stop = current
+    q = query[0]
+    partials = []
+    if kept:
+        hist_k = history_from_payloads([s["k"] for s in active], device=device)
+        hist_v = history_from_payloads([s["v"] for s in active], device=device)
+        op_k, op_v = operator_of(active[0]["k"], device), operator_of(active[0]["v"], device)
+        merged: list[list[int]] = []
+        for a, b, p in kept:                       # adjacent pieces become one launch
+            if merged and merged[-1][1] == a:
+                merged[-1][1] = b
+                merged[-1][2].append((p, p + b - a))
+            else:
+                merged.append([a, b, [(p, p + b - a)]])
+        for a, b, spans in merged:
+            positions = None
+            if rope is not None:
+                positions = torch.cat([torch.arange(s, e, device=device, dtype=torch.int32) for s, e in spans])
+            partials.append(attention.codec_attention(
+                q, hist_k.view_tokens(a, b), hist_v.view_tokens(a, b), op_k, op_v, scale=scale,
+                status=status, rope=rope, positions=positions))
+    if stop > lead:
+        rows_k = key[0, lead:stop]
+        if rope is not None:
+            now = torch.arange(current_start + lead, current_start + stop, device=device, dtype=torch.int32)
+            rows_k = rope.rotate(rows_k, now)
+        partials.append(ops.attention_lse(q, rows_k, value[0, lead:stop], scale=scale))
+    if not partials:
+        raise ValueError("nothing to attend to")
+    out, lse = partials[0] if len(partials) == 1 else ops.lse_merge(partials)
+    _commit(cache, key, value, current_start=current_start, capacity=capacity, sink_tokens=sink_tokens)
+    return out[None], lse

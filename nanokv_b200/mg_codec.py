@@ -16,7 +16,7 @@ from typing import Any
 import torch
 
 from . import ops
-from .cache import CompressedHistory
+from .cache import CompressedHistory, PackedRows
 from .codec import F32_EPS, Operator, kmeans_init_rows
 
 CODEC = "worldplay_c64_pca_int4_v1"
@@ -227,3 +227,44 @@ def decode_value(value: Any, *, dtype: torch.dtype, device):
 def decode_pair_values(key: Any, value: Any, *, dtype: torch.dtype, device):
     return (decode_value(key, dtype=dtype, device=device),
             decode_value(value, dtype=dtype, device=device))
+
+
+@torch.no_grad()
+def direct_latent_pair_segments(key: Any, value: Any, *, device, token_keep: torch.Tensor | None = None):
+    """Paired K / V payload segments exposed for the low-width readers without reconstructing joint
+    K / V (MGF/nanokv_codec.py:708-797): one dictionary per segment with "k" / "v" (``PackedRows``:
+    the packed rows as stored, never dequantised to a latent tensor), "length" and
+    "logical_indices".  ``token_keep`` (bool over the whole history) keeps a subset; a segment it
+    empties is left out.  The stacked form of a payload is derived state cached on the payload."""
+    key_parts, value_parts = _parts(key), _parts(value)
+    if len(key_parts) != len(value_parts):
+        raise ValueError("paired codec segment count mismatch")
+    wanted = None
+    if token_keep is not None:
+        wanted = token_keep.to(device="cpu", dtype=torch.bool).reshape(-1)
+        if wanted.numel() != sum(int(value_shape(part)[1]) for part in key_parts):
+            raise ValueError("direct latent token mask/cache length mismatch")
+    result, offset = [], 0
+    for k_part, v_part in zip(key_parts, value_parts):
+        if (k_part.get("codec") != CODEC or v_part.get("codec") != CODEC or k_part.get("kind") != "k"
+                or v_part.get("kind") != "v" or tuple(k_part["shape"]) != tuple(v_part["shape"])
+                or int(k_part["layer"]) != int(v_part["layer"])):
+            raise RuntimeError("codec-native attention requires paired formal method payloads")
+        length = int(k_part["shape"][1])
+        local = None if wanted is None else wanted[offset:offset + length]
+        offset += length
+        if local is not None and not bool(local.any()):
+            continue
+        index = None if local is None else torch.nonzero(local).flatten().to(device)
+        rows = {}
+        for name, part in (("k", k_part), ("v", v_part)):
+            cached = part.get("_nkv_history")
+            if cached is None or cached.device.type != torch.device(device).type:
+                cached = part["_nkv_history"] = history_from_payloads([part], device=device)
+            rows[name] = PackedRows(cached, _operator(name, int(part["layer"]), device).mean, index)
+        logical = torch.arange(offset - length, offset, device=device)
+        if index is not None:
+            logical = logical.index_select(0, index)
+        result.append({"k": rows["k"], "v": rows["v"], "length": int(logical.numel()),
+                       "logical_indices": logical})
+    return result

@@ -210,3 +210,44 @@ def build_camera():
     indices = (blocks[:, :, None] * 8 + torch.arange(8)).reshape(heads, width)
     matrix = torch.randn(1, frames, 4, 4, 4, generator=gen)
     return {"value": value, "indices": indices, "matrix": matrix}
+
+
+# Matrix-Game positional hooks around the mixed-width read (rotation by per-token multipliers, PRoPE
+# camera blocks): FAST_CASES[1] with seeded multipliers and matrices
+HOOK_FRAMES = dict(query=2, low=4)
+
+
+def build_hooks(case: FastCase) -> dict:
+    """q_multiplier complex128 [Q, D/2]; per low segment "freqs" complex128 [tokens, D/2] and "camera"
+    (P^-1) [1, frames, 4, 4, 4]; "q_camera" (P^T) and "out_camera" (P) [1, frames, 4, 4, 4]."""
+    gen = synthetic.generator(case.codec.seed + 3000)
+    shape = case.codec.shape
+    half = shape.head_dim // 2
+
+    def multiplier(tokens):
+        angles = (torch.rand(tokens, half, generator=gen, dtype=torch.float64) - 0.5) * 40.0
+        return torch.polar(torch.ones_like(angles), angles)
+
+    def matrix(frames):
+        return torch.randn(1, frames, 4, 4, 4, generator=gen) * 0.5
+
+    out = {"q_multiplier": multiplier(shape.queries), "q_camera": matrix(HOOK_FRAMES["query"]),
+           "out_camera": matrix(HOOK_FRAMES["query"]), "segments": []}
+    for tokens in case.codec.segments[:case.low_segments]:
+        out["segments"].append({"freqs": multiplier(tokens), "camera": matrix(HOOK_FRAMES["low"])})
+    return out
+
+
+# LingBot streaming: the ROLLING chunks pushed through codec_cache_attention_inputs one by one, with
+# an attention limit small enough that the overflow cut applies to the late chunks
+STREAM_POLICY = dict(capacity=150, sink_tokens=40, max_attention_size=170)
+
+
+def protected_token_cases():
+    """(frame ids, recent, stride, sink): chronological frame runs with repeated ids, empty input."""
+    runs = lambda ids, per: torch.tensor([i for i in ids for _ in range(per)])
+    return [
+        (runs(range(12), 3), 4, 3, 1), (runs(range(12), 3), 0, 2, 0), (runs(range(12), 3), 20, 5, 0),
+        (runs([5, 5, 7, 5, 9, 9, 2], 2), 2, 2, 1), (runs(range(9), 1), 3, 0, 2),
+        (torch.tensor([], dtype=torch.long), 2, 1, 1), (runs(range(30), 2), 5, 7, 3),
+    ]

@@ -299,6 +299,103 @@ def run_value_mean_case(case: cases.CodecCase, root) -> dict:
             "input_digest": np.array([checksum(torch.cat(data["v_chunks"]))], dtype=np.uint64)}
 
 
+def run_fast_hooks_case(case: cases.FastCase, root) -> dict:
+    """hybrid_attention of codec_native/core.py with the Matrix-Game hooks: rope_selected on the
+    reduced query and the low-width keys, camera_selected on query, keys, values and output."""
+    codec = ref_import.load_mg_codec(root)
+    core = ref_import.load_mg_core(root)
+    os.environ["MG35_KVCODEC_C64_CLUSTERS"] = str(case.codec.shape.centers)
+    os.environ["MG35_KVCODEC_C64_ITERS"] = str(case.codec.iters)
+    for name in ("MG35_CODEC_NATIVE_FUSED_CAMERA", "MG35_CODEC_NATIVE_RUNTIME_OPT"):
+        os.environ.pop(name, None)
+    data = cases.build(case.codec)
+    shape = case.codec.shape
+    heads, dim, dtype = shape.heads, shape.head_dim, shape.torch_dtype
+    for kind in ("k", "v"):
+        op = data[f"{kind}_op"]
+        ref_import.inject_mg_operator(codec, kind, case.codec.layer, mean=op["mean"],
+                                      encoder=op["encoder"], decoder=op["decoder"])
+    payloads = {kind: [codec.encode_tensor(kind, case.codec.layer, chunk[None])
+                       for chunk in data[f"{kind}_chunks"]] for kind in ("k", "v")}
+    device = torch.device("cpu")
+    low = codec.direct_latent_pair_segments(
+        {"codec": "worldplay_segments_v1", "segments": payloads["k"][:case.low_segments]},
+        {"codec": "worldplay_segments_v1", "segments": payloads["v"][:case.low_segments]}, device=device)
+    hooks = cases.build_hooks(case)
+    for segment, extra in zip(low, hooks["segments"]):
+        segment.update(extra)
+    native = []
+    for pk, pv in zip(payloads["k"][case.low_segments:], payloads["v"][case.low_segments:]):
+        key = codec.decode_tensor(pk, dtype=dtype, device=device)
+        value = codec.decode_tensor(pv, dtype=dtype, device=device)
+        native.append((key.reshape(1, -1, heads, dim).permute(0, 2, 1, 3),
+                       value.reshape(1, -1, heads, dim).permute(0, 2, 1, 3), None))
+    reader = core.ReaderLayer(cases.build_reader(case, data))
+
+    def query_position(value, group):
+        value = core.rope_selected(value, hooks["q_multiplier"], group.indices)
+        return core.camera_selected(value, hooks["q_camera"], group.indices)
+
+    def kv_position(kk, vv, segment, group):
+        kk = core.rope_selected(kk, segment["freqs"], group.indices)
+        return (core.camera_selected(kk, segment["camera"], group.indices),
+                core.camera_selected(vv, segment["camera"], group.v_indices))
+
+    def output_position(value, group):
+        return core.camera_selected(value, hooks["out_camera"], group.v_indices)
+
+    q = data["q"][None].permute(0, 2, 1, 3).contiguous()
+    result = core.hybrid_attention(q, q, native, low, reader, query_position=query_position,
+                                   kv_position=kv_position, output_position=output_position)
+    rope_only = core.hybrid_attention(
+        q, q, native, low, reader,
+        query_position=lambda value, group: core.rope_selected(value, hooks["q_multiplier"], group.indices),
+        kv_position=lambda kk, vv, segment, group: (core.rope_selected(kk, segment["freqs"], group.indices), vv))
+    return {"hybrid": bits(result[0]), "rope_only": bits(rope_only[0]),
+            "q_digest": np.array([checksum(data["q"])], dtype=np.uint64)}
+
+
+def run_stream_case(case: cases.CodecCase, root) -> dict:
+    """LingBot's codec_cache_attention_inputs chunk by chunk with codec_commit set: the returned
+    K / V / positions of every step (history window + current chunk, cut to max_attention_size)."""
+    codec = ref_import.load_lingbot_codec(root)
+    runtime = load_lingbot_runtime(root)
+    data = cases.build(case)
+    heads, dim = case.shape.heads, case.shape.head_dim
+    for kind in ("k", "v"):
+        op = data[f"{kind}_op"]
+        ref_import.inject_lingbot_operator(
+            codec, "synthetic", kind, case.layer, joint_dim=case.shape.joint,
+            rank=case.shape.rank, mean=op["mean"], encoder=op["encoder"], decoder=op["decoder"])
+    cache = {"global_end_index": torch.zeros(1, dtype=torch.long),
+             "local_end_index": torch.zeros(1, dtype=torch.long)}
+    runtime.configure_cache(cache, layer=case.layer, sp_rank=0, options={
+        "codec_rank": case.shape.rank, "codec_clusters": case.shape.centers, "codec_iters": case.iters,
+        "codec_basis_root_k": "synthetic", "codec_basis_root_v": "synthetic"})
+    cache["codec_commit"] = True
+    out, start = {}, 0
+    for step, (key, value) in enumerate(zip(data["k_chunks"], data["v_chunks"])):
+        key_cache, value_cache, positions = runtime.codec_cache_attention_inputs(
+            cache, key.reshape(1, -1, heads, dim), value.reshape(1, -1, heads, dim),
+            current_start=start, **cases.STREAM_POLICY)
+        out[f"step{step}_positions"] = positions.numpy()
+        out[f"step{step}_key"] = bits(key_cache[0])
+        out[f"step{step}_value"] = bits(value_cache[0])
+        out[f"step{step}_segments"] = np.array(
+            [[s["global_start"], s["global_end"]] for s in cache["codec_segments"]], dtype=np.int64)
+        start += key.shape[0]
+    out["global_end"] = cache["global_end_index"].numpy()
+    out["local_end"] = cache["local_end_index"].numpy()
+    return out
+
+
+def run_protected_tokens_case(root) -> dict:
+    """protected_tokens of the MG core module on seeded frame-id sequences."""
+    core = ref_import.load_mg_core(root)
+    return {f"keep{index}": core.protected_tokens(ids, recent, stride, sink).numpy()
+            for index, (ids, recent, stride, sink) in enumerate(cases.protected_token_cases())}
+
+
 def run_rope_per_token_case(root) -> dict:
     """rope_selected of the MG core module: multipliers handed over per token."""
     core = ref_import.load_mg_core(root)
@@ -374,6 +471,9 @@ def main() -> None:
     for case in cases.FAST_CASES:
         save(case.name, lambda: run_fast_case(case, root))
     save("fast_masked_bf16", lambda: run_fast_case(cases.FAST_CASES[1], root, masked=True))
+    save("fast_hooks_bf16", lambda: run_fast_hooks_case(cases.FAST_CASES[1], root))
+    save("stream_lb_bf16", lambda: run_stream_case(cases.ROLLING, root))
+    save("protected_tokens", lambda: run_protected_tokens_case(root))
     save("merge_edge", lambda: run_merge_case(root))
     save("select_mg_bf16", lambda: run_select_case(cases.MINI_BF16, root))
     save("rope_selected_bf16", lambda: run_rope_selected_case(root))

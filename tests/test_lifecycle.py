@@ -38,6 +38,42 @@ def test_window_positions_match_reference_decode():
     assert positions == gold["positions"].tolist()
 
 
+def test_stream_window_and_overflow_cut_match_the_reference_entry_point():
+    """The window + max_attention_size cut behind codec_cache_attention_inputs, on segment tables
+    alone: positions and surviving segments of every step of the reference's streamed run."""
+    from nanokv_b200 import lingbot_attention
+    gold = load("stream_lb_bf16")
+    policy = {k: v for k, v in cases.STREAM_POLICY.items() if k != "max_attention_size"}
+    limit = cases.STREAM_POLICY["max_attention_size"]
+    segments, start = [], 0
+    for step, count in enumerate(cases.ROLLING.segments):
+        _, runs = lingbot_attention._window(segments, committed_end=start, **policy)
+        kept, lead = lingbot_attention._cut(runs, count, protected=min(policy["sink_tokens"], start, limit),
+                                            limit=limit)
+        positions = [p + i for a, b, p in kept for i in range(b - a)] + list(range(start + lead, start + count))
+        assert positions == gold[f"step{step}_positions"].tolist()
+        segments.append({"global_start": start, "global_end": start + count})
+        start += count
+        segments = lingbot_attention._prune_segments(segments, committed_end=start, **policy)
+        assert [[s["global_start"], s["global_end"]] for s in segments] == gold[f"step{step}_segments"].tolist()
+    # nothing to cut, everything cut, a cut inside the current chunk
+    assert lingbot_attention._cut([(0, 10, 0)], 5, protected=4, limit=15) == ([(0, 10, 0)], 0)
+    assert lingbot_attention._cut([(0, 10, 0)], 5, protected=4, limit=4) == ([(0, 4, 0)], 5)
+    assert lingbot_attention._cut([(0, 10, 0)], 5, protected=4, limit=7) == ([(0, 4, 0)], 2)
+    assert lingbot_attention._cut([(0, 10, 0), (10, 30, 50)], 5, protected=4, limit=12) == \
+        ([(0, 4, 0), (27, 30, 67)], 0)
+
+
+def test_protected_tokens_match_the_reference():
+    from nanokv_b200 import mg_core
+    gold = load("protected_tokens")
+    for index, (ids, recent, stride, sink) in enumerate(cases.protected_token_cases()):
+        got = mg_core.protected_tokens(ids, recent, stride, sink)
+        assert got.dtype == torch.bool and got.tolist() == gold[f"keep{index}"].tolist(), index
+    with pytest.raises(ValueError):
+        mg_core.protected_tokens(torch.arange(4), -1, 1)
+
+
 def test_active_intervals_edges():
     assert lifecycle.active_intervals(0, 10, 2) == []
     assert lifecycle.active_intervals(5, 10, 2) == [(0, 2), (2, 5)]
