@@ -223,6 +223,8 @@ def history_moments(low_segments):
     moments = []
     for segment in low_segments:
         view = _view(segment["v"])
+        if segment.get("visible") is not None:
+            view = ops.gather_view(view, segment["visible"])
         latent_sum, counts = ops.history_moments(view)
         moments.append((latent_sum, counts.float(), view.tokens))
     return moments

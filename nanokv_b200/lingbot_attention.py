@@ -13,10 +13,17 @@ Two entry points over the same cache dictionary the reference keeps per layer
   absolute positions), the current chunk is attended as plain rows, and the partial results are
   merged by log-sum-exp.  No history row is materialised.  Same cache side effects.
 
+* ``attend`` is the NanoKV-Fast step with the reference's name, argument list and
+  None-means-native-fallback contract (LB/codec_native_attention.py:588-817): protected tokens (sink
+  frames, recent frames, anchor frames) at full width, the rest of the window through the layer's
+  low-width readers, one global softmax.  Readers are registered (``register_reader``) with their
+  policy instead of being read from a manifest directory.
+
 The window policy (sink + recent, pruning, pieces of a cut segment) is ``lifecycle``'s.
 """
 from __future__ import annotations
 
+import os
 from typing import Any
 
 import torch
@@ -193,3 +200,104 @@ def codec_cache_attention(cache: dict[str, Any], query: torch.Tensor, key: torch
     out, lse = partials[0] if len(partials) == 1 else ops.lse_merge(partials)
     _commit(cache, key, value, current_start=current_start, capacity=capacity, sink_tokens=sink_tokens)
     return out[None], lse
+
+
+# ------------------------------------------------------------------ NanoKV-Fast step
+_READERS: dict[tuple[int, int], tuple["attention.Reader", dict]] = {}
+_ROPE_TABLES: dict[tuple, "attention.RopeTable"] = {}
+
+
+def register_reader(layer: int, payload: dict, *, sp_rank: int = 0, policy: dict | None = None,
+                    dtype: torch.dtype = torch.bfloat16, device="cuda") -> "attention.Reader":
+    """Make the reader groups of (sp_rank, layer) resident, with the layer's protection policy
+    (``recent_native_frames``, ``sink_native_frames``, ``anchor_stride``, ``native_prefix_chunks``,
+    ``native_denoise_calls``, ``native_commit``: the manifest's "policy" merged with its
+    "layer_policy" entry, LB/codec_native_attention.py:404-407).  A layer without a reader makes
+    ``attend`` return None, which the caller answers with its native path."""
+    reader = attention.Reader(payload, dtype=dtype, device=device)
+    _READERS[(int(sp_rank), int(layer))] = (reader, dict(policy or {}))
+    return reader
+
+
+def _rope_table(freqs: torch.Tensor, frame_seqlen: int, width: int, device) -> "attention.RopeTable":
+    key = (freqs.data_ptr(), tuple(freqs.shape), int(frame_seqlen), int(width), str(device))
+    if key not in _ROPE_TABLES:
+        _ROPE_TABLES[key] = attention.RopeTable(freqs, frame_seqlen=frame_seqlen, width=width, device=device)
+    return _ROPE_TABLES[key]
+
+
+@torch.no_grad()
+def attend(q_pre: torch.Tensor, q_native: torch.Tensor, key_current: torch.Tensor, value_current: torch.Tensor,
+           cache: dict[str, Any], *, current_start: int, capacity: int, sink_tokens: int,
+           max_attention_size: int, grid_sizes: torch.Tensor, freqs: torch.Tensor, frame_seqlen: int):
+    """[1,S,H,D], or None when this layer (or this call) is a native fallback.  ``q_pre`` and
+    ``key_current`` are pre-RoPE, ``q_native`` is rotated; ``freqs`` is the complex 3-D table."""
+    layer, sp_rank = int(cache["codec_layer"]), int(cache.get("codec_sp_rank", 0))
+    entry = _READERS.get((sp_rank, layer))
+    if entry is None:
+        return None
+    reader, policy = entry
+    if reader.heads != int(q_pre.shape[2]) or reader.native_dim != int(q_pre.shape[3]):
+        raise ValueError("reader does not match this sequence-parallel head shard")
+    if cache.get("a1_controller") is not None:
+        raise RuntimeError("codec-native deployment cannot share the legacy A1 training cache")
+    if 0 < int(policy.get("native_prefix_chunks", 0)) >= int(cache.get("codec_chunk_id", 0)):
+        return None
+    native_calls = policy.get("native_denoise_calls", [])
+    if native_calls:       # the call index restarts whenever a new chunk (a new current_start) begins
+        repeat = cache.get("_codec_native_schedule_start") == int(current_start)
+        index = int(cache.get("_codec_native_schedule_index", -1)) + 1 if repeat else 0
+        cache["_codec_native_schedule_start"], cache["_codec_native_schedule_index"] = int(current_start), index
+        if not cache.get("codec_commit", False) and index in native_calls:
+            return None
+    if policy.get("native_commit", False) and cache.get("codec_commit", False):
+        return None
+    device = q_pre.device
+    current = int(key_current.shape[1])
+    frame_seqlen = int(frame_seqlen)
+    recent_tokens = int(policy.get("recent_native_frames", 0)) * frame_seqlen
+    anchor_stride = int(policy.get("anchor_stride", 0))
+    native_sink = min(int(sink_tokens),
+                      int(policy.get("sink_native_frames", int(sink_tokens) // frame_seqlen)) * frame_seqlen)
+    committed = int(cache.get("codec_committed_end", 0))
+    budget = min(int(capacity), max(0, int(max_attention_size) - current))
+    active, runs = _window(cache.get("codec_segments", []), committed_end=committed, capacity=budget,
+                           sink_tokens=min(int(sink_tokens), budget))
+    # protected / low split on host integers: rows of the stacked active segments and their positions
+    rows = torch.cat([torch.arange(a, b) for a, b, _ in runs]) if runs else torch.empty(0, dtype=torch.long)
+    where = torch.cat([torch.arange(p, p + b - a) for a, b, p in runs]) if runs else rows
+    protect = where < native_sink
+    if recent_tokens:
+        protect |= where >= max(0, committed - recent_tokens)
+    if anchor_stride:
+        protect |= torch.div(where, frame_seqlen, rounding_mode="floor").remainder(anchor_stride) == 0
+    if bool(protect.all()):
+        return None                      # seed / all-protected: the caller's exact native path
+    hist_k = history_from_payloads([s["k"] for s in active], device=device)
+    hist_v = history_from_payloads([s["v"] for s in active], device=device)
+    op_k, op_v = operator_of(active[0]["k"], device), operator_of(active[0]["v"], device)
+    heads, dim = int(q_pre.shape[2]), int(q_pre.shape[3])
+    table = _rope_table(freqs, frame_seqlen, int(grid_sizes[0][2]), device)
+    now = torch.arange(current_start, current_start + current, device=device, dtype=torch.int32)
+    key_rows, value_rows = [table.rotate(key_current[0], now)], [value_current[0]]
+    if bool(protect.any()):
+        index = rows[protect].to(device=device, dtype=torch.int32)
+        spots = where[protect].to(device=device, dtype=torch.int32)
+        decoded_k = ops.decode_rows(hist_k.view(), op_k.decoder, op_k.mean, rows=index, dtype=q_pre.dtype)
+        decoded_v = ops.decode_rows(hist_v.view(), op_v.decoder, op_v.mean, rows=index, dtype=q_pre.dtype)
+        key_rows.insert(0, table.rotate(decoded_k.view(-1, heads, dim), spots))
+        value_rows.insert(0, decoded_v.view(-1, heads, dim))
+    native = [(torch.cat(key_rows).to(q_native.dtype), torch.cat(value_rows))]
+    visible = rows[~protect].to(device)
+    positions = torch.zeros(hist_k.tokens, dtype=torch.int32, device=device)
+    positions[visible] = where[~protect].to(device=device, dtype=torch.int32)
+    low = [{"k": hist_k, "v": hist_v, "k_mean": op_k.mean, "v_mean": op_v.mean, "v_decoder": op_v.decoder,
+            "positions": positions, "visible": visible}]
+    out = attention.hybrid_attention(
+        q_pre[0], q_native[0], native, low, reader, rope=table, q_positions=now,
+        value_mean_residual=os.environ.get("LINGBOT_CODEC_NATIVE_VALUE_MEAN_RESIDUAL", "0") == "1")
+    if cache.get("codec_commit", False) and current_start != committed:
+        raise RuntimeError("non-causal codec-native commit")
+    _commit(cache, key_current, value_current, current_start=current_start, capacity=capacity,
+            sink_tokens=sink_tokens)
+    return out[None]

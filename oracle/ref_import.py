@@ -89,9 +89,9 @@ def inject_mg_operator(codec, kind: str, layer: int, *, mean, encoder, decoder) 
 
 
 def inject_lingbot_operator(codec, root_tag: str, target: str, layer: int, *, joint_dim: int,
-                            rank: int, mean, encoder, decoder) -> None:
+                            rank: int, mean, encoder, decoder, prepacked: str = "") -> None:
     """Same for LingBot's ``_load_operator`` cache key
     (wan/modules/lingbot_v2_kv_codec.py:120-127)."""
-    key = (codec._resolved_path(root_tag), "", "", target, 0, int(layer), int(joint_dim),
-           int(rank), "cpu")
+    key = (codec._resolved_path(root_tag), "", codec._resolved_path(prepacked) if prepacked else "",
+           target, 0, int(layer), int(joint_dim), int(rank), "cpu")
     codec._OPERATORS[key] = {"mean": mean.float(), "encoder": encoder, "decoder": decoder}

@@ -251,3 +251,15 @@ def protected_token_cases():
         (runs([5, 5, 7, 5, 9, 9, 2], 2), 2, 2, 1), (runs(range(9), 1), 3, 0, 2),
         (torch.tensor([], dtype=torch.long), 2, 1, 1), (runs(range(30), 2), 5, 7, 3),
     ]
+
+
+# LingBot NanoKV-Fast step (attend): three ROLLING chunks committed, the fourth attends; one frame of
+# sink and one recent frame stay full width, the rest of the window is read through the readers
+ATTEND_POLICY = {"recent_native_frames": 1, "sink_native_frames": 1}
+ATTEND_GROUPS = (((0,), 64), ((1,), 128))
+
+
+def build_attend_reader(case: CodecCase, data: dict) -> dict:
+    gen = synthetic.generator(case.seed + 4000)
+    return synthetic.make_reader(case.shape, gen, [(list(heads), width) for heads, width in ATTEND_GROUPS],
+                                 k_decoder=data["k_op"]["decoder"], v_decoder=data["v_op"]["decoder"])

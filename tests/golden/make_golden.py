@@ -389,6 +389,71 @@ def run_stream_case(case: cases.CodecCase, root) -> dict:
     return out
 
 
+def run_attend_case(case: cases.CodecCase, root) -> dict:
+    """attend of the LingBot Fast module: the first chunks are committed through
+    codec_cache_attention_inputs, the last one attends (sink + recent frames at full width, the rest
+    of the window through a two-group reader), without and with the value-mean residual."""
+    codec = ref_import.load_lingbot_codec(root)
+    runtime = load_lingbot_runtime(root)
+    fast = ref_import._load("wan.modules.codec_native_attention",
+                            root / ref_import.LB / "wan/modules/codec_native_attention.py")
+    data = cases.build(case)
+    heads, dim = case.shape.heads, case.shape.head_dim
+    os.environ["LINGBOT_CODEC_NATIVE_ENABLE"] = "1"
+    os.environ["LINGBOT_CODEC_NATIVE_MANIFEST"] = "synthetic_manifest.json"
+    os.environ["LINGBOT_V2_KV_CODEC_PREPACKED_OPERATOR_PATH"] = "synthetic_operator.pt"
+    for name in ("LINGBOT_CODEC_NATIVE_HOST_POLICY", "LINGBOT_CODEC_NATIVE_TRITON_ROPE",
+                 "LINGBOT_CODEC_NATIVE_TRITON_NATIVE_ROPE", "LINGBOT_CODEC_NATIVE_FUSED_FINISH",
+                 "LINGBOT_CODEC_NATIVE_BATCH_READ", "LINGBOT_CODEC_NATIVE_DUMP_ROOT",
+                 "LINGBOT_CODEC_NATIVE_D128_JOINT"):
+        os.environ.pop(name, None)
+    os.environ["LINGBOT_PRE_ROPE_TRITON"] = "0"
+    for kind in ("k", "v"):
+        op = data[f"{kind}_op"]
+        ref_import.inject_lingbot_operator(
+            codec, "synthetic", kind, case.layer, joint_dim=case.shape.joint, rank=case.shape.rank,
+            mean=op["mean"], encoder=op["encoder"], decoder=op["decoder"], prepacked="synthetic_operator.pt")
+    manifest = {"format": "codec_native_manifest_v1", "model": "lingbot-world-v2",
+                "policy": dict(cases.ATTEND_POLICY), "layers": {f"0:{case.layer}": {"calibrated": True}}}
+    reader = fast._Layer(cases.build_attend_reader(case, data))
+    fast._BANK[(str(Path("synthetic_manifest.json").resolve()), "cpu")] = (manifest, {(0, case.layer): reader})
+    cache = {"global_end_index": torch.zeros(1, dtype=torch.long),
+             "local_end_index": torch.zeros(1, dtype=torch.long)}
+    runtime.configure_cache(cache, layer=case.layer, sp_rank=0, options={
+        "codec_rank": case.shape.rank, "codec_clusters": case.shape.centers, "codec_iters": case.iters,
+        "codec_basis_root_k": "synthetic", "codec_basis_root_v": "synthetic"})
+    cache["codec_commit"] = True
+    start = 0
+    chunks = list(zip(data["k_chunks"], data["v_chunks"]))
+    for key, value in chunks[:-1]:
+        runtime.codec_cache_attention_inputs(
+            cache, key.reshape(1, -1, heads, dim), value.reshape(1, -1, heads, dim),
+            current_start=start, **cases.STREAM_POLICY)
+        start += key.shape[0]
+    cache["codec_commit"] = False
+    key, value = (t.reshape(1, -1, heads, dim) for t in chunks[-1])
+    grid = cases.ROLLING_GRID
+    frame_seqlen = grid["height"] * grid["width"]
+    rope_params = reference_rope_params(root)
+    freqs = torch.cat([rope_params(1024, dim - 4 * (dim // 6)), rope_params(1024, 2 * (dim // 6)),
+                       rope_params(1024, 2 * (dim // 6))], dim=1)
+    grid_sizes = torch.tensor([[64, grid["height"], grid["width"]]])
+    count = key.shape[1]
+    q_pre = data["q"][:count][None]
+    positions = torch.arange(start, start + count)
+    q_native = runtime.rope_pre_key_by_positions(q_pre, positions, grid_sizes=grid_sizes, freqs=freqs,
+                                                 frame_seqlen=frame_seqlen)
+    common = dict(current_start=start, grid_sizes=grid_sizes, freqs=freqs, frame_seqlen=frame_seqlen,
+                  **cases.STREAM_POLICY)
+    os.environ["LINGBOT_CODEC_NATIVE_VALUE_MEAN_RESIDUAL"] = "0"
+    plain = fast.attend(q_pre, q_native, key, value, cache, **common)
+    os.environ["LINGBOT_CODEC_NATIVE_VALUE_MEAN_RESIDUAL"] = "1"
+    corrected = fast.attend(q_pre, q_native, key, value, cache, **common)
+    os.environ["LINGBOT_CODEC_NATIVE_VALUE_MEAN_RESIDUAL"] = "0"
+    return {"plain": bits(plain[0]), "corrected": bits(corrected[0]), "q_native": bits(q_native[0]),
+            "start": np.array([start], dtype=np.int64)}
+
+
 def run_protected_tokens_case(root) -> dict:
     """protected_tokens of the MG core module on seeded frame-id sequences."""
     core = ref_import.load_mg_core(root)
@@ -473,6 +538,7 @@ def main() -> None:
     save("fast_masked_bf16", lambda: run_fast_case(cases.FAST_CASES[1], root, masked=True))
     save("fast_hooks_bf16", lambda: run_fast_hooks_case(cases.FAST_CASES[1], root))
     save("stream_lb_bf16", lambda: run_stream_case(cases.ROLLING, root))
+    save("attend_lb_bf16", lambda: run_attend_case(cases.ROLLING, root))
     save("protected_tokens", lambda: run_protected_tokens_case(root))
     save("merge_edge", lambda: run_merge_case(root))
     save("select_mg_bf16", lambda: run_select_case(cases.MINI_BF16, root))

@@ -175,3 +175,75 @@ def test_codec_cache_attention_inputs_stream_against_the_reference_fixture():
     with pytest.raises(RuntimeError):
         lingbot_attention.codec_cache_attention_inputs(
             cache, key4, value4, current_start=start + 5, **cases.STREAM_POLICY)
+
+
+def test_attend_against_the_reference_fixture(monkeypatch):
+    """NanoKV-Fast step with the reference's argument list: committed chunks, then a chunk that
+    attends (sink and recent frame at full width, the rest through a 64-wide and a 128-wide reader
+    group), without and with the value-mean residual; and the calls that fall back (None)."""
+    case = cases.ROLLING
+    gold, data = load("attend_lb_bf16"), cases.build(case)
+    register(case, data)
+    heads, dim = case.shape.heads, case.shape.head_dim
+    lingbot_attention.register_reader(case.layer, cases.build_attend_reader(case, data),
+                                      policy=cases.ATTEND_POLICY)
+    cache = stream_cache(case)
+    chunks = list(zip(data["k_chunks"], data["v_chunks"]))
+    start = 0
+    for key, value in chunks[:-1]:
+        lingbot_attention.codec_cache_attention_inputs(
+            cache, key.reshape(1, -1, heads, dim).cuda(), value.reshape(1, -1, heads, dim).cuda(),
+            current_start=start, **cases.STREAM_POLICY)
+        start += key.shape[0]
+    assert start == int(gold["start"][0])
+    cache["codec_commit"] = False
+    key, value = (t.reshape(1, -1, heads, dim).cuda() for t in chunks[-1])
+    grid = cases.ROLLING_GRID
+    frame_seqlen = grid["height"] * grid["width"]
+    freqs = oracle.rope_table(1024, dim)
+    count = key.shape[1]
+    q_pre = data["q"][:count][None].cuda()
+    q_native = from_bits(gold["q_native"], torch.bfloat16)[None].cuda()
+    common = dict(current_start=start, grid_sizes=torch.tensor([[64, grid["height"], grid["width"]]]),
+                  freqs=freqs, frame_seqlen=frame_seqlen, **cases.STREAM_POLICY)
+    monkeypatch.setenv("LINGBOT_CODEC_NATIVE_VALUE_MEAN_RESIDUAL", "0")
+    plain = lingbot_attention.attend(q_pre, q_native, key, value, cache, **common)
+    assert plain.shape == q_pre.shape
+    want = from_bits(gold["plain"], torch.bfloat16)
+    assert rel_err(plain[0].cpu(), want) <= BF16_REL_TOL
+    monkeypatch.setenv("LINGBOT_CODEC_NATIVE_VALUE_MEAN_RESIDUAL", "1")
+    corrected = lingbot_attention.attend(q_pre, q_native, key, value, cache, **common)
+    want_corrected = from_bits(gold["corrected"], torch.bfloat16)
+    assert rel_err(corrected[0].cpu(), want_corrected) <= BF16_REL_TOL
+    assert rel_err(want, want_corrected) > 1e-3, "the residual must matter in this case"
+    monkeypatch.setenv("LINGBOT_CODEC_NATIVE_VALUE_MEAN_RESIDUAL", "0")
+    assert cache["codec_committed_end"] == start and len(cache["codec_segments"]) == 3   # nothing committed
+    # fallbacks: no reader for the layer; everything protected; policy says native
+    other = dict(cache, codec_layer=case.layer + 40)
+    assert lingbot_attention.attend(q_pre, q_native, key, value, other, **common) is None
+    lingbot_attention.register_reader(case.layer, cases.build_attend_reader(case, data),
+                                      policy={"recent_native_frames": 1000})
+    assert lingbot_attention.attend(q_pre, q_native, key, value, cache, **common) is None
+    lingbot_attention.register_reader(case.layer, cases.build_attend_reader(case, data),
+                                      policy=dict(cases.ATTEND_POLICY, native_prefix_chunks=3))
+    assert lingbot_attention.attend(q_pre, q_native, key, value, dict(cache, codec_chunk_id=2), **common) is None
+    lingbot_attention.register_reader(case.layer, cases.build_attend_reader(case, data),
+                                      policy=dict(cases.ATTEND_POLICY, native_denoise_calls=[0, 2]))
+    seen = [lingbot_attention.attend(q_pre, q_native, key, value, cache, **common) is None for _ in range(4)]
+    assert seen == [True, False, True, False]
+    # anchors: every second frame stays full width; same softmax over the same tokens, so the
+    # result stays close to the unanchored one while taking the non-contiguous path
+    lingbot_attention.register_reader(case.layer, cases.build_attend_reader(case, data),
+                                      policy=dict(cases.ATTEND_POLICY, anchor_stride=2))
+    anchored = lingbot_attention.attend(q_pre, q_native, key, value, cache, **common)
+    assert anchored.shape == q_pre.shape and bool(torch.isfinite(anchored.float()).all())
+    # a committing call appends and prunes like the reference
+    lingbot_attention.register_reader(case.layer, cases.build_attend_reader(case, data),
+                                      policy=cases.ATTEND_POLICY)
+    cache["codec_commit"] = True
+    lingbot_attention.attend(q_pre, q_native, key, value, cache, **common)
+    assert cache["codec_committed_end"] == start + count
+    assert [[s["global_start"], s["global_end"]] for s in cache["codec_segments"]] == \
+        load("stream_lb_bf16")["step3_segments"].tolist()
+    with pytest.raises(ValueError):
+        lingbot_attention.attend(q_pre[:, :, :1], q_native[:, :, :1], key, value, cache, **common)
