@@ -268,3 +268,26 @@ def direct_latent_pair_segments(key: Any, value: Any, *, device, token_keep: tor
         result.append({"k": rows["k"], "v": rows["v"], "length": int(logical.numel()),
                        "logical_indices": logical})
     return result
+
+
+@torch.no_grad()
+def decode_pair_selected(key: Any, value: Any, token_keep: torch.Tensor, *, dtype: torch.dtype, device):
+    """Decode only the rows ``token_keep`` (bool over the whole history) marks -- protected recent /
+    sink / anchor tokens -- to native width: (K [1,n,J], V [1,n,J]) (MGF/nanokv_codec.py:801-861).
+    One decode launch per target over the stacked segments, rows chosen by index."""
+    key_parts, value_parts = _parts(key), _parts(value)
+    keep = token_keep.to(device="cpu", dtype=torch.bool).reshape(-1)
+    if keep.numel() != sum(int(value_shape(part)[1]) for part in key_parts):
+        raise ValueError("selected decode mask/cache length mismatch")
+    index = torch.nonzero(keep).flatten()
+    if index.numel() == 0:
+        shape = value_shape(key)
+        empty = torch.empty((shape[0], 0, shape[2]), device=device, dtype=dtype)
+        return empty, empty.clone()
+    rows = index.to(device=device, dtype=torch.int32)
+    out = []
+    for kind, parts in (("k", key_parts), ("v", value_parts)):
+        hist = history_from_payloads(parts, device=device)
+        op = _operator(kind, int(parts[0]["layer"]), device)
+        out.append(ops.decode_rows(hist.view(), op.decoder, op.mean, rows=rows, dtype=dtype)[None])
+    return out[0], out[1]

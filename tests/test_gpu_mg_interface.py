@@ -108,3 +108,42 @@ def test_select_value_cuts_and_reuses_segments_like_the_reference():
     with pytest.raises(RuntimeError):
         mg_codec.select_value(value, torch.tensor([5, 9999]), kind="k", layer=case.layer,
                               dtype=torch.bfloat16, device="cuda")
+
+
+def test_selected_decode_and_direct_rows_follow_the_token_mask():
+    """decode_pair_selected and direct_latent_pair_segments(token_keep=) on a two-segment history:
+    the selected rows equal the same rows of the whole decode; a segment the mask empties is left out."""
+    case = cases.MINI_BF16
+    data = cases.build(case)
+    os.environ["MG35_KVCODEC_C64_CLUSTERS"] = str(case.shape.centers)
+    os.environ["MG35_KVCODEC_C64_ITERS"] = str(case.iters)
+    containers = {}
+    for kind in ("k", "v"):
+        op = data[f"{kind}_op"]
+        mg_codec.register_operator(kind, case.layer, mean=op["mean"], encoder=op["encoder"], decoder=op["decoder"])
+        container = None
+        for chunk in data[f"{kind}_chunks"]:
+            container = mg_codec.concat_values(container, mg_codec.encode_tensor(kind, case.layer, chunk[None].cuda()))
+        containers[kind] = container
+    total = sum(case.segments)
+    gen = torch.Generator().manual_seed(3)
+    keep = torch.rand(total, generator=gen) < 0.3
+    key_rows, value_rows = mg_codec.decode_pair_selected(containers["k"], containers["v"], keep,
+                                                         dtype=torch.bfloat16, device="cuda")
+    whole_k, whole_v = mg_codec.decode_pair_values(containers["k"], containers["v"], dtype=torch.bfloat16,
+                                                   device="cuda")
+    assert torch.equal(key_rows, whole_k[:, keep.cuda()]) and torch.equal(value_rows, whole_v[:, keep.cuda()])
+    none_k, none_v = mg_codec.decode_pair_selected(containers["k"], containers["v"], torch.zeros(total, dtype=torch.bool),
+                                                   dtype=torch.bfloat16, device="cuda")
+    assert none_k.shape == (1, 0, case.shape.joint) and none_v.shape == none_k.shape
+    with pytest.raises(ValueError):
+        mg_codec.decode_pair_selected(containers["k"], containers["v"], keep[:-1], dtype=torch.bfloat16, device="cuda")
+    only_second = torch.zeros(total, dtype=torch.bool)
+    only_second[case.segments[0] + 3:case.segments[0] + 40] = True
+    low = mg_codec.direct_latent_pair_segments(containers["k"], containers["v"], device="cuda", token_keep=only_second)
+    assert len(low) == 1 and low[0]["length"] == 37 and low[0]["k"].tokens == 37
+    assert low[0]["logical_indices"].tolist() == list(range(case.segments[0] + 3, case.segments[0] + 40))
+    everything = mg_codec.direct_latent_pair_segments(containers["k"], containers["v"], device="cuda")
+    assert [item["length"] for item in everything] == list(case.segments)
+    with pytest.raises(ValueError):
+        mg_codec.direct_latent_pair_segments(containers["k"], containers["v"], device="cuda", token_keep=keep[:-1])
