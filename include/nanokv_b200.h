@@ -3,9 +3,11 @@
  *
  * Every entry point takes plain device pointers, sizes and a CUDA stream
  * (a cudaStream_t passed as void*), enqueues its kernels on that stream and
- * returns NKV_OK or a negative status; nothing here allocates device memory,
- * synchronises the device, or traps.  nkv_last_error() gives the detail text
- * of the calling thread's last failure.
+ * returns NKV_OK or a negative status; nothing here allocates device memory
+ * at call time (the scratch the library owns -- the fused read's staging ring,
+ * the static encoder scratch -- is __device__ storage inside the library; only
+ * nkv_peer_alloc allocates, by name), synchronises the device, or traps.
+ * nkv_last_error() gives the detail text of the calling thread's last failure.
  *
  * "Reference" citations name the function of the NanoKV project that each
  * entry point replaces, by path inside that project:
@@ -153,12 +155,29 @@ int nkv_quant_pack(const void* coeff, int coeff_dtype, int S, int r, int group, 
                    void* stream);
 
 /*
+ * Projection, quantiser and packing of one chunk whose centre ids are known (after nkv_kmeans or
+ * nkv_assign): coeff = ((x - centre[id]) - mean) @ encoder^T rounded once to the encoder dtype, then
+ * nkv_quant_pack of those coefficients, written to codes [S,r/2] and scales [S,r/group].
+ * Reference: the second half of encode_tensor, MGM/nanokv_codec.py:345-351, LB/lingbot_v2_kv_codec.py:280-287.
+ * With bf16 operands and one scale per token (group == r, r a multiple of 64 that tiles over at most
+ * two column parts) one kernel does all of it: the coefficients stay in tensor memory, the per-token
+ * maximum crosses the two column-half thread blocks through their shared memory, and `workspace`
+ * is not touched.  Otherwise it runs nkv_project into `workspace` (S * r elements of the encoder
+ * dtype) followed by nkv_quant_pack.  Same bytes either way.
+ */
+int nkv_project_quant(const void* x, int x_dtype, const void* centers_bf16, const void* ids, int id_bytes,
+                      const float* mean, const void* encoder, int encoder_dtype, int S, int J, int r,
+                      int group, float eps, int quant_mode, int scale_dtype, uint8_t* codes,
+                      void* scales, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Whole encoder of one chunk against given (stored, bf16) centres: assign,
  * project, quantise, pack, and write codes / scales / ids at token `offset`
  * of the destination arrays (the append).
  * Reference: encode_tensor, MGM/nanokv_codec.py:334-365,
  * LB/lingbot_v2_kv_codec.py:256-297.
- * workspace: S * r elements of the encoder dtype.
+ * workspace: S * r elements of the encoder dtype (unused when nkv_project_quant's single-kernel
+ * form applies).
  */
 int nkv_encode_append(const void* x, int x_dtype, const void* centers_bf16, int C,
                       const float* mean, const void* encoder, int encoder_dtype,
@@ -219,7 +238,13 @@ int nkv_decode_rows(const nkv_history* hist, const int32_t* rows_index, int n,
  *     K[t,h,:] = bf16( bf16(latent_k[t] @ wk[h]^T + bias_k[h]) + centers_k[row(t), h*dk : (h+1)*dk] )
  *     V[t,h,:] likewise with wv / bias_v / centers_v,
  * and computes O = softmax(q K^T * scale) V with an online softmax, returning
- * O and the natural-log LSE.  No K or V row is written to global memory.
+ * O and the natural-log LSE.  On the tensor-core path every K / V tile of 128 tokens is rebuilt ONCE
+ * per head by producer thread blocks and handed to the blocks that attend it through a staging ring
+ * the library owns (24 MiB of __device__ storage per GPU, reused tile after tile, so it stays in
+ * L2): no K or V row of the history is stored in HBM as a tensor, and none outlives the launch.
+ * Launches on one device are serialised on that ring (an event orders streams).  `status_word`
+ * (int32 on the device, zeroed by the caller, mandatory) receives a site code if a bounded
+ * device-side wait gave up or the score range guard tripped; the affected lse rows are NaN.
  * With wk / wv = the decoder viewed as [heads, head_dim, r] and bias = mean
  * this is the full-dimensional read (decode + attention); with reader
  * matrices and projected centre tables it is the NanoKV-Fast low-width read.
@@ -238,12 +263,12 @@ int nkv_attn_codec(const void* q, int dtype, int64_t q_stride_token, int64_t q_s
                    float scale, void* out, float* lse, int32_t* status_word, void* stream);
 
 /*
- * nkv_attn_codec with the history cut into `splits` (1..16) contiguous runs of tiles that are
- * attended by separate thread-block slices of ONE launch; their partial (O, lse) go to
- * `workspace` (nkv_attn_codec_workspace_bytes bytes) and are merged by log-sum-exp (the merge of
- * MGC/core.py:33-42).  More, shorter work units even out the rounds in which the GPU's resident
- * clusters finish; results equal nkv_attn_codec up to the rounding of the partials to the output
- * dtype.  The fp32 path ignores `splits`.
+ * nkv_attn_codec with the history cut into AT MOST `splits` (1..16) contiguous runs of tiles that
+ * are attended by separate groups of thread blocks of ONE launch (the library picks the count, up
+ * to this bound, that fills the GPU's SMs for the given Q, heads and history); their partial
+ * (O, lse) go to `workspace` (nkv_attn_codec_workspace_bytes(…, splits) bytes) and are merged by
+ * log-sum-exp (the merge of MGC/core.py:33-42).  Results equal nkv_attn_codec up to the rounding of
+ * the partials to the output dtype.  The fp32 path ignores `splits`.
  */
 size_t nkv_attn_codec_workspace_bytes(int Q, int heads, int dv, int splits);
 int nkv_attn_codec_split(const void* q, int dtype, int64_t q_stride_token, int64_t q_stride_head,

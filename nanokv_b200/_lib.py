@@ -56,6 +56,9 @@ SIGNATURES = {
                             c_int, c_int, c_int, c_void_p, c_void_p]),
     "nkv_quant_pack": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                c_void_p, c_void_p, c_void_p]),
+    "nkv_project_quant": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                  c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
+                                  c_void_p, c_size_t, c_void_p]),
     "nkv_encode_append": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                   c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
                                   c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),

@@ -106,10 +106,9 @@ def encode_append(hist: CompressedHistory, rows: torch.Tensor, op: Operator,
     if centers is None:
         init = kmeans_init_rows(S, clusters, seed).to(rows.device)
         ops.kmeans(rows, clusters, iters, init, centers=center_rows, ids=ids)
-        coeff = ops.project(rows, center_rows, ids, op.mean, op.encoder)
-        ops.quant_pack(coeff, group=hist.group, eps=quant.eps,
-                       in_coeff_dtype=quant.in_coeff_dtype and coeff.dtype == torch.bfloat16,
-                       codes=codes, scales=scales)
+        ops.project_quant(rows, center_rows, ids, op.mean, op.encoder, group=hist.group, eps=quant.eps,
+                          in_coeff_dtype=quant.in_coeff_dtype and op.dtype == torch.bfloat16,
+                          codes=codes, scales=scales)
         return offset
     if not resident:
         center_rows.copy_(centers.to(torch.bfloat16))

@@ -193,6 +193,35 @@ int nkv_quant_pack(const void* coeff, int coeff_dtype, int S, int r, int group, 
                     static_cast<cudaStream_t>(stream));
 }
 
+int nkv_project_quant(const void* x, int x_dtype, const void* centers_bf16, const void* ids, int id_bytes,
+                      const float* mean, const void* encoder, int encoder_dtype, int S, int J, int r,
+                      int group, float eps, int quant_mode, int scale_dtype, uint8_t* codes,
+                      void* scales, void* workspace, size_t workspace_bytes, void* stream) {
+  NKV_REQUIRE(S >= 0 && J > 0 && r > 0 && group > 0 && r % group == 0, NKV_ERR_INVALID,
+              "project_quant: S=%d J=%d r=%d group=%d", S, J, r, group);
+  NKV_REQUIRE(encoder_dtype == NKV_F32 || encoder_dtype == NKV_BF16, NKV_ERR_INVALID,
+              "project_quant: encoder dtype");
+  NKV_REQUIRE(scale_dtype == NKV_BF16 || scale_dtype == NKV_F16, NKV_ERR_INVALID,
+              "project_quant: scale dtype");
+  NKV_REQUIRE(quant_mode == NKV_QUANT_F32 || quant_mode == NKV_QUANT_IN_BF16, NKV_ERR_INVALID,
+              "project_quant: quant_mode=%d", quant_mode);
+  NKV_REQUIRE(quant_mode != NKV_QUANT_IN_BF16 || encoder_dtype == NKV_BF16, NKV_ERR_INVALID,
+              "project_quant: NKV_QUANT_IN_BF16 needs bf16 coefficients");
+  // bf16 operands with one scale per token: projection, quantiser and packing in one kernel, the
+  // coefficients stay on chip
+  if (encoder_dtype == NKV_BF16 && x_dtype == NKV_BF16 && !simt_forced() &&
+      tc_project_quant_supported(J, r, group) && (reinterpret_cast<uintptr_t>(codes) & 15) == 0)
+    return tc_project_quant(x, centers_bf16, ids, id_bytes, mean, encoder, S, J, r, eps, quant_mode,
+                            scale_dtype, codes, scales, static_cast<cudaStream_t>(stream));
+  NKV_REQUIRE(workspace && workspace_bytes >= static_cast<size_t>(S) * r * dtype_bytes(encoder_dtype),
+              NKV_ERR_INVALID, "project_quant: workspace of %zu bytes is too small", workspace_bytes);
+  int rc = nkv_project(x, x_dtype, centers_bf16, ids, id_bytes, mean, encoder, encoder_dtype, S, J, r,
+                       workspace, stream);
+  if (rc != NKV_OK) return rc;
+  return nkv_quant_pack(workspace, encoder_dtype, S, r, group, eps, quant_mode, scale_dtype, codes,
+                        scales, stream);
+}
+
 int nkv_encode_append(const void* x, int x_dtype, const void* centers_bf16, int C,
                       const float* mean, const void* encoder, int encoder_dtype, int S, int J,
                       int r, int group, float eps, int quant_mode, int scale_dtype, int id_bytes,
@@ -208,11 +237,9 @@ int nkv_encode_append(const void* x, int x_dtype, const void* centers_bf16, int 
   void* scales_at = static_cast<uint8_t*>(scales) + static_cast<size_t>(offset) * (r / group) * 2;
   int rc = nkv_assign(x, x_dtype, centers_bf16, NKV_BF16, S, J, C, ids_at, id_bytes, stream);
   if (rc != NKV_OK) return rc;
-  rc = nkv_project(x, x_dtype, centers_bf16, ids_at, id_bytes, mean, encoder, encoder_dtype, S, J,
-                   r, workspace, stream);
-  if (rc != NKV_OK) return rc;
-  return nkv_quant_pack(workspace, encoder_dtype, S, r, group, eps, quant_mode, scale_dtype,
-                        codes_at, scales_at, stream);
+  return nkv_project_quant(x, x_dtype, centers_bf16, ids_at, id_bytes, mean, encoder, encoder_dtype, S,
+                           J, r, group, eps, quant_mode, scale_dtype, codes_at, scales_at, workspace,
+                           workspace_bytes, stream);
 }
 
 int nkv_decode_rows(const nkv_history* hist, const int32_t* rows_index, int n,

@@ -51,6 +51,23 @@ __device__ __forceinline__ uint16_t float_to_bf16_bits(float v) {
   return __bfloat16_as_ushort(__float2bfloat16_rn(v));
 }
 
+// INT4 code (0..14, i.e. the signed code plus 7) of coefficient z for a group scale, with the
+// reference's rounding points.  IN_BF16: the quotient is rounded to bf16 before rint (LingBot's
+// form).  Otherwise rint(z / scale) in fp32, taken through the reciprocal: z * inv is within 2 ulp
+// of the IEEE quotient, so the two can only round to different integers when z * inv lies within
+// ~1e-6 of a half; exactly those values take the IEEE division.
+template <bool IN_BF16>
+__device__ __forceinline__ int quant_code(float z, float scale, float inv) {
+  float q;
+  if (IN_BF16) {
+    q = round_to_bf16(__fdiv_rn(z, scale));
+  } else {
+    q = z * inv;
+    if (fabsf(q - rintf(q)) > 0.49999f && fabsf(q) < 8.5f) q = __fdiv_rn(z, scale);
+  }
+  return static_cast<int>(fminf(fmaxf(rintf(q), -7.f), 7.f)) + 7;
+}
+
 // element i of an array of the given element type, as float (exact)
 __device__ __forceinline__ float load_float(const void* base, int dtype, size_t i) {
   if (dtype == NKV_F32) return static_cast<const float*>(base)[i];

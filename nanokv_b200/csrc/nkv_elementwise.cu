@@ -45,23 +45,32 @@ quant_pack_kernel(const void* coeff, int dtype, int S, int r, int group, float e
 }
 
 // Vectorised form for bf16 coefficients with one scale per token (group == r) or per 32
-// coefficients: one warp per token, every lane keeps its 16-byte pieces (8 coefficients) in
-// registers, so the row is read once (16-byte loads) and the codes leave as 4-byte stores.
-template <bool IN_BF16, bool GROUP32, int MAXJ>
+// coefficients.  LANES threads (8, 16 or 32: the smallest count that covers the row with at most
+// five 16-byte pieces each, so no lane idles on a 640-wide row) own one token; every lane keeps its
+// pieces (8 coefficients each) in registers, so the row is read once with 16-byte loads and the
+// codes leave as 4-byte stores.  Scale and reciprocal are formed once per token (once per piece in
+// the 32-wide mode, where four neighbouring lanes share a group).
+template <bool IN_BF16, bool GROUP32, int LANES>
 __global__ void __launch_bounds__(256)
 quant_pack_vec_kernel(const uint16_t* coeff, int S, int r, float eps, int scale_dtype,
                       uint8_t* codes, void* scales) {
-  const int lane = threadIdx.x & 31;
-  const long long t = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (t >= S) return;
+  constexpr int MAXJ = 5;
+  const int sub = threadIdx.x % LANES;
+  const long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) / LANES;
+  if (t >= S) return;     // S * LANES is a multiple of 32 only by accident: masks below name the row's lanes
+  const unsigned lane = threadIdx.x & 31;
+  const unsigned mask = LANES == 32 ? 0xffffffffu : (((1u << LANES) - 1u) << (lane - sub));
   const int pieces = r >> 3;
   const uint4* src = reinterpret_cast<const uint4*>(coeff + static_cast<size_t>(t) * r);
   uint4 v[MAXJ];
   float amax[MAXJ];
 #pragma unroll
   for (int j = 0; j < MAXJ; ++j) {
-    const int i = lane + 32 * j;
+    const int i = sub + LANES * j;
     v[j] = i < pieces ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (int j = 0; j < MAXJ; ++j) {
     const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
     float m = 0.f;
 #pragma unroll
@@ -71,52 +80,69 @@ quant_pack_vec_kernel(const uint16_t* coeff, int S, int r, float eps, int scale_
     }
     amax[j] = m;
   }
+  float scale_of[MAXJ], inv_of[MAXJ];
   if (GROUP32) {   // 4 consecutive pieces = 4 consecutive lanes form a group
 #pragma unroll
     for (int j = 0; j < MAXJ; ++j) {
-      amax[j] = fmaxf(amax[j], __shfl_xor_sync(0xffffffffu, amax[j], 1));
-      amax[j] = fmaxf(amax[j], __shfl_xor_sync(0xffffffffu, amax[j], 2));
+      amax[j] = fmaxf(amax[j], __shfl_xor_sync(mask, amax[j], 1));
+      amax[j] = fmaxf(amax[j], __shfl_xor_sync(mask, amax[j], 2));
+      if (IN_BF16) scale_of[j] = round_to_bf16(__fdiv_rn(fmaxf(amax[j], round_to_bf16(eps)), 7.0f));
+      else scale_of[j] = __fdiv_rn(fmaxf(amax[j], eps), 7.0f);
+      inv_of[j] = IN_BF16 ? 0.f : __frcp_rn(scale_of[j]);
     }
   } else {
     float m = amax[0];
 #pragma unroll
     for (int j = 1; j < MAXJ; ++j) m = fmaxf(m, amax[j]);
-    m = warp_max(m);
 #pragma unroll
-    for (int j = 0; j < MAXJ; ++j) amax[j] = m;
+    for (int off = LANES / 2; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(mask, m, off));
+    float scale;
+    if (IN_BF16) scale = round_to_bf16(__fdiv_rn(fmaxf(m, round_to_bf16(eps)), 7.0f));
+    else scale = __fdiv_rn(fmaxf(m, eps), 7.0f);
+    const float inv = IN_BF16 ? 0.f : __frcp_rn(scale);
+#pragma unroll
+    for (int j = 0; j < MAXJ; ++j) { scale_of[j] = scale; inv_of[j] = inv; }
   }
   uint32_t* dst = reinterpret_cast<uint32_t*>(codes + static_cast<size_t>(t) * (r >> 1));
   const int groups = GROUP32 ? (r >> 5) : 1;
 #pragma unroll
   for (int j = 0; j < MAXJ; ++j) {
-    const int i = lane + 32 * j;
+    const int i = sub + LANES * j;
     if (i >= pieces) continue;
-    float scale;
-    if (IN_BF16) scale = round_to_bf16(__fdiv_rn(fmaxf(amax[j], round_to_bf16(eps)), 7.0f));
-    else scale = __fdiv_rn(fmaxf(amax[j], eps), 7.0f);
+    const float scale = scale_of[j], inv = inv_of[j];
     const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
     uint32_t out = 0;
-    const float inv = IN_BF16 ? 0.f : __frcp_rn(scale);
+    if (IN_BF16) {
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const float z0 = __uint_as_float(w[k] << 16), z1 = __uint_as_float(w[k] & 0xFFFF0000u);
-      float q0, q1;
-      if (IN_BF16) {
-        q0 = round_to_bf16(__fdiv_rn(z0, scale));
-        q1 = round_to_bf16(__fdiv_rn(z1, scale));
-      } else {
-        // rint(z / scale) through the reciprocal: z * inv is within 2 ulp of the IEEE quotient, so
-        // the two can only round to different integers when z * inv lies within ~1e-6 of a half;
-        // exactly those values take the IEEE division
-        q0 = z0 * inv;
-        q1 = z1 * inv;
-        const float f0 = fabsf(q0 - rintf(q0)), f1 = fabsf(q1 - rintf(q1));
-        if (f0 > 0.49999f && fabsf(q0) < 8.5f) q0 = __fdiv_rn(z0, scale);
-        if (f1 > 0.49999f && fabsf(q1) < 8.5f) q1 = __fdiv_rn(z1, scale);
+      for (int k = 0; k < 4; ++k) {
+        const int c0 = quant_code<true>(__uint_as_float(w[k] << 16), scale, inv);
+        const int c1 = quant_code<true>(__uint_as_float(w[k] & 0xFFFF0000u), scale, inv);
+        out |= static_cast<uint32_t>(c0 | (c1 << 4)) << (8 * k);
       }
-      const int c0 = static_cast<int>(fminf(fmaxf(rintf(q0), -7.f), 7.f)) + 7;
-      const int c1 = static_cast<int>(fminf(fmaxf(rintf(q1), -7.f), 7.f)) + 7;
-      out |= static_cast<uint32_t>(c0 | (c1 << 4)) << (8 * k);
+    } else {
+      // whole piece through the reciprocal; a piece holding a value whose scaled form lies within
+      // 1e-5 of a half-integer (where the reciprocal and the IEEE quotient could round apart) is
+      // redone value by value with the exact rule
+      bool near_half = false;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float q0 = __uint_as_float(w[k] << 16) * inv, q1 = __uint_as_float(w[k] & 0xFFFF0000u) * inv;
+        const float r0 = rintf(q0), r1 = rintf(q1);
+        near_half |= fabsf(q0 - r0) > 0.49999f;
+        near_half |= fabsf(q1 - r1) > 0.49999f;
+        const int c0 = static_cast<int>(fminf(fmaxf(r0, -7.f), 7.f)) + 7;
+        const int c1 = static_cast<int>(fminf(fmaxf(r1, -7.f), 7.f)) + 7;
+        out |= static_cast<uint32_t>(c0 | (c1 << 4)) << (8 * k);
+      }
+      if (near_half) {
+        out = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int c0 = quant_code<false>(__uint_as_float(w[k] << 16), scale, inv);
+          const int c1 = quant_code<false>(__uint_as_float(w[k] & 0xFFFF0000u), scale, inv);
+          out |= static_cast<uint32_t>(c0 | (c1 << 4)) << (8 * k);
+        }
+      }
     }
     dst[i] = out;
     if (GROUP32) {
@@ -556,15 +582,20 @@ int quant_pack(const void* coeff, int coeff_dtype, int S, int r, int group, floa
   if (S == 0) return NKV_OK;
   const bool aligned = (reinterpret_cast<uintptr_t>(coeff) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(codes) & 3) == 0;
-  if (coeff_dtype == NKV_BF16 && r % 8 == 0 && r <= 1024 && aligned && (group == r || group == 32)) {
+  if (coeff_dtype == NKV_BF16 && r % 8 == 0 && r <= 1280 && aligned && (group == r || group == 32)) {
     const uint16_t* src = static_cast<const uint16_t*>(coeff);
-    const unsigned blocks = static_cast<unsigned>((static_cast<long long>(S) + 7) / 8);
+    const int pieces = r / 8;
+    const int lanes = pieces <= 40 ? 8 : (pieces <= 80 ? 16 : 32);
+    const unsigned blocks = static_cast<unsigned>((static_cast<long long>(S) * lanes + 255) / 256);
     const bool in_bf16 = quant_mode == NKV_QUANT_IN_BF16;
-#define NKV_QP(INB, G32)                                                                   \
-    quant_pack_vec_kernel<INB, G32, 4><<<blocks, 256, 0, stream>>>(src, S, r, eps, scale_dtype, \
+#define NKV_QP(INB, G32, L)                                                                   \
+    quant_pack_vec_kernel<INB, G32, L><<<blocks, 256, 0, stream>>>(src, S, r, eps, scale_dtype, \
                                                                    codes, scales)
-    if (group == 32) { if (in_bf16) NKV_QP(true, true); else NKV_QP(false, true); }
-    else             { if (in_bf16) NKV_QP(true, false); else NKV_QP(false, false); }
+#define NKV_QP_LANES(INB, G32) \
+    do { if (lanes == 8) NKV_QP(INB, G32, 8); else if (lanes == 16) NKV_QP(INB, G32, 16); else NKV_QP(INB, G32, 32); } while (0)
+    if (group == 32) { if (in_bf16) NKV_QP_LANES(true, true); else NKV_QP_LANES(false, true); }
+    else             { if (in_bf16) NKV_QP_LANES(true, false); else NKV_QP_LANES(false, false); }
+#undef NKV_QP_LANES
 #undef NKV_QP
     NKV_LAUNCH_CHECK("quant_pack_vec_kernel");
     return NKV_OK;

@@ -73,6 +73,10 @@ int tc_prepare_decoder(const void* w_bf16, int64_t rows, int rank, void* out_bf1
 bool tc_attn_supported(int dk, int dv, int rank);
 int tc_wait_expiry_selftest(int kind, long long budget_cycles, int32_t* status_word, cudaStream_t stream);
 bool tc_project_supported(int J, int r);
+bool tc_project_quant_supported(int J, int r, int group);
+int tc_project_quant(const void* x_bf16, const void* centers_bf16, const void* ids, int id_bytes,
+                     const float* mean, const void* encoder_bf16, int S, int J, int r, float eps,
+                     int quant_mode, int scale_dtype, uint8_t* codes, void* scales, cudaStream_t stream);
 bool tc_assign_supported(int J, int C);
 
 }  // namespace nkv

@@ -9,6 +9,11 @@
 //   project: A = bf16((x - centre[id]) - mean), formed by the compute warps in
 //            the swizzled operand layout; B = encoder rows (TMA); the epilogue
 //            rounds once to bf16.
+//   project + quantise: the same GEMM, but the epilogue keeps the coefficients in TMEM, takes the
+//            token's absolute maximum over the whole rank row (the two column-half CTAs of a token
+//            tile form a cluster and swap their half-row maxima through each other's shared
+//            memory), quantises to INT4, packs two codes per byte and writes codes and scale to
+//            their place in the history: the bf16 coefficients never travel to HBM.
 // A CTA covers up to 512 output columns as 1 or 2 accumulators of NB <= 256.
 // Warps 0-7 compute, warp 8 lane 0 issues TMA, warp 9 lane 0 issues MMA.
 #include <atomic>
@@ -27,7 +32,10 @@ constexpr int THREADS = COMPUTE_THREADS + 64;
 constexpr int A_BYTES = 128 * 128;
 
 constexpr int MAX_STAGES = 4;
-enum Bar { TMA_FULL = 0, A_FULL = 4, STAGE_FREE = 8, ACC_DONE = 12, SIDE_READY = 13, CAND_READY = 14, NUM_BARS = 15 };
+enum Bar { TMA_FULL = 0, A_FULL = 4, STAGE_FREE = 8, ACC_DONE = 12, SIDE_READY = 13, CAND_READY = 14,
+           PEER_READY = 15, NUM_BARS = 16 };
+enum Mode { PROJECT = 0, ASSIGN_IDS = 1, PROJECT_QUANT = 2 };
+constexpr int META_HEAD = 256;      // barriers, TMEM slot, abort flag
 
 struct Params {
   int S, J, NB, NACC, n_total;      // n_total = r (project) or C (assign)
@@ -38,6 +46,8 @@ struct Params {
   const float* mean; uint16_t* coeff;
   // assign
   void* ids_out;
+  // project + quantise: codes u8 [S, r/2] and scales [S] at the history's token offset
+  uint8_t* codes; void* scales; float eps; int in_bf16; int scale_dtype; int column_parts;
 };
 
 __device__ __forceinline__ float sumsq8(uint4 w) {
@@ -52,10 +62,12 @@ __device__ __forceinline__ float sumsq8(uint4 w) {
   return s;
 }
 
-template <bool ASSIGN>
+template <int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                    const __grid_constant__ CUtensorMap map_b, Params p) {
+  constexpr bool ASSIGN = MODE == ASSIGN_IDS;
+  constexpr bool QUANT = MODE == PROJECT_QUANT;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -66,7 +78,7 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   uint64_t* bars = reinterpret_cast<uint64_t*>(meta);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(meta + NUM_BARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(meta + NUM_BARS * 8 + 4);
-  float* xn_part = reinterpret_cast<float*>(meta + 128);          // [128][2]
+  float* xn_part = reinterpret_cast<float*>(meta + META_HEAD);    // [128][2]
   float* cand_d = xn_part + 256;                                  // [128]
   int* cand_i = reinterpret_cast<int*>(cand_d + 128);             // [128]
   float* cn_part = reinterpret_cast<float*>(cand_i + 128);        // [C][2]
@@ -86,6 +98,7 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     mbar_init(&bars[ACC_DONE], 1);
     mbar_init(&bars[SIDE_READY], COMPUTE_THREADS);
     mbar_init(&bars[CAND_READY], 128);
+    mbar_init(&bars[PEER_READY], 128);
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -95,6 +108,10 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // the column-half CTAs of one token tile write into each other's shared memory: nobody may do so
+  // before the peer's barriers exist
+  const bool paired = QUANT && p.column_parts == 2;
+  if (paired) cluster_sync_all();
 
   if (warp == 8) {
     if (lane == 0) {
@@ -281,7 +298,66 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         mbar_arrive(&bars[A_FULL + s]);
       }
       if (ok) ok = mbar_wait(&bars[ACC_DONE], 0, abort_flag, 450);
-      if (ok) {
+      if (ok && QUANT) {
+        // ---- quantise + pack from TMEM.  Pass 1: |max| of the bf16-rounded coefficients of this
+        // thread's column chunks; the two warpgroups, then the two column-half CTAs, combine.
+        tc_fence_after();
+        const int nc = p.NACC * p.NB;
+        const int tok = m0 + row;
+        float amax = 0.f;
+#pragma unroll 1
+        for (int cc = wg; cc < nc / 32; cc += 2) {
+          const int col = cc * 32, acc = col / p.NB;
+          float v[32];
+          tmem_ld32(tmem_base + lane_sel + acc * 256 + (col - acc * p.NB), v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(round_to_bf16(v[j])));
+        }
+        xn_part[wg * 128 + row] = amax;
+        mbar_arrive(&bars[SIDE_READY]);
+        ok = mbar_wait(&bars[SIDE_READY], 0, abort_flag, 451);
+        if (ok) {
+          amax = fmaxf(xn_part[row], xn_part[128 + row]);
+          if (paired) {
+            if (wg == 0) {
+              const uint32_t peer = cluster_ctarank() ^ 1u;
+              st_cluster_b32(map_to_cta(smem_u32(&cand_d[row]), peer), __float_as_uint(amax));
+              mbar_arrive_cluster(map_to_cta(smem_u32(&bars[PEER_READY]), peer));
+            }
+            ok = mbar_wait_cluster(&bars[PEER_READY], 0, abort_flag, 452);
+            if (ok) amax = fmaxf(amax, cand_d[row]);
+          }
+        }
+        if (ok) {
+          float scale;
+          if (p.in_bf16) scale = round_to_bf16(__fdiv_rn(fmaxf(amax, round_to_bf16(p.eps)), 7.0f));
+          else scale = __fdiv_rn(fmaxf(amax, p.eps), 7.0f);
+          const float inv = __frcp_rn(scale);
+#pragma unroll 1
+          for (int cc = wg; cc < nc / 32; cc += 2) {
+            const int col = cc * 32, acc = col / p.NB;
+            float v[32];
+            tmem_ld32(tmem_base + lane_sel + acc * 256 + (col - acc * p.NB), v);
+            uint32_t words[4];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              uint32_t out = 0;
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const float z0 = round_to_bf16(v[w * 8 + 2 * k]), z1 = round_to_bf16(v[w * 8 + 2 * k + 1]);
+                const int c0 = p.in_bf16 ? quant_code<true>(z0, scale, inv) : quant_code<false>(z0, scale, inv);
+                const int c1 = p.in_bf16 ? quant_code<true>(z1, scale, inv) : quant_code<false>(z1, scale, inv);
+                out |= static_cast<uint32_t>(c0 | (c1 << 4)) << (8 * k);
+              }
+              words[w] = out;
+            }
+            if (tok < m_end)
+              *reinterpret_cast<uint4*>(p.codes + static_cast<size_t>(tok) * (p.n_total >> 1) +
+                                        ((n_base + col) >> 1)) = make_uint4(words[0], words[1], words[2], words[3]);
+          }
+          if (wg == 0 && blockIdx.y == 0 && tok < m_end) store_float(p.scales, p.scale_dtype, tok, scale);
+        }
+      } else if (ok) {
         tc_fence_after();
         const int nc = p.NACC * p.NB;
         const int tok = m0 + row;
@@ -309,6 +385,8 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   tc_fence_before();
   __syncthreads();
   if (warp == 9) tmem_dealloc(tmem_base, 512);
+  // neither CTA of a pair leaves while the other may still write into its shared memory
+  if (paired) cluster_sync_all();
 }
 
 // split n_total columns into grid.y CTAs x NACC accumulators x NB columns
@@ -323,7 +401,7 @@ bool plan_columns(int n_total, int* gy, int* nacc, int* nb) {
 }
 
 size_t smem_bytes(int nacc, int nb, int n_total, int stages = 2) {
-  return stages * static_cast<size_t>(A_BYTES + nacc * nb * 128) + 128 + 4 * (256 + 128 + 128) +
+  return stages * static_cast<size_t>(A_BYTES + nacc * nb * 128) + META_HEAD + 4 * (256 + 128 + 128) +
          8 * static_cast<size_t>(n_total) + 1024;
 }
 
@@ -396,13 +474,68 @@ int tc_project(const void* x_bf16, const void* centers_bf16, const void* ids, in
   if (rc != NKV_OK) return rc;
   p.nstages = pick_stages(p.NACC, p.NB, 0);
   size_t smem = smem_bytes(p.NACC, p.NB, 0, p.nstages);
-  auto kernel = encode_gemm_kernel<false>;
+  auto kernel = encode_gemm_kernel<PROJECT>;
   NKV_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(smem)));
   p.rows = pick_rows(S, gy);
   dim3 grid(ceil_div(S, p.rows), gy);
   kernel<<<grid, THREADS, smem, stream>>>(map_b, map_b, p);
   NKV_LAUNCH_CHECK("encode_gemm_kernel<project>");
+  return NKV_OK;
+}
+
+bool tc_project_quant_supported(int J, int r, int group) {
+  int gy, nacc, nb;
+  return group == r && r % 64 == 0 && tc_project_supported(J, r) && plan_columns(r, &gy, &nacc, &nb) && gy <= 2;
+}
+
+int tc_project_quant(const void* x_bf16, const void* centers_bf16, const void* ids, int id_bytes,
+                     const float* mean, const void* encoder_bf16, int S, int J, int r, float eps,
+                     int quant_mode, int scale_dtype, uint8_t* codes, void* scales, cudaStream_t stream) {
+  if (S == 0) return NKV_OK;
+  Params p{};
+  int gy;
+  NKV_REQUIRE(plan_columns(r, &gy, &p.NACC, &p.NB) && gy <= 2, NKV_ERR_UNSUPPORTED,
+              "fused projection: rank %d cannot be tiled over at most two column parts", r);
+  NKV_REQUIRE((reinterpret_cast<uintptr_t>(x_bf16) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(centers_bf16) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(mean) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(codes) & 15) == 0 && (r / 2) % 16 == 0,
+              NKV_ERR_INVALID, "fused projection operands must be 16-byte aligned");
+  p.S = S; p.J = J; p.n_total = r;
+  p.x = static_cast<const uint16_t*>(x_bf16);
+  p.centers = static_cast<const uint16_t*>(centers_bf16);
+  p.ids = ids; p.id_bytes = id_bytes; p.mean = mean;
+  p.codes = codes; p.scales = scales; p.eps = eps;
+  p.in_bf16 = quant_mode == NKV_QUANT_IN_BF16 ? 1 : 0;
+  p.scale_dtype = scale_dtype;
+  p.column_parts = gy;
+  CUtensorMap map_b;
+  uint64_t dims[2] = {static_cast<uint64_t>(J), static_cast<uint64_t>(r)};
+  uint64_t strides[1] = {static_cast<uint64_t>(J) * 2};
+  uint32_t box[2] = {64, static_cast<uint32_t>(p.NB)};
+  int rc = encode_tensor_map(&map_b, 2, encoder_bf16, 2, dims, strides, box, 128);
+  if (rc != NKV_OK) return rc;
+  p.nstages = pick_stages(p.NACC, p.NB, 0);
+  size_t smem = smem_bytes(p.NACC, p.NB, 0, p.nstages);
+  auto kernel = encode_gemm_kernel<PROJECT_QUANT>;
+  NKV_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                static_cast<int>(smem)));
+  p.rows = pick_rows(S, gy);
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(ceil_div(S, p.rows), gy);
+  config.blockDim = dim3(THREADS);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeClusterDimension;
+  attribute.val.clusterDim.x = 1;
+  attribute.val.clusterDim.y = gy;
+  attribute.val.clusterDim.z = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  NKV_CUDA(cudaLaunchKernelEx(&config, kernel, map_b, map_b, p));
+  NKV_LAUNCH_CHECK("encode_gemm_kernel<project + quantise>");
   return NKV_OK;
 }
 
@@ -431,7 +564,7 @@ int tc_assign(const void* x_bf16, const void* centers_bf16, int S, int J, int C,
   }
   p.nstages = pick_stages(p.NACC, p.NB, C);
   size_t smem = smem_bytes(p.NACC, p.NB, C, p.nstages);
-  auto kernel = encode_gemm_kernel<true>;
+  auto kernel = encode_gemm_kernel<ASSIGN_IDS>;
   NKV_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(smem)));
   p.rows = pick_rows(S, 1);

@@ -159,8 +159,8 @@ def encode_tensor(value: torch.Tensor, *, target: str, layer: int, sp_rank: int,
     rows = value.reshape(sequence, joint_dim).contiguous()
     init = kmeans_init_rows(sequence, clusters, _seed(layer, sp_rank, target)).to(value.device)
     centers, ids = ops.kmeans(rows, clusters, iters, init)
-    coeff = ops.project(rows, centers, ids, op.mean, op.encoder)
-    packed, scale = ops.quant_pack(coeff, eps=LINGBOT_QUANT.eps, in_coeff_dtype=False)
+    packed, scale = ops.project_quant(rows, centers, ids, op.mean, op.encoder, eps=LINGBOT_QUANT.eps,
+                                      in_coeff_dtype=False)
     return {
         "format": FORMAT, "target": target, "layer": layer, "sp_rank": sp_rank,
         "shape": (batch, sequence, heads, head_dim), "rank": rank,

@@ -67,9 +67,8 @@ def encode_tensor(kind: str, layer: int, value: torch.Tensor) -> dict:
     rows = value[0].contiguous()
     init = kmeans_init_rows(sequence, clusters, 20260804 + int(layer)).to(value.device)
     centers, ids = ops.kmeans(rows, clusters, _iterations(), init)
-    coeff = ops.project(rows, centers, ids, op.mean, op.encoder)
-    packed, scale = ops.quant_pack(coeff, eps=F32_EPS,
-                                   in_coeff_dtype=coeff.dtype == torch.bfloat16)
+    packed, scale = ops.project_quant(rows, centers, ids, op.mean, op.encoder, eps=F32_EPS,
+                                      in_coeff_dtype=op.dtype == torch.bfloat16)
     return {
         "codec": CODEC, "kind": kind, "layer": int(layer),
         "shape": tuple(int(v) for v in value.shape),

@@ -115,6 +115,40 @@ def quant_pack(coeff, *, group=None, eps=1.1920928955078125e-07, in_coeff_dtype=
     return codes, scales
 
 
+def project_quant(x, centers_bf16, ids, mean, encoder, *, group=None, eps=1.1920928955078125e-07,
+                  in_coeff_dtype=False, scale_dtype=torch.bfloat16, codes=None, scales=None):
+    """project + quant_pack of rows whose centre ids are known -> (codes u8 [S,r/2], scales
+    [S,r/group]); one kernel (coefficients never leave the chip) for bf16 operands with one scale per
+    token, the two kernels through a scratch tensor otherwise.  Same bytes either way."""
+    device = _require_cuda(x, centers_bf16, ids, mean, encoder, codes, scales)
+    S, J = x.shape
+    r = encoder.shape[0]
+    group = r if group is None else int(group)
+    if codes is None:
+        codes = torch.empty(S, r // 2, dtype=torch.uint8, device=device)
+    if scales is None:
+        scales = torch.empty(S, r // group, dtype=scale_dtype, device=device)
+    fused = (x.dtype == encoder.dtype == torch.bfloat16 and group == r and r % 64 == 0
+             and not _SIMT_FORCED[0] and codes.data_ptr() % 16 == 0)
+    workspace = None if fused else torch.empty(S, r, dtype=encoder.dtype, device=device)
+    status = _lib.library().nkv_project_quant(
+        _ptr(x), dtype_code(x.dtype), _ptr(centers_bf16), _ptr(ids), ids.element_size(), _ptr(mean),
+        _ptr(encoder), dtype_code(encoder.dtype), S, J, r, group, float(eps),
+        NKV_QUANT_IN_BF16 if in_coeff_dtype else NKV_QUANT_F32, dtype_code(scales.dtype), _ptr(codes),
+        _ptr(scales), _ptr(workspace), 0 if workspace is None else workspace.numel() * workspace.element_size(),
+        _stream(device))
+    if status == _lib.NKV_ERR_INVALID and workspace is None:
+        # the single-kernel form did not apply to this shape after all: once more with scratch
+        workspace = torch.empty(S, r, dtype=encoder.dtype, device=device)
+        status = _lib.library().nkv_project_quant(
+            _ptr(x), dtype_code(x.dtype), _ptr(centers_bf16), _ptr(ids), ids.element_size(), _ptr(mean),
+            _ptr(encoder), dtype_code(encoder.dtype), S, J, r, group, float(eps),
+            NKV_QUANT_IN_BF16 if in_coeff_dtype else NKV_QUANT_F32, dtype_code(scales.dtype), _ptr(codes),
+            _ptr(scales), _ptr(workspace), workspace.numel() * workspace.element_size(), _stream(device))
+    _lib.check(status)
+    return codes, scales
+
+
 # ---------------------------------------------------------------------- history view
 @dataclass
 class HistoryView:

@@ -39,6 +39,56 @@ def test_quant_pack_is_bit_exact(dtype, group, in_coeff_dtype, scale_dtype):
     assert torch.equal(got_scale.cpu().view(torch.int16), want_scale.view(torch.int16))
 
 
+@pytest.mark.parametrize("rank", [64, 320, 384, 640, 1024])
+@pytest.mark.parametrize("group", [None, 32])
+@pytest.mark.parametrize("in_coeff_dtype", [False, True])
+def test_quant_pack_row_widths_are_bit_exact(rank, group, in_coeff_dtype):
+    """Every lanes-per-token layout of the vectorised kernel (8, 16, 32 lanes), a token count that
+    leaves the last warp partly empty, ties at exact halves."""
+    gen = synthetic.generator(rank)
+    coeff = (torch.randn(1001, rank, generator=gen) * torch.logspace(-2, 2, 1001)[:, None]).to(torch.bfloat16)
+    coeff[3] = 0
+    coeff[4, ::2] = 3.5
+    coeff[4, 1] = 7.0
+    want_codes, want_scale = oracle.quantize_rows(coeff, group=group, eps=oracle.F32_EPS,
+                                                  in_coeff_dtype=in_coeff_dtype)
+    want_packed, _ = oracle.pack_int4(want_codes)
+    got_packed, got_scale = ops.quant_pack(coeff.cuda(), group=group, eps=oracle.F32_EPS,
+                                           in_coeff_dtype=in_coeff_dtype)
+    assert torch.equal(got_packed.cpu().reshape(-1), want_packed)
+    assert torch.equal(got_scale.cpu().view(torch.int16), want_scale.view(torch.int16))
+
+
+@pytest.mark.parametrize("S,J,rank,clusters", [(1000, 512, 640, 64), (12480, 1024, 640, 64), (300, 256, 384, 16),
+                                               (129, 256, 64, 8), (2000, 512, 320, 32), (700, 256, 1024, 8)])
+@pytest.mark.parametrize("in_coeff_dtype", [False, True])
+@pytest.mark.parametrize("scale_dtype", [torch.bfloat16, torch.float16])
+def test_project_quant_equals_project_then_quant_pack(S, J, rank, clusters, in_coeff_dtype, scale_dtype):
+    """The single-kernel projection + quantiser + packing (coefficients kept on chip, per-token
+    maximum swapped between the two column-half thread blocks) writes the same bytes as the
+    projection kernel followed by the quantiser kernel; shapes outside it take the two kernels."""
+    gen = synthetic.generator(S + rank)
+    centers = torch.randn(clusters, J, generator=gen).to(torch.bfloat16).cuda()
+    ids = torch.randint(clusters, (S,), generator=gen).to(torch.uint8).cuda()
+    rows = (centers[ids.long()].float().cpu() + 0.4 * torch.randn(S, J, generator=gen)).to(torch.bfloat16).cuda()
+    mean = (0.05 * torch.randn(J, generator=gen)).cuda()
+    encoder = (torch.randn(rank, J, generator=gen) / math.sqrt(J)).to(torch.bfloat16).cuda()
+    coeff = ops.project(rows, centers, ids, mean, encoder)
+    want_codes, want_scales = ops.quant_pack(coeff, eps=oracle.F32_EPS, in_coeff_dtype=in_coeff_dtype,
+                                             scale_dtype=scale_dtype)
+    got_codes, got_scales = ops.project_quant(rows, centers, ids, mean, encoder, eps=oracle.F32_EPS,
+                                              in_coeff_dtype=in_coeff_dtype, scale_dtype=scale_dtype)
+    assert torch.equal(got_codes, want_codes)
+    assert torch.equal(got_scales.view(torch.int16), want_scales.view(torch.int16))
+    # 32-wide groups are outside the single-kernel form: same entry point, two kernels
+    grouped = ops.project_quant(rows, centers, ids, mean, encoder, group=32, eps=oracle.F32_EPS,
+                                in_coeff_dtype=in_coeff_dtype, scale_dtype=scale_dtype)
+    want_grouped = ops.quant_pack(coeff, group=32, eps=oracle.F32_EPS, in_coeff_dtype=in_coeff_dtype,
+                                  scale_dtype=scale_dtype)
+    assert torch.equal(grouped[0], want_grouped[0])
+    assert torch.equal(grouped[1].view(torch.int16), want_grouped[1].view(torch.int16))
+
+
 def test_quant_pack_empty_input():
     packed, scale = ops.quant_pack(torch.zeros(0, 64, device="cuda"))
     assert packed.shape == (0, 32) and scale.shape == (0, 1)
