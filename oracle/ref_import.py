@@ -20,6 +20,7 @@ from pathlib import Path
 
 MG = "models/Matrix-Game-3.5/fast"
 LB = "models/LingBot-World-2.0/fast"
+HY = "models/HY-WorldPlay/fast"
 
 
 def reference_root(root: str | os.PathLike | None = None) -> Path:
@@ -95,3 +96,17 @@ def inject_lingbot_operator(codec, root_tag: str, target: str, layer: int, *, jo
     key = (codec._resolved_path(root_tag), "", codec._resolved_path(prepacked) if prepacked else "",
            target, 0, int(layer), int(joint_dim), int(rank), "cpu")
     codec._OPERATORS[key] = {"mean": mean.float(), "encoder": encoder, "decoder": decoder}
+
+
+def load_hy_reader(root=None):
+    """HY-WorldPlay's direct latent attention module (two-branch dictionary reader) and its codec
+    helpers, under empty stand-in parent packages (hyvideo/.../direct_codec_latent_attention.py)."""
+    root = reference_root(root)
+    base = root / HY / "hyvideo"
+    for name, path in (("hyvideo", base), ("hyvideo.models", base / "models"),
+                       ("hyvideo.models.transformers", base / "models/transformers"),
+                       ("hyvideo.models.transformers.modules", base / "models/transformers/modules"),
+                       ("hyvideo.prope", base / "prope")):
+        _stub_package(name, path)
+    import importlib
+    return importlib.import_module("hyvideo.models.transformers.modules.direct_codec_latent_attention")

@@ -263,3 +263,67 @@ def build_attend_reader(case: CodecCase, data: dict) -> dict:
     gen = synthetic.generator(case.seed + 4000)
     return synthetic.make_reader(case.shape, gen, [(list(heads), width) for heads, width in ATTEND_GROUPS],
                                  k_decoder=data["k_op"]["decoder"], v_decoder=data["v_op"]["decoder"])
+
+
+# HY-WorldPlay two-branch dictionary reader (Main-RoPE branch + PRoPE branch over all heads)
+HY_SHAPE = dict(heads=4, head_dim=128, rank=64, centres=16, history=512, history_cameras=4, queries=96,
+                query_cameras=2, text=24, main_width=64, prope_quartets=16)
+
+
+def _se3(count: int, gen) -> torch.Tensor:
+    """Random rigid transforms [1, count, 4, 4]."""
+    rotation, _ = torch.linalg.qr(torch.randn(count, 3, 3, generator=gen))
+    out = torch.zeros(1, count, 4, 4)
+    out[0, :, :3, :3] = rotation
+    out[0, :, :3, 3] = 0.3 * torch.randn(count, 3, generator=gen)
+    out[0, :, 3, 3] = 1.0
+    return out
+
+
+def _rope_tables(tokens: int, dim: int, gen):
+    """(cos, sin) [tokens, dim] with every pair of neighbouring channels sharing its angle."""
+    angles = (torch.rand(tokens, dim // 2, generator=gen) - 0.5) * 30.0
+    return angles.cos().repeat_interleave(2, dim=1), angles.sin().repeat_interleave(2, dim=1)
+
+
+def build_hy() -> dict:
+    """State, cache payloads and call inputs of one HY two-branch read, seeded."""
+    cfg = HY_SHAPE
+    gen = synthetic.generator(6001)
+    H, D, r, C, N, S, E = (cfg[k] for k in ("heads", "head_dim", "rank", "centres", "history", "queries", "text"))
+    dm, dp = cfg["main_width"], 4 * cfg["prope_quartets"]
+    bf = torch.bfloat16
+    pairs = torch.stack([torch.randperm(D // 2, generator=gen)[:dm // 2].sort().values for _ in range(H)])
+    state = {
+        "main_indices": torch.stack((2 * pairs, 2 * pairs + 1), dim=2).reshape(H, dm),
+        "q_main_reduce": (torch.randn(H, dm, D, generator=gen) / math.sqrt(D) * 1.5).to(bf),
+        "q_prope_mix": torch.randn(H, cfg["prope_quartets"], D // 4, generator=gen) / math.sqrt(D // 4) * 1.5,
+        "k_main_read": (torch.randn(H, dm, r, generator=gen) / math.sqrt(r)).to(bf),
+        "k_prope_read": (torch.randn(H, dp, r, generator=gen) / math.sqrt(r)).to(bf),
+        "v_main_read": (torch.randn(H, dm, r, generator=gen) / math.sqrt(r)).to(bf),
+        "v_prope_read": (torch.randn(H, dp, r, generator=gen) / math.sqrt(r)).to(bf),
+        "v_main_lift": (torch.randn(H, dm, D, generator=gen) / math.sqrt(dm)).to(bf),
+        "v_prope_mix": torch.randn(H, cfg["prope_quartets"], D // 4, generator=gen) / math.sqrt(cfg["prope_quartets"]),
+        "log_residual_scale_main": 0.2 * torch.randn(H, generator=gen),
+        "log_residual_scale_prope": 0.2 * torch.randn(H, generator=gen),
+    }
+
+    def payload():
+        codes = torch.randint(-7, 8, (1, N, r), generator=gen, dtype=torch.int8)
+        return {"codes": codes,
+                "latent_scale": (torch.rand(1, N, 1, generator=gen) * 0.3 + 0.05).to(bf),
+                "latent_shape": (1, N, r), "latent_numel": N * r,
+                "centre_main": (0.5 * torch.randn(1, H, C, dm, generator=gen)).to(bf),
+                "centre_prope": (0.5 * torch.randn(1, H, C, dp, generator=gen)).to(bf),
+                "semantic_ids": torch.randint(C, (1, N), generator=gen)}
+
+    out = {"state": state, "k_vision": payload(), "v_vision": payload(),
+           "vision_freqs": _rope_tables(N, D, gen), "current_freqs": _rope_tables(S, D, gen),
+           "vision_viewmats": _se3(cfg["history_cameras"], gen), "current_viewmats": _se3(cfg["query_cameras"], gen),
+           "q_pre": torch.randn(1, S, H, D, generator=gen).to(bf),
+           "query": torch.randn(2, H, S, D, generator=gen).to(bf),
+           "current_key": torch.randn(2, H, S, D, generator=gen).to(bf),
+           "current_value": torch.randn(2, H, S, D, generator=gen).to(bf),
+           "encoder_key": torch.randn(2, H, E, D, generator=gen).to(bf),
+           "encoder_value": torch.randn(2, H, E, D, generator=gen).to(bf)}
+    return out

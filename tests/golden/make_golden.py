@@ -454,6 +454,37 @@ def run_attend_case(case: cases.CodecCase, root) -> dict:
             "start": np.array([start], dtype=np.int64)}
 
 
+def run_hy_case(root) -> dict:
+    """_attend_dictionary_lowkv of HY-WorldPlay's direct latent attention module: Main-RoPE and PRoPE
+    branches over a packed INT4 history with per-branch centre tables, native attention over the
+    text and current tokens, lift and log-sum-exp combine.  The module's _flash_lse calls a
+    CUDA-only ATen kernel; for this CPU run it is replaced by the exact fp32 softmax attention of
+    the Matrix-Game core module (attention_lse), which is the only substituted piece."""
+    hy = ref_import.load_hy_reader(root)
+    core = ref_import.load_mg_core(root)
+    from hyvideo.models.transformers.modules.kv_codecs import pack_quantized_codes
+    data = cases.build_hy()
+    for name in list(os.environ):
+        if name.startswith("HY_DIRECT_CODEC"):
+            os.environ.pop(name)
+    os.environ["HY_DIRECT_CODEC_LATENT_READ_CACHE"] = "0"
+    hy._flash_lse = lambda q, k, v, scale=None: core.attention_lse(q, k, v, scale=scale)
+    cache = {"vision_freqs_cis": data["vision_freqs"], "vision_viewmats": data["vision_viewmats"],
+             "vision_Ks": None}
+    for name in ("k_vision", "v_vision"):
+        part = dict(data[name])
+        part["latent_int4"] = pack_quantized_codes(part.pop("codes"), 4)
+        cache[name] = part
+    cfg = cases.HY_SHAPE
+    runtime = {"recent_native_frames": 0, "attention": data["state"], "main_k_mode": "learned_rope",
+               "shape": (cfg["heads"], cfg["head_dim"], cfg["heads"], cfg["head_dim"])}
+    main, prope = hy._attend_dictionary_lowkv(
+        0, data["q_pre"], data["query"], data["current_key"], data["current_value"], data["encoder_key"],
+        data["encoder_value"], cache, data["current_freqs"], data["current_viewmats"], None, runtime)
+    return {"main": bits(main), "prope": bits(prope), "packed_k": cache["k_vision"]["latent_int4"].numpy(),
+            "q_digest": np.array([checksum(data["q_pre"])], dtype=np.uint64)}
+
+
 def run_protected_tokens_case(root) -> dict:
     """protected_tokens of the MG core module on seeded frame-id sequences."""
     core = ref_import.load_mg_core(root)
@@ -539,6 +570,7 @@ def main() -> None:
     save("fast_hooks_bf16", lambda: run_fast_hooks_case(cases.FAST_CASES[1], root))
     save("stream_lb_bf16", lambda: run_stream_case(cases.ROLLING, root))
     save("attend_lb_bf16", lambda: run_attend_case(cases.ROLLING, root))
+    save("hy_two_branch_bf16", lambda: run_hy_case(root))
     save("protected_tokens", lambda: run_protected_tokens_case(root))
     save("merge_edge", lambda: run_merge_case(root))
     save("select_mg_bf16", lambda: run_select_case(cases.MINI_BF16, root))

@@ -1,0 +1,73 @@
+"""HY-WorldPlay's two-branch dictionary reader (the reference function's argument list) on the GPU,
+against a fixture the reference function produced (its CUDA-only attention call replaced by exact
+fp32 softmax attention for the CPU run; everything else unmodified)."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+from helpers import BF16_REL_TOL, rel_err
+from nanokv_b200 import hy_reader, ops
+from oracle import nkv_oracle as oracle
+from test_oracle_golden import from_bits, load
+
+pytestmark = pytest.mark.gpu
+
+
+def build_call(data):
+    cfg = cases.HY_SHAPE
+    cache = {"vision_freqs_cis": data["vision_freqs"], "vision_viewmats": data["vision_viewmats"],
+             "vision_Ks": None}
+    for name in ("k_vision", "v_vision"):
+        part = dict(data[name])
+        codes = part.pop("codes")
+        packed, _ = oracle.pack_int4(codes.reshape(-1, cfg["rank"]))
+        part["latent_int4"] = packed
+        cache[name] = part
+    runtime = {"recent_native_frames": 0, "attention": data["state"], "main_k_mode": "learned_rope",
+               "shape": (cfg["heads"], cfg["head_dim"], cfg["heads"], cfg["head_dim"])}
+    return cache, runtime
+
+
+def test_two_branch_reader_against_the_reference_fixture():
+    gold, data = load("hy_two_branch_bf16"), cases.build_hy()
+    cache, runtime = build_call(data)
+    # the packed bytes the reference's own packer made are the bytes this library reads
+    assert np.array_equal(gold["packed_k"], cache["k_vision"]["latent_int4"].numpy())
+    cuda = lambda name: data[name].cuda()
+    main, prope = hy_reader.attend_dictionary_lowkv(
+        0, cuda("q_pre"), cuda("query"), cuda("current_key"), cuda("current_value"), cuda("encoder_key"),
+        cuda("encoder_value"), cache, data["current_freqs"], data["current_viewmats"], None, runtime)
+    ops.check_status()
+    cfg = cases.HY_SHAPE
+    assert main.shape == prope.shape == (1, cfg["queries"], cfg["heads"] * cfg["head_dim"])
+    want_main = from_bits(gold["main"], torch.bfloat16)
+    want_prope = from_bits(gold["prope"], torch.bfloat16)
+    assert rel_err(main.cpu(), want_main) <= BF16_REL_TOL
+    assert rel_err(prope.cpu(), want_prope) <= BF16_REL_TOL
+    # the two branches are different reads: neither output equals the other
+    assert rel_err(main.cpu(), want_prope) > 4 * BF16_REL_TOL
+    # second call on the same state reuses the prepared operands and the cached views
+    again, _ = hy_reader.attend_dictionary_lowkv(
+        0, cuda("q_pre"), cuda("query"), cuda("current_key"), cuda("current_value"), cuda("encoder_key"),
+        cuda("encoder_value"), cache, data["current_freqs"], data["current_viewmats"], None, runtime)
+    assert torch.equal(again, main)
+    with pytest.raises(NotImplementedError):
+        hy_reader.attend_dictionary_lowkv(
+            0, cuda("q_pre"), cuda("query"), cuda("current_key"), cuda("current_value"), cuda("encoder_key"),
+            cuda("encoder_value"), cache, data["current_freqs"], data["current_viewmats"], None,
+            dict(runtime, recent_native_frames=2))
+
+
+def test_projection_matrices_match_the_closed_forms():
+    gen = torch.Generator().manual_seed(4)
+    view = cases._se3(3, gen)
+    P, P_T, P_inv = hy_reader.projection_matrices(view, None)
+    assert torch.allclose(P @ P_inv, torch.eye(4).expand(1, 3, 4, 4), atol=1e-5)
+    assert torch.equal(P_T, P.transpose(-1, -2))
+    Ks = torch.zeros(1, 3, 3, 3)
+    Ks[..., 0, 0], Ks[..., 1, 1], Ks[..., 2, 2] = 1.3, 0.8, 1.0
+    Ks[..., 0, 2], Ks[..., 1, 2] = 0.4, 0.6          # the principal point is dropped by the reference
+    P, _, P_inv = hy_reader.projection_matrices(view, Ks)
+    assert torch.allclose(P @ P_inv, torch.eye(4).expand(1, 3, 4, 4), atol=1e-5)
+    assert torch.allclose(P[..., 0, :], 1.3 * view[..., 0, :], atol=1e-6)
