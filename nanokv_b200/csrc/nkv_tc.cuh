@@ -53,6 +53,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait that lets the hardware park the thread for up to `ns` nanoseconds while the phase is
+// pending (it wakes when the phase completes), instead of coming back at once to spin
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  `abort_flag` lives in shared memory; `code` identifies the
 // wait site in the status word the host reads.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,

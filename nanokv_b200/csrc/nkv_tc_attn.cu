@@ -57,11 +57,14 @@ constexpr int NSTAGE = 4;         // latent staging slots in tensor memory
 constexpr int NDONE = 8;          // "MMAs of pair g are complete" barriers, indexed by g % 8
 constexpr int KVS = 2;            // K / V stages of a consumer
 constexpr int META_BYTES = 3072;  // barriers, flags and per-token metadata at the head of shared memory
-constexpr int MAX_RING = 16;      // ring slots per group (GF - GF_DONE flag words)
+constexpr int MAX_RING = 56;      // ring slots per group (GF - GF_DONE flag words)
 constexpr int NMETA = 4;          // metadata buffers of a producer (it prepares up to four jobs ahead)
 constexpr float RESCALE_THRESHOLD = 8.0f;
 constexpr float SCORE_WINDOW = 96.0f;   // log2 units a score may exceed the row's reference point by
-constexpr int STATUS_SCORE_RANGE = 950; // status word: a row's scores left that window (its LSE is NaN)
+constexpr int STATUS_SCORE_RANGE = 950;
+// log2(1 + 2^-9) and 1 / (1 + 2^-9): half a bf16 step above a value, as an exponent offset and back
+constexpr float HALF_STEP_LOG2 = 0.0028150156070540f;
+constexpr float HALF_STEP_INV = 0.998050682261209f; // status word: a row's scores left that window (its LSE is NaN)
 
 enum Bar {
   // consumer
@@ -81,8 +84,8 @@ static_assert(M_ABORT + 4 <= M_CROW && M_CROW + NMETA * TOK * 4 <= META_BYTES, "
 // global flag words
 constexpr int F_ABORT = 0;        // launch-wide abort (wait-site code)
 constexpr int F_GROUPS = 32;      // then per group GF words:
-constexpr int GF = 32;            //   [0, 8): tiles published by producer p of the group (K producers first)
-constexpr int GF_DONE = 8;        //   [8, 24): per ring slot, consumers that have taken the slot's tiles
+constexpr int GF = 64;            //   [0, 8): tiles published by producer p of the group (K producers first)
+constexpr int GF_DONE = 8;        //   [8, 64): per ring slot, consumers that have taken the slot's tiles
 constexpr int MAX_PROD = 8;
 
 struct Params {
@@ -131,6 +134,10 @@ __device__ __forceinline__ int ld_relaxed(const int32_t* p) {
   asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+// two positive fp32 values -> bf16 pair (lo in the low half) by dropping their low 16 bits
+__device__ __forceinline__ uint32_t truncate_bf16x2(float lo, float hi) {
+  return __byte_perm(__float_as_uint(lo), __float_as_uint(hi), 0x7632);
+}
 __device__ __forceinline__ int ld_acquire(const int32_t* p) {
   int v;
   asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -174,9 +181,12 @@ __device__ __forceinline__ bool mwait(uint64_t* bar, uint32_t parity, const Ctx&
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
   unsigned spins = 0;
+  // A waiting warp must not eat the issue slots of the warps that compute on its scheduler (the
+  // other query tile's softmax, above all): it parks in the barrier unit and comes back when the
+  // phase completes or after a microsecond, whichever is first.
   while (true) {
     if (*c.abort_flag) return false;
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_parked(bar, parity, 1000u)) return true;
     if ((++spins & 63u) == 0 && wait_expired(c, start, code)) return false;
   }
 }
@@ -628,6 +638,12 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
         // One pass over the scores: P (bf16 pairs) replaces S in place -- the 16 cells written per
         // step lie below the 32 read -- and the load of the next 32 scores stays in flight under the
         // exponentials of the current ones.
+        // Weights go to bf16 by dropping the low 16 bits (one byte permute per pair) instead of a
+        // rounding conversion, which runs on the same quarter-rate unit as the exponentials and
+        // would take a third of its time.  So that the dropped bits do not bias the weights, every
+        // weight is raised by half a bf16 step first -- for free, as HALF_STEP_LOG2 in the exponent --
+        // and the row sum, which then carries the same factor, is divided by it once per unit.
+        const float neg_ref = HALF_STEP_LOG2 - m_used;
         float sum = 0.f, sum_b = 0.f, sum_c = 0.f, sum_d = 0.f;   // four chains instead of one
         uint32_t pmax_a = 0u, pmax_b = 0u;
         {
@@ -636,19 +652,25 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
 #pragma unroll
           for (int cc = 0; cc < TOK / 32; ++cc) {
             uint32_t (&cur)[32] = raw[cc & 1];
+            laps.lap(1);
             tmem_ld32_wait(cur);
+            laps.lap(cc == 0 ? 4 : 5);
             if (cc + 1 < TOK / 32) tmem_ld32_issue(s_addr + (cc + 1) * 32, raw[(cc + 1) & 1]);
             uint32_t packed[16];
             if (valid == TOK) {
+              // three passes over the chunk, each a run of independent instructions: exponent
+              // arguments, exponentials (back to back, so the unit never waits for a consumer of an
+              // earlier result), then sums and packing
+              float w[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) w[j] = fmaf(__uint_as_float(cur[j]), p.scale_log2, neg_ref);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) w[j] = exp2_approx(w[j]);
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
-                const float p0 = exp2_approx(fmaf(__uint_as_float(cur[j]), p.scale_log2, -m_used));
-                const float p1 = exp2_approx(fmaf(__uint_as_float(cur[j + 1]), p.scale_log2, -m_used));
-                const float p2 = exp2_approx(fmaf(__uint_as_float(cur[j + 2]), p.scale_log2, -m_used));
-                const float p3 = exp2_approx(fmaf(__uint_as_float(cur[j + 3]), p.scale_log2, -m_used));
-                sum += p0; sum_b += p1; sum_c += p2; sum_d += p3;
-                packed[j >> 1] = pack_bf16x2(p0, p1);
-                packed[(j >> 1) + 1] = pack_bf16x2(p2, p3);
+                sum += w[j]; sum_b += w[j + 1]; sum_c += w[j + 2]; sum_d += w[j + 3];
+                packed[j >> 1] = truncate_bf16x2(w[j], w[j + 1]);
+                packed[(j >> 1) + 1] = truncate_bf16x2(w[j + 2], w[j + 3]);
               }
               // the largest weight of the chunk, on the packed pairs (weights are positive, so the
               // bf16 bit patterns order like the numbers): half an instruction per score
@@ -660,10 +682,10 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
             } else {
 #pragma unroll
               for (int j = 0; j < 32; j += 2) {
-                float p0 = (cc * 32 + j < valid) ? exp2f(fmaf(__uint_as_float(cur[j]), p.scale_log2, -m_used)) : 0.f;
-                float p1 = (cc * 32 + j + 1 < valid) ? exp2f(fmaf(__uint_as_float(cur[j + 1]), p.scale_log2, -m_used)) : 0.f;
+                float p0 = (cc * 32 + j < valid) ? exp2f(fmaf(__uint_as_float(cur[j]), p.scale_log2, neg_ref)) : 0.f;
+                float p1 = (cc * 32 + j + 1 < valid) ? exp2f(fmaf(__uint_as_float(cur[j + 1]), p.scale_log2, neg_ref)) : 0.f;
                 sum += p0 + p1;
-                packed[j >> 1] = pack_bf16x2(p0, p1);
+                packed[j >> 1] = truncate_bf16x2(p0, p1);
               }
             }
             tmem_st16(s_addr + cc * 16, packed);
@@ -677,9 +699,10 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
           // a weight beyond the window has overflowed or lost its meaning: the row cannot be trusted
           saturated = saturated || !(wmax < exp2f(SCORE_WINDOW));
         }
-        tmem_wait_st();
-        l_run += (sum + sum_b) + (sum_c + sum_d);
         laps.lap(1);
+        tmem_wait_st();
+        laps.lap(6);
+        l_run += (sum + sum_b) + (sum_c + sum_d);
         tc_fence_before();
         warp_arrive(&bars[P_READY + wg], lane);
       }
@@ -689,6 +712,7 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
       if (!ok) break;
       tc_fence_after();
       const int qrow = q0 + wg * QT + row;
+      l_run *= HALF_STEP_INV;    // the weights were summed with the half-step factor on them
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
       const uint32_t o_addr = tmem_base + lane_sel + 256 + wg * 128;
       const size_t split_rows = static_cast<size_t>(un.z) * p.Q * p.heads;
@@ -817,7 +841,7 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
     bool ok = true;
     int seq = 0, gp = 0, wgen = 0, jobs = 0;   // wgen: units whose rows this CTA has loaded (resident form)
     Laps laps;
-    laps.start(p.prof + 32, p.prof != nullptr && g == 0 && pidx == 0 && leader);
+    laps.start(p.prof + (pidx == 0 ? 32 : 48), p.prof != nullptr && g == 0 && (pidx == 0 || pidx == PH) && leader);
     for (int u = g; u < p.units && ok; u += p.groups) {
       const Unit un = unit_of(p, u);
       bool first = true;
@@ -931,7 +955,7 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
     bool ok = true;
     int seq = 0, jobs = 0, gp = 0;
     Laps laps;
-    laps.start(p.prof + 24, p.prof != nullptr && g == 0 && pidx == 0 && tid == 0);
+    laps.start(p.prof + (pidx == 0 ? 24 : 40), p.prof != nullptr && g == 0 && (pidx == 0 || pidx == PH) && tid == 0);
     // A job runs in two stages: the codes are expanded (and the MMAs started) right away, its
     // epilogue follows after the NEXT job's expansion, so that the MMAs' tail, the accumulator read
     // and the ring stores of one job hide under the expansion of the following one.
