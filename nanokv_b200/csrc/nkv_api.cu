@@ -133,8 +133,14 @@ int nkv_assign(const void* x, int x_dtype, const void* centers, int centers_dtyp
   return simt_assign(x, x_dtype, centers, centers_dtype, S, J, C, ids, id_bytes, nullptr, s);
 }
 
+// fp32 centres, 32-bit labels, and (for the tensor-core assignment of bf16 rows) the centres' three
+// bf16 planes with their squared norms
+static size_t kmeans_planes_offset(int S, int J, int C) {
+  const size_t head = sizeof(float) * static_cast<size_t>(C) * J + sizeof(int32_t) * static_cast<size_t>(S);
+  return (head + 255) / 256 * 256;
+}
 size_t nkv_kmeans_workspace_bytes(int S, int J, int C) {
-  return sizeof(float) * static_cast<size_t>(C) * J + sizeof(int32_t) * static_cast<size_t>(S) + 256;
+  return kmeans_planes_offset(S, J, C) + tc_assign_f32_workspace_bytes(J, C) + 256;
 }
 
 int nkv_kmeans(const void* x, int x_dtype, int S, int J, int C, int iters,
@@ -154,8 +160,15 @@ int nkv_kmeans(const void* x, int x_dtype, int S, int J, int C, int iters,
   int rc = kmeans_gather_init(x, x_dtype, J, C, init_rows, centers, s);
   if (rc != NKV_OK) return rc;
   NKV_CUDA(cudaMemsetAsync(labels, 0, sizeof(int32_t) * S, s));
+  // bf16 rows: the assignment runs on the tensor cores against the fp32 centres split into bf16
+  // planes (fp32-accurate distances); anything else on the fp32 CUDA-core kernel
+  const bool planes = x_dtype == NKV_BF16 && !simt_forced() && tc_assign_supported(J, C) &&
+                      (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  uint8_t* plane_space = static_cast<uint8_t*>(workspace) + kmeans_planes_offset(S, J, C);
+  plane_space += (256 - (reinterpret_cast<uintptr_t>(plane_space) & 255)) & 255;
   for (int it = 0; it < iters; ++it) {
-    rc = simt_assign(x, x_dtype, centers, NKV_F32, S, J, C, nullptr, id_bytes, labels, s);
+    rc = planes ? tc_assign_f32(x, centers, S, J, C, labels, plane_space, s)
+                : simt_assign(x, x_dtype, centers, NKV_F32, S, J, C, nullptr, id_bytes, labels, s);
     if (rc != NKV_OK) return rc;
     rc = kmeans_update(x, x_dtype, S, J, C, labels, centers, s);
     if (rc != NKV_OK) return rc;

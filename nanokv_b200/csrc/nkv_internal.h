@@ -78,5 +78,8 @@ int tc_project_quant(const void* x_bf16, const void* centers_bf16, const void* i
                      const float* mean, const void* encoder_bf16, int S, int J, int r, float eps,
                      int quant_mode, int scale_dtype, uint8_t* codes, void* scales, cudaStream_t stream);
 bool tc_assign_supported(int J, int C);
+size_t tc_assign_f32_workspace_bytes(int J, int C);
+int tc_assign_f32(const void* x_bf16, const float* centers_f32, int S, int J, int C, int32_t* labels,
+                  void* workspace, cudaStream_t stream);
 
 }  // namespace nkv

@@ -501,20 +501,59 @@ __global__ void gather_init_kernel(const void* x, int x_dtype, int J, const int3
 __global__ void __launch_bounds__(256)
 kmeans_update_kernel(const void* x, int x_dtype, int S, int J, const int32_t* labels,
                      float* centers) {
-  __shared__ int lab[2048];
+  // Block (c, column block): the mean of the rows labelled c, summed in increasing token order (one
+  // fp32 addition per row, the order a sequential scatter-add takes) so that the result does not
+  // depend on the launch shape.  Labels are taken 2,048 at a time: every thread looks at eight of
+  // them, a block-wide exclusive scan turns the match counts into positions, and the matching
+  // tokens land in shared memory in order; the columns are then summed over that short list only,
+  // four loads in flight at a time.
+  __shared__ int list[2048];
+  __shared__ int warp_total[8];
   const int c = blockIdx.x, j = blockIdx.y * 256 + threadIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float sum = 0.f;
   int count = 0;
   for (int s0 = 0; s0 < S; s0 += 2048) {
-    int len = min(2048, S - s0);
+    const int len = min(2048, S - s0);
+    int mine[8], n = 0;
+    const int first = threadIdx.x * 8;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int i = first + k;
+      mine[k] = (i < len && __ldg(labels + s0 + i) == c) ? 1 : 0;
+      n += mine[k];
+    }
+    int scan = n;                                           // inclusive scan inside the warp
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, scan, off);
+      if (lane >= off) scan += v;
+    }
+    __syncthreads();                                        // the previous list has been consumed
+    if (lane == 31) warp_total[warp] = scan;
     __syncthreads();
-    for (int i = threadIdx.x; i < len; i += 256) lab[i] = labels[s0 + i];
+    int base = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      if (w < warp) base += warp_total[w];
+      total += warp_total[w];
+    }
+    int at = base + scan - n;
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (mine[k]) list[at++] = s0 + first + k;
     __syncthreads();
-    for (int i = 0; i < len; ++i) {
-      if (lab[i] == c) {
-        ++count;
-        if (j < J) sum = __fadd_rn(sum, load_float(x, x_dtype, static_cast<size_t>(s0 + i) * J + j));
+    count += total;
+    if (j < J) {
+      int i = 0;
+      for (; i + 4 <= total; i += 4) {
+        const float a = load_float(x, x_dtype, static_cast<size_t>(list[i]) * J + j);
+        const float b = load_float(x, x_dtype, static_cast<size_t>(list[i + 1]) * J + j);
+        const float d = load_float(x, x_dtype, static_cast<size_t>(list[i + 2]) * J + j);
+        const float e = load_float(x, x_dtype, static_cast<size_t>(list[i + 3]) * J + j);
+        sum = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(sum, a), b), d), e);
       }
+      for (; i < total; ++i) sum = __fadd_rn(sum, load_float(x, x_dtype, static_cast<size_t>(list[i]) * J + j));
     }
   }
   if (j < J && count > 0) centers[static_cast<size_t>(c) * J + j] = __fdiv_rn(sum, static_cast<float>(count));

@@ -46,6 +46,9 @@ struct Params {
   const float* mean; uint16_t* coeff;
   // assign
   void* ids_out;
+  int32_t* labels_out;              // optional 32-bit copy of the ids (the C-means update reads it)
+  int a_chunks;                     // 64-column chunks of a token row; K runs over planes * a_chunks chunks
+  const float* cnorm;               // squared norms of the centres when B holds bf16 planes of fp32 centres
   // project + quantise: codes u8 [S, r/2] and scales [S] at the history's token offset
   uint8_t* codes; void* scales; float eps; int in_bf16; int scale_dtype; int column_parts;
 };
@@ -87,7 +90,9 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   const int m0 = blockIdx.x * p.rows;                   // this CTA's tokens: [m0, m_end)
   const int m_end = min(p.S, m0 + p.rows);
   const int n_base = blockIdx.y * p.NACC * p.NB;
-  const int nchunks = p.J / 64;
+  // assign against fp32 centres: B is the centres split into bf16 planes laid side by side along
+  // K, A (the token rows) is walked once per plane
+  const int nchunks = ASSIGN ? p.a_chunks * (p.cnorm != nullptr ? 3 : 1) : p.J / 64;
 
   if (tid == 0) {
     for (int s = 0; s < MAX_STAGES; ++s) {
@@ -124,7 +129,7 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         if (!ok) break;
         uint8_t* stage = smem + s * stage_bytes;
         mbar_arrive_expect_tx(&bars[TMA_FULL + s], p.NACC * b_bytes + (ASSIGN ? A_BYTES : 0));
-        if (ASSIGN) tma_load_2d(stage, &map_a, c * 64, m0, &bars[TMA_FULL + s]);
+        if (ASSIGN) tma_load_2d(stage, &map_a, (c % p.a_chunks) * 64, m0, &bars[TMA_FULL + s]);
         for (int a = 0; a < p.NACC; ++a)
           tma_load_2d(stage + A_BYTES + a * b_bytes, &map_b, c * 64, n_base + a * p.NB,
                       &bars[TMA_FULL + s]);
@@ -176,7 +181,7 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         ok = mbar_wait(&bars[TMA_FULL + s], u & 1, abort_flag, 420 + s);
         if (!ok) break;
         const uint8_t* stage = smem + s * stage_bytes;
-        {
+        if (c < p.a_chunks) {
           const uint4* src = reinterpret_cast<const uint4*>(stage + (tid >> 1) * 128 + (tid & 1) * 64);
 #pragma unroll
           for (int j = 0; j < 4; ++j) xs += sumsq8(src[j]);
@@ -184,7 +189,7 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int item = tid + i * COMPUTE_THREADS;
-          if (item < 2 * C) {
+          if (p.cnorm == nullptr && item < 2 * C) {
             const uint4* src = reinterpret_cast<const uint4*>(stage + A_BYTES + (item >> 1) * 128 + (item & 1) * 64);
 #pragma unroll
             for (int j = 0; j < 4; ++j) cs[i] += sumsq8(src[j]);
@@ -219,7 +224,7 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           for (int j = 0; j < 32; ++j) {
             const int cidx = col + j;
             if (cidx < C) {
-              const float cn = cn_part[2 * cidx] + cn_part[2 * cidx + 1];
+              const float cn = p.cnorm != nullptr ? __ldg(p.cnorm + cidx) : cn_part[2 * cidx] + cn_part[2 * cidx + 1];
               const float dist = __fsub_rn(__fadd_rn(xn, cn), __fmul_rn(2.0f, v[j]));
               if (dist < best) { best = dist; best_i = cidx; }
             }
@@ -235,8 +240,11 @@ encode_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
             if (cand_d[row] < best) { best = cand_d[row]; best_i = cand_i[row]; }
             const int t = m0 + row;
             if (t < m_end) {
-              if (p.id_bytes == 1) static_cast<uint8_t*>(p.ids_out)[t] = static_cast<uint8_t>(best_i);
-              else static_cast<uint16_t*>(p.ids_out)[t] = static_cast<uint16_t>(best_i);
+              if (p.ids_out != nullptr) {
+                if (p.id_bytes == 1) static_cast<uint8_t*>(p.ids_out)[t] = static_cast<uint8_t>(best_i);
+                else static_cast<uint16_t*>(p.ids_out)[t] = static_cast<uint16_t>(best_i);
+              }
+              if (p.labels_out != nullptr) p.labels_out[t] = best_i;
             }
           }
         }
@@ -547,6 +555,7 @@ int tc_assign(const void* x_bf16, const void* centers_bf16, int S, int J, int C,
   p.NACC = C > 256 ? 2 : 1;
   p.NB = C / p.NACC;
   p.ids_out = ids; p.id_bytes = id_bytes;
+  p.a_chunks = J / 64;
   CUtensorMap map_a, map_b;
   {
     uint64_t dims[2] = {static_cast<uint64_t>(J), static_cast<uint64_t>(S)};
@@ -571,6 +580,89 @@ int tc_assign(const void* x_bf16, const void* centers_bf16, int S, int J, int C,
   dim3 grid(ceil_div(S, p.rows), 1);
   kernel<<<grid, THREADS, smem, stream>>>(map_a, map_b, p);
   NKV_LAUNCH_CHECK("encode_gemm_kernel<assign>");
+  return NKV_OK;
+}
+
+namespace {
+
+// fp32 centre rows -> three bf16 planes side by side ([C, 3 J]: c = hi + mid + lo exactly, up to the
+// last bit of the third term) and the rows' squared norms in fp32
+__global__ void __launch_bounds__(256)
+split_centers_kernel(const float* centers, int J, uint16_t* planes, float* cnorm) {
+  __shared__ float part[256];
+  const int c = blockIdx.x;
+  const float* row = centers + static_cast<size_t>(c) * J;
+  uint16_t* out = planes + static_cast<size_t>(c) * 3 * J;
+  float sum = 0.f;
+  for (int j = threadIdx.x; j < J; j += 256) {
+    const float v = row[j];
+    sum = fmaf(v, v, sum);
+    const uint16_t hi = float_to_bf16_bits(v);
+    const float r1 = __fsub_rn(v, bf16_bits_to_float(hi));
+    const uint16_t mid = float_to_bf16_bits(r1);
+    const float r2 = __fsub_rn(r1, bf16_bits_to_float(mid));
+    out[j] = hi;
+    out[J + j] = mid;
+    out[2 * J + j] = float_to_bf16_bits(r2);
+  }
+  part[threadIdx.x] = sum;
+  __syncthreads();
+  for (int width = 128; width >= 1; width >>= 1) {
+    if (threadIdx.x < width) part[threadIdx.x] += part[threadIdx.x + width];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) cnorm[c] = part[0];
+}
+
+}  // namespace
+
+size_t tc_assign_f32_workspace_bytes(int J, int C) {
+  return static_cast<size_t>(C) * 3 * J * 2 + static_cast<size_t>(C) * 4 + 256;
+}
+
+// Nearest centre against fp32 centres on the tensor cores: every bf16 x bf16 product is exact in the
+// fp32 accumulator, and the three planes restore the centres' 24 mantissa bits, so the distances
+// carry fp32 accuracy (the accumulation order is the tensor core's).  Writes 32-bit labels.
+int tc_assign_f32(const void* x_bf16, const float* centers_f32, int S, int J, int C, int32_t* labels,
+                  void* workspace, cudaStream_t stream) {
+  if (S == 0) return NKV_OK;
+  NKV_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, NKV_ERR_INVALID,
+              "assign: plane workspace must be 256-byte aligned");
+  uint16_t* planes = static_cast<uint16_t*>(workspace);
+  float* cnorm = reinterpret_cast<float*>(planes + static_cast<size_t>(C) * 3 * J);
+  split_centers_kernel<<<C, 256, 0, stream>>>(centers_f32, J, planes, cnorm);
+  NKV_LAUNCH_CHECK("split_centers_kernel");
+  Params p{};
+  p.S = S; p.J = J; p.n_total = C;
+  p.NACC = C > 256 ? 2 : 1;
+  p.NB = C / p.NACC;
+  p.labels_out = labels; p.id_bytes = 1;
+  p.a_chunks = J / 64;
+  p.cnorm = cnorm;
+  CUtensorMap map_a, map_b;
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(J), static_cast<uint64_t>(S)};
+    uint64_t strides[1] = {static_cast<uint64_t>(J) * 2};
+    uint32_t box[2] = {64, TM};
+    int rc = encode_tensor_map(&map_a, 2, x_bf16, 2, dims, strides, box, 128);
+    if (rc != NKV_OK) return rc;
+  }
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(J) * 3, static_cast<uint64_t>(C)};
+    uint64_t strides[1] = {static_cast<uint64_t>(J) * 3 * 2};
+    uint32_t box[2] = {64, static_cast<uint32_t>(p.NB)};
+    int rc = encode_tensor_map(&map_b, 2, planes, 2, dims, strides, box, 128);
+    if (rc != NKV_OK) return rc;
+  }
+  p.nstages = pick_stages(p.NACC, p.NB, C);
+  size_t smem = smem_bytes(p.NACC, p.NB, C, p.nstages);
+  auto kernel = encode_gemm_kernel<ASSIGN_IDS>;
+  NKV_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                static_cast<int>(smem)));
+  p.rows = pick_rows(S, 1);
+  dim3 grid(ceil_div(S, p.rows), 1);
+  kernel<<<grid, THREADS, smem, stream>>>(map_a, map_b, p);
+  NKV_LAUNCH_CHECK("encode_gemm_kernel<assign, fp32 centres>");
   return NKV_OK;
 }
 

@@ -142,6 +142,34 @@ def test_assign_ties_take_the_lowest_index():
     assert got.cpu().tolist() == [3] * 70
 
 
+@pytest.mark.parametrize("S,J,C,spread", [(3000, 1024, 64, 0.3), (4100, 512, 256, 0.3), (1560, 1024, 256, 1.0),
+                                          (2500, 768, 512, 0.5)])
+def test_kmeans_tensor_core_assignment_matches_oracle(S, J, C, spread):
+    """bf16 rows with 16 | C: the assignment inside the online C-means runs on the tensor cores
+    against the fp32 centres split into three bf16 planes.  Ids must equal the fp32 CPU oracle's
+    (sequential-order means included), also when clusters overlap (spread 1.0) and for C > 256."""
+    gen = synthetic.generator(S + C)
+    true_centers = torch.randn(C, J, generator=gen)
+    pick = torch.randint(C, (S,), generator=gen)
+    rows = (true_centers[pick] + spread * torch.randn(S, J, generator=gen)).to(torch.bfloat16)
+    seed = 424242 + C
+    want_centers, want_labels = oracle.kmeans(rows[None].float(), C, 2, seed)
+    init = codec.kmeans_init_rows(S, C, seed)
+    got_centers, got_ids = ops.kmeans(rows.cuda(), C, 2, init.cuda())
+    assert torch.equal(got_ids.cpu().long(), want_labels[0])
+    got = got_centers.cpu().float()
+    want = want_centers[0].to(torch.bfloat16).float()
+    assert (got - want).abs().max() <= 2.0 ** -7 * want.abs().max()
+    assert (got != want).float().mean() < 0.02
+    # and the CUDA-core path (forced) gives the same ids: the two assignments agree
+    ops.force_simt(True)
+    try:
+        _, simt_ids = ops.kmeans(rows.cuda(), C, 2, init.cuda())
+    finally:
+        ops.force_simt(False)
+    assert torch.equal(simt_ids, got_ids)
+
+
 @pytest.mark.parametrize("case", [cases.MINI_F32, cases.MINI_BF16, cases.C1], ids=lambda c: c.name)
 def test_kmeans_matches_oracle(case):
     data = cases.build(case)
