@@ -5,12 +5,14 @@ as the reference module MGM/nanokv_codec.py (encode_tensor :334-365,
 decode_tensor :369-390, decode_value :516-539, concat_values :600-609,
 value_shape :489-513, payload_bytes :697-704), so its call sites in the
 backbone (MGM/wan_video_dit.py:493-500,710-795) can import this module
-instead.  Operators are registered explicitly (`register_operator`) rather
-than read from checkpoint directories.
+instead.  Operators come from `register_operator`, or -- when nothing is
+registered for a (kind, layer) -- from the reference's artefact files named by
+its environment variables (`_from_artifacts`).
 """
 from __future__ import annotations
 
 import os
+from pathlib import Path
 from typing import Any
 
 import torch
@@ -36,12 +38,79 @@ def register_operator(kind: str, layer: int, *, mean, encoder, decoder, device="
     return op
 
 
+def _pack_int8(weight: torch.Tensor) -> dict:
+    """The reference's INT8 operator packing (per row, or per MG35_KVCODEC_INT8_WEIGHT_GROUP_SIZE
+    input columns): symmetric, scale = amax / 127 kept in bf16 (MGM/nanokv_codec.py:108-131)."""
+    weight = weight.detach().float().cpu().contiguous()
+    group = int(os.environ.get("MG35_KVCODEC_INT8_WEIGHT_GROUP_SIZE", "0") or 0) or int(weight.shape[1])
+    if group > weight.shape[1] or weight.shape[1] % group:
+        raise ValueError(f"INT8 group size {group} must divide {weight.shape[1]}")
+    grouped = weight.reshape(weight.shape[0], -1, group)
+    scale = grouped.abs().amax(dim=2).clamp_min(1e-12) / 127.0
+    quantised = (grouped / scale[:, :, None]).round().clamp(-127, 127).to(torch.int8)
+    return {"qweight": quantised.reshape_as(weight), "scale": scale.to(torch.bfloat16), "group_size": group}
+
+
+def _from_artifacts(kind: str, layer: int, device) -> Operator | None:
+    """Operator of (kind, layer) from the reference's artefact files, as its `_operator` reads them
+    (MGM/nanokv_codec.py:151-249): the prepacked INT8 file named by
+    MG35_KVCODEC_PREPACKED_OPERATOR_PATH, else the K basis under MG35_KVCODEC_BASIS_DIR/k_c64 with an
+    optional trained decoder under MG35_KVCODEC_DECODER_DIR_K, resp. the V-QAT checkpoint under
+    MG35_KVCODEC_DECODER_DIR_V; stored per MG35_KVCODEC_OPERATOR_WEIGHT_MODE (int8 | bf16 | fp32).
+    None when no such variable is set.  Provenance bookkeeping (centre storage mode, directory
+    hashes) stays with the caller."""
+    prepacked = os.environ.get("MG35_KVCODEC_PREPACKED_OPERATOR_PATH", "").strip()
+    if prepacked:
+        packed = torch.load(prepacked, map_location="cpu", weights_only=True)
+        if packed.get("format") != "mg35_worldplay_operator_int8_v1":
+            raise RuntimeError(f"bad prepacked WorldPlay operator: {prepacked}")
+        entry = packed["entries"][f"{kind}:{int(layer):02d}"]
+        return Operator.from_int8(entry["mean"].float(), entry["encoder"], entry["decoder"], device=device)
+    if kind == "k":
+        root = os.environ.get("MG35_KVCODEC_BASIS_DIR", "").strip()
+        if not root:
+            return None
+        basis = torch.load(Path(root) / "k_c64" / f"layer_{int(layer):02d}.pt", map_location="cpu",
+                           weights_only=True)
+        mean, encoder = basis["mean"].float(), basis["components"].float()
+        decoder = encoder.t().contiguous()
+        trained = os.environ.get("MG35_KVCODEC_DECODER_DIR_K", "").strip()
+        if trained:
+            checkpoint = torch.load(Path(trained) / f"layer_{int(layer):02d}.pt", map_location="cpu",
+                                    weights_only=True)
+            if checkpoint.get("target") != "k_c64":
+                raise RuntimeError(f"bad WorldPlay K decoder L{layer}: {trained}")
+            decoder = checkpoint["decoder"].float()
+    else:
+        root = os.environ.get("MG35_KVCODEC_DECODER_DIR_V", "").strip()
+        if not root:
+            return None
+        checkpoint = torch.load(Path(root) / f"layer_{int(layer):02d}.pt", map_location="cpu", weights_only=True)
+        if checkpoint.get("format") != "mg35_worldplay_v_c64_int4_qat_v1":
+            raise RuntimeError(f"bad WorldPlay V-QAT checkpoint L{layer}: {root}")
+        mean, encoder, decoder = (checkpoint[name].float() for name in ("mean", "encoder", "decoder"))
+    mode = os.environ.get("MG35_KVCODEC_OPERATOR_WEIGHT_MODE", "int8").strip().lower()
+    if mode == "fp32":
+        return Operator(mean, encoder, decoder, device=device)
+    if mode == "bf16":
+        return Operator(mean, encoder.to(torch.bfloat16), decoder.to(torch.bfloat16), device=device)
+    if mode != "int8":
+        raise ValueError(f"unsupported MG35 operator mode={mode}")
+    return Operator.from_int8(mean, _pack_int8(encoder), _pack_int8(decoder), device=device)
+
+
 def _operator(kind: str, layer: int, device) -> Operator:
     device = torch.device(device)
     for key in ((kind, int(layer), str(device)), (kind, int(layer), device.type)):
         if key in _OPERATORS:
             return _OPERATORS[key]
-    raise KeyError(f"no operator registered for {kind}:{int(layer):02d} on {device}")
+    loaded = _from_artifacts(kind, layer, device)
+    if loaded is None:
+        raise KeyError(f"no operator registered for {kind}:{int(layer):02d} on {device} and none of "
+                       "MG35_KVCODEC_PREPACKED_OPERATOR_PATH / MG35_KVCODEC_BASIS_DIR / "
+                       "MG35_KVCODEC_DECODER_DIR_V names its artefacts")
+    _OPERATORS[(kind, int(layer), str(device))] = loaded
+    return loaded
 
 
 def _clusters() -> int:

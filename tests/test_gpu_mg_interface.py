@@ -147,3 +147,57 @@ def test_selected_decode_and_direct_rows_follow_the_token_mask():
     assert [item["length"] for item in everything] == list(case.segments)
     with pytest.raises(ValueError):
         mg_codec.direct_latent_pair_segments(containers["k"], containers["v"], device="cuda", token_keep=keep[:-1])
+
+
+@pytest.mark.parametrize("mode", ["bf16", "int8", "fp32"])
+def test_operators_load_from_the_reference_artefact_layout(tmp_path, monkeypatch, mode):
+    """With nothing registered for a layer the module reads the reference's artefact files (K basis
+    directory, V-QAT checkpoint directory, weight mode variable), as the backbone's environment names
+    them; the result equals registering the same weights by hand."""
+    case = cases.MINI_BF16
+    data = cases.build(case)
+    layer = 31                                   # a layer nothing else registers
+    k_op, v_op = data["k_op"], data["v_op"]
+    basis = tmp_path / "basis" / "k_c64"
+    basis.mkdir(parents=True)
+    torch.save({"mean": k_op["mean"].float(), "components": k_op["encoder"].float()}, basis / f"layer_{layer:02d}.pt")
+    vdir = tmp_path / "vqat"
+    vdir.mkdir()
+    torch.save({"format": "mg35_worldplay_v_c64_int4_qat_v1", "mean": v_op["mean"].float(),
+                "encoder": v_op["encoder"].float(), "decoder": v_op["decoder"].float()}, vdir / f"layer_{layer:02d}.pt")
+    monkeypatch.setenv("MG35_KVCODEC_BASIS_DIR", str(tmp_path / "basis"))
+    monkeypatch.setenv("MG35_KVCODEC_DECODER_DIR_V", str(vdir))
+    monkeypatch.delenv("MG35_KVCODEC_DECODER_DIR_K", raising=False)
+    monkeypatch.delenv("MG35_KVCODEC_PREPACKED_OPERATOR_PATH", raising=False)
+    monkeypatch.setenv("MG35_KVCODEC_OPERATOR_WEIGHT_MODE", mode)
+    monkeypatch.setenv("MG35_KVCODEC_C64_CLUSTERS", str(case.shape.centers))
+    monkeypatch.setenv("MG35_KVCODEC_C64_ITERS", str(case.iters))
+    for key in [k for k in mg_codec._OPERATORS if k[1] in (layer, layer + 1)]:
+        del mg_codec._OPERATORS[key]
+    rows = data["k_chunks"][0][None].cuda()
+    rows = rows.float() if mode == "fp32" else rows
+    loaded = {kind: mg_codec.encode_tensor(kind, layer, rows) for kind in ("k", "v")}
+    # the same weights handed over explicitly (K decoder = encoder transposed, as the basis file implies)
+    cast = (lambda w: w.float()) if mode == "fp32" else (lambda w: w.float().to(torch.bfloat16))
+    if mode == "int8":
+        from nanokv_b200.codec import Operator
+        for kind, op, decoder in (("k", k_op, k_op["encoder"].float().t().contiguous()), ("v", v_op, v_op["decoder"].float())):
+            mg_codec._OPERATORS[(kind, layer + 1, "cuda")] = Operator.from_int8(
+                op["mean"].float(), mg_codec._pack_int8(op["encoder"].float()), mg_codec._pack_int8(decoder))
+    else:
+        mg_codec.register_operator("k", layer + 1, mean=k_op["mean"], encoder=cast(k_op["encoder"]),
+                                   decoder=cast(k_op["encoder"].float().t().contiguous()))
+        mg_codec.register_operator("v", layer + 1, mean=v_op["mean"], encoder=cast(v_op["encoder"]),
+                                   decoder=cast(v_op["decoder"]))
+    for kind in ("k", "v"):
+        by_hand = mg_codec.encode_tensor(kind, layer + 1, rows)
+        # the seed of the online C-means depends on the layer: compare through a decode of the same payload
+        dtype = torch.float32 if mode == "fp32" else torch.bfloat16
+        a = mg_codec.decode_tensor(loaded[kind], dtype=dtype, device="cuda")
+        redo = dict(loaded[kind], layer=layer + 1)
+        b = mg_codec.decode_tensor(redo, dtype=dtype, device="cuda")
+        assert torch.equal(a, b)
+        assert by_hand["packed_codes"].shape == loaded[kind]["packed_codes"].shape
+    monkeypatch.delenv("MG35_KVCODEC_BASIS_DIR")
+    with pytest.raises(KeyError):
+        mg_codec.encode_tensor("k", 77, rows)

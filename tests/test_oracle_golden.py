@@ -218,3 +218,15 @@ def test_camera_selected():
     assert int(gold["value_digest"][0]) == checksum(data["value"]), "input generator drifted"
     got = oracle.camera_selected(data["value"], data["matrix"], data["indices"])
     assert torch.equal(got.view(torch.int16), from_bits(gold["transformed"], torch.bfloat16).view(torch.int16))
+
+
+@pytest.mark.parametrize("name,group", [("per_row", 0), ("group64", 64)])
+def test_mg_operator_int8_packing_matches_the_reference(name, group, monkeypatch):
+    """mg_codec._pack_int8 (what an operator read from the reference's artefact files is stored as in
+    its default weight mode) against the bits the reference's own packer produced."""
+    from nanokv_b200 import mg_codec
+    gold = load("int8_operator")
+    monkeypatch.setenv("MG35_KVCODEC_INT8_WEIGHT_GROUP_SIZE", str(group))
+    packed = mg_codec._pack_int8(cases.build_int8_weight())
+    assert np.array_equal(packed["qweight"].numpy(), gold[f"{name}_qweight"])
+    assert np.array_equal(packed["scale"].view(torch.int16).numpy(), gold[f"{name}_scale"])
