@@ -61,10 +61,10 @@ constexpr int MAX_RING = 56;      // ring slots per group (GF - GF_DONE flag wor
 constexpr int NMETA = 4;          // metadata buffers of a producer (it prepares up to four jobs ahead)
 constexpr float RESCALE_THRESHOLD = 8.0f;
 constexpr float SCORE_WINDOW = 96.0f;   // log2 units a score may exceed the row's reference point by
-constexpr int STATUS_SCORE_RANGE = 950;
+constexpr int STATUS_SCORE_RANGE = 950;  // status word: a row's scores left that window (its LSE is NaN)
 // log2(1 + 2^-9) and 1 / (1 + 2^-9): half a bf16 step above a value, as an exponent offset and back
 constexpr float HALF_STEP_LOG2 = 0.0028150156070540f;
-constexpr float HALF_STEP_INV = 0.998050682261209f; // status word: a row's scores left that window (its LSE is NaN)
+constexpr float HALF_STEP_INV = 0.998050682261209f;
 
 enum Bar {
   // consumer
