@@ -149,6 +149,7 @@ class ReaderGroup:
         self.k_read_tc = ops.prepare_decoder(self.k_read) if self.prepared else None
         self.v_read_tc = ops.prepare_decoder(self.v_read) if self.prepared else None
         self._tables: dict = {}
+        self._biases: dict = {}
         # native pair retained by every pair of the (padded) low-width row, for the selected RoPE
         # (LB/codec_native_attention.py:111, :271-272: indices keep native complex pairs together)
         self.pair_index = None
@@ -183,9 +184,15 @@ class ReaderGroup:
 
     def bias(self, mean: torch.Tensor, target: str) -> torch.Tensor:
         """(mean_h @ affine) in the working dtype, as float [h, pad] (MGC/core.py:179-180)."""
+        key = (id(mean), mean._version, target)
+        cached = self._biases.get(target)
+        if cached is not None and cached[0] == key:
+            return cached[1]
         affine = self.k_affine if target == "k" else self.v_affine
         mean_heads = mean.reshape(-1, self.native_dim).index_select(0, self.heads).to(self.dtype)
-        return self._pad_last(torch.einsum("hd,hde->he", mean_heads, affine).float())
+        value = self._pad_last(torch.einsum("hd,hde->he", mean_heads, affine).float())
+        self._biases[target] = (key, value, mean)     # the mean is kept so that its id cannot be reused
+        return value
 
     def projected_centers(self, hist: CompressedHistory, target: str) -> HistoryView:
         """History view whose centre table is projected to this group's heads and width

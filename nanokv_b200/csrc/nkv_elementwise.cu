@@ -870,32 +870,56 @@ template <int DTYPE>
 __global__ void __launch_bounds__(256)
 head_linear_kernel(const void* x, long long stride_row, long long stride_head, const int32_t* heads,
                    const void* w, long long rows, int din, int dout, int dout_pad, void* out) {
+  // Block = 64 rows of one head.  The head's map and the 64 input rows sit in shared memory as
+  // fp32; thread (ty, tx) owns rows 4 ty .. 4 ty + 3 and the output columns tx, tx + 16, ...: every
+  // value read from shared memory feeds four (a map entry) or dout / 16 (an input) multiply-adds.
+  // Each output is one fp32 chain over the input columns in increasing order.
   extern __shared__ float head_linear_smem[];
+  constexpr int ROWS = 64, MAXC = 8;            // up to 128 output columns
   float* ws = head_linear_smem;                 // [din][dout]
-  float* xs = head_linear_smem + din * dout;    // [32][din + 1]
+  float* xs = head_linear_smem + din * dout;    // [din][ROWS + 4]: a column of inputs is contiguous
   const int g = blockIdx.y;
   const int head = heads ? heads[g] : g;
-  const long long row0 = static_cast<long long>(blockIdx.x) * 32;
+  const long long row0 = static_cast<long long>(blockIdx.x) * ROWS;
   for (int i = threadIdx.x; i < din * dout; i += 256)
     ws[i] = load_float(w, DTYPE, static_cast<size_t>(g) * din * dout + i);
-  for (int i = threadIdx.x; i < 32 * din; i += 256) {
+  for (int i = threadIdx.x; i < ROWS * din; i += 256) {
     const int r = i / din, d = i - r * din;
     const long long row = row0 + r;
-    xs[r * (din + 1) + d] = row < rows
+    xs[d * (ROWS + 4) + r] = row < rows
         ? load_float(x, DTYPE, static_cast<size_t>(row * stride_row + head * stride_head + d)) : 0.f;
   }
   __syncthreads();
-  const int r = threadIdx.x >> 3, c0 = threadIdx.x & 7;
-  const long long row = row0 + r;
-  if (row >= rows) return;
-  const size_t base = (static_cast<size_t>(row) * gridDim.y + g) * dout_pad;
-  for (int e = c0; e < dout_pad; e += 8) {
-    float acc = 0.f;
-    if (e < dout) {
-      const float* xr = xs + r * (din + 1);
-      for (int d = 0; d < din; ++d) acc = fmaf(xr[d], ws[d * dout + e], acc);
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+  const int ncol = (dout + 15) / 16;            // columns tx + 16 k, k < ncol (guarded below)
+  float acc[4][MAXC];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int k = 0; k < MAXC; ++k) acc[a][k] = 0.f;
+  for (int d = 0; d < din; ++d) {
+    const float4 xv = *reinterpret_cast<const float4*>(xs + d * (ROWS + 4) + 4 * ty);
+    const float xr[4] = {xv.x, xv.y, xv.z, xv.w};
+    const float* wr = ws + d * dout + tx;
+#pragma unroll
+    for (int k = 0; k < MAXC; ++k) {
+      if (k < ncol) {
+        const float wv = (tx + 16 * k < dout) ? wr[16 * k] : 0.f;
+#pragma unroll
+        for (int a = 0; a < 4; ++a) acc[a][k] = fmaf(xr[a], wv, acc[a][k]);
+      }
     }
-    store_float(out, DTYPE, base + e, acc);
+  }
+#pragma unroll
+  for (int a = 0; a < 4; ++a) {
+    const long long row = row0 + 4 * ty + a;
+    if (row >= rows) continue;
+    const size_t base = (static_cast<size_t>(row) * gridDim.y + g) * dout_pad;
+#pragma unroll
+    for (int k = 0; k < MAXC; ++k) {
+      const int e = tx + 16 * k;
+      if (e < dout_pad) store_float(out, DTYPE, base + e, (k < ncol && e < dout) ? acc[a][k] : 0.f);
+    }
   }
 }
 
@@ -905,11 +929,11 @@ int head_linear(const void* x, int dtype, int64_t stride_row, int64_t stride_hea
   NKV_REQUIRE(dtype == NKV_BF16 || dtype == NKV_F32, NKV_ERR_UNSUPPORTED, "head_linear: dtype %d", dtype);
   NKV_REQUIRE(group_heads > 0 && din > 0 && dout > 0 && dout_pad >= dout, NKV_ERR_INVALID,
               "head_linear: heads=%d din=%d dout=%d pad=%d", group_heads, din, dout, dout_pad);
-  const size_t smem = (static_cast<size_t>(din) * dout + 32 * (din + 1)) * sizeof(float);
-  NKV_REQUIRE(smem <= 200 * 1024, NKV_ERR_UNSUPPORTED, "head_linear: a %d x %d map does not fit shared memory",
-              din, dout);
+  const size_t smem = (static_cast<size_t>(din) * dout + static_cast<size_t>(din) * 68) * sizeof(float);
+  NKV_REQUIRE(smem <= 200 * 1024 && dout_pad <= 128 && (din * dout) % 4 == 0, NKV_ERR_UNSUPPORTED,
+              "head_linear: a %d x %d map (padded to %d) is beyond the built kernel", din, dout, dout_pad);
   if (rows == 0) return NKV_OK;
-  dim3 grid(static_cast<unsigned>((rows + 31) / 32), static_cast<unsigned>(group_heads));
+  dim3 grid(static_cast<unsigned>((rows + 63) / 64), static_cast<unsigned>(group_heads));
   if (dtype == NKV_F32) {
     NKV_CUDA(cudaFuncSetAttribute(head_linear_kernel<NKV_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   static_cast<int>(smem)));
