@@ -92,7 +92,7 @@ struct Params {
   int Q, heads, N, rank, nchunks, npairs, ngroups, group;
   int scale_dtype, nw, w_perm;
   int tiles, tiles_per_split, splits, qchunks;
-  int groups, cons, prod, ring, units;
+  int groups, cons, prod, prod_k, ring, units;   // prod producers per group, the first prod_k of them rebuild K tiles
   float scale_log2;
   long long wait_budget;
   nkv_history hk, hv;
@@ -387,7 +387,7 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
       int seq = 0, cseq = 0, ucount = 0;
       int pend_slot = -1, pend_stage = 0, pend_phase = 0;
       int pub[MAX_PROD] = {0, 0, 0, 0, 0, 0, 0, 0};   // cached copy of the producers' counters
-      const int PH = p.prod / 2;
+      const int PK = p.prod_k, PV = p.prod - p.prod_k;
       Laps laps;
       laps.start(p.prof, p.prof != nullptr && g == 0 && c == 0);
       for (int u = g; u < p.units && ok; u += p.groups) {
@@ -409,11 +409,12 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
           const int stage = cseq % KVS, use = cseq / KVS;
           const int row = (g * R + slot) * TOK;
           laps.lap(7);
-          // tile `seq` of K comes from producer seq % PH as its job number seq / PH, V from
-          // producer PH + seq % PH; the counters are re-read only when the cached copy falls short
+          // tile `seq` of K comes from K producer seq % PK as its job number seq / PK, V likewise from
+          // V producer PK + seq % PV; the counters are re-read only when the cached copy falls short
           {
-            const int who = seq % PH, need = seq / PH + 1;
-            if (pub[who] < need || pub[PH + who] < need) {
+            const int who = seq % PK, need = seq / PK + 1;
+            const int who_v = PK + seq % PV, need_v = seq / PV + 1;
+            if (pub[who] < need || pub[who_v] < need_v) {
               const long long start = clock64();
               unsigned spins = 0;
               while (true) {
@@ -423,7 +424,7 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
                   const int4 hi = ld_acquire_v4(gflags + 4);
                   pub[4] = hi.x; pub[5] = hi.y; pub[6] = hi.z; pub[7] = hi.w;
                 }
-                if (pub[who] >= need && pub[PH + who] >= need) break;
+                if (pub[who] >= need && pub[who_v] >= need_v) break;
                 if (*ctx.abort_flag) { ok = false; break; }
                 if ((++spins & 31u) == 0 && wait_expired(ctx, start, 102)) { ok = false; break; }
                 __nanosleep(40);
@@ -767,9 +768,10 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
                                               const Params& p, const Ctx& ctx, int g, int pidx) {
   using L = Layout<D>;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int R = p.ring, PH = p.prod / 2;
-  const int tensor = pidx / PH;            // 0: this CTA rebuilds K tiles, 1: V tiles
-  const int mine = pidx % PH;              // it takes the tiles with seq % PH == mine
+  const int R = p.ring;
+  const int tensor = pidx < p.prod_k ? 0 : 1;                   // 0: this CTA rebuilds K tiles, 1: V tiles
+  const int PH = tensor ? p.prod - p.prod_k : p.prod_k;         // producers of its kind
+  const int mine = tensor ? pidx - p.prod_k : pidx;             // it takes the tiles with seq % PH == mine
   const nkv_history& hist = tensor ? p.hv : p.hk;
   const int nchunks = p.nchunks, npairs = p.npairs, ng = p.ngroups, nw = p.nw;
   const bool resident = npairs <= nw;      // the head's decoder rows stay in shared memory for a whole unit
@@ -841,7 +843,7 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
     bool ok = true;
     int seq = 0, gp = 0, wgen = 0, jobs = 0;   // wgen: units whose rows this CTA has loaded (resident form)
     Laps laps;
-    laps.start(p.prof + (pidx == 0 ? 32 : 48), p.prof != nullptr && g == 0 && (pidx == 0 || pidx == PH) && leader);
+    laps.start(p.prof + (pidx == 0 ? 32 : 48), p.prof != nullptr && g == 0 && (pidx == 0 || pidx == p.prod_k) && leader);
     for (int u = g; u < p.units && ok; u += p.groups) {
       const Unit un = unit_of(p, u);
       bool first = true;
@@ -955,7 +957,7 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
     bool ok = true;
     int seq = 0, jobs = 0, gp = 0;
     Laps laps;
-    laps.start(p.prof + (pidx == 0 ? 24 : 40), p.prof != nullptr && g == 0 && (pidx == 0 || pidx == PH) && tid == 0);
+    laps.start(p.prof + (pidx == 0 ? 24 : 40), p.prof != nullptr && g == 0 && (pidx == 0 || pidx == p.prod_k) && tid == 0);
     // A job runs in two stages: the codes are expanded (and the MMAs started) right away, its
     // epilogue follows after the NEXT job's expansion, so that the MMAs' tail, the accumulator read
     // and the ring stores of one job hide under the expansion of the following one.
@@ -1323,7 +1325,7 @@ attn_codec_kernel(const __grid_constant__ CUtensorMap map_q,
       consumer_role<D>(smem, bars, tmem_base, &map_q, &map_rk, &map_rv, p, ctx, g, role);
     } else {
       const int pidx = role - p.cons;
-      const bool value = pidx >= p.prod / 2;
+      const bool value = pidx >= p.prod_k;
       producer_role<D, ROPE, CAM>(smem, bars, tmem_base, value ? &map_wv : &map_wk,
                                   value ? &map_cv : &map_ck, p, ctx, g, pidx);
     }
@@ -1458,17 +1460,31 @@ int launch_for(int dk, bool rope, bool cam, const CUtensorMap maps[7], Params& p
 }
 
 // Work decomposition of one launch: consumers and producers per group, groups, history splits.
-struct Plan { int cons, prod, groups, qchunks, splits, tiles_per_split, ring; };
+struct Plan { int cons, prod, prod_k, groups, qchunks, splits, tiles_per_split, ring; };
 
 Plan make_plan(int sms, int Q, int heads, int tiles, int rank, int dk, int max_splits) {
   Plan plan{};
   // a producer needs roughly rank-proportional time per tile; one pair of producers (K, V) per
-  // tensor keeps up with the consumers at small ranks, two pairs at the codec's ranks
-  int prod = rank >= 256 ? 4 : 2;
-  prod = tuning("NKV_ATTN_PROD", prod);
-  if (prod < 2) prod = 2;
-  if (prod > MAX_PROD) prod = MAX_PROD;
-  prod &= ~1;
+  // tensor keeps up with the consumers at small ranks, two pairs at the codec's ranks.
+  int prod_k = rank >= 256 ? 2 : 1, prod_v = prod_k;
+  const int qblocks_all = ceil_div(Q, NQ * QT);
+  {
+    // Producers beyond that are free as long as the SMs still hold the same number of groups: at the
+    // codec's ranks the producers set the pace, so the spare SMs of a group's row go to them, K first
+    // (a rotated K tile costs its producer nearly twice a V tile).
+    const int cons_all = qblocks_all < sms - 2 ? qblocks_all : sms - 2;
+    const int groups_now = sms / (cons_all + prod_k + prod_v);
+    while (rank >= 256 && groups_now > 0 && prod_k + prod_v < MAX_PROD &&
+           sms / (cons_all + prod_k + prod_v + 1) == groups_now) {
+      if (prod_k <= prod_v) ++prod_k; else ++prod_v;
+    }
+  }
+  prod_k = tuning("NKV_ATTN_PROD_K", prod_k);
+  prod_v = tuning("NKV_ATTN_PROD_V", prod_v);
+  if (prod_k < 1) prod_k = 1;
+  if (prod_v < 1) prod_v = 1;
+  while (prod_k + prod_v > MAX_PROD) { if (prod_k > prod_v) --prod_k; else --prod_v; }
+  const int prod = prod_k + prod_v, prod_max = prod_k > prod_v ? prod_k : prod_v;
   const int qblocks = ceil_div(Q, NQ * QT);
   int cons = qblocks < sms - prod ? qblocks : sms - prod;
   const int qchunks = ceil_div(qblocks, cons);
@@ -1476,8 +1492,8 @@ Plan make_plan(int sms, int Q, int heads, int tiles, int rank, int dk, int max_s
   const int ring_slots = static_cast<int>(RING_BYTES / (2u * TOK * dk * 2u));
   // A producer prepares its jobs up to NMETA ahead and checks the ring slot of a job at that
   // point, with up to NMETA - 1 of its own earlier tiles not yet published; the slot's previous
-  // tile must be older than those, which takes more than (NMETA - 1) * prod / 2 slots.
-  const int min_ring = (NMETA - 1) * (prod / 2) + 1 > 4 ? (NMETA - 1) * (prod / 2) + 1 : 4;
+  // tile must be older than those, which takes more than (NMETA - 1) * (producers of a kind) slots.
+  const int min_ring = (NMETA - 1) * prod_max + 1 > 4 ? (NMETA - 1) * prod_max + 1 : 4;
   int wmax = sms / (cons + prod);
   if (wmax > ring_slots / min_ring) wmax = ring_slots / min_ring;
   if (wmax < 1) wmax = 1;
@@ -1502,6 +1518,7 @@ Plan make_plan(int sms, int Q, int heads, int tiles, int rank, int dk, int max_s
   }
   plan.cons = cons;
   plan.prod = prod;
+  plan.prod_k = prod_k;
   plan.qchunks = qchunks;
   int ring = ring_slots / plan.groups;
   plan.ring = ring > MAX_RING ? MAX_RING : ring;
@@ -1657,7 +1674,7 @@ int tc_attn_codec(const void* q, int64_t q_stride_token, int64_t q_stride_head, 
   p.tiles_per_split = plan.tiles_per_split;
   p.splits = plan.splits;
   p.qchunks = plan.qchunks;
-  p.groups = plan.groups; p.cons = plan.cons; p.prod = plan.prod; p.ring = plan.ring;
+  p.groups = plan.groups; p.cons = plan.cons; p.prod = plan.prod; p.prod_k = plan.prod_k; p.ring = plan.ring;
   p.units = plan.qchunks * heads * plan.splits;
   p.wait_budget = 1ll << 31;   // about a second of SM cycles per wait
 #ifdef NKV_DEV
