@@ -647,47 +647,54 @@ __device__ __forceinline__ void consumer_role(uint8_t* smem, uint64_t* bars, uin
         const float neg_ref = HALF_STEP_LOG2 - m_used;
         float sum = 0.f, sum_b = 0.f, sum_c = 0.f, sum_d = 0.f;   // four chains instead of one
         uint32_t pmax_a = 0u, pmax_b = 0u;
-        {
+        if (valid == TOK) {
+          // The whole row at once: four 32-column loads, ONE wait, and then a single run of
+          // instructions without a fence in it, so that the exponential unit's work of one quarter
+          // overlaps the arithmetic and the packing of its neighbours (a wait per quarter kept every
+          // quarter a closed block: arguments, exponentials, sums, each draining before the next).
+          uint32_t raw[4][32];
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) tmem_ld32_issue(s_addr + cc * 32, raw[cc]);
+          tmem_ld128_wait(raw[0], raw[1], raw[2], raw[3]);
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t (&cur)[32] = raw[cc];
+            uint32_t packed[16];
+            float w[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) w[j] = fmaf(__uint_as_float(cur[j]), p.scale_log2, neg_ref);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) w[j] = exp2_approx(w[j]);
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              sum += w[j]; sum_b += w[j + 1]; sum_c += w[j + 2]; sum_d += w[j + 3];
+              packed[j >> 1] = truncate_bf16x2(w[j], w[j + 1]);
+              packed[(j >> 1) + 1] = truncate_bf16x2(w[j + 2], w[j + 3]);
+            }
+            // the largest weight of the quarter, on the packed pairs (weights are positive, so the
+            // bf16 bit patterns order like the numbers): half an instruction per score
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) {
+              pmax_a = bf16x2_max(pmax_a, packed[j]);
+              pmax_b = bf16x2_max(pmax_b, packed[j + 1]);
+            }
+            tmem_st16(s_addr + cc * 16, packed);
+          }
+        } else {
           uint32_t raw[2][32];
           tmem_ld32_issue(s_addr, raw[0]);
 #pragma unroll
           for (int cc = 0; cc < TOK / 32; ++cc) {
             uint32_t (&cur)[32] = raw[cc & 1];
-            laps.lap(1);
             tmem_ld32_wait(cur);
-            laps.lap(cc == 0 ? 4 : 5);
             if (cc + 1 < TOK / 32) tmem_ld32_issue(s_addr + (cc + 1) * 32, raw[(cc + 1) & 1]);
             uint32_t packed[16];
-            if (valid == TOK) {
-              // three passes over the chunk, each a run of independent instructions: exponent
-              // arguments, exponentials (back to back, so the unit never waits for a consumer of an
-              // earlier result), then sums and packing
-              float w[32];
 #pragma unroll
-              for (int j = 0; j < 32; ++j) w[j] = fmaf(__uint_as_float(cur[j]), p.scale_log2, neg_ref);
-#pragma unroll
-              for (int j = 0; j < 32; ++j) w[j] = exp2_approx(w[j]);
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                sum += w[j]; sum_b += w[j + 1]; sum_c += w[j + 2]; sum_d += w[j + 3];
-                packed[j >> 1] = truncate_bf16x2(w[j], w[j + 1]);
-                packed[(j >> 1) + 1] = truncate_bf16x2(w[j + 2], w[j + 3]);
-              }
-              // the largest weight of the chunk, on the packed pairs (weights are positive, so the
-              // bf16 bit patterns order like the numbers): half an instruction per score
-#pragma unroll
-              for (int j = 0; j < 16; j += 2) {
-                pmax_a = bf16x2_max(pmax_a, packed[j]);
-                pmax_b = bf16x2_max(pmax_b, packed[j + 1]);
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; j += 2) {
-                float p0 = (cc * 32 + j < valid) ? exp2f(fmaf(__uint_as_float(cur[j]), p.scale_log2, neg_ref)) : 0.f;
-                float p1 = (cc * 32 + j + 1 < valid) ? exp2f(fmaf(__uint_as_float(cur[j + 1]), p.scale_log2, neg_ref)) : 0.f;
-                sum += p0 + p1;
-                packed[j >> 1] = truncate_bf16x2(p0, p1);
-              }
+            for (int j = 0; j < 32; j += 2) {
+              float p0 = (cc * 32 + j < valid) ? exp2f(fmaf(__uint_as_float(cur[j]), p.scale_log2, neg_ref)) : 0.f;
+              float p1 = (cc * 32 + j + 1 < valid) ? exp2f(fmaf(__uint_as_float(cur[j + 1]), p.scale_log2, neg_ref)) : 0.f;
+              sum += p0 + p1;
+              packed[j >> 1] = truncate_bf16x2(p0, p1);
             }
             tmem_st16(s_addr + cc * 16, packed);
           }
