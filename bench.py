@@ -196,6 +196,14 @@ def time_encode(shape, device, steps: int, warmup: int, frames: int = 8):
     torch.cuda.synchronize()
     quant_seconds = q_start.elapsed_time(q_stop) / 1e3 / 5
     quant_bytes = coeff.shape[0] * (shape.rank * 2 + shape.rank // 2 + 2)
+    # the same with Matrix-Game's rule (quotient rounded to bf16 before rint)
+    for index in range(3 + 5):
+        if index == 3:
+            q_start.record()
+        ops.quant_pack(coeff, codes=codes, scales=scales, in_coeff_dtype=True)
+    q_stop.record()
+    torch.cuda.synchronize()
+    quant_bf16_seconds = q_start.elapsed_time(q_stop) / 1e3 / 5
     del coeff, codes, scales
     # online C-means form (the reference's encode_tensor: 2 iterations from a seeded permutation,
     # then projection + quantiser): one chunk (1 frame) and one encode call (`frames` frames)
@@ -221,6 +229,7 @@ def time_encode(shape, device, steps: int, warmup: int, frames: int = 8):
             "fused": True,
             "form": "given centres: assign kernel, then projection + quantise + pack in one kernel",
             "quant_pack_gbs": quant_bytes / quant_seconds / 1e9,
+            "quant_pack_bf16_rule_gbs": quant_bytes / quant_bf16_seconds / 1e9,
             "quant_pack_tokens": 399360,
             "kmeans_tokens_per_s": online["call"], "kmeans_tokens_per_s_one_frame": online["chunk"],
             "kmeans_form": "online C-means (256 centres, 2 iterations, host-seeded start rows) + projection "

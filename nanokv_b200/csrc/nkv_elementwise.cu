@@ -83,7 +83,7 @@ __device__ __forceinline__ void quant_pack_row(const uint4 (&v)[QP_MAXJ], int su
       amax[j] = fmaxf(amax[j], __shfl_xor_sync(mask, amax[j], 2));
       if (IN_BF16) scale_of[j] = round_to_bf16(__fdiv_rn(fmaxf(amax[j], round_to_bf16(eps)), 7.0f));
       else scale_of[j] = __fdiv_rn(fmaxf(amax[j], eps), 7.0f);
-      inv_of[j] = IN_BF16 ? 0.f : __frcp_rn(scale_of[j]);
+      inv_of[j] = __frcp_rn(scale_of[j]);
     }
   } else {
     float m = amax[0];
@@ -94,7 +94,7 @@ __device__ __forceinline__ void quant_pack_row(const uint4 (&v)[QP_MAXJ], int su
     float scale;
     if (IN_BF16) scale = round_to_bf16(__fdiv_rn(fmaxf(m, round_to_bf16(eps)), 7.0f));
     else scale = __fdiv_rn(fmaxf(m, eps), 7.0f);
-    const float inv = IN_BF16 ? 0.f : __frcp_rn(scale);
+    const float inv = __frcp_rn(scale);
 #pragma unroll
     for (int j = 0; j < MAXJ; ++j) { scale_of[j] = scale; inv_of[j] = inv; }
   }
@@ -108,11 +108,40 @@ __device__ __forceinline__ void quant_pack_row(const uint4 (&v)[QP_MAXJ], int su
     const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
     uint32_t out = 0;
     if (IN_BF16) {
+      // The quotient is rounded to bf16 before rint.  z * inv is within 2 ulp of the IEEE quotient,
+      // so both round to the same bf16 number unless the product's low 16 bits lie within 4 of the
+      // rounding boundary 0x8000; only such values take the division (an exact boundary case cannot
+      // occur: a ratio of two 8-bit mantissas is never a 9-bit midpoint).  rint of the bf16 quotient
+      // is again the addition of 1.5 * 2^23 (exact on a bf16 number, ties to even as rint has them).
+      constexpr float MAGIC = 12582912.0f;
+      constexpr uint32_t MAGIC_BITS = 0x4B400000u;
+      constexpr uint32_t PACK_BIAS = (MAGIC_BITS - 7u) * 0x11111111u;
+      bool ambiguous = false;
+      uint32_t acc = 0;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int c0 = quant_code<true>(__uint_as_float(w[k] << 16), scale, inv);
-        const int c1 = quant_code<true>(__uint_as_float(w[k] & 0xFFFF0000u), scale, inv);
-        out |= static_cast<uint32_t>(c0 | (c1 << 4)) << (8 * k);
+      for (int k = 3; k >= 0; --k) {
+        const float q1 = __uint_as_float(w[k] & 0xFFFF0000u) * inv;
+        const float q0 = __uint_as_float(w[k] << 16) * inv;
+        ambiguous |= ((__float_as_uint(q1) + 0x8004u) & 0xFFFFu) <= 8u;
+        ambiguous |= ((__float_as_uint(q0) + 0x8004u) & 0xFFFFu) <= 8u;
+        const __nv_bfloat162 rounded = __floats2bfloat162_rn(q0, q1);
+        const uint32_t both = *reinterpret_cast<const uint32_t*>(&rounded);
+        const float t1 = __uint_as_float(both & 0xFFFF0000u) + MAGIC;
+        const float t0 = __uint_as_float(both << 16) + MAGIC;
+        acc = (acc << 4) + __float_as_uint(t1);
+        acc = (acc << 4) + __float_as_uint(t0);
+      }
+      out = acc - PACK_BIAS;
+      if (ambiguous) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const uint32_t word = w[e >> 1];
+          const float z = __uint_as_float((e & 1) ? (word & 0xFFFF0000u) : (word << 16));
+          if (((__float_as_uint(z * inv) + 0x8004u) & 0xFFFFu) <= 8u) {
+            const uint32_t code = static_cast<uint32_t>(quant_code<true>(z, scale, inv));
+            out = (out & ~(0xFu << (4 * e))) | (code << (4 * e));
+          }
+        }
       }
     } else {
       // whole piece through the reciprocal; a piece holding a value whose scaled form lies within
