@@ -277,24 +277,6 @@ __device__ __forceinline__ uint4 dequant8_bf16_perm(uint32_t word, __nv_bfloat16
   return r;
 }
 
-// Kernel-order codes as the bf16 integers n - 7 themselves: where one scale covers a token's whole
-// latent row it commutes with the decode product and is applied to the accumulator instead.
-__device__ __forceinline__ uint4 expand8_perm(uint32_t word) {
-  const uint32_t lo = word & 0x0F0F0F0Fu, hi = (word >> 4) & 0x0F0F0F0Fu, magic = 0x43434343u;
-  const uint32_t t[4] = {__byte_perm(lo, magic, 0x4140), __byte_perm(lo, magic, 0x4342),
-                         __byte_perm(hi, magic, 0x4140), __byte_perm(hi, magic, 0x4342)};
-  const uint32_t bias_bits = 0x43074307u;   // bf16 pair (135, 135)
-  const __nv_bfloat162 bias2 = *reinterpret_cast<const __nv_bfloat162*>(&bias_bits);
-  uint4 r;
-  uint32_t* o = &r.x;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const __nv_bfloat162 v = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&t[i]), bias2);
-    o[i] = *reinterpret_cast<const uint32_t*>(&v);
-  }
-  return r;
-}
-
 __device__ __forceinline__ uint4 dequant8_perm(uint32_t word, float scale) {
   float e[8];
 #pragma unroll
@@ -337,9 +319,6 @@ struct Laps {
       last = now;
     }
   }
-  __device__ __forceinline__ void mark() {   // what ran since the previous lap belongs to no bucket
-    if (out) last = static_cast<unsigned>(clock64());
-  }
   __device__ __forceinline__ void flush() {
     if (out) {
 #pragma unroll
@@ -351,7 +330,6 @@ struct Laps {
 struct Laps {
   __device__ __forceinline__ void start(long long*, bool) {}
   __device__ __forceinline__ void lap(int) {}
-  __device__ __forceinline__ void mark() {}
   __device__ __forceinline__ void flush() {}
 };
 #endif
@@ -987,8 +965,6 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
     int seq = 0, jobs = 0, gp = 0;
     Laps laps;
     laps.start(p.prof + (pidx == 0 ? 24 : 40), p.prof != nullptr && g == 0 && (pidx == 0 || pidx == p.prod_k) && tid == 0);
-    Laps fine;   // the first V producer's expansion and epilogue, step by step
-    fine.start(p.prof + 56, p.prof != nullptr && g == 0 && pidx == p.prod_k && tid == 0);
     // A job runs in two stages: the codes are expanded (and the MMAs started) right away, its
     // epilogue follows after the NEXT job's expansion, so that the MMAs' tail, the accumulator read
     // and the ring stores of one job hide under the expansion of the following one.
@@ -1027,13 +1003,11 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
             if (c0 + 2 < nchunks) code_next[0] = code_at(c0 + 2);
             if (c0 + 3 < nchunks) code_next[1] = code_at(c0 + 3);
             const int st = gp % NSTAGE;
-            fine.mark();
             // the staging slot's previous tenant is pair gp - NSTAGE
             if (gp >= NSTAGE)
               ok = mwait_all(&bars[PAIR_DONE + ((gp - NSTAGE) & (NDONE - 1))], ((gp - NSTAGE) / NDONE) & 1, ctx, 502);
             if (!ok) break;
             tc_fence_after();
-            fine.lap(0);
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
               if (j < n) {
@@ -1044,18 +1018,13 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
                 const uint16_t sbits = my_scales[gi];
                 const uint32_t words[4] = {code.x, code.y, code.z, code.w};
                 uint32_t packed[16];
-                if (FASTQ) {
-#pragma unroll
-                  for (int k = 0; k < 4; ++k) {
-                    const uint4 v = expand8_perm(words[k]);
-                    packed[4 * k] = v.x; packed[4 * k + 1] = v.y; packed[4 * k + 2] = v.z; packed[4 * k + 3] = v.w;
-                  }
-                } else if (p.scale_dtype == NKV_BF16) {
+                if (FASTQ || p.scale_dtype == NKV_BF16) {
                   const uint32_t pair = static_cast<uint32_t>(sbits) * 0x00010001u;
                   const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&pair);
 #pragma unroll
                   for (int k = 0; k < 4; ++k) {
-                    const uint4 v = p.w_perm ? dequant8_bf16_perm(words[k], scale2) : dequant8_bf16(words[k], scale2);
+                    const uint4 v = (FASTQ || p.w_perm) ? dequant8_bf16_perm(words[k], scale2)
+                                                         : dequant8_bf16(words[k], scale2);
                     packed[4 * k] = v.x; packed[4 * k + 1] = v.y; packed[4 * k + 2] = v.z; packed[4 * k + 3] = v.w;
                   }
                 } else {
@@ -1069,12 +1038,9 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
                 tmem_st16(tmem_base + lane_sel + 256 + st * 64 + j * 32 + wg * 16, packed);
               }
             }
-            fine.lap(1);
             tmem_wait_st();
-            fine.lap(2);
             tc_fence_before();
             warp_arrive(&bars[LAT_FULL + st], lane);
-            fine.lap(3);
           }
         };
         if (p.w_perm && p.scale_dtype == NKV_BF16 && ng == 1) expand_pairs(std::true_type{});
@@ -1084,107 +1050,7 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
         fence_proxy_async();   // the codes were read; TMA may overwrite them
         warp_arrive(&bars[CODES_FREE], lane);
     };
-    // Epilogue of a plain rebuild (no positional restore): bf16(acc * scale + bias) per thread in the
-    // row-owner layout of tensor memory, staged through shared memory into the layout of the ring
-    // stores (D / 16 lanes per token row, whole lines), where the centre pieces -- gathered in that same
-    // layout -- are added with the second bf16 rounding.  The epilogue is bound by the load / store
-    // unit: whole-line gathers and stores and no redistribution of the centres halve its work.
-    auto epilogue_plain = [&](const Job& job) {
-        constexpr int COLS = D / 2;          // columns of a thread's row piece
-        constexpr int ROWB = COLS * 2;       // its bytes: 128 or 64
-        constexpr int LPR = ROWB / 16;       // lanes per token row in the store layout
-        constexpr int RPI = 32 / LPR;        // token rows per load / store instruction
-        constexpr int SROWS = 2048 / ROWB;   // token rows the warp's staging area holds: 16 or 32
-        constexpr int PHASES = 32 / SROWS;
-        constexpr int NI = SROWS / RPI;      // instructions per phase
-        const int head = job.head, valid = job.valid, mb = job.num % NMETA;
-        const uint32_t acc = tmem_base + (job.num & 1) * 128;
-        const int wrow0 = 32 * (warp & 3);
-        uint16_t* const slot_rows = ring + static_cast<size_t>(g * R + job.slot) * TOK * D;
-        const float* bias_head = (tensor ? p.bias_v : p.bias_k) + head * D + wg * COLS;
-        const bool late_scale = p.w_perm && p.scale_dtype == NKV_BF16 && ng == 1;
-        const float row_scale = late_scale ? bf16_bits_to_float(scales[mb * TOK + row]) : 1.f;
-        const int prow = lane / LPR, piece = lane % LPR;   // this lane's place in the store layout
-        fine.mark();
-        uint4 cen[PHASES * NI];
-        {
-          const uint16_t* cbase = static_cast<const uint16_t*>(hist.centers) + static_cast<size_t>(head) * D +
-                                  wg * COLS + piece * 8;
-#pragma unroll
-          for (int i = 0; i < PHASES * NI; ++i) {
-            const int crow_i = crow[mb * TOK + wrow0 + i * RPI + prow];
-            cen[i] = __ldg(reinterpret_cast<const uint4*>(cbase + static_cast<size_t>(crow_i) * hist.center_width));
-          }
-        }
-        fine.lap(4);
-        ok = mwait_all(&bars[PAIR_DONE + (job.last_pair & (NDONE - 1))], (job.last_pair / NDONE) & 1, ctx, 503);
-        tc_fence_after();
-        laps.lap(2);
-        fine.mark();
-        uint32_t packed[COLS / 2];
-#pragma unroll
-        for (int sub = 0; sub < COLS / 32; ++sub) {
-          uint32_t acc_raw[32];
-          tmem_ld32_issue(acc + lane_sel + wg * COLS + sub * 32, acc_raw);
-          float bias[32];
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const float4 b4 = __ldg(reinterpret_cast<const float4*>(bias_head + sub * 32 + j));
-            bias[j] = b4.x; bias[j + 1] = b4.y; bias[j + 2] = b4.z; bias[j + 3] = b4.w;
-          }
-          tmem_ld32_wait(acc_raw);
-#pragma unroll
-          for (int j = 0; j < 32; j += 2)
-            packed[sub * 16 + j / 2] = pack_bf16x2(fmaf(__uint_as_float(acc_raw[j]), row_scale, bias[j]),
-                                                    fmaf(__uint_as_float(acc_raw[j + 1]), row_scale, bias[j + 1]));
-        }
-        fine.lap(5);
-        uint8_t* stage = smem + L::scratch_off(npairs) + warp * 2048;
-#pragma unroll
-        for (int ph = 0; ph < PHASES; ++ph) {
-          if (lane / SROWS == ph) {   // the row owners of this phase stage their pieces
-            const int r = lane % SROWS;
-            const int x = ROWB == 128 ? (r & 7) : ((r >> 1) & 3);
-#pragma unroll
-            for (int j = 0; j < LPR; ++j)
-              *reinterpret_cast<uint4*>(stage + r * ROWB + ((j ^ x) << 4)) =
-                  make_uint4(packed[j * 4], packed[j * 4 + 1], packed[j * 4 + 2], packed[j * 4 + 3]);
-          }
-          __syncwarp();
-#pragma unroll
-          for (int i = 0; i < NI; ++i) {
-            const int r = i * RPI + prow;                  // staged row
-            const int x = ROWB == 128 ? (r & 7) : ((r >> 1) & 3);
-            const uint4 first = *reinterpret_cast<const uint4*>(stage + r * ROWB + ((piece ^ x) << 4));
-            const uint4 centre = cen[ph * NI + i];
-            const uint32_t fw[4] = {first.x, first.y, first.z, first.w};
-            const uint32_t cw[4] = {centre.x, centre.y, centre.z, centre.w};
-            uint32_t ow[4];
-            const bool row_in = wrow0 + ph * SROWS + r < valid;
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-              const __nv_bfloat162 sum = __hadd2(*reinterpret_cast<const __nv_bfloat162*>(&fw[w]),
-                                                 *reinterpret_cast<const __nv_bfloat162*>(&cw[w]));
-              ow[w] = row_in ? *reinterpret_cast<const uint32_t*>(&sum) : 0u;
-            }
-            *reinterpret_cast<uint4*>(slot_rows + static_cast<size_t>(wrow0 + ph * SROWS + r) * D + wg * COLS +
-                                      piece * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-          }
-          __syncwarp();
-        }
-        fine.lap(7);
-        if (!ok) return;
-        laps.lap(3);
-        warp_arrive(&bars[META_FREE + mb], lane);
-        tc_fence_before();
-        warp_arrive(&bars[OUT_DONE + job.num % NMETA], lane);
-        laps.lap(5);
-    };
     auto epilogue = [&](const Job& job) {
-        if constexpr (!ROPE && !CAM) {
-          epilogue_plain(job);
-          return;
-        }
         const int head = job.head, t0 = job.t0, valid = job.valid, mb = job.num % NMETA;
         const int slot = job.slot;   // free: the metadata warp has checked that before META_FULL
         const uint32_t acc = tmem_base + (job.num & 1) * 128;
@@ -1219,9 +1085,6 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
             cam_frame = cam.matrices +
                         static_cast<size_t>(min((t0 + row) / cam.tokens_per_frame, cam.frames - 1)) * 64;
           const float* bias_head = (tensor ? p.bias_v : p.bias_k) + head * D;
-          // one scale per token and kernel-order rows: the latents went in unscaled (see expand8_perm)
-          const bool late_scale = p.w_perm && p.scale_dtype == NKV_BF16 && ng == 1;
-          const float row_scale = late_scale ? bf16_bits_to_float(scales[mb * TOK + row]) : 1.f;
           // accumulator complete: the tile's last pair is pair gp - 1
           // Centre rows of this warp's 32 tokens (32 columns = 64 bytes per round), gathered
           // cooperatively: 4 lanes read one row's 16-byte pieces, so a load instruction touches
@@ -1278,7 +1141,6 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
               tc_fence_after();
               laps.lap(2);
             }
-            fine.mark();
             // the accumulator read stays in flight under the centre staging
             uint32_t acc_raw[32];
             tmem_ld32_issue(acc + lane_sel + col0, acc_raw);
@@ -1297,9 +1159,7 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
                                                          ((j ^ (lane & (PIECES - 1))) << 4));
               __syncwarp();
             }
-            fine.lap(4);
             tmem_ld32_wait(acc_raw);
-            fine.lap(5);
             float v[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc_raw[i]);
@@ -1315,7 +1175,7 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
                   const int j = j4 * 8 + w * 2;
-                  const uint32_t first = pack_bf16x2(fmaf(v[j], row_scale, bias[j]), fmaf(v[j + 1], row_scale, bias[j + 1]));
+                  const uint32_t first = pack_bf16x2(v[j] + bias[j], v[j + 1] + bias[j + 1]);
                   const __nv_bfloat162 sum = __hadd2(*reinterpret_cast<const __nv_bfloat162*>(&first),
                                                      *reinterpret_cast<const __nv_bfloat162*>(&cwords[w]));
                   packed[j4 * 4 + w] = in ? *reinterpret_cast<const uint32_t*>(&sum) : 0u;
@@ -1326,7 +1186,7 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
               for (int w = 0; w < 4; ++w) {
                 const int j = j4 * 8 + w * 2;
                 // the rebuilt pair in packed bf16 arithmetic (as above), then widened for the transforms
-                const uint32_t first = pack_bf16x2(fmaf(v[j], row_scale, bias[j]), fmaf(v[j + 1], row_scale, bias[j + 1]));
+                const uint32_t first = pack_bf16x2(v[j] + bias[j], v[j + 1] + bias[j + 1]);
                 const __nv_bfloat162 sum = __hadd2(*reinterpret_cast<const __nv_bfloat162*>(&first),
                                                    *reinterpret_cast<const __nv_bfloat162*>(&cwords[w]));
                 const uint32_t rebuilt = *reinterpret_cast<const uint32_t*>(&sum);
@@ -1359,7 +1219,6 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
                 }
               }
             }
-            fine.lap(6);
             // Into the ring through the warp's staging area, so that a store instruction writes whole
             // 64-byte row pieces (4 lanes per row, 8 rows) instead of 16 bytes of 32 different rows.
             {
@@ -1379,7 +1238,6 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
               }
               __syncwarp();
             }
-            fine.lap(7);
           }
         }
         if (!ok) return;
@@ -1412,7 +1270,6 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
     }
     if (ok && have_prev) epilogue(prev);
     laps.flush();
-    fine.flush();
   }
 }
 
