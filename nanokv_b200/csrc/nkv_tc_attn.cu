@@ -908,22 +908,65 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
       if (done && lane == 0) st_release(gflags + pidx, j + 1);
       return done;
     };
-    for (int u = g; u < p.units && ok; u += p.groups) {
-      const Unit un = unit_of(p, u);
-      for (int t = 0; t < un.nt && ok; ++t, ++seq) {
-        if (seq % PH != mine) continue;
-        const int b = jobs % NMETA, use = jobs / NMETA;
-        // the job's metadata is fetched into registers while job jobs - NMETA is still running
-        const int t0 = (un.tile0 + t) * TOK;
-        int crow_reg[TOK / 32];
-        uint16_t scale_reg[TOK / 32];
-#pragma unroll
-        for (int k = 0; k < TOK / 32; ++k) {
-          const int tok = t0 + lane + 32 * k;
-          const bool in = tok < p.N;
-          crow_reg[k] = in ? center_row_of(hist, tok) : 0;
-          scale_reg[k] = (in && ng == 1) ? __ldg(static_cast<const uint16_t*>(hist.scales) + tok) : uint16_t(0);
+    // This producer's jobs in order: (first token, tile number within the group).
+    int it_u = g, it_t = 0, it_seq = 0;
+    Unit it_un = unit_of(p, it_u < p.units ? it_u : 0);
+    auto next_job = [&](int& t0, int& tile_seq) {
+      while (it_u < p.units) {
+        if (it_t < it_un.nt) {
+          const int t = it_t++, sq = it_seq++;
+          if (sq % PH == mine) {
+            t0 = (it_un.tile0 + t) * TOK;
+            tile_seq = sq;
+            return true;
+          }
+        } else {
+          it_u += p.groups;
+          it_t = 0;
+          if (it_u < p.units) it_un = unit_of(p, it_u);
         }
+      }
+      return false;
+    };
+    // A job's per-token metadata (centre row, scale).  The centre row needs the token's segment: a
+    // binary search over the segment table, four or five DEPENDENT loads that miss the first-level
+    // cache (the centre gathers sweep it) -- several thousand cycles per job when every token
+    // searches, more than the compute warps need for the job.  A tile nearly always lies inside one
+    // segment, so the segment found last (its token range and centre-row base) is kept in registers
+    // and only a tile that leaves it searches again; a tile that straddles segments searches per
+    // token.  The id and scale loads of job j + 2 are issued before job j is handled.
+    struct Meta { int t0, seq, crow[TOK / 32]; uint16_t scale[TOK / 32]; bool valid; };
+    int seg_lo = 0, seg_hi = 0, seg_row = 0;   // tokens [seg_lo, seg_hi) take centre rows from seg_row on
+    auto fetch = [&](Meta& m) {
+      m.valid = next_job(m.t0, m.seq);
+      bool one_segment = false;
+      if (m.valid) {
+        const int first = m.t0, last = min(m.t0 + TOK, p.N) - 1;
+        if (first < seg_lo || first >= seg_hi) {
+          const int sg = find_segment(hist.seg_start, hist.segments, first);
+          seg_lo = hist.seg_start[sg];
+          seg_hi = sg + 1 < hist.segments ? hist.seg_start[sg + 1] : 0x7fffffff;
+          seg_row = hist.seg_center_row[sg];
+        }
+        one_segment = first >= seg_lo && last < seg_hi;
+      }
+#pragma unroll
+      for (int k = 0; k < TOK / 32; ++k) {
+        const int tok = m.t0 + lane + 32 * k;
+        const bool in = m.valid && tok < p.N;
+        m.crow[k] = !in ? 0 : (one_segment ? seg_row + load_id(hist.ids, hist.id_bytes, tok) : center_row_of(hist, tok));
+        m.scale[k] = (in && ng == 1) ? __ldg(static_cast<const uint16_t*>(hist.scales) + tok) : uint16_t(0);
+      }
+    };
+    Meta cur{}, ahead1{}, ahead2{};
+    fetch(cur);
+    fetch(ahead1);
+    fetch(ahead2);
+    while (cur.valid && ok) {
+      {
+        const int b = jobs % NMETA, use = jobs / NMETA;
+        const int t0 = cur.t0;
+        seq = cur.seq;
         if (use >= 1) {   // job jobs - NMETA is finished: its metadata buffer is free, its tile is stored
           ok = mwait_all(&bars[META_FREE + b], (use - 1) & 1, ctx, 420 + b);
           ok = ok && publish(jobs - NMETA);
@@ -938,8 +981,8 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
 #pragma unroll
         for (int k = 0; k < TOK / 32; ++k) {
           const int r = lane + 32 * k;
-          crow[b * TOK + r] = crow_reg[k];
-          if (ng == 1) scales[b * TOK + r] = scale_reg[k];
+          crow[b * TOK + r] = cur.crow[k];
+          if (ng == 1) scales[b * TOK + r] = cur.scale[k];
         }
         if (ng > 1) {
           for (int r = lane; r < TOK; r += 32) {
@@ -953,6 +996,9 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
         warp_arrive(&bars[META_FULL + b], lane);
         ++jobs;
       }
+      cur = ahead1;
+      ahead1 = ahead2;
+      fetch(ahead2);
     }
     for (int j = jobs >= NMETA ? jobs - NMETA : 0; j < jobs && ok; ++j) ok = publish(j);
   } else {
