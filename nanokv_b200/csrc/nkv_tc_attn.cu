@@ -1160,21 +1160,16 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
             uint4 cen[PIECES];
 #pragma unroll
             for (int i = 0; i < PIECES; ++i) cen[i] = cen_all[sub][i];
-            // rotation entries of this thread's 16 pairs, requested before the accumulator wait
-            float2 rot[16];
-            if (ROPE) {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                rot[i] = make_float2(1.f, 0.f);
-                if (rotate) {
-                  const int local = col0 / 2 + i;   // pair of the head row
-                  const int pg = p.rope.pair_index ? __ldg(p.rope.pair_index + head * (D / 2) + local) : local;
-                  const int coord = pg < band_a ? coord_t : (pg < band_b ? coord_h : coord_w);
-                  rot[i] = __ldg(reinterpret_cast<const float2*>(p.rope.cos_sin) +
-                                 static_cast<size_t>(coord) * p.rope.table_half + pg);
-                }
-              }
-            }
+            // rotation entry of pair i of this thread's 16: fetched per block of four pairs, right where
+            // it is used (all sixteen held across the accumulator wait cost more in registers than the
+            // table's latency does: the table sits in the cache)
+            auto rotation_of = [&](int i) {
+              const int local = col0 / 2 + i;   // pair of the head row
+              const int pg = p.rope.pair_index ? __ldg(p.rope.pair_index + head * (D / 2) + local) : local;
+              const int coord = pg < band_a ? coord_t : (pg < band_b ? coord_h : coord_w);
+              return __ldg(reinterpret_cast<const float2*>(p.rope.cos_sin) +
+                           static_cast<size_t>(coord) * p.rope.table_half + pg);
+            };
             float bias[32];
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
@@ -1214,6 +1209,11 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
             for (int j4 = 0; j4 < 4; ++j4) {
               const uint32_t cwords[4] = {cen[j4].x, cen[j4].y, cen[j4].z, cen[j4].w};
               float block[8];   // the 8-wide block j4 of this thread's columns (camera transform only)
+              float2 rot[4];
+              if (ROPE) {
+#pragma unroll
+                for (int w = 0; w < 4; ++w) rot[w] = rotate ? rotation_of(j4 * 4 + w) : make_float2(1.f, 0.f);
+              }
               if (!ROPE && !CAM) {
                 // plain rebuild in packed bf16 arithmetic: bf16x2(acc + bias) then one bf16x2 add of the
                 // centre word -- the same two roundings (the sum of two bf16 numbers is exact in fp32
@@ -1238,7 +1238,7 @@ __device__ __forceinline__ void producer_role(uint8_t* smem, uint64_t* bars, uin
                 const uint32_t rebuilt = *reinterpret_cast<const uint32_t*>(&sum);
                 float x0 = __uint_as_float(rebuilt << 16), x1 = __uint_as_float(rebuilt & 0xFFFF0000u);
                 if (rotate) {   // the pair (x0, x1) of the rebuilt bf16 key is one complex number
-                  const float2 cs = rot[j >> 1];
+                  const float2 cs = rot[w];
                   const float k0 = x0, k1 = x1;
                   x0 = fmaf(k0, cs.x, -(k1 * cs.y));
                   x1 = fmaf(k0, cs.y, k1 * cs.x);
