@@ -290,6 +290,42 @@ def decode_rows(segment: dict, *, decoder: torch.Tensor, mean: torch.Tensor,
     return rows.to(dtype)
 
 
+def hy_compress(x: torch.Tensor, *, encoder: torch.Tensor, mean: torch.Tensor, clusters: int, iters: int,
+                layer: int, scale_dtype: torch.dtype = torch.bfloat16) -> dict:
+    """HY-WorldPlay's form of the encoder on x [1, H, S, D] (HY/kv_codecs.py:1000-1146 with
+    _joint_semantic_smooth :116-208).  The same algorithm as encode_rows with three differences that
+    change bits: the C-means residual is rounded to the input dtype before anything else happens to
+    it (:207), the coefficients are quantised in fp32 whatever the encoder produced (:237-255), and
+    the seed of the start rows is 20260804 + layer (:139).
+    """
+    batch, heads, sequence, dim = x.shape
+    rows = x.permute(0, 2, 1, 3).reshape(batch, sequence, heads * dim)
+    residual, stored, ids = semantic_residual(rows, clusters, iters, 20260804 + int(layer))
+    residual = residual.to(x.dtype)
+    flat = residual.reshape(-1, heads * dim).float() - mean.float()
+    coeff = operator_linear(flat, encoder)
+    codes, scale = quantize_rows(coeff, eps=F32_EPS, in_coeff_dtype=False, scale_dtype=scale_dtype)
+    packed, count = pack_int4(codes)
+    return {"shape": (batch, sequence, heads * dim), "rank": int(encoder.shape[0]), "packed": packed,
+            "count": count, "codes": codes, "scale": scale, "centers": stored, "ids": ids}
+
+
+def hy_decompress(segment: dict, *, decoder: torch.Tensor, mean: torch.Tensor, heads: int,
+                  dtype: torch.dtype) -> torch.Tensor:
+    """segment -> [1, H, S, D] in `dtype` as HY decodes it (HY/kv_codecs.py:1264-1437): latent =
+    code * scale in fp32, the decoder GEMM in the operator's arithmetic with the mean as bias, the
+    centre added in FP32 (:1391-1404), one cast to `dtype`, layout [B, H, S, D]."""
+    batch, sequence, joint = segment["shape"]
+    codes = unpack_int4(segment["packed"], segment["count"], (batch * sequence, segment["rank"]))
+    latent = codes.float() * segment["scale"].float().reshape(-1, 1)
+    rows = operator_linear(latent, decoder, mean)
+    table = segment["centers"].float()
+    ids = segment["ids"].to(torch.long)
+    assigned = torch.gather(table, 1, ids[..., None].expand(-1, -1, joint)).reshape(-1, joint)
+    rows = rows + assigned
+    return rows.reshape(batch, sequence, heads, joint // heads).permute(0, 2, 1, 3).contiguous().to(dtype)
+
+
 # --------------------------------------------------------------------------- #
 # Attention with log-sum-exp, and the LSE merge
 # --------------------------------------------------------------------------- #

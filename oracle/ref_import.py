@@ -18,6 +18,8 @@ import sys
 import types
 from pathlib import Path
 
+import torch
+
 MG = "models/Matrix-Game-3.5/fast"
 LB = "models/LingBot-World-2.0/fast"
 HY = "models/HY-WorldPlay/fast"
@@ -110,3 +112,34 @@ def load_hy_reader(root=None):
         _stub_package(name, path)
     import importlib
     return importlib.import_module("hyvideo.models.transformers.modules.direct_codec_latent_attention")
+
+
+def load_hy_codec(root=None):
+    """HY-WorldPlay's codec module (hyvideo/models/transformers/modules/kv_codecs.py), imported under
+    the same stand-in parent packages as the reader."""
+    load_hy_reader(root)
+    import importlib
+    return importlib.import_module("hyvideo.models.transformers.modules.kv_codecs")
+
+
+def inject_hy_operator(codec, tensor_name: str, layer: int, *, mean, encoder, decoder, storage: str) -> None:
+    """Stand in for the artefact files of one (tensor, layer): global_pca_compress_v and
+    decompress_kv_tensor obtain their operator from _global_device_operator_weights
+    (kv_codecs.py:834-912), the available rank from _load_global_basis (:428-458) and the encoder-delta
+    flag from _load_global_linear_delta (:542-582); the three are replaced by functions that return the
+    given matrices, packed by the module's own _pack_operator_weight (:647-679)."""
+    table = codec.__dict__.setdefault("_INJECTED_OPERATORS", {})
+    table[(tensor_name, int(layer))] = {
+        "mean": mean.float(),
+        "encoder": codec._pack_operator_weight(encoder, storage, "cpu"),
+        "decoder": codec._pack_operator_weight(decoder, storage, "cpu"),
+        "mode": storage,
+        "rank": int(encoder.shape[0]),
+    }
+    codec._global_device_operator_weights = (
+        lambda root_, linear_root, layer_idx, name, rank, device: table[(name, int(layer_idx))])
+    codec._load_global_basis = (
+        lambda root_, layer_idx, name="v": {"components": torch.zeros(table[(name, int(layer_idx))]["rank"], 1),
+                                              "mean": table[(name, int(layer_idx))]["mean"]})
+    codec._load_global_linear_delta = lambda *args, **kwargs: {"model": {}}
+

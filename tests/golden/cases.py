@@ -327,3 +327,9 @@ def build_hy() -> dict:
            "encoder_key": torch.randn(2, H, E, D, generator=gen).to(bf),
            "encoder_value": torch.randn(2, H, E, D, generator=gen).to(bf)}
     return out
+
+
+# HY-WorldPlay's codec entry points: joint dimension 2048 (fixed in the reference), layout [B, H, S, D]
+HY_CODEC = CodecCase("hy_codec_bf16", Shape("hy_codec", 16, 128, 128, 16, 200, 8, "bf16"), (200,),
+                     layer=4, seed=31, mean_std=0.05)
+

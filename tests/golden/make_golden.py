@@ -485,6 +485,49 @@ def run_hy_case(root) -> dict:
             "q_digest": np.array([checksum(data["q_pre"])], dtype=np.uint64)}
 
 
+def hy_codec_environment(case: cases.CodecCase) -> None:
+    """The environment the reference's HY codec reads for the global-PCA INT4 form with online
+    joint-head C-means (kv_codecs.py:70-113,1009-1075)."""
+    for name in list(os.environ):
+        if name.startswith("HY_KV_CODEC"):
+            os.environ.pop(name)
+    os.environ.update({
+        "HY_KV_CODEC_ENABLE": "1", "HY_KV_CODEC_MODE": "global_pca", "HY_KV_CODEC_COEFF_QUANT": "int4",
+        "HY_KV_CODEC_GLOBAL_PCA_RANK": str(case.shape.rank), "HY_KV_CODEC_OPERATOR_WEIGHT_MODE": "bf16",
+        "HY_KV_CODEC_SEMANTIC_SMOOTH_K": "1", "HY_KV_CODEC_SEMANTIC_SMOOTH_V": "1",
+        "HY_KV_CODEC_SEMANTIC_CLUSTERS": str(case.shape.centers), "HY_KV_CODEC_SEMANTIC_ITERS": str(case.iters),
+        "HY_KV_CODEC_DETERMINISTIC_CENTERS": "1", "HY_KV_CODEC_PROFILE": "0",
+        "HY_KV_CODEC_SEMANTIC_BASIS_DIR_K": "synthetic_k", "HY_KV_CODEC_SEMANTIC_BASIS_DIR_V": "synthetic_v",
+        "HY_KV_CODEC_SEMANTIC_LINEAR_DIR_K": "synthetic_k", "HY_KV_CODEC_SEMANTIC_LINEAR_DIR_V": "synthetic_v",
+    })
+
+
+def run_hy_codec_case(case: cases.CodecCase, root) -> dict:
+    """compress_kv_tensor / decompress_kv_tensor of HY-WorldPlay's codec module on [1, H, S, D] tensors
+    (global PCA, INT4 coefficients, online joint-head C-means, bf16 operators)."""
+    codec = ref_import.load_hy_codec(root)
+    hy_codec_environment(case)
+    data = cases.build(case)
+    shape = case.shape
+    out = {}
+    for name in ("k", "v"):
+        op = data[f"{name}_op"]
+        ref_import.inject_hy_operator(codec, name, case.layer, mean=op["mean"], encoder=op["encoder"],
+                                      decoder=op["decoder"], storage="bf16")
+        rows = data[f"{name}_chunks"][0]
+        x = rows.reshape(1, -1, shape.heads, shape.head_dim).permute(0, 2, 1, 3).contiguous()
+        payload, stats = codec.compress_kv_tensor(x, case.layer, name)
+        out[f"{name}_ids"] = payload["semantic_ids"].numpy()
+        out[f"{name}_centers"] = bits(payload["semantic_centers"])
+        out[f"{name}_packed"] = payload["latent_int8"].numpy()
+        out[f"{name}_scale"] = bits(payload["latent_scale"])
+        out[f"{name}_bytes"] = np.array([int(stats["actual_bytes"])], dtype=np.int64)
+        out[f"{name}_decoded_bf16"] = bits(codec.decompress_kv_tensor(payload, torch.bfloat16, "cpu")[:, :, :48])
+        out[f"{name}_decoded_f32"] = codec.decompress_kv_tensor(payload, torch.float32, "cpu")[:, :, :16].numpy()
+        out[f"{name}_digest"] = np.array([checksum(x)], dtype=np.uint64)
+    return out
+
+
 def run_protected_tokens_case(root) -> dict:
     """protected_tokens of the MG core module on seeded frame-id sequences."""
     core = ref_import.load_mg_core(root)
@@ -571,6 +614,7 @@ def main() -> None:
     save("stream_lb_bf16", lambda: run_stream_case(cases.ROLLING, root))
     save("attend_lb_bf16", lambda: run_attend_case(cases.ROLLING, root))
     save("hy_two_branch_bf16", lambda: run_hy_case(root))
+    save(cases.HY_CODEC.name, lambda: run_hy_codec_case(cases.HY_CODEC, root))
     save("protected_tokens", lambda: run_protected_tokens_case(root))
     save("merge_edge", lambda: run_merge_case(root))
     save("select_mg_bf16", lambda: run_select_case(cases.MINI_BF16, root))

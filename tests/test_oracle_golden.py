@@ -230,3 +230,30 @@ def test_mg_operator_int8_packing_matches_the_reference(name, group, monkeypatch
     packed = mg_codec._pack_int8(cases.build_int8_weight())
     assert np.array_equal(packed["qweight"].numpy(), gold[f"{name}_qweight"])
     assert np.array_equal(packed["scale"].view(torch.int16).numpy(), gold[f"{name}_scale"])
+
+
+def test_hy_codec_entry_points():
+    """The oracle's restatement of HY-WorldPlay's compress / decompress against the reference's own
+    payload and decoded rows (bit-exact: same arithmetic, same CPU library)."""
+    case = cases.HY_CODEC
+    gold = load(case.name)
+    data = cases.build(case)
+    shape = case.shape
+    for name in ("k", "v"):
+        op = data[f"{name}_op"]
+        rows = data[f"{name}_chunks"][0]
+        x = rows.reshape(1, -1, shape.heads, shape.head_dim).permute(0, 2, 1, 3).contiguous()
+        assert int(gold[f"{name}_digest"][0]) == checksum(x), "input generator drifted from the fixture"
+        seg = oracle.hy_compress(x, encoder=op["encoder"], mean=op["mean"], clusters=shape.centers,
+                                 iters=case.iters, layer=case.layer)
+        assert np.array_equal(seg["ids"].numpy(), gold[f"{name}_ids"])
+        assert torch.equal(seg["centers"], from_bits(gold[f"{name}_centers"], torch.bfloat16))
+        assert np.array_equal(seg["packed"].numpy(), gold[f"{name}_packed"])
+        assert torch.equal(seg["scale"].reshape(1, -1, 1), from_bits(gold[f"{name}_scale"], torch.bfloat16))
+        out = oracle.hy_decompress(seg, decoder=op["decoder"], mean=op["mean"], heads=shape.heads,
+                                   dtype=torch.bfloat16)
+        assert torch.equal(out[:, :, :48], from_bits(gold[f"{name}_decoded_bf16"], torch.bfloat16))
+        out32 = oracle.hy_decompress(seg, decoder=op["decoder"], mean=op["mean"], heads=shape.heads,
+                                     dtype=torch.float32)
+        assert torch.equal(out32[:, :, :16], torch.from_numpy(gold[f"{name}_decoded_f32"]))
+
