@@ -11,11 +11,8 @@ What differs from the Matrix-Game form of the same algorithm, and is kept: the C
 rounded to the input dtype before the mean is taken off and the encoder applied (:190-208, :1078-1081),
 the coefficients are quantised in fp32 whatever dtype the encoder produced them in (:237-255), the
 scale may be stored as bf16 or fp16 (HY_KV_CODEC_SCALE_DTYPE), and payloads and results keep the
-[B, H, S, D] layout.  One difference is NOT kept: asked for fp32 rows from bf16 operators, the
-reference adds the centre in fp32 and returns that sum (:1391-1404); the decode kernel rounds the
-sum to bf16 first, as the Matrix-Game and LingBot forms do, so fp32 results differ from the
-reference's by up to one bf16 rounding step (bf16 results, the deployed case, are the same).
-Operators come from `register_operator` (the reference reads them from
+[B, H, S, D] layout; asked for fp32 rows from bf16 operators, the centre is added in fp32 as there
+(:1391-1404).  Operators come from `register_operator` (the reference reads them from
 artefact files through _global_device_operator_weights :834-912).  The other modes of that module
 (uniform INT2/3/8, per-head PCA, block sketches, residual MLP) are research baselines and raise
 NotImplementedError here.
@@ -262,7 +259,16 @@ def decompress_kv_tensor(obj_or_tensor: Any, dtype: torch.dtype = torch.float32,
     device = payload["latent_int8"].device if device is None else torch.device(device)
     op = _operator(str(payload.get("tensor_name", "v")), int(payload["layer_idx"]), device)
     hist = history_from_payload(payload, device=device)
-    rows = ops.decode_rows(hist.view(), op.decoder, op.mean, dtype=dtype)
+    if dtype == torch.float32 and op.dtype == torch.bfloat16:
+        # the reference adds the centre to the bf16 decoder output in fp32 and returns that sum
+        # (:1391-1404); the decode kernel's centre add rounds to bf16, so the centres are taken out of
+        # the kernel's sight (a zero table) and added here
+        table = hist.centers.clone()
+        hist.centers.zero_()
+        rows = ops.decode_rows(hist.view(), op.decoder, op.mean, dtype=torch.bfloat16).float()
+        rows += table.float().index_select(0, hist.ids[:sequence].long())
+    else:
+        rows = ops.decode_rows(hist.view(), op.decoder, op.mean, dtype=dtype)
     return rows.reshape(batch, sequence, heads, dim).permute(0, 2, 1, 3).contiguous()
 
 

@@ -90,6 +90,9 @@ def test_decompress_of_the_reference_payload():
         want32 = torch.from_numpy(gold[f"{name}_decoded_f32"])
         err32 = (out32[:, :, :16].cpu() - want32).abs().max() / want32.abs().max()
         assert out32.dtype == torch.float32 and float(err32) <= 2.0 ** -7
+        # fp32 rows carry the centre in full precision: they are not the bf16 rows widened
+        assert not torch.equal(out32, out.float())
+        assert float((out32 - out.float()).abs().max() / out.float().abs().max()) <= 2.0 ** -8
         # this module's own payload of the same input decodes to the same rows (up to the few codes that
         # may differ by one step at an exact rounding tie)
         back = hy_codec.decompress_kv_tensor(hy_codec.compress_kv_tensor(x, case.layer, name)[0], x.dtype, "cuda")
