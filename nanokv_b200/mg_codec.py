@@ -3,7 +3,7 @@
 Same function names, argument meaning, payload dictionaries and error classes
 as the reference module MGM/nanokv_codec.py (encode_tensor :334-365,
 decode_tensor :369-390, decode_value :516-539, concat_values :600-609,
-value_shape :489-513, payload_bytes :697-704), so its call sites in the
+value_shape :489-513, payload_bytes :697-704, preload_operator_weights :258-279), so its call sites in the
 backbone (MGM/wan_video_dit.py:493-500,710-795) can import this module
 instead.  Operators come from `register_operator`, or -- when nothing is
 registered for a (kind, layer) -- from the reference's artefact files named by
@@ -111,6 +111,26 @@ def _operator(kind: str, layer: int, device) -> Operator:
                        "MG35_KVCODEC_DECODER_DIR_V names its artefacts")
     _OPERATORS[(kind, int(layer), str(device))] = loaded
     return loaded
+
+
+@torch.no_grad()
+def preload_operator_weights(device) -> None:
+    """Make every operator of the prepacked file resident before the timed rollout
+    (MGM/nanokv_codec.py:258-279): the file named by MG35_KVCODEC_PREPACKED_OPERATOR_PATH is read
+    once and each entry expanded to its bf16 form on `device`.  Same errors as there for a missing
+    variable or a file of another format; the provenance checks stay with the caller."""
+    path = os.environ.get("MG35_KVCODEC_PREPACKED_OPERATOR_PATH", "").strip()
+    if not path:
+        raise RuntimeError("formal worldplay_method requires MG35_KVCODEC_PREPACKED_OPERATOR_PATH")
+    payload = torch.load(path, map_location="cpu", weights_only=True)
+    if payload.get("format") != "mg35_worldplay_operator_int8_v1":
+        raise RuntimeError(f"bad prepacked WorldPlay operator: {path}")
+    device = torch.device(device)
+    for name in sorted(payload["entries"]):
+        kind, layer = name.split(":", 1)
+        entry = payload["entries"][name]
+        _OPERATORS[(kind, int(layer), str(device))] = Operator.from_int8(
+            entry["mean"].float(), entry["encoder"], entry["decoder"], device=device)
 
 
 def _clusters() -> int:

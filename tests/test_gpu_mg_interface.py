@@ -201,3 +201,47 @@ def test_operators_load_from_the_reference_artefact_layout(tmp_path, monkeypatch
     monkeypatch.delenv("MG35_KVCODEC_BASIS_DIR")
     with pytest.raises(KeyError):
         mg_codec.encode_tensor("k", 77, rows)
+
+
+def test_preload_operator_weights_reads_the_prepacked_file(tmp_path, monkeypatch):
+    """preload_operator_weights (MGM/nanokv_codec.py:258-279): every entry of the prepacked INT8 file
+    becomes resident; encoding then needs no other artefact and gives the bytes of the same operator
+    registered by hand."""
+    case = cases.MINI_BF16
+    data = cases.build(case)
+    layers = (41, 42)
+    for key in [k for k in mg_codec._OPERATORS if k[1] in layers or k[1] == 43]:
+        del mg_codec._OPERATORS[key]
+    entries = {}
+    for layer in layers:
+        for kind in ("k", "v"):
+            op = data[f"{kind}_op"]
+            entries[f"{kind}:{layer:02d}"] = {"mean": op["mean"].float(),
+                                              "encoder": mg_codec._pack_int8(op["encoder"].float()),
+                                              "decoder": mg_codec._pack_int8(op["decoder"].float())}
+    path = tmp_path / "operators.pt"
+    torch.save({"format": "mg35_worldplay_operator_int8_v1", "entries": entries}, path)
+    monkeypatch.delenv("MG35_KVCODEC_PREPACKED_OPERATOR_PATH", raising=False)
+    with pytest.raises(RuntimeError):
+        mg_codec.preload_operator_weights(torch.device("cuda"))
+    monkeypatch.setenv("MG35_KVCODEC_PREPACKED_OPERATOR_PATH", str(path))
+    mg_codec.preload_operator_weights(torch.device("cuda"))
+    assert all((kind, layer, "cuda") in mg_codec._OPERATORS for kind in ("k", "v") for layer in layers)
+    monkeypatch.delenv("MG35_KVCODEC_PREPACKED_OPERATOR_PATH")      # resident: the file is not needed again
+    monkeypatch.setenv("MG35_KVCODEC_C64_CLUSTERS", str(case.shape.centers))
+    monkeypatch.setenv("MG35_KVCODEC_C64_ITERS", str(case.iters))
+    rows = data["k_chunks"][0][None].cuda()
+    from nanokv_b200.codec import Operator
+    op = data["k_op"]
+    mg_codec._OPERATORS[("k", 43, "cuda")] = Operator.from_int8(
+        op["mean"].float(), mg_codec._pack_int8(op["encoder"].float()), mg_codec._pack_int8(op["decoder"].float()))
+    loaded = mg_codec.encode_tensor("k", 41, rows)
+    by_hand = dict(mg_codec.encode_tensor("k", 43, rows))
+    a = mg_codec.decode_tensor(loaded, dtype=torch.bfloat16, device="cuda")
+    b = mg_codec.decode_tensor(dict(loaded, layer=43), dtype=torch.bfloat16, device="cuda")
+    assert torch.equal(a, b) and by_hand["packed_codes"].shape == loaded["packed_codes"].shape
+    bad = tmp_path / "bad.pt"
+    torch.save({"format": "something else", "entries": {}}, bad)
+    monkeypatch.setenv("MG35_KVCODEC_PREPACKED_OPERATOR_PATH", str(bad))
+    with pytest.raises(RuntimeError):
+        mg_codec.preload_operator_weights(torch.device("cuda"))
