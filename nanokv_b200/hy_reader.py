@@ -20,16 +20,24 @@ neighbouring quartets form one 8-wide (component, quartet) block, the layout the
 transform works on; queries, read matrices, centre tables and the lift are permuted alike, so the
 permutation cancels in every product.  ``recent_native_frames > 0`` (a second, full-width history
 partition) is not built: the call raises.
+
+``compress_layer_cache`` is the write side (`compress_layer_cache` :1657-1675 with `_compress_one`
+:1457-1596 for the dictionary low-KV payload): the layer cache's raw `k_vision` / `v_vision` tensors
+become the packed payloads the reader takes.  The per-layer runtime the reference builds from its
+manifest (`_device_layer`) is handed over with ``register_runtime``.
 """
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
 from . import attention, ops
+from .codec import kmeans_init_rows
 
 _PREPARED: dict = {}
+_RUNTIMES: dict = {}
 
 
 def projection_matrices(viewmats: torch.Tensor, Ks: torch.Tensor | None):
@@ -217,3 +225,99 @@ def attend_dictionary_lowkv(layer_idx, q_pre_bshd, query_bhsd, current_key_bhsd,
         merged, _ = ops.lse_merge([(native.float(), native_lse), (lifted, low_lse)])
         outputs.append(merged.to(dtype).reshape(1, queries, heads * prepared["native"]))
     return outputs[0], outputs[1]
+
+
+# --------------------------------------------------------------------------------- write side
+def register_runtime(layer_idx: int, runtime: dict) -> None:
+    """The runtime of one layer as the reference's `_device_layer` returns it: ``operators`` (per
+    target ``mean`` f32 [2048] and ``encoder`` bf16 [r, 2048]), ``attention`` (the reader state with
+    `k_main_anchor_reduce` / `main_indices`, `q_prope_mix` or `k_prope_anchor_mix`,
+    `v_main_anchor_reduce`, `v_prope_anchor_mix`), ``main_k_mode``, ``shape``
+    (k_heads, k_dim, v_heads, v_dim), ``payload_mode`` = "dictionary_lowkv"."""
+    if runtime.get("payload_mode", "dictionary_lowkv") != "dictionary_lowkv":
+        raise NotImplementedError("only the dictionary low-KV payload is built")
+    if runtime.get("grouped_attention") is not None:
+        raise NotImplementedError("grouped head widths are not built")
+    _RUNTIMES[int(layer_idx)] = runtime
+
+
+def _quartet_reduce(native: torch.Tensor, mix: torch.Tensor) -> torch.Tensor:
+    """[B, H, n, 128] -> [B, H, n, 4 * quartets]: the 32 quartets of a head row mixed per component
+    (`_quartet_reduce_runtime` :1191-1193)."""
+    quartets = native.float().reshape(*native.shape[:-1], 32, 4)
+    return torch.einsum("hro,bhnoc->bhnrc", mix.float(), quartets).flatten(-2)
+
+
+@torch.no_grad()
+def _compress_one(x: torch.Tensor, layer_idx: int, target: str, runtime: dict) -> dict:
+    """x [1, 16, S, 128] -> the dictionary low-KV payload of one tensor (:1457-1596): online joint-head
+    C-means (HY/kv_codecs.py:116-208, residual rounded to the input dtype), encoder in bf16, INT4
+    codes against an fp32 scale with floor 1e-12, and the centre table projected once into the two
+    branches' low widths (centres + mean, per head: the Main reduce resp. the quartet mix)."""
+    if x.ndim != 4 or x.shape[0] != 1 or x.shape[1] * x.shape[3] != 2048 or x.shape[1] != 16:
+        raise ValueError(f"expected [1,16,S,128], got {tuple(x.shape)}")
+    batch, heads, sequence, dim = x.shape
+    op = runtime["operators"][target]
+    state = runtime["attention"]
+    mean = op["mean"].to(device=x.device, dtype=torch.float32).contiguous()
+    encoder = op["encoder"].to(device=x.device, dtype=torch.bfloat16).contiguous()
+    clusters = int(os.environ.get("HY_KV_CODEC_SEMANTIC_CLUSTERS", "64"))
+    iters = int(os.environ.get("HY_KV_CODEC_SEMANTIC_ITERS", "2"))
+    if clusters <= 0 or clusters > sequence or clusters > 256:
+        raise ValueError(f"semantic clusters must be in [1,min(S,256)], got {clusters}")
+    rows = x.permute(0, 2, 1, 3).reshape(sequence, heads * dim).contiguous()
+    init = kmeans_init_rows(sequence, clusters, 20260804 + int(layer_idx)).to(x.device)
+    centers, ids = ops.kmeans(rows, clusters, iters, init)
+    residual = (rows.float() - centers.float().index_select(0, ids.long())).to(x.dtype)
+    zero_center = torch.zeros(1, heads * dim, dtype=torch.bfloat16, device=x.device)
+    zero_ids = torch.zeros(sequence, dtype=torch.uint8, device=x.device)
+    coeff = ops.project(residual, zero_center, zero_ids, mean, encoder)          # bf16 [S, r]
+    packed, _ = ops.quant_pack(coeff, eps=1e-12, in_coeff_dtype=False)
+    amax = coeff.float().abs().amax(dim=-1, keepdim=True).clamp_min(1e-12)
+    scale = (amax / torch.full_like(amax, 7.0)).reshape(batch, sequence, 1)      # the fp32 scale the codes used
+    native = (centers.float() + mean[None]).reshape(batch, clusters, heads, dim).permute(0, 2, 1, 3)
+    to = lambda name: state[name].to(x.device)
+    if target == "k":
+        if runtime.get("main_k_mode", "learned_rope") == "learned_rope":
+            centre_main = torch.einsum("bhnr,hdr->bhnd", native, to("k_main_anchor_reduce").float())
+        else:
+            index = to("main_indices")
+            centre_main = torch.gather(native, -1, index[None, :, None].expand(batch, -1, native.shape[2], -1))
+        mix = to("k_prope_anchor_mix") if "k_prope_anchor_mix" in state else to("q_prope_mix")
+        centre_prope = _quartet_reduce(native, mix)
+    else:
+        centre_main = torch.einsum("bhco,hdo->bhcd", native, to("v_main_anchor_reduce").float())
+        centre_prope = _quartet_reduce(native, to("v_prope_anchor_mix"))
+    k_heads, k_dim, v_heads, v_dim = runtime["shape"]
+    kv_heads, head_dim = (k_heads, k_dim) if target == "k" else (v_heads, v_dim)
+    return {
+        "direct_codec_latent": True, "layer_idx": int(layer_idx), "tensor_name": target,
+        "shape": tuple(int(v) for v in x.shape),
+        "latent_int4": packed.reshape(-1), "latent_shape": (batch, sequence, int(encoder.shape[0])),
+        "latent_numel": batch * sequence * int(encoder.shape[0]), "latent_scale": scale,
+        "centre_latent": None, "centre_main": centre_main.to(torch.bfloat16),
+        "centre_prope": centre_prope.to(torch.bfloat16), "semantic_ids": ids[None].to(torch.uint8),
+        "kv_heads": kv_heads, "head_dim": head_dim, "payload_mode": "dictionary_lowkv",
+    }
+
+
+def compress_layer_cache(layer_cache: dict, layer_idx: int) -> dict:
+    """Replace the raw `k_vision` / `v_vision` history of a layer cache by packed payloads (:1657-1675).
+    A layer without a registered runtime is left alone, as a layer outside the manifest is there."""
+    runtime = _RUNTIMES.get(int(layer_idx))
+    if runtime is None:
+        return layer_cache
+    if int(runtime.get("recent_native_frames", 0)) > 0:
+        raise NotImplementedError("the recent-native history partition is not built")
+    first, second = layer_cache.get("k_vision"), layer_cache.get("v_vision")
+    if not isinstance(first, torch.Tensor):
+        raise RuntimeError("direct codec-latent compression must run before the formal codec")
+    if not isinstance(second, torch.Tensor):
+        raise RuntimeError("direct codec-latent compression requires raw V history")
+    layer_cache.pop("_direct_codec_positioned_history", None)
+    layer_cache.pop("_direct_codec_recent_native_pre", None)
+    layer_cache["k_vision"] = _compress_one(first, layer_idx, "k", runtime)
+    layer_cache["v_vision"] = _compress_one(second, layer_idx, "v", runtime)
+    layer_cache["direct_codec_latent"] = True
+    return layer_cache
+

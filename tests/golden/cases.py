@@ -333,3 +333,30 @@ def build_hy() -> dict:
 HY_CODEC = CodecCase("hy_codec_bf16", Shape("hy_codec", 16, 128, 128, 16, 200, 8, "bf16"), (200,),
                      layer=4, seed=31, mean_std=0.05)
 
+HY_WRITE = dict(heads=16, head_dim=128, rank=64, centres=16, tokens=160, main_width=32, prope_quartets=8, layer=6)
+
+
+def build_hy_write() -> dict:
+    """Raw K / V history of one HY layer, its codec operators and the reader state the write side
+    projects the centre tables with, seeded."""
+    cfg = HY_WRITE
+    gen = synthetic.generator(6101)
+    H, D, r, C, S = (cfg[k] for k in ("heads", "head_dim", "rank", "centres", "tokens"))
+    dm, quartets = cfg["main_width"], cfg["prope_quartets"]
+    shape = Shape("hy_write", H, D, r, C, S, 8, "bf16")
+    pairs = torch.stack([torch.randperm(D // 2, generator=gen)[:dm // 2].sort().values for _ in range(H)])
+    out = {"operators": {}, "attention": {
+        "main_indices": torch.stack((2 * pairs, 2 * pairs + 1), dim=2).reshape(H, dm),
+        "k_main_anchor_reduce": torch.randn(H, dm, D, generator=gen) / math.sqrt(D),
+        "q_prope_mix": torch.randn(H, quartets, D // 4, generator=gen) / math.sqrt(D // 4),
+        "v_main_anchor_reduce": torch.randn(H, dm, D, generator=gen) / math.sqrt(D),
+        "v_prope_anchor_mix": torch.randn(H, quartets, D // 4, generator=gen) / math.sqrt(D // 4),
+    }}
+    for name in ("k", "v"):
+        centers = synthetic.make_centers(shape, gen)
+        rows = synthetic.make_rows(S, centers, gen, dtype=torch.bfloat16)
+        out[f"{name}_vision"] = rows.reshape(1, S, H, D).permute(0, 2, 1, 3).contiguous()
+        op = synthetic.make_operator(shape, gen, mean_std=0.05)
+        out["operators"][name] = {"mean": op["mean"], "encoder": op["encoder"]}
+    return out
+

@@ -528,6 +528,37 @@ def run_hy_codec_case(case: cases.CodecCase, root) -> dict:
     return out
 
 
+def hy_write_runtime(data: dict) -> dict:
+    cfg = cases.HY_WRITE
+    return {"operators": data["operators"], "attention": data["attention"], "payload_mode": "dictionary_lowkv",
+            "main_k_mode": "learned_rope", "recent_native_frames": 0,
+            "shape": (cfg["heads"], cfg["head_dim"], cfg["heads"], cfg["head_dim"])}
+
+
+def run_hy_write_case(root) -> dict:
+    """_compress_one of HY-WorldPlay's direct latent attention module (the body of compress_layer_cache)
+    on raw [1, 16, S, 128] history: packed codes, fp32 scales, ids and the two branches' centre tables."""
+    hy = ref_import.load_hy_reader(root)
+    cfg = cases.HY_WRITE
+    for name in list(os.environ):
+        if name.startswith("HY_KV_CODEC") or name.startswith("HY_DIRECT_CODEC"):
+            os.environ.pop(name)
+    os.environ.update({"HY_KV_CODEC_SEMANTIC_CLUSTERS": str(cfg["centres"]), "HY_KV_CODEC_SEMANTIC_ITERS": "2",
+                       "HY_KV_CODEC_DETERMINISTIC_CENTERS": "1", "HY_KV_CODEC_PROFILE": "0"})
+    data = cases.build_hy_write()
+    runtime = hy_write_runtime(data)
+    out = {}
+    for name in ("k", "v"):
+        payload = hy._compress_one(data[f"{name}_vision"], cfg["layer"], name, runtime)
+        out[f"{name}_packed"] = payload["latent_int4"].numpy()
+        out[f"{name}_scale"] = payload["latent_scale"].numpy()
+        out[f"{name}_ids"] = payload["semantic_ids"].numpy()
+        out[f"{name}_centre_main"] = bits(payload["centre_main"])
+        out[f"{name}_centre_prope"] = bits(payload["centre_prope"])
+        out[f"{name}_digest"] = np.array([checksum(data[f"{name}_vision"])], dtype=np.uint64)
+    return out
+
+
 def run_protected_tokens_case(root) -> dict:
     """protected_tokens of the MG core module on seeded frame-id sequences."""
     core = ref_import.load_mg_core(root)
@@ -615,6 +646,7 @@ def main() -> None:
     save("attend_lb_bf16", lambda: run_attend_case(cases.ROLLING, root))
     save("hy_two_branch_bf16", lambda: run_hy_case(root))
     save(cases.HY_CODEC.name, lambda: run_hy_codec_case(cases.HY_CODEC, root))
+    save("hy_write_bf16", lambda: run_hy_write_case(root))
     save("protected_tokens", lambda: run_protected_tokens_case(root))
     save("merge_edge", lambda: run_merge_case(root))
     save("select_mg_bf16", lambda: run_select_case(cases.MINI_BF16, root))

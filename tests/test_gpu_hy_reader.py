@@ -71,3 +71,53 @@ def test_projection_matrices_match_the_closed_forms():
     P, _, P_inv = hy_reader.projection_matrices(view, Ks)
     assert torch.allclose(P @ P_inv, torch.eye(4).expand(1, 3, 4, 4), atol=1e-5)
     assert torch.allclose(P[..., 0, :], 1.3 * view[..., 0, :], atol=1e-6)
+
+
+def write_runtime(data):
+    cfg = cases.HY_WRITE
+    return {"operators": data["operators"], "attention": data["attention"], "payload_mode": "dictionary_lowkv",
+            "main_k_mode": "learned_rope", "recent_native_frames": 0,
+            "shape": (cfg["heads"], cfg["head_dim"], cfg["heads"], cfg["head_dim"])}
+
+
+def test_compress_layer_cache_against_the_reference_fixture(monkeypatch):
+    """The write side (`compress_layer_cache` / `_compress_one` of the reference module): packed codes,
+    fp32 scales and ids as the reference made them, the branches' centre tables within a bf16 step."""
+    cfg = cases.HY_WRITE
+    gold, data = load("hy_write_bf16"), cases.build_hy_write()
+    monkeypatch.setenv("HY_KV_CODEC_SEMANTIC_CLUSTERS", str(cfg["centres"]))
+    monkeypatch.setenv("HY_KV_CODEC_SEMANTIC_ITERS", "2")
+    hy_reader.register_runtime(cfg["layer"], write_runtime(data))
+    cache = {"k_vision": data["k_vision"].cuda(), "v_vision": data["v_vision"].cuda(), "vision_thw": (1, 1, 1),
+             "_direct_codec_positioned_history": object()}
+    out = hy_reader.compress_layer_cache(cache, cfg["layer"])
+    assert out is cache and cache["direct_codec_latent"] and "_direct_codec_positioned_history" not in cache
+    flips = 0
+    for name in ("k", "v"):
+        payload = cache[f"{name}_vision"]
+        S, r = cfg["tokens"], cfg["rank"]
+        assert payload["shape"] == (1, 16, S, 128) and payload["latent_shape"] == (1, S, r)
+        assert payload["payload_mode"] == "dictionary_lowkv" and payload["tensor_name"] == name
+        assert np.array_equal(payload["semantic_ids"].cpu().numpy(), gold[f"{name}_ids"])
+        assert payload["latent_scale"].dtype == torch.float32
+        assert np.array_equal(payload["latent_scale"].cpu().numpy(), gold[f"{name}_scale"])
+        got, _ = None, None
+        got = torch.from_numpy(gold[f"{name}_packed"])
+        mine = payload["latent_int4"].cpu()
+        assert mine.shape == got.shape
+        lo = (mine & 15).int() - (got & 15).int()
+        hi = (mine >> 4).int() - (got >> 4).int()
+        assert int(lo.abs().max()) <= 1 and int(hi.abs().max()) <= 1
+        flips += int(lo.abs().sum() + hi.abs().sum())
+        for table in ("centre_main", "centre_prope"):
+            want = from_bits(gold[f"{name}_{table}"], torch.bfloat16)
+            assert payload[table].shape == want.shape and payload[table].dtype == torch.bfloat16
+            assert rel_err(payload[table].cpu(), want) <= 2.0 ** -7
+    print(f"code flips against the reference: {flips}")
+    assert flips <= 4
+    again = hy_reader.compress_layer_cache(dict(k_vision=data["k_vision"].cuda(), v_vision=data["v_vision"].cuda()), 99)
+    assert isinstance(again["k_vision"], torch.Tensor)            # no runtime for that layer: left alone
+    with pytest.raises(RuntimeError):
+        hy_reader.compress_layer_cache(cache, cfg["layer"])       # already compressed
+    with pytest.raises(NotImplementedError):
+        hy_reader.register_runtime(3, dict(write_runtime(data), grouped_attention=[{}]))
