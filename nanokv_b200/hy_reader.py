@@ -321,3 +321,19 @@ def compress_layer_cache(layer_cache: dict, layer_idx: int) -> dict:
     layer_cache["direct_codec_latent"] = True
     return layer_cache
 
+
+def attend(layer_idx: int, q_pre_bshd, query_bhsd, current_key_bhsd, current_value_bhsd, encoder_key_bhsd,
+           encoder_value_bhsd, layer_cache: dict, current_freqs_cis, current_viewmats, current_Ks):
+    """The reference's public entry point (`attend` :4251-4279) for the dictionary low-KV runtime: the
+    layer's registered runtime, the same two checks, then `attend_dictionary_lowkv`."""
+    if not layer_cache.get("direct_codec_latent"):
+        raise RuntimeError("selected direct layer is missing a direct latent payload")
+    if query_bhsd.shape[0] != 2 * q_pre_bshd.shape[0]:
+        raise RuntimeError("direct codec attention expects stacked main/PRoPE batches")
+    runtime = _RUNTIMES.get(int(layer_idx))
+    if runtime is None:
+        raise KeyError(f"no runtime registered for layer {int(layer_idx)}")
+    return attend_dictionary_lowkv(layer_idx, q_pre_bshd, query_bhsd, current_key_bhsd, current_value_bhsd,
+                                   encoder_key_bhsd, encoder_value_bhsd, layer_cache, current_freqs_cis,
+                                   current_viewmats, current_Ks, runtime)
+

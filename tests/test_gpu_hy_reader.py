@@ -52,6 +52,25 @@ def test_two_branch_reader_against_the_reference_fixture():
         0, cuda("q_pre"), cuda("query"), cuda("current_key"), cuda("current_value"), cuda("encoder_key"),
         cuda("encoder_value"), cache, data["current_freqs"], data["current_viewmats"], None, runtime)
     assert torch.equal(again, main)
+    # the public entry point: the runtime registered per layer, the reference's two checks
+    hy_reader.register_runtime(11, dict(runtime, payload_mode="dictionary_lowkv"))
+    with pytest.raises(RuntimeError):
+        hy_reader.attend(11, cuda("q_pre"), cuda("query"), cuda("current_key"), cuda("current_value"),
+                         cuda("encoder_key"), cuda("encoder_value"), cache, data["current_freqs"],
+                         data["current_viewmats"], None)          # the cache is not marked as compressed
+    marked = dict(cache, direct_codec_latent=True)
+    public, _ = hy_reader.attend(11, cuda("q_pre"), cuda("query"), cuda("current_key"), cuda("current_value"),
+                                 cuda("encoder_key"), cuda("encoder_value"), marked, data["current_freqs"],
+                                 data["current_viewmats"], None)
+    assert torch.equal(public, main)
+    with pytest.raises(RuntimeError):
+        hy_reader.attend(11, cuda("q_pre"), cuda("query")[:1], cuda("current_key"), cuda("current_value"),
+                         cuda("encoder_key"), cuda("encoder_value"), marked, data["current_freqs"],
+                         data["current_viewmats"], None)
+    with pytest.raises(KeyError):
+        hy_reader.attend(12, cuda("q_pre"), cuda("query"), cuda("current_key"), cuda("current_value"),
+                         cuda("encoder_key"), cuda("encoder_value"), marked, data["current_freqs"],
+                         data["current_viewmats"], None)
     with pytest.raises(NotImplementedError):
         hy_reader.attend_dictionary_lowkv(
             0, cuda("q_pre"), cuda("query"), cuda("current_key"), cuda("current_value"), cuda("encoder_key"),
