@@ -360,3 +360,59 @@ def build_hy_write() -> dict:
         out["operators"][name] = {"mean": op["mean"], "encoder": op["encoder"]}
     return out
 
+
+HY_CHAIN = dict(HY_WRITE, main_width=64, prope_quartets=16, queries=64, text=16, history_cameras=4,
+                query_cameras=2, layer=8)   # branch widths the fused read is built for (64)
+
+
+def build_hy_chain() -> dict:
+    """One HY layer end to end: raw history -> compress_layer_cache -> two-branch read, seeded."""
+    cfg = HY_CHAIN
+    gen = synthetic.generator(6201)
+    H, D, r, C, N, S, E = (cfg[k] for k in ("heads", "head_dim", "rank", "centres", "tokens", "queries", "text"))
+    dm, quartets = cfg["main_width"], cfg["prope_quartets"]
+    dp = 4 * quartets
+    bf = torch.bfloat16
+    shape = Shape("hy_chain", H, D, r, C, N, S, "bf16")
+    pairs = torch.stack([torch.randperm(D // 2, generator=gen)[:dm // 2].sort().values for _ in range(H)])
+    state = {
+        "main_indices": torch.stack((2 * pairs, 2 * pairs + 1), dim=2).reshape(H, dm),
+        "q_main_reduce": (torch.randn(H, dm, D, generator=gen) / math.sqrt(D) * 1.5).to(bf),
+        "q_prope_mix": torch.randn(H, quartets, D // 4, generator=gen) / math.sqrt(D // 4) * 1.5,
+        "k_main_read": (torch.randn(H, dm, r, generator=gen) / math.sqrt(r)).to(bf),
+        "k_prope_read": (torch.randn(H, dp, r, generator=gen) / math.sqrt(r)).to(bf),
+        "v_main_read": (torch.randn(H, dm, r, generator=gen) / math.sqrt(r)).to(bf),
+        "v_prope_read": (torch.randn(H, dp, r, generator=gen) / math.sqrt(r)).to(bf),
+        "v_main_lift": (torch.randn(H, dm, D, generator=gen) / math.sqrt(dm)).to(bf),
+        "v_prope_mix": torch.randn(H, quartets, D // 4, generator=gen) / math.sqrt(quartets),
+        "log_residual_scale_main": 0.2 * torch.randn(H, generator=gen),
+        "log_residual_scale_prope": 0.2 * torch.randn(H, generator=gen),
+        "k_main_anchor_reduce": torch.randn(H, dm, D, generator=gen) / math.sqrt(D),
+        "v_main_anchor_reduce": torch.randn(H, dm, D, generator=gen) / math.sqrt(D),
+        "v_prope_anchor_mix": torch.randn(H, quartets, D // 4, generator=gen) / math.sqrt(D // 4),
+    }
+    out = {"attention": state, "operators": {}}
+    for name in ("k", "v"):
+        centers = synthetic.make_centers(shape, gen)
+        rows = synthetic.make_rows(N, centers, gen, dtype=bf)
+        out[f"{name}_vision"] = rows.reshape(1, N, H, D).permute(0, 2, 1, 3).contiguous()
+        op = synthetic.make_operator(shape, gen, mean_std=0.05)
+        out["operators"][name] = {"mean": op["mean"], "encoder": op["encoder"]}
+    out.update({
+        "vision_freqs": _rope_tables(N, D, gen), "current_freqs": _rope_tables(S, D, gen),
+        "vision_viewmats": _se3(cfg["history_cameras"], gen), "current_viewmats": _se3(cfg["query_cameras"], gen),
+        "q_pre": torch.randn(1, S, H, D, generator=gen).to(bf),
+        "query": torch.randn(2, H, S, D, generator=gen).to(bf),
+        "current_key": torch.randn(2, H, S, D, generator=gen).to(bf),
+        "current_value": torch.randn(2, H, S, D, generator=gen).to(bf),
+        "encoder_key": torch.randn(2, H, E, D, generator=gen).to(bf),
+        "encoder_value": torch.randn(2, H, E, D, generator=gen).to(bf)})
+    return out
+
+
+def hy_chain_runtime(data: dict) -> dict:
+    cfg = HY_CHAIN
+    return {"operators": data["operators"], "attention": data["attention"], "payload_mode": "dictionary_lowkv",
+            "main_k_mode": "learned_rope", "recent_native_frames": 0,
+            "shape": (cfg["heads"], cfg["head_dim"], cfg["heads"], cfg["head_dim"])}
+

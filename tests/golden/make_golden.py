@@ -559,6 +559,33 @@ def run_hy_write_case(root) -> dict:
     return out
 
 
+def run_hy_chain_case(root) -> dict:
+    """HY-WorldPlay Fast end to end on one layer: the module's _compress_one on the raw K / V history,
+    then its _attend_dictionary_lowkv over the payloads it made (the CUDA-only _flash_lse replaced by the
+    exact fp32 attention of the Matrix-Game core module, as in the two-branch fixture)."""
+    hy = ref_import.load_hy_reader(root)
+    core = ref_import.load_mg_core(root)
+    cfg = cases.HY_CHAIN
+    for name in list(os.environ):
+        if name.startswith("HY_KV_CODEC") or name.startswith("HY_DIRECT_CODEC"):
+            os.environ.pop(name)
+    os.environ.update({"HY_KV_CODEC_SEMANTIC_CLUSTERS": str(cfg["centres"]), "HY_KV_CODEC_SEMANTIC_ITERS": "2",
+                       "HY_KV_CODEC_DETERMINISTIC_CENTERS": "1", "HY_KV_CODEC_PROFILE": "0",
+                       "HY_DIRECT_CODEC_LATENT_READ_CACHE": "0"})
+    hy._flash_lse = lambda q, k, v, scale=None: core.attention_lse(q, k, v, scale=scale)
+    data = cases.build_hy_chain()
+    runtime = cases.hy_chain_runtime(data)
+    cache = {"vision_freqs_cis": data["vision_freqs"], "vision_viewmats": data["vision_viewmats"], "vision_Ks": None}
+    for name in ("k", "v"):
+        cache[f"{name}_vision"] = hy._compress_one(data[f"{name}_vision"], cfg["layer"], name, runtime)
+    main, prope = hy._attend_dictionary_lowkv(
+        cfg["layer"], data["q_pre"], data["query"], data["current_key"], data["current_value"], data["encoder_key"],
+        data["encoder_value"], cache, data["current_freqs"], data["current_viewmats"], None, runtime)
+    return {"main": bits(main[:, ::4]), "prope": bits(prope[:, ::4]),
+            "k_ids": cache["k_vision"]["semantic_ids"].numpy(),
+            "q_digest": np.array([checksum(data["q_pre"])], dtype=np.uint64)}
+
+
 def run_protected_tokens_case(root) -> dict:
     """protected_tokens of the MG core module on seeded frame-id sequences."""
     core = ref_import.load_mg_core(root)
@@ -647,6 +674,7 @@ def main() -> None:
     save("hy_two_branch_bf16", lambda: run_hy_case(root))
     save(cases.HY_CODEC.name, lambda: run_hy_codec_case(cases.HY_CODEC, root))
     save("hy_write_bf16", lambda: run_hy_write_case(root))
+    save("hy_chain_bf16", lambda: run_hy_chain_case(root))
     save("protected_tokens", lambda: run_protected_tokens_case(root))
     save("merge_edge", lambda: run_merge_case(root))
     save("select_mg_bf16", lambda: run_select_case(cases.MINI_BF16, root))

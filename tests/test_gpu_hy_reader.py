@@ -140,3 +140,25 @@ def test_compress_layer_cache_against_the_reference_fixture(monkeypatch):
         hy_reader.compress_layer_cache(cache, cfg["layer"])       # already compressed
     with pytest.raises(NotImplementedError):
         hy_reader.register_runtime(3, dict(write_runtime(data), grouped_attention=[{}]))
+
+
+def test_write_then_read_of_one_layer_against_the_reference_chain(monkeypatch):
+    """compress_layer_cache followed by attend on the payloads it made, against the reference's
+    _compress_one + _attend_dictionary_lowkv on the same raw history and queries."""
+    cfg = cases.HY_CHAIN
+    gold, data = load("hy_chain_bf16"), cases.build_hy_chain()
+    monkeypatch.setenv("HY_KV_CODEC_SEMANTIC_CLUSTERS", str(cfg["centres"]))
+    monkeypatch.setenv("HY_KV_CODEC_SEMANTIC_ITERS", "2")
+    hy_reader.register_runtime(cfg["layer"], cases.hy_chain_runtime(data))
+    cache = {"k_vision": data["k_vision"].cuda(), "v_vision": data["v_vision"].cuda(),
+             "vision_freqs_cis": data["vision_freqs"], "vision_viewmats": data["vision_viewmats"], "vision_Ks": None}
+    hy_reader.compress_layer_cache(cache, cfg["layer"])
+    assert np.array_equal(cache["k_vision"]["semantic_ids"].cpu().numpy(), gold["k_ids"])
+    cuda = lambda name: data[name].cuda()
+    main, prope = hy_reader.attend(
+        cfg["layer"], cuda("q_pre"), cuda("query"), cuda("current_key"), cuda("current_value"), cuda("encoder_key"),
+        cuda("encoder_value"), cache, data["current_freqs"], data["current_viewmats"], None)
+    ops.check_status()
+    assert main.shape == prope.shape == (1, cfg["queries"], cfg["heads"] * cfg["head_dim"])
+    assert rel_err(main[:, ::4].cpu(), from_bits(gold["main"], torch.bfloat16)) <= BF16_REL_TOL
+    assert rel_err(prope[:, ::4].cpu(), from_bits(gold["prope"], torch.bfloat16)) <= BF16_REL_TOL
