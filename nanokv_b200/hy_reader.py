@@ -17,7 +17,8 @@ quartet lift, the final combine) stays fp32 here.
 
 The PRoPE branch's low-width channels are stored permuted inside the prepared state so that two
 neighbouring quartets form one 8-wide (component, quartet) block, the layout the kernel's camera
-transform works on; queries, read matrices, centre tables and the lift are permuted alike, so the
+transform works on (branches narrower than the kernel's 64 columns -- HY's deployed heads are 32 wide -- are
+padded with zero channels first); queries, read matrices, centre tables and the lift are permuted alike, so the
 permutation cancels in every product.  ``recent_native_frames > 0`` (a second, full-width history
 partition) is not built: the call raises.
 
@@ -69,6 +70,24 @@ def _block_order(width: int, device) -> torch.Tensor:
     return (2 * block + inside % 2) * 4 + inside // 2
 
 
+def _kernel_width(width: int) -> int:
+    """The fused read is built for head widths 64 and 128: a narrower branch (HY's deployed heads are 32
+    wide) is padded with zero channels, which add nothing to a score and give zero output columns."""
+    if width <= 64:
+        return 64
+    if width <= 128:
+        return 128
+    raise ValueError(f"branch width {width} exceeds 128")
+
+
+def _pad_rows(tensor: torch.Tensor, width: int) -> torch.Tensor:      # [H, d, X] -> [H, width, X]
+    return torch.nn.functional.pad(tensor, (0, 0, 0, width - tensor.shape[1]))
+
+
+def _pad_cols(tensor: torch.Tensor, width: int) -> torch.Tensor:      # [..., d] -> [..., width]
+    return torch.nn.functional.pad(tensor, (0, width - tensor.shape[-1]))
+
+
 def _prepare(state: dict, device, dtype):
     """Device-resident operands of both branches in the kernels' layouts, cached per state dict."""
     key = (id(state), str(device), dtype)
@@ -78,35 +97,38 @@ def _prepare(state: dict, device, dtype):
     heads, main_width, native = state["q_main_reduce"].shape
     quartets = state["q_prope_mix"].shape[1]
     prope_width = 4 * quartets
-    if prope_width % 8 or native % 4:
-        raise ValueError("the PRoPE branch needs an even number of quartets")
-    order = _block_order(prope_width, device)
+    if native % 4 or main_width % 2:
+        raise ValueError("branch widths must hold whole pairs and quartets")
+    main_pad, prope_pad = _kernel_width(main_width), _kernel_width(prope_width)
+    order = _block_order(prope_pad, device)      # over the padded width: the added quartets are zero
     eye = torch.eye(4, device=device)
     # quartet mixes as dense per-head matrices: reduce [H, native, 4q], lift [H, 4q, native]
     reduce = torch.einsum("hro,cd->hocrd", state["q_prope_mix"].to(device).float(), eye)
-    reduce = reduce.reshape(heads, native, prope_width).index_select(2, order)
+    reduce = _pad_cols(reduce.reshape(heads, native, prope_width), prope_pad).index_select(2, order)
     lift = torch.einsum("hro,cd->hrcod", state["v_prope_mix"].to(device).float(), eye)
-    lift = lift.reshape(heads, prope_width, native).index_select(1, order)
+    lift = _pad_rows(lift.reshape(heads, prope_width, native), prope_pad).index_select(1, order)
     indices = state["main_indices"].long().cpu()
     if not torch.equal(indices[:, 1::2], indices[:, ::2] + 1) or bool((indices[:, ::2] % 2).any()):
         raise ValueError("RoPE mapping must retain complete original pairs")
     prepared = {
         "heads": heads, "main_width": main_width, "prope_width": prope_width, "native": native,
+        "main_pad": main_pad, "prope_pad": prope_pad,
         "order": order, "indices": state["main_indices"].long().to(device),
-        "pair_index": (indices[:, ::2] // 2).to(torch.int32).to(device).contiguous(),
-        "q_main": state["q_main_reduce"].to(**to).transpose(1, 2).contiguous(),
+        # the padded pairs rotate zeros: any table column will do
+        "pair_index": _pad_cols((indices[:, ::2] // 2).to(torch.int32), main_pad // 2).to(device).contiguous(),
+        "q_main": _pad_cols(state["q_main_reduce"].to(**to).transpose(1, 2), main_pad).contiguous(),
         "q_prope": reduce.contiguous(),
-        "k_main": state["k_main_read"].to(**to).contiguous(),
-        "v_main": state["v_main_read"].to(**to).contiguous(),
-        "k_prope": state["k_prope_read"].to(**to).index_select(1, order).contiguous(),
-        "v_prope": state["v_prope_read"].to(**to).index_select(1, order).contiguous(),
-        "lift_main": state["v_main_lift"].to(**to).contiguous(),
+        "k_main": _pad_rows(state["k_main_read"].to(**to), main_pad).contiguous(),
+        "v_main": _pad_rows(state["v_main_read"].to(**to), main_pad).contiguous(),
+        "k_prope": _pad_rows(state["k_prope_read"].to(**to), prope_pad).index_select(1, order).contiguous(),
+        "v_prope": _pad_rows(state["v_prope_read"].to(**to), prope_pad).index_select(1, order).contiguous(),
+        "lift_main": _pad_rows(state["v_main_lift"].to(**to), main_pad).contiguous(),
         "lift_prope": lift.contiguous(),
         "scale_main": state["log_residual_scale_main"].to(device).float().exp(),
         "scale_prope": state["log_residual_scale_prope"].to(device).float().exp(),
-        "zero_main": torch.zeros(heads, main_width, device=device),
-        "zero_prope": torch.zeros(heads, prope_width, device=device),
-        "cam_index": torch.zeros(heads, prope_width // 8, dtype=torch.int32, device=device),
+        "zero_main": torch.zeros(heads, main_pad, device=device),
+        "zero_prope": torch.zeros(heads, prope_pad, device=device),
+        "cam_index": torch.zeros(heads, prope_pad // 8, dtype=torch.int32, device=device),
     }
     _PREPARED[key] = prepared
     return prepared
@@ -134,8 +156,8 @@ def _history_views(payload: dict, prepared: dict, device):
                                centers=rows.reshape(centres, -1).contiguous(), seg_start=seg_start,
                                seg_center_row=seg_row, tokens=tokens, segments=1, rank=rank, group=rank)
 
-    prope_table = payload["centre_prope"].to(device).index_select(3, prepared["order"])
-    views = (view(payload["centre_main"]), view(prope_table))
+    prope_table = _pad_cols(payload["centre_prope"].to(device), prepared["prope_pad"]).index_select(3, prepared["order"])
+    views = (view(_pad_cols(payload["centre_main"].to(device), prepared["main_pad"])), view(prope_table))
     payload["_nkv_views"] = ((str(device), id(prepared)), views)
     return views
 
@@ -188,6 +210,7 @@ def attend_dictionary_lowkv(layer_idx, q_pre_bshd, query_bhsd, current_key_bhsd,
         q_main = _multiplier(current_freqs_cis, device).rotate(q_main, now, prepared["pair_index"])
     else:
         q_main = torch.gather(_rows(query_bhsd[0]), -1, prepared["indices"][None].expand(queries, -1, -1))
+        q_main = _pad_cols(q_main, prepared["main_pad"])
     q_main = (q_main * prepared["scale_main"][None, :, None]).to(dtype)
     # ---- PRoPE query: quartet reduction and P^T in fp32, as the reference keeps them
     _, p_transpose, _ = projection_matrices(current_viewmats.to(device), None if current_Ks is None

@@ -361,8 +361,7 @@ def build_hy_write() -> dict:
     return out
 
 
-HY_CHAIN = dict(HY_WRITE, main_width=64, prope_quartets=16, queries=64, text=16, history_cameras=4,
-                query_cameras=2, layer=8)   # branch widths the fused read is built for (64)
+HY_CHAIN = dict(HY_WRITE, queries=64, text=16, history_cameras=4, query_cameras=2, layer=8)   # 32-wide branches
 
 
 def build_hy_chain() -> dict:
